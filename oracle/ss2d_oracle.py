@@ -1,0 +1,279 @@
+"""CPU oracle for the SS2D core of VMamba -- TEST INFRASTRUCTURE, NOT A PRODUCT PATH.
+
+This file restates, in plain numpy, the reference's pure-torch algorithm for the
+SS2D hot path so that the CUDA kernels can be checked against it on machines where
+the reference itself is not present.  Only tests, the smoke check and the
+`cpu_baseline` / `--impl reference` legs of the benchmark may import it; the
+package `vmamba_b200` never does.
+
+Parity status: PINNED.  Every function here is compared (tests/test_oracle_golden.py)
+against outputs of the unmodified reference (root `vmamba.py`, imported on CPU)
+stored under tests/golden/ by tests/golden/make_golden.py.
+
+Reference anchors (paths inside MzeroMiko/VMamba):
+  cross_scan        vmamba.py:41-84    (cross_scan_fwd,  channel-first branch)
+  cross_merge       vmamba.py:87-130   (cross_merge_fwd, channel-first branch)
+  selective_scan    vmamba.py:791-834  (selective_scan_torch) == classification/models/csms6s.py:25-68
+  layer_norm_cf     vmamba.py:1078-1093 (LayerNorm with channel_first=True)
+  ss2d_core         vmamba.py:1504-1571 (SS2Dv2.forward_corev2, no_einsum/conv1d form)
+  dt/A/D init       vmamba.py:1170-1237 (mamba_init)
+
+Arrays are float32 numpy arrays.  bf16 is represented as float32 values that have
+been rounded to the bf16 grid with `round_bf16` (numpy has no bf16 type).
+"""
+from __future__ import annotations
+
+import math
+import numpy as np
+
+K_ROUTES = 4
+
+
+# --------------------------------------------------------------------------- #
+# dtype helpers
+# --------------------------------------------------------------------------- #
+def round_bf16(a: np.ndarray) -> np.ndarray:
+    """Round float32 values to the nearest bfloat16 (ties to even), return float32."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    u = a.view(np.uint32).astype(np.uint64)
+    lsb = (u >> 16) & 1
+    r = ((u + 0x7FFF + lsb) >> 16) << 16
+    out = r.astype(np.uint32).view(np.float32).reshape(a.shape).copy()
+    nan = np.isnan(a)
+    if nan.any():
+        out[nan] = np.nan
+    return out
+
+
+def round_f16(a: np.ndarray) -> np.ndarray:
+    return np.asarray(a, dtype=np.float32).astype(np.float16).astype(np.float32)
+
+
+def _round_to(a: np.ndarray, dtype: str) -> np.ndarray:
+    if dtype in ("f32", "fp32", "float32"):
+        return np.asarray(a, dtype=np.float32)
+    if dtype in ("bf16", "bfloat16"):
+        return round_bf16(a)
+    if dtype in ("f16", "fp16", "float16"):
+        return round_f16(a)
+    raise ValueError(f"unknown dtype tag {dtype!r}")
+
+
+# --------------------------------------------------------------------------- #
+# a1: CrossScan  (vmamba.py:41-84)
+# --------------------------------------------------------------------------- #
+def cross_scan(x: np.ndarray, scans: int = 0) -> np.ndarray:
+    """(B, C, H, W) -> (B, 4, C, H*W).
+
+    scans=0: route 0 row-major, route 1 column-major, routes 2/3 the same reversed
+             (vmamba.py:45-49).
+    scans=1: the row-major sequence repeated four times (vmamba.py:50-51).
+    scans=2: row-major twice, then its reversal twice (vmamba.py:52-54).
+    scans=3: row-major sequences of the map rotated by 0/90/180/270 degrees
+             (vmamba.py:55-60).
+    """
+    B, C, H, W = x.shape
+    L = H * W
+    y = np.empty((B, 4, C, L), dtype=x.dtype)
+    if scans == 0:
+        y[:, 0] = x.reshape(B, C, L)
+        y[:, 1] = x.transpose(0, 1, 3, 2).reshape(B, C, L)
+        y[:, 2] = y[:, 0, :, ::-1]
+        y[:, 3] = y[:, 1, :, ::-1]
+    elif scans == 1:
+        y[:] = x.reshape(B, 1, C, L)
+    elif scans == 2:
+        y[:, 0] = x.reshape(B, C, L)
+        y[:, 1] = y[:, 0]
+        y[:, 2] = y[:, 0, :, ::-1]
+        y[:, 3] = y[:, 2]
+    elif scans == 3:
+        for k in range(4):
+            y[:, k] = np.rot90(x, k, axes=(2, 3)).reshape(B, C, L)
+    else:
+        raise ValueError("scans must be 0, 1, 2 or 3")
+    return y
+
+
+# --------------------------------------------------------------------------- #
+# a7: CrossMerge  (vmamba.py:87-130)
+# --------------------------------------------------------------------------- #
+def cross_merge(ys: np.ndarray, scans: int = 0) -> np.ndarray:
+    """(B, 4, C, H, W) -> (B, C, H*W); the adjoint of cross_scan.
+
+    The summation ORDER follows the reference so that fp32 results are bit-identical:
+    scans=0: (y0 + flip(y2)) + transpose((y1 + flip(y3)))  (vmamba.py:92-94)
+    scans=1: sum over the route axis, routes added in order 0,1,2,3 (vmamba.py:95-96)
+    scans=2: (y0+flip(y2)) + (y1+flip(y3))                 (vmamba.py:97-99)
+    scans=3: y0 + rot-90(y1) + rot-180(y2) + rot-270(y3)   (vmamba.py:100-105)
+    """
+    B, K, C, H, W = ys.shape
+    assert K == 4
+    L = H * W
+    y = ys.reshape(B, K, C, L)
+    if scans == 0:
+        t = y[:, 0:2] + y[:, 2:4, :, ::-1]
+        col = t[:, 1].reshape(B, C, W, H).transpose(0, 1, 3, 2).reshape(B, C, L)
+        return t[:, 0] + col
+    if scans == 1:
+        return ((y[:, 0] + y[:, 1]) + y[:, 2]) + y[:, 3]
+    if scans == 2:
+        t = y[:, 0:2] + y[:, 2:4, :, ::-1]
+        return t[:, 0] + t[:, 1]
+    if scans == 3:
+        oy = y[:, 0].copy()
+        oy = oy + np.rot90(y[:, 1].reshape(B, C, W, H), -1, axes=(2, 3)).reshape(B, C, L)
+        oy = oy + np.rot90(y[:, 2].reshape(B, C, H, W), -2, axes=(2, 3)).reshape(B, C, L)
+        oy = oy + np.rot90(y[:, 3].reshape(B, C, W, H), -3, axes=(2, 3)).reshape(B, C, L)
+        return oy
+    raise ValueError("scans must be 0, 1, 2 or 3")
+
+
+# --------------------------------------------------------------------------- #
+# a5/a6: selective scan  (vmamba.py:791-834)
+# --------------------------------------------------------------------------- #
+def softplus(x: np.ndarray) -> np.ndarray:
+    """torch.nn.functional.softplus with beta=1, threshold=20 (vmamba.py:816)."""
+    x = np.asarray(x, dtype=np.float32)
+    with np.errstate(over="ignore"):
+        sp = np.log1p(np.exp(np.minimum(x, np.float32(20.0)))).astype(np.float32)
+    return np.where(x > 20.0, x, sp).astype(np.float32)
+
+
+def selective_scan(u, delta, A, B, C, D=None, delta_bias=None, delta_softplus=True,
+                   oflex=True, dtype_in: str = "f32") -> np.ndarray:
+    """Sequential recurrence, fp32 state (vmamba.py:805-834).
+
+    u, delta: (Bt, K*Cd, L); A: (K*Cd, N); B, C: (Bt, K, N, L); D, delta_bias: (K*Cd,).
+    h_n <- exp(delta' * A_n) * h_n + delta' * B_n * u ;  y = sum_n C_n h_n (+ D u)
+    with delta' = softplus(delta + delta_bias).
+    `dtype_in` names the storage type of u/delta/B/C; with a bias the sum
+    delta + bias is formed in fp32 (the bias is fp32, vmamba.py:813-814); without one
+    the softplus runs in the storage type (vmamba.py:815-816) and is rounded to it.
+    Output fp32 when `oflex`, else rounded to `dtype_in` (vmamba.py:834).
+    """
+    u = np.asarray(u, dtype=np.float32)
+    delta = np.asarray(delta, dtype=np.float32)
+    A = np.asarray(A, dtype=np.float32)
+    B = np.asarray(B, dtype=np.float32)
+    C = np.asarray(C, dtype=np.float32)
+    Bt, K, N, L = B.shape
+    KC = u.shape[1]
+    Cd = KC // K
+    assert u.shape == (Bt, KC, L) and delta.shape == (Bt, KC, L)
+    assert A.shape == (KC, N) and C.shape == B.shape
+
+    if delta_bias is not None:
+        delta = delta + np.asarray(delta_bias, dtype=np.float32)[None, :, None]
+        if delta_softplus:
+            delta = softplus(delta)
+    elif delta_softplus:
+        delta = _round_to(softplus(delta), dtype_in)
+
+    Bx = np.repeat(B, Cd, axis=1).reshape(Bt, KC, N, L)   # (Bt, K, 1, N, L) repeated over Cd
+    Cx = np.repeat(C, Cd, axis=1).reshape(Bt, KC, N, L)
+    # note: np.repeat on axis 1 of (Bt, K, N, L) gives k-major order k0,k0,..,k1,.. == view(K,1)->repeat(Cd)
+    h = np.zeros((Bt, KC, N), dtype=np.float32)
+    y = np.empty((Bt, KC, L), dtype=np.float32)
+    for i in range(L):
+        dl = delta[:, :, i]                                   # (Bt, KC)
+        dA = np.exp(dl[:, :, None] * A[None]).astype(np.float32)
+        dBu = (dl * u[:, :, i])[:, :, None] * Bx[:, :, :, i]
+        h = dA * h + dBu
+        y[:, :, i] = np.sum(h * Cx[:, :, :, i], axis=-1, dtype=np.float32)
+    out = y if D is None else y + u * np.asarray(D, dtype=np.float32)[None, :, None]
+    out = out.astype(np.float32)
+    return out if oflex else _round_to(out, dtype_in)
+
+
+# --------------------------------------------------------------------------- #
+# a8: channel-first LayerNorm  (vmamba.py:1078-1093)
+# --------------------------------------------------------------------------- #
+def layer_norm_cf(y: np.ndarray, weight=None, bias=None, eps: float = 1e-5) -> np.ndarray:
+    """LayerNorm over axis 1 of a (B, D, ...) array (biased variance, as torch)."""
+    y = np.asarray(y, dtype=np.float32)
+    mean = y.mean(axis=1, keepdims=True, dtype=np.float32)
+    var = ((y - mean) ** 2).mean(axis=1, keepdims=True, dtype=np.float32)
+    out = (y - mean) / np.sqrt(var + np.float32(eps))
+    shp = (1, -1) + (1,) * (y.ndim - 2)
+    if weight is not None:
+        out = out * np.asarray(weight, dtype=np.float32).reshape(shp)
+    if bias is not None:
+        out = out + np.asarray(bias, dtype=np.float32).reshape(shp)
+    return out.astype(np.float32)
+
+
+# --------------------------------------------------------------------------- #
+# a1-a8 composed: SS2D core  (vmamba.py:1504-1571)
+# --------------------------------------------------------------------------- #
+def ss2d_core(x, x_proj_weight, dt_projs_weight, dt_projs_bias, A_logs, Ds,
+              out_norm_weight=None, out_norm_bias=None, *, d_state: int, dt_rank: int,
+              scans: int = 0, act_dtype: str = "f32", eps: float = 1e-5,
+              with_out_norm: bool = True, return_parts: bool = False):
+    """forward_corev2 for channel-first input, LayerNorm out-norm.
+
+    x: (B, D, H, W) activation (already conv+SiLU'd).  x_proj_weight: (K*(R+2N), D);
+    dt_projs_weight: (K*D, R); dt_projs_bias: (K, D) or (K*D,); A_logs: (K*D, N); Ds: (K*D,).
+    `act_dtype` emulates autocast: with "bf16" the tensors the reference would hold in
+    bf16 (xs, x_dbl, dts, Bs, Cs and the returned y) are rounded to bf16 at the same
+    points; the recurrence, merge and LayerNorm stay fp32 (vmamba.py:1544-1571).
+    """
+    x = _round_to(x, act_dtype)
+    Bt, D, H, W = x.shape
+    K, N, R = K_ROUTES, int(d_state), int(dt_rank)
+    L = H * W
+    Wx = np.asarray(x_proj_weight, dtype=np.float32).reshape(K, R + 2 * N, D)
+    Wdt = np.asarray(dt_projs_weight, dtype=np.float32).reshape(K, D, R)
+    if act_dtype != "f32":   # autocast casts the conv weights to the activation dtype
+        Wx, Wdt = _round_to(Wx, act_dtype), _round_to(Wdt, act_dtype)
+
+    xs = cross_scan(x, scans)                                   # (B, K, D, L)   :1536
+    x_dbl = np.einsum("kcd,bkdl->bkcl", Wx, xs, dtype=np.float32)   # grouped conv1d :1537
+    x_dbl = _round_to(x_dbl, act_dtype)
+    dts_low, Bs, Cs = x_dbl[:, :, :R], x_dbl[:, :, R:R + N], x_dbl[:, :, R + N:]   # :1538
+    dts = np.einsum("kdr,bkrl->bkdl", Wdt, dts_low, dtype=np.float32)          # :1539-1540
+    dts = _round_to(dts, act_dtype).reshape(Bt, K * D, L)
+    As = -np.exp(np.asarray(A_logs, dtype=np.float32)).reshape(K * D, N)        # :1544
+    Dsf = np.asarray(Ds, dtype=np.float32).reshape(K * D)
+    bias = np.asarray(dt_projs_bias, dtype=np.float32).reshape(K * D)          # :1548
+    ys = selective_scan(xs.reshape(Bt, K * D, L), dts, As, np.ascontiguousarray(Bs),
+                        np.ascontiguousarray(Cs), Dsf, bias, True, True, act_dtype)   # :1553
+    y = cross_merge(ys.reshape(Bt, K, D, H, W), scans).reshape(Bt, D, H, W)    # :1557
+    merged = y
+    if with_out_norm:
+        y = layer_norm_cf(y, out_norm_weight, out_norm_bias, eps)              # :1569
+    y = _round_to(y, act_dtype)                                                # :1571
+    if return_parts:
+        return y, dict(xs=xs, dts=dts, Bs=Bs, Cs=Cs, As=As, ys=ys, merged=merged)
+    return y
+
+
+# --------------------------------------------------------------------------- #
+# seeded synthetic inputs (value distributions of mamba_init, vmamba.py:1170-1237)
+# --------------------------------------------------------------------------- #
+def make_scan_inputs(Bt: int, D: int, H: int, W: int, N: int = 1, seed: int = 0,
+                     act_dtype: str = "f32"):
+    """Synthetic operator-level inputs: x ~ N(0,1); raw delta ~ N(0,1);
+    delta_bias = inverse-softplus(dt), dt log-uniform in [1e-3, 1e-1] (vmamba.py:1185-1190);
+    A = -exp(A_log), A_log = log(1..N) (vmamba.py:1201-1203); B, C ~ N(0,1); D = 1."""
+    rng = np.random.default_rng(seed)
+    K, L = K_ROUTES, H * W
+    x = rng.standard_normal((Bt, D, H, W), dtype=np.float32)
+    delta = rng.standard_normal((Bt, K * D, L), dtype=np.float32)
+    dt = np.exp(rng.random(K * D, dtype=np.float32) * (math.log(0.1) - math.log(1e-3)) + math.log(1e-3))
+    dt = np.maximum(dt, 1e-4).astype(np.float32)
+    delta_bias = (dt + np.log(-np.expm1(-dt))).astype(np.float32)
+    A = -np.tile(np.arange(1, N + 1, dtype=np.float32)[None], (K * D, 1))
+    Bs = rng.standard_normal((Bt, K, N, L), dtype=np.float32)
+    Cs = rng.standard_normal((Bt, K, N, L), dtype=np.float32)
+    Dp = np.ones(K * D, dtype=np.float32)
+    x, delta, Bs, Cs = (_round_to(t, act_dtype) for t in (x, delta, Bs, Cs))
+    return dict(x=x, delta=delta, A=A, Bs=Bs, Cs=Cs, D=Dp, delta_bias=delta_bias)
+
+
+def max_rel_err(got, ref) -> float:
+    """max |got - ref| / max |ref| -- the 'max relative error' used for float parity."""
+    got = np.asarray(got, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    denom = max(float(np.max(np.abs(ref))), 1e-30)
+    return float(np.max(np.abs(got - ref))) / denom
