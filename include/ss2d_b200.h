@@ -1,0 +1,155 @@
+/* ss2d_b200 -- C ABI of the B200 (sm_100a) SS2D core library, libss2d_b200.so.
+ *
+ * Plain C types only: raw device pointers, sizes and strides in ELEMENTS (int64),
+ * a CUDA stream passed as an opaque pointer.  The library never allocates, frees or
+ * retains memory: the caller owns every buffer (inputs, outputs, workspace), inputs are
+ * read-only, outputs are fully overwritten.  Every entry point validates its arguments
+ * before launching anything, launches asynchronously on the given stream, never
+ * synchronises, and returns 0 or a negative ss2d_status.  No exception crosses the ABI.
+ *
+ * File names cited below are paths inside MzeroMiko/VMamba.
+ */
+#ifndef SS2D_B200_H
+#define SS2D_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SS2D_ABI_VERSION 1
+#define SS2D_ROUTES 4            /* K: the four scan routes of SS2D */
+#define SS2D_MAX_DSTATE 256      /* as kernels/selective_scan/cusoflex/selective_scan_oflex.cpp:180 */
+
+typedef enum ss2d_dtype { SS2D_F32 = 0, SS2D_F16 = 1, SS2D_BF16 = 2 } ss2d_dtype;
+
+typedef enum ss2d_status {
+    SS2D_OK = 0,
+    SS2D_EINVAL_NULL = -1,     /* a required pointer is NULL */
+    SS2D_EINVAL_SHAPE = -2,    /* a size is zero/negative or sizes disagree */
+    SS2D_EINVAL_DTYPE = -3,    /* unknown or unsupported dtype combination */
+    SS2D_EINVAL_ALIGN = -4,    /* a pointer is not aligned to its element size */
+    SS2D_EINVAL_STRIDE = -5,   /* a stride is impossible for the given sizes */
+    SS2D_ENOTSUP = -6,         /* valid request that this build does not implement */
+    SS2D_ECUDA = -7,           /* the CUDA runtime reported an error at launch */
+    SS2D_EWORKSPACE = -8       /* workspace missing or too small */
+} ss2d_status;
+
+/* ------------------------------------------------------------------------------------
+ * Selective-scan forward.  Replaces selective_scan_cuda_oflex.fwd
+ * (kernels/selective_scan/cusoflex/selective_scan_oflex.cpp:143-231, kernel
+ * cusoflex/selective_scan_fwd_kernel_oflex.cuh:67-181) as called by SelectiveScanCuda.forward
+ * (classification/models/csms6s.py:74-87, vmamba.py:840-853); same mathematics as
+ * selective_scan_torch (csms6s.py:25-68).
+ *
+ * For every row (b, r), r in [0, dim), group k = r / (dim / n_groups), state h in R^dstate = 0:
+ *   dl   = delta[b, r % delta_dim ... see note] (+ delta_bias[r]) ; dl = softplus(dl) if delta_softplus
+ *   h_n  = exp(dl * A[r, n]) * h_n + dl * B[b, k, n, l] * u[b, r, l]
+ *   out[b, r, l] = sum_n C[b, k, n, l] * h_n (+ D[r] * u[b, r, l])
+ * u, delta, out: (batch, dim, seqlen), last dimension contiguous, strides in elements.
+ * A: (dim, dstate) fp32 contiguous.  B, C: (batch, n_groups, dstate, seqlen), last dimension
+ * contiguous.  D, delta_bias: (dim) fp32 or NULL.  in_dtype is the type of u, delta, B, C;
+ * out_dtype is SS2D_F32 ("oflex") or equal to in_dtype.  State and arithmetic are fp32.
+ * -------------------------------------------------------------------------------- */
+typedef struct ss2d_scan_params {
+    const void *u, *delta, *A, *B, *C, *D, *delta_bias;
+    void *out;
+    int32_t in_dtype, out_dtype;
+    int32_t delta_softplus;
+    int32_t reserved0;
+    int64_t batch, dim, dstate, seqlen, n_groups;
+    int64_t u_batch_stride, u_dim_stride;
+    int64_t delta_batch_stride, delta_dim_stride;
+    int64_t out_batch_stride, out_dim_stride;
+    int64_t B_batch_stride, B_group_stride, B_state_stride;
+    int64_t C_batch_stride, C_group_stride, C_state_stride;
+} ss2d_scan_params;
+
+int ss2d_selective_scan_fwd(const ss2d_scan_params *p, void *cuda_stream);
+
+/* ------------------------------------------------------------------------------------
+ * CrossScan / CrossMerge, channel-first tensors.  Replace CrossScanTritonF.forward and
+ * CrossMergeTritonF.forward / triton_cross_scan_flex (classification/models/csm_triton.py:
+ * 278-497; vmamba.py:350-575) and compute exactly cross_scan_fwd / cross_merge_fwd
+ * (vmamba.py:41-130): pure data movement, bit-exact.
+ *   scan : x (B, C, H, W)      -> xs (B, 4, C, H*W)
+ *   merge: ys (B, 4, C, H, W)  -> y  (B, C, H*W), summed in the reference's association order
+ * scans: 0 cross (row-major, column-major, both reversed), 1 unidirectional, 2 bidirectional,
+ * 3 rotations by 90 degrees.  All tensors contiguous.
+ * -------------------------------------------------------------------------------- */
+typedef struct ss2d_cross_params {
+    const void *in;
+    void *out;
+    int32_t dtype;
+    int32_t scans;
+    int64_t B, C, H, W;
+} ss2d_cross_params;
+
+int ss2d_cross_scan(const ss2d_cross_params *p, void *cuda_stream);
+int ss2d_cross_merge(const ss2d_cross_params *p, void *cuda_stream);
+
+/* ------------------------------------------------------------------------------------
+ * Fused SS2D core: CrossScan folded into the scan's loads + four-route selective scan
+ * (d_state >= 1) + CrossMerge + LayerNorm over channels, for scans mode 0.  Replaces the
+ * chain cross_scan_fn -> selective_scan_fn -> cross_merge_fn -> out_norm -> cast of
+ * SS2Dv2.forward_corev2 (vmamba.py:1536, 1553-1557, 1566-1571); the (B, 4, D, L) copy of x
+ * and the per-route outputs never exist in memory.
+ *
+ *   x        (B, D, H, W) contiguous, act_dtype
+ *   delta[k] (B, D, L) per route k, act_dtype, contiguous planes (batch stride given), raw
+ *            (pre-bias, pre-softplus) step sizes, stored in the ORIENTATION ORDER of route k:
+ *            index h*W+w for k = 0, 2 and w*H+h for k = 1, 3 (never reversed)
+ *   Bm[k], Cm[k] (B, N, L) per route, same order and dtype
+ *   A (4*D, N), Dskip (4*D), delta_bias (4*D): fp32, row index k*D + d
+ *   ln_weight, ln_bias (D) fp32 or NULL (NULL: no affine); ln_eps; with_norm = 0 skips LayerNorm
+ *   y        (B, D, H, W) contiguous, y_dtype (act_dtype or SS2D_F32)
+ *   workspace: ss2d_core_workspace_bytes() bytes, 256-byte aligned (holds the fp32 merged map)
+ * -------------------------------------------------------------------------------- */
+typedef struct ss2d_core_params {
+    const void *x;
+    const void *delta[SS2D_ROUTES];
+    const void *Bm[SS2D_ROUTES];
+    const void *Cm[SS2D_ROUTES];
+    const void *A, *Dskip, *delta_bias;
+    const void *ln_weight, *ln_bias;
+    void *y;
+    void *workspace;
+    int64_t workspace_bytes;
+    int64_t delta_batch_stride[SS2D_ROUTES];
+    int64_t bc_batch_stride[SS2D_ROUTES];
+    int64_t B, D, H, W, N;
+    int32_t act_dtype, y_dtype;
+    int32_t with_norm;
+    float ln_eps;
+} ss2d_core_params;
+
+int64_t ss2d_core_workspace_bytes(const ss2d_core_params *p);
+int ss2d_core_fwd(const ss2d_core_params *p, void *cuda_stream);
+
+/* LayerNorm over the channel axis of a channel-first map, optionally summing `n_terms`
+ * fp32 maps first.  Replaces LayerNorm(channel_first=True).forward (vmamba.py:1087-1093)
+ * + the trailing cast (vmamba.py:1571).  in: (n_terms, B, D, L) fp32; out: (B, D, L). */
+typedef struct ss2d_norm_params {
+    const void *in;
+    const void *weight, *bias;
+    void *out;
+    int64_t B, D, L;
+    int32_t n_terms, out_dtype;
+    float eps;
+    int32_t reserved0;
+} ss2d_norm_params;
+
+int ss2d_layer_norm_cf(const ss2d_norm_params *p, void *cuda_stream);
+
+/* library identification and error text */
+int ss2d_version(void);
+const char *ss2d_strerror(int status);
+/* number of kernel launches issued by this library in this process so far (all entry points) */
+int64_t ss2d_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SS2D_B200_H */

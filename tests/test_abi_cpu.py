@@ -1,0 +1,113 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every declared symbol, the ctypes
+mirrors match the C structs, and argument validation rejects bad calls before any launch."""
+import ctypes
+import os
+import re
+import subprocess
+
+import pytest
+
+from vmamba_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "ss2d_b200.h")
+
+
+def declared_functions():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(ss2d_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = declared_functions()
+    assert "ss2d_selective_scan_fwd" in names and "ss2d_core_fwd" in names
+    handle = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(handle, n), f"{n} declared in include/ss2d_b200.h but not exported"
+    assert set(names) == set(_lib.EXPORTS), "python binding and header disagree on the entry points"
+
+
+def test_struct_layout_matches_header(tmp_path):
+    prog = tmp_path / "sz.c"
+    prog.write_text('#include "ss2d_b200.h"\n#include <stdio.h>\n#include <stddef.h>\nint main(){printf("%zu %zu %zu %zu %zu %zu\\n",'
+                    'sizeof(ss2d_scan_params),sizeof(ss2d_cross_params),sizeof(ss2d_core_params),sizeof(ss2d_norm_params),'
+                    'offsetof(ss2d_core_params,delta_batch_stride),offsetof(ss2d_scan_params,batch));return 0;}\n')
+    exe = tmp_path / "sz"
+    subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), str(prog), "-o", str(exe)])
+    got = [int(t) for t in subprocess.check_output([str(exe)]).split()]
+    want = [ctypes.sizeof(_lib.ScanParams), ctypes.sizeof(_lib.CrossParams), ctypes.sizeof(_lib.CoreParams),
+            ctypes.sizeof(_lib.NormParams), _lib.CoreParams.delta_batch_stride.offset, _lib.ScanParams.batch.offset]
+    assert got == want
+
+
+def test_version_and_strerror():
+    L = _lib.lib()
+    assert L.ss2d_version() == 1
+    assert L.ss2d_strerror(0) == b"ok"
+    assert b"NULL" in L.ss2d_strerror(-1)
+    assert L.ss2d_strerror(-99) == b"unknown status"
+
+
+def test_validation_rejects_before_launch():
+    """None of these calls reaches a kernel launch, so they run without a GPU."""
+    L = _lib.lib()
+    before = _lib.launch_count()
+    assert L.ss2d_selective_scan_fwd(None, None) == -1
+    p = _lib.ScanParams()
+    assert L.ss2d_selective_scan_fwd(p, None) == -1                 # null tensors
+    buf = (ctypes.c_float * 64)()
+    addr = ctypes.addressof(buf)
+    for f in ("u", "delta", "A", "B", "C", "out"):
+        setattr(p, f, addr)
+    p.in_dtype = 7
+    assert L.ss2d_selective_scan_fwd(p, None) == -3                 # bad dtype
+    p.in_dtype, p.out_dtype = _lib.SS2D_BF16, _lib.SS2D_F16
+    assert L.ss2d_selective_scan_fwd(p, None) == -3                 # out must be fp32 or the input type
+    p.in_dtype = p.out_dtype = _lib.SS2D_F32
+    assert L.ss2d_selective_scan_fwd(p, None) == -2                 # zero sizes
+    p.batch, p.dim, p.dstate, p.seqlen, p.n_groups = 1, 6, 1, 8, 4
+    assert L.ss2d_selective_scan_fwd(p, None) == -2                 # dim not a multiple of groups
+    p.dim = 8
+    p.dstate = 1000
+    assert L.ss2d_selective_scan_fwd(p, None) == -6                 # d_state above the limit
+    p.dstate = 1
+    assert L.ss2d_selective_scan_fwd(p, None) == -5                 # strides smaller than the row
+    for f in ("u_dim_stride", "delta_dim_stride", "out_dim_stride", "B_state_stride", "C_state_stride",
+              "B_group_stride", "C_group_stride"):
+        setattr(p, f, 8)
+    p.u = addr + 2
+    assert L.ss2d_selective_scan_fwd(p, None) == -4                 # misaligned fp32 pointer
+
+    c = _lib.CrossParams()
+    assert L.ss2d_cross_scan(c, None) == -1
+    c.in_, c.out, c.dtype, c.scans = addr, addr, 0, 9
+    assert L.ss2d_cross_scan(c, None) == -6
+    c.scans = 0
+    assert L.ss2d_cross_merge(c, None) == -2
+
+    k = _lib.CoreParams()
+    assert L.ss2d_core_fwd(k, None) == -1
+    assert L.ss2d_core_workspace_bytes(k) == -1
+    n = _lib.NormParams()
+    assert L.ss2d_layer_norm_cf(n, None) == -1
+    assert _lib.launch_count() == before
+
+
+def test_missing_library_fails_loudly(tmp_path, monkeypatch):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(ImportError, match="no CPU or eager fallback"):
+        _lib.lib()
+
+
+def test_operators_refuse_cpu_tensors():
+    import torch
+    import vmamba_b200 as vb
+    x = torch.zeros(1, 2, 3, 4)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        vb.cross_scan_fn(x)
+    with pytest.raises(NotImplementedError):
+        vb.selective_scan_fn(x, x, x, x, x, backend="torch")
+    with pytest.raises(NotImplementedError):
+        vb.cross_scan_fn(x, in_channel_first=False)

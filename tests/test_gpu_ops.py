@@ -1,0 +1,262 @@
+"""Parity of the CUDA operators (through the C-ABI library) with the CPU oracle.  Needs a GPU.
+
+Tolerances: data movement is bit-exact; floating point uses max|got-ref| / max|ref|
+<= 1e-4 for fp32 tensors and <= 2e-2 for bf16 activations with fp32 state."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle as CO
+from oracle import ss2d_oracle as O
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+TOL_F32, TOL_BF16 = 1e-4, 2e-2
+
+
+@pytest.fixture(scope="module")
+def vb():
+    import vmamba_b200
+    assert torch.cuda.is_available()
+    return vmamba_b200
+
+
+def dev(a, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a)).to("cuda").to(dtype)
+
+
+def host(t):
+    return t.detach().float().cpu().numpy()
+
+
+# ------------------------------------------------------------------------------ cross scan / merge
+@pytest.mark.parametrize("scans", [0, 1, 2, 3])
+def test_cross_scan_merge_golden(vb, scans):
+    g = np.load(os.path.join(G, "csm_small.npz"))
+    assert np.array_equal(host(vb.cross_scan_fn(dev(g["x"]), scans=scans)), g[f"scan_s{scans}"])
+    assert np.array_equal(host(vb.cross_merge_fn(dev(g["ys"]), scans=scans)), g[f"merge_s{scans}"])
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1, 1), (2, 3, 5, 7), (1, 5, 56, 57), (3, 2, 33, 32), (2, 7, 64, 31), (1, 2, 1, 40)])
+@pytest.mark.parametrize("scans", [0, 1, 2, 3])
+def test_cross_scan_merge_vs_oracle(vb, shape, scans):
+    rng = np.random.default_rng(hash((shape, scans)) & 0xffff)
+    x = rng.standard_normal(shape, dtype=np.float32)
+    ys = rng.standard_normal((shape[0], 4) + shape[1:], dtype=np.float32)
+    assert np.array_equal(host(vb.cross_scan_fn(dev(x), scans=scans)), O.cross_scan(x, scans))
+    assert np.array_equal(host(vb.cross_merge_fn(dev(ys), scans=scans)), O.cross_merge(ys, scans))
+    xb = O.round_bf16(x)
+    assert np.array_equal(host(vb.cross_scan_fn(dev(xb, torch.bfloat16), scans=scans)), O.cross_scan(xb, scans))
+
+
+def test_cross_merge_is_adjoint_of_scan(vb):
+    x = torch.randn(2, 6, 28, 28, device="cuda")
+    xs = vb.cross_scan_fn(x)
+    assert torch.equal(vb.cross_merge_fn(xs.view(2, 4, 6, 28, 28)), (4 * x).view(2, 6, -1))
+
+
+# ------------------------------------------------------------------------------ selective scan
+@pytest.mark.parametrize("n", ["c0", "c1", "c2", "c3", "c4", "c5", "c6"])
+def test_selective_scan_golden(vb, n):
+    g = np.load(os.path.join(G, "selscan_small.npz"))
+    dt = dict(f32=torch.float32, bf16=torch.bfloat16, f16=torch.float16)[str(g[f"{n}_dtype"])]
+    D = dev(g[f"{n}_D"]) if f"{n}_D" in g.files else None
+    bias = dev(g[f"{n}_bias"]) if f"{n}_bias" in g.files else None
+    oflex = bool(g[f"{n}_oflex"])
+    if bias is None and dt != torch.float32:
+        pytest.skip("softplus without bias in low precision is not a supported combination")
+    y = vb.selective_scan_fn(dev(g[f"{n}_u"], dt), dev(g[f"{n}_delta"], dt), dev(g[f"{n}_A"]), dev(g[f"{n}_B"], dt),
+                             dev(g[f"{n}_C"], dt), D, bias, bool(g[f"{n}_sp"]), oflex)
+    assert y.dtype == (torch.float32 if oflex else dt)
+    assert O.max_rel_err(host(y), g[f"{n}_y"]) <= (TOL_F32 if oflex else 8e-3)
+
+
+@pytest.mark.parametrize("L", [1, 2, 7, 8, 31, 32, 33, 49, 196, 255, 256, 257, 784, 1000, 3136, 4099])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_selective_scan_lengths(vb, L, dtype):
+    rng = np.random.default_rng(L)
+    Bt, K, Cd, N = 2, 4, 3, 1
+    inp = dict(u=rng.standard_normal((Bt, K * Cd, L), dtype=np.float32),
+               delta=rng.standard_normal((Bt, K * Cd, L), dtype=np.float32),
+               A=-np.exp(rng.standard_normal((K * Cd, N), dtype=np.float32) * 0.5),
+               B=rng.standard_normal((Bt, K, N, L), dtype=np.float32),
+               C=rng.standard_normal((Bt, K, N, L), dtype=np.float32),
+               D=rng.standard_normal(K * Cd, dtype=np.float32),
+               bias=(rng.standard_normal(K * Cd, dtype=np.float32) - 3.0))
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    if dtype == "bf16":
+        for k in ("u", "delta", "B", "C"):
+            inp[k] = O.round_bf16(inp[k])
+    ref = CO.selective_scan(inp["u"], inp["delta"], inp["A"], inp["B"], inp["C"], inp["D"], inp["bias"], True)
+    y = vb.selective_scan_fn(dev(inp["u"], td), dev(inp["delta"], td), dev(inp["A"]), dev(inp["B"], td),
+                             dev(inp["C"], td), dev(inp["D"]), dev(inp["bias"]), True, True)
+    assert O.max_rel_err(host(y), ref) <= TOL_F32      # same rounded inputs, fp32 state: fp32 tolerance holds
+    y2 = vb.selective_scan_fn(dev(inp["u"], td), dev(inp["delta"], td), dev(inp["A"]), dev(inp["B"], td),
+                              dev(inp["C"], td), dev(inp["D"]), dev(inp["bias"]), True, True)
+    assert torch.equal(y, y2), "the scan must be deterministic"
+
+
+@pytest.mark.parametrize("N,L,K", [(2, 100, 4), (16, 640, 4), (16, 196, 1), (64, 50, 2), (256, 33, 1)])
+def test_selective_scan_dstate(vb, N, L, K):
+    rng = np.random.default_rng(N * 1000 + L)
+    Bt, Cd = 2, 2
+    u = rng.standard_normal((Bt, K * Cd, L), dtype=np.float32)
+    delta = rng.standard_normal((Bt, K * Cd, L), dtype=np.float32)
+    A = -np.tile(np.arange(1, N + 1, dtype=np.float32)[None], (K * Cd, 1))
+    Bm = rng.standard_normal((Bt, K, N, L), dtype=np.float32)
+    Cm = rng.standard_normal((Bt, K, N, L), dtype=np.float32)
+    D = np.ones(K * Cd, dtype=np.float32)
+    bias = rng.standard_normal(K * Cd).astype(np.float32) - 4.0
+    ref = CO.selective_scan(u, delta, A, Bm, Cm, D, bias, True)
+    y = vb.selective_scan_fn(dev(u), dev(delta), dev(A), dev(Bm), dev(Cm), dev(D), dev(bias), True, True)
+    assert O.max_rel_err(host(y), ref) <= TOL_F32
+
+
+def test_selective_scan_strided_and_optional_args(vb):
+    rng = np.random.default_rng(5)
+    Bt, KC, L = 2, 8, 96
+    big_u = rng.standard_normal((Bt, KC, 2 * L), dtype=np.float32)
+    big_d = rng.standard_normal((Bt, 2 * KC, L), dtype=np.float32)
+    A = -np.exp(rng.standard_normal((KC, 1), dtype=np.float32))
+    Bm = rng.standard_normal((Bt, 4, 1, L), dtype=np.float32)
+    Cm = rng.standard_normal((Bt, 4, 1, L), dtype=np.float32)
+    u_t, d_t = dev(big_u)[:, :, 3:3 + L], dev(big_d)[:, ::2, :]
+    ref = CO.selective_scan(big_u[:, :, 3:3 + L], big_d[:, ::2, :], A, Bm, Cm, None, None, False)
+    y = vb.selective_scan_fn(u_t, d_t, dev(A), dev(Bm), dev(Cm), None, None, False, True)
+    assert O.max_rel_err(host(y), ref) <= TOL_F32
+
+
+def test_selective_scan_long_rows_keep_tolerance(vb):
+    """L = 65536 (the dense-prediction stage) with step sizes down to 1e-3."""
+    inp = O.make_scan_inputs(1, 2, 256, 256, N=1, seed=3)
+    xs = CO.cross_scan(inp["x"], 0).reshape(1, 8, 65536)
+    ref = CO.selective_scan(xs, inp["delta"], inp["A"], inp["Bs"], inp["Cs"], inp["D"], inp["delta_bias"], True)
+    y = vb.selective_scan_fn(dev(xs), dev(inp["delta"]), dev(inp["A"]), dev(inp["Bs"]), dev(inp["Cs"]), dev(inp["D"]),
+                             dev(inp["delta_bias"]), True, True)
+    assert O.max_rel_err(host(y), ref) <= TOL_F32
+
+
+# ------------------------------------------------------------------------------ layer norm
+@pytest.mark.parametrize("shape", [(2, 96, 56, 56), (1, 5, 3, 3), (2, 192, 7, 9), (1, 384, 14, 14), (1, 768, 7, 7), (1, 1536, 4, 5)])
+def test_layer_norm_cf(vb, shape):
+    rng = np.random.default_rng(shape[1])
+    y = (rng.standard_normal(shape, dtype=np.float32) * 3 + 0.7)
+    w = rng.standard_normal(shape[1], dtype=np.float32)
+    b = rng.standard_normal(shape[1], dtype=np.float32)
+    ref = O.layer_norm_cf(y, w, b)
+    got = vb.layer_norm_cf(dev(y), dev(w), dev(b))
+    assert O.max_rel_err(host(got), ref) <= 2e-5
+    got16 = vb.layer_norm_cf(dev(y), dev(w), dev(b), out_dtype=torch.bfloat16)
+    assert O.max_rel_err(host(got16), ref) <= 8e-3
+    assert O.max_rel_err(host(vb.layer_norm_cf(dev(y))), O.layer_norm_cf(y)) <= 2e-5
+
+
+# ------------------------------------------------------------------------------ fused core
+def _core_case(Bt, D, H, W, N, seed, Cmodel=None):
+    import math
+    rng = np.random.default_rng(seed)
+    R = math.ceil((Cmodel or D) / 16)
+    K = 4
+    x = rng.standard_normal((Bt, D, H, W), dtype=np.float32)
+    wx = (rng.standard_normal((K * (R + 2 * N), D), dtype=np.float32) / np.sqrt(D)).astype(np.float32)
+    wdt = (rng.standard_normal((K * D, R), dtype=np.float32) * R ** -0.5).astype(np.float32)
+    dt = np.exp(rng.random((K, D), dtype=np.float32) * (np.log(0.1) - np.log(1e-3)) + np.log(1e-3))
+    bias = (dt + np.log(-np.expm1(-dt))).astype(np.float32)
+    A_logs = np.log(np.tile(np.arange(1, N + 1, dtype=np.float32)[None], (K * D, 1))) + \
+        0.2 * rng.standard_normal((K * D, N), dtype=np.float32)
+    Ds = (1.0 + 0.2 * rng.standard_normal(K * D)).astype(np.float32)
+    lw = (1.0 + 0.2 * rng.standard_normal(D)).astype(np.float32)
+    lb = (0.2 * rng.standard_normal(D)).astype(np.float32)
+    return dict(x=x, wx=wx, wdt=wdt, bias=bias, A_logs=A_logs.astype(np.float32), Ds=Ds, lw=lw, lb=lb, N=N, R=R)
+
+
+def _run_core(vb, c, dtype, with_norm=True, unfused=False):
+    from vmamba_b200 import fused
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    w = vb.CoreWeights.build(dev(c["wx"]), dev(c["wdt"]), dev(c["bias"]), dev(c["A_logs"]), dev(c["Ds"]), dev(c["lw"]),
+                             dev(c["lb"]), d_state=c["N"], dt_rank=c["R"], dtype=td)
+    x = dev(c["x"], td)
+    if unfused:
+        return fused._ss2d_core_unfused(x, w, with_norm, td if with_norm else torch.float32)
+    return vb.ss2d_core(x, w, with_norm=with_norm)
+
+
+CORE_SHAPES = [(2, 96, 56, 56), (2, 192, 28, 28), (2, 384, 14, 14), (3, 768, 7, 7), (1, 5, 9, 11), (2, 3, 6, 10),
+               (1, 2, 64, 64), (2, 7, 12, 20), (1, 4, 1, 16), (1, 3, 8, 1), (2, 10, 32, 24)]
+
+
+@pytest.mark.parametrize("shape", CORE_SHAPES)
+def test_fused_core_fp32(vb, shape):
+    c = _core_case(*shape, N=1, seed=sum(shape))
+    ref, parts = O.ss2d_core(c["x"], c["wx"], c["wdt"], c["bias"], c["A_logs"], c["Ds"], c["lw"], c["lb"],
+                             d_state=1, dt_rank=c["R"], return_parts=True)
+    merged = _run_core(vb, c, "f32", with_norm=False)
+    assert O.max_rel_err(host(merged), parts["merged"]) <= TOL_F32
+    y = _run_core(vb, c, "f32")
+    assert y.dtype == torch.float32 and tuple(y.shape) == shape
+    assert O.max_rel_err(host(y), ref) <= TOL_F32
+    assert torch.equal(y, _run_core(vb, c, "f32")), "atomic-free design: results must be bit-identical run to run"
+    yu = _run_core(vb, c, "f32", unfused=True)
+    assert O.max_rel_err(host(yu), ref) <= TOL_F32
+
+
+@pytest.mark.parametrize("shape", CORE_SHAPES[:6])
+def test_fused_core_bf16(vb, shape):
+    c = _core_case(*shape, N=1, seed=sum(shape) + 1)
+    ref = O.ss2d_core(c["x"], c["wx"], c["wdt"], c["bias"], c["A_logs"], c["Ds"], c["lw"], c["lb"],
+                      d_state=1, dt_rank=c["R"], act_dtype="bf16")
+    y = _run_core(vb, c, "bf16")
+    assert y.dtype == torch.bfloat16
+    assert O.max_rel_err(host(y), ref) <= TOL_BF16
+
+
+def test_core_dstate_gt1_takes_surface_kernels(vb):
+    c = _core_case(2, 6, 10, 12, N=4, seed=9, Cmodel=32)
+    ref = O.ss2d_core(c["x"], c["wx"], c["wdt"], c["bias"], c["A_logs"], c["Ds"], c["lw"], c["lb"], d_state=4, dt_rank=c["R"])
+    y = _run_core(vb, c, "f32")
+    assert O.max_rel_err(host(y), ref) <= TOL_F32
+
+
+@pytest.mark.parametrize("tag", ["m0", "m1"])
+def test_core_against_reference_module_golden(vb, tag):
+    g = np.load(os.path.join(G, "ss2d_module_small.npz"))
+    sd = {k[len(tag) + 4:]: g[k] for k in g.files if k.startswith(f"{tag}_sd_")}
+    N, R = int(g[f"{tag}_d_state"]), int(g[f"{tag}_dt_rank"])
+    w = vb.CoreWeights.build(dev(sd["x_proj.weight"]), dev(sd["dt_projs.weight"]), dev(sd["dt_projs_bias"]),
+                             dev(sd["A_logs"]), dev(sd["Ds"]), dev(sd["out_norm.weight"]), dev(sd["out_norm.bias"]),
+                             d_state=N, dt_rank=R, dtype=torch.float32)
+    y = vb.ss2d_core(dev(g[f"{tag}_core_x"]), w)
+    assert O.max_rel_err(host(y), g[f"{tag}_core_y"]) <= TOL_F32
+    # the operator-surface chain on the reference's own intermediate tensors
+    ys = vb.selective_scan_fn(dev(g[f"{tag}_us"]), dev(g[f"{tag}_dts"]), w.A, dev(g[f"{tag}_Bs"]), dev(g[f"{tag}_Cs"]),
+                              w.Ds, w.dt_bias, True, True)
+    assert O.max_rel_err(host(ys), g[f"{tag}_ys"].reshape(ys.shape)) <= TOL_F32
+
+
+def test_config0_full_size_digest(vb):
+    """The (2,96,56,56) fp32 single-op workload against digests of the reference's own run."""
+    import sys
+    sys.path.insert(0, G)
+    from make_golden import config0_inputs, digest
+    g = np.load(os.path.join(G, "config0_digest.npz"))
+    inp = config0_inputs(0)
+    x = inp["x"].cuda()
+    xs = vb.cross_scan_fn(x)
+    ys = vb.selective_scan_fn(xs.view(2, 384, 3136), inp["delta"].cuda(), inp["A"].cuda(), inp["Bs"].cuda(),
+                              inp["Cs"].cuda(), inp["D"].cuda(), inp["delta_bias"].cuda(), True, True)
+    merged = vb.cross_merge_fn(ys.view(2, 4, 96, 56, 56))
+    normed = vb.layer_norm_cf(merged)
+    for name, t in (("ys", ys), ("merged", merged), ("normed", normed)):
+        d = digest(host(t))
+        ref = g[f"{name}_sample"]
+        assert np.max(np.abs(d["sample"] - ref)) <= TOL_F32 * np.max(np.abs(ref)), name
+        assert abs(d["abssum"] - float(g[f"{name}_abssum"])) <= 1e-5 * float(g[f"{name}_abssum"]), name
+
+
+def test_launches_are_counted(vb):
+    from vmamba_b200 import _lib
+    before = _lib.launch_count()
+    vb.cross_scan_fn(torch.zeros(1, 1, 2, 2, device="cuda"))
+    assert _lib.launch_count() == before + 1

@@ -1,0 +1,97 @@
+"""ctypes binding of libss2d_b200.so (include/ss2d_b200.h).
+
+There is no CPU or eager fallback: if the library is missing or cannot be loaded the
+import of any operator fails with an explicit error.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libss2d_b200.so")
+
+SS2D_F32, SS2D_F16, SS2D_BF16 = 0, 1, 2
+SS2D_OK = 0
+SS2D_ENOTSUP = -6
+ROUTES = 4
+
+_i32, _i64, _vp, _f32 = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float
+
+
+class ScanParams(ctypes.Structure):
+    _fields_ = [(n, _vp) for n in ("u", "delta", "A", "B", "C", "D", "delta_bias", "out")] + \
+               [(n, _i32) for n in ("in_dtype", "out_dtype", "delta_softplus", "reserved0")] + \
+               [(n, _i64) for n in ("batch", "dim", "dstate", "seqlen", "n_groups",
+                                    "u_batch_stride", "u_dim_stride", "delta_batch_stride", "delta_dim_stride",
+                                    "out_batch_stride", "out_dim_stride",
+                                    "B_batch_stride", "B_group_stride", "B_state_stride",
+                                    "C_batch_stride", "C_group_stride", "C_state_stride")]
+
+
+class CrossParams(ctypes.Structure):
+    _fields_ = [("in_", _vp), ("out", _vp), ("dtype", _i32), ("scans", _i32),
+                ("B", _i64), ("C", _i64), ("H", _i64), ("W", _i64)]
+
+
+class CoreParams(ctypes.Structure):
+    _fields_ = [("x", _vp), ("delta", _vp * ROUTES), ("Bm", _vp * ROUTES), ("Cm", _vp * ROUTES),
+                ("A", _vp), ("Dskip", _vp), ("delta_bias", _vp), ("ln_weight", _vp), ("ln_bias", _vp),
+                ("y", _vp), ("workspace", _vp), ("workspace_bytes", _i64),
+                ("delta_batch_stride", _i64 * ROUTES), ("bc_batch_stride", _i64 * ROUTES),
+                ("B", _i64), ("D", _i64), ("H", _i64), ("W", _i64), ("N", _i64),
+                ("act_dtype", _i32), ("y_dtype", _i32), ("with_norm", _i32), ("ln_eps", _f32)]
+
+
+class NormParams(ctypes.Structure):
+    _fields_ = [("in_", _vp), ("weight", _vp), ("bias", _vp), ("out", _vp),
+                ("B", _i64), ("D", _i64), ("L", _i64),
+                ("n_terms", _i32), ("out_dtype", _i32), ("eps", _f32), ("reserved0", _i32)]
+
+
+EXPORTS = {
+    # name: (restype, argtypes)
+    "ss2d_selective_scan_fwd": (ctypes.c_int, [ctypes.POINTER(ScanParams), _vp]),
+    "ss2d_cross_scan": (ctypes.c_int, [ctypes.POINTER(CrossParams), _vp]),
+    "ss2d_cross_merge": (ctypes.c_int, [ctypes.POINTER(CrossParams), _vp]),
+    "ss2d_core_workspace_bytes": (_i64, [ctypes.POINTER(CoreParams)]),
+    "ss2d_core_fwd": (ctypes.c_int, [ctypes.POINTER(CoreParams), _vp]),
+    "ss2d_layer_norm_cf": (ctypes.c_int, [ctypes.POINTER(NormParams), _vp]),
+    "ss2d_version": (ctypes.c_int, []),
+    "ss2d_strerror": (ctypes.c_char_p, [ctypes.c_int]),
+    "ss2d_launch_count": (_i64, []),
+}
+
+_lib = None
+
+
+class Ss2dError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = lib().ss2d_strerror(status).decode()
+        super().__init__(f"{where}: {msg} (status {status})")
+
+
+def lib():
+    """The loaded library; raises if it has not been built (python -m vmamba_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} not found. vmamba_b200 has no CPU or eager fallback: build the CUDA "
+                "library first with `python -m vmamba_b200.build` (needs nvcc, targets sm_100a).")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in EXPORTS.items():
+            fn = getattr(handle, name)   # AttributeError if a declared symbol is missing
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(status: int, where: str):
+    if status != SS2D_OK:
+        raise Ss2dError(status, where)
+
+
+def launch_count() -> int:
+    return int(lib().ss2d_launch_count())

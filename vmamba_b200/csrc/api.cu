@@ -1,0 +1,48 @@
+// extern "C" entry points of libss2d_b200.so (declared in include/ss2d_b200.h).
+#include <atomic>
+
+#include "common.cuh"
+
+namespace ss2d {
+int selective_scan_fwd(const ss2d_scan_params* p, cudaStream_t st);
+int cross_scan(const ss2d_cross_params* p, cudaStream_t st);
+int cross_merge(const ss2d_cross_params* p, cudaStream_t st);
+int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st);
+long long core_workspace_bytes(const ss2d_core_params* p);
+int core_fwd(const ss2d_core_params* p, cudaStream_t st);
+
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int check_launch() { return cudaPeekAtLastError() == cudaSuccess ? SS2D_OK : SS2D_ECUDA; }
+}  // namespace ss2d
+
+extern "C" {
+
+int ss2d_selective_scan_fwd(const ss2d_scan_params* p, void* stream) {
+    return ss2d::selective_scan_fwd(p, (cudaStream_t)stream);
+}
+int ss2d_cross_scan(const ss2d_cross_params* p, void* stream) { return ss2d::cross_scan(p, (cudaStream_t)stream); }
+int ss2d_cross_merge(const ss2d_cross_params* p, void* stream) { return ss2d::cross_merge(p, (cudaStream_t)stream); }
+int ss2d_layer_norm_cf(const ss2d_norm_params* p, void* stream) { return ss2d::layer_norm_cf(p, (cudaStream_t)stream); }
+int64_t ss2d_core_workspace_bytes(const ss2d_core_params* p) { return ss2d::core_workspace_bytes(p); }
+int ss2d_core_fwd(const ss2d_core_params* p, void* stream) { return ss2d::core_fwd(p, (cudaStream_t)stream); }
+
+int ss2d_version(void) { return SS2D_ABI_VERSION; }
+int64_t ss2d_launch_count(void) { return ss2d::g_launches.load(std::memory_order_relaxed); }
+
+const char* ss2d_strerror(int status) {
+    switch (status) {
+        case SS2D_OK: return "ok";
+        case SS2D_EINVAL_NULL: return "a required pointer is NULL";
+        case SS2D_EINVAL_SHAPE: return "invalid or inconsistent sizes";
+        case SS2D_EINVAL_DTYPE: return "unsupported dtype combination";
+        case SS2D_EINVAL_ALIGN: return "pointer not aligned to its element size";
+        case SS2D_EINVAL_STRIDE: return "stride too small for the given sizes";
+        case SS2D_ENOTSUP: return "request not supported by this build";
+        case SS2D_ECUDA: return "CUDA runtime error at kernel launch";
+        case SS2D_EWORKSPACE: return "workspace missing or too small";
+        default: return "unknown status";
+    }
+}
+
+}  // extern "C"

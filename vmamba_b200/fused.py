@@ -1,0 +1,213 @@
+"""Fused SS2D core: host side of `ss2d_core_fwd` and the hook that installs it into SS2D modules.
+
+`ss2d_core(x, weights)` computes what SS2Dv2.forward_corev2 computes for scan mode "cross2d" on a
+channel-first map (vmamba.py:1504-1571): CrossScan -> x_proj -> dt_projs -> selective scan ->
+CrossMerge -> out_norm -> cast, without ever materialising the (B, 4, D, L) scan copy or the
+per-route outputs.
+
+Because a 1x1 projection commutes with a permutation of the pixels, the x_proj contraction is done
+once on x in its native layout (one library GEMM, (4(R+2N) x D) . (D x L) per image); the rows of
+the two column-major routes are then transposed (they are (R+2N)/D of the size of x), the step
+sizes are expanded per route (R -> D, a batched library GEMM) and the CUDA kernel consumes x plus
+the per-route (delta, B, C) streams in the orientation order of each route.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib, ops
+from ._lib import CoreParams, check, lib
+
+K = 4
+
+
+@dataclass
+class CoreWeights:
+    """Inference-time constants of one SS2D core, laid out for the fused path."""
+    wx: torch.Tensor            # (K*(R+2N), D) activation dtype
+    wdt_even: torch.Tensor      # (2, D, R) routes 0, 2, activation dtype
+    wdt_odd: torch.Tensor       # (2, D, R) routes 1, 3
+    A: torch.Tensor             # (K*D, N) fp32, = -exp(A_logs)
+    Ds: torch.Tensor            # (K*D,) fp32
+    dt_bias: torch.Tensor       # (K*D,) fp32
+    ln_weight: Optional[torch.Tensor]
+    ln_bias: Optional[torch.Tensor]
+    d_state: int
+    dt_rank: int
+    d_inner: int
+    eps: float = 1e-5
+
+    @staticmethod
+    def build(x_proj_weight, dt_projs_weight, dt_projs_bias, A_logs, Ds, ln_weight, ln_bias, *,
+              d_state: int, dt_rank: int, dtype: torch.dtype, eps: float = 1e-5) -> "CoreWeights":
+        N, R = int(d_state), int(dt_rank)
+        KD = A_logs.shape[0]
+        D = KD // K
+        wx = x_proj_weight.detach().reshape(K * (R + 2 * N), D).to(dtype).contiguous()
+        wdt = dt_projs_weight.detach().reshape(K, D, R).to(dtype)
+        f32 = lambda t: None if t is None else t.detach().float().contiguous()
+        return CoreWeights(wx, wdt[0::2].contiguous(), wdt[1::2].contiguous(),
+                           (-torch.exp(A_logs.detach().float())).reshape(KD, N).contiguous(),
+                           f32(Ds.reshape(-1)), f32(dt_projs_bias.reshape(-1)), f32(ln_weight), f32(ln_bias),
+                           N, R, D, float(eps))
+
+
+def project(x: torch.Tensor, w: CoreWeights):
+    """x (B, D, H, W) -> per-orientation projections.
+
+    Returns (xd_even, xd_odd, delta_even, delta_odd):
+      xd_even  (B, 2, R+2N, L) view, routes 0 and 2, row-major pixel order
+      xd_odd   (B, 2, R+2N, L) routes 1 and 3, column-major pixel order
+      delta_*  (B, 2, D, L) raw step sizes in the same orders
+    """
+    B, D, H, W = x.shape
+    L, R, N = H * W, w.dt_rank, w.d_state
+    C = R + 2 * N
+    xd = torch.matmul(w.wx, x.reshape(B, D, L)).view(B, 2, 2, C, H, W)    # route k = 2*i + j
+    xd_even = xd[:, :, 0].reshape(B, 2, C, L)
+    xd_odd = xd[:, :, 1].transpose(-1, -2).reshape(B, 2, C, L)
+    delta_even = torch.matmul(w.wdt_even, xd_even[:, :, :R])
+    delta_odd = torch.matmul(w.wdt_odd, xd_odd[:, :, :R])
+    return xd_even, xd_odd, delta_even, delta_odd
+
+
+def ss2d_core(x: torch.Tensor, w: CoreWeights, *, with_norm: bool = True, out_dtype=None,
+              workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Fused forward of the SS2D core.  x: (B, D, H, W) CUDA tensor; returns (B, D, H, W) in
+    `out_dtype` (default x.dtype; fp32 required when `with_norm` is False).  Falls back to the
+    operator-surface kernels (still CUDA, never CPU) for d_state > 1 or planes too long for one CTA."""
+    if not x.is_cuda:
+        raise RuntimeError("vmamba_b200.ss2d_core runs on CUDA tensors only (no CPU fallback)")
+    x = x.contiguous()
+    B, D, H, W = x.shape
+    if D != w.d_inner:
+        raise RuntimeError(f"x has {D} channels, weights were built for {w.d_inner}")
+    L, R, N = H * W, w.dt_rank, w.d_state
+    out_dtype = out_dtype or (x.dtype if with_norm else torch.float32)
+    with torch.autocast("cuda", enabled=False):
+        if N != 1 or (L // _vec_of(L)) > 1024:
+            return _ss2d_core_unfused(x, w, with_norm, out_dtype)
+        xd_even, xd_odd, delta_even, delta_odd = project(x, w)
+        y = torch.empty((B, D, H, W), device=x.device, dtype=out_dtype)
+        p = CoreParams()
+        p.x = x.data_ptr()
+        srcs = (xd_even, xd_odd)
+        deltas = (delta_even, delta_odd)
+        esz = x.element_size()
+        for k in range(K):
+            j, i = k % 2, k // 2          # j: orientation (0 row, 1 column); i: index inside the pair
+            xd, dl = srcs[j], deltas[j]
+            p.delta[k] = dl.data_ptr() + i * dl.stride(1) * esz
+            p.delta_batch_stride[k] = dl.stride(0)
+            base = xd.data_ptr() + i * xd.stride(1) * esz
+            p.Bm[k] = base + R * xd.stride(2) * esz
+            p.Cm[k] = base + (R + N) * xd.stride(2) * esz
+            p.bc_batch_stride[k] = xd.stride(0)
+        p.A, p.Dskip, p.delta_bias = w.A.data_ptr(), w.Ds.data_ptr(), w.dt_bias.data_ptr()
+        p.ln_weight = None if w.ln_weight is None else w.ln_weight.data_ptr()
+        p.ln_bias = None if w.ln_bias is None else w.ln_bias.data_ptr()
+        p.y = y.data_ptr()
+        p.B, p.D, p.H, p.W, p.N = B, D, H, W, N
+        p.act_dtype, p.y_dtype = ops.dtype_code(x), ops.dtype_code(y)
+        p.with_norm, p.ln_eps = int(with_norm), w.eps
+        need = int(lib().ss2d_core_workspace_bytes(p))
+        if need < 0:
+            raise RuntimeError("ss2d_core_workspace_bytes: invalid arguments")
+        if need > 0:
+            if workspace is None or workspace.numel() * workspace.element_size() < need:
+                workspace = torch.empty(need, device=x.device, dtype=torch.uint8)
+            p.workspace, p.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+        with torch.cuda.device(x.device):
+            check(lib().ss2d_core_fwd(p, torch.cuda.current_stream(x.device).cuda_stream), "ss2d_core_fwd")
+        return y
+
+
+def _vec_of(L: int) -> int:
+    v = 8
+    while v > 1 and L % v:
+        v >>= 1
+    return v
+
+
+def _ss2d_core_unfused(x, w: CoreWeights, with_norm: bool, out_dtype):
+    """Same mathematics through the operator-surface kernels (cross scan -> projections ->
+    selective scan -> cross merge -> LayerNorm), the order of vmamba.py:1536-1571."""
+    B, D, H, W = x.shape
+    L, R, N = H * W, w.dt_rank, w.d_state
+    C = R + 2 * N
+    xs = ops.cross_scan_fwd(x, 0)                                        # (B, K, D, L)
+    x_dbl = torch.matmul(w.wx.view(K, C, D), xs)                         # (B, K, C, L)
+    wdt = torch.stack((w.wdt_even[0], w.wdt_odd[0], w.wdt_even[1], w.wdt_odd[1]))
+    dts = torch.matmul(wdt, x_dbl[:, :, :R]).reshape(B, K * D, L)
+    Bs = x_dbl[:, :, R:R + N].contiguous()
+    Cs = x_dbl[:, :, R + N:].contiguous()
+    ys = ops.selective_scan_fwd(xs.view(B, K * D, L), dts, w.A, Bs, Cs, w.Ds, w.dt_bias, True, True)
+    y = ops.cross_merge_fwd(ys.view(B, K, D, H, W), 0).view(B, D, H, W)
+    if with_norm:
+        y = ops.layer_norm_cf(y, w.ln_weight, w.ln_bias, w.eps, out_dtype)
+    return y.to(out_dtype)
+
+
+# --------------------------------------------------------------------------------------------
+# installing the fused core into reference SS2D modules without touching their source
+# --------------------------------------------------------------------------------------------
+def _supported(m) -> bool:
+    fc = getattr(m, "forward_core", None)
+    kw = getattr(fc, "keywords", None)
+    if fc is None or kw is None:
+        return False
+    if kw.get("scan_mode", "cross2d") not in ("cross2d", 0):
+        return False
+    if kw.get("force_fp32", False):
+        return False
+    if not getattr(m, "channel_first", False):
+        return False
+    if not isinstance(getattr(m, "out_norm", None), torch.nn.LayerNorm):
+        return False
+    return all(hasattr(m, n) for n in ("x_proj", "dt_projs", "A_logs", "Ds", "dt_projs_bias"))
+
+
+def enable_fused(model: torch.nn.Module, verbose: bool = False) -> int:
+    """Rebind `forward_core` (an instance attribute set in SS2Dv2.__initv2__, vmamba.py:1448) of
+    every supported SS2D module to the fused path.  Weights are snapshotted per activation dtype at
+    first use, so call it on a model in eval mode; `disable_fused` restores the original."""
+    n = 0
+    for mod in model.modules():
+        if not _supported(mod):
+            continue
+        cache = {}
+        orig = mod.forward_core
+
+        def fused_core(x, _m=mod, _cache=cache, _orig=orig, **kwargs):
+            if getattr(_m, "__DEBUG__", False) or _m.training or not x.is_cuda:
+                return _orig(x, **kwargs)
+            w = _cache.get(x.dtype)
+            if w is None:
+                w = CoreWeights.build(_m.x_proj.weight, _m.dt_projs.weight, _m.dt_projs_bias, _m.A_logs, _m.Ds,
+                                      _m.out_norm.weight, _m.out_norm.bias, d_state=_m.d_state,
+                                      dt_rank=_m.dt_rank, dtype=x.dtype, eps=_m.out_norm.eps)
+                _cache[x.dtype] = w
+            return ss2d_core(x, w)
+
+        fused_core._vmamba_b200_original = orig
+        mod.forward_core = fused_core
+        n += 1
+    if verbose:
+        print(f"vmamba_b200: fused SS2D core enabled on {n} modules")
+    return n
+
+
+def disable_fused(model: torch.nn.Module) -> int:
+    n = 0
+    for mod in model.modules():
+        fc = getattr(mod, "forward_core", None)
+        orig = getattr(fc, "_vmamba_b200_original", None)
+        if orig is not None:
+            mod.forward_core = orig
+            n += 1
+    return n

@@ -1,0 +1,235 @@
+"""Operator surface of the reference, backed by the sm_100a kernels of libss2d_b200.so.
+
+Mirrors, name for name, what MzeroMiko/VMamba's modules resolve at call time:
+  selective_scan_fn, SelectiveScanCuda (+ alias SelectiveScanOflex)   classification/models/csms6s.py:71-126,
+                                                                       vmamba.py:837-885
+  cross_scan_fn, cross_merge_fn, CrossScanF, CrossMergeF (+ aliases)  classification/models/csm_triton.py:182-273,
+                                                                       403-517; vmamba.py:254-345, 481-601
+Forward (inference) only.  Tensors must live on a CUDA device; there is no torch/CPU path here
+(`backend="torch"` raises).  Argument meaning, output shapes/dtypes and the error behaviour on bad
+shapes follow the reference.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import CrossParams, NormParams, ScanParams, check, lib
+
+_DTYPES = {torch.float32: _lib.SS2D_F32, torch.float16: _lib.SS2D_F16, torch.bfloat16: _lib.SS2D_BF16}
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}: expected float32, float16 or bfloat16") from None
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("vmamba_b200 operators run on CUDA tensors only (no CPU fallback); "
+                               "use the oracle under oracle/ for CPU reference values")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+# --------------------------------------------------------------------------------------------
+# selective scan
+# --------------------------------------------------------------------------------------------
+def selective_scan_fwd(u, delta, A, B, C, D=None, delta_bias=None, delta_softplus=False, out_float=True):
+    """out = selective scan of (u, delta, A, B, C [, D, delta_bias]); see include/ss2d_b200.h.
+
+    u, delta: (batch, K*C, L); A: (K*C, N); B, C: (batch, K, N, L); D, delta_bias: (K*C,) fp32.
+    Output fp32 if `out_float` (the reference's "oflex") else u.dtype.
+    """
+    _require_cuda(u, delta, A, B, C, D, delta_bias)
+    if u.dim() != 3 or delta.shape != u.shape:
+        raise RuntimeError(f"u and delta must be (batch, dim, L) with equal shapes, got {tuple(u.shape)} {tuple(delta.shape)}")
+    if B.dim() != 4 or C.shape != B.shape:
+        raise RuntimeError("B and C must be (batch, n_groups, dstate, L) with equal shapes")
+    batch, dim, L = u.shape
+    _, K, N, Lb = B.shape
+    if B.shape[0] != batch or Lb != L or dim % K != 0:
+        raise RuntimeError("B/C shape does not match u")
+    if tuple(A.shape) != (dim, N):
+        raise RuntimeError(f"A must be (dim, dstate) = ({dim}, {N}), got {tuple(A.shape)}")
+    if delta.dtype != u.dtype or B.dtype != u.dtype or C.dtype != u.dtype:
+        raise RuntimeError("u, delta, B, C must share one dtype")
+    if u.stride(-1) != 1:
+        u = u.contiguous()
+    if delta.stride(-1) != 1:
+        delta = delta.contiguous()
+    if B.stride(-1) != 1:
+        B = B.contiguous()
+    if C.stride(-1) != 1:
+        C = C.contiguous()
+    A = A.contiguous().float()
+    D = None if D is None else D.contiguous().float()
+    delta_bias = None if delta_bias is None else delta_bias.contiguous().float()
+    if D is not None and D.numel() != dim:
+        raise RuntimeError("D must have dim elements")
+    if delta_bias is not None and delta_bias.numel() != dim:
+        raise RuntimeError("delta_bias must have dim elements")
+    out = torch.empty((batch, dim, L), device=u.device, dtype=torch.float32 if out_float else u.dtype)
+    p = ScanParams()
+    p.u, p.delta, p.A, p.B, p.C, p.D, p.delta_bias, p.out = (_ptr(t) for t in (u, delta, A, B, C, D, delta_bias, out))
+    p.in_dtype, p.out_dtype = dtype_code(u), dtype_code(out)
+    p.delta_softplus = int(bool(delta_softplus))
+    p.batch, p.dim, p.dstate, p.seqlen, p.n_groups = batch, dim, N, L, K
+    p.u_batch_stride, p.u_dim_stride = u.stride(0), u.stride(1)
+    p.delta_batch_stride, p.delta_dim_stride = delta.stride(0), delta.stride(1)
+    p.out_batch_stride, p.out_dim_stride = out.stride(0), out.stride(1)
+    p.B_batch_stride, p.B_group_stride, p.B_state_stride = B.stride(0), B.stride(1), B.stride(2)
+    p.C_batch_stride, p.C_group_stride, p.C_state_stride = C.stride(0), C.stride(1), C.stride(2)
+    with torch.cuda.device(u.device):
+        check(lib().ss2d_selective_scan_fwd(p, _stream(u)), "ss2d_selective_scan_fwd")
+    return out
+
+
+class SelectiveScanCuda(torch.autograd.Function):
+    """Same call signature as the reference Function (csms6s.py:71-87).  Forward only:
+    calling backward raises, this build is an inference drop-in."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(ctx, u, delta, A, B, C, D=None, delta_bias=None, delta_softplus=False, oflex=True, backend=None):
+        if backend == "torch":
+            raise NotImplementedError("backend='torch' is not provided: vmamba_b200 has no eager/CPU path "
+                                      "(reference values come from the oracle under oracle/)")
+        if backend not in (None, "oflex", "mamba", "core"):
+            raise ValueError(f"unknown selective-scan backend {backend!r}")
+        ctx.delta_softplus = delta_softplus
+        ctx.backend = backend
+        return selective_scan_fwd(u, delta, A, B, C, D, delta_bias, delta_softplus, bool(oflex))
+
+    @staticmethod
+    def backward(ctx, dout, *args):
+        raise NotImplementedError("vmamba_b200 implements the forward (inference) path of the selective scan only")
+
+
+SelectiveScanOflex = SelectiveScanCuda   # name used by older revisions of the reference
+
+
+def selective_scan_fn(u, delta, A, B, C, D=None, delta_bias=None, delta_softplus=True, oflex=True, backend=None):
+    """Drop-in for selective_scan_fn (csms6s.py:112-126, vmamba.py:872-885)."""
+    if backend == "torch":
+        raise NotImplementedError("backend='torch' is not provided: vmamba_b200 has no eager/CPU path "
+                                  "(reference values come from the oracle under oracle/)")
+    if torch.is_grad_enabled() and any(isinstance(t, torch.Tensor) and t.requires_grad for t in (u, delta, A, B, C, D, delta_bias)):
+        return SelectiveScanCuda.apply(u, delta, A, B, C, D, delta_bias, delta_softplus, oflex, backend)
+    with torch.autocast("cuda", enabled=False):
+        return selective_scan_fwd(u, delta, A, B, C, D, delta_bias, delta_softplus, bool(oflex))
+
+
+# --------------------------------------------------------------------------------------------
+# CrossScan / CrossMerge
+# --------------------------------------------------------------------------------------------
+def _check_flags(in_channel_first, out_channel_first, one_by_one, scans):
+    if not (in_channel_first and out_channel_first):
+        raise NotImplementedError("vmamba_b200: channel-last CrossScan/CrossMerge is not implemented")
+    if one_by_one:
+        raise NotImplementedError("vmamba_b200: one_by_one CrossScan/CrossMerge is not implemented")
+    if scans not in (0, 1, 2, 3):
+        raise NotImplementedError(f"vmamba_b200: scans={scans} is not implemented")
+
+
+def cross_scan_fwd(x: torch.Tensor, scans: int = 0) -> torch.Tensor:
+    """(B, C, H, W) -> (B, 4, C, H*W), bit-exact data movement (vmamba.py:41-84)."""
+    _require_cuda(x)
+    if x.dim() != 4:
+        raise RuntimeError("cross scan expects a (B, C, H, W) tensor")
+    x = x.contiguous()
+    B, C, H, W = x.shape
+    y = torch.empty((B, 4, C, H * W), device=x.device, dtype=x.dtype)
+    p = CrossParams(x.data_ptr(), y.data_ptr(), dtype_code(x), scans, B, C, H, W)
+    with torch.cuda.device(x.device):
+        check(lib().ss2d_cross_scan(p, _stream(x)), "ss2d_cross_scan")
+    return y
+
+
+def cross_merge_fwd(ys: torch.Tensor, scans: int = 0) -> torch.Tensor:
+    """(B, 4, C, H, W) -> (B, C, H*W) (vmamba.py:87-130)."""
+    _require_cuda(ys)
+    if ys.dim() != 5 or ys.shape[1] != 4:
+        raise RuntimeError("cross merge expects a (B, 4, C, H, W) tensor")
+    ys = ys.contiguous()
+    B, _, C, H, W = ys.shape
+    y = torch.empty((B, C, H * W), device=ys.device, dtype=ys.dtype)
+    p = CrossParams(ys.data_ptr(), y.data_ptr(), dtype_code(ys), scans, B, C, H, W)
+    with torch.cuda.device(ys.device):
+        check(lib().ss2d_cross_merge(p, _stream(ys)), "ss2d_cross_merge")
+    return y
+
+
+class CrossScanF(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, in_channel_first=True, out_channel_first=True, one_by_one=False, scans=0):
+        _check_flags(in_channel_first, out_channel_first, one_by_one, scans)
+        ctx.shape = x.shape
+        return cross_scan_fwd(x, scans)
+
+    @staticmethod
+    def backward(ctx, ys):
+        raise NotImplementedError("vmamba_b200 implements the forward (inference) path of CrossScan only")
+
+
+class CrossMergeF(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ys, in_channel_first=True, out_channel_first=True, one_by_one=False, scans=0):
+        _check_flags(in_channel_first, out_channel_first, one_by_one, scans)
+        return cross_merge_fwd(ys, scans)
+
+    @staticmethod
+    def backward(ctx, x):
+        raise NotImplementedError("vmamba_b200 implements the forward (inference) path of CrossMerge only")
+
+
+# the CUDA-backed Functions stand in for the reference's Triton Functions too
+CrossScanTritonF, CrossMergeTritonF = CrossScanF, CrossMergeF
+CrossScan, CrossMerge = CrossScanF, CrossMergeF
+
+
+def cross_scan_fn(x, in_channel_first=True, out_channel_first=True, one_by_one=False, scans=0, force_torch=False):
+    """Drop-in for cross_scan_fn (vmamba.py:577-588).  `force_torch` is accepted and ignored:
+    there is one implementation."""
+    _check_flags(in_channel_first, out_channel_first, one_by_one, scans)
+    if torch.is_grad_enabled() and x.requires_grad:
+        return CrossScanF.apply(x, in_channel_first, out_channel_first, one_by_one, scans)
+    return cross_scan_fwd(x, scans)
+
+
+def cross_merge_fn(y, in_channel_first=True, out_channel_first=True, one_by_one=False, scans=0, force_torch=False):
+    """Drop-in for cross_merge_fn (vmamba.py:591-601)."""
+    _check_flags(in_channel_first, out_channel_first, one_by_one, scans)
+    if torch.is_grad_enabled() and y.requires_grad:
+        return CrossMergeF.apply(y, in_channel_first, out_channel_first, one_by_one, scans)
+    return cross_merge_fwd(y, scans)
+
+
+# --------------------------------------------------------------------------------------------
+# channel-first LayerNorm (out_norm of SS2D)
+# --------------------------------------------------------------------------------------------
+def layer_norm_cf(y: torch.Tensor, weight=None, bias=None, eps: float = 1e-5, out_dtype=None) -> torch.Tensor:
+    """LayerNorm over dim 1 of an fp32 (B, D, ...) map, as LayerNorm(channel_first=True)
+    (vmamba.py:1078-1093); output in `out_dtype` (default fp32)."""
+    _require_cuda(y, weight, bias)
+    if y.dtype != torch.float32:
+        y = y.float()
+    y = y.contiguous()
+    B, D = y.shape[0], y.shape[1]
+    L = y[0, 0].numel()
+    out = torch.empty(y.shape, device=y.device, dtype=out_dtype or torch.float32)
+    w = None if weight is None else weight.contiguous().float()
+    b = None if bias is None else bias.contiguous().float()
+    p = NormParams(y.data_ptr(), _ptr(w), _ptr(b), out.data_ptr(), B, D, L, 1, dtype_code(out), eps, 0)
+    with torch.cuda.device(y.device):
+        check(lib().ss2d_layer_norm_cf(p, _stream(y)), "ss2d_layer_norm_cf")
+    return out
