@@ -1,0 +1,331 @@
+#!/usr/bin/env python
+"""Benchmark: VMamba-T inference throughput (img/s, 224x224, bf16, batch 128 per GPU) on the
+fused SS2D core, with the roofline of the dominant kernel and a CPU baseline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N > 1 is launched with torchrun (one process per GPU); each rank runs its own replica on its own
+batch shard (weak scaling, no collective on the data path) and the time is the max over ranks.
+`--impl reference` times the CPU oracle (the port of the reference's pure-torch path) on the host
+cores instead, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+MODEL = "vmamba_tiny_s1l8"
+BATCH = 128            # per GPU, the batch the reference quotes its throughput on
+IMG = 224
+NUM_CLASSES = 1000
+METRIC = "VMamba-T img/s @224^2 bf16 (batch 128 per GPU, inference)"
+UNIT = "img/s"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower() == "active":
+                    reasons.add(name)
+        sm.sort()
+        busy = [v for v in sm if v > 0.5 * (mx[0] if mx else 1)] or sm
+        med = busy[len(busy) // 2] if busy else None
+        return {"sm_mhz": med, "sm_max_mhz": mx[0] if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+def synthetic_state_dict(seed: int = 0):
+    """Random init of VMamba-T in the reference's value distributions (no checkpoint can travel)."""
+    from oracle import backbone_oracle as BO     # host-side generator of the synthetic weights only
+    cfg = BO.CONFIGS[MODEL]
+    return BO.random_state_dict(cfg["depths"], cfg["dims"], cfg["d_state"], cfg["ssm_ratio"], 4.0, NUM_CLASSES, 3, seed)
+
+
+def cpu_baseline(sd, n_images: int, repeats: int = 1):
+    """The oracle's VMamba-T forward on the host cores; returns (img/s, cores, description)."""
+    import numpy as np
+    import torch
+    from oracle import backbone_oracle as BO
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    rng = np.random.default_rng(1)
+    img = rng.standard_normal((n_images, 3, IMG, IMG), dtype=np.float32)
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        BO.vssm_logits(img, sd)
+        best = min(best, time.perf_counter() - t0)
+    return n_images / best, cores, f"{n_images} images of the {BATCH}-image batch, fp32, full VMamba-T forward, {cores} threads"
+
+
+def run_reference(args):
+    """`--impl reference`: the CPU oracle on this box's host cores (rank 0 only)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    sd = synthetic_state_dict(0)
+    n_img = 4
+    for _ in range(max(0, min(args.warmup, 1))):
+        cpu_baseline(sd, 1)
+    times = []
+    val = cores = desc = None
+    for _ in range(max(1, min(args.steps, 3))):
+        v, cores, desc = cpu_baseline(sd, n_img)
+        times.append(n_img / v)
+    sec = sum(times) / len(times)
+    val = n_img / sec
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
+        "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{MODEL} inference, {IMG}x{IMG}, CPU oracle (port of the reference's pure-torch path); "
+                               f"each step = {n_img} images", "batch_per_step": n_img},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+def time_events(fn, iters, warmup=3):
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters   # ms
+
+
+def roofline_of_core(model, peak_gbs, peak_kind):
+    """Times the dominant kernel chain alone: the stage-0 SS2D scan+merge (+LayerNorm) of VMamba-T at
+    batch 128 (x 77 MB + delta 308 MB per launch: larger than L2, so every launch streams from HBM)."""
+    import torch
+    from vmamba_b200 import fused
+    w = model.blocks[0][0].core
+    B, D, H, W = BATCH, w.d_inner, IMG // 4, IMG // 4
+    L = H * W
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((B, D, H, W), device="cuda", generator=g).to(model.dtype)
+    proj = fused.project(x, w)
+    ws = torch.empty(B * D * L * 4, device="cuda", dtype=torch.uint8)
+    y = torch.empty((B, D, H, W), device="cuda", dtype=model.dtype)
+    ym = torch.empty((B, D, H, W), device="cuda", dtype=torch.float32)
+    t_chain = time_events(lambda: fused.scan_merge_norm(x, proj, w, with_norm=True, workspace=ws, out=y), 20)
+    t_scan = time_events(lambda: fused.scan_merge_norm(x, proj, w, with_norm=False, out=ym), 20)
+    s = x.element_size()
+    N, K = w.d_state, 4
+    alg = B * L * (D * s + K * D * s + 2 * K * N * s + D * s) + 4 * (K * D * N + 2 * K * D) + 2 * 4 * D
+    scan_bytes = B * L * (D * s + K * D * s + 2 * K * N * s + D * 4)
+    ach = alg / (t_chain * 1e-3) / 1e9
+    return {
+        "bound": "hbm", "achieved": ach, "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs, "traffic": None,
+        "peak_kind": f"of {peak_kind}",
+        "kernel": "core_plane_kernel + layer_norm_cf_kernel (fused SS2D scan+merge+LayerNorm chain)",
+        "workload": f"stage 0 of {MODEL}: B={B} D={D} H=W={H} bf16",
+        "algorithmic_bytes_per_launch": alg, "chain_ms": t_chain,
+        "scan_merge_kernel_ms": t_scan, "scan_merge_kernel_gbs": scan_bytes / (t_scan * 1e-3) / 1e9,
+        "scan_merge_kernel_bytes": scan_bytes,
+    }
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    import vmamba_b200  # noqa: F401  (fails loudly if the CUDA library is missing)
+    from vmamba_b200 import _lib
+    from vmamba_b200.backbone import VSSMInfer
+
+    sd = synthetic_state_dict(0)
+    model = VSSMInfer.from_state_dict(sd, dtype=torch.bfloat16, device=f"cuda:{local}")
+
+    # synthetic images: N(0,1), seeded per rank, bf16 in pinned host memory
+    g = torch.Generator().manual_seed(1234 + rank)
+    host_img = torch.randn((BATCH, 3, IMG, IMG), generator=g).to(torch.bfloat16).pin_memory()
+    host_out = torch.empty((BATCH, NUM_CLASSES), dtype=torch.bfloat16).pin_memory()
+    dev_img = host_img.cuda(non_blocking=True)
+    torch.cuda.synchronize()
+
+    # ---- capture one forward in a CUDA graph (static input / output buffers) -------------------
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            model(dev_img)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    l0 = _lib.launch_count()
+    with torch.cuda.graph(graph):
+        dev_out = model(dev_img)
+    launches_per_forward = _lib.launch_count() - l0
+    graph.replay()
+    torch.cuda.synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn, steps, warmup):
+        for _ in range(warmup):
+            step_fn()
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(steps):
+            step_fn()
+        e.record()
+        barrier()
+        ms = s.elapsed_time(e)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def step_device():
+        graph.replay()
+
+    def step_e2e():
+        dev_img.copy_(host_img, non_blocking=True)
+        graph.replay()
+        host_out.copy_(dev_out, non_blocking=True)
+
+    warm = max(args.warmup, 3)
+    sampler = ClockSampler(local).start() if rank == 0 else None
+    ms_dev = timed(step_device, args.steps, warm)
+    clocks = sampler.stop() if sampler else None
+    ms_e2e = timed(step_e2e, args.steps, warm)
+
+    total_imgs = BATCH * world * args.steps
+    value = total_imgs / (ms_dev * 1e-3)
+    e2e = total_imgs / (ms_e2e * 1e-3)
+
+    roof = cpu = None
+    if rank == 0:
+        peak, kind = peaks()
+        roof = roofline_of_core(model, peak, kind)
+        if world == 1 and not args.no_cpu_baseline:
+            v, cores, desc = cpu_baseline(sd, 4)
+            cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    act_mb = BATCH * 96 * 56 * 56 * 2 / 1e6
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
+        "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{MODEL} (VMamba-T, dims 96/192/384/768, depths 2/2/8/2, v05_noz, d_state 1) "
+                               f"backbone inference, random init, {BATCH} images of 3x{IMG}x{IMG} per GPU per step",
+                   "global_batch": BATCH * world, "parallelism": f"replicas x{world}, batch-sharded, no collective",
+                   "l2": f"no flush needed: one stage-0 activation is {act_mb:.0f} MB and a step streams several GB, "
+                         "far more than the 126 MB L2",
+                   "precision": "bf16 activations into every contraction, fp32 LayerNorm statistics, fp32 residual "
+                                "stream, fp32 scan state", "cuda_graph": True,
+                   "published_reference": "1686 img/s on A100, fp32 without AMP (README.md:91) - other hardware and "
+                                          "precision, so vs_baseline stays null"},
+        "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": host_img.numel() * 2 * world,
+                "d2h_bytes_per_step": host_out.numel() * 2 * world, "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": launches_per_forward * args.steps * world,
+        "gpu_launches_per_step_per_gpu": launches_per_forward,
+        "clocks": clocks, "roofline": roof,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

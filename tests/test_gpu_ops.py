@@ -260,3 +260,38 @@ def test_launches_are_counted(vb):
     before = _lib.launch_count()
     vb.cross_scan_fn(torch.zeros(1, 1, 2, 2, device="cuda"))
     assert _lib.launch_count() == before + 1
+
+
+# ------------------------------------------------------------------------------ backbone
+def _load_small_backbone():
+    g = np.load(os.path.join(G, "vssm_small.npz"))
+    sd = {k[3:]: g[k] for k in g.files if k.startswith("sd_")}
+    f = np.load(os.path.join(G, "vssm_small_features.npz"))
+    sd.update({k[3:]: f[k] for k in f.files if k.startswith("sd_")})
+    return g, f, sd
+
+
+def test_backbone_fp32_vs_reference_golden(vb):
+    from vmamba_b200.backbone import VSSMInfer
+    g, f, sd = _load_small_backbone()
+    old = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        m = VSSMInfer.from_state_dict(sd, dtype=torch.float32)
+        logits = m(dev(g["img"]))
+        feats = m.features(dev(g["img"]))
+    finally:
+        torch.backends.cudnn.allow_tf32 = old
+    assert O.max_rel_err(host(logits), g["logits"]) <= TOL_F32
+    assert np.array_equal(host(logits).argmax(1), g["logits"].argmax(1))
+    for i, o in enumerate(feats):
+        assert O.max_rel_err(host(o), f[f"feat{i}"]) <= TOL_F32
+
+
+def test_backbone_bf16_vs_reference_golden(vb):
+    from vmamba_b200.backbone import VSSMInfer
+    g, f, sd = _load_small_backbone()
+    m = VSSMInfer.from_state_dict(sd, dtype=torch.bfloat16)
+    logits = m(dev(g["img"]))
+    assert logits.dtype == torch.bfloat16
+    assert O.max_rel_err(host(logits), g["logits"]) <= TOL_BF16

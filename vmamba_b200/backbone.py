@@ -1,0 +1,175 @@
+"""Inference-only VMamba backbone around the fused SS2D core.
+
+Host-side mirror of the reference's `VSSM` / `Backbone_VSSM` forward for the model family the
+headline numbers are quoted on: forward_type "v05_noz", channel-first ("ln2d"), patch embed v2,
+downsample v3, ssm_conv 3 without bias (vmamba.py:2250-2300).  It consumes a state dict in the
+reference's own key layout (vmamba.py:1788-2035), so weights trained with or initialised by the
+reference load unchanged.
+
+Only the SS2D core and the channel-first LayerNorms are this package's kernels; the dense
+contractions (1x1 projections, MLP, strided 3x3 convolutions) are library calls, the rest are
+elementwise torch ops.  Precision follows the reference's autocast recipe: bf16 (or fp16/fp32)
+activations into every contraction, fp32 LayerNorm statistics, fp32 residual stream, fp32 state in
+the scan.
+"""
+from __future__ import annotations
+
+import math
+import re
+from typing import Dict, List, Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+from . import ops
+from .fused import CoreWeights, ss2d_core
+
+# vmamba.py:2286-2300 (tiny), 2250-2264 (small), 2268-2282 (base)
+CONFIGS = dict(
+    vmamba_tiny_s1l8=dict(depths=[2, 2, 8, 2], dims=[96, 192, 384, 768], d_state=1, ssm_ratio=1.0),
+    vmamba_small_s2l15=dict(depths=[2, 2, 15, 2], dims=[96, 192, 384, 768], d_state=1, ssm_ratio=2.0),
+    vmamba_base_s2l15=dict(depths=[2, 2, 15, 2], dims=[128, 256, 512, 1024], d_state=1, ssm_ratio=2.0),
+)
+
+
+class _Block:
+    __slots__ = ("n1w", "n1b", "w_in", "w_dw", "core", "w_out", "n2w", "n2b", "w1", "b1", "w2", "b2", "D")
+
+
+class VSSMInfer:
+    """Functional VMamba forward.  `VSSMInfer.from_state_dict(sd, dtype=torch.bfloat16)`."""
+
+    def __init__(self):
+        self.blocks: List[List[_Block]] = []
+        self.down: List[Optional[dict]] = []
+        self.stem: dict = {}
+        self.head: Optional[dict] = None
+        self.outnorm: Dict[int, tuple] = {}
+        self.dtype = torch.bfloat16
+        self.device = torch.device("cuda")
+
+    # ------------------------------------------------------------------ construction
+    @staticmethod
+    def from_state_dict(sd: dict, dtype=torch.bfloat16, device="cuda") -> "VSSMInfer":
+        dev = torch.device(device)
+        m = VSSMInfer()
+        m.dtype, m.device = dtype, dev
+
+        def T(name, dt=None):
+            v = sd[name]
+            v = torch.as_tensor(v) if not isinstance(v, torch.Tensor) else v
+            return v.detach().to(device=dev, dtype=dt or torch.float32).contiguous()
+
+        depths = {}
+        for k in sd:
+            mt = re.match(r"layers\.(\d+)\.blocks\.(\d+)\.", k)
+            if mt:
+                i, j = int(mt.group(1)), int(mt.group(2))
+                depths[i] = max(depths.get(i, 0), j + 1)
+        m.stem = dict(w0=T("patch_embed.0.weight", dtype), b0=T("patch_embed.0.bias", dtype),
+                      n0w=T("patch_embed.2.weight"), n0b=T("patch_embed.2.bias"),
+                      w1=T("patch_embed.5.weight", dtype), b1=T("patch_embed.5.bias", dtype),
+                      n1w=T("patch_embed.7.weight"), n1b=T("patch_embed.7.bias"))
+        for i in sorted(depths):
+            stage = []
+            for j in range(depths[i]):
+                p = f"layers.{i}.blocks.{j}."
+                if p + "op.in_proj.bias" in sd or p + "op.conv2d.bias" in sd:
+                    raise NotImplementedError("in_proj / conv2d biases are not part of the v05_noz family")
+                b = _Block()
+                b.n1w, b.n1b = T(p + "norm.weight"), T(p + "norm.bias")
+                b.w_in = T(p + "op.in_proj.weight", dtype)
+                b.D = b.w_in.shape[0]
+                if sd[p + "op.out_proj.weight"].shape[1] != b.D:
+                    raise NotImplementedError("models with a z branch (no '_noz') are not supported")
+                b.w_dw = T(p + "op.conv2d.weight", dtype)
+                N = sd[p + "op.A_logs"].shape[1]
+                R = sd[p + "op.dt_projs.weight"].shape[1]
+                b.core = CoreWeights.build(T(p + "op.x_proj.weight"), T(p + "op.dt_projs.weight"),
+                                           T(p + "op.dt_projs_bias"), T(p + "op.A_logs"), T(p + "op.Ds"),
+                                           T(p + "op.out_norm.weight"), T(p + "op.out_norm.bias"),
+                                           d_state=N, dt_rank=R, dtype=dtype)
+                b.w_out = T(p + "op.out_proj.weight", dtype)
+                b.n2w, b.n2b = T(p + "norm2.weight"), T(p + "norm2.bias")
+                b.w1, b.b1 = T(p + "mlp.fc1.weight", dtype), T(p + "mlp.fc1.bias", dtype)
+                b.w2, b.b2 = T(p + "mlp.fc2.weight", dtype), T(p + "mlp.fc2.bias", dtype)
+                stage.append(b)
+            m.blocks.append(stage)
+            q = f"layers.{i}.downsample."
+            if q + "1.weight" in sd:
+                m.down.append(dict(w=T(q + "1.weight", dtype), b=T(q + "1.bias", dtype),
+                                   nw=T(q + "3.weight"), nb=T(q + "3.bias")))
+            else:
+                m.down.append(None)
+            if f"outnorm{i}.weight" in sd:
+                m.outnorm[i] = (T(f"outnorm{i}.weight"), T(f"outnorm{i}.bias"))
+        if "classifier.head.weight" in sd:
+            m.head = dict(nw=T("classifier.norm.weight"), nb=T("classifier.norm.bias"),
+                          w=T("classifier.head.weight", dtype), b=T("classifier.head.bias", dtype))
+        return m
+
+    # ------------------------------------------------------------------ layers
+    def _ln(self, x, w, b, out_dtype=None):
+        """channel-first LayerNorm (vmamba.py:1078-1093), fp32 statistics."""
+        return ops.layer_norm_cf(x, w, b, 1e-5, out_dtype or self.dtype)
+
+    @staticmethod
+    def _pw(w, x, bias=None):
+        """1x1 convolution of a channel-first map as a batched GEMM (vmamba.py:1060-1064)."""
+        B, C, H, W = x.shape
+        y = torch.matmul(w, x.view(B, C, H * W))
+        if bias is not None:
+            y += bias.view(1, -1, 1)
+        return y.view(B, w.shape[0], H, W)
+
+    def _block(self, x: torch.Tensor, b: _Block) -> torch.Tensor:
+        """VSSBlock._forward, eval mode (vmamba.py:1766-1778).  x: fp32 residual stream."""
+        h = self._ln(x, b.n1w, b.n1b)
+        h = self._pw(b.w_in, h)                                       # in_proj          :1574
+        h = F.silu(F.conv2d(h, b.w_dw, None, padding=1, groups=b.D))  # dwconv 3x3, SiLU :1582-1583
+        h = ss2d_core(h, b.core)                                      # forward_core     :1584
+        x = x + self._pw(b.w_out, h)                                  # out_proj + skip  :1588, 1772
+        h = self._ln(x, b.n2w, b.n2b)
+        h = F.gelu(self._pw(b.w1, h, b.b1))                           # Mlp              :1160-1166
+        return x + self._pw(b.w2, h, b.b2)
+
+    def _stem(self, img):
+        s = self.stem
+        x = F.conv2d(img.to(self.dtype), s["w0"], s["b0"], stride=2, padding=1)
+        x = F.gelu(self._ln(x.float(), s["n0w"], s["n0b"]))
+        x = F.conv2d(x, s["w1"], s["b1"], stride=2, padding=1)
+        return self._ln(x.float(), s["n1w"], s["n1b"], torch.float32)
+
+    def _stages(self, img):
+        x = self._stem(img)
+        outs = []
+        for i, stage in enumerate(self.blocks):
+            for b in stage:
+                x = self._block(x, b)
+            outs.append(x)
+            d = self.down[i]
+            if d is not None:      # downsample v3 (vmamba.py:1964-1971)
+                y = F.conv2d(x.to(self.dtype), d["w"], d["b"], stride=2, padding=1)
+                x = self._ln(y.float(), d["nw"], d["nb"], torch.float32)
+        return outs, x
+
+    # ------------------------------------------------------------------ public
+    @torch.no_grad()
+    def __call__(self, img: torch.Tensor) -> torch.Tensor:
+        """VSSM.forward (vmamba.py:2027-2035): (B, 3, H, W) -> (B, num_classes) logits."""
+        if self.head is None:
+            raise RuntimeError("this model was built without a classifier")
+        _, x = self._stages(img)
+        hd = self.head
+        x = self._ln(x, hd["nw"], hd["nb"], torch.float32).mean(dim=(2, 3))
+        return F.linear(x.to(self.dtype), hd["w"], hd["b"])
+
+    @torch.no_grad()
+    def features(self, img: torch.Tensor, out_indices: Sequence[int] = (0, 1, 2, 3)):
+        """Backbone_VSSM.forward (vmamba.py:2133-2153): LayerNorm'ed per-stage maps."""
+        outs, _ = self._stages(img)
+        res = []
+        for i in out_indices:
+            w, b = self.outnorm[i]
+            res.append(self._ln(outs[i], w, b, torch.float32))
+        return res

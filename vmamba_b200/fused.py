@@ -76,6 +76,55 @@ def project(x: torch.Tensor, w: CoreWeights):
     return xd_even, xd_odd, delta_even, delta_odd
 
 
+def scan_merge_norm(x: torch.Tensor, proj, w: CoreWeights, *, with_norm: bool = True, out_dtype=None,
+                    workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The CUDA part of the fused core (`ss2d_core_fwd`): x plus the projections returned by
+    `project` -> merged (and normalised) map.  Launches one scan+merge kernel and, with
+    `with_norm`, one LayerNorm kernel; allocates the output and the fp32 workspace unless given."""
+    xd_even, xd_odd, delta_even, delta_odd = proj
+    B, D, H, W = x.shape
+    R, N = w.dt_rank, w.d_state
+    out_dtype = out_dtype or (x.dtype if with_norm else torch.float32)
+    y = out if out is not None else torch.empty((B, D, H, W), device=x.device, dtype=out_dtype)
+    p = CoreParams()
+    p.x = x.data_ptr()
+    srcs = (xd_even, xd_odd)
+    deltas = (delta_even, delta_odd)
+    esz = x.element_size()
+    for k in range(K):
+        j, i = k % 2, k // 2          # j: orientation (0 row, 1 column); i: index inside the pair
+        xd, dl = srcs[j], deltas[j]
+        p.delta[k] = dl.data_ptr() + i * dl.stride(1) * esz
+        p.delta_batch_stride[k] = dl.stride(0)
+        base = xd.data_ptr() + i * xd.stride(1) * esz
+        p.Bm[k] = base + R * xd.stride(2) * esz
+        p.Cm[k] = base + (R + N) * xd.stride(2) * esz
+        p.bc_batch_stride[k] = xd.stride(0)
+    p.A, p.Dskip, p.delta_bias = w.A.data_ptr(), w.Ds.data_ptr(), w.dt_bias.data_ptr()
+    p.ln_weight = None if w.ln_weight is None else w.ln_weight.data_ptr()
+    p.ln_bias = None if w.ln_bias is None else w.ln_bias.data_ptr()
+    p.y = y.data_ptr()
+    p.B, p.D, p.H, p.W, p.N = B, D, H, W, N
+    p.act_dtype, p.y_dtype = ops.dtype_code(x), ops.dtype_code(y)
+    p.with_norm, p.ln_eps = int(with_norm), w.eps
+    need = int(lib().ss2d_core_workspace_bytes(p))
+    if need < 0:
+        raise RuntimeError("ss2d_core_workspace_bytes: invalid arguments")
+    if need > 0:
+        if workspace is None or workspace.numel() * workspace.element_size() < need:
+            workspace = torch.empty(need, device=x.device, dtype=torch.uint8)
+        p.workspace, p.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    with torch.cuda.device(x.device):
+        check(lib().ss2d_core_fwd(p, torch.cuda.current_stream(x.device).cuda_stream), "ss2d_core_fwd")
+    return y
+
+
+def fused_supported(x_shape, d_state: int) -> bool:
+    """True when `ss2d_core_fwd` handles the case itself (d_state 1, plane fits one CTA)."""
+    L = x_shape[2] * x_shape[3]
+    return d_state == 1 and (L // _vec_of(L)) <= 1024
+
+
 def ss2d_core(x: torch.Tensor, w: CoreWeights, *, with_norm: bool = True, out_dtype=None,
               workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Fused forward of the SS2D core.  x: (B, D, H, W) CUDA tensor; returns (B, D, H, W) in
@@ -84,47 +133,13 @@ def ss2d_core(x: torch.Tensor, w: CoreWeights, *, with_norm: bool = True, out_dt
     if not x.is_cuda:
         raise RuntimeError("vmamba_b200.ss2d_core runs on CUDA tensors only (no CPU fallback)")
     x = x.contiguous()
-    B, D, H, W = x.shape
-    if D != w.d_inner:
-        raise RuntimeError(f"x has {D} channels, weights were built for {w.d_inner}")
-    L, R, N = H * W, w.dt_rank, w.d_state
+    if x.shape[1] != w.d_inner:
+        raise RuntimeError(f"x has {x.shape[1]} channels, weights were built for {w.d_inner}")
     out_dtype = out_dtype or (x.dtype if with_norm else torch.float32)
     with torch.autocast("cuda", enabled=False):
-        if N != 1 or (L // _vec_of(L)) > 1024:
+        if not fused_supported(x.shape, w.d_state):
             return _ss2d_core_unfused(x, w, with_norm, out_dtype)
-        xd_even, xd_odd, delta_even, delta_odd = project(x, w)
-        y = torch.empty((B, D, H, W), device=x.device, dtype=out_dtype)
-        p = CoreParams()
-        p.x = x.data_ptr()
-        srcs = (xd_even, xd_odd)
-        deltas = (delta_even, delta_odd)
-        esz = x.element_size()
-        for k in range(K):
-            j, i = k % 2, k // 2          # j: orientation (0 row, 1 column); i: index inside the pair
-            xd, dl = srcs[j], deltas[j]
-            p.delta[k] = dl.data_ptr() + i * dl.stride(1) * esz
-            p.delta_batch_stride[k] = dl.stride(0)
-            base = xd.data_ptr() + i * xd.stride(1) * esz
-            p.Bm[k] = base + R * xd.stride(2) * esz
-            p.Cm[k] = base + (R + N) * xd.stride(2) * esz
-            p.bc_batch_stride[k] = xd.stride(0)
-        p.A, p.Dskip, p.delta_bias = w.A.data_ptr(), w.Ds.data_ptr(), w.dt_bias.data_ptr()
-        p.ln_weight = None if w.ln_weight is None else w.ln_weight.data_ptr()
-        p.ln_bias = None if w.ln_bias is None else w.ln_bias.data_ptr()
-        p.y = y.data_ptr()
-        p.B, p.D, p.H, p.W, p.N = B, D, H, W, N
-        p.act_dtype, p.y_dtype = ops.dtype_code(x), ops.dtype_code(y)
-        p.with_norm, p.ln_eps = int(with_norm), w.eps
-        need = int(lib().ss2d_core_workspace_bytes(p))
-        if need < 0:
-            raise RuntimeError("ss2d_core_workspace_bytes: invalid arguments")
-        if need > 0:
-            if workspace is None or workspace.numel() * workspace.element_size() < need:
-                workspace = torch.empty(need, device=x.device, dtype=torch.uint8)
-            p.workspace, p.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
-        with torch.cuda.device(x.device):
-            check(lib().ss2d_core_fwd(p, torch.cuda.current_stream(x.device).cuda_stream), "ss2d_core_fwd")
-        return y
+        return scan_merge_norm(x, project(x, w), w, with_norm=with_norm, out_dtype=out_dtype, workspace=workspace)
 
 
 def _vec_of(L: int) -> int:
