@@ -160,13 +160,13 @@ def time_events(fn, iters, warmup=3):
     return s.elapsed_time(e) / iters   # ms
 
 
-def roofline_of_core(model, peak_gbs, peak_kind):
+def roofline_of_core(model, peak_gbs, peak_kind, batch=None, iters=20):
     """Times the dominant kernel chain alone: the stage-0 SS2D scan+merge (+LayerNorm) of VMamba-T at
     batch 128 (x 77 MB + delta 308 MB per launch: larger than L2, so every launch streams from HBM)."""
     import torch
     from vmamba_b200 import fused
     w = model.blocks[0][0].core
-    B, D, H, W = BATCH, w.d_inner, IMG // 4, IMG // 4
+    B, D, H, W = batch or BATCH, w.d_inner, IMG // 4, IMG // 4
     L = H * W
     g = torch.Generator(device="cuda").manual_seed(0)
     x = torch.randn((B, D, H, W), device="cuda", generator=g).to(model.dtype)
@@ -174,8 +174,8 @@ def roofline_of_core(model, peak_gbs, peak_kind):
     ws = torch.empty(B * D * L * 4, device="cuda", dtype=torch.uint8)
     y = torch.empty((B, D, H, W), device="cuda", dtype=model.dtype)
     ym = torch.empty((B, D, H, W), device="cuda", dtype=torch.float32)
-    t_chain = time_events(lambda: fused.scan_merge_norm(x, proj, w, with_norm=True, workspace=ws, out=y), 20)
-    t_scan = time_events(lambda: fused.scan_merge_norm(x, proj, w, with_norm=False, out=ym), 20)
+    t_chain = time_events(lambda: fused.scan_merge_norm(x, proj, w, with_norm=True, workspace=ws, out=y), iters)
+    t_scan = time_events(lambda: fused.scan_merge_norm(x, proj, w, with_norm=False, out=ym), iters)
     s = x.element_size()
     N, K = w.d_state, 4
     alg = B * L * (D * s + K * D * s + 2 * K * N * s + D * s) + 4 * (K * D * N + 2 * K * D) + 2 * 4 * D
@@ -211,6 +211,10 @@ def run_ours(args):
 
     sd = synthetic_state_dict(0)
     model = VSSMInfer.from_state_dict(sd, dtype=torch.bfloat16, device=f"cuda:{local}")
+    if args.roofline_only:     # the dominant kernel chain alone (small cases for profiler captures)
+        peak, kind = peaks()
+        print(json.dumps({"roofline": roofline_of_core(model, peak, kind, args.roofline_batch, args.steps)}), flush=True)
+        return
 
     # synthetic images: N(0,1), seeded per rank, bf16 in pinned host memory
     g = torch.Generator().manual_seed(1234 + rank)
@@ -320,6 +324,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--roofline-only", action="store_true", help="time only the fused SS2D core chain of stage 0")
+    ap.add_argument("--roofline-batch", type=int, default=None, help="batch for --roofline-only (default 128)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
