@@ -45,7 +45,7 @@ typedef enum ss2d_status {
  * selective_scan_torch (csms6s.py:25-68).
  *
  * For every row (b, r), r in [0, dim), group k = r / (dim / n_groups), state h in R^dstate = 0:
- *   dl   = delta[b, r % delta_dim ... see note] (+ delta_bias[r]) ; dl = softplus(dl) if delta_softplus
+ *   dl   = delta[b, r, l] (+ delta_bias[r]) ; dl = softplus(dl) if delta_softplus
  *   h_n  = exp(dl * A[r, n]) * h_n + dl * B[b, k, n, l] * u[b, r, l]
  *   out[b, r, l] = sum_n C[b, k, n, l] * h_n (+ D[r] * u[b, r, l])
  * u, delta, out: (batch, dim, seqlen), last dimension contiguous, strides in elements.
@@ -101,7 +101,8 @@ int ss2d_cross_merge(const ss2d_cross_params *p, void *cuda_stream);
  *   delta[k] (B, D, L) per route k, act_dtype, contiguous planes (batch stride given), raw
  *            (pre-bias, pre-softplus) step sizes, stored in the ORIENTATION ORDER of route k:
  *            index h*W+w for k = 0, 2 and w*H+h for k = 1, 3 (never reversed)
- *   Bm[k], Cm[k] (B, N, L) per route, same order and dtype
+ *   Bm[k], Cm[k] (B, N, L) per route, same order, always fp32 (values may have been rounded to
+ *            act_dtype by the projection that produced them)
  *   A (4*D, N), Dskip (4*D), delta_bias (4*D): fp32, row index k*D + d
  *   ln_weight, ln_bias (D) fp32 or NULL (NULL: no affine); ln_eps; with_norm = 0 skips LayerNorm
  *   y        (B, D, H, W) contiguous, y_dtype (act_dtype or SS2D_F32)

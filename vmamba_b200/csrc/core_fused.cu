@@ -26,18 +26,21 @@ namespace ss2d {
 struct CoreArgs {
     const void* x;
     const void* delta[4];
-    const void* Bm[4];
-    const void* Cm[4];
+    const float* Bm[4];
+    const float* Cm[4];
     const float *A, *Dskip, *bias;
     float* merged;
     long long d_bs[4], bc_bs[4];
     int B, D, H, W, L, G, PP, Wp, groups_per_image;
+    unsigned magic_G, magic_W, magic_H;   // ceil(2^32 / d): n / d == umulhi(n, magic) for n * d < 2^32
 };
 
 struct ScanScratch {
     AB wtot[2][32];
     float wpre[2][32];
 };
+
+__device__ __forceinline__ int fast_div(int n, unsigned magic) { return magic ? (int)__umulhi((unsigned)n, magic) : n; }   // magic 0: divisor 1
 
 // CTA-wide scan of per-thread aggregates in thread order (forward) and in reverse thread order
 // (backward).  The state before the first thread is zero, so only the state entering each thread
@@ -72,19 +75,40 @@ __device__ __forceinline__ void cta_scan_pair(AB f, AB bk, int lane, int warp, i
     hin_b = fmaf(ra, s.wpre[1][warp], rb);
 }
 
+// Per-row constants of one route, pre-scaled for the arithmetic below.
+struct RouteConst {
+    float A;        // A (negative): decay = 2^(A * log2(1 + e^x))
+    float bias2;    // delta_bias * log2(e)
+    float bias;     // delta_bias
+};
+
 // One direction of one route over the VEC register elements of a thread.
+// `ul` holds u * ln2.  With t = log2(1 + e^x), x = delta + bias:  softplus(x) = ln2 * t  and
+// exp(softplus(x) * A) = 2^(A t), so one ex2 and one lg2 serve both the step size and the decay.
 // Adds C*h_local to ysum, leaves C*prod(a) in cP, returns the thread aggregate.
-template <int VEC, bool kForward>
-__device__ __forceinline__ AB route_local(const float (&u)[VEC], const float (&dv)[VEC], const float (&bv)[VEC],
-                                          const float (&cv)[VEC], float A2, float bias, float (&cP)[VEC],
+// kPrecise (fp32 tensors): softplus keeps torch's threshold and a series for small e^x, so that
+// the result is accurate to fp32 rounding; otherwise (16-bit tensors, whose own rounding is four
+// orders of magnitude coarser) the shortest instruction sequence is used.
+template <int VEC, bool kForward, bool kPrecise>
+__device__ __forceinline__ AB route_local(const float (&ul)[VEC], const float (&dv)[VEC], const float (&bv)[VEC],
+                                          const float (&cv)[VEC], const RouteConst rc, float (&cP)[VEC],
                                           float (&ysum)[VEC]) {
     float p = 1.f, h = 0.f;
 #pragma unroll
     for (int ii = 0; ii < VEC; ++ii) {
         const int i = kForward ? ii : VEC - 1 - ii;
-        const float dl = softplus_fast(dv[i] + bias);
-        const float aa = decay_fast(dl, A2);
-        h = fmaf(aa, h, dl * bv[i] * u[i]);
+        float t, aa;
+        if constexpr (kPrecise) {
+            const float dl = softplus_fast(dv[i] + rc.bias);
+            t = dl * kLog2e;
+            aa = ex2_approx(t * rc.A);
+        } else {
+            // clamp keeps e^x finite; above x = 87 the reference returns x itself
+            const float e = ex2_approx(fminf(fmaf(dv[i], kLog2e, rc.bias2), 126.f));
+            t = lg2_approx(1.0f + e);
+            aa = ex2_approx(t * rc.A);
+        }
+        h = fmaf(aa, h, t * (bv[i] * ul[i]));
         p *= aa;
         cP[i] = cv[i] * p;
         ysum[i] = fmaf(cv[i], h, ysum[i]);
@@ -92,22 +116,38 @@ __device__ __forceinline__ AB route_local(const float (&u)[VEC], const float (&d
     return AB{p, h};
 }
 
+// Shared-memory word of element i of a VEC-segment that starts at (major0, minor0) of a plane
+// walked with `minor` fastest (length n_minor), stored with `minor_stride` / `major_stride`.
+// A segment covers at most two lines because VEC <= n_minor.
+template <int VEC>
+struct SegAddr {
+    int a0, n1, jump;
+    __device__ __forceinline__ SegAddr(int major0, int minor0, int n_minor, int major_stride, int minor_stride) {
+        a0 = major0 * major_stride + minor0 * minor_stride;
+        n1 = n_minor - minor0;                                   // elements left in the first line
+        jump = major_stride - n_minor * minor_stride;            // extra offset once the line wraps
+    }
+    __device__ __forceinline__ int at(int i, int minor_stride) const { return a0 + i * minor_stride + (i >= n1 ? jump : 0); }
+};
+
 template <typename T, int VEC, int MAXT, int MINB>
 __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a) {
     extern __shared__ __align__(16) float smem[];
     __shared__ ScanScratch scr;
+    constexpr bool kPrecise = sizeof(T) == 4;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = (blockDim.x + 31) >> 5;
     const int b = blockIdx.x / a.groups_per_image;
-    const int d0 = (blockIdx.x % a.groups_per_image) * a.PP;
+    const int d0 = (blockIdx.x - b * a.groups_per_image) * a.PP;
     const int pp_here = min(a.PP, a.D - d0);
-    const int pl = t / a.G, v = t - pl * a.G;
+    const int pl = fast_div(t, a.magic_G), v = t - pl * a.G;
     const bool active = pl < pp_here;
     const int d = d0 + pl;
     const int L = a.L, H = a.H, W = a.W, Wp = a.Wp, D = a.D;
-    const int plane_words = H * Wp;
-    float* xs = smem + (size_t)pl * plane_words;                       // x, fp32, pitch Wp
-    float* ys = smem + (size_t)(a.PP + pl) * plane_words;              // column-orientation result
+    // one padded fp32 plane per channel: first x (for the transposed read), then, once every
+    // column-orientation thread has taken its x values, the column-orientation result
+    float* plane = smem + (size_t)pl * (H * Wp);
     using VT = Vec<T, VEC>;
+    using VF = Vec<float, VEC>;
     const int e0 = v * VEC;   // first element of this thread in either orientation order
     const long long plane_off = (long long)d * L + e0;
 
@@ -120,45 +160,46 @@ __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a
         rd1 = VT::load_raw((const T*)a.delta[1] + b * a.d_bs[1] + plane_off);
         rd3 = VT::load_raw((const T*)a.delta[3] + b * a.d_bs[3] + plane_off);
     }
-    float u[VEC], yrow[VEC];
-    VT::unpack(rx, u);
+    float ul[VEC], yrow[VEC];
+    VT::unpack(rx, ul);
 
-    // ---- x into shared memory for the transposed read -----------------------------------------
-    int h = 0, w = 0;
+    // ---- x into shared memory (row-major, padded pitch) -------------------------------------
+    const int h0 = fast_div(e0, a.magic_W), w0 = e0 - h0 * W;
+    const SegAddr<VEC> rs(h0, w0, W, Wp, 1);
     if (active) {
-        h = e0 / W; w = e0 - h * W;
-        int hh = h, ww = w;
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-            xs[hh * Wp + ww] = u[i];
-            if (++ww == W) { ww = 0; ++hh; }
-        }
+        for (int i = 0; i < VEC; ++i) plane[rs.at(i, 1)] = ul[i];
     }
+    const int wc = fast_div(e0, a.magic_H), hc = e0 - wc * H;
+    const SegAddr<VEC> cs(wc, hc, H, 1, Wp);   // column-major walk: h is the fast index, stride Wp
 
     // ---- row orientation: routes 0 (forward) and 2 (backward) ---------------------------------
     {
         float dv[VEC], bv[VEC], cv[VEC], cPf[VEC], cPb[VEC];
         AB af{1.f, 0.f}, ab{1.f, 0.f};
         if (active) {
-            const float D0 = __ldg(a.Dskip + d), D2 = __ldg(a.Dskip + 2 * D + d);
+            const float Dsum = (__ldg(a.Dskip + d) + __ldg(a.Dskip + 2 * D + d));
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) yrow[i] = (D0 + D2) * u[i];
+            for (int i = 0; i < VEC; ++i) { yrow[i] = Dsum * ul[i]; ul[i] *= kLn2; }
+            RouteConst rc;
+            rc.A = __ldg(a.A + d); rc.bias = __ldg(a.bias + d); rc.bias2 = rc.bias * kLog2e;
             VT::unpack(rd0, dv);
-            VT::load((const T*)a.Bm[0] + b * a.bc_bs[0] + e0, bv);
-            VT::load((const T*)a.Cm[0] + b * a.bc_bs[0] + e0, cv);
-            af = route_local<VEC, true>(u, dv, bv, cv, __ldg(a.A + d) * kLog2e, __ldg(a.bias + d), cPf, yrow);
+            VF::load(a.Bm[0] + b * a.bc_bs[0] + e0, bv);
+            VF::load(a.Cm[0] + b * a.bc_bs[0] + e0, cv);
+            af = route_local<VEC, true, kPrecise>(ul, dv, bv, cv, rc, cPf, yrow);
             if (v == 0) af.a = 0.f;
+            rc.A = __ldg(a.A + 2 * D + d); rc.bias = __ldg(a.bias + 2 * D + d); rc.bias2 = rc.bias * kLog2e;
             VT::unpack(rd2, dv);
-            VT::load((const T*)a.Bm[2] + b * a.bc_bs[2] + e0, bv);
-            VT::load((const T*)a.Cm[2] + b * a.bc_bs[2] + e0, cv);
-            ab = route_local<VEC, false>(u, dv, bv, cv, __ldg(a.A + 2 * D + d) * kLog2e, __ldg(a.bias + 2 * D + d), cPb, yrow);
+            VF::load(a.Bm[2] + b * a.bc_bs[2] + e0, bv);
+            VF::load(a.Cm[2] + b * a.bc_bs[2] + e0, cv);
+            ab = route_local<VEC, false, kPrecise>(ul, dv, bv, cv, rc, cPb, yrow);
             if (v == a.G - 1) ab.a = 0.f;
         } else {
 #pragma unroll
             for (int i = 0; i < VEC; ++i) { yrow[i] = 0.f; cPf[i] = 0.f; cPb[i] = 0.f; }
         }
         float hf, hb;
-        cta_scan_pair(af, ab, lane, warp, nwarps, scr, hf, hb);   // also orders the xs stores before the reads below
+        cta_scan_pair(af, ab, lane, warp, nwarps, scr, hf, hb);   // its barriers also order the x stores before the reads below
         if (v == 0) hf = 0.f;
         if (v == a.G - 1) hb = 0.f;
 #pragma unroll
@@ -167,58 +208,47 @@ __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a
 
     // ---- column orientation: routes 1 (forward) and 3 (backward) -------------------------------
     {
-        float dv[VEC], bv[VEC], cv[VEC], cPf[VEC], cPb[VEC], ycol[VEC], ut[VEC];
+        float dv[VEC], bv[VEC], cv[VEC], cPf[VEC], cPb[VEC], ycol[VEC];
         AB af{1.f, 0.f}, ab{1.f, 0.f};
-        int wc = 0, hc = 0;
         if (active) {
-            wc = e0 / H; hc = e0 - wc * H;
-            int hh = hc, ww = wc;
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-                ut[i] = xs[hh * Wp + ww];
-                if (++hh == H) { hh = 0; ++ww; }
-            }
-            const float D1 = __ldg(a.Dskip + D + d), D3 = __ldg(a.Dskip + 3 * D + d);
+            for (int i = 0; i < VEC; ++i) ul[i] = plane[cs.at(i, Wp)];
+            const float Dsum = (__ldg(a.Dskip + D + d) + __ldg(a.Dskip + 3 * D + d));
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) ycol[i] = (D1 + D3) * ut[i];
+            for (int i = 0; i < VEC; ++i) { ycol[i] = Dsum * ul[i]; ul[i] *= kLn2; }
+            RouteConst rc;
+            rc.A = __ldg(a.A + D + d); rc.bias = __ldg(a.bias + D + d); rc.bias2 = rc.bias * kLog2e;
             VT::unpack(rd1, dv);
-            VT::load((const T*)a.Bm[1] + b * a.bc_bs[1] + e0, bv);
-            VT::load((const T*)a.Cm[1] + b * a.bc_bs[1] + e0, cv);
-            af = route_local<VEC, true>(ut, dv, bv, cv, __ldg(a.A + D + d) * kLog2e, __ldg(a.bias + D + d), cPf, ycol);
+            VF::load(a.Bm[1] + b * a.bc_bs[1] + e0, bv);
+            VF::load(a.Cm[1] + b * a.bc_bs[1] + e0, cv);
+            af = route_local<VEC, true, kPrecise>(ul, dv, bv, cv, rc, cPf, ycol);
             if (v == 0) af.a = 0.f;
+            rc.A = __ldg(a.A + 3 * D + d); rc.bias = __ldg(a.bias + 3 * D + d); rc.bias2 = rc.bias * kLog2e;
             VT::unpack(rd3, dv);
-            VT::load((const T*)a.Bm[3] + b * a.bc_bs[3] + e0, bv);
-            VT::load((const T*)a.Cm[3] + b * a.bc_bs[3] + e0, cv);
-            ab = route_local<VEC, false>(ut, dv, bv, cv, __ldg(a.A + 3 * D + d) * kLog2e, __ldg(a.bias + 3 * D + d), cPb, ycol);
+            VF::load(a.Bm[3] + b * a.bc_bs[3] + e0, bv);
+            VF::load(a.Cm[3] + b * a.bc_bs[3] + e0, cv);
+            ab = route_local<VEC, false, kPrecise>(ul, dv, bv, cv, rc, cPb, ycol);
             if (v == a.G - 1) ab.a = 0.f;
         } else {
 #pragma unroll
             for (int i = 0; i < VEC; ++i) { ycol[i] = 0.f; cPf[i] = 0.f; cPb[i] = 0.f; }
         }
         float hf, hb;
-        cta_scan_pair(af, ab, lane, warp, nwarps, scr, hf, hb);
+        cta_scan_pair(af, ab, lane, warp, nwarps, scr, hf, hb);   // every x value has been read before these barriers
         if (v == 0) hf = 0.f;
         if (v == a.G - 1) hb = 0.f;
         if (active) {
-            int hh = hc, ww = wc;
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-                ys[hh * Wp + ww] = fmaf(cPf[i], hf, fmaf(cPb[i], hb, ycol[i]));
-                if (++hh == H) { hh = 0; ++ww; }
-            }
+            for (int i = 0; i < VEC; ++i) plane[cs.at(i, Wp)] = fmaf(cPf[i], hf, fmaf(cPb[i], hb, ycol[i]));
         }
     }
     __syncthreads();
 
     // ---- merge: row result (registers) + column result (transposed read), one vector store ------
     if (active) {
-        int hh = h, ww = w;
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-            yrow[i] += ys[hh * Wp + ww];
-            if (++ww == W) { ww = 0; ++hh; }
-        }
-        Vec<float, VEC>::store(a.merged + (long long)b * D * L + plane_off, yrow);
+        for (int i = 0; i < VEC; ++i) yrow[i] += plane[rs.at(i, 1)];
+        VF::store(a.merged + (long long)b * D * L + plane_off, yrow);
     }
 }
 
@@ -232,9 +262,11 @@ static bool plan_planes(const ss2d_core_params* p, PlaneConfig& c) {
     auto fit = [&](long long x) { if (x < 0) x = -x; while (vec > 1 && (x % vec) != 0) vec >>= 1; };
     fit(L); fit(el(p->x));
     for (int k = 0; k < 4; ++k) {
-        fit(el(p->delta[k])); fit(el(p->Bm[k])); fit(el(p->Cm[k]));
+        fit(el(p->delta[k]));
+        fit((long long)(reinterpret_cast<uintptr_t>(p->Bm[k]) / 4)); fit((long long)(reinterpret_cast<uintptr_t>(p->Cm[k]) / 4));
         fit(p->delta_batch_stride[k]); fit(p->bc_batch_stride[k]);
     }
+    while (vec > 1 && (vec > p->H || vec > p->W)) vec >>= 1;   // a thread's segment spans at most two lines
     // 16-byte loads are enough: an 8-wide fp32 vector is two of them
     // (alignment of the fp32 workspace is checked by the caller)
     const long long G = L / vec;
@@ -243,8 +275,8 @@ static bool plan_planes(const ss2d_core_params* p, PlaneConfig& c) {
     if (PP < 1) PP = 1;
     if (PP > p->D) PP = (int)p->D;
     const int Wp = (int)(p->W | 1);   // odd pitch spreads the transposed accesses over banks
-    size_t smem = (size_t)2 * PP * p->H * Wp * sizeof(float);
-    while (smem > 200 * 1024 && PP > 1) { --PP; smem = (size_t)2 * PP * p->H * Wp * sizeof(float); }
+    size_t smem = (size_t)PP * p->H * Wp * sizeof(float);
+    while (smem > 200 * 1024 && PP > 1) { --PP; smem = (size_t)PP * p->H * Wp * sizeof(float); }
     if (smem > 200 * 1024) return false;
     c.vec = vec; c.G = (int)G; c.PP = PP; c.Wp = Wp; c.smem = smem;
     c.threads = (int)((PP * G + 31) / 32 * 32);
@@ -300,7 +332,7 @@ static int validate_core(const ss2d_core_params* p) {
         !aligned_to(p->ln_bias, 4))
         return SS2D_EINVAL_ALIGN;
     for (int k = 0; k < 4; ++k)
-        if (!aligned_to(p->delta[k], s) || !aligned_to(p->Bm[k], s) || !aligned_to(p->Cm[k], s)) return SS2D_EINVAL_ALIGN;
+        if (!aligned_to(p->delta[k], s) || !aligned_to(p->Bm[k], 4) || !aligned_to(p->Cm[k], 4)) return SS2D_EINVAL_ALIGN;
     return SS2D_OK;
 }
 
@@ -330,13 +362,15 @@ int core_fwd(const ss2d_core_params* p, cudaStream_t st) {
     CoreArgs a;
     a.x = p->x;
     for (int k = 0; k < 4; ++k) {
-        a.delta[k] = p->delta[k]; a.Bm[k] = p->Bm[k]; a.Cm[k] = p->Cm[k];
+        a.delta[k] = p->delta[k]; a.Bm[k] = (const float*)p->Bm[k]; a.Cm[k] = (const float*)p->Cm[k];
         a.d_bs[k] = p->delta_batch_stride[k]; a.bc_bs[k] = p->bc_batch_stride[k];
     }
     a.A = (const float*)p->A; a.Dskip = (const float*)p->Dskip; a.bias = (const float*)p->delta_bias;
     a.merged = merged;
     a.B = (int)p->B; a.D = (int)p->D; a.H = (int)p->H; a.W = (int)p->W; a.L = (int)(p->H * p->W);
     a.G = c.G; a.PP = c.PP; a.Wp = c.Wp;
+    auto magic = [](long long d) { return (unsigned)(((1ULL << 32) + (unsigned long long)d - 1) / (unsigned long long)d); };
+    a.magic_G = c.G > 1 ? magic(c.G) : 0; a.magic_W = p->W > 1 ? magic(p->W) : 0; a.magic_H = p->H > 1 ? magic(p->H) : 0;
     a.groups_per_image = (int)((p->D + c.PP - 1) / c.PP);
     const long long grid = (long long)p->B * a.groups_per_image;
     if (grid > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;

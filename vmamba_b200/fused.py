@@ -60,10 +60,13 @@ class CoreWeights:
 def project(x: torch.Tensor, w: CoreWeights):
     """x (B, D, H, W) -> per-orientation projections.
 
-    Returns (xd_even, xd_odd, delta_even, delta_odd):
-      xd_even  (B, 2, R+2N, L) view, routes 0 and 2, row-major pixel order
-      xd_odd   (B, 2, R+2N, L) routes 1 and 3, column-major pixel order
-      delta_*  (B, 2, D, L) raw step sizes in the same orders
+    Returns (bc_even, bc_odd, delta_even, delta_odd):
+      bc_even  (B, 2, 2N, L) fp32: B then C rows of routes 0 and 2, row-major pixel order
+      bc_odd   (B, 2, 2N, L) fp32: routes 1 and 3, column-major pixel order
+      delta_*  (B, 2, D, L) raw step sizes in the same orders, activation dtype
+    B and C are first rounded to the activation dtype (as the reference's projection output is)
+    and then widened: they are 2N rows per route against D rows of delta, and fp32 saves the
+    scan kernel two unpack instructions per element.
     """
     B, D, H, W = x.shape
     L, R, N = H * W, w.dt_rank, w.d_state
@@ -73,7 +76,7 @@ def project(x: torch.Tensor, w: CoreWeights):
     xd_odd = xd[:, :, 1].transpose(-1, -2).reshape(B, 2, C, L)
     delta_even = torch.matmul(w.wdt_even, xd_even[:, :, :R])
     delta_odd = torch.matmul(w.wdt_odd, xd_odd[:, :, :R])
-    return xd_even, xd_odd, delta_even, delta_odd
+    return xd_even[:, :, R:].float(), xd_odd[:, :, R:].float(), delta_even, delta_odd
 
 
 def scan_merge_norm(x: torch.Tensor, proj, w: CoreWeights, *, with_norm: bool = True, out_dtype=None,
@@ -81,25 +84,25 @@ def scan_merge_norm(x: torch.Tensor, proj, w: CoreWeights, *, with_norm: bool = 
     """The CUDA part of the fused core (`ss2d_core_fwd`): x plus the projections returned by
     `project` -> merged (and normalised) map.  Launches one scan+merge kernel and, with
     `with_norm`, one LayerNorm kernel; allocates the output and the fp32 workspace unless given."""
-    xd_even, xd_odd, delta_even, delta_odd = proj
+    bc_even, bc_odd, delta_even, delta_odd = proj
     B, D, H, W = x.shape
     R, N = w.dt_rank, w.d_state
     out_dtype = out_dtype or (x.dtype if with_norm else torch.float32)
     y = out if out is not None else torch.empty((B, D, H, W), device=x.device, dtype=out_dtype)
     p = CoreParams()
     p.x = x.data_ptr()
-    srcs = (xd_even, xd_odd)
+    srcs = (bc_even, bc_odd)
     deltas = (delta_even, delta_odd)
     esz = x.element_size()
     for k in range(K):
         j, i = k % 2, k // 2          # j: orientation (0 row, 1 column); i: index inside the pair
-        xd, dl = srcs[j], deltas[j]
+        bc, dl = srcs[j], deltas[j]
         p.delta[k] = dl.data_ptr() + i * dl.stride(1) * esz
         p.delta_batch_stride[k] = dl.stride(0)
-        base = xd.data_ptr() + i * xd.stride(1) * esz
-        p.Bm[k] = base + R * xd.stride(2) * esz
-        p.Cm[k] = base + (R + N) * xd.stride(2) * esz
-        p.bc_batch_stride[k] = xd.stride(0)
+        base = bc.data_ptr() + i * bc.stride(1) * 4
+        p.Bm[k] = base
+        p.Cm[k] = base + N * bc.stride(2) * 4
+        p.bc_batch_stride[k] = bc.stride(0)
     p.A, p.Dskip, p.delta_bias = w.A.data_ptr(), w.Ds.data_ptr(), w.dt_bias.data_ptr()
     p.ln_weight = None if w.ln_weight is None else w.ln_weight.data_ptr()
     p.ln_bias = None if w.ln_bias is None else w.ln_bias.data_ptr()
