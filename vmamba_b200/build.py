@@ -1,6 +1,8 @@
 """Builds libss2d_b200.so (the C-ABI library of include/ss2d_b200.h) in-tree with nvcc for sm_100a.
 
-    python -m vmamba_b200.build [--force] [--verbose]
+    python vmamba_b200/build.py [--force] [--verbose]
+
+(run as a file: importing the package needs the library this script produces)
 
 Each translation unit of csrc/ is compiled to an object in parallel, then linked with the
 static CUDA runtime.  No torch headers are involved: the library has a plain C interface.
