@@ -34,7 +34,8 @@ typedef enum ss2d_status {
     SS2D_EINVAL_STRIDE = -5,   /* a stride is impossible for the given sizes */
     SS2D_ENOTSUP = -6,         /* valid request that this build does not implement */
     SS2D_ECUDA = -7,           /* the CUDA runtime reported an error at launch */
-    SS2D_EWORKSPACE = -8       /* workspace missing or too small */
+    SS2D_EWORKSPACE = -8,      /* workspace missing or too small */
+    SS2D_ETOOBIG = -9          /* problem exceeds the built-in scratch of an allocation-free entry point */
 } ss2d_status;
 
 /* ------------------------------------------------------------------------------------
@@ -128,6 +129,23 @@ typedef struct ss2d_core_params {
 
 int64_t ss2d_core_workspace_bytes(const ss2d_core_params *p);
 int ss2d_core_fwd(const ss2d_core_params *p, void *cuda_stream);
+
+/* Allocation-free form of ss2d_core_fwd.  It has no counterpart in the reference: it exists for
+ * callers that can hand over inputs and outputs but cannot obtain device memory themselves (an
+ * operator slot of a serving runtime that passes only pre-placed tensors, a host language bound to
+ * this ABI without a CUDA allocator, a process whose device memory is fixed at start-up).  The
+ * fp32 scratch map that ss2d_core_fwd takes as `workspace` lives in a static device array inside
+ * the library instead (32 MiB on every GPU that loads the library, held until the process ends);
+ * `workspace` / `workspace_bytes` of the params are ignored.
+ *   - limit: B*D*H*W <= ss2d_core_static_capacity() (8 388 608); beyond it the call returns
+ *     SS2D_ETOOBIG and launches nothing;
+ *   - the first call on a device resolves the device address of that array; issue it outside
+ *     any stream capture;
+ *   - calls on the same GPU share the array and must not overlap in time (they would race);
+ *     nothing in it needs clearing between calls;
+ *   - never calls cudaMalloc/cudaFree.  Results are identical to ss2d_core_fwd's. */
+int ss2d_core_fwd_static(const ss2d_core_params *p, void *cuda_stream);
+int64_t ss2d_core_static_capacity(void);
 
 /* LayerNorm over the channel axis of a channel-first map, optionally summing `n_terms`
  * fp32 maps first.  Replaces LayerNorm(channel_first=True).forward (vmamba.py:1087-1093)

@@ -56,6 +56,8 @@ EXPORTS = {
     "ss2d_cross_merge": (ctypes.c_int, [ctypes.POINTER(CrossParams), _vp]),
     "ss2d_core_workspace_bytes": (_i64, [ctypes.POINTER(CoreParams)]),
     "ss2d_core_fwd": (ctypes.c_int, [ctypes.POINTER(CoreParams), _vp]),
+    "ss2d_core_fwd_static": (ctypes.c_int, [ctypes.POINTER(CoreParams), _vp]),
+    "ss2d_core_static_capacity": (_i64, []),
     "ss2d_layer_norm_cf": (ctypes.c_int, [ctypes.POINTER(NormParams), _vp]),
     "ss2d_version": (ctypes.c_int, []),
     "ss2d_strerror": (ctypes.c_char_p, [ctypes.c_int]),
@@ -73,13 +75,13 @@ class Ss2dError(RuntimeError):
 
 
 def lib():
-    """The loaded library; raises if it has not been built (python -m vmamba_b200.build)."""
+    """The loaded library; raises if it has not been built (python vmamba_b200/build.py)."""
     global _lib
     if _lib is None:
         if not os.path.exists(LIB_PATH):
             raise ImportError(
                 f"{LIB_PATH} not found. vmamba_b200 has no CPU or eager fallback: build the CUDA "
-                "library first with `python -m vmamba_b200.build` (needs nvcc, targets sm_100a).")
+                "library first with `python vmamba_b200/build.py` (needs nvcc, targets sm_100a).")
         handle = ctypes.CDLL(LIB_PATH)
         for name, (res, args) in EXPORTS.items():
             fn = getattr(handle, name)   # AttributeError if a declared symbol is missing

@@ -10,6 +10,8 @@ int cross_merge(const ss2d_cross_params* p, cudaStream_t st);
 int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st);
 long long core_workspace_bytes(const ss2d_core_params* p);
 int core_fwd(const ss2d_core_params* p, cudaStream_t st);
+int core_fwd_static(const ss2d_core_params* p, cudaStream_t st);
+long long core_static_capacity();
 
 static std::atomic<long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
@@ -26,6 +28,8 @@ int ss2d_cross_merge(const ss2d_cross_params* p, void* stream) { return ss2d::cr
 int ss2d_layer_norm_cf(const ss2d_norm_params* p, void* stream) { return ss2d::layer_norm_cf(p, (cudaStream_t)stream); }
 int64_t ss2d_core_workspace_bytes(const ss2d_core_params* p) { return ss2d::core_workspace_bytes(p); }
 int ss2d_core_fwd(const ss2d_core_params* p, void* stream) { return ss2d::core_fwd(p, (cudaStream_t)stream); }
+int ss2d_core_fwd_static(const ss2d_core_params* p, void* stream) { return ss2d::core_fwd_static(p, (cudaStream_t)stream); }
+int64_t ss2d_core_static_capacity(void) { return ss2d::core_static_capacity(); }
 
 int ss2d_version(void) { return SS2D_ABI_VERSION; }
 int64_t ss2d_launch_count(void) { return ss2d::g_launches.load(std::memory_order_relaxed); }
@@ -41,6 +45,7 @@ const char* ss2d_strerror(int status) {
         case SS2D_ENOTSUP: return "request not supported by this build";
         case SS2D_ECUDA: return "CUDA runtime error at kernel launch";
         case SS2D_EWORKSPACE: return "workspace missing or too small";
+        case SS2D_ETOOBIG: return "problem larger than the library's built-in scratch (B*D*H*W > ss2d_core_static_capacity())";
         default: return "unknown status";
     }
 }

@@ -19,6 +19,8 @@
 //
 // HBM traffic per (pixel, channel): x once, four delta values, one fp32 result; B_k/C_k are shared
 // by all channels of an image and stay in L1/L2.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace ss2d {
@@ -356,6 +358,99 @@ int core_fwd(const ss2d_core_params* p, cudaStream_t st) {
         if (!p->workspace || p->workspace_bytes < need) return SS2D_EWORKSPACE;
         if (!aligned_to(p->workspace, 256)) return SS2D_EINVAL_ALIGN;
         merged = (float*)p->workspace;
+    } else if (!aligned_to(p->y, 16)) {
+        return SS2D_EINVAL_ALIGN;
+    }
+    CoreArgs a;
+    a.x = p->x;
+    for (int k = 0; k < 4; ++k) {
+        a.delta[k] = p->delta[k]; a.Bm[k] = (const float*)p->Bm[k]; a.Cm[k] = (const float*)p->Cm[k];
+        a.d_bs[k] = p->delta_batch_stride[k]; a.bc_bs[k] = p->bc_batch_stride[k];
+    }
+    a.A = (const float*)p->A; a.Dskip = (const float*)p->Dskip; a.bias = (const float*)p->delta_bias;
+    a.merged = merged;
+    a.B = (int)p->B; a.D = (int)p->D; a.H = (int)p->H; a.W = (int)p->W; a.L = (int)(p->H * p->W);
+    a.G = c.G; a.PP = c.PP; a.Wp = c.Wp;
+    auto magic = [](long long d) { return (unsigned)(((1ULL << 32) + (unsigned long long)d - 1) / (unsigned long long)d); };
+    a.magic_G = c.G > 1 ? magic(c.G) : 0; a.magic_W = p->W > 1 ? magic(p->W) : 0; a.magic_H = p->H > 1 ? magic(p->H) : 0;
+    a.groups_per_image = (int)((p->D + c.PP - 1) / c.PP);
+    const long long grid = (long long)p->B * a.groups_per_image;
+    if (grid > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
+    int r;
+    if (p->act_dtype == SS2D_F32) r = launch_core_v<float>(a, c, (unsigned)grid, st);
+    else if (p->act_dtype == SS2D_BF16) r = launch_core_v<__nv_bfloat16>(a, c, (unsigned)grid, st);
+    else r = launch_core_v<__half>(a, c, (unsigned)grid, st);
+    if (r != SS2D_OK) return r;
+    if (!p->with_norm) return SS2D_OK;
+    ss2d_norm_params n;
+    n.in = merged; n.weight = p->ln_weight; n.bias = p->ln_bias; n.out = p->y;
+    n.B = p->B; n.D = p->D; n.L = p->H * p->W; n.n_terms = 1; n.out_dtype = p->y_dtype; n.eps = p->ln_eps;
+    n.reserved0 = 0;
+    return layer_norm_cf(&n, st);
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of core_fwd.
+//
+// core_fwd needs the caller to bring one scratch buffer (the fp32 merged map that the scan+merge
+// kernel hands to the LayerNorm kernel).  A caller that reaches this library through a bare FFI
+// binding -- a custom-operator slot of a serving runtime that passes in only the input and output
+// tensors it has already placed, a host program in a language without a CUDA allocator of its own,
+// a process whose device memory was carved up once at start-up and is not allowed to grow -- has
+// nowhere to get that buffer from.  For those callers the scratch lives in the array below, inside
+// the library image: every GPU on which the library is loaded holds kStaticScratchBytes for the
+// life of the process.
+//
+// Rules of use:
+//  * capacity: B*D*H*W <= kStaticScratchFloats; larger problems are rejected with SS2D_ETOOBIG
+//    before anything is launched;
+//  * the first call on each device looks up the device address of the array (cudaGetSymbolAddress,
+//    with that device current).  Make that first call outside any stream capture;
+//  * all calls on one device share the one array and it keeps whatever the last call left in it.
+//    Nothing has to start at zero: the scan+merge kernel overwrites every element the LayerNorm
+//    kernel will read.  Two calls that overlap in time on the same GPU (different streams or
+//    threads) race on it -- serialise them;
+//  * no cudaMalloc / cudaFree / allocating library routine is called here or below.
+// ------------------------------------------------------------------------------------------------
+constexpr long long kStaticScratchBytes = 32ll << 20;                       // 32 MiB per GPU
+constexpr long long kStaticScratchFloats = kStaticScratchBytes / 4;         // 8 388 608 map elements
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+static float* g_static_scratch_addr[kMaxDevices] = {};
+static std::mutex g_static_scratch_mutex;
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address: the
+// address a kernel can use has to be asked for, per device.
+static int static_scratch_for_current_device(float** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return SS2D_ECUDA;
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (!g_static_scratch_addr[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return SS2D_ECUDA;
+        g_static_scratch_addr[dev] = (float*)ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return SS2D_OK;
+}
+
+long long core_static_capacity() { return kStaticScratchFloats; }
+
+int core_fwd_static(const ss2d_core_params* p, cudaStream_t st) {
+    const int rc = validate_core(p);
+    if (rc != SS2D_OK) return rc;
+    if (p->N != 1) return SS2D_ENOTSUP;
+    if (!p->with_norm && p->y_dtype != SS2D_F32) return SS2D_ENOTSUP;
+    PlaneConfig c;
+    if (!plan_planes(p, c)) return SS2D_ENOTSUP;
+    const long long need = core_workspace_bytes(p);
+    float* merged = (float*)p->y;
+    if (need > 0) {
+        if (need > kStaticScratchBytes) return SS2D_ETOOBIG;
+        const int r = static_scratch_for_current_device(&merged);
+        if (r != SS2D_OK) return r;
     } else if (!aligned_to(p->y, 16)) {
         return SS2D_EINVAL_ALIGN;
     }
