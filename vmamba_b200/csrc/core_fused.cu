@@ -84,52 +84,98 @@ struct RouteConst {
     float bias;     // delta_bias
 };
 
-// One direction of one route over the VEC register elements of a thread.
-// `ul` holds u * ln2.  With t = log2(1 + e^x), x = delta + bias:  softplus(x) = ln2 * t  and
-// exp(softplus(x) * A) = 2^(A t), so one ex2 and one lg2 serve both the step size and the decay.
-// Adds C*h_local to ysum, leaves C*prod(a) in cP, returns the thread aggregate.
-// kPrecise (fp32 tensors): softplus keeps torch's threshold and a series for small e^x, so that
-// the result is accurate to fp32 rounding; otherwise (16-bit tensors, whose own rounding is four
-// orders of magnitude coarser) the shortest instruction sequence is used.
+// Packed fp32 pairs: sm_100 executes two independent fp32 operations per FFMA2 / FMUL2 / FADD2
+// instruction.  The kernel is bound by instruction issue, so everything elementwise is written on pairs.
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 splat(float v) { return make_float2(v, v); }
+
+// One direction of one route over the VEC register elements of a thread (NP = VEC/2 pairs; VEC = 1
+// uses the .x half of a single pair).  `ul` holds u * ln2.  With t = log2(1 + e^x), x = delta + bias:
+// softplus(x) = ln2 * t and exp(softplus(x) * A) = 2^(A t), so one ex2 and one lg2 serve both the
+// step size and the decay.  Adds C*h_local to ysum, leaves C*prod(a) in cP, returns the thread aggregate.
+// kPrecise (fp32 tensors): softplus keeps torch's threshold and a series for small e^x, so that the
+// result is accurate to fp32 rounding; otherwise (16-bit tensors, whose own rounding is four orders
+// of magnitude coarser) the shortest instruction sequence is used.
 template <int VEC, bool kForward, bool kPrecise>
-__device__ __forceinline__ AB route_local(const float (&ul)[VEC], const float (&dv)[VEC], const float (&bv)[VEC],
-                                          const float (&cv)[VEC], const RouteConst rc, float (&cP)[VEC],
-                                          float (&ysum)[VEC]) {
+__device__ __forceinline__ AB route_local(const float2 (&ul)[(VEC + 1) / 2], const float2 (&dv)[(VEC + 1) / 2],
+                                          const float2 (&bv)[(VEC + 1) / 2], const float2 (&cv)[(VEC + 1) / 2],
+                                          const RouteConst rc, float2 (&cP)[(VEC + 1) / 2],
+                                          float2 (&ysum)[(VEC + 1) / 2]) {
+    constexpr int NP = (VEC + 1) / 2;
+    float2 aa[NP], bb[NP];
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+        float2 t;
+        if constexpr (kPrecise) {
+            const float2 x = add2(dv[j], splat(rc.bias));
+            t = mul2(make_float2(softplus_fast(x.x), softplus_fast(x.y)), splat(kLog2e));
+        } else {
+            // clamp keeps e^x finite; above x = 87 the reference returns x itself
+            float2 arg = fma2(dv[j], splat(kLog2e), splat(rc.bias2));
+            arg.x = fminf(arg.x, 126.f); arg.y = fminf(arg.y, 126.f);
+            const float2 w = add2(make_float2(ex2_approx(arg.x), ex2_approx(arg.y)), splat(1.0f));
+            t = make_float2(lg2_approx(w.x), lg2_approx(w.y));
+        }
+        const float2 ta = mul2(t, splat(rc.A));
+        aa[j] = make_float2(ex2_approx(ta.x), ex2_approx(ta.y));
+        bb[j] = mul2(t, mul2(bv[j], ul[j]));
+    }
+    // the recurrence itself is serial; afterwards aa holds the running product, bb the local state
     float p = 1.f, h = 0.f;
 #pragma unroll
     for (int ii = 0; ii < VEC; ++ii) {
         const int i = kForward ? ii : VEC - 1 - ii;
-        float t, aa;
-        if constexpr (kPrecise) {
-            const float dl = softplus_fast(dv[i] + rc.bias);
-            t = dl * kLog2e;
-            aa = ex2_approx(t * rc.A);
-        } else {
-            // clamp keeps e^x finite; above x = 87 the reference returns x itself
-            const float e = ex2_approx(fminf(fmaf(dv[i], kLog2e, rc.bias2), 126.f));
-            t = lg2_approx(1.0f + e);
-            aa = ex2_approx(t * rc.A);
-        }
-        h = fmaf(aa, h, t * (bv[i] * ul[i]));
-        p *= aa;
-        cP[i] = cv[i] * p;
-        ysum[i] = fmaf(cv[i], h, ysum[i]);
+        float& a_i = (i & 1) ? aa[i >> 1].y : aa[i >> 1].x;
+        float& b_i = (i & 1) ? bb[i >> 1].y : bb[i >> 1].x;
+        h = fmaf(a_i, h, b_i);
+        p *= a_i;
+        a_i = p; b_i = h;
+    }
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+        cP[j] = mul2(cv[j], aa[j]);
+        ysum[j] = fma2(cv[j], bb[j], ysum[j]);
     }
     return AB{p, h};
 }
 
-// Shared-memory word of element i of a VEC-segment that starts at (major0, minor0) of a plane
-// walked with `minor` fastest (length n_minor), stored with `minor_stride` / `major_stride`.
-// A segment covers at most two lines because VEC <= n_minor.
+// VEC consecutive fp32 values -> pairs (odd VEC = 1: the .y half is zero)
+template <typename T, int VEC>
+__device__ __forceinline__ void unpack_pairs(const typename Vec<T, VEC>::Raw& r, float2 (&v)[(VEC + 1) / 2]) {
+    float f[VEC];
+    Vec<T, VEC>::unpack(r, f);
+    if constexpr (VEC == 1) v[0] = make_float2(f[0], 0.f);
+    else {
+#pragma unroll
+        for (int j = 0; j < VEC / 2; ++j) v[j] = make_float2(f[2 * j], f[2 * j + 1]);
+    }
+}
+template <int VEC>
+__device__ __forceinline__ void load_pairs(const float* p, float2 (&v)[(VEC + 1) / 2]) {
+    float f[VEC];
+    Vec<float, VEC>::load(p, f);
+    if constexpr (VEC == 1) v[0] = make_float2(f[0], 0.f);
+    else {
+#pragma unroll
+        for (int j = 0; j < VEC / 2; ++j) v[j] = make_float2(f[2 * j], f[2 * j + 1]);
+    }
+}
+
+// Shared-memory words of a VEC-segment of a plane walked with one index fastest ("minor", line
+// length n_minor).  The host picks VEC so that VEC/2 divides n_minor: a segment then either lies
+// in one line or wraps exactly at its middle, so the first half is affine from `lo` and the second
+// half affine from `hi` (two bases, no per-element test).
 template <int VEC>
 struct SegAddr {
-    int a0, n1, jump;
+    int lo, hi;
     __device__ __forceinline__ SegAddr(int major0, int minor0, int n_minor, int major_stride, int minor_stride) {
-        a0 = major0 * major_stride + minor0 * minor_stride;
-        n1 = n_minor - minor0;                                   // elements left in the first line
-        jump = major_stride - n_minor * minor_stride;            // extra offset once the line wraps
+        lo = major0 * major_stride + minor0 * minor_stride;
+        const bool wrap = minor0 + VEC > n_minor;
+        hi = wrap ? lo + major_stride - n_minor * minor_stride : lo;
     }
-    __device__ __forceinline__ int at(int i, int minor_stride) const { return a0 + i * minor_stride + (i >= n1 ? jump : 0); }
+    __device__ __forceinline__ int at(int i, int minor_stride) const { return (i < VEC / 2 || VEC == 1 ? lo : hi) + i * minor_stride; }
 };
 
 template <typename T, int VEC, int MAXT, int MINB>
@@ -137,120 +183,119 @@ __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a
     extern __shared__ __align__(16) float smem[];
     __shared__ ScanScratch scr;
     constexpr bool kPrecise = sizeof(T) == 4;
+    constexpr int NP = (VEC + 1) / 2;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = (blockDim.x + 31) >> 5;
     const int b = blockIdx.x / a.groups_per_image;
     const int d0 = (blockIdx.x - b * a.groups_per_image) * a.PP;
     const int pp_here = min(a.PP, a.D - d0);
-    const int pl = fast_div(t, a.magic_G), v = t - pl * a.G;
+    int pl = fast_div(t, a.magic_G);
+    const int v = t - pl * a.G;
+    // Threads past the last plane of the CTA (round-up to a warp, last channel group) run on the
+    // last valid plane so that every load below is in range; they take no part in the scans
+    // (identity aggregates) and store nothing.
     const bool active = pl < pp_here;
+    pl = min(pl, pp_here - 1);
     const int d = d0 + pl;
     const int L = a.L, H = a.H, W = a.W, Wp = a.Wp, D = a.D;
     // one padded fp32 plane per channel: first x (for the transposed read), then, once every
     // column-orientation thread has taken its x values, the column-orientation result
     float* plane = smem + (size_t)pl * (H * Wp);
     using VT = Vec<T, VEC>;
-    using VF = Vec<float, VEC>;
     const int e0 = v * VEC;   // first element of this thread in either orientation order
     const long long plane_off = (long long)d * L + e0;
+    const bool first = v == 0, last = v == a.G - 1;
 
     // ---- issue every HBM load of the pass up front: x and the four delta vectors -------------
-    typename VT::Raw rx = {}, rd0 = {}, rd1 = {}, rd2 = {}, rd3 = {};
-    if (active) {
-        rx = VT::load_raw((const T*)a.x + (long long)b * D * L + plane_off);
-        rd0 = VT::load_raw((const T*)a.delta[0] + b * a.d_bs[0] + plane_off);
-        rd2 = VT::load_raw((const T*)a.delta[2] + b * a.d_bs[2] + plane_off);
-        rd1 = VT::load_raw((const T*)a.delta[1] + b * a.d_bs[1] + plane_off);
-        rd3 = VT::load_raw((const T*)a.delta[3] + b * a.d_bs[3] + plane_off);
-    }
-    float ul[VEC], yrow[VEC];
-    VT::unpack(rx, ul);
+    const typename VT::Raw rx = VT::load_raw((const T*)a.x + (long long)b * D * L + plane_off);
+    const typename VT::Raw rd0 = VT::load_raw((const T*)a.delta[0] + b * a.d_bs[0] + plane_off);
+    const typename VT::Raw rd2 = VT::load_raw((const T*)a.delta[2] + b * a.d_bs[2] + plane_off);
+    const typename VT::Raw rd1 = VT::load_raw((const T*)a.delta[1] + b * a.d_bs[1] + plane_off);
+    const typename VT::Raw rd3 = VT::load_raw((const T*)a.delta[3] + b * a.d_bs[3] + plane_off);
+    float2 ul[NP], yrow[NP];
+    unpack_pairs<T, VEC>(rx, ul);
 
     // ---- x into shared memory (row-major, padded pitch) -------------------------------------
     const int h0 = fast_div(e0, a.magic_W), w0 = e0 - h0 * W;
     const SegAddr<VEC> rs(h0, w0, W, Wp, 1);
     if (active) {
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) plane[rs.at(i, 1)] = ul[i];
+        for (int i = 0; i < VEC; ++i) plane[rs.at(i, 1)] = (i & 1) ? ul[i >> 1].y : ul[i >> 1].x;
     }
     const int wc = fast_div(e0, a.magic_H), hc = e0 - wc * H;
     const SegAddr<VEC> cs(wc, hc, H, 1, Wp);   // column-major walk: h is the fast index, stride Wp
 
     // ---- row orientation: routes 0 (forward) and 2 (backward) ---------------------------------
     {
-        float dv[VEC], bv[VEC], cv[VEC], cPf[VEC], cPb[VEC];
-        AB af{1.f, 0.f}, ab{1.f, 0.f};
-        if (active) {
-            const float Dsum = (__ldg(a.Dskip + d) + __ldg(a.Dskip + 2 * D + d));
+        float2 dv[NP], bv[NP], cv[NP], cPf[NP], cPb[NP];
+        const float2 Dsum = splat(__ldg(a.Dskip + d) + __ldg(a.Dskip + 2 * D + d));
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) { yrow[i] = Dsum * ul[i]; ul[i] *= kLn2; }
-            RouteConst rc;
-            rc.A = __ldg(a.A + d); rc.bias = __ldg(a.bias + d); rc.bias2 = rc.bias * kLog2e;
-            VT::unpack(rd0, dv);
-            VF::load(a.Bm[0] + b * a.bc_bs[0] + e0, bv);
-            VF::load(a.Cm[0] + b * a.bc_bs[0] + e0, cv);
-            af = route_local<VEC, true, kPrecise>(ul, dv, bv, cv, rc, cPf, yrow);
-            if (v == 0) af.a = 0.f;
-            rc.A = __ldg(a.A + 2 * D + d); rc.bias = __ldg(a.bias + 2 * D + d); rc.bias2 = rc.bias * kLog2e;
-            VT::unpack(rd2, dv);
-            VF::load(a.Bm[2] + b * a.bc_bs[2] + e0, bv);
-            VF::load(a.Cm[2] + b * a.bc_bs[2] + e0, cv);
-            ab = route_local<VEC, false, kPrecise>(ul, dv, bv, cv, rc, cPb, yrow);
-            if (v == a.G - 1) ab.a = 0.f;
-        } else {
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) { yrow[i] = 0.f; cPf[i] = 0.f; cPb[i] = 0.f; }
-        }
+        for (int j = 0; j < NP; ++j) { yrow[j] = mul2(Dsum, ul[j]); ul[j] = mul2(ul[j], splat(kLn2)); }
+        RouteConst rc;
+        rc.A = __ldg(a.A + d); rc.bias = __ldg(a.bias + d); rc.bias2 = rc.bias * kLog2e;
+        unpack_pairs<T, VEC>(rd0, dv);
+        load_pairs<VEC>(a.Bm[0] + b * a.bc_bs[0] + e0, bv);
+        load_pairs<VEC>(a.Cm[0] + b * a.bc_bs[0] + e0, cv);
+        AB af = route_local<VEC, true, kPrecise>(ul, dv, bv, cv, rc, cPf, yrow);
+        rc.A = __ldg(a.A + 2 * D + d); rc.bias = __ldg(a.bias + 2 * D + d); rc.bias2 = rc.bias * kLog2e;
+        unpack_pairs<T, VEC>(rd2, dv);
+        load_pairs<VEC>(a.Bm[2] + b * a.bc_bs[2] + e0, bv);
+        load_pairs<VEC>(a.Cm[2] + b * a.bc_bs[2] + e0, cv);
+        AB ab = route_local<VEC, false, kPrecise>(ul, dv, bv, cv, rc, cPb, yrow);
+        if (first) af.a = 0.f;
+        if (last) ab.a = 0.f;
+        if (!active) { af = AB{1.f, 0.f}; ab = AB{1.f, 0.f}; }
         float hf, hb;
         cta_scan_pair(af, ab, lane, warp, nwarps, scr, hf, hb);   // its barriers also order the x stores before the reads below
-        if (v == 0) hf = 0.f;
-        if (v == a.G - 1) hb = 0.f;
+        if (first) hf = 0.f;
+        if (last) hb = 0.f;
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) yrow[i] = fmaf(cPf[i], hf, fmaf(cPb[i], hb, yrow[i]));
+        for (int j = 0; j < NP; ++j) yrow[j] = fma2(cPf[j], splat(hf), fma2(cPb[j], splat(hb), yrow[j]));
     }
 
     // ---- column orientation: routes 1 (forward) and 3 (backward) -------------------------------
     {
-        float dv[VEC], bv[VEC], cv[VEC], cPf[VEC], cPb[VEC], ycol[VEC];
-        AB af{1.f, 0.f}, ab{1.f, 0.f};
-        if (active) {
+        float2 dv[NP], bv[NP], cv[NP], cPf[NP], cPb[NP], ycol[NP];
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) ul[i] = plane[cs.at(i, Wp)];
-            const float Dsum = (__ldg(a.Dskip + D + d) + __ldg(a.Dskip + 3 * D + d));
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) { ycol[i] = Dsum * ul[i]; ul[i] *= kLn2; }
-            RouteConst rc;
-            rc.A = __ldg(a.A + D + d); rc.bias = __ldg(a.bias + D + d); rc.bias2 = rc.bias * kLog2e;
-            VT::unpack(rd1, dv);
-            VF::load(a.Bm[1] + b * a.bc_bs[1] + e0, bv);
-            VF::load(a.Cm[1] + b * a.bc_bs[1] + e0, cv);
-            af = route_local<VEC, true, kPrecise>(ul, dv, bv, cv, rc, cPf, ycol);
-            if (v == 0) af.a = 0.f;
-            rc.A = __ldg(a.A + 3 * D + d); rc.bias = __ldg(a.bias + 3 * D + d); rc.bias2 = rc.bias * kLog2e;
-            VT::unpack(rd3, dv);
-            VF::load(a.Bm[3] + b * a.bc_bs[3] + e0, bv);
-            VF::load(a.Cm[3] + b * a.bc_bs[3] + e0, cv);
-            ab = route_local<VEC, false, kPrecise>(ul, dv, bv, cv, rc, cPb, ycol);
-            if (v == a.G - 1) ab.a = 0.f;
-        } else {
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) { ycol[i] = 0.f; cPf[i] = 0.f; cPb[i] = 0.f; }
+        for (int j = 0; j < NP; ++j) {
+            ul[j].x = plane[cs.at(2 * j, Wp)];
+            ul[j].y = (VEC > 1) ? plane[cs.at(2 * j + 1, Wp)] : 0.f;
         }
+        const float2 Dsum = splat(__ldg(a.Dskip + D + d) + __ldg(a.Dskip + 3 * D + d));
+#pragma unroll
+        for (int j = 0; j < NP; ++j) { ycol[j] = mul2(Dsum, ul[j]); ul[j] = mul2(ul[j], splat(kLn2)); }
+        RouteConst rc;
+        rc.A = __ldg(a.A + D + d); rc.bias = __ldg(a.bias + D + d); rc.bias2 = rc.bias * kLog2e;
+        unpack_pairs<T, VEC>(rd1, dv);
+        load_pairs<VEC>(a.Bm[1] + b * a.bc_bs[1] + e0, bv);
+        load_pairs<VEC>(a.Cm[1] + b * a.bc_bs[1] + e0, cv);
+        AB af = route_local<VEC, true, kPrecise>(ul, dv, bv, cv, rc, cPf, ycol);
+        rc.A = __ldg(a.A + 3 * D + d); rc.bias = __ldg(a.bias + 3 * D + d); rc.bias2 = rc.bias * kLog2e;
+        unpack_pairs<T, VEC>(rd3, dv);
+        load_pairs<VEC>(a.Bm[3] + b * a.bc_bs[3] + e0, bv);
+        load_pairs<VEC>(a.Cm[3] + b * a.bc_bs[3] + e0, cv);
+        AB ab = route_local<VEC, false, kPrecise>(ul, dv, bv, cv, rc, cPb, ycol);
+        if (first) af.a = 0.f;
+        if (last) ab.a = 0.f;
+        if (!active) { af = AB{1.f, 0.f}; ab = AB{1.f, 0.f}; }
         float hf, hb;
         cta_scan_pair(af, ab, lane, warp, nwarps, scr, hf, hb);   // every x value has been read before these barriers
-        if (v == 0) hf = 0.f;
-        if (v == a.G - 1) hb = 0.f;
+        if (first) hf = 0.f;
+        if (last) hb = 0.f;
+#pragma unroll
+        for (int j = 0; j < NP; ++j) ycol[j] = fma2(cPf[j], splat(hf), fma2(cPb[j], splat(hb), ycol[j]));
         if (active) {
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) plane[cs.at(i, Wp)] = fmaf(cPf[i], hf, fmaf(cPb[i], hb, ycol[i]));
+            for (int i = 0; i < VEC; ++i) plane[cs.at(i, Wp)] = (i & 1) ? ycol[i >> 1].y : ycol[i >> 1].x;
         }
     }
     __syncthreads();
 
     // ---- merge: row result (registers) + column result (transposed read), one vector store ------
     if (active) {
+        float out[VEC];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) yrow[i] += plane[rs.at(i, 1)];
-        VF::store(a.merged + (long long)b * D * L + plane_off, yrow);
+        for (int i = 0; i < VEC; ++i) out[i] = ((i & 1) ? yrow[i >> 1].y : yrow[i >> 1].x) + plane[rs.at(i, 1)];
+        Vec<float, VEC>::store(a.merged + (long long)b * D * L + plane_off, out);
     }
 }
 
@@ -268,7 +313,8 @@ static bool plan_planes(const ss2d_core_params* p, PlaneConfig& c) {
         fit((long long)(reinterpret_cast<uintptr_t>(p->Bm[k]) / 4)); fit((long long)(reinterpret_cast<uintptr_t>(p->Cm[k]) / 4));
         fit(p->delta_batch_stride[k]); fit(p->bc_batch_stride[k]);
     }
-    while (vec > 1 && (vec > p->H || vec > p->W)) vec >>= 1;   // a thread's segment spans at most two lines
+    // a thread's segment may wrap to the next line only at its middle: vec/2 divides H and W
+    while (vec > 1 && (vec > p->H || vec > p->W || (p->H % (vec / 2)) != 0 || (p->W % (vec / 2)) != 0)) vec >>= 1;
     // 16-byte loads are enough: an 8-wide fp32 vector is two of them
     // (alignment of the fp32 workspace is checked by the caller)
     const long long G = L / vec;
@@ -288,8 +334,8 @@ static bool plan_planes(const ss2d_core_params* p, PlaneConfig& c) {
 template <typename T, int VEC>
 static int launch_core_t(const CoreArgs& a, const PlaneConfig& c, unsigned grid, cudaStream_t st) {
     cudaError_t e;
-    if (c.threads <= 512) {
-        auto kern = core_plane_kernel<T, VEC, 512, 2>;
+    if (c.threads <= 448) {           // 72 registers per thread at two CTAs per SM
+        auto kern = core_plane_kernel<T, VEC, 448, 2>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem);
         if (e != cudaSuccess) return SS2D_ECUDA;
         kern<<<grid, c.threads, c.smem, st>>>(a);
