@@ -130,6 +130,54 @@ typedef struct ss2d_core_params {
 int64_t ss2d_core_workspace_bytes(const ss2d_core_params *p);
 int ss2d_core_fwd(const ss2d_core_params *p, void *cuda_stream);
 
+/* ------------------------------------------------------------------------------------
+ * Elementwise producers around the core, channel-first (B, D, H, W) contiguous maps of `dtype`.
+ *   ss2d_bias_act:      y = act(x + bias[d]); x and y may be the same buffer.  Replaces the bias
+ *                       addition and activation of Mlp.forward (vmamba.py:1160-1163).
+ *   ss2d_dwconv3x3_act: y = act(depthwise 3x3 convolution of x, stride 1, zero padding 1,
+ *                       weight (D, 3, 3) of `dtype`, optional fp32 bias).  Replaces
+ *                       self.conv2d followed by self.act in SS2Dv2.forwardv2 (vmamba.py:1582-1583).
+ * act: 0 none, 1 GELU (erf form), 2 SiLU.  Sums are formed in fp32, rounded to `dtype`, then the
+ * activation is applied and rounded, like the separate kernels these calls replace.
+ * -------------------------------------------------------------------------------- */
+typedef struct ss2d_pointwise_params {
+    const void *x;
+    const void *weight;     /* dwconv only */
+    const void *bias;       /* (D) fp32 or NULL */
+    void *y;
+    int64_t B, D, H, W;
+    int32_t dtype, act;
+} ss2d_pointwise_params;
+
+int ss2d_bias_act(const ss2d_pointwise_params *p, void *cuda_stream);
+int ss2d_dwconv3x3_act(const ss2d_pointwise_params *p, void *cuda_stream);
+
+/* ------------------------------------------------------------------------------------
+ * Route expansion: from x_dbl = x_proj(x), computed once on the map in its native pixel order, to
+ * the per-route streams ss2d_core_fwd consumes.  Replaces, for scans mode 0, the dt_projs grouped
+ * 1x1 convolution, the split and the three .contiguous() copies of SS2Dv2.forward_corev2
+ * (vmamba.py:1538-1543, 1546-1547), applied to projections of the un-scanned map (a 1x1 projection
+ * commutes with the CrossScan permutation, vmamba.py:1536-1537).
+ *   x_dbl     (B, 4, R+2N, L) act_dtype, pixel order h*W+w; strides in elements for batch and route
+ *   dt_weight (4, D, R) act_dtype contiguous (dt_projs.weight viewed per route)
+ *   delta[k]  (B, D, L) act_dtype  = dt_weight[k] . x_dbl[:, k, :R]  in the orientation order of route k
+ *   bc[k]     (B, 2N, L) fp32      = x_dbl[:, k, R:] (B rows then C rows) in the same order
+ * -------------------------------------------------------------------------------- */
+typedef struct ss2d_expand_params {
+    const void *x_dbl;
+    const void *dt_weight;
+    void *delta[SS2D_ROUTES];
+    void *bc[SS2D_ROUTES];
+    int64_t x_dbl_batch_stride, x_dbl_route_stride;
+    int64_t delta_batch_stride[SS2D_ROUTES];
+    int64_t bc_batch_stride[SS2D_ROUTES];
+    int64_t B, D, R, N, H, W;
+    int32_t act_dtype;
+    int32_t reserved0;
+} ss2d_expand_params;
+
+int ss2d_route_expand(const ss2d_expand_params *p, void *cuda_stream);
+
 /* Allocation-free form of ss2d_core_fwd.  It has no counterpart in the reference: it exists for
  * callers that can hand over inputs and outputs but cannot obtain device memory themselves (an
  * operator slot of a serving runtime that passes only pre-placed tensors, a host language bound to
@@ -147,17 +195,27 @@ int ss2d_core_fwd(const ss2d_core_params *p, void *cuda_stream);
 int ss2d_core_fwd_static(const ss2d_core_params *p, void *cuda_stream);
 int64_t ss2d_core_static_capacity(void);
 
-/* LayerNorm over the channel axis of a channel-first map, optionally summing `n_terms`
- * fp32 maps first.  Replaces LayerNorm(channel_first=True).forward (vmamba.py:1087-1093)
- * + the trailing cast (vmamba.py:1571).  in: (n_terms, B, D, L) fp32; out: (B, D, L). */
+/* LayerNorm over the channel axis of a channel-first map with an optional fused residual update:
+ *   s = in (+ add) (+ add_bias[d]);  sum_out = s (if given);  out = LN_D(s) * weight + bias.
+ * Replaces LayerNorm(channel_first=True).forward (vmamba.py:1087-1093) + the trailing cast
+ * (vmamba.py:1571) and, with `add`, the residual additions of VSSBlock._forward
+ * (vmamba.py:1772, 1777) together with the norm that follows them.
+ *   in       (B, D, L) fp32          add      (B, D, L) io_dtype or NULL
+ *   add_bias (D) fp32 or NULL        sum_out  (B, D, L) fp32 or NULL; may be the same buffer as `in`
+ *   weight, bias (D) fp32 or NULL    out      (B, D, L) io_dtype
+ * All four maps share one layout: pixels contiguous, `channel_stride` and `batch_stride` in
+ * elements (0 = dense channel-first: L and D*L). */
 typedef struct ss2d_norm_params {
     const void *in;
+    const void *add;
+    const void *add_bias;
+    void *sum_out;
     const void *weight, *bias;
     void *out;
     int64_t B, D, L;
-    int32_t n_terms, out_dtype;
+    int64_t batch_stride, channel_stride;
+    int32_t io_dtype;
     float eps;
-    int32_t reserved0;
 } ss2d_norm_params;
 
 int ss2d_layer_norm_cf(const ss2d_norm_params *p, void *cuda_stream);

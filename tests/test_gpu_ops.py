@@ -153,6 +153,66 @@ def test_layer_norm_cf(vb, shape):
     assert O.max_rel_err(host(vb.layer_norm_cf(dev(y))), O.layer_norm_cf(y)) <= 2e-5
 
 
+@pytest.mark.parametrize("shape", [(2, 96, 56, 56), (3, 192, 28, 28), (2, 384, 14, 14), (2, 768, 7, 7), (1, 1536, 7, 7), (1, 7, 5, 3)])
+def test_layer_norm_cf_fused_residual_update(vb, shape):
+    rng = np.random.default_rng(sum(shape))
+    x = rng.standard_normal(shape, dtype=np.float32) * 2
+    add = O.round_bf16(rng.standard_normal(shape, dtype=np.float32))
+    ab = rng.standard_normal(shape[1], dtype=np.float32)
+    w = rng.standard_normal(shape[1], dtype=np.float32)
+    b = rng.standard_normal(shape[1], dtype=np.float32)
+    s = x + add + ab.reshape(1, -1, 1, 1)
+    ref = O.layer_norm_cf(s, w, b)
+    xt = dev(x)
+    got = vb.layer_norm_cf(xt, dev(w), dev(b), out_dtype=torch.bfloat16, add=dev(add, torch.bfloat16), add_bias=dev(ab), update=True)
+    assert np.array_equal(host(xt), s.astype(np.float32)), "residual stream must hold in + add + bias exactly"
+    assert O.max_rel_err(host(got), ref) <= 8e-3
+    xt2 = dev(x)
+    got32 = vb.layer_norm_cf(xt2, dev(w), dev(b), add=dev(add), update=False)
+    assert np.array_equal(host(xt2), x)
+    assert O.max_rel_err(host(got32), O.layer_norm_cf(x + add, w, b)) <= 2e-5
+
+
+# ------------------------------------------------------------------------------ elementwise producers
+@pytest.mark.parametrize("shape", [(2, 96, 56, 56), (2, 192, 28, 28), (3, 384, 14, 14), (2, 768, 7, 7), (1, 3, 5, 9), (1, 2, 1, 1)])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_dwconv3x3_silu(vb, shape, dtype):
+    import torch.nn.functional as F
+    from vmamba_b200 import ops
+    rng = np.random.default_rng(sum(shape))
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    x = rng.standard_normal(shape, dtype=np.float32)
+    w = rng.standard_normal((shape[1], 1, 3, 3), dtype=np.float32) / 3
+    if dtype == "bf16":
+        x, w = O.round_bf16(x), O.round_bf16(w)
+    ref = F.conv2d(torch.from_numpy(x), torch.from_numpy(w), None, padding=1, groups=shape[1])
+    if dtype == "bf16":
+        ref = ref.to(torch.bfloat16).float()          # the convolution result is stored before the activation
+    ref = F.silu(ref).numpy()
+    got = ops.dwconv3x3_act(dev(x, td), dev(w, td), None, "silu")
+    assert got.dtype == td and tuple(got.shape) == shape
+    assert O.max_rel_err(host(got), ref) <= (1e-5 if dtype == "f32" else 8e-3)
+
+
+@pytest.mark.parametrize("shape", [(2, 384, 56, 56), (2, 1536, 14, 14), (3, 3072, 7, 7), (1, 5, 3, 3)])
+@pytest.mark.parametrize("act", ["gelu", "silu", "none"])
+def test_bias_act(vb, shape, act):
+    import torch.nn.functional as F
+    from vmamba_b200 import ops
+    rng = np.random.default_rng(shape[1])
+    x = O.round_bf16(rng.standard_normal(shape, dtype=np.float32) * 2)
+    b = O.round_bf16(rng.standard_normal(shape[1], dtype=np.float32))
+    s = (torch.from_numpy(x) + torch.from_numpy(b).view(1, -1, 1, 1)).to(torch.bfloat16).float()
+    ref = {"gelu": F.gelu, "silu": F.silu, "none": lambda t: t}[act](s).numpy()
+    xt = dev(x, torch.bfloat16)
+    got = ops.bias_act_(xt, dev(b), act)
+    assert got.data_ptr() == xt.data_ptr()
+    assert O.max_rel_err(host(got), ref) <= 8e-3
+    x32 = rng.standard_normal(shape, dtype=np.float32)
+    ref32 = {"gelu": F.gelu, "silu": F.silu, "none": lambda t: t}[act](torch.from_numpy(x32) + torch.from_numpy(b).view(1, -1, 1, 1)).numpy()
+    assert O.max_rel_err(host(ops.bias_act_(dev(x32), dev(b), act)), ref32) <= 1e-5
+
+
 # ------------------------------------------------------------------------------ fused core
 def _core_case(Bt, D, H, W, N, seed, Cmodel=None):
     import math
@@ -210,6 +270,28 @@ def test_fused_core_bf16(vb, shape):
     y = _run_core(vb, c, "bf16")
     assert y.dtype == torch.bfloat16
     assert O.max_rel_err(host(y), ref) <= TOL_BF16
+
+
+@pytest.mark.parametrize("shape,N,Cm", [((2, 96, 56, 56), 1, None), ((3, 384, 14, 14), 1, None), ((2, 768, 7, 7), 1, None),
+                                        ((1, 5, 9, 11), 1, None), ((2, 12, 6, 10), 4, 64), ((1, 256, 16, 8), 2, 1024)])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_route_expand_vs_library_projection(vb, shape, N, Cm, dtype):
+    """ss2d_route_expand against the same projections done with library GEMMs and copies."""
+    from vmamba_b200 import fused
+    c = _core_case(*shape, N=N, seed=7, Cmodel=Cm)
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    w = vb.CoreWeights.build(dev(c["wx"]), dev(c["wdt"]), dev(c["bias"]), dev(c["A_logs"]), dev(c["Ds"]), dev(c["lw"]),
+                             dev(c["lb"]), d_state=N, dt_rank=c["R"], dtype=td)
+    x = dev(c["x"], td)
+    got = fused.project(x, w)
+    ref = fused.project_library(x, w)
+    for g_, r_, name in zip(got, ref, ("bc_even", "bc_odd", "delta_even", "delta_odd")):
+        assert g_.shape == r_.shape, name
+        if name.startswith("bc"):
+            assert torch.equal(g_, r_), name          # pure data movement
+        else:
+            err = O.max_rel_err(host(g_), host(r_))
+            assert err <= (1e-5 if dtype == "f32" else 8e-3), (name, err)   # bf16: one ulp of the storage type
 
 
 def test_core_dstate_gt1_takes_surface_kernels(vb):

@@ -43,10 +43,23 @@ class CoreParams(ctypes.Structure):
                 ("act_dtype", _i32), ("y_dtype", _i32), ("with_norm", _i32), ("ln_eps", _f32)]
 
 
+class ExpandParams(ctypes.Structure):
+    _fields_ = [("x_dbl", _vp), ("dt_weight", _vp), ("delta", _vp * ROUTES), ("bc", _vp * ROUTES),
+                ("x_dbl_batch_stride", _i64), ("x_dbl_route_stride", _i64),
+                ("delta_batch_stride", _i64 * ROUTES), ("bc_batch_stride", _i64 * ROUTES),
+                ("B", _i64), ("D", _i64), ("R", _i64), ("N", _i64), ("H", _i64), ("W", _i64),
+                ("act_dtype", _i32), ("reserved0", _i32)]
+
+
+class PointwiseParams(ctypes.Structure):
+    _fields_ = [("x", _vp), ("weight", _vp), ("bias", _vp), ("y", _vp),
+                ("B", _i64), ("D", _i64), ("H", _i64), ("W", _i64), ("dtype", _i32), ("act", _i32)]
+
+
 class NormParams(ctypes.Structure):
-    _fields_ = [("in_", _vp), ("weight", _vp), ("bias", _vp), ("out", _vp),
-                ("B", _i64), ("D", _i64), ("L", _i64),
-                ("n_terms", _i32), ("out_dtype", _i32), ("eps", _f32), ("reserved0", _i32)]
+    _fields_ = [("in_", _vp), ("add", _vp), ("add_bias", _vp), ("sum_out", _vp), ("weight", _vp), ("bias", _vp),
+                ("out", _vp), ("B", _i64), ("D", _i64), ("L", _i64), ("batch_stride", _i64), ("channel_stride", _i64),
+                ("io_dtype", _i32), ("eps", _f32)]
 
 
 EXPORTS = {
@@ -59,6 +72,9 @@ EXPORTS = {
     "ss2d_core_fwd_static": (ctypes.c_int, [ctypes.POINTER(CoreParams), _vp]),
     "ss2d_core_static_capacity": (_i64, []),
     "ss2d_layer_norm_cf": (ctypes.c_int, [ctypes.POINTER(NormParams), _vp]),
+    "ss2d_route_expand": (ctypes.c_int, [ctypes.POINTER(ExpandParams), _vp]),
+    "ss2d_bias_act": (ctypes.c_int, [ctypes.POINTER(PointwiseParams), _vp]),
+    "ss2d_dwconv3x3_act": (ctypes.c_int, [ctypes.POINTER(PointwiseParams), _vp]),
     "ss2d_version": (ctypes.c_int, []),
     "ss2d_strerror": (ctypes.c_char_p, [ctypes.c_int]),
     "ss2d_launch_count": (_i64, []),

@@ -33,7 +33,7 @@ CONFIGS = dict(
 
 
 class _Block:
-    __slots__ = ("n1w", "n1b", "w_in", "w_dw", "core", "w_out", "n2w", "n2b", "w1", "b1", "w2", "b2", "D")
+    __slots__ = ("n1w", "n1b", "w_in", "w_dw", "core", "w_out", "n2w", "n2b", "w1", "b1f", "w2", "b2f", "D")
 
 
 class VSSMInfer:
@@ -91,8 +91,8 @@ class VSSMInfer:
                                            d_state=N, dt_rank=R, dtype=dtype)
                 b.w_out = T(p + "op.out_proj.weight", dtype)
                 b.n2w, b.n2b = T(p + "norm2.weight"), T(p + "norm2.bias")
-                b.w1, b.b1 = T(p + "mlp.fc1.weight", dtype), T(p + "mlp.fc1.bias", dtype)
-                b.w2, b.b2 = T(p + "mlp.fc2.weight", dtype), T(p + "mlp.fc2.bias", dtype)
+                b.w1, b.b1f = T(p + "mlp.fc1.weight", dtype), T(p + "mlp.fc1.bias", dtype).float()   # bias rounded as autocast does
+                b.w2, b.b2f = T(p + "mlp.fc2.weight", dtype), T(p + "mlp.fc2.bias", dtype).float()
                 stage.append(b)
             m.blocks.append(stage)
             q = f"layers.{i}.downsample."
@@ -122,16 +122,22 @@ class VSSMInfer:
             y += bias.view(1, -1, 1)
         return y.view(B, w.shape[0], H, W)
 
-    def _block(self, x: torch.Tensor, b: _Block) -> torch.Tensor:
-        """VSSBlock._forward, eval mode (vmamba.py:1766-1778).  x: fp32 residual stream."""
-        h = self._ln(x, b.n1w, b.n1b)
+    def _block(self, x: torch.Tensor, h: torch.Tensor, b: _Block, nxt):
+        """VSSBlock._forward, eval mode (vmamba.py:1766-1778).  x: fp32 residual stream (updated in
+        place), h = norm(x) of this block.  Returns (x, norm_next(x)) where norm_next is the first
+        norm of the following block (`nxt` = its weight/bias) or None at the end of a stage: both
+        residual additions are fused into the LayerNorm that consumes their result."""
         h = self._pw(b.w_in, h)                                       # in_proj          :1574
-        h = F.silu(F.conv2d(h, b.w_dw, None, padding=1, groups=b.D))  # dwconv 3x3, SiLU :1582-1583
+        h = ops.dwconv3x3_act(h, b.w_dw, None, "silu")                # dwconv 3x3, SiLU :1582-1583
         h = ss2d_core(h, b.core)                                      # forward_core     :1584
-        x = x + self._pw(b.w_out, h)                                  # out_proj + skip  :1588, 1772
-        h = self._ln(x, b.n2w, b.n2b)
-        h = F.gelu(self._pw(b.w1, h, b.b1))                           # Mlp              :1160-1166
-        return x + self._pw(b.w2, h, b.b2)
+        o = self._pw(b.w_out, h)                                      # out_proj         :1588
+        h = ops.layer_norm_cf(x, b.n2w, b.n2b, 1e-5, self.dtype, add=o, update=True)     # x += o; norm2  :1772, 1777
+        h = ops.bias_act_(self._pw(b.w1, h), b.b1f, "gelu")           # Mlp fc1 + GELU   :1160-1163
+        m = self._pw(b.w2, h)                                         # fc2 (its bias joins the residual update)
+        if nxt is None:
+            x.add_(m).add_(b.b2f.view(1, -1, 1, 1))
+            return x, None
+        return x, ops.layer_norm_cf(x, nxt[0], nxt[1], 1e-5, self.dtype, add=m, add_bias=b.b2f, update=True)
 
     def _stem(self, img):
         s = self.stem
@@ -144,8 +150,10 @@ class VSSMInfer:
         x = self._stem(img)
         outs = []
         for i, stage in enumerate(self.blocks):
-            for b in stage:
-                x = self._block(x, b)
+            h = self._ln(x, stage[0].n1w, stage[0].n1b)
+            for j, b in enumerate(stage):
+                nxt = (stage[j + 1].n1w, stage[j + 1].n1b) if j + 1 < len(stage) else None
+                x, h = self._block(x, h, b, nxt)
             outs.append(x)
             d = self.down[i]
             if d is not None:      # downsample v3 (vmamba.py:1964-1971)

@@ -12,6 +12,9 @@ long long core_workspace_bytes(const ss2d_core_params* p);
 int core_fwd(const ss2d_core_params* p, cudaStream_t st);
 int core_fwd_static(const ss2d_core_params* p, cudaStream_t st);
 long long core_static_capacity();
+int route_expand(const ss2d_expand_params* p, cudaStream_t st);
+int bias_act(const ss2d_pointwise_params* p, cudaStream_t st);
+int dwconv3x3_act(const ss2d_pointwise_params* p, cudaStream_t st);
 
 static std::atomic<long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
@@ -30,6 +33,11 @@ int64_t ss2d_core_workspace_bytes(const ss2d_core_params* p) { return ss2d::core
 int ss2d_core_fwd(const ss2d_core_params* p, void* stream) { return ss2d::core_fwd(p, (cudaStream_t)stream); }
 int ss2d_core_fwd_static(const ss2d_core_params* p, void* stream) { return ss2d::core_fwd_static(p, (cudaStream_t)stream); }
 int64_t ss2d_core_static_capacity(void) { return ss2d::core_static_capacity(); }
+
+int ss2d_route_expand(const ss2d_expand_params* p, void* stream) { return ss2d::route_expand(p, (cudaStream_t)stream); }
+
+int ss2d_bias_act(const ss2d_pointwise_params* p, void* stream) { return ss2d::bias_act(p, (cudaStream_t)stream); }
+int ss2d_dwconv3x3_act(const ss2d_pointwise_params* p, void* stream) { return ss2d::dwconv3x3_act(p, (cudaStream_t)stream); }
 
 int ss2d_version(void) { return SS2D_ABI_VERSION; }
 int64_t ss2d_launch_count(void) { return ss2d::g_launches.load(std::memory_order_relaxed); }

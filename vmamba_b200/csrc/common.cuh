@@ -91,6 +91,8 @@ template <typename T, int VEC> struct Vec {
         }
     }
     static __device__ __forceinline__ void load(const T* p, float (&v)[VEC]) { unpack(load_raw(p), v); }
+    // for shared memory (or global data written earlier in the same kernel): no read-only path
+    static __device__ __forceinline__ void load_plain(const T* p, float (&v)[VEC]) { unpack(load_raw<false>(p), v); }
     static __device__ __forceinline__ void store(T* p, const float (&v)[VEC]) {
         Raw r;
         if constexpr (sizeof(T) == 4) {

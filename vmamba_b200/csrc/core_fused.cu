@@ -428,10 +428,9 @@ int core_fwd(const ss2d_core_params* p, cudaStream_t st) {
     else r = launch_core_v<__half>(a, c, (unsigned)grid, st);
     if (r != SS2D_OK) return r;
     if (!p->with_norm) return SS2D_OK;
-    ss2d_norm_params n;
+    ss2d_norm_params n = {};
     n.in = merged; n.weight = p->ln_weight; n.bias = p->ln_bias; n.out = p->y;
-    n.B = p->B; n.D = p->D; n.L = p->H * p->W; n.n_terms = 1; n.out_dtype = p->y_dtype; n.eps = p->ln_eps;
-    n.reserved0 = 0;
+    n.B = p->B; n.D = p->D; n.L = p->H * p->W; n.io_dtype = p->y_dtype; n.eps = p->ln_eps;
     return layer_norm_cf(&n, st);
 }
 
@@ -521,10 +520,9 @@ int core_fwd_static(const ss2d_core_params* p, cudaStream_t st) {
     else r = launch_core_v<__half>(a, c, (unsigned)grid, st);
     if (r != SS2D_OK) return r;
     if (!p->with_norm) return SS2D_OK;
-    ss2d_norm_params n;
+    ss2d_norm_params n = {};
     n.in = merged; n.weight = p->ln_weight; n.bias = p->ln_bias; n.out = p->y;
-    n.B = p->B; n.D = p->D; n.L = p->H * p->W; n.n_terms = 1; n.out_dtype = p->y_dtype; n.eps = p->ln_eps;
-    n.reserved0 = 0;
+    n.B = p->B; n.D = p->D; n.L = p->H * p->W; n.io_dtype = p->y_dtype; n.eps = p->ln_eps;
     return layer_norm_cf(&n, st);
 }
 

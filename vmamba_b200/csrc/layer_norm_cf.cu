@@ -1,123 +1,227 @@
-// LayerNorm over the channel axis of a channel-first map (B, D, L), fp32 statistics.
+// LayerNorm over the channel axis of a channel-first map, fp32 statistics, with an optional fused
+// residual update:   s = in (+ add) (+ add_bias[d]);   [sum_out = s];   out = LN_D(s) * weight + bias.
 //
-// A CTA owns 32 consecutive pixels of one image: threadIdx.x runs along the pixels (every global
-// access is a full 128-byte line per channel), threadIdx.y splits the D channels.  Mean and
-// variance are the two-pass kind (sum of squared deviations), as the torch operator this replaces.
-// Values are kept in registers between the passes when D / NTY fits the cache, else re-read
-// (second and third reads come from L1/L2).  Optionally sums n_terms input maps on the way in.
+// An "item" is PV consecutive pixels of one image; items are numbered across the whole batch so
+// that every lane of every warp has work whatever the map size (L = 49 or 196 pixels per image
+// would otherwise leave most of a 32-pixel tile empty).  threadIdx.x runs along items (each global
+// access of a warp is one contiguous PV*32-element run per channel), threadIdx.y splits the D
+// channels.  Mean and variance are the two-pass kind (sum of squared deviations), like the torch
+// operator this replaces; values stay in registers between the passes when D / NTY fits, else
+// they are re-read (from L1/L2).
 #include "common.cuh"
 
 namespace ss2d {
 
 struct NormArgs {
     const float* in;
+    const void* add;
+    const float* add_bias;
+    float* sum_out;
     const float *w, *b;
     void* out;
-    long long B, D, L, term_stride;
-    int n_terms;
+    long long bs, cs;        // element strides between images and between channels (pixels are contiguous)
+    int D, L, nv, items;     // nv = L / PV items per image, items = B * nv
     float eps;
 };
 
-template <typename Tout, int NTY, int CACHE>
+template <typename Tio, int NTY, int CACHE, int PV>
 __global__ void __launch_bounds__(32 * NTY) layer_norm_cf_kernel(const NormArgs a) {
-    __shared__ float red[NTY][33];
+    __shared__ float red[NTY][32][PV];
     const int tx = threadIdx.x, ty = threadIdx.y;
-    const long long tiles = (a.L + 31) / 32;
-    const long long bimg = blockIdx.x / tiles, p = (blockIdx.x % tiles) * 32 + tx;
-    const bool in = p < a.L;
-    const float* __restrict__ src = a.in + bimg * a.D * a.L + p;
-    const int D = (int)a.D;
+    const int item = blockIdx.x * 32 + tx;
+    const bool live = item < a.items;
+    const int bimg = live ? item / a.nv : 0;
+    const long long base = (long long)bimg * a.bs + (long long)(live ? (item - bimg * a.nv) : 0) * PV;
+    const float* __restrict__ src = a.in + base;
+    const Tio* __restrict__ addp = a.add ? (const Tio*)a.add + base : nullptr;
+    const int D = a.D;
 
-    auto fetch = [&](int d) -> float {
-        float v = 0.f;
-        if (in) {
-            const float* q = src + (long long)d * a.L;
-            v = q[0];
-            for (int t = 1; t < a.n_terms; ++t) v += q[t * a.term_stride];
-        }
-        return v;
-    };
-    auto reduce_over_ty = [&](float v) -> float {
-        red[ty][tx] = v;
-        __syncthreads();
-        float s = 0.f;
+    auto fetch = [&](int d, float (&v)[PV]) {
+        if (!live) {
 #pragma unroll
-        for (int j = 0; j < NTY; ++j) s += red[j][tx];
+            for (int i = 0; i < PV; ++i) v[i] = 0.f;
+            return;
+        }
+        const long long off = (long long)d * a.cs;
+        Vec<float, PV>::load_plain(src + off, v);      // `in` may alias `sum_out`: no read-only path
+        if (addp) {
+            float t[PV];
+            Vec<Tio, PV>::load(addp + off, t);
+#pragma unroll
+            for (int i = 0; i < PV; ++i) v[i] += t[i];
+        }
+        if (a.add_bias) {
+            const float bb = __ldg(a.add_bias + d);
+#pragma unroll
+            for (int i = 0; i < PV; ++i) v[i] += bb;
+        }
+        if (a.sum_out) Vec<float, PV>::store(a.sum_out + base + off, v);
+    };
+    auto reduce_over_ty = [&](float (&v)[PV]) {
+#pragma unroll
+        for (int i = 0; i < PV; ++i) red[ty][tx][i] = v[i];
         __syncthreads();
-        return s;
+#pragma unroll
+        for (int i = 0; i < PV; ++i) {
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < NTY; ++j) s += red[j][tx][i];
+            v[i] = s;
+        }
+        __syncthreads();
     };
 
-    float cache[CACHE > 0 ? CACHE : 1];
-    float s = 0.f;
+    float cache[CACHE > 0 ? CACHE : 1][PV];
+    float s[PV];
+#pragma unroll
+    for (int i = 0; i < PV; ++i) s[i] = 0.f;
     if constexpr (CACHE > 0) {
 #pragma unroll
-        for (int i = 0; i < CACHE; ++i) {
-            const int d = ty + i * NTY;
-            cache[i] = (d < D) ? fetch(d) : 0.f;
-            s += cache[i];
-        }
-    } else {
-        for (int d = ty; d < D; d += NTY) s += fetch(d);
-    }
-    const float mean = reduce_over_ty(s) / (float)D;
-    float q = 0.f;
-    if constexpr (CACHE > 0) {
+        for (int c = 0; c < CACHE; ++c) {
+            const int d = ty + c * NTY;
+            if (d < D) fetch(d, cache[c]);
+            else {
 #pragma unroll
-        for (int i = 0; i < CACHE; ++i) {
-            const int d = ty + i * NTY;
-            const float t = cache[i] - mean;
-            if (d < D) q = fmaf(t, t, q);
+                for (int i = 0; i < PV; ++i) cache[c][i] = 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < PV; ++i) s[i] += cache[c][i];
         }
     } else {
-        for (int d = ty; d < D; d += NTY) { const float t = fetch(d) - mean; q = fmaf(t, t, q); }
+        for (int d = ty; d < D; d += NTY) {
+            float v[PV];
+            fetch(d, v);
+#pragma unroll
+            for (int i = 0; i < PV; ++i) s[i] += v[i];
+        }
     }
-    const float rstd = rsqrtf(reduce_over_ty(q) / (float)D + a.eps);
-    if (!in) return;
-    Tout* __restrict__ dst = (Tout*)a.out + bimg * a.D * a.L + p;
-    auto emit = [&](int d, float v) {
-        float t = (v - mean) * rstd;
-        if (a.w) t *= __ldg(a.w + d);
-        if (a.b) t += __ldg(a.b + d);
-        dst[(long long)d * a.L] = from_f<Tout>(t);
+    reduce_over_ty(s);
+    float mean[PV], q[PV];
+#pragma unroll
+    for (int i = 0; i < PV; ++i) { mean[i] = s[i] / (float)D; q[i] = 0.f; }
+    // after the first pass the sum lives in sum_out (if any): re-reads must not add again
+    const float* __restrict__ again = a.sum_out ? a.sum_out + base : nullptr;
+    auto refetch = [&](int d, float (&v)[PV]) {
+        if (!live) {
+#pragma unroll
+            for (int i = 0; i < PV; ++i) v[i] = 0.f;
+            return;
+        }
+        const long long off = (long long)d * a.cs;
+        if (again) { Vec<float, PV>::load_plain(again + off, v); return; }
+        Vec<float, PV>::load_plain(src + off, v);
+        if (addp) {
+            float t[PV];
+            Vec<Tio, PV>::load(addp + off, t);
+#pragma unroll
+            for (int i = 0; i < PV; ++i) v[i] += t[i];
+        }
+        if (a.add_bias) {
+            const float bb = __ldg(a.add_bias + d);
+#pragma unroll
+            for (int i = 0; i < PV; ++i) v[i] += bb;
+        }
     };
     if constexpr (CACHE > 0) {
 #pragma unroll
-        for (int i = 0; i < CACHE; ++i) {
-            const int d = ty + i * NTY;
-            if (d < D) emit(d, cache[i]);
+        for (int c = 0; c < CACHE; ++c) {
+            if (ty + c * NTY < D) {
+#pragma unroll
+                for (int i = 0; i < PV; ++i) { const float t = cache[c][i] - mean[i]; q[i] = fmaf(t, t, q[i]); }
+            }
         }
     } else {
-        for (int d = ty; d < D; d += NTY) emit(d, fetch(d));
+        for (int d = ty; d < D; d += NTY) {
+            float v[PV];
+            refetch(d, v);
+#pragma unroll
+            for (int i = 0; i < PV; ++i) { const float t = v[i] - mean[i]; q[i] = fmaf(t, t, q[i]); }
+        }
+    }
+    reduce_over_ty(q);
+    if (!live) return;
+    float rstd[PV];
+#pragma unroll
+    for (int i = 0; i < PV; ++i) rstd[i] = rsqrtf(q[i] / (float)D + a.eps);
+    Tio* __restrict__ dst = (Tio*)a.out + base;
+    auto emit = [&](int d, const float (&v)[PV]) {
+        const float g = a.w ? __ldg(a.w + d) : 1.f, be = a.b ? __ldg(a.b + d) : 0.f;
+        float o[PV];
+#pragma unroll
+        for (int i = 0; i < PV; ++i) o[i] = fmaf((v[i] - mean[i]) * rstd[i], g, be);
+        Vec<Tio, PV>::store(dst + (long long)d * a.cs, o);
+    };
+    if constexpr (CACHE > 0) {
+#pragma unroll
+        for (int c = 0; c < CACHE; ++c) {
+            const int d = ty + c * NTY;
+            if (d < D) emit(d, cache[c]);
+        }
+    } else {
+        for (int d = ty; d < D; d += NTY) {
+            float v[PV];
+            refetch(d, v);
+            emit(d, v);
+        }
     }
 }
 
-template <typename Tout>
-static void launch_norm(const NormArgs& a, cudaStream_t st) {
-    const long long ctas = a.B * ((a.L + 31) / 32);
-    const unsigned g = (unsigned)ctas;
-    if (a.D <= 8 * 12) layer_norm_cf_kernel<Tout, 8, 12><<<g, dim3(32, 8), 0, st>>>(a);
-    else if (a.D <= 8 * 24) layer_norm_cf_kernel<Tout, 8, 24><<<g, dim3(32, 8), 0, st>>>(a);
-    else if (a.D <= 16 * 24) layer_norm_cf_kernel<Tout, 16, 24><<<g, dim3(32, 16), 0, st>>>(a);
-    else if (a.D <= 32 * 24) layer_norm_cf_kernel<Tout, 32, 24><<<g, dim3(32, 32), 0, st>>>(a);
-    else layer_norm_cf_kernel<Tout, 32, 0><<<g, dim3(32, 32), 0, st>>>(a);
+template <typename Tio, int NTY, int CACHE, int PV>
+static void launch_one(const NormArgs& a, cudaStream_t st) {
+    layer_norm_cf_kernel<Tio, NTY, CACHE, PV><<<(unsigned)((a.items + 31) / 32), dim3(32, NTY), 0, st>>>(a);
+}
+
+template <typename Tio>
+static void launch_norm(NormArgs a, int pv, long long B, cudaStream_t st) {
+    const int D = a.D;
+    // registers hold CACHE * PV values per thread: at most 48 for CTAs of up to 512 threads,
+    // at most 24 for the 1024-thread CTAs (64 registers per thread)
+    if (D > 32 * 12) pv = 1;
+    else if (D > 16 * 12 && pv > 2) pv = 2;
+    a.nv = a.L / pv;
+    a.items = (int)(B * a.nv);
+    if (D <= 8 * 12) {
+        if (pv == 4) launch_one<Tio, 8, 12, 4>(a, st); else if (pv == 2) launch_one<Tio, 8, 12, 2>(a, st); else launch_one<Tio, 8, 12, 1>(a, st);
+    } else if (D <= 16 * 12) {
+        if (pv == 4) launch_one<Tio, 16, 12, 4>(a, st); else if (pv == 2) launch_one<Tio, 16, 12, 2>(a, st); else launch_one<Tio, 16, 12, 1>(a, st);
+    } else if (D <= 32 * 12) {
+        if (pv == 2) launch_one<Tio, 32, 12, 2>(a, st); else launch_one<Tio, 32, 12, 1>(a, st);
+    } else if (D <= 32 * 24) {
+        launch_one<Tio, 32, 24, 1>(a, st);
+    } else if (D <= 32 * 48) {
+        launch_one<Tio, 32, 48, 1>(a, st);
+    } else {
+        launch_one<Tio, 32, 0, 1>(a, st);
+    }
 }
 
 int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st) {
     if (!p) return SS2D_EINVAL_NULL;
     if (!p->in || !p->out) return SS2D_EINVAL_NULL;
-    if (!dtype_ok(p->out_dtype)) return SS2D_EINVAL_DTYPE;
-    if (p->B <= 0 || p->D <= 0 || p->L <= 0 || p->n_terms < 1 || p->n_terms > 8) return SS2D_EINVAL_SHAPE;
-    if (!aligned_to(p->in, 4) || !aligned_to(p->out, dtype_size(p->out_dtype)) || !aligned_to(p->weight, 4) ||
-        !aligned_to(p->bias, 4))
+    if (!dtype_ok(p->io_dtype)) return SS2D_EINVAL_DTYPE;
+    if (p->B <= 0 || p->D <= 0 || p->L <= 0) return SS2D_EINVAL_SHAPE;
+    if (p->D > 0x7fffffffLL || p->B * p->L > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
+    const long long bs = p->batch_stride ? p->batch_stride : p->D * p->L;
+    const long long cs = p->channel_stride ? p->channel_stride : p->L;
+    if (cs < p->L || (p->B > 1 && bs < p->L)) return SS2D_EINVAL_STRIDE;
+    const size_t so = dtype_size(p->io_dtype);
+    if (!aligned_to(p->in, 4) || !aligned_to(p->out, so) || !aligned_to(p->weight, 4) || !aligned_to(p->bias, 4) ||
+        !aligned_to(p->add, so) || !aligned_to(p->add_bias, 4) || !aligned_to(p->sum_out, 4))
         return SS2D_EINVAL_ALIGN;
-    if (p->B * ((p->L + 31) / 32) > 0x7fffffffLL || p->D > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
+    int pv = 4;
+    auto fit = [&](long long x) { if (x < 0) x = -x; while (pv > 1 && (x % pv) != 0) pv >>= 1; };
+    fit(p->L); fit(bs); fit(cs);
+    fit((long long)(reinterpret_cast<uintptr_t>(p->in) / 4));
+    fit((long long)(reinterpret_cast<uintptr_t>(p->out) / so));
+    if (p->add) fit((long long)(reinterpret_cast<uintptr_t>(p->add) / so));
+    if (p->sum_out) fit((long long)(reinterpret_cast<uintptr_t>(p->sum_out) / 4));
     NormArgs a;
-    a.in = (const float*)p->in; a.w = (const float*)p->weight; a.b = (const float*)p->bias; a.out = p->out;
-    a.B = p->B; a.D = p->D; a.L = p->L; a.term_stride = p->B * p->D * p->L;
-    a.n_terms = p->n_terms; a.eps = p->eps;
-    if (p->out_dtype == SS2D_F32) launch_norm<float>(a, st);
-    else if (p->out_dtype == SS2D_BF16) launch_norm<__nv_bfloat16>(a, st);
-    else launch_norm<__half>(a, st);
+    a.in = (const float*)p->in; a.add = p->add; a.add_bias = (const float*)p->add_bias; a.sum_out = (float*)p->sum_out;
+    a.w = (const float*)p->weight; a.b = (const float*)p->bias; a.out = p->out;
+    a.bs = bs; a.cs = cs; a.D = (int)p->D; a.L = (int)p->L; a.eps = p->eps; a.nv = 0; a.items = 0;
+    if (p->io_dtype == SS2D_F32) launch_norm<float>(a, pv, p->B, st);
+    else if (p->io_dtype == SS2D_BF16) launch_norm<__nv_bfloat16>(a, pv, p->B, st);
+    else launch_norm<__half>(a, pv, p->B, st);
     count_launch();
     return check_launch();
 }

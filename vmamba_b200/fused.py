@@ -30,8 +30,7 @@ K = 4
 class CoreWeights:
     """Inference-time constants of one SS2D core, laid out for the fused path."""
     wx: torch.Tensor            # (K*(R+2N), D) activation dtype
-    wdt_even: torch.Tensor      # (2, D, R) routes 0, 2, activation dtype
-    wdt_odd: torch.Tensor       # (2, D, R) routes 1, 3
+    wdt: torch.Tensor           # (K, D, R) activation dtype
     A: torch.Tensor             # (K*D, N) fp32, = -exp(A_logs)
     Ds: torch.Tensor            # (K*D,) fp32
     dt_bias: torch.Tensor       # (K*D,) fp32
@@ -49,9 +48,9 @@ class CoreWeights:
         KD = A_logs.shape[0]
         D = KD // K
         wx = x_proj_weight.detach().reshape(K * (R + 2 * N), D).to(dtype).contiguous()
-        wdt = dt_projs_weight.detach().reshape(K, D, R).to(dtype)
+        wdt = dt_projs_weight.detach().reshape(K, D, R).to(dtype).contiguous()
         f32 = lambda t: None if t is None else t.detach().float().contiguous()
-        return CoreWeights(wx, wdt[0::2].contiguous(), wdt[1::2].contiguous(),
+        return CoreWeights(wx, wdt,
                            (-torch.exp(A_logs.detach().float())).reshape(KD, N).contiguous(),
                            f32(Ds.reshape(-1)), f32(dt_projs_bias.reshape(-1)), f32(ln_weight), f32(ln_bias),
                            N, R, D, float(eps))
@@ -64,18 +63,44 @@ def project(x: torch.Tensor, w: CoreWeights):
       bc_even  (B, 2, 2N, L) fp32: B then C rows of routes 0 and 2, row-major pixel order
       bc_odd   (B, 2, 2N, L) fp32: routes 1 and 3, column-major pixel order
       delta_*  (B, 2, D, L) raw step sizes in the same orders, activation dtype
-    B and C are first rounded to the activation dtype (as the reference's projection output is)
-    and then widened: they are 2N rows per route against D rows of delta, and fp32 saves the
-    scan kernel two unpack instructions per element.
+    One library GEMM (x_proj on the un-scanned map) and one `ss2d_route_expand` launch.  B and C keep
+    the rounding of the projection output (activation dtype) and are then widened: they are 2N rows
+    per route against D rows of delta, and fp32 saves the scan kernel two unpack instructions per element.
     """
+    B, D, H, W = x.shape
+    L, R, N = H * W, w.dt_rank, w.d_state
+    C = R + 2 * N
+    xd = torch.matmul(w.wx, x.reshape(B, D, L))                       # (B, 4*C, L), route-major rows
+    delta = torch.empty((2, B, 2, D, L), device=x.device, dtype=x.dtype)   # [orientation][b][pair index]
+    bc = torch.empty((2, B, 2, 2 * N, L), device=x.device, dtype=torch.float32)
+    p = _lib.ExpandParams()
+    p.x_dbl, p.dt_weight = xd.data_ptr(), w.wdt.data_ptr()
+    p.x_dbl_batch_stride, p.x_dbl_route_stride = xd.stride(0), C * L
+    esz = x.element_size()
+    for k in range(K):
+        j, i = k % 2, k // 2
+        p.delta[k] = delta[j, :, i].data_ptr()
+        p.delta_batch_stride[k] = delta.stride(1)
+        p.bc[k] = bc[j, :, i].data_ptr()
+        p.bc_batch_stride[k] = bc.stride(1)
+    p.B, p.D, p.R, p.N, p.H, p.W = B, D, R, N, H, W
+    p.act_dtype = ops.dtype_code(x)
+    with torch.cuda.device(x.device):
+        check(lib().ss2d_route_expand(p, torch.cuda.current_stream(x.device).cuda_stream), "ss2d_route_expand")
+    return bc[0], bc[1], delta[0], delta[1]
+
+
+def project_library(x: torch.Tensor, w: CoreWeights):
+    """Same result as `project` with library calls only (batched GEMMs and copies); kept as the
+    cross-check of `ss2d_route_expand` in the tests."""
     B, D, H, W = x.shape
     L, R, N = H * W, w.dt_rank, w.d_state
     C = R + 2 * N
     xd = torch.matmul(w.wx, x.reshape(B, D, L)).view(B, 2, 2, C, H, W)    # route k = 2*i + j
     xd_even = xd[:, :, 0].reshape(B, 2, C, L)
     xd_odd = xd[:, :, 1].transpose(-1, -2).reshape(B, 2, C, L)
-    delta_even = torch.matmul(w.wdt_even, xd_even[:, :, :R])
-    delta_odd = torch.matmul(w.wdt_odd, xd_odd[:, :, :R])
+    delta_even = torch.matmul(w.wdt[0::2], xd_even[:, :, :R])
+    delta_odd = torch.matmul(w.wdt[1::2], xd_odd[:, :, :R])
     return xd_even[:, :, R:].float(), xd_odd[:, :, R:].float(), delta_even, delta_odd
 
 
@@ -160,8 +185,7 @@ def _ss2d_core_unfused(x, w: CoreWeights, with_norm: bool, out_dtype):
     C = R + 2 * N
     xs = ops.cross_scan_fwd(x, 0)                                        # (B, K, D, L)
     x_dbl = torch.matmul(w.wx.view(K, C, D), xs)                         # (B, K, C, L)
-    wdt = torch.stack((w.wdt_even[0], w.wdt_odd[0], w.wdt_even[1], w.wdt_odd[1]))
-    dts = torch.matmul(wdt, x_dbl[:, :, :R]).reshape(B, K * D, L)
+    dts = torch.matmul(w.wdt, x_dbl[:, :, :R]).reshape(B, K * D, L)
     Bs = x_dbl[:, :, R:R + N].contiguous()
     Cs = x_dbl[:, :, R + N:].contiguous()
     ys = ops.selective_scan_fwd(xs.view(B, K * D, L), dts, w.A, Bs, Cs, w.Ds, w.dt_bias, True, True)
