@@ -98,7 +98,7 @@ int ss2d_cross_merge(const ss2d_cross_params *p, void *cuda_stream);
  * SS2Dv2.forward_corev2 (vmamba.py:1536, 1553-1557, 1566-1571); the (B, 4, D, L) copy of x
  * and the per-route outputs never exist in memory.
  *
- *   x        (B, D, H, W) contiguous, act_dtype
+ *   x        (B, D, H, W), act_dtype; planes contiguous, batch / channel strides given (see below)
  *   delta[k] (B, D, L) per route k, act_dtype, contiguous planes (batch stride given), raw
  *            (pre-bias, pre-softplus) step sizes, stored in the ORIENTATION ORDER of route k:
  *            index h*W+w for k = 0, 2 and w*H+h for k = 1, 3 (never reversed)
@@ -106,7 +106,7 @@ int ss2d_cross_merge(const ss2d_cross_params *p, void *cuda_stream);
  *            act_dtype by the projection that produced them)
  *   A (4*D, N), Dskip (4*D), delta_bias (4*D): fp32, row index k*D + d
  *   ln_weight, ln_bias (D) fp32 or NULL (NULL: no affine); ln_eps; with_norm = 0 skips LayerNorm
- *   y        (B, D, H, W) contiguous, y_dtype (act_dtype or SS2D_F32)
+ *   y        (B, D, H, W), y_dtype (act_dtype or SS2D_F32), own batch / channel strides
  *   workspace: ss2d_core_workspace_bytes() bytes, 256-byte aligned (holds the fp32 merged map)
  * -------------------------------------------------------------------------------- */
 typedef struct ss2d_core_params {
@@ -125,6 +125,11 @@ typedef struct ss2d_core_params {
     int32_t act_dtype, y_dtype;
     int32_t with_norm;
     float ln_eps;
+    /* layout of x and of y: element strides between images and between channels; pixels of one
+     * (image, channel) plane are always contiguous.  0 = dense channel-first (D*L and L).
+     * (D, B, H, W) "channel-major" maps are batch stride L, channel stride B*L. */
+    int64_t x_batch_stride, x_channel_stride;
+    int64_t y_batch_stride, y_channel_stride;
 } ss2d_core_params;
 
 int64_t ss2d_core_workspace_bytes(const ss2d_core_params *p);
@@ -147,6 +152,8 @@ typedef struct ss2d_pointwise_params {
     void *y;
     int64_t B, D, H, W;
     int32_t dtype, act;
+    int32_t channel_major;   /* 0: maps are (B, D, H, W); 1: (D, B, H, W) */
+    int32_t reserved0;
 } ss2d_pointwise_params;
 
 int ss2d_bias_act(const ss2d_pointwise_params *p, void *cuda_stream);
@@ -158,7 +165,8 @@ int ss2d_dwconv3x3_act(const ss2d_pointwise_params *p, void *cuda_stream);
  * 1x1 convolution, the split and the three .contiguous() copies of SS2Dv2.forward_corev2
  * (vmamba.py:1538-1543, 1546-1547), applied to projections of the un-scanned map (a 1x1 projection
  * commutes with the CrossScan permutation, vmamba.py:1536-1537).
- *   x_dbl     (B, 4, R+2N, L) act_dtype, pixel order h*W+w; strides in elements for batch and route
+ *   x_dbl     (B, 4, R+2N, L) act_dtype, pixel order h*W+w; strides in elements for batch, route and row
+ *             (a GEMM on a channel-major map yields (4, R+2N, B, L): batch L, route (R+2N)*B*L, row B*L)
  *   dt_weight (4, D, R) act_dtype contiguous (dt_projs.weight viewed per route)
  *   delta[k]  (B, D, L) act_dtype  = dt_weight[k] . x_dbl[:, k, :R]  in the orientation order of route k
  *   bc[k]     (B, 2N, L) fp32      = x_dbl[:, k, R:] (B rows then C rows) in the same order
@@ -169,6 +177,7 @@ typedef struct ss2d_expand_params {
     void *delta[SS2D_ROUTES];
     void *bc[SS2D_ROUTES];
     int64_t x_dbl_batch_stride, x_dbl_route_stride;
+    int64_t x_dbl_row_stride;           /* between projected rows; 0 = L (dense (B, 4, R+2N, L)) */
     int64_t delta_batch_stride[SS2D_ROUTES];
     int64_t bc_batch_stride[SS2D_ROUTES];
     int64_t B, D, R, N, H, W;
@@ -203,8 +212,9 @@ int64_t ss2d_core_static_capacity(void);
  *   in       (B, D, L) fp32          add      (B, D, L) io_dtype or NULL
  *   add_bias (D) fp32 or NULL        sum_out  (B, D, L) fp32 or NULL; may be the same buffer as `in`
  *   weight, bias (D) fp32 or NULL    out      (B, D, L) io_dtype
- * All four maps share one layout: pixels contiguous, `channel_stride` and `batch_stride` in
- * elements (0 = dense channel-first: L and D*L). */
+ * Pixels of a plane are contiguous; `channel_stride` and `batch_stride` in elements (0 = dense
+ * channel-first: L and D*L).  `out` may use a different pair, which converts between the
+ * (B, D, L) and (D, B, L) layouts on the way. */
 typedef struct ss2d_norm_params {
     const void *in;
     const void *add;
@@ -213,7 +223,8 @@ typedef struct ss2d_norm_params {
     const void *weight, *bias;
     void *out;
     int64_t B, D, L;
-    int64_t batch_stride, channel_stride;
+    int64_t batch_stride, channel_stride;           /* of in, add, sum_out */
+    int64_t out_batch_stride, out_channel_stride;   /* of out; 0 = same as the inputs */
     int32_t io_dtype;
     float eps;
 } ss2d_norm_params;

@@ -294,6 +294,30 @@ def test_route_expand_vs_library_projection(vb, shape, N, Cm, dtype):
             assert err <= (1e-5 if dtype == "f32" else 8e-3), (name, err)   # bf16: one ulp of the storage type
 
 
+@pytest.mark.parametrize("shape", [(2, 96, 56, 56), (3, 384, 14, 14), (2, 768, 7, 7), (2, 6, 10, 12)])
+def test_channel_major_layout(vb, shape):
+    """(D, B, H, W) maps through the fused core, the LayerNorm and the elementwise producers."""
+    from vmamba_b200 import ops
+    c = _core_case(*shape, N=1, seed=3)
+    w = vb.CoreWeights.build(dev(c["wx"]), dev(c["wdt"]), dev(c["bias"]), dev(c["A_logs"]), dev(c["Ds"]), dev(c["lw"]),
+                             dev(c["lb"]), d_state=1, dt_rank=c["R"], dtype=torch.float32)
+    x = dev(c["x"])
+    xc = x.transpose(0, 1).contiguous()
+    y = vb.ss2d_core(x, w)
+    yc = vb.ss2d_core(xc, w, channel_major=True)
+    # the x_proj GEMM runs batched in one layout and as a single GEMM in the other: summation order may differ
+    assert O.max_rel_err(host(yc.transpose(0, 1)), host(y)) <= 1e-5
+    lw, lb = dev(c["lw"]), dev(c["lb"])
+    ref = vb.layer_norm_cf(x, lw, lb)
+    assert torch.equal(vb.layer_norm_cf(xc, lw, lb, channel_major=True).transpose(0, 1), ref)
+    assert torch.equal(vb.layer_norm_cf(xc, lw, lb, channel_major=True, out_channel_major=False), ref)
+    assert torch.equal(vb.layer_norm_cf(x, lw, lb, out_channel_major=True).transpose(0, 1), ref)
+    wdw = torch.randn(shape[1], 1, 3, 3, device="cuda")
+    assert torch.equal(ops.dwconv3x3_act(xc, wdw, None, "silu", channel_major=True).transpose(0, 1), ops.dwconv3x3_act(x, wdw))
+    bb = torch.randn(shape[1], device="cuda")
+    assert torch.equal(ops.bias_act_(xc.clone(), bb, "gelu", channel_major=True).transpose(0, 1), ops.bias_act_(x.clone(), bb, "gelu"))
+
+
 def test_core_dstate_gt1_takes_surface_kernels(vb):
     c = _core_case(2, 6, 10, 12, N=4, seed=9, Cmodel=32)
     ref = O.ss2d_core(c["x"], c["wx"], c["wdt"], c["bias"], c["A_logs"], c["Ds"], c["lw"], c["lb"], d_state=4, dt_rank=c["R"])

@@ -40,12 +40,13 @@ class CoreParams(ctypes.Structure):
                 ("y", _vp), ("workspace", _vp), ("workspace_bytes", _i64),
                 ("delta_batch_stride", _i64 * ROUTES), ("bc_batch_stride", _i64 * ROUTES),
                 ("B", _i64), ("D", _i64), ("H", _i64), ("W", _i64), ("N", _i64),
-                ("act_dtype", _i32), ("y_dtype", _i32), ("with_norm", _i32), ("ln_eps", _f32)]
+                ("act_dtype", _i32), ("y_dtype", _i32), ("with_norm", _i32), ("ln_eps", _f32),
+                ("x_batch_stride", _i64), ("x_channel_stride", _i64), ("y_batch_stride", _i64), ("y_channel_stride", _i64)]
 
 
 class ExpandParams(ctypes.Structure):
     _fields_ = [("x_dbl", _vp), ("dt_weight", _vp), ("delta", _vp * ROUTES), ("bc", _vp * ROUTES),
-                ("x_dbl_batch_stride", _i64), ("x_dbl_route_stride", _i64),
+                ("x_dbl_batch_stride", _i64), ("x_dbl_route_stride", _i64), ("x_dbl_row_stride", _i64),
                 ("delta_batch_stride", _i64 * ROUTES), ("bc_batch_stride", _i64 * ROUTES),
                 ("B", _i64), ("D", _i64), ("R", _i64), ("N", _i64), ("H", _i64), ("W", _i64),
                 ("act_dtype", _i32), ("reserved0", _i32)]
@@ -53,13 +54,14 @@ class ExpandParams(ctypes.Structure):
 
 class PointwiseParams(ctypes.Structure):
     _fields_ = [("x", _vp), ("weight", _vp), ("bias", _vp), ("y", _vp),
-                ("B", _i64), ("D", _i64), ("H", _i64), ("W", _i64), ("dtype", _i32), ("act", _i32)]
+                ("B", _i64), ("D", _i64), ("H", _i64), ("W", _i64), ("dtype", _i32), ("act", _i32),
+                ("channel_major", _i32), ("reserved0", _i32)]
 
 
 class NormParams(ctypes.Structure):
     _fields_ = [("in_", _vp), ("add", _vp), ("add_bias", _vp), ("sum_out", _vp), ("weight", _vp), ("bias", _vp),
                 ("out", _vp), ("B", _i64), ("D", _i64), ("L", _i64), ("batch_stride", _i64), ("channel_stride", _i64),
-                ("io_dtype", _i32), ("eps", _f32)]
+                ("out_batch_stride", _i64), ("out_channel_stride", _i64), ("io_dtype", _i32), ("eps", _f32)]
 
 
 EXPORTS = {

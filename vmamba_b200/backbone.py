@@ -109,42 +109,44 @@ class VSSMInfer:
         return m
 
     # ------------------------------------------------------------------ layers
-    def _ln(self, x, w, b, out_dtype=None):
+    # Between the stem and the head every map is kept CHANNEL-MAJOR, (C, B, H, W): each 1x1 projection
+    # is then ONE GEMM  (C_out x C_in) . (C_in x B*H*W)  whose long dimension is a multiple of 8 for any
+    # map size (14x14 and 7x7 maps would otherwise give 128 small GEMMs with unaligned leading dimensions),
+    # while every (channel, image) plane stays a contiguous run of H*W pixels for the scan kernels.
+    def _ln(self, x, w, b, out_dtype=None, cm=True, out_cm=None):
         """channel-first LayerNorm (vmamba.py:1078-1093), fp32 statistics."""
-        return ops.layer_norm_cf(x, w, b, 1e-5, out_dtype or self.dtype)
+        return ops.layer_norm_cf(x, w, b, 1e-5, out_dtype or self.dtype, channel_major=cm, out_channel_major=out_cm)
 
     @staticmethod
-    def _pw(w, x, bias=None):
-        """1x1 convolution of a channel-first map as a batched GEMM (vmamba.py:1060-1064)."""
-        B, C, H, W = x.shape
-        y = torch.matmul(w, x.view(B, C, H * W))
-        if bias is not None:
-            y += bias.view(1, -1, 1)
-        return y.view(B, w.shape[0], H, W)
+    def _pw(w, x):
+        """1x1 convolution of a channel-major map as one GEMM (vmamba.py:1060-1064)."""
+        C, B, H, W = x.shape
+        return torch.matmul(w, x.view(C, B * H * W)).view(w.shape[0], B, H, W)
 
     def _block(self, x: torch.Tensor, h: torch.Tensor, b: _Block, nxt):
         """VSSBlock._forward, eval mode (vmamba.py:1766-1778).  x: fp32 residual stream (updated in
         place), h = norm(x) of this block.  Returns (x, norm_next(x)) where norm_next is the first
         norm of the following block (`nxt` = its weight/bias) or None at the end of a stage: both
         residual additions are fused into the LayerNorm that consumes their result."""
-        h = self._pw(b.w_in, h)                                       # in_proj          :1574
-        h = ops.dwconv3x3_act(h, b.w_dw, None, "silu")                # dwconv 3x3, SiLU :1582-1583
-        h = ss2d_core(h, b.core)                                      # forward_core     :1584
-        o = self._pw(b.w_out, h)                                      # out_proj         :1588
-        h = ops.layer_norm_cf(x, b.n2w, b.n2b, 1e-5, self.dtype, add=o, update=True)     # x += o; norm2  :1772, 1777
-        h = ops.bias_act_(self._pw(b.w1, h), b.b1f, "gelu")           # Mlp fc1 + GELU   :1160-1163
-        m = self._pw(b.w2, h)                                         # fc2 (its bias joins the residual update)
+        h = self._pw(b.w_in, h)                                                   # in_proj          :1574
+        h = ops.dwconv3x3_act(h, b.w_dw, None, "silu", channel_major=True)        # dwconv 3x3, SiLU :1582-1583
+        h = ss2d_core(h, b.core, channel_major=True)                              # forward_core     :1584
+        o = self._pw(b.w_out, h)                                                  # out_proj         :1588
+        h = ops.layer_norm_cf(x, b.n2w, b.n2b, 1e-5, self.dtype, add=o, update=True, channel_major=True)   # :1772, 1777
+        h = ops.bias_act_(self._pw(b.w1, h), b.b1f, "gelu", channel_major=True)   # Mlp fc1 + GELU   :1160-1163
+        m = self._pw(b.w2, h)                                                     # fc2 (its bias joins the residual update)
         if nxt is None:
-            x.add_(m).add_(b.b2f.view(1, -1, 1, 1))
+            x.add_(m).add_(b.b2f.view(-1, 1, 1, 1))
             return x, None
-        return x, ops.layer_norm_cf(x, nxt[0], nxt[1], 1e-5, self.dtype, add=m, add_bias=b.b2f, update=True)
+        return x, ops.layer_norm_cf(x, nxt[0], nxt[1], 1e-5, self.dtype, add=m, add_bias=b.b2f, update=True,
+                                    channel_major=True)
 
     def _stem(self, img):
         s = self.stem
         x = F.conv2d(img.to(self.dtype), s["w0"], s["b0"], stride=2, padding=1)
-        x = F.gelu(self._ln(x.float(), s["n0w"], s["n0b"]))
+        x = F.gelu(self._ln(x.float(), s["n0w"], s["n0b"], cm=False))
         x = F.conv2d(x, s["w1"], s["b1"], stride=2, padding=1)
-        return self._ln(x.float(), s["n1w"], s["n1b"], torch.float32)
+        return self._ln(x.float(), s["n1w"], s["n1b"], torch.float32, cm=False, out_cm=True)    # -> (C, B, H, W)
 
     def _stages(self, img):
         x = self._stem(img)
@@ -156,9 +158,11 @@ class VSSMInfer:
                 x, h = self._block(x, h, b, nxt)
             outs.append(x)
             d = self.down[i]
-            if d is not None:      # downsample v3 (vmamba.py:1964-1971)
-                y = F.conv2d(x.to(self.dtype), d["w"], d["b"], stride=2, padding=1)
-                x = self._ln(y.float(), d["nw"], d["nb"], torch.float32)
+            if d is not None:      # downsample v3 (vmamba.py:1964-1971): a strided 3x3 convolution wants (B, C, H, W)
+                C, B, H, W = x.shape
+                xin = torch.empty((B, C, H, W), device=x.device, dtype=self.dtype).copy_(x.permute(1, 0, 2, 3))
+                y = F.conv2d(xin, d["w"], d["b"], stride=2, padding=1)
+                x = self._ln(y.float(), d["nw"], d["nb"], torch.float32, cm=False, out_cm=True)
         return outs, x
 
     # ------------------------------------------------------------------ public
@@ -169,7 +173,7 @@ class VSSMInfer:
             raise RuntimeError("this model was built without a classifier")
         _, x = self._stages(img)
         hd = self.head
-        x = self._ln(x, hd["nw"], hd["nb"], torch.float32).mean(dim=(2, 3))
+        x = self._ln(x, hd["nw"], hd["nb"], torch.float32, out_cm=False).mean(dim=(2, 3))
         return F.linear(x.to(self.dtype), hd["w"], hd["b"])
 
     @torch.no_grad()
@@ -179,5 +183,5 @@ class VSSMInfer:
         res = []
         for i in out_indices:
             w, b = self.outnorm[i]
-            res.append(self._ln(outs[i], w, b, torch.float32))
+            res.append(self._ln(outs[i], w, b, torch.float32, out_cm=False))
         return res

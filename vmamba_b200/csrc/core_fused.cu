@@ -33,6 +33,7 @@ struct CoreArgs {
     const float *A, *Dskip, *bias;
     float* merged;
     long long d_bs[4], bc_bs[4];
+    long long x_bs, x_cs;
     int B, D, H, W, L, G, PP, Wp, groups_per_image;
     unsigned magic_G, magic_W, magic_H;   // ceil(2^32 / d): n / d == umulhi(n, magic) for n * d < 2^32
 };
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a
     const bool first = v == 0, last = v == a.G - 1;
 
     // ---- issue every HBM load of the pass up front: x and the four delta vectors -------------
-    const typename VT::Raw rx = VT::load_raw((const T*)a.x + (long long)b * D * L + plane_off);
+    const typename VT::Raw rx = VT::load_raw((const T*)a.x + b * a.x_bs + d * a.x_cs + e0);
     const typename VT::Raw rd0 = VT::load_raw((const T*)a.delta[0] + b * a.d_bs[0] + plane_off);
     const typename VT::Raw rd2 = VT::load_raw((const T*)a.delta[2] + b * a.d_bs[2] + plane_off);
     const typename VT::Raw rd1 = VT::load_raw((const T*)a.delta[1] + b * a.d_bs[1] + plane_off);
@@ -307,7 +308,7 @@ static bool plan_planes(const ss2d_core_params* p, PlaneConfig& c) {
     auto el = [&](const void* q) { return (long long)(reinterpret_cast<uintptr_t>(q) / s); };
     int vec = 8;
     auto fit = [&](long long x) { if (x < 0) x = -x; while (vec > 1 && (x % vec) != 0) vec >>= 1; };
-    fit(L); fit(el(p->x));
+    fit(L); fit(el(p->x)); fit(p->x_batch_stride); fit(p->x_channel_stride);
     for (int k = 0; k < 4; ++k) {
         fit(el(p->delta[k]));
         fit((long long)(reinterpret_cast<uintptr_t>(p->Bm[k]) / 4)); fit((long long)(reinterpret_cast<uintptr_t>(p->Cm[k]) / 4));
@@ -374,6 +375,8 @@ static int validate_core(const ss2d_core_params* p) {
     for (int k = 0; k < 4; ++k) {
         if (p->B > 1 && (p->delta_batch_stride[k] < p->D * L || p->bc_batch_stride[k] < p->N * L)) return SS2D_EINVAL_STRIDE;
     }
+    if (p->x_batch_stride < 0 || p->x_channel_stride < 0 || p->y_batch_stride < 0 || p->y_channel_stride < 0) return SS2D_EINVAL_STRIDE;
+    if ((p->x_channel_stride && p->x_channel_stride < L) || (p->y_channel_stride && p->y_channel_stride < L)) return SS2D_EINVAL_STRIDE;
     const size_t s = dtype_size(p->act_dtype);
     if (!aligned_to(p->x, s) || !aligned_to(p->y, dtype_size(p->y_dtype)) || !aligned_to(p->A, 4) ||
         !aligned_to(p->Dskip, 4) || !aligned_to(p->delta_bias, 4) || !aligned_to(p->ln_weight, 4) ||
@@ -406,6 +409,8 @@ int core_fwd(const ss2d_core_params* p, cudaStream_t st) {
         merged = (float*)p->workspace;
     } else if (!aligned_to(p->y, 16)) {
         return SS2D_EINVAL_ALIGN;
+    } else if (p->y_batch_stride || p->y_channel_stride) {
+        return SS2D_ENOTSUP;     // the un-normalised fp32 map is written dense
     }
     CoreArgs a;
     a.x = p->x;
@@ -415,6 +420,8 @@ int core_fwd(const ss2d_core_params* p, cudaStream_t st) {
     }
     a.A = (const float*)p->A; a.Dskip = (const float*)p->Dskip; a.bias = (const float*)p->delta_bias;
     a.merged = merged;
+    a.x_bs = p->x_batch_stride ? p->x_batch_stride : p->D * p->H * p->W;
+    a.x_cs = p->x_channel_stride ? p->x_channel_stride : p->H * p->W;
     a.B = (int)p->B; a.D = (int)p->D; a.H = (int)p->H; a.W = (int)p->W; a.L = (int)(p->H * p->W);
     a.G = c.G; a.PP = c.PP; a.Wp = c.Wp;
     auto magic = [](long long d) { return (unsigned)(((1ULL << 32) + (unsigned long long)d - 1) / (unsigned long long)d); };
@@ -431,6 +438,7 @@ int core_fwd(const ss2d_core_params* p, cudaStream_t st) {
     ss2d_norm_params n = {};
     n.in = merged; n.weight = p->ln_weight; n.bias = p->ln_bias; n.out = p->y;
     n.B = p->B; n.D = p->D; n.L = p->H * p->W; n.io_dtype = p->y_dtype; n.eps = p->ln_eps;
+    n.out_batch_stride = p->y_batch_stride; n.out_channel_stride = p->y_channel_stride;
     return layer_norm_cf(&n, st);
 }
 
@@ -507,6 +515,8 @@ int core_fwd_static(const ss2d_core_params* p, cudaStream_t st) {
     }
     a.A = (const float*)p->A; a.Dskip = (const float*)p->Dskip; a.bias = (const float*)p->delta_bias;
     a.merged = merged;
+    a.x_bs = p->x_batch_stride ? p->x_batch_stride : p->D * p->H * p->W;
+    a.x_cs = p->x_channel_stride ? p->x_channel_stride : p->H * p->W;
     a.B = (int)p->B; a.D = (int)p->D; a.H = (int)p->H; a.W = (int)p->W; a.L = (int)(p->H * p->W);
     a.G = c.G; a.PP = c.PP; a.Wp = c.Wp;
     auto magic = [](long long d) { return (unsigned)(((1ULL << 32) + (unsigned long long)d - 1) / (unsigned long long)d); };
@@ -523,6 +533,7 @@ int core_fwd_static(const ss2d_core_params* p, cudaStream_t st) {
     ss2d_norm_params n = {};
     n.in = merged; n.weight = p->ln_weight; n.bias = p->ln_bias; n.out = p->y;
     n.B = p->B; n.D = p->D; n.L = p->H * p->W; n.io_dtype = p->y_dtype; n.eps = p->ln_eps;
+    n.out_batch_stride = p->y_batch_stride; n.out_channel_stride = p->y_channel_stride;
     return layer_norm_cf(&n, st);
 }
 

@@ -20,6 +20,7 @@ struct NormArgs {
     const float *w, *b;
     void* out;
     long long bs, cs;        // element strides between images and between channels (pixels are contiguous)
+    long long obs, ocs;      // the same for `out`
     int D, L, nv, items;     // nv = L / PV items per image, items = B * nv
     float eps;
 };
@@ -31,7 +32,8 @@ __global__ void __launch_bounds__(32 * NTY) layer_norm_cf_kernel(const NormArgs 
     const int item = blockIdx.x * 32 + tx;
     const bool live = item < a.items;
     const int bimg = live ? item / a.nv : 0;
-    const long long base = (long long)bimg * a.bs + (long long)(live ? (item - bimg * a.nv) : 0) * PV;
+    const long long pix = (long long)(live ? (item - bimg * a.nv) : 0) * PV;
+    const long long base = (long long)bimg * a.bs + pix;
     const float* __restrict__ src = a.in + base;
     const Tio* __restrict__ addp = a.add ? (const Tio*)a.add + base : nullptr;
     const int D = a.D;
@@ -143,13 +145,13 @@ __global__ void __launch_bounds__(32 * NTY) layer_norm_cf_kernel(const NormArgs 
     float rstd[PV];
 #pragma unroll
     for (int i = 0; i < PV; ++i) rstd[i] = rsqrtf(q[i] / (float)D + a.eps);
-    Tio* __restrict__ dst = (Tio*)a.out + base;
+    Tio* __restrict__ dst = (Tio*)a.out + (long long)bimg * a.obs + pix;
     auto emit = [&](int d, const float (&v)[PV]) {
         const float g = a.w ? __ldg(a.w + d) : 1.f, be = a.b ? __ldg(a.b + d) : 0.f;
         float o[PV];
 #pragma unroll
         for (int i = 0; i < PV; ++i) o[i] = fmaf((v[i] - mean[i]) * rstd[i], g, be);
-        Vec<Tio, PV>::store(dst + (long long)d * a.cs, o);
+        Vec<Tio, PV>::store(dst + (long long)d * a.ocs, o);
     };
     if constexpr (CACHE > 0) {
 #pragma unroll
@@ -203,14 +205,16 @@ int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st) {
     if (p->D > 0x7fffffffLL || p->B * p->L > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
     const long long bs = p->batch_stride ? p->batch_stride : p->D * p->L;
     const long long cs = p->channel_stride ? p->channel_stride : p->L;
-    if (cs < p->L || (p->B > 1 && bs < p->L)) return SS2D_EINVAL_STRIDE;
+    const long long obs = p->out_batch_stride ? p->out_batch_stride : bs;
+    const long long ocs = p->out_channel_stride ? p->out_channel_stride : cs;
+    if (cs < p->L || (p->B > 1 && bs < p->L) || ocs < p->L || (p->B > 1 && obs < p->L)) return SS2D_EINVAL_STRIDE;
     const size_t so = dtype_size(p->io_dtype);
     if (!aligned_to(p->in, 4) || !aligned_to(p->out, so) || !aligned_to(p->weight, 4) || !aligned_to(p->bias, 4) ||
         !aligned_to(p->add, so) || !aligned_to(p->add_bias, 4) || !aligned_to(p->sum_out, 4))
         return SS2D_EINVAL_ALIGN;
     int pv = 4;
     auto fit = [&](long long x) { if (x < 0) x = -x; while (pv > 1 && (x % pv) != 0) pv >>= 1; };
-    fit(p->L); fit(bs); fit(cs);
+    fit(p->L); fit(bs); fit(cs); fit(obs); fit(ocs);
     fit((long long)(reinterpret_cast<uintptr_t>(p->in) / 4));
     fit((long long)(reinterpret_cast<uintptr_t>(p->out) / so));
     if (p->add) fit((long long)(reinterpret_cast<uintptr_t>(p->add) / so));
@@ -218,7 +222,7 @@ int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st) {
     NormArgs a;
     a.in = (const float*)p->in; a.add = p->add; a.add_bias = (const float*)p->add_bias; a.sum_out = (float*)p->sum_out;
     a.w = (const float*)p->weight; a.b = (const float*)p->bias; a.out = p->out;
-    a.bs = bs; a.cs = cs; a.D = (int)p->D; a.L = (int)p->L; a.eps = p->eps; a.nv = 0; a.items = 0;
+    a.bs = bs; a.cs = cs; a.obs = obs; a.ocs = ocs; a.D = (int)p->D; a.L = (int)p->L; a.eps = p->eps; a.nv = 0; a.items = 0;
     if (p->io_dtype == SS2D_F32) launch_norm<float>(a, pv, p->B, st);
     else if (p->io_dtype == SS2D_BF16) launch_norm<__nv_bfloat16>(a, pv, p->B, st);
     else launch_norm<__half>(a, pv, p->B, st);

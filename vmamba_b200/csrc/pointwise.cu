@@ -25,6 +25,7 @@ struct BiasActArgs {
     void* y;
     long long items;     // B * D * (L / PV)
     int D, nv;           // nv = L / PV vectors per row
+    int rows_per_channel;   // 1 for (B, D, ...) maps (channel = row % D); B for (D, B, ...) maps (channel = row / B)
 };
 
 template <typename T, int PV, int ACT>
@@ -32,7 +33,7 @@ __global__ void __launch_bounds__(256) bias_act_kernel(const BiasActArgs a) {
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long it = (long long)blockIdx.x * blockDim.x + threadIdx.x; it < a.items; it += stride) {
         const long long row = it / a.nv;
-        const int d = (int)(row % a.D);
+        const int d = (int)((row / a.rows_per_channel) % a.D);
         const float b = a.bias ? __ldg(a.bias + d) : 0.f;
         float v[PV];
         Vec<T, PV>::load_plain((const T*)a.x + it * PV, v);      // x may be y: no read-only path
@@ -79,6 +80,7 @@ int bias_act(const ss2d_pointwise_params* p, cudaStream_t st) {
     fit((long long)(reinterpret_cast<uintptr_t>(p->y) / s));
     BiasActArgs a;
     a.x = p->x; a.bias = (const float*)p->bias; a.y = p->y; a.D = (int)p->D; a.nv = 0; a.items = 0;
+    a.rows_per_channel = p->channel_major ? (int)p->B : 1;
     const long long rows = p->B * p->D;
     if (p->dtype == SS2D_F32) launch_bias_act_v<float>(a, pv, rows, L, p->act, st);
     else if (p->dtype == SS2D_BF16) launch_bias_act_v<__nv_bfloat16>(a, pv, rows, L, p->act, st);
@@ -98,6 +100,7 @@ struct DwArgs {
     const float* bias;   // (D) or null
     void* y;
     int D, H, W, PP, planes, nvw;   // nvw = W / PV runs per row
+    int planes_per_channel;         // 1 for (B, D, H, W) maps, B for (D, B, H, W) maps
 };
 
 template <typename T, int PV, int ACT>
@@ -131,7 +134,7 @@ __global__ void __launch_bounds__(256) dwconv3x3_act_kernel(const DwArgs a) {
         const int w = i % W, t = i / W;
         const int rb = t % nrb, pl = t / nrb;
         const int h0 = rb * kRows, h1 = min(h0 + kRows, H);
-        const int d = (plane0 + pl) % a.D;
+        const int d = ((plane0 + pl) / a.planes_per_channel) % a.D;
         const T* __restrict__ wk = (const T*)a.w + d * 9;
         float k[9];
 #pragma unroll
@@ -209,6 +212,7 @@ int dwconv3x3_act(const ss2d_pointwise_params* p, cudaStream_t st) {
     DwArgs a;
     a.x = p->x; a.w = p->weight; a.bias = (const float*)p->bias; a.y = p->y;
     a.D = (int)p->D; a.H = (int)p->H; a.W = (int)p->W; a.PP = (int)PP; a.planes = (int)planes; a.nvw = 0;
+    a.planes_per_channel = p->channel_major ? (int)p->B : 1;
     const unsigned grid = (unsigned)((planes + PP - 1) / PP);
     const size_t smem = (size_t)PP * frame;
     if (p->dtype == SS2D_F32) return launch_dw_v<float>(a, pv, p->act, smem, grid, st);

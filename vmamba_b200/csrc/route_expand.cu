@@ -25,7 +25,7 @@ struct ExpandArgs {
     const void* wdt;     // (4, D, R) activation dtype
     void* delta[4];      // (B, D, L) each
     float* bc[4];        // (B, 2N, L) each
-    long long xd_bs, xd_ks;            // element strides of x_dbl: batch, route (row stride is L)
+    long long xd_bs, xd_ks, xd_rs;     // element strides of x_dbl: batch, route, row
     long long d_bs[4], bc_bs[4];
     int B, D, R, N2, C, H, W, L;       // N2 = 2N, C = R + 2N
     int items_per_plane, items_total;  // L / VEC, B * L / VEC
@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(kExpThreads) route_expand_kernel(const ExpandA
 #pragma unroll
             for (int i = 0; i < VEC; ++i) v[i] = 0.f;
             if (live) {
-                const T* rp = src + (long long)row * a.L;
+                const T* rp = src + (long long)row * a.xd_rs;
                 if (!col) {
                     Vec<T, VEC>::load(rp + q0, v);
                 } else {
@@ -171,7 +171,8 @@ int route_expand(const ss2d_expand_params* p, cudaStream_t st) {
     const long long L = p->H * p->W;
     if (L > 0x3fffffffLL || p->B * L > 0x7fffffffLL || p->R > 1024 || p->N > SS2D_MAX_DSTATE) return SS2D_EINVAL_SHAPE;
     const long long C = p->R + 2 * p->N;
-    if (p->x_dbl_route_stride < C * L || (p->B > 1 && p->x_dbl_batch_stride < 4 * C * L)) return SS2D_EINVAL_STRIDE;
+    const long long xd_rs = p->x_dbl_row_stride ? p->x_dbl_row_stride : L;
+    if (xd_rs < L || p->x_dbl_route_stride < L || (p->B > 1 && p->x_dbl_batch_stride < L)) return SS2D_EINVAL_STRIDE;
     const size_t s = dtype_size(p->act_dtype);
     if (!aligned_to(p->x_dbl, s) || !aligned_to(p->dt_weight, s)) return SS2D_EINVAL_ALIGN;
     for (int k = 0; k < 4; ++k) {
@@ -181,7 +182,7 @@ int route_expand(const ss2d_expand_params* p, cudaStream_t st) {
     // widest pixel vector that keeps every row start aligned in every tensor
     int vec = 8;
     auto fit = [&](long long x) { if (x < 0) x = -x; while (vec > 1 && (x % vec) != 0) vec >>= 1; };
-    fit(L); fit(p->x_dbl_batch_stride); fit(p->x_dbl_route_stride);
+    fit(L); fit(p->x_dbl_batch_stride); fit(p->x_dbl_route_stride); fit(xd_rs);
     fit((long long)(reinterpret_cast<uintptr_t>(p->x_dbl) / s));
     for (int k = 0; k < 4; ++k) {
         fit(p->delta_batch_stride[k]); fit(p->bc_batch_stride[k]);
@@ -194,7 +195,7 @@ int route_expand(const ss2d_expand_params* p, cudaStream_t st) {
         a.delta[k] = p->delta[k]; a.bc[k] = (float*)p->bc[k];
         a.d_bs[k] = p->delta_batch_stride[k]; a.bc_bs[k] = p->bc_batch_stride[k];
     }
-    a.xd_bs = p->x_dbl_batch_stride; a.xd_ks = p->x_dbl_route_stride;
+    a.xd_bs = p->x_dbl_batch_stride; a.xd_ks = p->x_dbl_route_stride; a.xd_rs = xd_rs;
     a.B = (int)p->B; a.D = (int)p->D; a.R = (int)p->R; a.N2 = (int)(2 * p->N); a.C = (int)C;
     a.H = (int)p->H; a.W = (int)p->W; a.L = (int)L;
     a.items_per_plane = (int)(L / vec);

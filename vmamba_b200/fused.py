@@ -56,8 +56,8 @@ class CoreWeights:
                            N, R, D, float(eps))
 
 
-def project(x: torch.Tensor, w: CoreWeights):
-    """x (B, D, H, W) -> per-orientation projections.
+def project(x: torch.Tensor, w: CoreWeights, channel_major: bool = False):
+    """x (B, D, H, W), or (D, B, H, W) with `channel_major` -> per-orientation projections.
 
     Returns (bc_even, bc_odd, delta_even, delta_odd):
       bc_even  (B, 2, 2N, L) fp32: B then C rows of routes 0 and 2, row-major pixel order
@@ -67,15 +67,22 @@ def project(x: torch.Tensor, w: CoreWeights):
     the rounding of the projection output (activation dtype) and are then widened: they are 2N rows
     per route against D rows of delta, and fp32 saves the scan kernel two unpack instructions per element.
     """
-    B, D, H, W = x.shape
+    if channel_major:
+        D, B, H, W = x.shape
+    else:
+        B, D, H, W = x.shape
     L, R, N = H * W, w.dt_rank, w.d_state
     C = R + 2 * N
-    xd = torch.matmul(w.wx, x.reshape(B, D, L))                       # (B, 4*C, L), route-major rows
     delta = torch.empty((2, B, 2, D, L), device=x.device, dtype=x.dtype)   # [orientation][b][pair index]
     bc = torch.empty((2, B, 2, 2 * N, L), device=x.device, dtype=torch.float32)
     p = _lib.ExpandParams()
+    if channel_major:      # one GEMM over the whole batch: (4C x D) . (D x B*L) -> rows (route, c), columns (b, l)
+        xd = torch.matmul(w.wx, x.reshape(D, B * L))
+        p.x_dbl_batch_stride, p.x_dbl_route_stride, p.x_dbl_row_stride = L, C * B * L, B * L
+    else:
+        xd = torch.matmul(w.wx, x.reshape(B, D, L))                   # (B, 4*C, L), route-major rows
+        p.x_dbl_batch_stride, p.x_dbl_route_stride, p.x_dbl_row_stride = xd.stride(0), C * L, L
     p.x_dbl, p.dt_weight = xd.data_ptr(), w.wdt.data_ptr()
-    p.x_dbl_batch_stride, p.x_dbl_route_stride = xd.stride(0), C * L
     esz = x.element_size()
     for k in range(K):
         j, i = k % 2, k // 2
@@ -105,15 +112,19 @@ def project_library(x: torch.Tensor, w: CoreWeights):
 
 
 def scan_merge_norm(x: torch.Tensor, proj, w: CoreWeights, *, with_norm: bool = True, out_dtype=None,
-                    workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                    channel_major: bool = False) -> torch.Tensor:
     """The CUDA part of the fused core (`ss2d_core_fwd`): x plus the projections returned by
     `project` -> merged (and normalised) map.  Launches one scan+merge kernel and, with
     `with_norm`, one LayerNorm kernel; allocates the output and the fp32 workspace unless given."""
     bc_even, bc_odd, delta_even, delta_odd = proj
-    B, D, H, W = x.shape
+    if channel_major:
+        D, B, H, W = x.shape
+    else:
+        B, D, H, W = x.shape
     R, N = w.dt_rank, w.d_state
     out_dtype = out_dtype or (x.dtype if with_norm else torch.float32)
-    y = out if out is not None else torch.empty((B, D, H, W), device=x.device, dtype=out_dtype)
+    y = out if out is not None else torch.empty(x.shape, device=x.device, dtype=out_dtype)
     p = CoreParams()
     p.x = x.data_ptr()
     srcs = (bc_even, bc_odd)
@@ -135,6 +146,9 @@ def scan_merge_norm(x: torch.Tensor, proj, w: CoreWeights, *, with_norm: bool = 
     p.B, p.D, p.H, p.W, p.N = B, D, H, W, N
     p.act_dtype, p.y_dtype = ops.dtype_code(x), ops.dtype_code(y)
     p.with_norm, p.ln_eps = int(with_norm), w.eps
+    if channel_major:
+        p.x_batch_stride, p.x_channel_stride = H * W, B * H * W
+        p.y_batch_stride, p.y_channel_stride = H * W, B * H * W
     need = int(lib().ss2d_core_workspace_bytes(p))
     if need < 0:
         raise RuntimeError("ss2d_core_workspace_bytes: invalid arguments")
@@ -154,20 +168,25 @@ def fused_supported(x_shape, d_state: int) -> bool:
 
 
 def ss2d_core(x: torch.Tensor, w: CoreWeights, *, with_norm: bool = True, out_dtype=None,
-              workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Fused forward of the SS2D core.  x: (B, D, H, W) CUDA tensor; returns (B, D, H, W) in
-    `out_dtype` (default x.dtype; fp32 required when `with_norm` is False).  Falls back to the
-    operator-surface kernels (still CUDA, never CPU) for d_state > 1 or planes too long for one CTA."""
+              workspace: Optional[torch.Tensor] = None, channel_major: bool = False) -> torch.Tensor:
+    """Fused forward of the SS2D core.  x: (B, D, H, W) CUDA tensor, or (D, B, H, W) with
+    `channel_major`; returns a map of the same layout in `out_dtype` (default x.dtype; fp32
+    required when `with_norm` is False).  Falls back to the operator-surface kernels (still CUDA,
+    never CPU) for d_state > 1 or planes too long for one CTA."""
     if not x.is_cuda:
         raise RuntimeError("vmamba_b200.ss2d_core runs on CUDA tensors only (no CPU fallback)")
     x = x.contiguous()
-    if x.shape[1] != w.d_inner:
-        raise RuntimeError(f"x has {x.shape[1]} channels, weights were built for {w.d_inner}")
+    if x.shape[0 if channel_major else 1] != w.d_inner:
+        raise RuntimeError(f"x has {x.shape[0 if channel_major else 1]} channels, weights were built for {w.d_inner}")
     out_dtype = out_dtype or (x.dtype if with_norm else torch.float32)
     with torch.autocast("cuda", enabled=False):
-        if not fused_supported(x.shape, w.d_state):
+        if not fused_supported(x.shape, w.d_state) or (channel_major and not with_norm):
+            if channel_major:
+                y = _ss2d_core_unfused(x.transpose(0, 1).contiguous(), w, with_norm, out_dtype)
+                return y.transpose(0, 1).contiguous()
             return _ss2d_core_unfused(x, w, with_norm, out_dtype)
-        return scan_merge_norm(x, project(x, w), w, with_norm=with_norm, out_dtype=out_dtype, workspace=workspace)
+        return scan_merge_norm(x, project(x, w, channel_major), w, with_norm=with_norm, out_dtype=out_dtype,
+                               workspace=workspace, channel_major=channel_major)
 
 
 def _vec_of(L: int) -> int:

@@ -218,11 +218,14 @@ def cross_merge_fn(y, in_channel_first=True, out_channel_first=True, one_by_one=
 # channel-first LayerNorm (out_norm of SS2D)
 # --------------------------------------------------------------------------------------------
 def layer_norm_cf(y: torch.Tensor, weight=None, bias=None, eps: float = 1e-5, out_dtype=None, *,
-                  add: torch.Tensor = None, add_bias: torch.Tensor = None, update: bool = False) -> torch.Tensor:
-    """LayerNorm over dim 1 of an fp32 (B, D, ...) map, as LayerNorm(channel_first=True)
+                  add: torch.Tensor = None, add_bias: torch.Tensor = None, update: bool = False,
+                  channel_major: bool = False, out_channel_major=None) -> torch.Tensor:
+    """LayerNorm over the channel axis of an fp32 map, as LayerNorm(channel_first=True)
     (vmamba.py:1078-1093); output in `out_dtype` (default fp32).
 
-    With `add` (a map of the output dtype) and/or `add_bias` (per channel), the sum
+    The map is (B, D, ...) or, with `channel_major`, (D, B, ...); `out_channel_major` (default: same
+    as the input) picks the layout of the result, so the call also converts between the two.
+    With `add` (a map of the output dtype, input layout) and/or `add_bias` (per channel), the sum
     y + add + add_bias is what gets normalised; `update=True` also writes that sum back into `y`
     (the residual update of VSSBlock._forward, vmamba.py:1772/1777, fused with the next norm)."""
     _require_cuda(y, weight, bias, add, add_bias)
@@ -234,9 +237,12 @@ def layer_norm_cf(y: torch.Tensor, weight=None, bias=None, eps: float = 1e-5, ou
         if update:
             raise RuntimeError("update=True needs a contiguous residual tensor")
         y = y.contiguous()
-    B, D = y.shape[0], y.shape[1]
+    if out_channel_major is None:
+        out_channel_major = channel_major
+    B, D = (y.shape[1], y.shape[0]) if channel_major else (y.shape[0], y.shape[1])
     L = y[0, 0].numel()
-    out = torch.empty(y.shape, device=y.device, dtype=out_dtype or torch.float32)
+    rest = tuple(y.shape[2:])
+    out = torch.empty(((D, B) if out_channel_major else (B, D)) + rest, device=y.device, dtype=out_dtype or torch.float32)
     w = None if weight is None else weight.contiguous().float()
     b = None if bias is None else bias.contiguous().float()
     if add is not None:
@@ -249,6 +255,8 @@ def layer_norm_cf(y: torch.Tensor, weight=None, bias=None, eps: float = 1e-5, ou
     p.sum_out = y.data_ptr() if update else None
     p.weight, p.bias, p.out = _ptr(w), _ptr(b), out.data_ptr()
     p.B, p.D, p.L = B, D, L
+    p.batch_stride, p.channel_stride = (L, B * L) if channel_major else (D * L, L)
+    p.out_batch_stride, p.out_channel_stride = (L, B * L) if out_channel_major else (D * L, L)
     p.io_dtype, p.eps = dtype_code(out), eps
     with torch.cuda.device(y.device):
         check(lib().ss2d_layer_norm_cf(p, _stream(y)), "ss2d_layer_norm_cf")
@@ -261,34 +269,41 @@ def layer_norm_cf(y: torch.Tensor, weight=None, bias=None, eps: float = 1e-5, ou
 _ACTS = {None: 0, "none": 0, "gelu": 1, "silu": 2}
 
 
-def bias_act_(x: torch.Tensor, bias=None, act="gelu") -> torch.Tensor:
-    """In place x <- act(x + bias[channel]) on a contiguous channel-first (B, D, H, W) map: the bias
-    addition and activation of Mlp.forward (vmamba.py:1160-1163) in one pass."""
+def _bdhw(x, channel_major):
+    return (x.shape[1], x.shape[0], x.shape[2], x.shape[3]) if channel_major else tuple(x.shape)
+
+
+def bias_act_(x: torch.Tensor, bias=None, act="gelu", channel_major: bool = False) -> torch.Tensor:
+    """In place x <- act(x + bias[channel]) on a contiguous (B, D, H, W) map ((D, B, H, W) with
+    `channel_major`): the bias addition and activation of Mlp.forward (vmamba.py:1160-1163) in one pass."""
     _require_cuda(x, bias)
     if x.dim() != 4 or not x.is_contiguous():
-        raise RuntimeError("bias_act_ expects a contiguous (B, D, H, W) tensor")
+        raise RuntimeError("bias_act_ expects a contiguous 4-d tensor")
+    B, D, H, W = _bdhw(x, channel_major)
     b = None if bias is None else bias.contiguous().float()
-    if b is not None and b.numel() != x.shape[1]:
+    if b is not None and b.numel() != D:
         raise RuntimeError("bias must have one value per channel")
-    p = PointwiseParams(x.data_ptr(), None, _ptr(b), x.data_ptr(), *x.shape, dtype_code(x), _ACTS[act])
+    p = PointwiseParams(x.data_ptr(), None, _ptr(b), x.data_ptr(), B, D, H, W, dtype_code(x), _ACTS[act], int(channel_major), 0)
     with torch.cuda.device(x.device):
         check(lib().ss2d_bias_act(p, _stream(x)), "ss2d_bias_act")
     return x
 
 
-def dwconv3x3_act(x: torch.Tensor, weight: torch.Tensor, bias=None, act="silu") -> torch.Tensor:
-    """act(depthwise 3x3 convolution, padding 1) of a channel-first map: conv2d + SiLU in front of the
-    SS2D core (vmamba.py:1582-1583).  weight: (D, 1, 3, 3) or (D, 3, 3)."""
+def dwconv3x3_act(x: torch.Tensor, weight: torch.Tensor, bias=None, act="silu", channel_major: bool = False) -> torch.Tensor:
+    """act(depthwise 3x3 convolution, padding 1) of a (B, D, H, W) map ((D, B, H, W) with
+    `channel_major`): conv2d + SiLU in front of the SS2D core (vmamba.py:1582-1583).
+    weight: (D, 1, 3, 3) or (D, 3, 3)."""
     _require_cuda(x, weight, bias)
     if x.dim() != 4:
-        raise RuntimeError("dwconv3x3_act expects a (B, D, H, W) tensor")
+        raise RuntimeError("dwconv3x3_act expects a 4-d tensor")
     x = x.contiguous()
-    if weight.numel() != x.shape[1] * 9:
+    B, D, H, W = _bdhw(x, channel_major)
+    if weight.numel() != D * 9:
         raise RuntimeError("weight must be (D, 1, 3, 3)")
     w = weight.contiguous().to(x.dtype)
     b = None if bias is None else bias.contiguous().float()
     y = torch.empty_like(x)
-    p = PointwiseParams(x.data_ptr(), w.data_ptr(), _ptr(b), y.data_ptr(), *x.shape, dtype_code(x), _ACTS[act])
+    p = PointwiseParams(x.data_ptr(), w.data_ptr(), _ptr(b), y.data_ptr(), B, D, H, W, dtype_code(x), _ACTS[act], int(channel_major), 0)
     with torch.cuda.device(x.device):
         check(lib().ss2d_dwconv3x3_act(p, _stream(x)), "ss2d_dwconv3x3_act")
     return y
