@@ -130,6 +130,7 @@ typedef struct ss2d_core_params {
      * (D, B, H, W) "channel-major" maps are batch stride L, channel stride B*L. */
     int64_t x_batch_stride, x_channel_stride;
     int64_t y_batch_stride, y_channel_stride;
+    int64_t delta_channel_stride[SS2D_ROUTES];   /* 0 = L; (D, B, L) step-size maps: L as batch stride and B*L here */
 } ss2d_core_params;
 
 int64_t ss2d_core_workspace_bytes(const ss2d_core_params *p);
@@ -180,6 +181,8 @@ typedef struct ss2d_expand_params {
     int64_t x_dbl_row_stride;           /* between projected rows; 0 = L (dense (B, 4, R+2N, L)) */
     int64_t delta_batch_stride[SS2D_ROUTES];
     int64_t bc_batch_stride[SS2D_ROUTES];
+    int64_t delta_channel_stride[SS2D_ROUTES];   /* 0 = L; (D, B, L) outputs: batch stride L, channel stride B*L */
+    int64_t bc_row_stride[SS2D_ROUTES];          /* 0 = L; (2N, B, L) outputs: batch stride L, row stride B*L */
     int64_t B, D, R, N, H, W;
     int32_t act_dtype;
     int32_t reserved0;

@@ -285,6 +285,15 @@ def test_route_expand_vs_library_projection(vb, shape, N, Cm, dtype):
     x = dev(c["x"], td)
     got = fused.project(x, w)
     ref = fused.project_library(x, w)
+    # channel-major maps: the streams come out as (pair, rows, B, L); same values
+    got_cm = fused.project(x.transpose(0, 1).contiguous(), w, channel_major=True)
+    for g_, r_, name in zip(got_cm, ref, ("bc_even", "bc_odd", "delta_even", "delta_odd")):
+        g_ = g_.permute(2, 0, 1, 3)
+        assert g_.shape == r_.shape, name
+        if name.startswith("bc"):
+            assert O.max_rel_err(host(g_), host(r_)) <= (1e-5 if dtype == "f32" else 8e-3), name
+        else:
+            assert O.max_rel_err(host(g_), host(r_)) <= (1e-5 if dtype == "f32" else 8e-3), name
     for g_, r_, name in zip(got, ref, ("bc_even", "bc_odd", "delta_even", "delta_odd")):
         assert g_.shape == r_.shape, name
         if name.startswith("bc"):

@@ -41,13 +41,15 @@ class CoreParams(ctypes.Structure):
                 ("delta_batch_stride", _i64 * ROUTES), ("bc_batch_stride", _i64 * ROUTES),
                 ("B", _i64), ("D", _i64), ("H", _i64), ("W", _i64), ("N", _i64),
                 ("act_dtype", _i32), ("y_dtype", _i32), ("with_norm", _i32), ("ln_eps", _f32),
-                ("x_batch_stride", _i64), ("x_channel_stride", _i64), ("y_batch_stride", _i64), ("y_channel_stride", _i64)]
+                ("x_batch_stride", _i64), ("x_channel_stride", _i64), ("y_batch_stride", _i64), ("y_channel_stride", _i64),
+                ("delta_channel_stride", _i64 * ROUTES)]
 
 
 class ExpandParams(ctypes.Structure):
     _fields_ = [("x_dbl", _vp), ("dt_weight", _vp), ("delta", _vp * ROUTES), ("bc", _vp * ROUTES),
                 ("x_dbl_batch_stride", _i64), ("x_dbl_route_stride", _i64), ("x_dbl_row_stride", _i64),
                 ("delta_batch_stride", _i64 * ROUTES), ("bc_batch_stride", _i64 * ROUTES),
+                ("delta_channel_stride", _i64 * ROUTES), ("bc_row_stride", _i64 * ROUTES),
                 ("B", _i64), ("D", _i64), ("R", _i64), ("N", _i64), ("H", _i64), ("W", _i64),
                 ("act_dtype", _i32), ("reserved0", _i32)]
 

@@ -32,7 +32,7 @@ struct CoreArgs {
     const float* Cm[4];
     const float *A, *Dskip, *bias;
     float* merged;
-    long long d_bs[4], bc_bs[4];
+    long long d_bs[4], d_cs[4], bc_bs[4];
     long long x_bs, x_cs;
     int B, D, H, W, L, G, PP, Wp, groups_per_image;
     unsigned magic_G, magic_W, magic_H;   // ceil(2^32 / d): n / d == umulhi(n, magic) for n * d < 2^32
@@ -208,10 +208,10 @@ __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a
 
     // ---- issue every HBM load of the pass up front: x and the four delta vectors -------------
     const typename VT::Raw rx = VT::load_raw((const T*)a.x + b * a.x_bs + d * a.x_cs + e0);
-    const typename VT::Raw rd0 = VT::load_raw((const T*)a.delta[0] + b * a.d_bs[0] + plane_off);
-    const typename VT::Raw rd2 = VT::load_raw((const T*)a.delta[2] + b * a.d_bs[2] + plane_off);
-    const typename VT::Raw rd1 = VT::load_raw((const T*)a.delta[1] + b * a.d_bs[1] + plane_off);
-    const typename VT::Raw rd3 = VT::load_raw((const T*)a.delta[3] + b * a.d_bs[3] + plane_off);
+    const typename VT::Raw rd0 = VT::load_raw((const T*)a.delta[0] + b * a.d_bs[0] + d * a.d_cs[0] + e0);
+    const typename VT::Raw rd2 = VT::load_raw((const T*)a.delta[2] + b * a.d_bs[2] + d * a.d_cs[2] + e0);
+    const typename VT::Raw rd1 = VT::load_raw((const T*)a.delta[1] + b * a.d_bs[1] + d * a.d_cs[1] + e0);
+    const typename VT::Raw rd3 = VT::load_raw((const T*)a.delta[3] + b * a.d_bs[3] + d * a.d_cs[3] + e0);
     float2 ul[NP], yrow[NP];
     unpack_pairs<T, VEC>(rx, ul);
 
@@ -312,7 +312,7 @@ static bool plan_planes(const ss2d_core_params* p, PlaneConfig& c) {
     for (int k = 0; k < 4; ++k) {
         fit(el(p->delta[k]));
         fit((long long)(reinterpret_cast<uintptr_t>(p->Bm[k]) / 4)); fit((long long)(reinterpret_cast<uintptr_t>(p->Cm[k]) / 4));
-        fit(p->delta_batch_stride[k]); fit(p->bc_batch_stride[k]);
+        fit(p->delta_batch_stride[k]); fit(p->bc_batch_stride[k]); fit(p->delta_channel_stride[k]);
     }
     // a thread's segment may wrap to the next line only at its middle: vec/2 divides H and W
     while (vec > 1 && (vec > p->H || vec > p->W || (p->H % (vec / 2)) != 0 || (p->W % (vec / 2)) != 0)) vec >>= 1;
@@ -373,7 +373,8 @@ static int validate_core(const ss2d_core_params* p) {
     if (p->H * p->W > 0x3fffffffLL || p->B * p->D > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
     const long long L = p->H * p->W;
     for (int k = 0; k < 4; ++k) {
-        if (p->B > 1 && (p->delta_batch_stride[k] < p->D * L || p->bc_batch_stride[k] < p->N * L)) return SS2D_EINVAL_STRIDE;
+        if (p->B > 1 && (p->delta_batch_stride[k] < L || p->bc_batch_stride[k] < L)) return SS2D_EINVAL_STRIDE;
+        if (p->delta_channel_stride[k] && p->delta_channel_stride[k] < L) return SS2D_EINVAL_STRIDE;
     }
     if (p->x_batch_stride < 0 || p->x_channel_stride < 0 || p->y_batch_stride < 0 || p->y_channel_stride < 0) return SS2D_EINVAL_STRIDE;
     if ((p->x_channel_stride && p->x_channel_stride < L) || (p->y_channel_stride && p->y_channel_stride < L)) return SS2D_EINVAL_STRIDE;
@@ -417,6 +418,7 @@ int core_fwd(const ss2d_core_params* p, cudaStream_t st) {
     for (int k = 0; k < 4; ++k) {
         a.delta[k] = p->delta[k]; a.Bm[k] = (const float*)p->Bm[k]; a.Cm[k] = (const float*)p->Cm[k];
         a.d_bs[k] = p->delta_batch_stride[k]; a.bc_bs[k] = p->bc_batch_stride[k];
+        a.d_cs[k] = p->delta_channel_stride[k] ? p->delta_channel_stride[k] : p->H * p->W;
     }
     a.A = (const float*)p->A; a.Dskip = (const float*)p->Dskip; a.bias = (const float*)p->delta_bias;
     a.merged = merged;
@@ -512,6 +514,7 @@ int core_fwd_static(const ss2d_core_params* p, cudaStream_t st) {
     for (int k = 0; k < 4; ++k) {
         a.delta[k] = p->delta[k]; a.Bm[k] = (const float*)p->Bm[k]; a.Cm[k] = (const float*)p->Cm[k];
         a.d_bs[k] = p->delta_batch_stride[k]; a.bc_bs[k] = p->bc_batch_stride[k];
+        a.d_cs[k] = p->delta_channel_stride[k] ? p->delta_channel_stride[k] : p->H * p->W;
     }
     a.A = (const float*)p->A; a.Dskip = (const float*)p->Dskip; a.bias = (const float*)p->delta_bias;
     a.merged = merged;

@@ -26,8 +26,9 @@ struct ExpandArgs {
     void* delta[4];      // (B, D, L) each
     float* bc[4];        // (B, 2N, L) each
     long long xd_bs, xd_ks, xd_rs;     // element strides of x_dbl: batch, route, row
-    long long d_bs[4], bc_bs[4];
-    int B, D, R, N2, C, H, W, L;       // N2 = 2N, C = R + 2N
+    long long d_bs[4], d_cs[4], bc_bs[4], bc_rs[4];   // delta: batch / channel strides; B-C rows: batch / row strides
+    int B, D, R, N2, C, H, W, L;       // N2 = 2N, C = R + 2N; L = run length (H*W, or B*H*W when images are adjacent)
+    int Limg;                          // H * W
     int items_per_plane, items_total;  // L / VEC, B * L / VEC
 };
 
@@ -54,7 +55,8 @@ __global__ void __launch_bounds__(kExpThreads) route_expand_kernel(const ExpandA
     const int b = live ? item / a.items_per_plane : 0;
     const int q0 = live ? (item - b * a.items_per_plane) * VEC : 0;
     {
-        const int w0 = q0 / a.H, h0 = q0 - w0 * a.H;
+        const int img0 = (q0 / a.Limg) * a.Limg, qi = q0 - img0;     // image of the first pixel, position inside it
+        const int w0 = qi / a.H, h0 = qi - w0 * a.H;
         const T* src = xd + (long long)b * a.xd_bs;
         for (int row = dg; row < a.C; row += NDG) {
             float v[VEC];
@@ -65,11 +67,11 @@ __global__ void __launch_bounds__(kExpThreads) route_expand_kernel(const ExpandA
                 if (!col) {
                     Vec<T, VEC>::load(rp + q0, v);
                 } else {
-                    int w = w0, h = h0;
+                    int w = w0, h = h0, base = img0;      // a run may continue into the next image
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) {
-                        v[i] = to_f<T>(rp[h * a.W + w]);
-                        if (++h == a.H) { h = 0; ++w; }
+                        v[i] = to_f<T>(rp[base + h * a.W + w]);
+                        if (++h == a.H) { h = 0; if (++w == a.W) { w = 0; base += a.Limg; } }
                     }
                 }
             }
@@ -91,7 +93,7 @@ __global__ void __launch_bounds__(kExpThreads) route_expand_kernel(const ExpandA
         for (int n = dg; n < a.N2; n += NDG) {
             float v[VEC];
             Vec<float, VEC>::load_plain(s_rows + (size_t)(a.R + n) * (NI * VEC) + it * VEC, v);
-            Vec<float, VEC>::store(a.bc[k] + b * a.bc_bs[k] + (long long)n * a.L + q0, v);
+            Vec<float, VEC>::store(a.bc[k] + b * a.bc_bs[k] + (long long)n * a.bc_rs[k] + q0, v);
         }
     }
 
@@ -125,7 +127,7 @@ __global__ void __launch_bounds__(kExpThreads) route_expand_kernel(const ExpandA
                     float o[VEC];
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) o[i] = (i & 1) ? acc[c][i >> 1].y : acc[c][i >> 1].x;
-                    Vec<T, VEC>::store(dout + (long long)(dc + dl0 + c) * a.L, o);
+                    Vec<T, VEC>::store(dout + (long long)(dc + dl0 + c) * a.d_cs[k], o);
                 }
             }
         }
@@ -177,29 +179,42 @@ int route_expand(const ss2d_expand_params* p, cudaStream_t st) {
     if (!aligned_to(p->x_dbl, s) || !aligned_to(p->dt_weight, s)) return SS2D_EINVAL_ALIGN;
     for (int k = 0; k < 4; ++k) {
         if (!aligned_to(p->delta[k], s) || !aligned_to(p->bc[k], 4)) return SS2D_EINVAL_ALIGN;
-        if (p->B > 1 && (p->delta_batch_stride[k] < p->D * L || p->bc_batch_stride[k] < 2 * p->N * L)) return SS2D_EINVAL_STRIDE;
+        if (p->B > 1 && (p->delta_batch_stride[k] < L || p->bc_batch_stride[k] < L)) return SS2D_EINVAL_STRIDE;
+        if ((p->delta_channel_stride[k] && p->delta_channel_stride[k] < L) || (p->bc_row_stride[k] && p->bc_row_stride[k] < L)) return SS2D_EINVAL_STRIDE;
     }
+    // images adjacent in every tensor (channel-major maps): one run of B*L pixels per row, so that the
+    // vector width does not depend on the size of a single map
+    bool flat = p->B > 1 && p->x_dbl_batch_stride == L;
+    for (int k = 0; k < 4; ++k) flat = flat && p->delta_batch_stride[k] == L && p->bc_batch_stride[k] == L;
+    const long long run = flat ? p->B * L : L;
     // widest pixel vector that keeps every row start aligned in every tensor
     int vec = 8;
     auto fit = [&](long long x) { if (x < 0) x = -x; while (vec > 1 && (x % vec) != 0) vec >>= 1; };
-    fit(L); fit(p->x_dbl_batch_stride); fit(p->x_dbl_route_stride); fit(xd_rs);
+    fit(run); fit(p->x_dbl_route_stride); fit(xd_rs);
+    if (!flat) fit(p->x_dbl_batch_stride);
     fit((long long)(reinterpret_cast<uintptr_t>(p->x_dbl) / s));
     for (int k = 0; k < 4; ++k) {
-        fit(p->delta_batch_stride[k]); fit(p->bc_batch_stride[k]);
+        if (!flat) { fit(p->delta_batch_stride[k]); fit(p->bc_batch_stride[k]); }
+        fit(p->delta_channel_stride[k] ? p->delta_channel_stride[k] : L); fit(p->bc_row_stride[k] ? p->bc_row_stride[k] : L);
         fit((long long)(reinterpret_cast<uintptr_t>(p->delta[k]) / s));
         fit((long long)(reinterpret_cast<uintptr_t>(p->bc[k]) / 4));
     }
+    // the staged rows (C rows x 64 items x vec floats) should stay near 28 KB so that several CTAs share an SM
+    while (vec > 1 && C * 64 * vec * 4 > 28 * 1024) vec >>= 1;
     ExpandArgs a;
     a.xd = p->x_dbl; a.wdt = p->dt_weight;
     for (int k = 0; k < 4; ++k) {
         a.delta[k] = p->delta[k]; a.bc[k] = (float*)p->bc[k];
         a.d_bs[k] = p->delta_batch_stride[k]; a.bc_bs[k] = p->bc_batch_stride[k];
+        a.d_cs[k] = p->delta_channel_stride[k] ? p->delta_channel_stride[k] : L;
+        a.bc_rs[k] = p->bc_row_stride[k] ? p->bc_row_stride[k] : L;
     }
     a.xd_bs = p->x_dbl_batch_stride; a.xd_ks = p->x_dbl_route_stride; a.xd_rs = xd_rs;
     a.B = (int)p->B; a.D = (int)p->D; a.R = (int)p->R; a.N2 = (int)(2 * p->N); a.C = (int)C;
-    a.H = (int)p->H; a.W = (int)p->W; a.L = (int)L;
-    a.items_per_plane = (int)(L / vec);
-    a.items_total = (int)(p->B * (L / vec));
+    a.H = (int)p->H; a.W = (int)p->W; a.L = (int)run; a.Limg = (int)L;
+    if (flat) a.B = 1;
+    a.items_per_plane = (int)(run / vec);
+    a.items_total = (int)((flat ? 1 : p->B) * (run / vec));
     if (p->act_dtype == SS2D_F32) return launch_expand_v<float>(a, vec, st);
     if (p->act_dtype == SS2D_BF16) return launch_expand_v<__nv_bfloat16>(a, vec, st);
     return launch_expand_v<__half>(a, vec, st);

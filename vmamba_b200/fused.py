@@ -73,28 +73,44 @@ def project(x: torch.Tensor, w: CoreWeights, channel_major: bool = False):
         B, D, H, W = x.shape
     L, R, N = H * W, w.dt_rank, w.d_state
     C = R + 2 * N
-    delta = torch.empty((2, B, 2, D, L), device=x.device, dtype=x.dtype)   # [orientation][b][pair index]
-    bc = torch.empty((2, B, 2, 2 * N, L), device=x.device, dtype=torch.float32)
     p = _lib.ExpandParams()
-    if channel_major:      # one GEMM over the whole batch: (4C x D) . (D x B*L) -> rows (route, c), columns (b, l)
+    if channel_major:
+        # one GEMM over the whole batch: (4C x D) . (D x B*L) -> rows (route, c), columns (b, l); the route
+        # streams keep that shape: delta (orientation, pair, D, B, L), B/C rows (orientation, pair, 2N, B, L)
         xd = torch.matmul(w.wx, x.reshape(D, B * L))
         p.x_dbl_batch_stride, p.x_dbl_route_stride, p.x_dbl_row_stride = L, C * B * L, B * L
+        delta = torch.empty((2, 2, D, B, L), device=x.device, dtype=x.dtype)
+        bc = torch.empty((2, 2, 2 * N, B, L), device=x.device, dtype=torch.float32)
+        for k in range(K):
+            j, i = k % 2, k // 2
+            p.delta[k], p.delta_batch_stride[k], p.delta_channel_stride[k] = delta[j, i].data_ptr(), L, B * L
+            p.bc[k], p.bc_batch_stride[k], p.bc_row_stride[k] = bc[j, i].data_ptr(), L, B * L
     else:
         xd = torch.matmul(w.wx, x.reshape(B, D, L))                   # (B, 4*C, L), route-major rows
         p.x_dbl_batch_stride, p.x_dbl_route_stride, p.x_dbl_row_stride = xd.stride(0), C * L, L
+        delta = torch.empty((2, B, 2, D, L), device=x.device, dtype=x.dtype)   # [orientation][b][pair index]
+        bc = torch.empty((2, B, 2, 2 * N, L), device=x.device, dtype=torch.float32)
+        for k in range(K):
+            j, i = k % 2, k // 2
+            p.delta[k], p.delta_batch_stride[k] = delta[j, :, i].data_ptr(), delta.stride(1)
+            p.bc[k], p.bc_batch_stride[k] = bc[j, :, i].data_ptr(), bc.stride(1)
     p.x_dbl, p.dt_weight = xd.data_ptr(), w.wdt.data_ptr()
-    esz = x.element_size()
-    for k in range(K):
-        j, i = k % 2, k // 2
-        p.delta[k] = delta[j, :, i].data_ptr()
-        p.delta_batch_stride[k] = delta.stride(1)
-        p.bc[k] = bc[j, :, i].data_ptr()
-        p.bc_batch_stride[k] = bc.stride(1)
     p.B, p.D, p.R, p.N, p.H, p.W = B, D, R, N, H, W
     p.act_dtype = ops.dtype_code(x)
     with torch.cuda.device(x.device):
         check(lib().ss2d_route_expand(p, torch.cuda.current_stream(x.device).cuda_stream), "ss2d_route_expand")
-    return bc[0], bc[1], delta[0], delta[1]
+    if channel_major:       # (pair, rows, B, L) per orientation
+        return RouteStreams(bc[0], bc[1], delta[0], delta[1], True)
+    return RouteStreams(bc[0], bc[1], delta[0], delta[1], False)
+
+
+class RouteStreams(tuple):
+    """(bc_even, bc_odd, delta_even, delta_odd) plus the layout flag of the four tensors:
+    batch-major (B, pair, rows, L) or channel-major (pair, rows, B, L)."""
+    def __new__(cls, bc_even, bc_odd, delta_even, delta_odd, channel_major=False):
+        self = super().__new__(cls, (bc_even, bc_odd, delta_even, delta_odd))
+        self.channel_major = channel_major
+        return self
 
 
 def project_library(x: torch.Tensor, w: CoreWeights):
@@ -108,7 +124,7 @@ def project_library(x: torch.Tensor, w: CoreWeights):
     xd_odd = xd[:, :, 1].transpose(-1, -2).reshape(B, 2, C, L)
     delta_even = torch.matmul(w.wdt[0::2], xd_even[:, :, :R])
     delta_odd = torch.matmul(w.wdt[1::2], xd_odd[:, :, :R])
-    return xd_even[:, :, R:].float(), xd_odd[:, :, R:].float(), delta_even, delta_odd
+    return RouteStreams(xd_even[:, :, R:].float(), xd_odd[:, :, R:].float(), delta_even, delta_odd, False)
 
 
 def scan_merge_norm(x: torch.Tensor, proj, w: CoreWeights, *, with_norm: bool = True, out_dtype=None,
@@ -130,15 +146,23 @@ def scan_merge_norm(x: torch.Tensor, proj, w: CoreWeights, *, with_norm: bool = 
     srcs = (bc_even, bc_odd)
     deltas = (delta_even, delta_odd)
     esz = x.element_size()
+    streams_cm = getattr(proj, "channel_major", False)
     for k in range(K):
         j, i = k % 2, k // 2          # j: orientation (0 row, 1 column); i: index inside the pair
         bc, dl = srcs[j], deltas[j]
-        p.delta[k] = dl.data_ptr() + i * dl.stride(1) * esz
-        p.delta_batch_stride[k] = dl.stride(0)
-        base = bc.data_ptr() + i * bc.stride(1) * 4
-        p.Bm[k] = base
-        p.Cm[k] = base + N * bc.stride(2) * 4
-        p.bc_batch_stride[k] = bc.stride(0)
+        if streams_cm:                # delta (pair, D, B, L), B/C rows (pair, 2N, B, L)
+            p.delta[k] = dl[i].data_ptr()
+            p.delta_batch_stride[k], p.delta_channel_stride[k] = dl.stride(2), dl.stride(1)
+            p.Bm[k] = bc[i].data_ptr()
+            p.Cm[k] = bc[i, N].data_ptr()
+            p.bc_batch_stride[k] = bc.stride(2)
+        else:                         # delta (B, pair, D, L), B/C rows (B, pair, 2N, L)
+            p.delta[k] = dl.data_ptr() + i * dl.stride(1) * esz
+            p.delta_batch_stride[k], p.delta_channel_stride[k] = dl.stride(0), dl.stride(2)
+            base = bc.data_ptr() + i * bc.stride(1) * 4
+            p.Bm[k] = base
+            p.Cm[k] = base + N * bc.stride(2) * 4
+            p.bc_batch_stride[k] = bc.stride(0)
     p.A, p.Dskip, p.delta_bias = w.A.data_ptr(), w.Ds.data_ptr(), w.dt_bias.data_ptr()
     p.ln_weight = None if w.ln_weight is None else w.ln_weight.data_ptr()
     p.ln_bias = None if w.ln_bias is None else w.ln_bias.data_ptr()

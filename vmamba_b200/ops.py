@@ -254,9 +254,15 @@ def layer_norm_cf(y: torch.Tensor, weight=None, bias=None, eps: float = 1e-5, ou
     p.in_, p.add, p.add_bias = y.data_ptr(), _ptr(add), _ptr(ab)
     p.sum_out = y.data_ptr() if update else None
     p.weight, p.bias, p.out = _ptr(w), _ptr(b), out.data_ptr()
-    p.B, p.D, p.L = B, D, L
-    p.batch_stride, p.channel_stride = (L, B * L) if channel_major else (D * L, L)
-    p.out_batch_stride, p.out_channel_stride = (L, B * L) if out_channel_major else (D * L, L)
+    if channel_major and out_channel_major:
+        # images of a channel are adjacent in both maps: one run of B*L pixels per channel
+        p.B, p.D, p.L = 1, D, B * L
+        p.batch_stride, p.channel_stride = D * B * L, B * L
+        p.out_batch_stride, p.out_channel_stride = D * B * L, B * L
+    else:
+        p.B, p.D, p.L = B, D, L
+        p.batch_stride, p.channel_stride = (L, B * L) if channel_major else (D * L, L)
+        p.out_batch_stride, p.out_channel_stride = (L, B * L) if out_channel_major else (D * L, L)
     p.io_dtype, p.eps = dtype_code(out), eps
     with torch.cuda.device(y.device):
         check(lib().ss2d_layer_norm_cf(p, _stream(y)), "ss2d_layer_norm_cf")
@@ -283,6 +289,8 @@ def bias_act_(x: torch.Tensor, bias=None, act="gelu", channel_major: bool = Fals
     b = None if bias is None else bias.contiguous().float()
     if b is not None and b.numel() != D:
         raise RuntimeError("bias must have one value per channel")
+    if channel_major:      # all images of a channel are one contiguous run: vector width independent of the map size
+        B, H, W = 1, 1, B * H * W
     p = PointwiseParams(x.data_ptr(), None, _ptr(b), x.data_ptr(), B, D, H, W, dtype_code(x), _ACTS[act], int(channel_major), 0)
     with torch.cuda.device(x.device):
         check(lib().ss2d_bias_act(p, _stream(x)), "ss2d_bias_act")
