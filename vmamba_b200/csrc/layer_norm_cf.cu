@@ -78,16 +78,50 @@ __global__ void __launch_bounds__(32 * NTY) layer_norm_cf_kernel(const NormArgs 
 #pragma unroll
     for (int i = 0; i < PV; ++i) s[i] = 0.f;
     if constexpr (CACHE > 0) {
+        // All loads are issued before anything is stored: `sum_out` may be the buffer `in`, so a store
+        // in between would order every later load behind it and leave one load in flight per warp.
+        typename Vec<Tio, PV>::Raw addraw[CACHE];
 #pragma unroll
         for (int c = 0; c < CACHE; ++c) {
             const int d = ty + c * NTY;
-            if (d < D) fetch(d, cache[c]);
+            if (live && d < D) Vec<float, PV>::load_plain(src + (long long)d * a.cs, cache[c]);
             else {
 #pragma unroll
                 for (int i = 0; i < PV; ++i) cache[c][i] = 0.f;
             }
+        }
+        if (addp) {
+#pragma unroll
+            for (int c = 0; c < CACHE; ++c) {
+                const int d = ty + c * NTY;
+                if (live && d < D) addraw[c] = Vec<Tio, PV>::load_raw(addp + (long long)d * a.cs);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < CACHE; ++c) {
+            const int d = ty + c * NTY;
+            if (live && d < D) {
+                if (addp) {
+                    float tv[PV];
+                    Vec<Tio, PV>::unpack(addraw[c], tv);
+#pragma unroll
+                    for (int i = 0; i < PV; ++i) cache[c][i] += tv[i];
+                }
+                if (a.add_bias) {
+                    const float bb = __ldg(a.add_bias + d);
+#pragma unroll
+                    for (int i = 0; i < PV; ++i) cache[c][i] += bb;
+                }
+            }
 #pragma unroll
             for (int i = 0; i < PV; ++i) s[i] += cache[c][i];
+        }
+        if (a.sum_out && live) {
+#pragma unroll
+            for (int c = 0; c < CACHE; ++c) {
+                const int d = ty + c * NTY;
+                if (d < D) Vec<float, PV>::store(a.sum_out + base + (long long)d * a.cs, cache[c]);
+            }
         }
     } else {
         for (int d = ty; d < D; d += NTY) {
@@ -190,9 +224,7 @@ static void launch_norm(NormArgs a, int pv, long long B, cudaStream_t st) {
         if (pv == 2) launch_one<Tio, 32, 12, 2>(a, st); else launch_one<Tio, 32, 12, 1>(a, st);
     } else if (D <= 32 * 24) {
         launch_one<Tio, 32, 24, 1>(a, st);
-    } else if (D <= 32 * 48) {
-        launch_one<Tio, 32, 48, 1>(a, st);
-    } else {
+    } else {      // more channels than 1024 threads can keep in registers: statistics pass, then re-read (from L2)
         launch_one<Tio, 32, 0, 1>(a, st);
     }
 }

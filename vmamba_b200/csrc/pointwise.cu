@@ -18,6 +18,30 @@ template <int ACT> __device__ __forceinline__ float act_f(float v) {
     else return v;
 }
 
+// GELU (erf form) on a pair of values for 16-bit storage types.  erfc(z) = poly(t) * exp(-z^2),
+// t = 1 / (1 + p z)  (Abramowitz-Stegun 7.1.26, absolute error 1.5e-7): for v < 0 the factor
+// 1 + erf(v / sqrt 2) IS erfc(|v| / sqrt 2), so there is no cancellation and the relative error stays
+// below 4e-4 down to v = -3.5, a fifth of a bf16 rounding step; beyond that erff is used (rare).
+__device__ __forceinline__ float2 gelu_pair_fast(float2 v) {
+    const float2 z = __fmul2_rn(make_float2(fabsf(v.x), fabsf(v.y)), make_float2(0.70710678118654752f, 0.70710678118654752f));
+    const float2 den = __ffma2_rn(make_float2(0.3275911f, 0.3275911f), z, make_float2(1.f, 1.f));
+    float2 t;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.x) : "f"(den.x));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.y) : "f"(den.y));
+    float2 pl = __ffma2_rn(make_float2(1.061405429f, 1.061405429f), t, make_float2(-1.453152027f, -1.453152027f));
+    pl = __ffma2_rn(pl, t, make_float2(1.421413741f, 1.421413741f));
+    pl = __ffma2_rn(pl, t, make_float2(-0.284496736f, -0.284496736f));
+    pl = __ffma2_rn(pl, t, make_float2(0.254829592f, 0.254829592f));
+    pl = __fmul2_rn(pl, t);
+    const float2 arg = __fmul2_rn(__fmul2_rn(z, z), make_float2(-kLog2e, -kLog2e));
+    const float2 q = __fmul2_rn(pl, make_float2(ex2_approx(arg.x), ex2_approx(arg.y)));      // erfc(|v| / sqrt 2)
+    const float2 cdf2 = make_float2(v.x < 0.f ? q.x : 2.f - q.x, v.y < 0.f ? q.y : 2.f - q.y);   // 1 + erf(v / sqrt 2)
+    float2 r = __fmul2_rn(__fmul2_rn(v, make_float2(0.5f, 0.5f)), cdf2);
+    if (v.x < -3.5f) r.x = act_f<ACT_GELU>(v.x);
+    if (v.y < -3.5f) r.y = act_f<ACT_GELU>(v.y);
+    return r;
+}
+
 // ------------------------------------------------------------------------------------------------
 struct BiasActArgs {
     const void* x;
@@ -30,16 +54,37 @@ struct BiasActArgs {
 
 template <typename T, int PV, int ACT>
 __global__ void __launch_bounds__(256) bias_act_kernel(const BiasActArgs a) {
+    // x may be y: a store orders every later load behind it, so each pass loads kU vectors first
+    constexpr int kU = 4;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long it = (long long)blockIdx.x * blockDim.x + threadIdx.x; it < a.items; it += stride) {
-        const long long row = it / a.nv;
-        const int d = (int)((row / a.rows_per_channel) % a.D);
-        const float b = a.bias ? __ldg(a.bias + d) : 0.f;
-        float v[PV];
-        Vec<T, PV>::load_plain((const T*)a.x + it * PV, v);      // x may be y: no read-only path
+    for (long long it0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; it0 < a.items; it0 += kU * stride) {
+        typename Vec<T, PV>::Raw raw[kU];
 #pragma unroll
-        for (int i = 0; i < PV; ++i) v[i] = act_f<ACT>(round_to<T>(v[i] + b));
-        Vec<T, PV>::store((T*)a.y + it * PV, v);
+        for (int u = 0; u < kU; ++u) {
+            const long long it = it0 + u * stride;
+            if (it < a.items) raw[u] = Vec<T, PV>::template load_raw<false>((const T*)a.x + it * PV);
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const long long it = it0 + u * stride;
+            if (it >= a.items) break;
+            const long long row = it / a.nv;
+            const int d = (int)((row / a.rows_per_channel) % a.D);
+            const float b = a.bias ? __ldg(a.bias + d) : 0.f;
+            float v[PV];
+            Vec<T, PV>::unpack(raw[u], v);
+            if constexpr (ACT == ACT_GELU && sizeof(T) == 2 && PV >= 2) {
+#pragma unroll
+                for (int i = 0; i < PV; i += 2) {
+                    const float2 r = gelu_pair_fast(make_float2(round_to<T>(v[i] + b), round_to<T>(v[i + 1] + b)));
+                    v[i] = r.x; v[i + 1] = r.y;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < PV; ++i) v[i] = act_f<ACT>(round_to<T>(v[i] + b));
+            }
+            Vec<T, PV>::store((T*)a.y + it * PV, v);
+        }
     }
 }
 
@@ -101,7 +146,11 @@ struct DwArgs {
     void* y;
     int D, H, W, PP, planes, nvw;   // nvw = W / PV runs per row
     int planes_per_channel;         // 1 for (B, D, H, W) maps, B for (D, B, H, W) maps
+    int nrb;                        // row blocks of 8 per plane
+    unsigned magic_border, magic_nvw, magic_H, magic_W, magic_nrb, magic_ppc;   // ceil(2^32 / d) for the index splits
 };
+
+__device__ __forceinline__ int mdiv(int n, unsigned magic) { return magic ? (int)__umulhi((unsigned)n, magic) : n; }   // magic 0: divisor 1
 
 template <typename T, int PV, int ACT>
 __global__ void __launch_bounds__(256) dwconv3x3_act_kernel(const DwArgs a) {
@@ -110,31 +159,38 @@ __global__ void __launch_bounds__(256) dwconv3x3_act_kernel(const DwArgs a) {
     const int plane0 = blockIdx.x * a.PP;
     const int np = min(a.PP, a.planes - plane0);
     const int frame = (H + 2) * Wp;
-    // zero the frames, then drop the planes in
-    for (int i = threadIdx.x; i < np * frame; i += blockDim.x) sm[i] = 0.f;
-    __syncthreads();
+    // zero frame: only the one-pixel border is written here, the interior comes from the planes
+    const int border = 2 * Wp + 2 * H;
+    for (int i = threadIdx.x; i < np * border; i += blockDim.x) {
+        const int pl = mdiv(i, a.magic_border), j = i - pl * border;
+        int cell;
+        if (j < Wp) cell = j;                                  // top row
+        else if (j < 2 * Wp) cell = (H + 1) * Wp + (j - Wp);   // bottom row
+        else if (j < 2 * Wp + H) cell = (j - 2 * Wp + 1) * Wp; // left column
+        else cell = (j - 2 * Wp - H + 1) * Wp + W + 1;         // right column
+        sm[pl * frame + cell] = 0.f;
+    }
     const T* __restrict__ x = (const T*)a.x + (long long)plane0 * L;
-    const int nvec = L / PV;
-    for (int i = threadIdx.x; i < np * nvec; i += blockDim.x) {
-        const int pl = i / nvec, e = (i - pl * nvec) * PV;
-        float v[PV];
-        Vec<T, PV>::load(x + (long long)pl * L + e, v);
-        const int h = e / W, w0 = e - h * W;        // PV divides W: a run never leaves its row
-        float* dst = sm + pl * frame + (h + 1) * Wp + w0 + 1;
+    for (int i = threadIdx.x; i < np * H * a.nvw; i += blockDim.x) {
+        const int row = mdiv(i, a.magic_nvw), v = i - row * a.nvw;      // row = pl * H + h; PV divides W: a run never leaves its row
+        const int pl = mdiv(row, a.magic_H), h = row - pl * H;
+        float val[PV];
+        Vec<T, PV>::load(x + (long long)row * W + v * PV, val);
+        float* dst = sm + pl * frame + (h + 1) * Wp + v * PV + 1;
 #pragma unroll
-        for (int j = 0; j < PV; ++j) dst[j] = v[j];
+        for (int j = 0; j < PV; ++j) dst[j] = val[j];
     }
     __syncthreads();
     // compute: consecutive threads take consecutive columns w (conflict-free shared reads, 64-byte
     // store runs per warp) and walk kRows rows with the 3x3 window sliding in registers
     constexpr int kRows = 8;
-    const int nrb = (H + kRows - 1) / kRows;
+    const int nrb = a.nrb;
     T* __restrict__ y = (T*)a.y + (long long)plane0 * L;
     for (int i = threadIdx.x; i < np * nrb * W; i += blockDim.x) {
-        const int w = i % W, t = i / W;
-        const int rb = t % nrb, pl = t / nrb;
+        const int t = mdiv(i, a.magic_W), w = i - t * W;
+        const int pl = mdiv(t, a.magic_nrb), rb = t - pl * nrb;
         const int h0 = rb * kRows, h1 = min(h0 + kRows, H);
-        const int d = ((plane0 + pl) / a.planes_per_channel) % a.D;
+        const int d = mdiv(plane0 + pl, a.magic_ppc) % a.D;
         const T* __restrict__ wk = (const T*)a.w + d * 9;
         float k[9];
 #pragma unroll
@@ -179,6 +235,10 @@ static int launch_dw(const DwArgs& a, int act, size_t smem, unsigned grid, cudaS
 template <typename T>
 static int launch_dw_v(DwArgs a, int pv, int act, size_t smem, unsigned grid, cudaStream_t st) {
     a.nvw = a.W / pv;
+    a.nrb = (a.H + 7) / 8;
+    auto magic = [](long long d) { return d > 1 ? (unsigned)(((1ULL << 32) + (unsigned long long)d - 1) / (unsigned long long)d) : 0u; };
+    a.magic_border = magic(2 * (a.W + 2) + 2 * a.H); a.magic_nvw = magic(a.nvw); a.magic_H = magic(a.H);
+    a.magic_W = magic(a.W); a.magic_nrb = magic(a.nrb); a.magic_ppc = magic(a.planes_per_channel);
     if (pv == 8) return launch_dw<T, 8>(a, act, smem, grid, st);
     if (pv == 4) return launch_dw<T, 4>(a, act, smem, grid, st);
     if (pv == 2) return launch_dw<T, 2>(a, act, smem, grid, st);
@@ -192,7 +252,7 @@ int dwconv3x3_act(const ss2d_pointwise_params* p, cudaStream_t st) {
     if (!dtype_ok(p->dtype)) return SS2D_EINVAL_DTYPE;
     if (p->act < 0 || p->act > 2) return SS2D_ENOTSUP;
     if (p->B <= 0 || p->D <= 0 || p->H <= 0 || p->W <= 0) return SS2D_EINVAL_SHAPE;
-    if (p->B * p->D > 0x7fffffffLL || p->H * p->W > 0x3fffffffLL) return SS2D_EINVAL_SHAPE;
+    if (p->B * p->D > 0x7fffffffLL || p->H * p->W > 0x3fffffffLL || p->B * p->D * p->B >= (1LL << 32)) return SS2D_EINVAL_SHAPE;
     const size_t s = dtype_size(p->dtype);
     if (!aligned_to(p->x, s) || !aligned_to(p->y, s) || !aligned_to(p->weight, s) || !aligned_to(p->bias, 4)) return SS2D_EINVAL_ALIGN;
     const long long L = p->H * p->W;
