@@ -192,6 +192,51 @@ def roofline_of_core(model, peak_gbs, peak_kind, batch=None, iters=20):
     }
 
 
+def op_sweep(args):
+    """Operator-surface sweep (the selective-scan op alone, bf16 u/delta/B/C, fp32 state and output) over
+    d_state x channels x length, plus CrossScan / CrossMerge; one JSON line per cell with the achieved
+    HBM bandwidth on the op's algorithmic bytes.  Inputs are sized to `--sweep-gb` GB per cell (the
+    full-size sweep uses 40 GB; the value distributions and shapes are the same)."""
+    import torch
+    import vmamba_b200 as vb
+    peak, kind = peaks()
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    K = 4
+    for N in (1, 16):
+        for D in (96, 384, 768):
+            for L in (196, 3136, 16384, 65536):
+                Bt = max(1, int(args.sweep_gb * 1e9 / (16 * L * (D + N))))
+                u = torch.randn((Bt, K * D, L), device="cuda", generator=g).to(torch.bfloat16)
+                delta = torch.randn((Bt, K * D, L), device="cuda", generator=g).to(torch.bfloat16)
+                Bm = torch.randn((Bt, K, N, L), device="cuda", generator=g).to(torch.bfloat16)
+                Cm = torch.randn((Bt, K, N, L), device="cuda", generator=g).to(torch.bfloat16)
+                A = -torch.arange(1, N + 1, device="cuda", dtype=torch.float32).repeat(K * D, 1)
+                Dp = torch.ones(K * D, device="cuda")
+                dt = torch.exp(torch.rand(K * D, device="cuda", generator=g) * (math.log(0.1) - math.log(1e-3)) + math.log(1e-3))
+                bias = dt + torch.log(-torch.expm1(-dt))
+                ms = time_events(lambda: vb.selective_scan_fwd(u, delta, A, Bm, Cm, Dp, bias, True, True), args.steps)
+                nbytes = Bt * L * (K * D * (2 * 2 + 4) + 2 * K * N * 2) + 4 * (K * D * N + 2 * K * D)
+                gbs = nbytes / (ms * 1e-3) / 1e9
+                print(json.dumps({"op": "selective_scan_fwd", "dtype": "bf16->f32", "d_state": N, "D": D, "L": L, "batch": Bt,
+                                  "ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": gbs, "frac": gbs / peak,
+                                  "peak_gbs": peak, "peak_kind": f"of {kind}"}), flush=True)
+                del u, delta, Bm, Cm
+    for (D, H) in ((96, 56), (384, 14), (96, 256)):
+        Bt = max(1, int(args.sweep_gb * 1e9 / (10 * D * H * H)))
+        x = torch.randn((Bt, D, H, H), device="cuda", generator=g).to(torch.bfloat16)
+        ms = time_events(lambda: vb.cross_scan_fwd(x, 0), args.steps)
+        nb = x.numel() * 2 * 5
+        print(json.dumps({"op": "cross_scan", "dtype": "bf16", "D": D, "H": H, "batch": Bt, "ms": ms, "algorithmic_bytes": nb,
+                          "achieved_gbs": nb / (ms * 1e-3) / 1e9, "frac": nb / (ms * 1e-3) / 1e9 / peak}), flush=True)
+        ys = torch.randn((Bt, 4, D, H, H), device="cuda", generator=g)
+        ms = time_events(lambda: vb.cross_merge_fwd(ys, 0), args.steps)
+        nb = ys.numel() * 4 * 5 // 4
+        print(json.dumps({"op": "cross_merge", "dtype": "f32", "D": D, "H": H, "batch": Bt, "ms": ms, "algorithmic_bytes": nb,
+                          "achieved_gbs": nb / (ms * 1e-3) / 1e9, "frac": nb / (ms * 1e-3) / 1e9 / peak}), flush=True)
+        del x, ys
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -324,10 +369,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--op-sweep", action="store_true", help="selective-scan / CrossScan / CrossMerge operator sweep (1 GPU)")
+    ap.add_argument("--sweep-gb", type=float, default=2.0, help="input gigabytes per sweep cell")
     ap.add_argument("--roofline-only", action="store_true", help="time only the fused SS2D core chain of stage 0")
     ap.add_argument("--roofline-batch", type=int, default=None, help="batch for --roofline-only (default 128)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.op_sweep:
+        op_sweep(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
