@@ -76,6 +76,19 @@ template <typename T, int VEC> struct Vec {
         }
         return r;
     }
+    static __device__ __forceinline__ void store_raw(T* p, const Raw& r) {
+        if constexpr (kBytes % 16 == 0) {
+#pragma unroll
+            for (int i = 0; i < kBytes / 16; ++i)
+                reinterpret_cast<uint4*>(p)[i] = make_uint4(r.w[4 * i], r.w[4 * i + 1], r.w[4 * i + 2], r.w[4 * i + 3]);
+        } else if constexpr (kBytes == 8) {
+            *reinterpret_cast<uint2*>(p) = make_uint2(r.w[0], r.w[1]);
+        } else if constexpr (kBytes == 4) {
+            *reinterpret_cast<uint32_t*>(p) = r.w[0];
+        } else {
+            *reinterpret_cast<uint16_t*>(p) = (uint16_t)r.w[0];
+        }
+    }
     static __device__ __forceinline__ void unpack(const Raw& r, float (&v)[VEC]) {
         if constexpr (sizeof(T) == 4) {
 #pragma unroll

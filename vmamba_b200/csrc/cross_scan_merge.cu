@@ -112,6 +112,155 @@ __global__ void __launch_bounds__(kTile * kRowsPerPass) cross_merge_kernel(const
     }
 }
 
+// ---- whole-plane variants for maps that fit in shared memory ------------------------------------------
+// The tile kernels above leave most of a 32x32 tile idle on small maps (14x14, 7x7) and move one
+// element per lane.  Here a CTA owns PP whole planes: they are copied into shared memory with
+// flat vector loads, and every route is then produced (scan) or consumed (merge) as a flat run of
+// vectors in ITS OWN index order, so all global traffic is contiguous 16-byte vectors; the
+// permutation happens on the shared-memory side.
+struct PlaneArgs {
+    const void* in;
+    void* out;
+    long long planes;          // B * C
+    int C, H, W, L, PP, nvec;  // nvec = L / PV
+    RouteMap route[4];
+    unsigned magic_H, magic_W, magic_nvec;
+};
+
+__device__ __forceinline__ int mdiv_u(int n, unsigned magic) { return magic ? (int)__umulhi((unsigned)n, magic) : n; }
+
+// source position (flat h*W + w) read by step l of a route
+__device__ __forceinline__ int route_src(const RouteMap& m, int l, int H, int W, unsigned magic_H) {
+    if (!m.col_like) return m.sw > 0 ? l : (int)m.base - l;            // row-major, forward or reversed
+    // l = base + sh*h + sw*w with |sh| = 1, |sw| = H: recover (h, w)
+    const int t = (int)(m.sw > 0 ? 0 : -m.sw * (W - 1));                // offset so that the w term is non-negative
+    int r = l - (int)m.base + t + (m.sh < 0 ? (H - 1) : 0);            // = hh + H * ww with hh, ww in range
+    const int ww = mdiv_u(r, magic_H), hh = r - ww * H;
+    const int h = m.sh > 0 ? hh : H - 1 - hh;
+    const int w = m.sw > 0 ? ww : W - 1 - ww;
+    return h * W + w;
+}
+
+template <typename T, int PV>
+__global__ void __launch_bounds__(256) cross_scan_plane_kernel(const PlaneArgs a) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    T* sm = reinterpret_cast<T*>(smraw);
+    const long long plane0 = (long long)blockIdx.x * a.PP;
+    const int np = (int)min((long long)a.PP, a.planes - plane0);
+    const int L = a.L, n = np * a.nvec;
+    const T* __restrict__ x = (const T*)a.in + plane0 * L;
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        Vec<T, PV>::store_raw(sm + i * PV, Vec<T, PV>::load_raw(x + (long long)i * PV));
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const RouteMap m = a.route[k];
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const int pl = mdiv_u(i, a.magic_nvec), l0 = (i - pl * a.nvec) * PV;
+            const long long plane = plane0 + pl;
+            const long long b = plane / a.C, c = plane - b * a.C;
+            typename Vec<T, PV>::Raw r;
+            T* e = reinterpret_cast<T*>(&r);
+#pragma unroll
+            for (int j = 0; j < PV; ++j) e[j] = sm[pl * L + route_src(m, l0 + j, a.H, a.W, a.magic_H)];
+            Vec<T, PV>::store_raw((T*)a.out + ((b * 4 + k) * a.C + c) * L + l0, r);
+        }
+    }
+}
+
+template <typename T, int PV>
+__global__ void __launch_bounds__(256) cross_merge_plane_kernel(const PlaneArgs a, const int scans) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    T* sm = reinterpret_cast<T*>(smraw);                   // [4][PP][L]: every route's plane, in its own order
+    const long long plane0 = (long long)blockIdx.x * a.PP;
+    const int np = (int)min((long long)a.PP, a.planes - plane0);
+    const int L = a.L, n = np * a.nvec;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const int pl = mdiv_u(i, a.magic_nvec), l0 = (i - pl * a.nvec) * PV;
+            const long long plane = plane0 + pl;
+            const long long b = plane / a.C, c = plane - b * a.C;
+            Vec<T, PV>::store_raw(sm + ((size_t)k * a.PP + pl) * L + l0,
+                                  Vec<T, PV>::load_raw((const T*)a.in + ((b * 4 + k) * a.C + c) * L + l0));
+        }
+    }
+    __syncthreads();
+    T* __restrict__ y = (T*)a.out + plane0 * L;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int pl = mdiv_u(i, a.magic_nvec), p0 = (i - pl * a.nvec) * PV;
+        typename Vec<T, PV>::Raw r;
+        T* e = reinterpret_cast<T*>(&r);
+#pragma unroll
+        for (int j = 0; j < PV; ++j) {
+            const int p = p0 + j;
+            const int h = mdiv_u(p, a.magic_W), w = p - h * a.W;
+            T v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const RouteMap& m = a.route[k];
+                v[k] = sm[((size_t)k * a.PP + pl) * L + (int)(m.base + m.sh * h + m.sw * w)];
+            }
+            if (scans == 0 || scans == 2) e[j] = add_t(add_t(v[0], v[2]), add_t(v[1], v[3]));
+            else if (scans == 3) e[j] = add_t(add_t(add_t(v[0], v[1]), v[2]), v[3]);
+            else e[j] = from_f<T>(((to_f<T>(v[0]) + to_f<T>(v[1])) + to_f<T>(v[2])) + to_f<T>(v[3]));
+        }
+        Vec<T, PV>::store_raw(y + (long long)i * PV, r);
+    }
+}
+
+// returns false when the map is too large for the whole-plane kernels
+template <typename T>
+static bool plan_plane(const ss2d_cross_params* p, int copies, PlaneArgs& a, int& pv, size_t& smem) {
+    const long long L = p->H * p->W;
+    if (L * (long long)sizeof(T) * copies > 64 * 1024) return false;
+    pv = 16 / (int)sizeof(T);
+    auto fit = [&](long long x) { while (pv > 1 && (x % pv) != 0) pv >>= 1; };
+    fit(L);
+    fit((long long)(reinterpret_cast<uintptr_t>(p->in) / sizeof(T)));
+    fit((long long)(reinterpret_cast<uintptr_t>(p->out) / sizeof(T)));
+    long long PP = (4096 + L - 1) / L;        // about 4096 elements per CTA
+    while (PP > 1 && PP * L * (long long)sizeof(T) * copies > 64 * 1024) --PP;
+    a.in = p->in; a.out = p->out; a.planes = p->B * p->C; a.C = (int)p->C; a.H = (int)p->H; a.W = (int)p->W;
+    a.L = (int)L; a.PP = (int)PP; a.nvec = (int)(L / pv);
+    for (int k = 0; k < 4; ++k) a.route[k] = route_map(p->scans, k, p->H, p->W);
+    auto magic = [](long long d) { return d > 1 ? (unsigned)(((1ULL << 32) + (unsigned long long)d - 1) / (unsigned long long)d) : 0u; };
+    a.magic_H = magic(p->H); a.magic_W = magic(p->W); a.magic_nvec = magic(a.nvec);
+    smem = (size_t)PP * L * sizeof(T) * copies;
+    return (a.planes + PP - 1) / PP <= 0x7fffffffLL;
+}
+
+template <typename T, int PV>
+static int launch_scan_plane(const PlaneArgs& a, size_t smem, cudaStream_t st) {
+    auto k = cross_scan_plane_kernel<T, PV>;
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return SS2D_ECUDA;
+    k<<<(unsigned)((a.planes + a.PP - 1) / a.PP), 256, smem, st>>>(a);
+    count_launch();
+    return check_launch();
+}
+template <typename T, int PV>
+static int launch_merge_plane(const PlaneArgs& a, int scans, size_t smem, cudaStream_t st) {
+    auto k = cross_merge_plane_kernel<T, PV>;
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return SS2D_ECUDA;
+    k<<<(unsigned)((a.planes + a.PP - 1) / a.PP), 256, smem, st>>>(a, scans);
+    count_launch();
+    return check_launch();
+}
+template <typename T>
+static int scan_plane_v(const PlaneArgs& a, int pv, size_t smem, cudaStream_t st) {
+    if constexpr (sizeof(T) == 2) { if (pv == 8) return launch_scan_plane<T, 8>(a, smem, st); }
+    if (pv >= 4) return launch_scan_plane<T, 4>(a, smem, st);
+    if (pv == 2) return launch_scan_plane<T, 2>(a, smem, st);
+    return launch_scan_plane<T, 1>(a, smem, st);
+}
+template <typename T>
+static int merge_plane_v(const PlaneArgs& a, int scans, int pv, size_t smem, cudaStream_t st) {
+    if constexpr (sizeof(T) == 2) { if (pv == 8) return launch_merge_plane<T, 8>(a, scans, smem, st); }
+    if (pv >= 4) return launch_merge_plane<T, 4>(a, scans, smem, st);
+    if (pv == 2) return launch_merge_plane<T, 2>(a, scans, smem, st);
+    return launch_merge_plane<T, 1>(a, scans, smem, st);
+}
+
 static int fill_args(const ss2d_cross_params* p, CrossArgs& a) {
     if (!p) return SS2D_EINVAL_NULL;
     if (!p->in || !p->out) return SS2D_EINVAL_NULL;
@@ -134,6 +283,11 @@ int cross_scan(const ss2d_cross_params* p, cudaStream_t st) {
     CrossArgs a;
     const int rc = fill_args(p, a);
     if (rc != SS2D_OK) return rc;
+    {
+        PlaneArgs pa; int pv; size_t smem;
+        if (p->dtype == SS2D_F32) { if (plan_plane<float>(p, 1, pa, pv, smem)) return scan_plane_v<float>(pa, pv, smem, st); }
+        else if (plan_plane<uint16_t>(p, 1, pa, pv, smem)) return scan_plane_v<uint16_t>(pa, pv, smem, st);
+    }
     const dim3 blk(kTile, kRowsPerPass);
     if (p->dtype == SS2D_F32) cross_scan_kernel<float><<<(unsigned)a.n_tiles, blk, 0, st>>>(a);
     else cross_scan_kernel<uint16_t><<<(unsigned)a.n_tiles, blk, 0, st>>>(a);   // 16-bit types: bits are moved as-is
@@ -145,6 +299,12 @@ int cross_merge(const ss2d_cross_params* p, cudaStream_t st) {
     CrossArgs a;
     const int rc = fill_args(p, a);
     if (rc != SS2D_OK) return rc;
+    {
+        PlaneArgs pa; int pv; size_t smem;
+        if (p->dtype == SS2D_F32) { if (plan_plane<float>(p, 4, pa, pv, smem)) return merge_plane_v<float>(pa, p->scans, pv, smem, st); }
+        else if (p->dtype == SS2D_BF16) { if (plan_plane<__nv_bfloat16>(p, 4, pa, pv, smem)) return merge_plane_v<__nv_bfloat16>(pa, p->scans, pv, smem, st); }
+        else if (plan_plane<__half>(p, 4, pa, pv, smem)) return merge_plane_v<__half>(pa, p->scans, pv, smem, st);
+    }
     const dim3 blk(kTile, kRowsPerPass);
     if (p->dtype == SS2D_F32) cross_merge_kernel<float><<<(unsigned)a.n_tiles, blk, 0, st>>>(a, p->scans);
     else if (p->dtype == SS2D_BF16) cross_merge_kernel<__nv_bfloat16><<<(unsigned)a.n_tiles, blk, 0, st>>>(a, p->scans);
