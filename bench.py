@@ -254,6 +254,13 @@ def run_ours(args):
     from vmamba_b200 import _lib
     from vmamba_b200.backbone import VSSMInfer
 
+    global MODEL, BATCH, IMG
+    if args.model:
+        MODEL = args.model
+    if args.batch:
+        BATCH = args.batch
+    if args.img:
+        IMG = args.img
     sd = synthetic_state_dict(0)
     model = VSSMInfer.from_state_dict(sd, dtype=torch.bfloat16, device=f"cuda:{local}")
     if args.roofline_only:     # the dominant kernel chain alone (small cases for profiler captures)
@@ -329,7 +336,7 @@ def run_ours(args):
     if rank == 0:
         peak, kind = peaks()
         roof = roofline_of_core(model, peak, kind)
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and MODEL == "vmamba_tiny_s1l8" and IMG == 224:
             v, cores, desc = cpu_baseline(sd, 4)
             cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
     if world > 1:
@@ -342,8 +349,8 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
         "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{MODEL} (VMamba-T, dims 96/192/384/768, depths 2/2/8/2, v05_noz, d_state 1) "
-                               f"backbone inference, random init, {BATCH} images of 3x{IMG}x{IMG} per GPU per step",
+        "config": {"workload": f"{MODEL} (" + ("VMamba-T, dims 96/192/384/768, depths 2/2/8/2, " if MODEL == "vmamba_tiny_s1l8" else "") +
+                               f"v05_noz, d_state 1) backbone inference, random init, {BATCH} images of 3x{IMG}x{IMG} per GPU per step",
                    "global_batch": BATCH * world, "parallelism": f"replicas x{world}, batch-sharded, no collective",
                    "l2": f"no flush needed: one stage-0 activation is {act_mb:.0f} MB and a step streams several GB, "
                          "far more than the 126 MB L2",
@@ -369,6 +376,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--model", default=None, help="vmamba_tiny_s1l8 (default) | vmamba_small_s2l15 | vmamba_base_s2l15")
+    ap.add_argument("--batch", type=int, default=None, help="images per GPU per step (default 128)")
+    ap.add_argument("--img", type=int, default=None, help="image side (default 224)")
     ap.add_argument("--op-sweep", action="store_true", help="selective-scan / CrossScan / CrossMerge operator sweep (1 GPU)")
     ap.add_argument("--sweep-gb", type=float, default=2.0, help="input gigabytes per sweep cell")
     ap.add_argument("--roofline-only", action="store_true", help="time only the fused SS2D core chain of stage 0")

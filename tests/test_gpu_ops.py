@@ -410,3 +410,40 @@ def test_backbone_bf16_vs_reference_golden(vb):
     logits = m(dev(g["img"]))
     assert logits.dtype == torch.bfloat16
     assert O.max_rel_err(host(logits), g["logits"]) <= TOL_BF16
+
+
+# ------------------------------------------------------------------------------ other model families / long maps
+def test_core_long_map_takes_surface_kernels(vb):
+    """128x128 maps (L = 16384) exceed one CTA's plane: same mathematics through the operator kernels."""
+    c = _core_case(1, 4, 128, 128, N=1, seed=21, Cmodel=64)
+    ref = O.ss2d_core(c["x"], c["wx"], c["wdt"], c["bias"], c["A_logs"], c["Ds"], c["lw"], c["lb"], d_state=1, dt_rank=c["R"])
+    y = _run_core(vb, c, "f32")
+    assert O.max_rel_err(host(y), ref) <= TOL_F32
+
+
+@pytest.mark.parametrize("ssm_ratio,dims", [(2.0, [16, 32, 64, 128]), (1.0, [24, 48, 96, 192])])
+def test_backbone_random_init_vs_oracle(vb, ssm_ratio, dims):
+    """VMamba-S/B-style blocks (ssm_ratio 2) and a second width, random init, against the CPU oracle."""
+    from oracle import backbone_oracle as BO
+    from vmamba_b200.backbone import VSSMInfer
+    sd = BO.random_state_dict([1, 1, 2, 1], dims, 1, ssm_ratio, 4.0, 10, 3, seed=4, with_outnorm=True)
+    rng = np.random.default_rng(8)
+    for k in sd:                      # make LayerNorm affine terms and biases matter
+        if k.endswith(".bias") or "norm" in k:
+            sd[k] = (sd[k] + 0.1 * rng.standard_normal(sd[k].shape)).astype(np.float32)
+    img = rng.standard_normal((2, 3, 64, 64), dtype=np.float32)
+    ref = BO.vssm_logits(img, sd)
+    feats_ref = BO.backbone_features(img, sd)
+    old = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        m = VSSMInfer.from_state_dict(sd, dtype=torch.float32)
+        logits = m(dev(img))
+        feats = m.features(dev(img))
+    finally:
+        torch.backends.cudnn.allow_tf32 = old
+    assert O.max_rel_err(host(logits), ref) <= TOL_F32
+    for a_, b_ in zip(feats, feats_ref):
+        assert O.max_rel_err(host(a_), b_) <= TOL_F32
+    lb16 = VSSMInfer.from_state_dict(sd, dtype=torch.bfloat16)(dev(img))
+    assert O.max_rel_err(host(lb16), ref) <= TOL_BF16
