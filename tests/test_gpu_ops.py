@@ -174,7 +174,8 @@ def test_layer_norm_cf_fused_residual_update(vb, shape):
 
 
 # ------------------------------------------------------------------------------ elementwise producers
-@pytest.mark.parametrize("shape", [(2, 96, 56, 56), (2, 192, 28, 28), (3, 384, 14, 14), (2, 768, 7, 7), (1, 3, 5, 9), (1, 2, 1, 1)])
+@pytest.mark.parametrize("shape", [(2, 96, 56, 56), (2, 192, 28, 28), (3, 384, 14, 14), (2, 768, 7, 7), (1, 3, 5, 9), (1, 2, 1, 1),
+                                   (1, 3, 256, 256), (1, 2, 130, 72)])
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_dwconv3x3_silu(vb, shape, dtype):
     import torch.nn.functional as F

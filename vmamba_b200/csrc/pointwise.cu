@@ -135,19 +135,22 @@ int bias_act(const ss2d_pointwise_params* p, cudaStream_t st) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// Depthwise 3x3, stride 1, zero padding 1.  A CTA owns PP whole planes: each is staged once in
-// shared memory as fp32 inside a one-pixel zero frame (pitch W + 2), then every thread produces
-// runs of PV consecutive output pixels of one row from three shared rows.  HBM traffic is the
-// minimum: every input element read once, every output written once.
+// Depthwise 3x3, stride 1, zero padding 1.  A work unit is a band of BH rows of one plane (the whole
+// plane when it is small); a CTA owns PP units.  Each band is staged once in shared memory as fp32
+// with its two halo rows inside a one-pixel zero frame (pitch W + 2); consecutive threads then take
+// consecutive columns and walk 8 rows with the 3x3 window sliding in registers.  HBM traffic is the
+// minimum for whole planes (every element read once, written once); banded planes re-read two
+// halo rows per band.
 struct DwArgs {
     const void* x;
     const void* w;       // (D, 3, 3) storage type
     const float* bias;   // (D) or null
     void* y;
-    int D, H, W, PP, planes, nvw;   // nvw = W / PV runs per row
+    int D, H, W, PP, nvw;           // nvw = W / PV runs per row
+    int BH, nb, units;              // rows per band, bands per plane, planes * nb
     int planes_per_channel;         // 1 for (B, D, H, W) maps, B for (D, B, H, W) maps
-    int nrb;                        // row blocks of 8 per plane
-    unsigned magic_border, magic_nvw, magic_H, magic_W, magic_nrb, magic_ppc;   // ceil(2^32 / d) for the index splits
+    int nrb;                        // row blocks of 8 per band
+    unsigned magic_fr, magic_nvw, magic_W, magic_nrb, magic_ppc, magic_nb, magic_frnvw, magic_nrbW;
 };
 
 __device__ __forceinline__ int mdiv(int n, unsigned magic) { return magic ? (int)__umulhi((unsigned)n, magic) : n; }   // magic 0: divisor 1
@@ -155,59 +158,62 @@ __device__ __forceinline__ int mdiv(int n, unsigned magic) { return magic ? (int
 template <typename T, int PV, int ACT>
 __global__ void __launch_bounds__(256) dwconv3x3_act_kernel(const DwArgs a) {
     extern __shared__ __align__(16) float sm[];
-    const int H = a.H, W = a.W, Wp = W + 2, L = H * W;
-    const int plane0 = blockIdx.x * a.PP;
-    const int np = min(a.PP, a.planes - plane0);
-    const int frame = (H + 2) * Wp;
-    // zero frame: only the one-pixel border is written here, the interior comes from the planes
-    const int border = 2 * Wp + 2 * H;
-    for (int i = threadIdx.x; i < np * border; i += blockDim.x) {
-        const int pl = mdiv(i, a.magic_border), j = i - pl * border;
-        int cell;
-        if (j < Wp) cell = j;                                  // top row
-        else if (j < 2 * Wp) cell = (H + 1) * Wp + (j - Wp);   // bottom row
-        else if (j < 2 * Wp + H) cell = (j - 2 * Wp + 1) * Wp; // left column
-        else cell = (j - 2 * Wp - H + 1) * Wp + W + 1;         // right column
-        sm[pl * frame + cell] = 0.f;
+    const int H = a.H, W = a.W, Wp = W + 2, FR = a.BH + 2;      // frame rows
+    const int unit0 = blockIdx.x * a.PP;
+    const int np = min(a.PP, a.units - unit0);
+    const int frame = FR * Wp;
+    // frame cells that no load will write: the left and right columns, and the rows above / below the image
+    for (int i = threadIdx.x; i < np * FR; i += blockDim.x) {
+        const int pl = mdiv(i, a.magic_fr), fr = i - pl * FR;
+        float* row = sm + pl * frame + fr * Wp;
+        row[0] = 0.f; row[W + 1] = 0.f;
     }
-    const T* __restrict__ x = (const T*)a.x + (long long)plane0 * L;
-    for (int i = threadIdx.x; i < np * H * a.nvw; i += blockDim.x) {
-        const int row = mdiv(i, a.magic_nvw), v = i - row * a.nvw;      // row = pl * H + h; PV divides W: a run never leaves its row
-        const int pl = mdiv(row, a.magic_H), h = row - pl * H;
+    const T* __restrict__ x = (const T*)a.x;
+    for (int i = threadIdx.x; i < np * FR * a.nvw; i += blockDim.x) {
+        const int pl = mdiv(i, a.magic_frnvw), rem = i - pl * (FR * a.nvw);
+        const int fr = mdiv(rem, a.magic_nvw), v = rem - fr * a.nvw;
+        const int u = unit0 + pl;
+        const int plane = mdiv(u, a.magic_nb), band = u - plane * a.nb;
+        const int h = band * a.BH - 1 + fr;                       // image row held by this frame row
         float val[PV];
-        Vec<T, PV>::load(x + (long long)row * W + v * PV, val);
-        float* dst = sm + pl * frame + (h + 1) * Wp + v * PV + 1;
+        if (h >= 0 && h < H) Vec<T, PV>::load(x + ((long long)plane * H + h) * W + v * PV, val);   // PV divides W
+        else {
+#pragma unroll
+            for (int j = 0; j < PV; ++j) val[j] = 0.f;
+        }
+        float* dst = sm + pl * frame + fr * Wp + v * PV + 1;
 #pragma unroll
         for (int j = 0; j < PV; ++j) dst[j] = val[j];
     }
     __syncthreads();
-    // compute: consecutive threads take consecutive columns w (conflict-free shared reads, 64-byte
-    // store runs per warp) and walk kRows rows with the 3x3 window sliding in registers
     constexpr int kRows = 8;
     const int nrb = a.nrb;
-    T* __restrict__ y = (T*)a.y + (long long)plane0 * L;
     for (int i = threadIdx.x; i < np * nrb * W; i += blockDim.x) {
-        const int t = mdiv(i, a.magic_W), w = i - t * W;
-        const int pl = mdiv(t, a.magic_nrb), rb = t - pl * nrb;
-        const int h0 = rb * kRows, h1 = min(h0 + kRows, H);
-        const int d = mdiv(plane0 + pl, a.magic_ppc) % a.D;
+        const int pl = mdiv(i, a.magic_nrbW), rem = i - pl * (nrb * W);
+        const int rb = mdiv(rem, a.magic_W), w = rem - rb * W;
+        const int u = unit0 + pl;
+        const int plane = mdiv(u, a.magic_nb), band = u - plane * a.nb;
+        const int r0 = rb * kRows;                                 // first row of this block inside the band
+        const int rows = min(min(r0 + kRows, a.BH), H - band * a.BH) - r0;
+        if (rows <= 0) continue;
+        const int d = mdiv(plane, a.magic_ppc) % a.D;
         const T* __restrict__ wk = (const T*)a.w + d * 9;
         float k[9];
 #pragma unroll
         for (int j = 0; j < 9; ++j) k[j] = to_f<T>(wk[j]);
         const float b = a.bias ? __ldg(a.bias + d) : 0.f;
-        const float* src = sm + pl * frame + h0 * Wp + w;    // frame row h0 is image row h0 - 1
+        const float* src = sm + pl * frame + r0 * Wp + w;        // frame row r0 is the row above output row r0
         float t0 = src[0], t1 = src[1], t2 = src[2];
         float m0 = src[Wp], m1 = src[Wp + 1], m2 = src[Wp + 2];
-        T* __restrict__ out = y + (long long)pl * L + w;
-        for (int h = h0; h < h1; ++h) {
-            const float* bp = src + (h - h0 + 2) * Wp;
+        T* __restrict__ out = (T*)a.y + ((long long)plane * H + band * a.BH + r0) * W + w;
+        for (int r = 0; r < rows; ++r) {
+            const float* bp = src + (r + 2) * Wp;
             const float b0 = bp[0], b1 = bp[1], b2 = bp[2];
             float acc = b;
             acc = fmaf(k[0], t0, acc); acc = fmaf(k[1], t1, acc); acc = fmaf(k[2], t2, acc);
             acc = fmaf(k[3], m0, acc); acc = fmaf(k[4], m1, acc); acc = fmaf(k[5], m2, acc);
             acc = fmaf(k[6], b0, acc); acc = fmaf(k[7], b1, acc); acc = fmaf(k[8], b2, acc);
-            out[h * W] = from_f<T>(act_f<ACT>(round_to<T>(acc)));
+            out[r * W] = from_f<T>(act_f<ACT>(round_to<T>(acc)));
             t0 = m0; t1 = m1; t2 = m2; m0 = b0; m1 = b1; m2 = b2;
         }
     }
@@ -235,10 +241,12 @@ static int launch_dw(const DwArgs& a, int act, size_t smem, unsigned grid, cudaS
 template <typename T>
 static int launch_dw_v(DwArgs a, int pv, int act, size_t smem, unsigned grid, cudaStream_t st) {
     a.nvw = a.W / pv;
-    a.nrb = (a.H + 7) / 8;
+    a.nrb = (a.BH + 7) / 8;
     auto magic = [](long long d) { return d > 1 ? (unsigned)(((1ULL << 32) + (unsigned long long)d - 1) / (unsigned long long)d) : 0u; };
-    a.magic_border = magic(2 * (a.W + 2) + 2 * a.H); a.magic_nvw = magic(a.nvw); a.magic_H = magic(a.H);
-    a.magic_W = magic(a.W); a.magic_nrb = magic(a.nrb); a.magic_ppc = magic(a.planes_per_channel);
+    const int FR = a.BH + 2;
+    a.magic_fr = magic(FR); a.magic_nvw = magic(a.nvw); a.magic_W = magic(a.W); a.magic_nrb = magic(a.nrb);
+    a.magic_ppc = magic(a.planes_per_channel); a.magic_nb = magic(a.nb);
+    a.magic_frnvw = magic((long long)FR * a.nvw); a.magic_nrbW = magic((long long)a.nrb * a.W);
     if (pv == 8) return launch_dw<T, 8>(a, act, smem, grid, st);
     if (pv == 4) return launch_dw<T, 4>(a, act, smem, grid, st);
     if (pv == 2) return launch_dw<T, 2>(a, act, smem, grid, st);
@@ -252,7 +260,7 @@ int dwconv3x3_act(const ss2d_pointwise_params* p, cudaStream_t st) {
     if (!dtype_ok(p->dtype)) return SS2D_EINVAL_DTYPE;
     if (p->act < 0 || p->act > 2) return SS2D_ENOTSUP;
     if (p->B <= 0 || p->D <= 0 || p->H <= 0 || p->W <= 0) return SS2D_EINVAL_SHAPE;
-    if (p->B * p->D > 0x7fffffffLL || p->H * p->W > 0x3fffffffLL || p->B * p->D * p->B >= (1LL << 32)) return SS2D_EINVAL_SHAPE;
+    if (p->H * p->W > 0x3fffffffLL || p->W > 8192) return SS2D_EINVAL_SHAPE;
     const size_t s = dtype_size(p->dtype);
     if (!aligned_to(p->x, s) || !aligned_to(p->y, s) || !aligned_to(p->weight, s) || !aligned_to(p->bias, 4)) return SS2D_EINVAL_ALIGN;
     const long long L = p->H * p->W;
@@ -261,23 +269,32 @@ int dwconv3x3_act(const ss2d_pointwise_params* p, cudaStream_t st) {
     fit(p->W); fit(L);
     fit((long long)(reinterpret_cast<uintptr_t>(p->x) / s));
     fit((long long)(reinterpret_cast<uintptr_t>(p->y) / s));
-    const size_t frame = (size_t)(p->H + 2) * (p->W + 2) * sizeof(float);
-    if (frame > 200 * 1024) return SS2D_ENOTSUP;     // plane too large for one CTA's shared memory
-    // planes per CTA: about 2048 outputs per thread block pass, at most 48 KB of shared memory
-    long long PP = (2048 * 4 + L - 1) / L;
+    // band height: the whole plane if its frame fits in 40 KB, else as many rows as do
+    const long long Wp = p->W + 2;
+    long long BH = p->H;
+    while (BH > 8 && (BH + 2) * Wp * 4 > 40 * 1024) BH = (BH + 1) / 2;
+    BH = (BH + 7) / 8 * 8;                      // whole 8-row blocks
+    if (BH > p->H) BH = p->H;
+    const long long nb = (p->H + BH - 1) / BH;
+    const size_t frame = (size_t)(BH + 2) * Wp * sizeof(float);
+    if (frame > 160 * 1024) return SS2D_ENOTSUP;
+    const long long units = p->B * p->D * nb;
+    long long PP = (2048 * 4 + BH * p->W - 1) / (BH * p->W);      // about 8192 outputs per CTA
     if (PP < 1) PP = 1;
     while (PP > 1 && PP * frame > 48 * 1024) --PP;
-    const long long planes = p->B * p->D;
-    if (PP > planes) PP = planes;
+    if (PP > units) PP = units;
+    const long long grid = (units + PP - 1) / PP;
+    // every index split inside the kernel is a multiply-shift that needs numerator * divisor < 2^32
+    if (units * nb >= (1LL << 32) || p->B * p->D * p->B >= (1LL << 32) || grid > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
     DwArgs a;
     a.x = p->x; a.w = p->weight; a.bias = (const float*)p->bias; a.y = p->y;
-    a.D = (int)p->D; a.H = (int)p->H; a.W = (int)p->W; a.PP = (int)PP; a.planes = (int)planes; a.nvw = 0;
+    a.D = (int)p->D; a.H = (int)p->H; a.W = (int)p->W; a.PP = (int)PP; a.nvw = 0;
+    a.BH = (int)BH; a.nb = (int)nb; a.units = (int)units;
     a.planes_per_channel = p->channel_major ? (int)p->B : 1;
-    const unsigned grid = (unsigned)((planes + PP - 1) / PP);
     const size_t smem = (size_t)PP * frame;
-    if (p->dtype == SS2D_F32) return launch_dw_v<float>(a, pv, p->act, smem, grid, st);
-    if (p->dtype == SS2D_BF16) return launch_dw_v<__nv_bfloat16>(a, pv, p->act, smem, grid, st);
-    return launch_dw_v<__half>(a, pv, p->act, smem, grid, st);
+    if (p->dtype == SS2D_F32) return launch_dw_v<float>(a, pv, p->act, smem, (unsigned)grid, st);
+    if (p->dtype == SS2D_BF16) return launch_dw_v<__nv_bfloat16>(a, pv, p->act, smem, (unsigned)grid, st);
+    return launch_dw_v<__half>(a, pv, p->act, smem, (unsigned)grid, st);
 }
 
 }  // namespace ss2d
