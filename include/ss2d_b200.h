@@ -212,7 +212,7 @@ int64_t ss2d_core_static_capacity(void);
  * Replaces LayerNorm(channel_first=True).forward (vmamba.py:1087-1093) + the trailing cast
  * (vmamba.py:1571) and, with `add`, the residual additions of VSSBlock._forward
  * (vmamba.py:1772, 1777) together with the norm that follows them.
- *   in       (B, D, L) fp32          add      (B, D, L) io_dtype or NULL
+ *   in       (B, D, L) fp32 or NULL  add      (B, D, L) io_dtype or NULL (at least one of the two)
  *   add_bias (D) fp32 or NULL        sum_out  (B, D, L) fp32 or NULL; may be the same buffer as `in`
  *   weight, bias (D) fp32 or NULL    out      (B, D, L) io_dtype
  * Pixels of a plane are contiguous; `channel_stride` and `batch_stride` in elements (0 = dense
@@ -230,6 +230,8 @@ typedef struct ss2d_norm_params {
     int64_t out_batch_stride, out_channel_stride;   /* of out; 0 = same as the inputs */
     int32_t io_dtype;
     float eps;
+    int32_t skip_norm;      /* 1: out = s converted to io_dtype, no normalisation (fused add, cast, layout change) */
+    int32_t reserved0;
 } ss2d_norm_params;
 
 int ss2d_layer_norm_cf(const ss2d_norm_params *p, void *cuda_stream);

@@ -63,7 +63,8 @@ class PointwiseParams(ctypes.Structure):
 class NormParams(ctypes.Structure):
     _fields_ = [("in_", _vp), ("add", _vp), ("add_bias", _vp), ("sum_out", _vp), ("weight", _vp), ("bias", _vp),
                 ("out", _vp), ("B", _i64), ("D", _i64), ("L", _i64), ("batch_stride", _i64), ("channel_stride", _i64),
-                ("out_batch_stride", _i64), ("out_channel_stride", _i64), ("io_dtype", _i32), ("eps", _f32)]
+                ("out_batch_stride", _i64), ("out_channel_stride", _i64), ("io_dtype", _i32), ("eps", _f32),
+                ("skip_norm", _i32), ("reserved0", _i32)]
 
 
 EXPORTS = {

@@ -66,9 +66,9 @@ class VSSMInfer:
             if mt:
                 i, j = int(mt.group(1)), int(mt.group(2))
                 depths[i] = max(depths.get(i, 0), j + 1)
-        m.stem = dict(w0=T("patch_embed.0.weight", dtype), b0=T("patch_embed.0.bias", dtype),
+        m.stem = dict(w0=T("patch_embed.0.weight", dtype), b0=T("patch_embed.0.bias", dtype).float(),
                       n0w=T("patch_embed.2.weight"), n0b=T("patch_embed.2.bias"),
-                      w1=T("patch_embed.5.weight", dtype), b1=T("patch_embed.5.bias", dtype),
+                      w1=T("patch_embed.5.weight", dtype), b1=T("patch_embed.5.bias", dtype).float(),
                       n1w=T("patch_embed.7.weight"), n1b=T("patch_embed.7.bias"))
         for i in sorted(depths):
             stage = []
@@ -97,7 +97,7 @@ class VSSMInfer:
             m.blocks.append(stage)
             q = f"layers.{i}.downsample."
             if q + "1.weight" in sd:
-                m.down.append(dict(w=T(q + "1.weight", dtype), b=T(q + "1.bias", dtype),
+                m.down.append(dict(w=T(q + "1.weight", dtype), bf=T(q + "1.bias", dtype).float(),
                                    nw=T(q + "3.weight"), nb=T(q + "3.bias")))
             else:
                 m.down.append(None)
@@ -135,35 +135,56 @@ class VSSMInfer:
         h = ops.layer_norm_cf(x, b.n2w, b.n2b, 1e-5, self.dtype, add=o, update=True, channel_major=True)   # :1772, 1777
         h = ops.bias_act_(self._pw(b.w1, h), b.b1f, "gelu", channel_major=True)   # Mlp fc1 + GELU   :1160-1163
         m = self._pw(b.w2, h)                                                     # fc2 (its bias joins the residual update)
-        if nxt is None:
-            x.add_(m).add_(b.b2f.view(-1, 1, 1, 1))
-            return x, None
+        if nxt is None:          # end of a stage: the caller decides what consumes x + m + bias
+            return x, (m, b.b2f)
         return x, ops.layer_norm_cf(x, nxt[0], nxt[1], 1e-5, self.dtype, add=m, add_bias=b.b2f, update=True,
                                     channel_major=True)
 
     def _stem(self, img):
+        """patch embed v2 (vmamba.py:1928-1942).  The convolution biases are added inside the LayerNorm calls."""
         s = self.stem
-        x = F.conv2d(img.to(self.dtype), s["w0"], s["b0"], stride=2, padding=1)
-        x = F.gelu(self._ln(x.float(), s["n0w"], s["n0b"], cm=False))
-        x = F.conv2d(x, s["w1"], s["b1"], stride=2, padding=1)
-        return self._ln(x.float(), s["n1w"], s["n1b"], torch.float32, cm=False, out_cm=True)    # -> (C, B, H, W)
+        x = F.conv2d(img.to(self.dtype), s["w0"], None, stride=2, padding=1)
+        x = F.gelu(ops.layer_norm_cf(None, s["n0w"], s["n0b"], 1e-5, self.dtype, add=x, add_bias=s["b0"]))
+        x = F.conv2d(x, s["w1"], None, stride=2, padding=1)
+        return ops.layer_norm_cf(None, s["n1w"], s["n1b"], 1e-5, torch.float32, add=x, add_bias=s["b1"],
+                                 out_channel_major=True)                                   # -> (C, B, H, W) fp32
 
-    def _stages(self, img):
+    def _stages(self, img, want_features=False, head_norm=None):
+        """Runs the stages.  Returns (per-stage residual maps if wanted, last value):
+        the last value is the classifier-normalised (B, C, H, W) map when `head_norm` is given."""
         x = self._stem(img)
         outs = []
+        last = None
         for i, stage in enumerate(self.blocks):
             h = self._ln(x, stage[0].n1w, stage[0].n1b)
+            pend = None
             for j, b in enumerate(stage):
                 nxt = (stage[j + 1].n1w, stage[j + 1].n1b) if j + 1 < len(stage) else None
                 x, h = self._block(x, h, b, nxt)
-            outs.append(x)
+                if nxt is None:
+                    pend = h            # (m, bias): the last residual update of the stage, not applied yet
+            m, mb = pend
             d = self.down[i]
-            if d is not None:      # downsample v3 (vmamba.py:1964-1971): a strided 3x3 convolution wants (B, C, H, W)
-                C, B, H, W = x.shape
-                xin = torch.empty((B, C, H, W), device=x.device, dtype=self.dtype).copy_(x.permute(1, 0, 2, 3))
-                y = F.conv2d(xin, d["w"], d["b"], stride=2, padding=1)
-                x = self._ln(y.float(), d["nw"], d["nb"], torch.float32, cm=False, out_cm=True)
-        return outs, x
+            if d is not None:
+                # downsample v3 (vmamba.py:1964-1971): x += m + bias, and the strided 3x3 convolution's
+                # (B, C, H, W) 16-bit input, in one pass
+                xin = ops.layer_norm_cf(x, None, None, 1e-5, self.dtype, add=m, add_bias=mb, update=True,
+                                        channel_major=True, out_channel_major=False, normalize=False)
+                if want_features:
+                    outs.append(x.clone())
+                y = F.conv2d(xin, d["w"], None, stride=2, padding=1)
+                x = ops.layer_norm_cf(None, d["nw"], d["nb"], 1e-5, torch.float32, add=y, add_bias=d["bf"],
+                                      out_channel_major=True)
+            else:
+                if head_norm is not None:     # classifier norm fused with the last residual update
+                    last = ops.layer_norm_cf(x, head_norm[0], head_norm[1], 1e-5, torch.float32, add=m, add_bias=mb,
+                                             update=True, channel_major=True, out_channel_major=False)
+                else:
+                    ops.layer_norm_cf(x, None, None, 1e-5, self.dtype, add=m, add_bias=mb, update=True,
+                                      channel_major=True, normalize=False)
+                if want_features:
+                    outs.append(x)
+        return outs, (last if last is not None else x)
 
     # ------------------------------------------------------------------ public
     @torch.no_grad()
@@ -171,15 +192,14 @@ class VSSMInfer:
         """VSSM.forward (vmamba.py:2027-2035): (B, 3, H, W) -> (B, num_classes) logits."""
         if self.head is None:
             raise RuntimeError("this model was built without a classifier")
-        _, x = self._stages(img)
         hd = self.head
-        x = self._ln(x, hd["nw"], hd["nb"], torch.float32, out_cm=False).mean(dim=(2, 3))
-        return F.linear(x.to(self.dtype), hd["w"], hd["b"])
+        _, x = self._stages(img, head_norm=(hd["nw"], hd["nb"]))
+        return F.linear(x.mean(dim=(2, 3)).to(self.dtype), hd["w"], hd["b"])
 
     @torch.no_grad()
     def features(self, img: torch.Tensor, out_indices: Sequence[int] = (0, 1, 2, 3)):
         """Backbone_VSSM.forward (vmamba.py:2133-2153): LayerNorm'ed per-stage maps."""
-        outs, _ = self._stages(img)
+        outs, _ = self._stages(img, want_features=True)
         res = []
         for i in out_indices:
             w, b = self.outnorm[i]

@@ -23,6 +23,7 @@ struct NormArgs {
     long long obs, ocs;      // the same for `out`
     int D, L, nv, items;     // nv = L / PV items per image, items = B * nv
     float eps;
+    int skip_norm;           // 1: out = s converted, no statistics (a fused add + cast + layout change)
 };
 
 template <typename Tio, int NTY, int CACHE, int PV>
@@ -45,7 +46,11 @@ __global__ void __launch_bounds__(32 * NTY) layer_norm_cf_kernel(const NormArgs 
             return;
         }
         const long long off = (long long)d * a.cs;
-        Vec<float, PV>::load_plain(src + off, v);      // `in` may alias `sum_out`: no read-only path
+        if (a.in) Vec<float, PV>::load_plain(src + off, v);      // `in` may alias `sum_out`: no read-only path
+        else {
+#pragma unroll
+            for (int i = 0; i < PV; ++i) v[i] = 0.f;
+        }
         if (addp) {
             float t[PV];
             Vec<Tio, PV>::load(addp + off, t);
@@ -84,7 +89,7 @@ __global__ void __launch_bounds__(32 * NTY) layer_norm_cf_kernel(const NormArgs 
 #pragma unroll
         for (int c = 0; c < CACHE; ++c) {
             const int d = ty + c * NTY;
-            if (live && d < D) Vec<float, PV>::load_plain(src + (long long)d * a.cs, cache[c]);
+            if (live && d < D && a.in) Vec<float, PV>::load_plain(src + (long long)d * a.cs, cache[c]);
             else {
 #pragma unroll
                 for (int i = 0; i < PV; ++i) cache[c][i] = 0.f;
@@ -131,10 +136,11 @@ __global__ void __launch_bounds__(32 * NTY) layer_norm_cf_kernel(const NormArgs 
             for (int i = 0; i < PV; ++i) s[i] += v[i];
         }
     }
-    reduce_over_ty(s);
+    const bool norm = a.skip_norm == 0;      // uniform over the grid
+    if (norm) reduce_over_ty(s);
     float mean[PV], q[PV];
 #pragma unroll
-    for (int i = 0; i < PV; ++i) { mean[i] = s[i] / (float)D; q[i] = 0.f; }
+    for (int i = 0; i < PV; ++i) { mean[i] = norm ? s[i] / (float)D : 0.f; q[i] = 0.f; }
     // after the first pass the sum lives in sum_out (if any): re-reads must not add again
     const float* __restrict__ again = a.sum_out ? a.sum_out + base : nullptr;
     auto refetch = [&](int d, float (&v)[PV]) {
@@ -145,7 +151,11 @@ __global__ void __launch_bounds__(32 * NTY) layer_norm_cf_kernel(const NormArgs 
         }
         const long long off = (long long)d * a.cs;
         if (again) { Vec<float, PV>::load_plain(again + off, v); return; }
-        Vec<float, PV>::load_plain(src + off, v);
+        if (a.in) Vec<float, PV>::load_plain(src + off, v);
+        else {
+#pragma unroll
+            for (int i = 0; i < PV; ++i) v[i] = 0.f;
+        }
         if (addp) {
             float t[PV];
             Vec<Tio, PV>::load(addp + off, t);
@@ -158,30 +168,32 @@ __global__ void __launch_bounds__(32 * NTY) layer_norm_cf_kernel(const NormArgs 
             for (int i = 0; i < PV; ++i) v[i] += bb;
         }
     };
-    if constexpr (CACHE > 0) {
+    if (norm) {
+        if constexpr (CACHE > 0) {
 #pragma unroll
-        for (int c = 0; c < CACHE; ++c) {
-            if (ty + c * NTY < D) {
+            for (int c = 0; c < CACHE; ++c) {
+                if (ty + c * NTY < D) {
 #pragma unroll
-                for (int i = 0; i < PV; ++i) { const float t = cache[c][i] - mean[i]; q[i] = fmaf(t, t, q[i]); }
+                    for (int i = 0; i < PV; ++i) { const float t = cache[c][i] - mean[i]; q[i] = fmaf(t, t, q[i]); }
+                }
+            }
+        } else {
+            for (int d = ty; d < D; d += NTY) {
+                float v[PV];
+                refetch(d, v);
+#pragma unroll
+                for (int i = 0; i < PV; ++i) { const float t = v[i] - mean[i]; q[i] = fmaf(t, t, q[i]); }
             }
         }
-    } else {
-        for (int d = ty; d < D; d += NTY) {
-            float v[PV];
-            refetch(d, v);
-#pragma unroll
-            for (int i = 0; i < PV; ++i) { const float t = v[i] - mean[i]; q[i] = fmaf(t, t, q[i]); }
-        }
+        reduce_over_ty(q);
     }
-    reduce_over_ty(q);
     if (!live) return;
     float rstd[PV];
 #pragma unroll
-    for (int i = 0; i < PV; ++i) rstd[i] = rsqrtf(q[i] / (float)D + a.eps);
+    for (int i = 0; i < PV; ++i) rstd[i] = norm ? rsqrtf(q[i] / (float)D + a.eps) : 1.f;
     Tio* __restrict__ dst = (Tio*)a.out + (long long)bimg * a.obs + pix;
     auto emit = [&](int d, const float (&v)[PV]) {
-        const float g = a.w ? __ldg(a.w + d) : 1.f, be = a.b ? __ldg(a.b + d) : 0.f;
+        const float g = (norm && a.w) ? __ldg(a.w + d) : 1.f, be = (norm && a.b) ? __ldg(a.b + d) : 0.f;
         float o[PV];
 #pragma unroll
         for (int i = 0; i < PV; ++i) o[i] = fmaf((v[i] - mean[i]) * rstd[i], g, be);
@@ -231,7 +243,7 @@ static void launch_norm(NormArgs a, int pv, long long B, cudaStream_t st) {
 
 int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st) {
     if (!p) return SS2D_EINVAL_NULL;
-    if (!p->in || !p->out) return SS2D_EINVAL_NULL;
+    if ((!p->in && !p->add) || !p->out) return SS2D_EINVAL_NULL;
     if (!dtype_ok(p->io_dtype)) return SS2D_EINVAL_DTYPE;
     if (p->B <= 0 || p->D <= 0 || p->L <= 0) return SS2D_EINVAL_SHAPE;
     if (p->D > 0x7fffffffLL || p->B * p->L > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
@@ -247,7 +259,7 @@ int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st) {
     int pv = 4;
     auto fit = [&](long long x) { if (x < 0) x = -x; while (pv > 1 && (x % pv) != 0) pv >>= 1; };
     fit(p->L); fit(bs); fit(cs); fit(obs); fit(ocs);
-    fit((long long)(reinterpret_cast<uintptr_t>(p->in) / 4));
+    if (p->in) fit((long long)(reinterpret_cast<uintptr_t>(p->in) / 4));
     fit((long long)(reinterpret_cast<uintptr_t>(p->out) / so));
     if (p->add) fit((long long)(reinterpret_cast<uintptr_t>(p->add) / so));
     if (p->sum_out) fit((long long)(reinterpret_cast<uintptr_t>(p->sum_out) / 4));
@@ -255,6 +267,7 @@ int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st) {
     a.in = (const float*)p->in; a.add = p->add; a.add_bias = (const float*)p->add_bias; a.sum_out = (float*)p->sum_out;
     a.w = (const float*)p->weight; a.b = (const float*)p->bias; a.out = p->out;
     a.bs = bs; a.cs = cs; a.obs = obs; a.ocs = ocs; a.D = (int)p->D; a.L = (int)p->L; a.eps = p->eps; a.nv = 0; a.items = 0;
+    a.skip_norm = p->skip_norm ? 1 : 0;
     if (p->io_dtype == SS2D_F32) launch_norm<float>(a, pv, p->B, st);
     else if (p->io_dtype == SS2D_BF16) launch_norm<__nv_bfloat16>(a, pv, p->B, st);
     else launch_norm<__half>(a, pv, p->B, st);

@@ -217,41 +217,50 @@ def cross_merge_fn(y, in_channel_first=True, out_channel_first=True, one_by_one=
 # --------------------------------------------------------------------------------------------
 # channel-first LayerNorm (out_norm of SS2D)
 # --------------------------------------------------------------------------------------------
-def layer_norm_cf(y: torch.Tensor, weight=None, bias=None, eps: float = 1e-5, out_dtype=None, *,
+def layer_norm_cf(y, weight=None, bias=None, eps: float = 1e-5, out_dtype=None, *,
                   add: torch.Tensor = None, add_bias: torch.Tensor = None, update: bool = False,
-                  channel_major: bool = False, out_channel_major=None) -> torch.Tensor:
+                  channel_major: bool = False, out_channel_major=None, normalize: bool = True) -> torch.Tensor:
     """LayerNorm over the channel axis of an fp32 map, as LayerNorm(channel_first=True)
     (vmamba.py:1078-1093); output in `out_dtype` (default fp32).
 
     The map is (B, D, ...) or, with `channel_major`, (D, B, ...); `out_channel_major` (default: same
     as the input) picks the layout of the result, so the call also converts between the two.
     With `add` (a map of the output dtype, input layout) and/or `add_bias` (per channel), the sum
-    y + add + add_bias is what gets normalised; `update=True` also writes that sum back into `y`
-    (the residual update of VSSBlock._forward, vmamba.py:1772/1777, fused with the next norm)."""
+    y + add + add_bias is what gets normalised; `y` may be None (then `add` alone is the input, e.g. a
+    16-bit convolution output).  `update=True` also writes the sum back into `y` (the residual
+    update of VSSBlock._forward, vmamba.py:1772/1777, fused with the next norm).
+    `normalize=False` skips the normalisation: the call is then a fused add + cast + layout change."""
     _require_cuda(y, weight, bias, add, add_bias)
-    if y.dtype != torch.float32:
-        if update:
-            raise RuntimeError("update=True needs an fp32 residual tensor")
-        y = y.float()
-    if not y.is_contiguous():
-        if update:
-            raise RuntimeError("update=True needs a contiguous residual tensor")
-        y = y.contiguous()
+    if y is None:
+        if add is None or update:
+            raise RuntimeError("layer_norm_cf needs y or add (and y for update=True)")
+    else:
+        if y.dtype != torch.float32:
+            if update:
+                raise RuntimeError("update=True needs an fp32 residual tensor")
+            y = y.float()
+        if not y.is_contiguous():
+            if update:
+                raise RuntimeError("update=True needs a contiguous residual tensor")
+            y = y.contiguous()
+    ref = y if y is not None else add
     if out_channel_major is None:
         out_channel_major = channel_major
-    B, D = (y.shape[1], y.shape[0]) if channel_major else (y.shape[0], y.shape[1])
-    L = y[0, 0].numel()
-    rest = tuple(y.shape[2:])
-    out = torch.empty(((D, B) if out_channel_major else (B, D)) + rest, device=y.device, dtype=out_dtype or torch.float32)
+    B, D = (ref.shape[1], ref.shape[0]) if channel_major else (ref.shape[0], ref.shape[1])
+    L = ref[0, 0].numel()
+    rest = tuple(ref.shape[2:])
+    if out_dtype is None:
+        out_dtype = torch.float32 if add is None else add.dtype
+    out = torch.empty(((D, B) if out_channel_major else (B, D)) + rest, device=ref.device, dtype=out_dtype)
     w = None if weight is None else weight.contiguous().float()
     b = None if bias is None else bias.contiguous().float()
     if add is not None:
-        if add.shape != y.shape:
+        if add.shape != ref.shape:
             raise RuntimeError("add must have the shape of the normalised map")
         add = add.contiguous().to(out.dtype)
     ab = None if add_bias is None else add_bias.contiguous().float()
     p = NormParams()
-    p.in_, p.add, p.add_bias = y.data_ptr(), _ptr(add), _ptr(ab)
+    p.in_, p.add, p.add_bias = _ptr(y), _ptr(add), _ptr(ab)
     p.sum_out = y.data_ptr() if update else None
     p.weight, p.bias, p.out = _ptr(w), _ptr(b), out.data_ptr()
     if channel_major and out_channel_major:
@@ -263,9 +272,9 @@ def layer_norm_cf(y: torch.Tensor, weight=None, bias=None, eps: float = 1e-5, ou
         p.B, p.D, p.L = B, D, L
         p.batch_stride, p.channel_stride = (L, B * L) if channel_major else (D * L, L)
         p.out_batch_stride, p.out_channel_stride = (L, B * L) if out_channel_major else (D * L, L)
-    p.io_dtype, p.eps = dtype_code(out), eps
-    with torch.cuda.device(y.device):
-        check(lib().ss2d_layer_norm_cf(p, _stream(y)), "ss2d_layer_norm_cf")
+    p.io_dtype, p.eps, p.skip_norm = dtype_code(out), eps, int(not normalize)
+    with torch.cuda.device(ref.device):
+        check(lib().ss2d_layer_norm_cf(p, _stream(ref)), "ss2d_layer_norm_cf")
     return out
 
 
