@@ -30,14 +30,18 @@ def test_library_exports_every_declared_symbol():
 
 def test_struct_layout_matches_header(tmp_path):
     prog = tmp_path / "sz.c"
-    prog.write_text('#include "ss2d_b200.h"\n#include <stdio.h>\n#include <stddef.h>\nint main(){printf("%zu %zu %zu %zu %zu %zu\\n",'
+    prog.write_text('#include "ss2d_b200.h"\n#include <stdio.h>\n#include <stddef.h>\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",'
                     'sizeof(ss2d_scan_params),sizeof(ss2d_cross_params),sizeof(ss2d_core_params),sizeof(ss2d_norm_params),'
-                    'offsetof(ss2d_core_params,delta_batch_stride),offsetof(ss2d_scan_params,batch));return 0;}\n')
+                    'offsetof(ss2d_core_params,delta_batch_stride),offsetof(ss2d_scan_params,batch),'
+                    'sizeof(ss2d_expand_params),sizeof(ss2d_pointwise_params),offsetof(ss2d_expand_params,B),'
+                    'offsetof(ss2d_norm_params,io_dtype));return 0;}\n')
     exe = tmp_path / "sz"
     subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), str(prog), "-o", str(exe)])
     got = [int(t) for t in subprocess.check_output([str(exe)]).split()]
     want = [ctypes.sizeof(_lib.ScanParams), ctypes.sizeof(_lib.CrossParams), ctypes.sizeof(_lib.CoreParams),
-            ctypes.sizeof(_lib.NormParams), _lib.CoreParams.delta_batch_stride.offset, _lib.ScanParams.batch.offset]
+            ctypes.sizeof(_lib.NormParams), _lib.CoreParams.delta_batch_stride.offset, _lib.ScanParams.batch.offset,
+            ctypes.sizeof(_lib.ExpandParams), ctypes.sizeof(_lib.PointwiseParams), _lib.ExpandParams.B.offset,
+            _lib.NormParams.io_dtype.offset]
     assert got == want
 
 
@@ -111,3 +115,62 @@ def test_operators_refuse_cpu_tensors():
         vb.selective_scan_fn(x, x, x, x, x, backend="torch")
     with pytest.raises(NotImplementedError):
         vb.cross_scan_fn(x, in_channel_first=False)
+
+
+def test_install_patches_a_reference_like_module():
+    """`install` swaps the operator names a reference module resolves at call time; `uninstall` restores them."""
+    import types
+    import vmamba_b200 as vb
+    from vmamba_b200 import ops
+    fake = types.ModuleType("vmamba")
+    fake.selective_scan_fn = lambda *a, **k: "torch loop"
+    fake.cross_scan_fn = lambda *a, **k: "torch"
+    fake.cross_merge_fn = lambda *a, **k: "torch"
+    fake.SelectiveScanCuda = object
+    fake.WITH_SELECTIVESCAN_MAMBA = False
+    vb.install(fake)
+    assert fake.selective_scan_fn is ops.selective_scan_fn and fake.cross_scan_fn is ops.cross_scan_fn
+    assert fake.cross_merge_fn is ops.cross_merge_fn and fake.SelectiveScanCuda is ops.SelectiveScanCuda
+    assert fake.WITH_SELECTIVESCAN_MAMBA is True
+    vb.uninstall(fake)
+    assert fake.selective_scan_fn() == "torch loop" and fake.WITH_SELECTIVESCAN_MAMBA is False
+    import sys
+    saved = {k: sys.modules.pop(k, None) for k in ("csm_triton", "csms6s")}
+    try:
+        vb.preseed_sys_modules()
+        assert sys.modules["csms6s"].selective_scan_fn is ops.selective_scan_fn
+        assert sys.modules["csm_triton"].cross_scan_fn is ops.cross_scan_fn
+    finally:
+        for k, v in saved.items():
+            sys.modules.pop(k, None)
+            if v is not None:
+                sys.modules[k] = v
+
+
+def test_enable_fused_selects_supported_modules_only():
+    import functools
+    import torch
+    import vmamba_b200 as vb
+
+    class FakeSS2D(torch.nn.Module):
+        def __init__(self, scan_mode="cross2d", channel_first=True, norm=True):
+            super().__init__()
+            self.channel_first = channel_first
+            self.d_state, self.dt_rank = 1, 1
+            self.x_proj = torch.nn.Linear(4, 12, bias=False)
+            self.dt_projs = torch.nn.Linear(1, 16, bias=False)
+            self.A_logs = torch.nn.Parameter(torch.zeros(16, 1))
+            self.Ds = torch.nn.Parameter(torch.ones(16))
+            self.dt_projs_bias = torch.nn.Parameter(torch.zeros(4, 4))
+            self.out_norm = torch.nn.LayerNorm(4) if norm else torch.nn.Identity()
+            self.forward_core = functools.partial(self._core, scan_mode=scan_mode)
+
+        def _core(self, x, scan_mode="cross2d"):
+            return x
+
+    model = torch.nn.Sequential(FakeSS2D(), FakeSS2D(scan_mode="unidi"), FakeSS2D(channel_first=False), FakeSS2D(norm=False))
+    assert vb.enable_fused(model) == 1
+    x = torch.zeros(1, 4, 2, 2)
+    assert model[0].forward_core(x) is x          # CPU tensor: falls through to the original core
+    assert vb.disable_fused(model) == 1
+    assert isinstance(model[0].forward_core, functools.partial)
