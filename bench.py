@@ -181,8 +181,11 @@ def roofline_of_core(model, peak_gbs, peak_kind, batch=None, iters=20):
     alg = B * L * (D * s + K * D * s + 2 * K * N * s + D * s) + 4 * (K * D * N + 2 * K * D) + 2 * 4 * D
     scan_bytes = B * L * (D * s + K * D * s + 2 * K * N * s + D * 4)
     ach = alg / (t_chain * 1e-3) / 1e9
+    # DRAM bytes of the two kernels from an ncu capture of this chain at batch 48 (profiles/
+    # ss2d_chain_stage0_dram_traffic.md): 16.5 bytes per (pixel, channel), scaled by the units of this launch
+    traffic = 16.5 * B * D * L if (D == 96 and s == 2) else None
     return {
-        "bound": "hbm", "achieved": ach, "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs, "traffic": None,
+        "bound": "hbm", "achieved": ach, "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs, "traffic": traffic,
         "peak_kind": f"of {peak_kind}",
         "kernel": "core_plane_kernel + layer_norm_cf_kernel (fused SS2D scan+merge+LayerNorm chain)",
         "workload": f"stage 0 of {MODEL} at 224x224: B={B} D={D} H=W={H} bf16",
