@@ -320,16 +320,41 @@ def run_ours(args):
     def step_device():
         graph.replay()
 
+    # End to end: every step copies its batch from pinned host memory and reads its logits back.  The copy
+    # runs on its own stream into one of two staging buffers, so the upload of step i+1 overlaps the
+    # forward of step i; the forward's input buffer is then filled device-to-device.
+    copy_stream = torch.cuda.Stream()
+    staging = [torch.empty_like(dev_img) for _ in range(2)]
+    h2d_done = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    e2e_it = [0]
+
     def step_e2e():
-        dev_img.copy_(host_img, non_blocking=True)
+        k = e2e_it[0] & 1
+        e2e_it[0] += 1
+        cur = torch.cuda.current_stream()
+        copy_stream.wait_event(consumed[k])              # staging[k] has been read by its previous step
+        with torch.cuda.stream(copy_stream):
+            staging[k].copy_(host_img, non_blocking=True)
+            h2d_done[k].record(copy_stream)
+        cur.wait_event(h2d_done[k])
+        dev_img.copy_(staging[k], non_blocking=True)
+        consumed[k].record(cur)
         graph.replay()
         host_out.copy_(dev_out, non_blocking=True)
+
+    def timed_e2e(steps, warmup):
+        for _ in range(warmup):
+            step_e2e()
+        barrier()
+        copy_stream.wait_stream(torch.cuda.current_stream())   # no upload starts before the timed region does
+        return timed(step_e2e, steps, 0)
 
     warm = max(args.warmup, 3)
     sampler = ClockSampler(local).start() if rank == 0 else None
     ms_dev = timed(step_device, args.steps, warm)
     clocks = sampler.stop() if sampler else None
-    ms_e2e = timed(step_e2e, args.steps, warm)
+    ms_e2e = timed_e2e(args.steps, warm)
 
     total_imgs = BATCH * world * args.steps
     value = total_imgs / (ms_dev * 1e-3)
