@@ -112,8 +112,9 @@ def cpu_baseline(sd, n_images: int, repeats: int = 1):
     best = float("inf")
     for _ in range(repeats):
         t0 = time.perf_counter()
-        BO.vssm_logits(img, sd)
+        logits = BO.vssm_logits(img, sd)
         best = min(best, time.perf_counter() - t0)
+    cpu_baseline.last = (img, logits)      # kept for the parity line of the GPU arm
     return n_images / best, cores, f"{n_images} images of the {BATCH}-image batch, fp32, full VMamba-T forward, {cores} threads"
 
 
@@ -360,13 +361,29 @@ def run_ours(args):
     value = total_imgs / (ms_dev * 1e-3)
     e2e = total_imgs / (ms_e2e * 1e-3)
 
-    roof = cpu = None
+    roof = cpu = parity = None
     if rank == 0:
         peak, kind = peaks()
         roof = roofline_of_core(model, peak, kind)
         if world == 1 and not args.no_cpu_baseline and MODEL == "vmamba_tiny_s1l8" and IMG == 224:
             v, cores, desc = cpu_baseline(sd, 4)
             cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
+            # the same images through the GPU model: parity of the benchmarked path with the oracle
+            import numpy as np
+            img_np, ref = cpu_baseline.last
+            got16 = model(torch.from_numpy(img_np).cuda().to(torch.bfloat16)).float().cpu().numpy()
+            old_tf32 = torch.backends.cudnn.allow_tf32
+            torch.backends.cudnn.allow_tf32 = False
+            m32 = VSSMInfer.from_state_dict(sd, dtype=torch.float32, device=f"cuda:{local}")
+            got32 = m32(torch.from_numpy(img_np).cuda()).cpu().numpy()
+            torch.backends.cudnn.allow_tf32 = old_tf32
+            del m32
+            den = float(np.abs(ref).max())
+            parity = {"images": int(ref.shape[0]), "oracle": "oracle/backbone_oracle.vssm_logits (fp32, CPU)",
+                      "max_rel_err_fp32": float(np.abs(got32 - ref).max()) / den,
+                      "max_rel_err_bf16": float(np.abs(got16 - ref).max()) / den,
+                      "top1_agree_fp32": int((got32.argmax(1) == ref.argmax(1)).sum()),
+                      "top1_agree_bf16": int((got16.argmax(1) == ref.argmax(1)).sum())}
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -394,14 +411,16 @@ def run_ours(args):
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    if parity is not None:
+        line["parity"] = parity
     print(json.dumps(line), flush=True)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--model", default=None, help="vmamba_tiny_s1l8 (default) | vmamba_small_s2l15 | vmamba_base_s2l15")
