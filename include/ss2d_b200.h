@@ -102,8 +102,8 @@ int ss2d_cross_merge(const ss2d_cross_params *p, void *cuda_stream);
  *   delta[k] (B, D, L) per route k, act_dtype, contiguous planes (batch stride given), raw
  *            (pre-bias, pre-softplus) step sizes, stored in the ORIENTATION ORDER of route k:
  *            index h*W+w for k = 0, 2 and w*H+h for k = 1, 3 (never reversed)
- *   Bm[k], Cm[k] (B, N, L) per route, same order, always fp32 (values may have been rounded to
- *            act_dtype by the projection that produced them)
+ *   Bm[k], Cm[k] (B, N, L) per route, same order, act_dtype (the type the projection produced them in,
+ *            as the reference's Bs / Cs are: selective_scan_oflex.cpp:157-159)
  *   A (4*D, N), Dskip (4*D), delta_bias (4*D): fp32, row index k*D + d
  *   ln_weight, ln_bias (D) fp32 or NULL (NULL: no affine); ln_eps; with_norm = 0 skips LayerNorm
  *   y        (B, D, H, W), y_dtype (act_dtype or SS2D_F32), own batch / channel strides
@@ -170,7 +170,7 @@ int ss2d_dwconv3x3_act(const ss2d_pointwise_params *p, void *cuda_stream);
  *             (a GEMM on a channel-major map yields (4, R+2N, B, L): batch L, route (R+2N)*B*L, row B*L)
  *   dt_weight (4, D, R) act_dtype contiguous (dt_projs.weight viewed per route)
  *   delta[k]  (B, D, L) act_dtype  = dt_weight[k] . x_dbl[:, k, :R]  in the orientation order of route k
- *   bc[k]     (B, 2N, L) fp32      = x_dbl[:, k, R:] (B rows then C rows) in the same order
+ *   bc[k]     (B, 2N, L) act_dtype = x_dbl[:, k, R:] (B rows then C rows) in the same order
  * -------------------------------------------------------------------------------- */
 typedef struct ss2d_expand_params {
     const void *x_dbl;

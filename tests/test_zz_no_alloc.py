@@ -33,8 +33,8 @@ def _params(vb, x, proj, w, y, workspace=None):
         j, i = k % 2, k // 2
         p.delta[k] = dl[j].data_ptr() + i * dl[j].stride(1) * x.element_size()
         p.delta_batch_stride[k] = dl[j].stride(0)
-        base = bc[j].data_ptr() + i * bc[j].stride(1) * 4
-        p.Bm[k], p.Cm[k] = base, base + N * bc[j].stride(2) * 4
+        base = bc[j].data_ptr() + i * bc[j].stride(1) * x.element_size()
+        p.Bm[k], p.Cm[k] = base, base + N * bc[j].stride(2) * x.element_size()
         p.bc_batch_stride[k] = bc[j].stride(0)
     p.A, p.Dskip, p.delta_bias = w.A.data_ptr(), w.Ds.data_ptr(), w.dt_bias.data_ptr()
     p.ln_weight, p.ln_bias = w.ln_weight.data_ptr(), w.ln_bias.data_ptr()

@@ -18,7 +18,9 @@
 // map (B, D, H, W), consumed by the LayerNorm kernel.
 //
 // HBM traffic per (pixel, channel): x once, four delta values, one fp32 result; B_k/C_k are shared
-// by all channels of an image and stay in L1/L2.
+// by all channels of an image and stay in L1/L2.  They are read in the activation type (the type
+// the projection produced them in): every thread re-reads them for every plane, and with 16-bit
+// elements a warp's load is one contiguous 512-byte run instead of two half-used 1 KB runs.
 #include <mutex>
 
 #include "common.cuh"
@@ -28,8 +30,8 @@ namespace ss2d {
 struct CoreArgs {
     const void* x;
     const void* delta[4];
-    const float* Bm[4];
-    const float* Cm[4];
+    const void* Bm[4];   // activation dtype, like delta
+    const void* Cm[4];
     const float *A, *Dskip, *bias;
     float* merged;
     long long d_bs[4], d_cs[4], bc_bs[4];
@@ -234,13 +236,13 @@ __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a
         RouteConst rc;
         rc.A = __ldg(a.A + d); rc.bias = __ldg(a.bias + d); rc.bias2 = rc.bias * kLog2e;
         unpack_pairs<T, VEC>(rd0, dv);
-        load_pairs<VEC>(a.Bm[0] + b * a.bc_bs[0] + e0, bv);
-        load_pairs<VEC>(a.Cm[0] + b * a.bc_bs[0] + e0, cv);
+        unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Bm[0] + b * a.bc_bs[0] + e0), bv);
+        unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Cm[0] + b * a.bc_bs[0] + e0), cv);
         AB af = route_local<VEC, true, kPrecise>(ul, dv, bv, cv, rc, cPf, yrow);
         rc.A = __ldg(a.A + 2 * D + d); rc.bias = __ldg(a.bias + 2 * D + d); rc.bias2 = rc.bias * kLog2e;
         unpack_pairs<T, VEC>(rd2, dv);
-        load_pairs<VEC>(a.Bm[2] + b * a.bc_bs[2] + e0, bv);
-        load_pairs<VEC>(a.Cm[2] + b * a.bc_bs[2] + e0, cv);
+        unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Bm[2] + b * a.bc_bs[2] + e0), bv);
+        unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Cm[2] + b * a.bc_bs[2] + e0), cv);
         AB ab = route_local<VEC, false, kPrecise>(ul, dv, bv, cv, rc, cPb, yrow);
         if (first) af.a = 0.f;
         if (last) ab.a = 0.f;
@@ -267,13 +269,13 @@ __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a
         RouteConst rc;
         rc.A = __ldg(a.A + D + d); rc.bias = __ldg(a.bias + D + d); rc.bias2 = rc.bias * kLog2e;
         unpack_pairs<T, VEC>(rd1, dv);
-        load_pairs<VEC>(a.Bm[1] + b * a.bc_bs[1] + e0, bv);
-        load_pairs<VEC>(a.Cm[1] + b * a.bc_bs[1] + e0, cv);
+        unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Bm[1] + b * a.bc_bs[1] + e0), bv);
+        unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Cm[1] + b * a.bc_bs[1] + e0), cv);
         AB af = route_local<VEC, true, kPrecise>(ul, dv, bv, cv, rc, cPf, ycol);
         rc.A = __ldg(a.A + 3 * D + d); rc.bias = __ldg(a.bias + 3 * D + d); rc.bias2 = rc.bias * kLog2e;
         unpack_pairs<T, VEC>(rd3, dv);
-        load_pairs<VEC>(a.Bm[3] + b * a.bc_bs[3] + e0, bv);
-        load_pairs<VEC>(a.Cm[3] + b * a.bc_bs[3] + e0, cv);
+        unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Bm[3] + b * a.bc_bs[3] + e0), bv);
+        unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Cm[3] + b * a.bc_bs[3] + e0), cv);
         AB ab = route_local<VEC, false, kPrecise>(ul, dv, bv, cv, rc, cPb, ycol);
         if (first) af.a = 0.f;
         if (last) ab.a = 0.f;
@@ -311,7 +313,7 @@ static bool plan_planes(const ss2d_core_params* p, PlaneConfig& c) {
     fit(L); fit(el(p->x)); fit(p->x_batch_stride); fit(p->x_channel_stride);
     for (int k = 0; k < 4; ++k) {
         fit(el(p->delta[k]));
-        fit((long long)(reinterpret_cast<uintptr_t>(p->Bm[k]) / 4)); fit((long long)(reinterpret_cast<uintptr_t>(p->Cm[k]) / 4));
+        fit(el(p->Bm[k])); fit(el(p->Cm[k]));
         fit(p->delta_batch_stride[k]); fit(p->bc_batch_stride[k]); fit(p->delta_channel_stride[k]);
     }
     // a thread's segment may wrap to the next line only at its middle: vec/2 divides H and W
@@ -320,7 +322,7 @@ static bool plan_planes(const ss2d_core_params* p, PlaneConfig& c) {
     // (alignment of the fp32 workspace is checked by the caller)
     const long long G = L / vec;
     if (G > 1024) return false;
-    int PP = (int)(448 / G);          // ~14 warps per CTA: two to three CTAs per SM
+    int PP = (int)(448 / G);          // ~14 warps per CTA: two CTAs per SM
     if (PP < 1) PP = 1;
     if (PP > p->D) PP = (int)p->D;
     const int Wp = (int)(p->W | 1);   // odd pitch spreads the transposed accesses over banks
@@ -384,7 +386,7 @@ static int validate_core(const ss2d_core_params* p) {
         !aligned_to(p->ln_bias, 4))
         return SS2D_EINVAL_ALIGN;
     for (int k = 0; k < 4; ++k)
-        if (!aligned_to(p->delta[k], s) || !aligned_to(p->Bm[k], 4) || !aligned_to(p->Cm[k], 4)) return SS2D_EINVAL_ALIGN;
+        if (!aligned_to(p->delta[k], s) || !aligned_to(p->Bm[k], s) || !aligned_to(p->Cm[k], s)) return SS2D_EINVAL_ALIGN;
     return SS2D_OK;
 }
 
@@ -416,7 +418,7 @@ int core_fwd(const ss2d_core_params* p, cudaStream_t st) {
     CoreArgs a;
     a.x = p->x;
     for (int k = 0; k < 4; ++k) {
-        a.delta[k] = p->delta[k]; a.Bm[k] = (const float*)p->Bm[k]; a.Cm[k] = (const float*)p->Cm[k];
+        a.delta[k] = p->delta[k]; a.Bm[k] = p->Bm[k]; a.Cm[k] = p->Cm[k];
         a.d_bs[k] = p->delta_batch_stride[k]; a.bc_bs[k] = p->bc_batch_stride[k];
         a.d_cs[k] = p->delta_channel_stride[k] ? p->delta_channel_stride[k] : p->H * p->W;
     }
@@ -512,7 +514,7 @@ int core_fwd_static(const ss2d_core_params* p, cudaStream_t st) {
     CoreArgs a;
     a.x = p->x;
     for (int k = 0; k < 4; ++k) {
-        a.delta[k] = p->delta[k]; a.Bm[k] = (const float*)p->Bm[k]; a.Cm[k] = (const float*)p->Cm[k];
+        a.delta[k] = p->delta[k]; a.Bm[k] = p->Bm[k]; a.Cm[k] = p->Cm[k];
         a.d_bs[k] = p->delta_batch_stride[k]; a.bc_bs[k] = p->bc_batch_stride[k];
         a.d_cs[k] = p->delta_channel_stride[k] ? p->delta_channel_stride[k] : p->H * p->W;
     }

@@ -4,7 +4,7 @@
 // (B, 4, R+2N, L).  For every route k this kernel writes, in the ORIENTATION order of the route
 // (row-major pixels for k = 0, 2; column-major for k = 1, 3):
 //   delta_k[b, d, q] = sum_r Wdt[k, d, r] * x_dbl[b, k, r, pix(q)]     (R -> D, rounded to the activation type)
-//   bc_k[b, n, q]    = x_dbl[b, k, R + n, pix(q)]   n < 2N            (B then C rows, widened to fp32)
+//   bc_k[b, n, q]    = x_dbl[b, k, R + n, pix(q)]   n < 2N            (B then C rows, activation type)
 // i.e. dt_projs (a grouped 1x1 convolution with a contraction length of only R = 6..64), the
 // split/contiguous copies, and the CrossScan permutation of the projected rows, in one pass whose
 // cost is the write of delta.  The contraction is far too short and the output far too large for
@@ -24,7 +24,7 @@ struct ExpandArgs {
     const void* xd;      // (B, 4, C, L)
     const void* wdt;     // (4, D, R) activation dtype
     void* delta[4];      // (B, D, L) each
-    float* bc[4];        // (B, 2N, L) each
+    void* bc[4];         // (B, 2N, L) each, activation dtype
     long long xd_bs, xd_ks, xd_rs;     // element strides of x_dbl: batch, route, row
     long long d_bs[4], d_cs[4], bc_bs[4], bc_rs[4];   // delta: batch / channel strides; B-C rows: batch / row strides
     int B, D, R, N2, C, H, W, L;       // N2 = 2N, C = R + 2N; L = run length (H*W, or B*H*W when images are adjacent)
@@ -88,12 +88,12 @@ __global__ void __launch_bounds__(kExpThreads) route_expand_kernel(const ExpandA
     }
     __syncthreads();
 
-    // ---- B / C rows: widen and pass through (first channel slice only) --------------------------------
+    // ---- B / C rows: pass through (first channel slice only) --------------------------------
     if (live && blockIdx.z == 0) {
         for (int n = dg; n < a.N2; n += NDG) {
             float v[VEC];
             Vec<float, VEC>::load_plain(s_rows + (size_t)(a.R + n) * (NI * VEC) + it * VEC, v);
-            Vec<float, VEC>::store(a.bc[k] + b * a.bc_bs[k] + (long long)n * a.bc_rs[k] + q0, v);
+            Vec<T, VEC>::store((T*)a.bc[k] + b * a.bc_bs[k] + (long long)n * a.bc_rs[k] + q0, v);
         }
     }
 
@@ -178,7 +178,7 @@ int route_expand(const ss2d_expand_params* p, cudaStream_t st) {
     const size_t s = dtype_size(p->act_dtype);
     if (!aligned_to(p->x_dbl, s) || !aligned_to(p->dt_weight, s)) return SS2D_EINVAL_ALIGN;
     for (int k = 0; k < 4; ++k) {
-        if (!aligned_to(p->delta[k], s) || !aligned_to(p->bc[k], 4)) return SS2D_EINVAL_ALIGN;
+        if (!aligned_to(p->delta[k], s) || !aligned_to(p->bc[k], s)) return SS2D_EINVAL_ALIGN;
         if (p->B > 1 && (p->delta_batch_stride[k] < L || p->bc_batch_stride[k] < L)) return SS2D_EINVAL_STRIDE;
         if ((p->delta_channel_stride[k] && p->delta_channel_stride[k] < L) || (p->bc_row_stride[k] && p->bc_row_stride[k] < L)) return SS2D_EINVAL_STRIDE;
     }
@@ -197,14 +197,14 @@ int route_expand(const ss2d_expand_params* p, cudaStream_t st) {
         if (!flat) { fit(p->delta_batch_stride[k]); fit(p->bc_batch_stride[k]); }
         fit(p->delta_channel_stride[k] ? p->delta_channel_stride[k] : L); fit(p->bc_row_stride[k] ? p->bc_row_stride[k] : L);
         fit((long long)(reinterpret_cast<uintptr_t>(p->delta[k]) / s));
-        fit((long long)(reinterpret_cast<uintptr_t>(p->bc[k]) / 4));
+        fit((long long)(reinterpret_cast<uintptr_t>(p->bc[k]) / s));
     }
     // the staged rows (C rows x 64 items x vec floats) should stay near 28 KB so that several CTAs share an SM
     while (vec > 1 && C * 64 * vec * 4 > 28 * 1024) vec >>= 1;
     ExpandArgs a;
     a.xd = p->x_dbl; a.wdt = p->dt_weight;
     for (int k = 0; k < 4; ++k) {
-        a.delta[k] = p->delta[k]; a.bc[k] = (float*)p->bc[k];
+        a.delta[k] = p->delta[k]; a.bc[k] = p->bc[k];
         a.d_bs[k] = p->delta_batch_stride[k]; a.bc_bs[k] = p->bc_batch_stride[k];
         a.d_cs[k] = p->delta_channel_stride[k] ? p->delta_channel_stride[k] : L;
         a.bc_rs[k] = p->bc_row_stride[k] ? p->bc_row_stride[k] : L;

@@ -60,12 +60,11 @@ def project(x: torch.Tensor, w: CoreWeights, channel_major: bool = False):
     """x (B, D, H, W), or (D, B, H, W) with `channel_major` -> per-orientation projections.
 
     Returns (bc_even, bc_odd, delta_even, delta_odd):
-      bc_even  (B, 2, 2N, L) fp32: B then C rows of routes 0 and 2, row-major pixel order
-      bc_odd   (B, 2, 2N, L) fp32: routes 1 and 3, column-major pixel order
-      delta_*  (B, 2, D, L) raw step sizes in the same orders, activation dtype
-    One library GEMM (x_proj on the un-scanned map) and one `ss2d_route_expand` launch.  B and C keep
-    the rounding of the projection output (activation dtype) and are then widened: they are 2N rows
-    per route against D rows of delta, and fp32 saves the scan kernel two unpack instructions per element.
+      bc_even  (B, 2, 2N, L): B then C rows of routes 0 and 2, row-major pixel order
+      bc_odd   (B, 2, 2N, L): routes 1 and 3, column-major pixel order
+      delta_*  (B, 2, D, L) raw step sizes in the same orders
+    all in the activation dtype (the dtype the projection produced them in, as in the reference under
+    autocast).  One library GEMM (x_proj on the un-scanned map) and one `ss2d_route_expand` launch.
     """
     if channel_major:
         D, B, H, W = x.shape
@@ -80,7 +79,7 @@ def project(x: torch.Tensor, w: CoreWeights, channel_major: bool = False):
         xd = torch.matmul(w.wx, x.reshape(D, B * L))
         p.x_dbl_batch_stride, p.x_dbl_route_stride, p.x_dbl_row_stride = L, C * B * L, B * L
         delta = torch.empty((2, 2, D, B, L), device=x.device, dtype=x.dtype)
-        bc = torch.empty((2, 2, 2 * N, B, L), device=x.device, dtype=torch.float32)
+        bc = torch.empty((2, 2, 2 * N, B, L), device=x.device, dtype=x.dtype)
         for k in range(K):
             j, i = k % 2, k // 2
             p.delta[k], p.delta_batch_stride[k], p.delta_channel_stride[k] = delta[j, i].data_ptr(), L, B * L
@@ -89,7 +88,7 @@ def project(x: torch.Tensor, w: CoreWeights, channel_major: bool = False):
         xd = torch.matmul(w.wx, x.reshape(B, D, L))                   # (B, 4*C, L), route-major rows
         p.x_dbl_batch_stride, p.x_dbl_route_stride, p.x_dbl_row_stride = xd.stride(0), C * L, L
         delta = torch.empty((2, B, 2, D, L), device=x.device, dtype=x.dtype)   # [orientation][b][pair index]
-        bc = torch.empty((2, B, 2, 2 * N, L), device=x.device, dtype=torch.float32)
+        bc = torch.empty((2, B, 2, 2 * N, L), device=x.device, dtype=x.dtype)
         for k in range(K):
             j, i = k % 2, k // 2
             p.delta[k], p.delta_batch_stride[k] = delta[j, :, i].data_ptr(), delta.stride(1)
@@ -124,7 +123,7 @@ def project_library(x: torch.Tensor, w: CoreWeights):
     xd_odd = xd[:, :, 1].transpose(-1, -2).reshape(B, 2, C, L)
     delta_even = torch.matmul(w.wdt[0::2], xd_even[:, :, :R])
     delta_odd = torch.matmul(w.wdt[1::2], xd_odd[:, :, :R])
-    return RouteStreams(xd_even[:, :, R:].float(), xd_odd[:, :, R:].float(), delta_even, delta_odd, False)
+    return RouteStreams(xd_even[:, :, R:].contiguous(), xd_odd[:, :, R:].contiguous(), delta_even, delta_odd, False)
 
 
 def scan_merge_norm(x: torch.Tensor, proj, w: CoreWeights, *, with_norm: bool = True, out_dtype=None,
@@ -159,9 +158,9 @@ def scan_merge_norm(x: torch.Tensor, proj, w: CoreWeights, *, with_norm: bool = 
         else:                         # delta (B, pair, D, L), B/C rows (B, pair, 2N, L)
             p.delta[k] = dl.data_ptr() + i * dl.stride(1) * esz
             p.delta_batch_stride[k], p.delta_channel_stride[k] = dl.stride(0), dl.stride(2)
-            base = bc.data_ptr() + i * bc.stride(1) * 4
+            base = bc.data_ptr() + i * bc.stride(1) * esz
             p.Bm[k] = base
-            p.Cm[k] = base + N * bc.stride(2) * 4
+            p.Cm[k] = base + N * bc.stride(2) * esz
             p.bc_batch_stride[k] = bc.stride(0)
     p.A, p.Dskip, p.delta_bias = w.A.data_ptr(), w.Ds.data_ptr(), w.dt_bias.data_ptr()
     p.ln_weight = None if w.ln_weight is None else w.ln_weight.data_ptr()
