@@ -186,6 +186,68 @@ def selective_scan(u, delta, A, B, C, D=None, delta_bias=None, delta_softplus=Tr
     return out if oflex else _round_to(out, dtype_in)
 
 
+def selective_scan_bwd(u, delta, A, B, C, D, delta_bias, dout, delta_softplus=True, dtype_in: str = "f32"):
+    """Gradients of `selective_scan` for an upstream gradient dout (Bt, K*Cd, L).
+
+    What SelectiveScanCuda.backward returns (csms6s.py:89-109; shapes and types of the results
+    as in selective_scan_oflex.cpp:308-353): du, ddelta like u; dA (K*Cd, N) fp32; dB, dC like B, C
+    (accumulated in fp32 over the channels of a group, then rounded to the storage type);
+    dD, ddelta_bias (K*Cd,) fp32, or None where the input was None.  With
+    d' = softplus(delta + bias), a = exp(d' A), h_l = a_l h_{l-1} + d'_l B_l u_l, y_l = C_l . h_l + D u_l:
+        dh_l  = C_l dout_l + a_{l+1} dh_{l+1}                    (reverse recurrence)
+        dC_l  = sum_channels dout_l h_l          dB_l = sum_channels dh_l d'_l u_l
+        du_l  = dout_l D + d'_l (B_l . dh_l)     dD   = sum_{b,l} dout_l u_l
+        dd'_l = sum_n dh_l (B_l u_l + A a_l h_{l-1})             dA = sum_{b,l} dh_l d'_l a_l h_{l-1}
+        ddelta_l = dd'_l * sigmoid(delta_l + bias) where softplus is applied below its threshold 20
+    The forward states are recomputed exactly as in `selective_scan` (fp32).
+    """
+    u = np.asarray(u, dtype=np.float32)
+    draw = np.asarray(delta, dtype=np.float32)
+    A = np.asarray(A, dtype=np.float32)
+    B = np.asarray(B, dtype=np.float32)
+    C = np.asarray(C, dtype=np.float32)
+    g = np.asarray(dout, dtype=np.float32)
+    Bt, K, N, L = B.shape
+    KC = u.shape[1]
+    Cd = KC // K
+    x = draw if delta_bias is None else draw + np.asarray(delta_bias, dtype=np.float32)[None, :, None]
+    if delta_softplus:
+        dl = softplus(x)
+        if delta_bias is None:
+            dl = _round_to(dl, dtype_in)
+        with np.errstate(over="ignore"):
+            dsp = np.where(x > 20.0, 1.0, 1.0 / (1.0 + np.exp(-x))).astype(np.float32)
+    else:
+        dl, dsp = x, np.ones_like(x)
+    Bx = np.repeat(B, Cd, axis=1).reshape(Bt, KC, N, L)
+    Cx = np.repeat(C, Cd, axis=1).reshape(Bt, KC, N, L)
+    a = np.exp(dl[:, :, None, :] * A[None, :, :, None]).astype(np.float32)        # (Bt, KC, N, L)
+    hs = np.empty((Bt, KC, N, L), dtype=np.float32)
+    h = np.zeros((Bt, KC, N), dtype=np.float32)
+    for i in range(L):
+        h = a[..., i] * h + (dl[:, :, i] * u[:, :, i])[:, :, None] * Bx[..., i]
+        hs[..., i] = h
+    hprev = np.concatenate([np.zeros((Bt, KC, N, 1), np.float32), hs[..., :-1]], axis=-1)
+    dh = np.empty_like(hs)
+    e = np.zeros((Bt, KC, N), dtype=np.float32)      # a_{l+1} dh_{l+1}
+    for i in range(L - 1, -1, -1):
+        dh[..., i] = Cx[..., i] * g[:, :, None, i] + e
+        e = a[..., i] * dh[..., i]
+    dC = (g[:, :, None, :] * hs).reshape(Bt, K, Cd, N, L).sum(axis=2, dtype=np.float32)
+    dB = (dh * (dl * u)[:, :, None, :]).reshape(Bt, K, Cd, N, L).sum(axis=2, dtype=np.float32)
+    du = dl * np.sum(Bx * dh, axis=2, dtype=np.float32)
+    ddl = np.sum(dh * (Bx * u[:, :, None, :] + A[None, :, :, None] * a * hprev), axis=2, dtype=np.float32)
+    dA = np.sum(dh * a * hprev * dl[:, :, None, :], axis=(0, 3), dtype=np.float32)
+    dD = None
+    if D is not None:
+        du = du + g * np.asarray(D, dtype=np.float32)[None, :, None]
+        dD = np.sum(g * u, axis=(0, 2), dtype=np.float32)
+    ddelta = (ddl * dsp).astype(np.float32)
+    dbias = None if delta_bias is None else np.sum(ddelta, axis=(0, 2), dtype=np.float32)
+    return (_round_to(du.astype(np.float32), dtype_in), _round_to(ddelta, dtype_in), dA,
+            _round_to(dB, dtype_in), _round_to(dC, dtype_in), dD, dbias)
+
+
 # --------------------------------------------------------------------------- #
 # a8: channel-first LayerNorm  (vmamba.py:1078-1093)
 # --------------------------------------------------------------------------- #

@@ -161,6 +161,36 @@ def main():
             out[f"{n}_bias"] = npf(bias)
     np.savez_compressed(os.path.join(HERE, "selscan_small.npz"), **out)
 
+    # ---- 2b. gradients of the same cases: autograd through the reference's selective_scan_torch,
+    #          which is what SelectiveScanCuda.backward (csms6s.py:89-109) has to reproduce ----------
+    outb = {"names": np.array([c["name"] for c in cases])}
+    for c in cases:
+        g = torch.Generator().manual_seed(100 + len(c["name"]) + ord(c["name"][1]))
+        tdt = dict(f32=torch.float32, bf16=torch.bfloat16, f16=torch.float16)[c["dt"]]
+        KC = c["K"] * c["Cd"]
+        u = torch.randn((c["Bt"], KC, c["L"]), generator=g).to(tdt)
+        delta = (0.5 * torch.rand((c["Bt"], KC, c["L"]), generator=g)).to(tdt) if not c["sp"] \
+            else torch.randn((c["Bt"], KC, c["L"]), generator=g).to(tdt)
+        A = -0.5 * torch.rand((KC, c["N"]), generator=g) - 0.05
+        Bm = torch.randn((c["Bt"], c["K"], c["N"], c["L"]), generator=g).to(tdt)
+        Cm = torch.randn((c["Bt"], c["K"], c["N"], c["L"]), generator=g).to(tdt)
+        Dp = torch.randn(KC, generator=g) if c["D"] else None
+        bias = (0.5 * torch.rand(KC, generator=g) - 2.0) if c["bias"] else None
+        leaves = [t for t in (u, delta, A, Bm, Cm, Dp, bias) if t is not None]
+        with torch.enable_grad():
+            for t in leaves:
+                t.requires_grad_(True)
+            y = ref.selective_scan_torch(u, delta, A, Bm, Cm, Dp, bias, c["sp"], c["oflex"])
+            dout = torch.randn(y.shape, generator=torch.Generator().manual_seed(7 + ord(c["name"][1]))).to(y.dtype)
+            y.backward(dout)
+        n = c["name"]
+        outb[f"{n}_dout"] = npf(dout)
+        for nm, t in (("du", u), ("ddelta", delta), ("dA", A), ("dB", Bm), ("dC", Cm), ("dD", Dp), ("dbias", bias)):
+            if t is not None:
+                assert t.grad is not None and t.grad.dtype == t.dtype
+                outb[f"{n}_{nm}"] = npf(t.grad)
+    np.savez_compressed(os.path.join(HERE, "selscan_bwd_small.npz"), **outb)
+
     # ---- 3. SS2D module (forward_type v05_noz, channel-first), core in/out -------
     out = {}
     for tag, kw, shape in (

@@ -56,6 +56,25 @@ def test_selective_scan_vs_reference(n):
     assert O.max_rel_err(yc, g[f"{n}_y"]) <= (2e-6 if oflex else 8e-3)
 
 
+@pytest.mark.parametrize("n", ["c0", "c1", "c2", "c3", "c4", "c5", "c6"])
+def test_selective_scan_bwd_vs_reference_autograd(n):
+    """The oracle's gradient formulas against autograd through the reference's selective_scan_torch."""
+    g, gb = load("selscan_small.npz"), load("selscan_bwd_small.npz")
+    (u, delta, A, B, C), kw = _case(g, n)
+    dt = str(g[f"{n}_dtype"])
+    grads = O.selective_scan_bwd(u, delta, A, B, C, kw["D"], kw["delta_bias"], gb[f"{n}_dout"],
+                                 delta_softplus=kw["delta_softplus"], dtype_in=dt)
+    # 16-bit storage: the reference rounds its gradients to the storage type too; one ulp may flip
+    tol = 1e-5 if dt == "f32" else (8e-3 if dt == "bf16" else 2e-3)
+    for name, got in zip(("du", "ddelta", "dA", "dB", "dC", "dD", "dbias"), grads):
+        key = f"{n}_{name}"
+        if got is None:
+            assert key not in gb.files, name
+            continue
+        t = 1e-5 if name in ("dA", "dD", "dbias") else tol
+        assert O.max_rel_err(got, gb[key]) <= t, (name, O.max_rel_err(got, gb[key]))
+
+
 @pytest.mark.parametrize("tag", ["m0", "m1"])
 def test_ss2d_core_vs_reference_module(tag):
     g = load("ss2d_module_small.npz")
