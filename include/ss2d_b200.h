@@ -71,6 +71,42 @@ typedef struct ss2d_scan_params {
 int ss2d_selective_scan_fwd(const ss2d_scan_params *p, void *cuda_stream);
 
 /* ------------------------------------------------------------------------------------
+ * Selective-scan backward.  Replaces selective_scan_cuda_oflex.bwd
+ * (kernels/selective_scan/cusoflex/selective_scan_oflex.cpp:233-355, kernel
+ * cusoflex/selective_scan_bwd_kernel_oflex.cuh:73-290) as called by SelectiveScanCuda.backward
+ * (classification/models/csms6s.py:89-109); same gradients as autograd through
+ * selective_scan_torch (csms6s.py:25-68).
+ *
+ * Inputs as in the forward call plus dout (batch, dim, seqlen) of dout_dtype (SS2D_F32 or
+ * in_dtype), last dimension contiguous.  Nothing saved by the forward call is needed: the states
+ * are recomputed.  Results (all fully overwritten, all contiguous):
+ *   du, ddelta (batch, dim, seqlen) in_dtype;  dA (dim, dstate) fp32;
+ *   dB, dC (batch, n_groups, dstate, seqlen) in_dtype, summed in fp32 over the channels of a group;
+ *   dD, ddelta_bias (dim) fp32, required exactly when D / delta_bias is given.
+ * workspace: ss2d_selective_scan_bwd_workspace_bytes() bytes, 16-byte aligned (fp32 partial sums).
+ * No atomics: repeated calls give bit-identical results.
+ * -------------------------------------------------------------------------------- */
+typedef struct ss2d_scan_bwd_params {
+    const void *u, *delta, *A, *B, *C, *D, *delta_bias;
+    const void *dout;
+    void *du, *ddelta, *dA, *dB, *dC, *dD, *ddelta_bias;
+    void *workspace;
+    int64_t workspace_bytes;
+    int32_t in_dtype, dout_dtype;
+    int32_t delta_softplus;
+    int32_t reserved0;
+    int64_t batch, dim, dstate, seqlen, n_groups;
+    int64_t u_batch_stride, u_dim_stride;
+    int64_t delta_batch_stride, delta_dim_stride;
+    int64_t dout_batch_stride, dout_dim_stride;
+    int64_t B_batch_stride, B_group_stride, B_state_stride;
+    int64_t C_batch_stride, C_group_stride, C_state_stride;
+} ss2d_scan_bwd_params;
+
+int64_t ss2d_selective_scan_bwd_workspace_bytes(const ss2d_scan_bwd_params *p);   /* < 0: invalid or unsupported arguments */
+int ss2d_selective_scan_bwd(const ss2d_scan_bwd_params *p, void *cuda_stream);
+
+/* ------------------------------------------------------------------------------------
  * CrossScan / CrossMerge, channel-first tensors.  Replace CrossScanTritonF.forward and
  * CrossMergeTritonF.forward / triton_cross_scan_flex (classification/models/csm_triton.py:
  * 278-497; vmamba.py:350-575) and compute exactly cross_scan_fwd / cross_merge_fwd

@@ -1,0 +1,154 @@
+"""Parity of the backward operators (selective-scan gradients, CrossScan / CrossMerge adjoints)
+with the reference's autograd results (golden fixtures) and with the CPU oracle.  Needs a GPU.
+
+Tolerances: max|got-ref| / max|ref| <= 1e-4 for fp32 tensors, <= 2e-2 for 16-bit storage;
+the CrossScan / CrossMerge adjoints are data movement (and fp32 sums in the reference's order): bit-exact."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ss2d_oracle as O
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+TOL = {"f32": 1e-4, "bf16": 2e-2, "f16": 2e-2}
+TD = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}
+NAMES = ("du", "ddelta", "dA", "dB", "dC", "dD", "dbias")
+
+
+@pytest.fixture(scope="module")
+def vb():
+    import vmamba_b200
+    assert torch.cuda.is_available()
+    return vmamba_b200
+
+
+def dev(a, dtype=torch.float32):
+    return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to("cuda").to(dtype)
+
+
+def host(t):
+    return None if t is None else t.detach().float().cpu().numpy()
+
+
+def _autograd(vb, u, delta, A, B, C, D, bias, dout, sp, oflex, dt):
+    """Gradients through the public operator (SelectiveScanCuda.apply under selective_scan_fn)."""
+    td = TD[dt]
+    ts = [dev(u, td), dev(delta, td), dev(A), dev(B, td), dev(C, td), dev(D), dev(bias)]
+    for t in ts:
+        if t is not None:
+            t.requires_grad_(True)
+    y = vb.selective_scan_fn(*ts, sp, oflex)
+    assert y.dtype == (torch.float32 if oflex else td)
+    y.backward(dev(dout, y.dtype))
+    return [None if t is None else host(t.grad) for t in ts]
+
+
+@pytest.mark.parametrize("n", ["c0", "c1", "c2", "c3", "c4", "c5", "c6"])
+def test_selective_scan_bwd_golden(vb, n):
+    """Against autograd through the unmodified reference's selective_scan_torch (stored fixture)."""
+    g, gb = np.load(os.path.join(G, "selscan_small.npz")), np.load(os.path.join(G, "selscan_bwd_small.npz"))
+    dt = str(g[f"{n}_dtype"])
+    D = g[f"{n}_D"] if f"{n}_D" in g.files else None
+    bias = g[f"{n}_bias"] if f"{n}_bias" in g.files else None
+    got = _autograd(vb, g[f"{n}_u"], g[f"{n}_delta"], g[f"{n}_A"], g[f"{n}_B"], g[f"{n}_C"], D, bias, gb[f"{n}_dout"],
+                    bool(g[f"{n}_sp"]), bool(g[f"{n}_oflex"]), dt)
+    for name, x in zip(NAMES, got):
+        key = f"{n}_{name}"
+        if x is None:
+            assert key not in gb.files
+            continue
+        err = O.max_rel_err(x, gb[key])
+        assert err <= TOL[dt], (name, err)
+
+
+def _random_case(Bt, K, Cd, N, L, seed, with_D=True, with_bias=True):
+    rng = np.random.default_rng(seed)
+    KC = K * Cd
+    u = rng.standard_normal((Bt, KC, L), dtype=np.float32)
+    delta = rng.standard_normal((Bt, KC, L), dtype=np.float32)
+    A = -np.exp(0.3 * rng.standard_normal((KC, N), dtype=np.float32))
+    B = rng.standard_normal((Bt, K, N, L), dtype=np.float32)
+    C = rng.standard_normal((Bt, K, N, L), dtype=np.float32)
+    D = rng.standard_normal(KC).astype(np.float32) if with_D else None
+    bias = (rng.standard_normal(KC).astype(np.float32) - 3.0) if with_bias else None
+    dout = rng.standard_normal((Bt, KC, L), dtype=np.float32)
+    return u, delta, A, B, C, D, bias, dout
+
+
+@pytest.mark.parametrize("Bt,K,Cd,N,L", [(2, 4, 5, 1, 3136), (1, 4, 12, 1, 784), (3, 4, 3, 1, 49), (2, 4, 2, 1, 1),
+                                          (2, 4, 9, 1, 197), (1, 2, 3, 16, 330), (2, 1, 2, 64, 70), (1, 4, 2, 1, 16384)])
+def test_selective_scan_bwd_fp32_vs_oracle(vb, Bt, K, Cd, N, L):
+    u, delta, A, B, C, D, bias, dout = _random_case(Bt, K, Cd, N, L, seed=L + N)
+    ref = O.selective_scan_bwd(u, delta, A, B, C, D, bias, dout, True, "f32")
+    got = _autograd(vb, u, delta, A, B, C, D, bias, dout, True, True, "f32")
+    for name, x, r in zip(NAMES, got, ref):
+        err = O.max_rel_err(x, r)
+        assert err <= TOL["f32"], (name, err)
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("oflex", [True, False])
+def test_selective_scan_bwd_16bit_vs_oracle(vb, dt, oflex):
+    u, delta, A, B, C, D, bias, dout = _random_case(2, 4, 6, 1, 784, seed=11)
+    rnd = lambda a: O._round_to(a, dt)
+    u, delta, B, C = rnd(u), rnd(delta), rnd(B), rnd(C)
+    if not oflex:
+        dout = rnd(dout)
+    ref = O.selective_scan_bwd(u, delta, A, B, C, D, bias, dout, True, dt)
+    got = _autograd(vb, u, delta, A, B, C, D, bias, dout, True, oflex, dt)
+    for name, x, r in zip(NAMES, got, ref):
+        err = O.max_rel_err(x, r)
+        assert err <= TOL[dt], (name, err)
+
+
+def test_selective_scan_bwd_optional_args_strided_and_deterministic(vb):
+    u, delta, A, B, C, _, _, dout = _random_case(2, 4, 3, 2, 160, seed=3, with_D=False, with_bias=False)
+    ref = O.selective_scan_bwd(u, delta, A, B, C, None, None, dout, False, "f32")
+    from vmamba_b200 import ops
+    big_u = torch.zeros((2, 12, 2 * 160), device="cuda")
+    big_u[:, :, 8:8 + 160] = dev(u)
+    big_g = torch.zeros((2, 24, 160), device="cuda")
+    big_g[:, ::2] = dev(dout)
+    args = (big_u[:, :, 8:8 + 160], dev(delta), dev(A), dev(B), dev(C), None, None, big_g[:, ::2], False)
+    got = ops.selective_scan_bwd(*args)
+    assert got[5] is None and got[6] is None
+    for name, x, r in zip(NAMES, got, ref):
+        if r is not None:
+            assert O.max_rel_err(host(x), r) <= TOL["f32"], name
+    again = ops.selective_scan_bwd(*args)
+    for a_, b_ in zip(got, again):
+        if a_ is not None:
+            assert torch.equal(a_, b_)
+
+
+def test_selective_scan_bwd_rejects_bad_arguments(vb):
+    from vmamba_b200 import ops
+    u, delta, A, B, C, D, bias, dout = (dev(t) for t in _random_case(1, 4, 2, 1, 32, seed=1))
+    with pytest.raises(RuntimeError):
+        ops.selective_scan_bwd(u, delta, A, B, C, D, bias, dout[:, :, :16], True)
+    with pytest.raises(RuntimeError):
+        ops.selective_scan_bwd(u.cpu(), delta, A, B, C, D, bias, dout, True)
+
+
+@pytest.mark.parametrize("scans", [0, 1, 2, 3])
+@pytest.mark.parametrize("shape", [(2, 5, 7, 9), (1, 3, 14, 14)])
+def test_cross_scan_merge_adjoints(vb, scans, shape):
+    """CrossScan.backward is CrossMerge.forward and vice versa (csm_triton.py:207-225, 248-273)."""
+    if scans == 3 and shape[2] != shape[3]:
+        pytest.skip("rotations need square maps")
+    rng = np.random.default_rng(scans)
+    Bt, Cc, H, W = shape
+    x = rng.standard_normal(shape, dtype=np.float32)
+    gy = rng.standard_normal((Bt, 4, Cc, H * W), dtype=np.float32)
+    xt = dev(x).requires_grad_(True)
+    ys = vb.cross_scan_fn(xt, True, True, False, scans)
+    ys.backward(dev(gy))
+    assert np.array_equal(host(xt.grad).reshape(Bt, Cc, H * W), O.cross_merge(gy.reshape(Bt, 4, Cc, H, W), scans))
+    yt = dev(gy.reshape(Bt, 4, Cc, H, W)).requires_grad_(True)
+    gm = rng.standard_normal((Bt, Cc, H * W), dtype=np.float32)
+    m = vb.cross_merge_fn(yt, True, True, False, scans)
+    m.backward(dev(gm))
+    assert np.array_equal(host(yt.grad).reshape(Bt, 4, Cc, H * W), O.cross_scan(gm.reshape(Bt, Cc, H, W), scans))

@@ -29,6 +29,18 @@ class ScanParams(ctypes.Structure):
                                     "C_batch_stride", "C_group_stride", "C_state_stride")]
 
 
+class ScanBwdParams(ctypes.Structure):
+    _fields_ = [(n, _vp) for n in ("u", "delta", "A", "B", "C", "D", "delta_bias", "dout",
+                                   "du", "ddelta", "dA", "dB", "dC", "dD", "ddelta_bias", "workspace")] + \
+               [("workspace_bytes", _i64)] + \
+               [(n, _i32) for n in ("in_dtype", "dout_dtype", "delta_softplus", "reserved0")] + \
+               [(n, _i64) for n in ("batch", "dim", "dstate", "seqlen", "n_groups",
+                                    "u_batch_stride", "u_dim_stride", "delta_batch_stride", "delta_dim_stride",
+                                    "dout_batch_stride", "dout_dim_stride",
+                                    "B_batch_stride", "B_group_stride", "B_state_stride",
+                                    "C_batch_stride", "C_group_stride", "C_state_stride")]
+
+
 class CrossParams(ctypes.Structure):
     _fields_ = [("in_", _vp), ("out", _vp), ("dtype", _i32), ("scans", _i32),
                 ("B", _i64), ("C", _i64), ("H", _i64), ("W", _i64)]
@@ -70,6 +82,8 @@ class NormParams(ctypes.Structure):
 EXPORTS = {
     # name: (restype, argtypes)
     "ss2d_selective_scan_fwd": (ctypes.c_int, [ctypes.POINTER(ScanParams), _vp]),
+    "ss2d_selective_scan_bwd": (ctypes.c_int, [ctypes.POINTER(ScanBwdParams), _vp]),
+    "ss2d_selective_scan_bwd_workspace_bytes": (_i64, [ctypes.POINTER(ScanBwdParams)]),
     "ss2d_cross_scan": (ctypes.c_int, [ctypes.POINTER(CrossParams), _vp]),
     "ss2d_cross_merge": (ctypes.c_int, [ctypes.POINTER(CrossParams), _vp]),
     "ss2d_core_workspace_bytes": (_i64, [ctypes.POINTER(CoreParams)]),

@@ -5,6 +5,8 @@
 
 namespace ss2d {
 int selective_scan_fwd(const ss2d_scan_params* p, cudaStream_t st);
+int selective_scan_bwd(const ss2d_scan_bwd_params* p, cudaStream_t st);
+long long selective_scan_bwd_workspace_bytes(const ss2d_scan_bwd_params* p);
 int cross_scan(const ss2d_cross_params* p, cudaStream_t st);
 int cross_merge(const ss2d_cross_params* p, cudaStream_t st);
 int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st);
@@ -26,6 +28,10 @@ extern "C" {
 int ss2d_selective_scan_fwd(const ss2d_scan_params* p, void* stream) {
     return ss2d::selective_scan_fwd(p, (cudaStream_t)stream);
 }
+int ss2d_selective_scan_bwd(const ss2d_scan_bwd_params* p, void* stream) {
+    return ss2d::selective_scan_bwd(p, (cudaStream_t)stream);
+}
+int64_t ss2d_selective_scan_bwd_workspace_bytes(const ss2d_scan_bwd_params* p) { return ss2d::selective_scan_bwd_workspace_bytes(p); }
 int ss2d_cross_scan(const ss2d_cross_params* p, void* stream) { return ss2d::cross_scan(p, (cudaStream_t)stream); }
 int ss2d_cross_merge(const ss2d_cross_params* p, void* stream) { return ss2d::cross_merge(p, (cudaStream_t)stream); }
 int ss2d_layer_norm_cf(const ss2d_norm_params* p, void* stream) { return ss2d::layer_norm_cf(p, (cudaStream_t)stream); }

@@ -1,0 +1,390 @@
+// Selective-scan backward, operator surface: gradients of every input of selective_scan_fwd.
+//
+// With d' = softplus(delta + bias), a = exp(d' A), h_l = a_l h_{l-1} + d'_l B_l u_l and
+// y_l = C_l . h_l + D u_l, an upstream gradient g = dout gives
+//     dh_l  = C_l g_l + e_{l+1},   e_l = a_l dh_l                  (reverse recurrence, e_L = 0)
+//     dC_l  = sum over the channels of a group of g_l h_l
+//     dB_l  = sum over the channels of a group of dh_l d'_l u_l
+//     du_l  = g_l D + d'_l sum_n B_l dh_l          dD    = sum_{b,l} g_l u_l
+//     dd'_l = sum_n dh_l (B_l u_l + A a_l h_{l-1})  dA_n  = sum_{b,l} dh_l d'_l a_l h_{l-1}
+//     ddelta_l = dd'_l * sigmoid(delta_l + bias) (1 above softplus' threshold 20),  dbias = sum_{b,l} ddelta_l
+//
+// Mapping: as in the forward kernel one warp owns one row (b, r) and walks it in steps of 32*VEC
+// elements, a lane holding VEC consecutive elements.  The warps of a CTA own rows of the SAME
+// (image, group), so that their contributions to dB / dC (which are shared by the channels of a
+// group) are summed inside the CTA, in a fixed order, through shared memory.
+//   pass 1 (forward over the row): the state entering every step is recomputed and kept in shared
+//           memory (nothing is saved by the forward kernel);
+//   pass 2 (backward over the steps): within a step the states h come from a forward shuffle scan
+//           started at the saved state, e from a backward shuffle scan started at the carry of the
+//           step after; every gradient of the step follows elementwise.
+// Sums that cross CTAs (dB / dC over the CTAs of a group, dA / dD / dbias over the batch) go to an
+// fp32 workspace as partials and are folded by a second kernel in a fixed order: no atomics, the
+// result is bit-identical from run to run.
+#include "common.cuh"
+
+namespace ss2d {
+
+struct BwdArgs {
+    const void *u, *delta, *B, *C, *dout;
+    const float *A, *D, *bias;
+    void *du, *ddelta;
+    float* rowred;      // (batch, dim, N + 2): dA partials, dD, dbias of one row
+    float* bcpart;      // (batch, n_groups, parts, 2, N, L): dB then dC partials of one CTA
+    int64_t dim, seqlen, group_size;
+    int64_t u_bs, u_ds, d_bs, d_ds, g_bs, g_ds;
+    int64_t B_bs, B_gs, B_ss, C_bs, C_gs, C_ss;
+    int N, n_groups, parts, nsteps, softplus;
+};
+
+template <typename Tin, typename Tg, int VEC>
+__global__ void __launch_bounds__(256) selscan_bwd_kernel(const BwdArgs a) {
+    extern __shared__ float sm[];
+    constexpr int STEP = 32 * VEC;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, RW = blockDim.x >> 5;
+    const int N = a.N, L = (int)a.seqlen, nsteps = a.nsteps;
+    int cta = blockIdx.x;
+    const int part = cta % a.parts; cta /= a.parts;
+    const int k = cta % a.n_groups;
+    const int64_t b = cta / a.n_groups;
+    const int64_t in_group = (int64_t)part * RW + warp;
+    const bool valid = in_group < a.group_size;
+    const int64_t r = (int64_t)k * a.group_size + (valid ? in_group : 0);
+
+    float* hstart = sm + (size_t)warp * nsteps * N;                        // [RW][nsteps][N]
+    float* carry = sm + (size_t)RW * nsteps * N + (size_t)warp * N;         // [RW][N]
+    float* A_s = sm + (size_t)RW * (nsteps + 1) * N + (size_t)warp * N;     // [RW][N]
+    float* dA_s = sm + (size_t)RW * (nsteps + 2) * N + (size_t)warp * N;    // [RW][N]
+    float* red = sm + (size_t)RW * (nsteps + 3) * N;                        // [RW][2][STEP]
+
+    const Tin* __restrict__ u = (const Tin*)a.u + b * a.u_bs + r * a.u_ds;
+    const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + r * a.d_ds;
+    const Tg* __restrict__ gp = (const Tg*)a.dout + b * a.g_bs + r * a.g_ds;
+    const Tin* __restrict__ Bm = (const Tin*)a.B + b * a.B_bs + k * a.B_gs;
+    const Tin* __restrict__ Cm = (const Tin*)a.C + b * a.C_bs + k * a.C_gs;
+    Tin* __restrict__ du = (Tin*)a.du + (b * a.dim + r) * L;
+    Tin* __restrict__ dd = (Tin*)a.ddelta + (b * a.dim + r) * L;
+    const bool has_D = a.D != nullptr;
+    const float Dv = has_D ? __ldg(a.D + r) : 0.f;
+    const float bias = a.bias ? __ldg(a.bias + r) : 0.f;
+    const bool sp = a.softplus != 0;
+    using VI = Vec<Tin, VEC>;
+    using VG = Vec<Tg, VEC>;
+
+    for (int n = lane; n < N; n += 32) {
+        carry[n] = 0.f; dA_s[n] = 0.f;
+        A_s[n] = __ldg(a.A + r * N + n);
+    }
+    __syncwarp();
+
+    // ---- pass 1: the state entering every step ---------------------------------------------------
+    for (int s = 0; s < nsteps; ++s) {
+        const int pos = s * STEP + lane * VEC;
+        const bool in = valid && pos < L;
+        float uv[VEC], dl[VEC];
+        if (in) { VI::load(u + pos, uv); VI::load(dt + pos, dl); }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            if (in) { float d = dl[i] + bias; if (sp) d = softplus_fast(d); dl[i] = d; uv[i] *= d; }
+            else { dl[i] = 0.f; uv[i] = 0.f; }
+        }
+        for (int n = 0; n < N; ++n) {
+            float bv[VEC];
+            if (in) VI::load(Bm + n * a.B_ss + pos, bv);
+            const float A2 = A_s[n] * kLog2e;
+            float p = 1.f, h = 0.f;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                const float aa = in ? decay_fast(dl[i], A2) : 1.f;
+                h = fmaf(aa, h, in ? uv[i] * bv[i] : 0.f);
+                p *= aa;
+            }
+            const AB inc = warp_scan_inclusive(AB{p, h}, lane);
+            const float ta = __shfl_sync(0xffffffffu, inc.a, 31), tb = __shfl_sync(0xffffffffu, inc.b, 31);
+            const float hc = carry[n];
+            __syncwarp();
+            if (lane == 0) { hstart[s * N + n] = hc; carry[n] = fmaf(ta, hc, tb); }
+            __syncwarp();
+        }
+    }
+    for (int n = lane; n < N; n += 32) carry[n] = 0.f;     // from here on: e entering the step from behind
+    __syncwarp();
+
+    // ---- pass 2: backwards over the steps ----------------------------------------------------------
+    float dD_acc = 0.f, dbias_acc = 0.f;
+    float* bc_out = a.bcpart + (((size_t)b * a.n_groups + k) * a.parts + part) * 2 * (size_t)N * L;
+    for (int s = nsteps - 1; s >= 0; --s) {
+        const int pos = s * STEP + lane * VEC;
+        const bool in = valid && pos < L;
+        float uv[VEC], dl[VEC], gv[VEC], dsp[VEC], du_acc[VEC], ddl[VEC];
+        if (in) { VI::load(u + pos, uv); VI::load(dt + pos, dl); VG::load(gp + pos, gv); }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            if (in) {
+                float x = dl[i] + bias;
+                dsp[i] = 1.f;
+                if (sp) {
+                    dsp[i] = x > 20.f ? 1.f : 1.f / (1.f + expf(-x));
+                    x = softplus_fast(x);
+                }
+                dl[i] = x;
+            } else { dl[i] = 0.f; uv[i] = 0.f; gv[i] = 0.f; dsp[i] = 0.f; }
+            du_acc[i] = has_D ? gv[i] * Dv : 0.f;
+            ddl[i] = 0.f;
+            dD_acc = fmaf(gv[i], uv[i], dD_acc);
+        }
+        for (int n = 0; n < N; ++n) {
+            float bv[VEC], cv[VEC], av[VEC], P[VEC], hl[VEC], Q[VEC], El[VEC];
+            if (in) { VI::load(Bm + n * a.B_ss + pos, bv); VI::load(Cm + n * a.C_ss + pos, cv); }
+            else {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) { bv[i] = 0.f; cv[i] = 0.f; }
+            }
+            const float An = A_s[n], A2 = An * kLog2e;
+            float p = 1.f, h = 0.f;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                av[i] = in ? decay_fast(dl[i], A2) : 1.f;
+                h = fmaf(av[i], h, dl[i] * uv[i] * bv[i]);
+                p *= av[i];
+                P[i] = p; hl[i] = h;
+            }
+            float q = 1.f, e = 0.f;
+#pragma unroll
+            for (int i = VEC - 1; i >= 0; --i) {
+                e = av[i] * fmaf(cv[i], gv[i], e);
+                q *= av[i];
+                Q[i] = q; El[i] = e;
+            }
+            const AB fi = warp_scan_inclusive(AB{p, h}, lane);
+            const AB ri = warp_scan_inclusive_rev(AB{q, e}, lane);
+            float ea = __shfl_up_sync(0xffffffffu, fi.a, 1), eb = __shfl_up_sync(0xffffffffu, fi.b, 1);
+            if (lane == 0) { ea = 1.f; eb = 0.f; }
+            float ra = __shfl_down_sync(0xffffffffu, ri.a, 1), rb = __shfl_down_sync(0xffffffffu, ri.b, 1);
+            if (lane == 31) { ra = 1.f; rb = 0.f; }
+            const float hin = fmaf(ea, hstart[s * N + n], eb);       // h just before this lane's first element
+            const float ec = carry[n];
+            const float ein = fmaf(ra, ec, rb);                      // e just after this lane's last element
+            const float ca = __shfl_sync(0xffffffffu, ri.a, 0), cb = __shfl_sync(0xffffffffu, ri.b, 0);
+            __syncwarp();
+            if (lane == 0) carry[n] = fmaf(ca, ec, cb);
+            float dBv[VEC], dCv[VEC], dA_loc = 0.f;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                const float hprev = (i == 0) ? hin : fmaf(P[i > 0 ? i - 1 : 0], hin, hl[i > 0 ? i - 1 : 0]);
+                const float hi = fmaf(P[i], hin, hl[i]);
+                const float enext = (i + 1 < VEC) ? fmaf(Q[i + 1 < VEC ? i + 1 : i], ein, El[i + 1 < VEC ? i + 1 : i]) : ein;
+                const float dh = fmaf(cv[i], gv[i], enext);
+                dCv[i] = gv[i] * hi;
+                dBv[i] = dh * dl[i] * uv[i];
+                du_acc[i] = fmaf(dh * dl[i], bv[i], du_acc[i]);
+                const float t = av[i] * hprev;
+                ddl[i] = fmaf(dh, fmaf(An, t, bv[i] * uv[i]), ddl[i]);
+                dA_loc = fmaf(dh * dl[i], t, dA_loc);
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) dA_loc += __shfl_xor_sync(0xffffffffu, dA_loc, off);
+            if (lane == 0) dA_s[n] += dA_loc;
+            // sum of the CTA's rows for this (step, state), in warp order
+            float* my = red + (size_t)warp * 2 * STEP + lane * VEC;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) { my[i] = in ? dBv[i] : 0.f; my[STEP + i] = in ? dCv[i] : 0.f; }
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < 2 * STEP; idx += blockDim.x) {
+                const int which = idx / STEP, el = idx - which * STEP;
+                const int gpos = s * STEP + el;
+                if (gpos < L) {
+                    float acc = 0.f;
+                    for (int w = 0; w < RW; ++w) acc += red[(size_t)w * 2 * STEP + idx];
+                    bc_out[((size_t)which * N + n) * L + gpos] = acc;
+                }
+            }
+            __syncthreads();
+        }
+        if (in) {
+            float dv[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) { dv[i] = ddl[i] * dsp[i]; dbias_acc += dv[i]; }
+            VI::store(du + pos, du_acc);
+            VI::store(dd + pos, dv);
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        dD_acc += __shfl_xor_sync(0xffffffffu, dD_acc, off);
+        dbias_acc += __shfl_xor_sync(0xffffffffu, dbias_acc, off);
+    }
+    __syncwarp();
+    if (valid) {
+        float* rr = a.rowred + (b * a.dim + r) * (N + 2);
+        for (int n = lane; n < N; n += 32) rr[n] = dA_s[n];
+        if (lane == 0) { rr[N] = dD_acc; rr[N + 1] = dbias_acc; }
+    }
+}
+
+// Folds the partials: dA / dD / dbias over the batch, dB / dC over the CTAs of a group (and rounds
+// them to the storage type).  One thread per output element, fixed summation order.
+template <typename Tin>
+__global__ void selscan_bwd_fold_kernel(const float* rowred, const float* bcpart, float* dA, float* dD, float* dbias,
+                                        Tin* dB, Tin* dC, int64_t batch, int64_t dim, int N, int64_t L,
+                                        int n_groups, int parts) {
+    const int64_t n_small = dim * (N + 2);
+    const int64_t n_bc = batch * n_groups * N * L;       // per tensor
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_small + 2 * n_bc;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        if (i < n_small) {
+            const int64_t r = i / (N + 2);
+            const int j = (int)(i - r * (N + 2));
+            float acc = 0.f;
+            for (int64_t b = 0; b < batch; ++b) acc += rowred[(b * dim + r) * (N + 2) + j];
+            if (j < N) dA[r * N + j] = acc;
+            else if (j == N) { if (dD) dD[r] = acc; }
+            else if (dbias) dbias[r] = acc;
+        } else {
+            int64_t q = i - n_small;
+            const int which = q >= n_bc;
+            if (which) q -= n_bc;
+            const int64_t l = q % L; int64_t t = q / L;
+            const int n = (int)(t % N); t /= N;                 // t = b * n_groups + k
+            const float* src = bcpart + ((size_t)t * parts * 2 + which) * (size_t)N * L + (size_t)n * L + l;
+            float acc = 0.f;
+            for (int pq = 0; pq < parts; ++pq) acc += src[(size_t)pq * 2 * N * L];
+            (which ? dC : dB)[q] = from_f<Tin>(acc);
+        }
+    }
+}
+
+struct BwdPlan { int vec, rw, parts, nsteps; size_t smem; int64_t ws_floats, rowred_floats; };
+
+static int common_pow2b(std::initializer_list<int64_t> xs, int cap) {
+    int v = cap;
+    for (int64_t x : xs) {
+        if (x < 0) x = -x;
+        while (v > 1 && (x % v) != 0) v >>= 1;
+    }
+    return v;
+}
+
+static int validate_bwd(const ss2d_scan_bwd_params* p) {
+    if (!p) return SS2D_EINVAL_NULL;
+    if (!p->u || !p->delta || !p->A || !p->B || !p->C || !p->dout || !p->du || !p->ddelta || !p->dA || !p->dB || !p->dC)
+        return SS2D_EINVAL_NULL;
+    if ((p->D != nullptr) != (p->dD != nullptr) || (p->delta_bias != nullptr) != (p->ddelta_bias != nullptr)) return SS2D_EINVAL_NULL;
+    if (!dtype_ok(p->in_dtype) || !dtype_ok(p->dout_dtype)) return SS2D_EINVAL_DTYPE;
+    if (p->dout_dtype != SS2D_F32 && p->dout_dtype != p->in_dtype) return SS2D_EINVAL_DTYPE;
+    if (p->batch <= 0 || p->dim <= 0 || p->dstate <= 0 || p->seqlen <= 0 || p->n_groups <= 0) return SS2D_EINVAL_SHAPE;
+    if (p->dstate > SS2D_MAX_DSTATE) return SS2D_ENOTSUP;
+    if (p->dim % p->n_groups != 0) return SS2D_EINVAL_SHAPE;
+    if (p->seqlen > 0x3fffffffLL) return SS2D_ENOTSUP;
+    const int64_t L = p->seqlen;
+    if (p->u_dim_stride < L || p->delta_dim_stride < L || p->dout_dim_stride < L) return SS2D_EINVAL_STRIDE;
+    if (p->B_state_stride < L || p->C_state_stride < L) return SS2D_EINVAL_STRIDE;
+    if (p->batch > 1 && (p->u_batch_stride < L || p->delta_batch_stride < L || p->dout_batch_stride < L ||
+                         p->B_batch_stride < L || p->C_batch_stride < L)) return SS2D_EINVAL_STRIDE;
+    if (p->n_groups > 1 && (p->B_group_stride < L || p->C_group_stride < L)) return SS2D_EINVAL_STRIDE;
+    const size_t si = dtype_size(p->in_dtype), sg = dtype_size(p->dout_dtype);
+    if (!aligned_to(p->u, si) || !aligned_to(p->delta, si) || !aligned_to(p->B, si) || !aligned_to(p->C, si) ||
+        !aligned_to(p->dout, sg) || !aligned_to(p->du, si) || !aligned_to(p->ddelta, si) || !aligned_to(p->dB, si) ||
+        !aligned_to(p->dC, si) || !aligned_to(p->A, 4) || !aligned_to(p->D, 4) || !aligned_to(p->delta_bias, 4) ||
+        !aligned_to(p->dA, 4) || !aligned_to(p->dD, 4) || !aligned_to(p->ddelta_bias, 4))
+        return SS2D_EINVAL_ALIGN;
+    return SS2D_OK;
+}
+
+static int plan_bwd(const ss2d_scan_bwd_params* p, BwdPlan& c) {
+    const size_t si = dtype_size(p->in_dtype), sg = dtype_size(p->dout_dtype);
+    const int64_t L = p->seqlen;
+    auto ptr_el = [](const void* q, size_t s) { return (int64_t)(reinterpret_cast<uintptr_t>(q) / s); };
+    const int cap = (si == 2) ? 8 : 4;
+    c.vec = common_pow2b({L, p->u_batch_stride, p->u_dim_stride, p->delta_batch_stride, p->delta_dim_stride,
+                          p->dout_batch_stride, p->dout_dim_stride, p->B_batch_stride, p->B_group_stride, p->B_state_stride,
+                          p->C_batch_stride, p->C_group_stride, p->C_state_stride, ptr_el(p->u, si), ptr_el(p->delta, si),
+                          ptr_el(p->B, si), ptr_el(p->C, si), ptr_el(p->dout, sg), ptr_el(p->du, si), ptr_el(p->ddelta, si)}, cap);
+    const int64_t step = 32 * c.vec;
+    c.nsteps = (int)((L + step - 1) / step);
+    const int64_t gs = p->dim / p->n_groups;
+    int rw = 8;
+    while (rw > 1 && rw / 2 >= gs) rw >>= 1;
+    auto smem_of = [&](int w) { return ((size_t)w * (c.nsteps + 3) * p->dstate + (size_t)w * 2 * step) * sizeof(float); };
+    while (rw > 1 && smem_of(rw) > 160 * 1024) rw >>= 1;
+    if (smem_of(rw) > 160 * 1024) return SS2D_ENOTSUP;      // row too long for the saved step states
+    c.rw = rw; c.smem = smem_of(rw);
+    c.parts = (int)((gs + rw - 1) / rw);
+    c.rowred_floats = p->batch * p->dim * (p->dstate + 2);
+    c.ws_floats = c.rowred_floats + p->batch * p->n_groups * c.parts * 2 * p->dstate * L;
+    return SS2D_OK;
+}
+
+long long selective_scan_bwd_workspace_bytes(const ss2d_scan_bwd_params* p) {
+    if (validate_bwd(p) != SS2D_OK) return -1;
+    BwdPlan c;
+    if (plan_bwd(p, c) != SS2D_OK) return -1;
+    return (long long)c.ws_floats * 4;
+}
+
+template <typename Tin, typename Tg, int VEC>
+static int launch_bwd(const BwdArgs& a, const BwdPlan& c, int64_t ctas, cudaStream_t st) {
+    auto kern = selscan_bwd_kernel<Tin, Tg, VEC>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem) != cudaSuccess) return SS2D_ECUDA;
+    kern<<<(unsigned)ctas, c.rw * 32, c.smem, st>>>(a);
+    count_launch();
+    return check_launch();
+}
+
+template <typename Tin, typename Tg>
+static int dispatch_bwd(const BwdArgs& a, const BwdPlan& c, int64_t ctas, cudaStream_t st) {
+    if constexpr (sizeof(Tin) == 2) {
+        if (c.vec >= 8) return launch_bwd<Tin, Tg, 8>(a, c, ctas, st);
+    }
+    if (c.vec >= 4) return launch_bwd<Tin, Tg, 4>(a, c, ctas, st);
+    if (c.vec >= 2) return launch_bwd<Tin, Tg, 2>(a, c, ctas, st);
+    return launch_bwd<Tin, Tg, 1>(a, c, ctas, st);
+}
+
+template <typename Tin>
+static int launch_fold(const ss2d_scan_bwd_params* p, const BwdArgs& a, const BwdPlan& c, cudaStream_t st) {
+    const int64_t total = p->dim * (p->dstate + 2) + 2 * p->batch * p->n_groups * p->dstate * p->seqlen;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    selscan_bwd_fold_kernel<Tin><<<(unsigned)blocks, 256, 0, st>>>(a.rowred, a.bcpart, (float*)p->dA, (float*)p->dD,
+                                                                  (float*)p->ddelta_bias, (Tin*)p->dB, (Tin*)p->dC, p->batch,
+                                                                  p->dim, (int)p->dstate, p->seqlen, (int)p->n_groups, c.parts);
+    count_launch();
+    return check_launch();
+}
+
+int selective_scan_bwd(const ss2d_scan_bwd_params* p, cudaStream_t st) {
+    const int rc = validate_bwd(p);
+    if (rc != SS2D_OK) return rc;
+    BwdPlan c;
+    const int pr = plan_bwd(p, c);
+    if (pr != SS2D_OK) return pr;
+    if (!p->workspace || p->workspace_bytes < (long long)c.ws_floats * 4) return SS2D_EWORKSPACE;
+    if (!aligned_to(p->workspace, 16)) return SS2D_EINVAL_ALIGN;
+    BwdArgs a;
+    a.u = p->u; a.delta = p->delta; a.B = p->B; a.C = p->C; a.dout = p->dout;
+    a.A = (const float*)p->A; a.D = (const float*)p->D; a.bias = (const float*)p->delta_bias;
+    a.du = p->du; a.ddelta = p->ddelta;
+    a.rowred = (float*)p->workspace; a.bcpart = a.rowred + c.rowred_floats;
+    a.dim = p->dim; a.seqlen = p->seqlen; a.group_size = p->dim / p->n_groups;
+    a.u_bs = p->u_batch_stride; a.u_ds = p->u_dim_stride; a.d_bs = p->delta_batch_stride; a.d_ds = p->delta_dim_stride;
+    a.g_bs = p->dout_batch_stride; a.g_ds = p->dout_dim_stride;
+    a.B_bs = p->B_batch_stride; a.B_gs = p->B_group_stride; a.B_ss = p->B_state_stride;
+    a.C_bs = p->C_batch_stride; a.C_gs = p->C_group_stride; a.C_ss = p->C_state_stride;
+    a.N = (int)p->dstate; a.n_groups = (int)p->n_groups; a.parts = c.parts; a.nsteps = c.nsteps; a.softplus = p->delta_softplus;
+    const int64_t ctas = p->batch * p->n_groups * c.parts;
+    if (ctas > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
+    const bool gf32 = p->dout_dtype == SS2D_F32;
+    int r;
+    if (p->in_dtype == SS2D_F32) r = dispatch_bwd<float, float>(a, c, ctas, st);
+    else if (p->in_dtype == SS2D_BF16)
+        r = gf32 ? dispatch_bwd<__nv_bfloat16, float>(a, c, ctas, st) : dispatch_bwd<__nv_bfloat16, __nv_bfloat16>(a, c, ctas, st);
+    else
+        r = gf32 ? dispatch_bwd<__half, float>(a, c, ctas, st) : dispatch_bwd<__half, __half>(a, c, ctas, st);
+    if (r != SS2D_OK) return r;
+    if (p->in_dtype == SS2D_F32) return launch_fold<float>(p, a, c, st);
+    if (p->in_dtype == SS2D_BF16) return launch_fold<__nv_bfloat16>(p, a, c, st);
+    return launch_fold<__half>(p, a, c, st);
+}
+
+}  // namespace ss2d

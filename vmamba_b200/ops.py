@@ -14,7 +14,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from ._lib import CrossParams, NormParams, PointwiseParams, ScanParams, check, lib
+from ._lib import ScanBwdParams, CrossParams, NormParams, PointwiseParams, ScanParams, check, lib
 
 _DTYPES = {torch.float32: _lib.SS2D_F32, torch.float16: _lib.SS2D_F16, torch.bfloat16: _lib.SS2D_BF16}
 
@@ -94,9 +94,54 @@ def selective_scan_fwd(u, delta, A, B, C, D=None, delta_bias=None, delta_softplu
     return out
 
 
+def selective_scan_bwd(u, delta, A, B, C, D, delta_bias, dout, delta_softplus=False):
+    """Gradients (du, ddelta, dA, dB, dC, dD, ddelta_bias) of `selective_scan_fwd` for the upstream
+    gradient dout (batch, dim, L), fp32 or u.dtype; dD / ddelta_bias are None where the input was None.
+    Shapes and types of the results as selective_scan_cuda_oflex.bwd returns them
+    (selective_scan_oflex.cpp:308-353)."""
+    _require_cuda(u, delta, A, B, C, D, delta_bias, dout)
+    batch, dim, L = u.shape
+    _, K, N, _ = B.shape
+    if dout.shape != u.shape:
+        raise RuntimeError(f"dout must have the shape of u, got {tuple(dout.shape)}")
+    if dout.dtype not in (torch.float32, u.dtype):
+        raise RuntimeError("dout must be fp32 or of u's dtype")
+    cont = lambda t: t if t.stride(-1) == 1 else t.contiguous()
+    u, delta, B, C, dout = cont(u), cont(delta), cont(B), cont(C), cont(dout)
+    A = A.contiguous().float()
+    D = None if D is None else D.contiguous().float()
+    delta_bias = None if delta_bias is None else delta_bias.contiguous().float()
+    du = torch.empty((batch, dim, L), device=u.device, dtype=u.dtype)
+    ddelta = torch.empty_like(du)
+    dA = torch.empty((dim, N), device=u.device, dtype=torch.float32)
+    dB = torch.empty((batch, K, N, L), device=u.device, dtype=u.dtype)
+    dC = torch.empty_like(dB)
+    dD = None if D is None else torch.empty(dim, device=u.device, dtype=torch.float32)
+    dbias = None if delta_bias is None else torch.empty(dim, device=u.device, dtype=torch.float32)
+    p = ScanBwdParams()
+    p.u, p.delta, p.A, p.B, p.C, p.D, p.delta_bias, p.dout = (_ptr(t) for t in (u, delta, A, B, C, D, delta_bias, dout))
+    p.du, p.ddelta, p.dA, p.dB, p.dC, p.dD, p.ddelta_bias = (_ptr(t) for t in (du, ddelta, dA, dB, dC, dD, dbias))
+    p.in_dtype, p.dout_dtype = dtype_code(u), dtype_code(dout)
+    p.delta_softplus = int(bool(delta_softplus))
+    p.batch, p.dim, p.dstate, p.seqlen, p.n_groups = batch, dim, N, L, K
+    p.u_batch_stride, p.u_dim_stride = u.stride(0), u.stride(1)
+    p.delta_batch_stride, p.delta_dim_stride = delta.stride(0), delta.stride(1)
+    p.dout_batch_stride, p.dout_dim_stride = dout.stride(0), dout.stride(1)
+    p.B_batch_stride, p.B_group_stride, p.B_state_stride = B.stride(0), B.stride(1), B.stride(2)
+    p.C_batch_stride, p.C_group_stride, p.C_state_stride = C.stride(0), C.stride(1), C.stride(2)
+    need = int(lib().ss2d_selective_scan_bwd_workspace_bytes(p))
+    if need < 0:
+        raise RuntimeError("ss2d_selective_scan_bwd_workspace_bytes: invalid or unsupported arguments")
+    ws = torch.empty(max(need, 16), device=u.device, dtype=torch.uint8)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    with torch.cuda.device(u.device):
+        check(lib().ss2d_selective_scan_bwd(p, _stream(u)), "ss2d_selective_scan_bwd")
+    return du, ddelta, dA, dB, dC, dD, dbias
+
+
 class SelectiveScanCuda(torch.autograd.Function):
-    """Same call signature as the reference Function (csms6s.py:71-87).  Forward only:
-    calling backward raises, this build is an inference drop-in."""
+    """Same call signature, saved tensors and gradient tuple as the reference Function
+    (csms6s.py:71-109)."""
 
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda")
@@ -108,11 +153,28 @@ class SelectiveScanCuda(torch.autograd.Function):
             raise ValueError(f"unknown selective-scan backend {backend!r}")
         ctx.delta_softplus = delta_softplus
         ctx.backend = backend
+        ctx.has_D, ctx.has_bias = D is not None, delta_bias is not None
+        saved = [u, delta, A, B, C] + ([D] if ctx.has_D else []) + ([delta_bias] if ctx.has_bias else [])
+        ctx.save_for_backward(*saved)
         return selective_scan_fwd(u, delta, A, B, C, D, delta_bias, delta_softplus, bool(oflex))
 
     @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
     def backward(ctx, dout, *args):
-        raise NotImplementedError("vmamba_b200 implements the forward (inference) path of the selective scan only")
+        saved = list(ctx.saved_tensors)
+        u, delta, A, B, C = saved[:5]
+        rest = saved[5:]
+        D = rest.pop(0) if ctx.has_D else None
+        delta_bias = rest.pop(0) if ctx.has_bias else None
+        if dout.stride(-1) != 1:
+            dout = dout.contiguous()
+        du, ddelta, dA, dB, dC, dD, dbias = selective_scan_bwd(u, delta, A, B, C, D, delta_bias, dout, ctx.delta_softplus)
+        dA = dA.to(A.dtype)
+        if dD is not None:
+            dD = dD.to(D.dtype)
+        if dbias is not None:
+            dbias = dbias.to(delta_bias.dtype)
+        return du, ddelta, dA, dB, dC, dD, dbias, None, None, None
 
 
 SelectiveScanOflex = SelectiveScanCuda   # name used by older revisions of the reference
@@ -173,23 +235,30 @@ class CrossScanF(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, in_channel_first=True, out_channel_first=True, one_by_one=False, scans=0):
         _check_flags(in_channel_first, out_channel_first, one_by_one, scans)
-        ctx.shape = x.shape
+        ctx.shape, ctx.scans = tuple(x.shape), scans
         return cross_scan_fwd(x, scans)
 
     @staticmethod
     def backward(ctx, ys):
-        raise NotImplementedError("vmamba_b200 implements the forward (inference) path of CrossScan only")
+        # the adjoint of the four-route copy is the four-route sum (csm_triton.py:207-225)
+        B, C, H, W = ctx.shape
+        ys = ys.contiguous().view(B, 4, C, H, W)
+        return cross_merge_fwd(ys, ctx.scans).view(B, C, H, W), None, None, None, None
 
 
 class CrossMergeF(torch.autograd.Function):
     @staticmethod
     def forward(ctx, ys, in_channel_first=True, out_channel_first=True, one_by_one=False, scans=0):
         _check_flags(in_channel_first, out_channel_first, one_by_one, scans)
+        ctx.shape, ctx.scans = (ys.shape[0], ys.shape[2], ys.shape[3], ys.shape[4]), scans
         return cross_merge_fwd(ys, scans)
 
     @staticmethod
     def backward(ctx, x):
-        raise NotImplementedError("vmamba_b200 implements the forward (inference) path of CrossMerge only")
+        # the adjoint of the four-route sum is the four-route copy (csm_triton.py:248-273)
+        B, C, H, W = ctx.shape
+        xs = cross_scan_fwd(x.contiguous().view(B, C, H, W), ctx.scans)
+        return xs.view(B, 4, C, H, W), None, None, None, None
 
 
 # the CUDA-backed Functions stand in for the reference's Triton Functions too
