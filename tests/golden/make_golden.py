@@ -230,6 +230,36 @@ def main():
             out[f"{tag}_sd_{k}"] = npf(v)
     np.savez_compressed(os.path.join(HERE, "ss2d_module_small.npz"), **out)
 
+    # ---- 3b. gradients of the same modules' cores: autograd through the reference's forward_core
+    #          (CrossScan -> x_proj -> dt_projs -> selective_scan_torch -> CrossMerge -> out_norm) -------
+    outg = {}
+    for tag, kw, shape in (
+        ("m0", dict(d_model=16, d_state=1, ssm_ratio=1.0), (2, 16, 9, 11)),
+        ("m1", dict(d_model=8, d_state=2, ssm_ratio=2.0), (1, 8, 6, 5)),
+    ):
+        torch.manual_seed(7)
+        m = ref.SS2D(dt_rank="auto", act_layer=torch.nn.SiLU, d_conv=3, conv_bias=False,
+                     forward_type="v05_noz", channel_first=True, initialize="v0", **kw).eval()
+        torch.nn.init.normal_(m.out_norm.weight, 1.0, 0.2)
+        torch.nn.init.normal_(m.out_norm.bias, 0.0, 0.2)
+        torch.nn.init.normal_(m.Ds, 1.0, 0.3)
+        torch.nn.init.normal_(m.A_logs, 0.0, 0.5)
+        d_inner = m.out_norm.weight.numel()
+        g = torch.Generator().manual_seed(13)
+        xc = torch.randn((shape[0], d_inner, shape[2], shape[3]), generator=g)
+        gy = torch.randn((shape[0], d_inner, shape[2], shape[3]), generator=g)
+        with torch.enable_grad():
+            xc.requires_grad_(True)
+            y = m.forward_core(xc)
+            assert y.shape == gy.shape
+            y.backward(gy)
+        outg.update({f"{tag}_core_x": npf(xc), f"{tag}_core_gy": npf(gy), f"{tag}_core_y": npf(y), f"{tag}_core_gx": npf(xc.grad)})
+        for k, v in m.named_parameters():
+            if v.grad is not None:
+                outg[f"{tag}_grad_{k}"] = npf(v.grad)
+        m.zero_grad()
+    np.savez_compressed(os.path.join(HERE, "ss2d_core_grads_small.npz"), **outg)
+
     # ---- 4. the full-size single-op workload (2,96,56,56), digests only ----------
     inp = config0_inputs(0)
     xs = ref.cross_scan_fn(inp["x"], True, True, False, 0, True)

@@ -152,3 +152,26 @@ def test_cross_scan_merge_adjoints(vb, scans, shape):
     m = vb.cross_merge_fn(yt, True, True, False, scans)
     m.backward(dev(gm))
     assert np.array_equal(host(yt.grad).reshape(Bt, 4, Cc, H * W), O.cross_scan(gm.reshape(Bt, Cc, H, W), scans))
+
+
+@pytest.mark.parametrize("tag", ["m0", "m1"])
+def test_core_training_chain_vs_reference_grads(vb, tag):
+    """Forward + backward of the whole SS2D core through this package's autograd Functions against
+    autograd through the unmodified reference module's forward_core (stored fixture): the output,
+    the input gradient and the gradient of every parameter."""
+    from vmamba_b200 import fused
+    gm = np.load(os.path.join(G, "ss2d_module_small.npz"))
+    gg = np.load(os.path.join(G, "ss2d_core_grads_small.npz"))
+    sd = {k[len(tag) + 4:]: gm[k] for k in gm.files if k.startswith(f"{tag}_sd_")}
+    N, R = int(gm[f"{tag}_d_state"]), int(gm[f"{tag}_dt_rank"])
+    names = ("x_proj.weight", "dt_projs.weight", "dt_projs_bias", "A_logs", "Ds", "out_norm.weight", "out_norm.bias")
+    params = [dev(sd[n]).requires_grad_(True) for n in names]
+    x = dev(gg[f"{tag}_core_x"]).requires_grad_(True)
+    y = fused.ss2d_core_autograd(x, *params, d_state=N, dt_rank=R)
+    assert O.max_rel_err(host(y), gg[f"{tag}_core_y"]) <= 1e-4
+    y.backward(dev(gg[f"{tag}_core_gy"]))
+    assert O.max_rel_err(host(x.grad), gg[f"{tag}_core_gx"]) <= 1e-4
+    for n, p_ in zip(names, params):
+        ref = gg[f"{tag}_grad_{n}"]
+        err = O.max_rel_err(host(p_.grad).reshape(ref.shape), ref)
+        assert err <= 1e-4, (n, err)

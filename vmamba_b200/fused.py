@@ -237,6 +237,29 @@ def _ss2d_core_unfused(x, w: CoreWeights, with_norm: bool, out_dtype):
     return y.to(out_dtype)
 
 
+def ss2d_core_autograd(x, x_proj_weight, dt_projs_weight, dt_projs_bias, A_logs, Ds, ln_weight, ln_bias, *,
+                       d_state: int, dt_rank: int, eps: float = 1e-5, oflex: bool = True):
+    """Differentiable SS2D core for training: the statements of SS2Dv2.forward_corev2
+    (vmamba.py:1536-1571) with this package's autograd Functions for CrossScan, the selective scan and
+    CrossMerge, and torch for the projections and the LayerNorm.  Gradients flow to x and to every
+    parameter; this is what a reference module computes after `vmamba_b200.install()`.
+    x: (B, D, H, W); x_proj_weight: (K*(R+2N), D) or (K, R+2N, D); dt_projs_weight: (K*D, R) or (K, D, R)."""
+    B, D, H, W = x.shape
+    L, N, R = H * W, int(d_state), int(dt_rank)
+    xs = ops.cross_scan_fn(x, True, True, False, 0)                                     # (B, K, D, L)
+    wx = x_proj_weight.reshape(K, R + 2 * N, D).to(x.dtype)
+    x_dbl = torch.einsum("bkdl,kcd->bkcl", xs.view(B, K, D, L), wx)
+    dts, Bs, Cs = torch.split(x_dbl, [R, N, N], dim=2)
+    wdt = dt_projs_weight.reshape(K, D, R).to(x.dtype)
+    dts = torch.einsum("bkrl,kdr->bkdl", dts, wdt).reshape(B, K * D, L)
+    As = -torch.exp(A_logs.float())
+    ys = ops.selective_scan_fn(xs.reshape(B, K * D, L), dts.contiguous(), As, Bs.contiguous(), Cs.contiguous(),
+                               Ds.float(), dt_projs_bias.reshape(-1).float(), True, oflex)
+    y = ops.cross_merge_fn(ys.view(B, K, D, H, W), True, True, False, 0).view(B, D, H, W)
+    y = torch.nn.functional.layer_norm(y.permute(0, 2, 3, 1), (D,), ln_weight, ln_bias, eps).permute(0, 3, 1, 2)
+    return y.to(x.dtype)
+
+
 # --------------------------------------------------------------------------------------------
 # installing the fused core into reference SS2D modules without touching their source
 # --------------------------------------------------------------------------------------------
