@@ -225,7 +225,16 @@ def op_sweep(args):
                 print(json.dumps({"op": "selective_scan_fwd", "dtype": "bf16->f32", "d_state": N, "D": D, "L": L, "batch": Bt,
                                   "ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": gbs, "frac": gbs / peak,
                                   "peak_gbs": peak, "peak_kind": f"of {kind}"}), flush=True)
-                del u, delta, Bm, Cm
+                # gradients of the same cell: reads u, delta, dout (fp32), B, C; writes du, ddelta, dB, dC
+                from vmamba_b200 import ops as _ops
+                dout = torch.randn((Bt, K * D, L), device="cuda", generator=g)
+                ms = time_events(lambda: _ops.selective_scan_bwd(u, delta, A, Bm, Cm, Dp, bias, dout, True), args.steps)
+                nbytes = Bt * L * (K * D * (2 * 2 + 4 + 2 * 2) + 4 * K * N * 2) + 4 * (2 * K * D * N + 4 * K * D)
+                gbs = nbytes / (ms * 1e-3) / 1e9
+                print(json.dumps({"op": "selective_scan_bwd", "dtype": "bf16, dout f32", "d_state": N, "D": D, "L": L, "batch": Bt,
+                                  "ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": gbs, "frac": gbs / peak,
+                                  "peak_gbs": peak, "peak_kind": f"of {kind}"}), flush=True)
+                del u, delta, Bm, Cm, dout
     for (D, H) in ((96, 56), (384, 14), (96, 256)):
         Bt = max(1, int(args.sweep_gb * 1e9 / (10 * D * H * H)))
         x = torch.randn((Bt, D, H, H), device="cuda", generator=g).to(torch.bfloat16)

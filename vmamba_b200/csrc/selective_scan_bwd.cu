@@ -222,6 +222,211 @@ __global__ void __launch_bounds__(256) selscan_bwd_kernel(const BwdArgs a) {
     }
 }
 
+// d_state 1 (every VMamba backbone): a warp walks R rows of the group per step, so that the B / C
+// vectors of the step are loaded once per warp, the dB / dC contributions of its rows are summed in
+// registers, and the CTA-wide sum (two barriers) is paid once per step for RW * R rows.  The next
+// row's u / delta / dout vectors are fetched before the current row's arithmetic.
+template <typename Tin, typename Tg, int VEC>
+__global__ void __launch_bounds__(256) selscan_bwd_n1_kernel(const BwdArgs a, const int R) {
+    extern __shared__ float sm[];
+    constexpr int STEP = 32 * VEC;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, RW = blockDim.x >> 5;
+    const int L = (int)a.seqlen, nsteps = a.nsteps;
+    int cta = blockIdx.x;
+    const int part = cta % a.parts; cta /= a.parts;
+    const int k = cta % a.n_groups;
+    const int64_t b = cta / a.n_groups;
+    const int rows_cta = RW * R;
+    // local row lr = i * RW + warp, i < R; row inside the group = part * rows_cta + lr
+    float* hstart = sm;                                   // [rows_cta][nsteps]
+    float* ecar = sm + (size_t)rows_cta * nsteps;         // [rows_cta]
+    float* racc = ecar + rows_cta;                        // [rows_cta][3][32]: per-lane partials of dA, dD, dbias
+    float* red = racc + (size_t)rows_cta * 96;            // [RW][2][STEP]
+    const bool has_D = a.D != nullptr;
+    const bool sp = a.softplus != 0;
+    using VI = Vec<Tin, VEC>;
+    using VG = Vec<Tg, VEC>;
+    const Tin* __restrict__ Bm = (const Tin*)a.B + b * a.B_bs + k * a.B_gs;
+    const Tin* __restrict__ Cm = (const Tin*)a.C + b * a.C_bs + k * a.C_gs;
+    const int64_t row0 = (int64_t)part * rows_cta;
+
+    // ---- pass 1: the state entering every step, row by row ------------------------------------------
+    for (int i = 0; i < R; ++i) {
+        const int lr = i * RW + warp;
+        const int64_t ig = row0 + lr;
+#pragma unroll
+        for (int j = 0; j < 3; ++j) racc[lr * 96 + j * 32 + lane] = 0.f;
+        if (lane == 0) ecar[lr] = 0.f;
+        if (ig >= a.group_size) continue;               // uniform over the warp
+        const int64_t r = (int64_t)k * a.group_size + ig;
+        const Tin* __restrict__ u = (const Tin*)a.u + b * a.u_bs + r * a.u_ds;
+        const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + r * a.d_ds;
+        const float A2 = __ldg(a.A + r) * kLog2e;
+        const float bias = a.bias ? __ldg(a.bias + r) : 0.f;
+        float hc = 0.f;
+        typename VI::Raw ru = {}, rd = {}, rb = {};
+        int pos = lane * VEC;
+        if (pos < L) { ru = VI::load_raw(u + pos); rd = VI::load_raw(dt + pos); rb = VI::load_raw(Bm + pos); }
+        for (int s = 0; s < nsteps; ++s) {
+            typename VI::Raw nu = {}, nd = {}, nb = {};
+            const int npos = pos + STEP;
+            if (npos < L) { nu = VI::load_raw(u + npos); nd = VI::load_raw(dt + npos); nb = VI::load_raw(Bm + npos); }
+            const bool in = pos < L;
+            float uv[VEC], dl[VEC], bv[VEC];
+            VI::unpack(ru, uv); VI::unpack(rd, dl); VI::unpack(rb, bv);
+            float p = 1.f, h = 0.f;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                float d = dl[e] + bias;
+                if (sp) d = softplus_fast(d);
+                const float aa = in ? decay_fast(d, A2) : 1.f;
+                h = fmaf(aa, h, in ? d * uv[e] * bv[e] : 0.f);
+                p *= aa;
+            }
+            const AB inc = warp_scan_inclusive(AB{p, h}, lane);
+            const float ta = __shfl_sync(0xffffffffu, inc.a, 31), tb = __shfl_sync(0xffffffffu, inc.b, 31);
+            if (lane == 0) hstart[(size_t)lr * nsteps + s] = hc;
+            hc = fmaf(ta, hc, tb);
+            ru = nu; rd = nd; rb = nb; pos = npos;
+        }
+    }
+    __syncwarp();
+
+    // ---- pass 2: backwards over the steps; inside a step over this warp's rows ------------------------
+    float* bc_out = a.bcpart + (((size_t)b * a.n_groups + k) * a.parts + part) * 2 * (size_t)L;
+    for (int s = nsteps - 1; s >= 0; --s) {
+        const int pos = s * STEP + lane * VEC;
+        const bool in_l = pos < L;
+        float bv[VEC], cv[VEC], accB[VEC], accC[VEC];
+        if (in_l) { VI::load(Bm + pos, bv); VI::load(Cm + pos, cv); }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            if (!in_l) { bv[e] = 0.f; cv[e] = 0.f; }
+            accB[e] = 0.f; accC[e] = 0.f;
+        }
+        // first row's vectors
+        typename VI::Raw ru = {}, rd = {};
+        typename VG::Raw rg = {};
+        auto fetch = [&](int i, typename VI::Raw& xu, typename VI::Raw& xd, typename VG::Raw& xg) {
+            const int64_t ig = row0 + i * RW + warp;
+            if (i < R && ig < a.group_size && in_l) {
+                const int64_t r = (int64_t)k * a.group_size + ig;
+                xu = VI::load_raw((const Tin*)a.u + b * a.u_bs + r * a.u_ds + pos);
+                xd = VI::load_raw((const Tin*)a.delta + b * a.d_bs + r * a.d_ds + pos);
+                xg = VG::load_raw((const Tg*)a.dout + b * a.g_bs + r * a.g_ds + pos);
+            }
+        };
+        fetch(0, ru, rd, rg);
+        for (int i = 0; i < R; ++i) {
+            typename VI::Raw nu = {}, nd = {};
+            typename VG::Raw ng = {};
+            fetch(i + 1, nu, nd, ng);
+            const int lr = i * RW + warp;
+            const int64_t ig = row0 + lr;
+            if (ig < a.group_size) {                    // uniform over the warp
+                const int64_t r = (int64_t)k * a.group_size + ig;
+                const float An = __ldg(a.A + r), A2 = An * kLog2e;
+                const float bias = a.bias ? __ldg(a.bias + r) : 0.f;
+                const float Dv = has_D ? __ldg(a.D + r) : 0.f;
+                float uv[VEC], dl[VEC], gv[VEC], dsp[VEC], av[VEC], P[VEC], hl[VEC], Q[VEC], El[VEC];
+                VI::unpack(ru, uv); VI::unpack(rd, dl); VG::unpack(rg, gv);
+                float p = 1.f, h = 0.f, dD_loc = 0.f;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    if (in_l) {
+                        float x = dl[e] + bias;
+                        dsp[e] = 1.f;
+                        if (sp) {
+                            dsp[e] = x > 20.f ? 1.f : 1.f / (1.f + expf(-x));
+                            x = softplus_fast(x);
+                        }
+                        dl[e] = x;
+                        av[e] = decay_fast(x, A2);
+                    } else { dl[e] = 0.f; uv[e] = 0.f; gv[e] = 0.f; dsp[e] = 0.f; av[e] = 1.f; }
+                    dD_loc = fmaf(gv[e], uv[e], dD_loc);
+                    h = fmaf(av[e], h, dl[e] * uv[e] * bv[e]);
+                    p *= av[e];
+                    P[e] = p; hl[e] = h;
+                }
+                float q = 1.f, ee = 0.f;
+#pragma unroll
+                for (int e = VEC - 1; e >= 0; --e) {
+                    ee = av[e] * fmaf(cv[e], gv[e], ee);
+                    q *= av[e];
+                    Q[e] = q; El[e] = ee;
+                }
+                const AB fi = warp_scan_inclusive(AB{p, h}, lane);
+                const AB ri = warp_scan_inclusive_rev(AB{q, ee}, lane);
+                float ea = __shfl_up_sync(0xffffffffu, fi.a, 1), eb = __shfl_up_sync(0xffffffffu, fi.b, 1);
+                if (lane == 0) { ea = 1.f; eb = 0.f; }
+                float ra = __shfl_down_sync(0xffffffffu, ri.a, 1), rb = __shfl_down_sync(0xffffffffu, ri.b, 1);
+                if (lane == 31) { ra = 1.f; rb = 0.f; }
+                const float hin = fmaf(ea, hstart[(size_t)lr * nsteps + s], eb);
+                const float ec = ecar[lr];
+                const float ein = fmaf(ra, ec, rb);
+                const float ca = __shfl_sync(0xffffffffu, ri.a, 0), cb = __shfl_sync(0xffffffffu, ri.b, 0);
+                __syncwarp();
+                if (lane == 0) ecar[lr] = fmaf(ca, ec, cb);
+                float duv[VEC], ddv[VEC], dA_loc = 0.f, db_loc = 0.f;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    const float hprev = (e == 0) ? hin : fmaf(P[e > 0 ? e - 1 : 0], hin, hl[e > 0 ? e - 1 : 0]);
+                    const float hi = fmaf(P[e], hin, hl[e]);
+                    const float enext = (e + 1 < VEC) ? fmaf(Q[e + 1 < VEC ? e + 1 : e], ein, El[e + 1 < VEC ? e + 1 : e]) : ein;
+                    const float dh = fmaf(cv[e], gv[e], enext);
+                    accC[e] = fmaf(gv[e], hi, accC[e]);
+                    const float dhd = dh * dl[e];
+                    accB[e] = fmaf(dhd, uv[e], accB[e]);
+                    duv[e] = fmaf(dhd, bv[e], has_D ? gv[e] * Dv : 0.f);
+                    const float t = av[e] * hprev;
+                    ddv[e] = dh * fmaf(An, t, bv[e] * uv[e]) * dsp[e];
+                    db_loc += ddv[e];
+                    dA_loc = fmaf(dhd, t, dA_loc);
+                }
+                float* rq = racc + lr * 96 + lane;
+                rq[0] += dA_loc; rq[32] += dD_loc; rq[64] += db_loc;
+                if (in_l) {
+                    VI::store((Tin*)a.du + (b * a.dim + r) * L + pos, duv);
+                    VI::store((Tin*)a.ddelta + (b * a.dim + r) * L + pos, ddv);
+                }
+            }
+            ru = nu; rd = nd; rg = ng;
+        }
+        float* my = red + (size_t)warp * 2 * STEP + lane * VEC;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { my[e] = accB[e]; my[STEP + e] = accC[e]; }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 2 * STEP; idx += blockDim.x) {
+            const int which = idx / STEP, el = idx - which * STEP;
+            const int gpos = s * STEP + el;
+            if (gpos < L) {
+                float acc = 0.f;
+                for (int w = 0; w < RW; ++w) acc += red[(size_t)w * 2 * STEP + idx];
+                bc_out[(size_t)which * L + gpos] = acc;
+            }
+        }
+        __syncthreads();
+    }
+    // ---- per-row sums ------------------------------------------------------------------------------------
+    for (int i = 0; i < R; ++i) {
+        const int lr = i * RW + warp;
+        const int64_t ig = row0 + lr;
+        if (ig >= a.group_size) continue;
+        const int64_t r = (int64_t)k * a.group_size + ig;
+        float v0 = racc[lr * 96 + lane], v1 = racc[lr * 96 + 32 + lane], v2 = racc[lr * 96 + 64 + lane];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            v0 += __shfl_xor_sync(0xffffffffu, v0, off);
+            v1 += __shfl_xor_sync(0xffffffffu, v1, off);
+            v2 += __shfl_xor_sync(0xffffffffu, v2, off);
+        }
+        if (lane == 0) {
+            float* rr = a.rowred + (b * a.dim + r) * 3;
+            rr[0] = v0; rr[1] = v1; rr[2] = v2;
+        }
+    }
+}
+
 // Folds the partials: dA / dD / dbias over the batch, dB / dC over the CTAs of a group (and rounds
 // them to the storage type).  One thread per output element, fixed summation order.
 template <typename Tin>
@@ -254,7 +459,7 @@ __global__ void selscan_bwd_fold_kernel(const float* rowred, const float* bcpart
     }
 }
 
-struct BwdPlan { int vec, rw, parts, nsteps; size_t smem; int64_t ws_floats, rowred_floats; };
+struct BwdPlan { int vec, rw, parts, nsteps, R; size_t smem; int64_t ws_floats, rowred_floats; };
 
 static int common_pow2b(std::initializer_list<int64_t> xs, int cap) {
     int v = cap;
@@ -295,7 +500,7 @@ static int plan_bwd(const ss2d_scan_bwd_params* p, BwdPlan& c) {
     const size_t si = dtype_size(p->in_dtype), sg = dtype_size(p->dout_dtype);
     const int64_t L = p->seqlen;
     auto ptr_el = [](const void* q, size_t s) { return (int64_t)(reinterpret_cast<uintptr_t>(q) / s); };
-    const int cap = (si == 2) ? 8 : 4;
+    const int cap = 4;     // four elements per lane: 80 registers, three CTAs per SM; eight-wide was slower (one CTA per SM)
     c.vec = common_pow2b({L, p->u_batch_stride, p->u_dim_stride, p->delta_batch_stride, p->delta_dim_stride,
                           p->dout_batch_stride, p->dout_dim_stride, p->B_batch_stride, p->B_group_stride, p->B_state_stride,
                           p->C_batch_stride, p->C_group_stride, p->C_state_stride, ptr_el(p->u, si), ptr_el(p->delta, si),
@@ -308,8 +513,22 @@ static int plan_bwd(const ss2d_scan_bwd_params* p, BwdPlan& c) {
     auto smem_of = [&](int w) { return ((size_t)w * (c.nsteps + 3) * p->dstate + (size_t)w * 2 * step) * sizeof(float); };
     while (rw > 1 && smem_of(rw) > 160 * 1024) rw >>= 1;
     if (smem_of(rw) > 160 * 1024) return SS2D_ENOTSUP;      // row too long for the saved step states
-    c.rw = rw; c.smem = smem_of(rw);
+    c.rw = rw; c.smem = smem_of(rw); c.R = 1;
     c.parts = (int)((gs + rw - 1) / rw);
+    if (p->dstate == 1) {
+        // rows per warp: as many as keep about two CTAs per SM busy and the saved states in shared memory
+        auto smem_n1 = [&](int w, int R) { return ((size_t)w * R * (c.nsteps + 1 + 96) + (size_t)w * 2 * step) * sizeof(float); };
+        int R = 1;
+        while (R < 16 && (int64_t)rw * R < gs) {
+            const int R2 = R * 2;
+            const int64_t parts2 = (gs + (int64_t)rw * R2 - 1) / ((int64_t)rw * R2);
+            if (p->batch * p->n_groups * parts2 < 2 * 148 || smem_n1(rw, R2) > 100 * 1024) break;
+            R = R2;
+        }
+        if (smem_n1(rw, R) > 200 * 1024) return SS2D_ENOTSUP;
+        c.R = R; c.smem = smem_n1(rw, R);
+        c.parts = (int)((gs + (int64_t)rw * R - 1) / ((int64_t)rw * R));
+    }
     c.rowred_floats = p->batch * p->dim * (p->dstate + 2);
     c.ws_floats = c.rowred_floats + p->batch * p->n_groups * c.parts * 2 * p->dstate * L;
     return SS2D_OK;
@@ -324,18 +543,21 @@ long long selective_scan_bwd_workspace_bytes(const ss2d_scan_bwd_params* p) {
 
 template <typename Tin, typename Tg, int VEC>
 static int launch_bwd(const BwdArgs& a, const BwdPlan& c, int64_t ctas, cudaStream_t st) {
-    auto kern = selscan_bwd_kernel<Tin, Tg, VEC>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem) != cudaSuccess) return SS2D_ECUDA;
-    kern<<<(unsigned)ctas, c.rw * 32, c.smem, st>>>(a);
+    if (a.N == 1) {
+        auto kern = selscan_bwd_n1_kernel<Tin, Tg, VEC>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem) != cudaSuccess) return SS2D_ECUDA;
+        kern<<<(unsigned)ctas, c.rw * 32, c.smem, st>>>(a, c.R);
+    } else {
+        auto kern = selscan_bwd_kernel<Tin, Tg, VEC>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem) != cudaSuccess) return SS2D_ECUDA;
+        kern<<<(unsigned)ctas, c.rw * 32, c.smem, st>>>(a);
+    }
     count_launch();
     return check_launch();
 }
 
 template <typename Tin, typename Tg>
 static int dispatch_bwd(const BwdArgs& a, const BwdPlan& c, int64_t ctas, cudaStream_t st) {
-    if constexpr (sizeof(Tin) == 2) {
-        if (c.vec >= 8) return launch_bwd<Tin, Tg, 8>(a, c, ctas, st);
-    }
     if (c.vec >= 4) return launch_bwd<Tin, Tg, 4>(a, c, ctas, st);
     if (c.vec >= 2) return launch_bwd<Tin, Tg, 2>(a, c, ctas, st);
     return launch_bwd<Tin, Tg, 1>(a, c, ctas, st);
