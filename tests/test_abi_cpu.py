@@ -142,11 +142,42 @@ def test_install_patches_a_reference_like_module():
         vb.preseed_sys_modules()
         assert sys.modules["csms6s"].selective_scan_fn is ops.selective_scan_fn
         assert sys.modules["csm_triton"].cross_scan_fn is ops.cross_scan_fn
+        assert sys.modules["csms6s"].flops_selective_scan_fn is ops.flops_selective_scan_fn
     finally:
         for k, v in saved.items():
             sys.modules.pop(k, None)
             if v is not None:
                 sys.modules[k] = v
+    saved = sys.modules.pop("selective_scan_cuda_oflex", None)
+    try:
+        vb.preseed_extension_module()
+        import selective_scan_cuda_oflex as ext      # what the reference's csms6s.py does (csms6s.py:9-14)
+        assert ext is ops.selective_scan_cuda_oflex and callable(ext.fwd) and callable(ext.bwd)
+    finally:
+        sys.modules.pop("selective_scan_cuda_oflex", None)
+        if saved is not None:
+            sys.modules["selective_scan_cuda_oflex"] = saved
+
+
+def test_flop_helpers_match_the_reference_formula():
+    """9 B L D N (+ B D L for the D skip, + B D L for a z gate): csms6s.py:136-160; the jit handle reads
+    the sizes of u and A from the traced inputs (csms6s.py:212-219)."""
+    import vmamba_b200 as vb
+    assert vb.flops_selective_scan_fn(B=2, L=3136, D=384, N=1) == 9 * 2 * 3136 * 384 + 2 * 384 * 3136
+    assert vb.flops_selective_scan_fn(B=1, L=10, D=4, N=16, with_D=False, with_Z=True) == 9 * 10 * 4 * 16 + 4 * 10
+
+    class _T:
+        def __init__(self, sizes):
+            self._s = sizes
+
+        def type(self):
+            return self
+
+        def sizes(self):
+            return self._s
+
+    ins = [_T([2, 384, 3136]), _T([2, 384, 3136]), _T([384, 1])]
+    assert vb.selective_scan_flop_jit(ins, None, verbose=False) == vb.flops_selective_scan_fn(B=2, L=3136, D=384, N=1)
 
 
 def test_enable_fused_selects_supported_modules_only():

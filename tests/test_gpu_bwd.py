@@ -175,3 +175,17 @@ def test_core_training_chain_vs_reference_grads(vb, tag):
         ref = gg[f"{tag}_grad_{n}"]
         err = O.max_rel_err(host(p_.grad).reshape(ref.shape), ref)
         assert err <= 1e-4, (n, err)
+
+
+def test_extension_module_surface(vb):
+    """fwd / bwd of the stand-in for the compiled extension, called as the reference calls them
+    (csms6s.py:81, 97-99): same values as the operator and its autograd."""
+    u, delta, A, B, C, D, bias, dout = (dev(t) for t in _random_case(2, 4, 3, 1, 200, seed=9))
+    ext = vb.selective_scan_cuda_oflex
+    out, x, *rest = ext.fwd(u, delta, A, B, C, D, bias, True, 1, True)
+    assert torch.equal(out, vb.selective_scan_fwd(u, delta, A, B, C, D, bias, True, True))
+    assert tuple(x.shape) == (2, 12, 1, 2)
+    du, ddelta, dA, dB, dC, dD, dbias, *rest = ext.bwd(u, delta, A, B, C, D, bias, dout, x, True, 1)
+    ref = O.selective_scan_bwd(*(host(t) for t in (u, delta, A, B, C, D, bias, dout)), True, "f32")
+    for name, got, r in zip(NAMES, (du, ddelta, dA, dB, dC, dD, dbias), ref):
+        assert O.max_rel_err(host(got), r) <= TOL["f32"], name

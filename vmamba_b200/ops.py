@@ -191,6 +191,51 @@ def selective_scan_fn(u, delta, A, B, C, D=None, delta_bias=None, delta_softplus
         return selective_scan_fwd(u, delta, A, B, C, D, delta_bias, delta_softplus, bool(oflex))
 
 
+def flops_selective_scan_fn(B=1, L=256, D=768, N=16, with_D=True, with_Z=False, with_complex=False):
+    """FLOP count of one selective scan as the reference counts it (csms6s.py:136-160): nine per
+    (batch, position, channel, state) plus one per element for the D skip and for a z gate."""
+    assert not with_complex
+    flops = 9 * B * L * D * N
+    if with_D:
+        flops += B * D * L
+    if with_Z:
+        flops += B * D * L
+    return flops
+
+
+def selective_scan_flop_jit(inputs, outputs, backend="prefixsum", verbose=True):
+    """fvcore / torch-jit FLOP handle for the Function (csms6s.py:212-219): sizes are read from the
+    traced inputs u (B, D, L) and A (D, N)."""
+    if backend == "naive":
+        raise NotImplementedError("the 'naive' count belongs to the reference's python loop, which this package does not provide")
+    B, D, L = inputs[0].type().sizes()
+    N = inputs[2].type().sizes()[1]
+    return flops_selective_scan_fn(B=B, L=L, D=D, N=N, with_D=True, with_Z=False)
+
+
+class _ExtShim:
+    """Stand-in for the compiled module `selective_scan_cuda_oflex` (pybind11 surface of
+    selective_scan_oflex.cpp:357-360): `fwd` and `bwd` with the reference's argument lists, for code
+    that calls the extension directly (csms6s.py:81, 97-99; test_selective_scan.py:62)."""
+    __name__ = "selective_scan_cuda_oflex"
+
+    @staticmethod
+    def fwd(u, delta, A, B, C, D=None, delta_bias=None, delta_softplus=False, nrows=1, out_float=True):
+        out = selective_scan_fwd(u, delta, A, B, C, D, delta_bias, delta_softplus, bool(out_float))
+        # the reference returns its chunk states here and wants them back in bwd; this library
+        # recomputes the states, so the tensor only keeps the shape (batch, dim, n_chunks, 2 * dstate)
+        n_chunks = (u.shape[-1] + 2047) // 2048
+        x = torch.zeros((u.shape[0], u.shape[1], n_chunks, 2 * A.shape[1]), device=u.device, dtype=torch.float32)
+        return [out, x]
+
+    @staticmethod
+    def bwd(u, delta, A, B, C, D, delta_bias, dout, x=None, delta_softplus=False, nrows=1):
+        return list(selective_scan_bwd(u, delta, A, B, C, D, delta_bias, dout, delta_softplus))
+
+
+selective_scan_cuda_oflex = _ExtShim()
+
+
 # --------------------------------------------------------------------------------------------
 # CrossScan / CrossMerge
 # --------------------------------------------------------------------------------------------

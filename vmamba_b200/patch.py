@@ -47,10 +47,6 @@ def uninstall(module) -> None:
         del module.__vmamba_b200_saved__
 
 
-def _flops_passthrough(*args, **kwargs):
-    raise NotImplementedError("FLOP-count helpers are not part of vmamba_b200; use the reference's own")
-
-
 def preseed_sys_modules() -> None:
     """Register `csm_triton` and `csms6s` stand-ins so that `classification/models/vmamba.py`
     picks up the CUDA-backed operators when it is imported afterwards."""
@@ -61,7 +57,14 @@ def preseed_sys_modules() -> None:
     s6 = types.ModuleType("csms6s")
     for name in ("selective_scan_fn", "SelectiveScanCuda", "SelectiveScanOflex"):
         setattr(s6, name, getattr(ops, name))
-    s6.selective_scan_flop_jit = _flops_passthrough
-    s6.flops_selective_scan_fn = _flops_passthrough
+    s6.selective_scan_flop_jit = ops.selective_scan_flop_jit
+    s6.flops_selective_scan_fn = ops.flops_selective_scan_fn
     sys.modules.setdefault("csm_triton", csm)
     sys.modules.setdefault("csms6s", s6)
+
+
+def preseed_extension_module() -> None:
+    """Register the stand-in for the compiled extension `selective_scan_cuda_oflex`, so that the
+    reference's OWN csms6s.py (imported unchanged afterwards) finds it and routes
+    SelectiveScanCuda.forward / backward through this library (csms6s.py:9-14, 81, 97-99)."""
+    sys.modules.setdefault("selective_scan_cuda_oflex", ops.selective_scan_cuda_oflex)
