@@ -53,3 +53,38 @@ def test_two_ranks_over_gloo():
     assert [(r[1], r[2]) for r in res] == [(0, 65), (65, 64)]
     assert all(abs(r[3] - 15.0) < 1e-9 for r in res)
     assert all(abs(r[4] - 129 / 0.015) < 1e-6 for r in res)
+
+
+def _worker_with_failure(rank, world, port, q):
+    """Rank 1 leaves between steps (before the bookkeeping collective); rank 0 must get a ShardFailure,
+    not a hang.  No GPU is involved: the failure is made on the host."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    dist.barrier()                       # step 0 completed by everyone
+    if rank == 1:
+        os._exit(3)                      # the rank dies without closing the group
+    try:
+        shard.aggregate_throughput_or_fail(64, 10.0)
+        q.put((rank, "no error"))
+    except shard.ShardFailure as e:
+        q.put((rank, "ShardFailure", str(e)))
+
+
+def test_lost_rank_is_reported_not_hung():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker_with_failure, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=120)
+    assert res[0] == 0 and res[1] == "ShardFailure" and "rank 0" in res[2]
+    procs[1].join(timeout=60)
+    assert procs[1].exitcode == 3
+    procs[0].join(timeout=60)
+    if procs[0].is_alive():              # the group's destructor may wait for the dead peer: end exactly this child
+        procs[0].kill()
+        procs[0].join(timeout=30)

@@ -47,3 +47,20 @@ def aggregate_throughput(images_this_rank: int, elapsed_ms_this_rank: float, dev
     total = sum_over_ranks(float(images_this_rank), device)
     ms = max_over_ranks(float(elapsed_ms_this_rank), device)
     return total / (ms * 1e-3)
+
+
+class ShardFailure(RuntimeError):
+    """A rank of the job did not take part in the host-side bookkeeping (it exited or hung): the
+    whole-job number of this step is void.  Raised on the surviving ranks instead of a backend error."""
+
+
+def aggregate_throughput_or_fail(images_this_rank: int, elapsed_ms_this_rank: float, device: str = "cpu") -> float:
+    """`aggregate_throughput`, with any failure of the collective (a peer that closed its connection,
+    the process group's timeout running out) reported as ShardFailure naming this rank.  The data path
+    has no collective, so a lost rank cannot leave a kernel of another rank waiting: the survivors'
+    GPUs finish their own step; only the bookkeeping fails, on the host, between steps."""
+    try:
+        return aggregate_throughput(images_this_rank, elapsed_ms_this_rank, device)
+    except Exception as e:  # noqa: BLE001 - gloo / nccl raise backend-specific RuntimeErrors
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        raise ShardFailure(f"rank {rank}: a peer left the job during the step bookkeeping ({type(e).__name__}: {e})") from e
