@@ -273,6 +273,52 @@ typedef struct ss2d_norm_params {
 int ss2d_layer_norm_cf(const ss2d_norm_params *p, void *cuda_stream);
 
 /* library identification and error text */
+/* ------------------------------------------------------------------------------------
+ * First layer of the patch embedding, fused: 3x3 convolution, stride 2, padding 1, in_channels 3 -> C0
+ * (+ bias), LayerNorm over the C0 channels of each pixel, GELU.  Replaces the first three modules of
+ * VSSM._make_patch_embed_v2 (vmamba.py:1928-1942: Conv2d, LayerNorm2d, GELU).
+ *   x (B, 3, H, W) dtype, contiguous;  weight (C0, 3, 3, 3) dtype;  conv_bias, ln_weight, ln_bias (C0) fp32 or NULL
+ *   y (B, ceil(H/2), ceil(W/2), C0) dtype, PIXEL-MAJOR (channels of a pixel contiguous), 16-byte aligned
+ * C0 in {32, 48, 64}, act = 1 (GELU); anything else returns SS2D_ENOTSUP.
+ * -------------------------------------------------------------------------------- */
+typedef struct ss2d_stem_params {
+    const void *x, *weight, *conv_bias, *ln_weight, *ln_bias;
+    void *y;
+    int64_t B, H, W, C0, in_channels;
+    int32_t dtype, act;
+    float eps;
+    int32_t reserved0;
+} ss2d_stem_params;
+
+int ss2d_stem_conv_norm_act(const ss2d_stem_params *p, void *cuda_stream);
+
+/* ------------------------------------------------------------------------------------
+ * Layout changes between pixel-major rows (N, C) - the layout the library convolutions of the patch
+ * embedding and of the downsampling layers run in - and channel planes (C, N), N = all pixels of the
+ * batch in (image, row, column) order, with the neighbouring elementwise work folded in.
+ *
+ * ss2d_pixels_norm_to_planes: planes[c, n] = LayerNorm_c(rows[n, :] + bias)[c]   (the LayerNorm2d after a
+ *   strided convolution, vmamba.py:1940, 1969; the convolution's bias joins here).  rows: rows_dtype,
+ *   16-byte aligned, C a multiple of 8 (16-bit) or 4 (fp32), C <= 2048 / 1024; planes: SS2D_F32 or rows_dtype.
+ * ss2d_planes_to_pixels: v = planes[c, n] (+ add[c, n] + bias[c]); rows[n, c] = v; with sum_out == planes the
+ *   fp32 planes are updated in place (the last residual addition of a stage, vmamba.py:1772/1777, in front of
+ *   the downsampling convolution).  planes: SS2D_F32; add: rows_dtype, same plane stride.
+ * plane_stride: elements between planes, 0 = N.  Fields a call does not use must be NULL.
+ * -------------------------------------------------------------------------------- */
+typedef struct ss2d_relayout_params {
+    void *rows;
+    void *planes;
+    const void *add, *bias, *ln_weight, *ln_bias;
+    void *sum_out;
+    int64_t N, C, plane_stride;
+    int32_t rows_dtype, planes_dtype;
+    float eps;
+    int32_t reserved0;
+} ss2d_relayout_params;
+
+int ss2d_pixels_norm_to_planes(const ss2d_relayout_params *p, void *cuda_stream);
+int ss2d_planes_to_pixels(const ss2d_relayout_params *p, void *cuda_stream);
+
 int ss2d_version(void);
 const char *ss2d_strerror(int status);
 /* number of kernel launches issued by this library in this process so far (all entry points) */

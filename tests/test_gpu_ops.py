@@ -448,3 +448,48 @@ def test_backbone_random_init_vs_oracle(vb, ssm_ratio, dims):
         assert O.max_rel_err(host(a_), b_) <= TOL_F32
     lb16 = VSSMInfer.from_state_dict(sd, dtype=torch.bfloat16)(dev(img))
     assert O.max_rel_err(host(lb16), ref) <= TOL_BF16
+
+
+# ------------------------------------------------------------------ patch-embedding / downsampling seam
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("B,H,W,C0", [(2, 32, 32, 48), (1, 17, 23, 32), (3, 8, 10, 64)])
+def test_stem_conv_norm_act(vb, dtype, B, H, W, C0):
+    """conv 3x3 s2 p1 (3 -> C0) + bias + LayerNorm2d + GELU (vmamba.py:1928-1942) against torch fp32 on the CPU."""
+    from vmamba_b200 import ops
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    g = torch.Generator().manual_seed(B * 100 + C0)
+    img = torch.randn((B, 3, H, W), generator=g).to(td)
+    w = (0.3 * torch.randn((C0, 3, 3, 3), generator=g)).to(td)
+    cb, lw, lb = 0.1 * torch.randn(C0, generator=g), 1 + 0.2 * torch.randn(C0, generator=g), 0.2 * torch.randn(C0, generator=g)
+    ref = torch.nn.functional.conv2d(img.float(), w.float(), cb, stride=2, padding=1)
+    ref = torch.nn.functional.layer_norm(ref.permute(0, 2, 3, 1), (C0,), lw, lb, 1e-5)
+    ref = torch.nn.functional.gelu(ref).numpy()
+    got = ops.stem_conv_norm_act(img.cuda(), w.cuda(), cb.cuda(), lw.cuda(), lb.cuda())
+    assert tuple(got.shape) == ref.shape
+    assert O.max_rel_err(host(got), ref) <= (TOL_F32 if dtype == "f32" else TOL_BF16)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("B,H,W,C", [(2, 7, 9, 96), (1, 5, 5, 768), (3, 4, 11, 40), (1, 3, 3, 1024)])
+def test_pixels_norm_to_planes_and_back(vb, dtype, B, H, W, C):
+    from vmamba_b200 import ops
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    rng = np.random.default_rng(C + H)
+    rows = O._round_to(rng.standard_normal((B, H, W, C), dtype=np.float32), dtype)
+    bias = rng.standard_normal(C).astype(np.float32)
+    lw, lb = (1 + 0.2 * rng.standard_normal(C)).astype(np.float32), (0.2 * rng.standard_normal(C)).astype(np.float32)
+    ref = O.layer_norm_cf(np.moveaxis(rows + bias, -1, 1), lw, lb)                     # (B, C, H, W)
+    got = ops.pixels_norm_to_planes(dev(rows, td), dev(bias), dev(lw), dev(lb))
+    assert tuple(got.shape) == (C, B, H, W) and got.dtype == torch.float32
+    assert O.max_rel_err(host(got).transpose(1, 0, 2, 3), ref) <= 1e-5
+    # planes -> pixels with the residual update: exact in fp32, one rounding in 16-bit
+    planes = rng.standard_normal((C, B, H, W), dtype=np.float32)
+    add = O._round_to(rng.standard_normal((C, B, H, W), dtype=np.float32), dtype)
+    pt = dev(planes)
+    out = ops.planes_to_pixels(pt, add=dev(add, td), add_bias=dev(bias), update=True, out_dtype=td)
+    want = planes + add + bias[:, None, None, None]
+    assert np.array_equal(host(pt), want)
+    assert np.array_equal(host(out), O._round_to(np.transpose(want, (1, 2, 3, 0)), dtype))
+    # pure layout change
+    out2 = ops.planes_to_pixels(dev(planes), out_dtype=torch.float32)
+    assert np.array_equal(host(out2), np.transpose(planes, (1, 2, 3, 0)))

@@ -79,6 +79,18 @@ class NormParams(ctypes.Structure):
                 ("skip_norm", _i32), ("reserved0", _i32)]
 
 
+class StemParams(ctypes.Structure):
+    _fields_ = [(n, _vp) for n in ("x", "weight", "conv_bias", "ln_weight", "ln_bias", "y")] + \
+               [(n, _i64) for n in ("B", "H", "W", "C0", "in_channels")] + \
+               [("dtype", _i32), ("act", _i32), ("eps", _f32), ("reserved0", _i32)]
+
+
+class RelayoutParams(ctypes.Structure):
+    _fields_ = [(n, _vp) for n in ("rows", "planes", "add", "bias", "ln_weight", "ln_bias", "sum_out")] + \
+               [(n, _i64) for n in ("N", "C", "plane_stride")] + \
+               [("rows_dtype", _i32), ("planes_dtype", _i32), ("eps", _f32), ("reserved0", _i32)]
+
+
 EXPORTS = {
     # name: (restype, argtypes)
     "ss2d_selective_scan_fwd": (ctypes.c_int, [ctypes.POINTER(ScanParams), _vp]),
@@ -92,6 +104,9 @@ EXPORTS = {
     "ss2d_core_static_capacity": (_i64, []),
     "ss2d_layer_norm_cf": (ctypes.c_int, [ctypes.POINTER(NormParams), _vp]),
     "ss2d_route_expand": (ctypes.c_int, [ctypes.POINTER(ExpandParams), _vp]),
+    "ss2d_stem_conv_norm_act": (ctypes.c_int, [ctypes.POINTER(StemParams), _vp]),
+    "ss2d_pixels_norm_to_planes": (ctypes.c_int, [ctypes.POINTER(RelayoutParams), _vp]),
+    "ss2d_planes_to_pixels": (ctypes.c_int, [ctypes.POINTER(RelayoutParams), _vp]),
     "ss2d_bias_act": (ctypes.c_int, [ctypes.POINTER(PointwiseParams), _vp]),
     "ss2d_dwconv3x3_act": (ctypes.c_int, [ctypes.POINTER(PointwiseParams), _vp]),
     "ss2d_version": (ctypes.c_int, []),

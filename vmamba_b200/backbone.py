@@ -68,7 +68,8 @@ class VSSMInfer:
                 depths[i] = max(depths.get(i, 0), j + 1)
         m.stem = dict(w0=T("patch_embed.0.weight", dtype), b0=T("patch_embed.0.bias", dtype).float(),
                       n0w=T("patch_embed.2.weight"), n0b=T("patch_embed.2.bias"),
-                      w1=T("patch_embed.5.weight", dtype), b1=T("patch_embed.5.bias", dtype).float(),
+                      w1=T("patch_embed.5.weight", dtype).contiguous(memory_format=torch.channels_last),
+                      b1=T("patch_embed.5.bias", dtype).float(),
                       n1w=T("patch_embed.7.weight"), n1b=T("patch_embed.7.bias"))
         for i in sorted(depths):
             stage = []
@@ -97,7 +98,8 @@ class VSSMInfer:
             m.blocks.append(stage)
             q = f"layers.{i}.downsample."
             if q + "1.weight" in sd:
-                m.down.append(dict(w=T(q + "1.weight", dtype), bf=T(q + "1.bias", dtype).float(),
+                m.down.append(dict(w=T(q + "1.weight", dtype).contiguous(memory_format=torch.channels_last),
+                                   bf=T(q + "1.bias", dtype).float(),
                                    nw=T(q + "3.weight"), nb=T(q + "3.bias")))
             else:
                 m.down.append(None)
@@ -140,14 +142,28 @@ class VSSMInfer:
         return x, ops.layer_norm_cf(x, nxt[0], nxt[1], 1e-5, self.dtype, add=m, add_bias=b.b2f, update=True,
                                     channel_major=True)
 
+    @staticmethod
+    def _conv_s2(rows, w_cl):
+        """3x3 stride-2 convolution (library) of a pixel-major (B, H, W, C) map; returns pixel-major.
+        The tensor is handed over as a channels-last view, so the library runs its pixel-major kernel
+        without converting."""
+        y = F.conv2d(rows.permute(0, 3, 1, 2), w_cl, None, stride=2, padding=1)
+        y = y.permute(0, 2, 3, 1)
+        return y if y.is_contiguous() else y.contiguous()
+
     def _stem(self, img):
-        """patch embed v2 (vmamba.py:1928-1942).  The convolution biases are added inside the LayerNorm calls."""
+        """patch embed v2 (vmamba.py:1928-1942): conv+LayerNorm+GELU in one kernel, the second convolution in
+        the library on the pixel-major map, its bias + LayerNorm + the change to channel planes in one kernel."""
         s = self.stem
-        x = F.conv2d(img.to(self.dtype), s["w0"], None, stride=2, padding=1)
-        x = F.gelu(ops.layer_norm_cf(None, s["n0w"], s["n0b"], 1e-5, self.dtype, add=x, add_bias=s["b0"]))
-        x = F.conv2d(x, s["w1"], None, stride=2, padding=1)
-        return ops.layer_norm_cf(None, s["n1w"], s["n1b"], 1e-5, torch.float32, add=x, add_bias=s["b1"],
-                                 out_channel_major=True)                                   # -> (C, B, H, W) fp32
+        img = img.to(self.dtype)
+        if ops.stem_supported(img.shape[1], s["w0"].shape[0]):
+            x = ops.stem_conv_norm_act(img, s["w0"], s["b0"], s["n0w"], s["n0b"])            # (B, H/2, W/2, C0)
+        else:
+            x = F.conv2d(img, s["w0"], None, stride=2, padding=1)
+            x = F.gelu(ops.layer_norm_cf(None, s["n0w"], s["n0b"], 1e-5, self.dtype, add=x, add_bias=s["b0"]))
+            x = x.permute(0, 2, 3, 1).contiguous()
+        x = self._conv_s2(x, s["w1"])
+        return ops.pixels_norm_to_planes(x, s["b1"], s["n1w"], s["n1b"])                     # -> (C, B, H, W) fp32
 
     def _stages(self, img, want_features=False, head_norm=None):
         """Runs the stages.  Returns (per-stage residual maps if wanted, last value):
@@ -166,15 +182,12 @@ class VSSMInfer:
             m, mb = pend
             d = self.down[i]
             if d is not None:
-                # downsample v3 (vmamba.py:1964-1971): x += m + bias, and the strided 3x3 convolution's
-                # (B, C, H, W) 16-bit input, in one pass
-                xin = ops.layer_norm_cf(x, None, None, 1e-5, self.dtype, add=m, add_bias=mb, update=True,
-                                        channel_major=True, out_channel_major=False, normalize=False)
+                # downsample v3 (vmamba.py:1964-1971): x += m + bias and the pixel-major 16-bit input of the
+                # strided convolution in one pass; its bias + LayerNorm + the way back to planes in another
+                xin = ops.planes_to_pixels(x, add=m, add_bias=mb, update=True, out_dtype=self.dtype)
                 if want_features:
                     outs.append(x.clone())
-                y = F.conv2d(xin, d["w"], None, stride=2, padding=1)
-                x = ops.layer_norm_cf(None, d["nw"], d["nb"], 1e-5, torch.float32, add=y, add_bias=d["bf"],
-                                      out_channel_major=True)
+                x = ops.pixels_norm_to_planes(self._conv_s2(xin, d["w"]), d["bf"], d["nw"], d["nb"])
             else:
                 if head_norm is not None:     # classifier norm fused with the last residual update
                     last = ops.layer_norm_cf(x, head_norm[0], head_norm[1], 1e-5, torch.float32, add=m, add_bias=mb,

@@ -1,0 +1,356 @@
+// The strided 3x3 convolutions of the patch embedding and of the downsampling layers run in the
+// library (cuDNN) on pixel-major (B, H, W, C) maps, the layout its tensor-core kernels use; the trunk
+// of the backbone keeps channel-major planes (C, B, H, W).  The three kernels here sit on that seam
+// and fold the neighbouring elementwise work into the layout change, so that no separate conversion
+// pass and no separate LayerNorm / cast pass touches HBM:
+//
+//   stem_conv_norm_act   image (B, 3, H, W) -> conv 3x3 stride 2 (3 -> C0) + bias -> LayerNorm over C0 -> GELU
+//                        -> (B, H/2, W/2, C0).  The first layer has 27 inputs per output value: far
+//                        too thin for tensor cores, bound by the 4x larger output write; one thread
+//                        owns two neighbouring output pixels with all C0 channels in registers, so the
+//                        LayerNorm needs no communication and the pixel-major store is one run per pixel.
+//   pixels_norm_to_planes (N, C) pixel-major rows + bias -> LayerNorm over C -> (C, N) planes (fp32 or 16-bit)
+//   planes_to_pixels      (C, N) fp32 planes (+ add + bias, optionally written back) -> (N, C) pixel-major 16-bit
+// N counts the pixels of the whole batch (b, h, w): pixel-major row n and element n of every plane
+// are the same pixel.
+#include "activations.cuh"
+
+namespace ss2d {
+
+// ------------------------------------------------------------------------------------------------
+struct StemArgs {
+    const void* x;        // (B, 3, H, W)
+    const void* w;        // (C0, 3, 3, 3)
+    const float *cbias, *lnw, *lnb;
+    void* y;              // (B, Ho, Wo, C0)
+    int B, H, W, Ho, Wo;
+    float eps;
+};
+
+template <typename T, int C0>
+__global__ void __launch_bounds__(128, 4) stem_conv_norm_act_kernel(const StemArgs a) {
+    // weights as [tap][channel] fp32 so that one 16-byte broadcast load brings a tap's weights of four channels
+    __shared__ __align__(16) float sw[27 * C0];
+    __shared__ float sb[3 * C0];
+    constexpr int CH = C0 / 2;                    // two neighbouring lanes share a pixel pair: half of the channels each
+    static_assert(CH % 8 == 0, "16-byte stores per half");
+    for (int i = threadIdx.x; i < 27 * C0; i += blockDim.x) {
+        const int c = i / 27, tap = i - c * 27;
+        sw[tap * C0 + c] = to_f<T>(((const T*)a.w)[i]);
+    }
+    for (int i = threadIdx.x; i < C0; i += blockDim.x) {
+        sb[i] = a.cbias ? a.cbias[i] : 0.f;
+        sb[C0 + i] = a.lnw ? a.lnw[i] : 1.f;
+        sb[2 * C0 + i] = a.lnb ? a.lnb[i] : 0.f;
+    }
+    __syncthreads();
+    const int pairs_per_row = (a.Wo + 1) / 2;
+    const long long total = (long long)a.B * a.Ho * pairs_per_row;
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int half = (int)(tid & 1);
+    const bool live = (tid >> 1) < total;
+    const long long gid = live ? (tid >> 1) : total - 1;      // idle lanes shadow the last pair and store nothing
+    const int px = (int)(gid % pairs_per_row);
+    const long long rest = gid / pairs_per_row;
+    const int oy = (int)(rest % a.Ho);
+    const int b = (int)(rest / a.Ho);
+    const int ox0 = 2 * px;                       // output pixels (oy, ox0) and (oy, ox0 + 1)
+    const bool two = ox0 + 1 < a.Wo;
+    // input window: rows 2*oy-1 .. 2*oy+1, columns 2*ox0-1 .. 2*ox0+3 (five columns serve both pixels)
+    float in[3][3][5];
+    const T* xb = (const T*)a.x + (long long)b * 3 * a.H * a.W;
+#pragma unroll
+    for (int ky = 0; ky < 3; ++ky) {
+        const int iy = 2 * oy - 1 + ky;
+        const bool oky = iy >= 0 && iy < a.H;
+#pragma unroll
+        for (int kx = 0; kx < 5; ++kx) {
+            const int ix = 2 * ox0 - 1 + kx;
+            const bool ok = oky && ix >= 0 && ix < a.W;
+            const int off = iy * a.W + ix;
+#pragma unroll
+            for (int ci = 0; ci < 3; ++ci) in[ci][ky][kx] = ok ? to_f<T>(xb[ci * a.H * a.W + off]) : 0.f;
+        }
+    }
+    float2 acc0[CH / 2], acc1[CH / 2];            // pixel 0 / pixel 1, channel pairs of this half
+#pragma unroll
+    for (int c = 0; c < CH / 2; ++c) { acc0[c] = make_float2(0.f, 0.f); acc1[c] = make_float2(0.f, 0.f); }
+    const float* swh = sw + half * CH;
+#pragma unroll
+    for (int ci = 0; ci < 3; ++ci)
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky)
+#pragma unroll
+            for (int kx = 0; kx < 3; ++kx) {
+                const int tap = (ci * 3 + ky) * 3 + kx;
+                const float2 v0 = make_float2(in[ci][ky][kx], in[ci][ky][kx]);
+                const float2 v1 = make_float2(in[ci][ky][kx + 2], in[ci][ky][kx + 2]);
+#pragma unroll
+                for (int c4 = 0; c4 < CH / 4; ++c4) {
+                    const float4 w4 = *reinterpret_cast<const float4*>(swh + tap * C0 + 4 * c4);
+                    acc0[2 * c4] = __ffma2_rn(v0, make_float2(w4.x, w4.y), acc0[2 * c4]);
+                    acc0[2 * c4 + 1] = __ffma2_rn(v0, make_float2(w4.z, w4.w), acc0[2 * c4 + 1]);
+                    acc1[2 * c4] = __ffma2_rn(v1, make_float2(w4.x, w4.y), acc1[2 * c4]);
+                    acc1[2 * c4 + 1] = __ffma2_rn(v1, make_float2(w4.z, w4.w), acc1[2 * c4 + 1]);
+                }
+            }
+    // per pixel: conv output rounded to the storage type (as the stand-alone convolution would leave it),
+    // + bias, LayerNorm in fp32 over both halves (one exchange with the neighbouring lane), rounded, GELU, rounded
+    const float* bh = sb + half * CH;
+    auto finish = [&](float2 (&acc)[CH / 2], int ox, bool store) {
+        float s = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH / 2; ++c) {
+            acc[c].x = round_to<T>(acc[c].x) + bh[2 * c];
+            acc[c].y = round_to<T>(acc[c].y) + bh[2 * c + 1];
+            s += acc[c].x + acc[c].y;
+        }
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        const float mean = s * (1.f / C0);
+        float q = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH / 2; ++c) {
+            const float dx = acc[c].x - mean, dy = acc[c].y - mean;
+            q = fmaf(dx, dx, q); q = fmaf(dy, dy, q);
+        }
+        q += __shfl_xor_sync(0xffffffffu, q, 1);
+        const float rstd = rsqrtf(q * (1.f / C0) + a.eps);
+        T* out = (T*)a.y + (((long long)b * a.Ho + oy) * a.Wo + ox) * C0 + half * CH;
+#pragma unroll
+        for (int c8 = 0; c8 < CH / 8; ++c8) {
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = 4 * c8 + j;
+                float2 v;
+                v.x = round_to<T>(fmaf((acc[c].x - mean) * rstd, bh[C0 + 2 * c], bh[2 * C0 + 2 * c]));
+                v.y = round_to<T>(fmaf((acc[c].y - mean) * rstd, bh[C0 + 2 * c + 1], bh[2 * C0 + 2 * c + 1]));
+                float2 r;
+                if constexpr (sizeof(T) == 2) r = gelu_pair_fast(v);
+                else r = make_float2(act_f<ACT_GELU>(v.x), act_f<ACT_GELU>(v.y));
+                o[2 * j] = r.x; o[2 * j + 1] = r.y;
+            }
+            if (store) Vec<T, 8>::store(out + 8 * c8, o);
+        }
+    };
+    finish(acc0, ox0, live);
+    finish(acc1, two ? ox0 + 1 : ox0, live && two);
+}
+
+int stem_conv_norm_act(const ss2d_stem_params* p, cudaStream_t st) {
+    if (!p) return SS2D_EINVAL_NULL;
+    if (!p->x || !p->weight || !p->y) return SS2D_EINVAL_NULL;
+    if (!dtype_ok(p->dtype)) return SS2D_EINVAL_DTYPE;
+    if (p->B <= 0 || p->H <= 0 || p->W <= 0 || p->C0 <= 0) return SS2D_EINVAL_SHAPE;
+    if (p->B * p->H * p->W > 0x3fffffffLL) return SS2D_EINVAL_SHAPE;
+    const size_t s = dtype_size(p->dtype);
+    if (!aligned_to(p->x, s) || !aligned_to(p->weight, s) || !aligned_to(p->y, 16) || !aligned_to(p->conv_bias, 4) ||
+        !aligned_to(p->ln_weight, 4) || !aligned_to(p->ln_bias, 4))
+        return SS2D_EINVAL_ALIGN;
+    if (p->in_channels != 3 || p->act != ACT_GELU) return SS2D_ENOTSUP;
+    StemArgs a;
+    a.x = p->x; a.w = p->weight; a.cbias = (const float*)p->conv_bias; a.lnw = (const float*)p->ln_weight;
+    a.lnb = (const float*)p->ln_bias; a.y = p->y;
+    a.B = (int)p->B; a.H = (int)p->H; a.W = (int)p->W; a.Ho = (int)((p->H + 1) / 2); a.Wo = (int)((p->W + 1) / 2);
+    a.eps = p->eps;
+    const long long total = 2LL * a.B * a.Ho * ((a.Wo + 1) / 2);      // two threads per pixel pair
+    const unsigned grid = (unsigned)((total + 127) / 128);
+#define SS2D_STEM_CASE(TT, CC) stem_conv_norm_act_kernel<TT, CC><<<grid, 128, 0, st>>>(a)
+#define SS2D_STEM_T(TT) \
+    switch (p->C0) { case 32: SS2D_STEM_CASE(TT, 32); break; case 48: SS2D_STEM_CASE(TT, 48); break; \
+                     case 64: SS2D_STEM_CASE(TT, 64); break; default: return SS2D_ENOTSUP; }
+    if (p->dtype == SS2D_F32) { SS2D_STEM_T(float) }
+    else if (p->dtype == SS2D_BF16) { SS2D_STEM_T(__nv_bfloat16) }
+    else { SS2D_STEM_T(__half) }
+#undef SS2D_STEM_T
+#undef SS2D_STEM_CASE
+    count_launch();
+    return check_launch();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Pixel-major rows -> LayerNorm -> planes.  A CTA takes TP consecutive pixels (32, or 16 for wide rows):
+//   A  all threads bring the rows (+ bias) into a shared fp32 tile [TP][C + 1], 16 bytes per load;
+//   B  each warp computes mean and 1/std of TP/8 pixels from the tile (two passes, lanes along C);
+//   C  warp w takes channels w, w+8, ...: lane = pixel, so every plane receives its TP pixels as one run
+//      (the odd pitch makes the column read conflict-free).
+struct RowsArgs {
+    const void* in;        // (N, C)
+    const float *bias, *lnw, *lnb;
+    void* out;             // (C, N) with out_cs between planes
+    long long N, out_cs;
+    int C;
+    float eps;
+};
+
+template <typename Tin, typename Tout, int TP>
+__global__ void __launch_bounds__(256) pixels_norm_to_planes_kernel(const RowsArgs a) {
+    extern __shared__ float tile[];                       // [TP][C + 1], then mean[TP], rstd[TP]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long n0 = (long long)blockIdx.x * TP;
+    const int C = a.C, P = C + 1;
+    float* stat = tile + TP * P;
+    constexpr int PV = sizeof(Tin) == 2 ? 8 : 4;
+    const int pieces = C / PV;
+    const int live = (int)min((long long)TP, a.N - n0);
+    for (int idx = threadIdx.x; idx < live * pieces; idx += 256) {
+        const int pp = idx / pieces, c = (idx - pp * pieces) * PV;
+        float v[PV];
+        Vec<Tin, PV>::load((const Tin*)a.in + (n0 + pp) * C + c, v);
+#pragma unroll
+        for (int i = 0; i < PV; ++i) tile[pp * P + c + i] = v[i] + (a.bias ? __ldg(a.bias + c + i) : 0.f);
+    }
+    __syncthreads();
+    for (int pp = warp; pp < live; pp += 8) {
+        float s = 0.f, q = 0.f;
+        for (int c = lane; c < C; c += 32) s += tile[pp * P + c];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        const float mean = s / C;
+        for (int c = lane; c < C; c += 32) { const float d = tile[pp * P + c] - mean; q = fmaf(d, d, q); }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) q += __shfl_xor_sync(0xffffffffu, q, off);
+        if (lane == 0) { stat[pp] = mean; stat[TP + pp] = rsqrtf(q / C + a.eps); }
+    }
+    __syncthreads();
+    const int pl = threadIdx.x % TP, cw = threadIdx.x / TP;      // TP = 32: a warp per channel; TP = 16: two channels per warp
+    if (pl < live) {
+        const float mean = stat[pl], rstd = stat[TP + pl];
+        for (int c = cw; c < C; c += 256 / TP) {
+            const float w = a.lnw ? __ldg(a.lnw + c) : 1.f, bb = a.lnb ? __ldg(a.lnb + c) : 0.f;
+            ((Tout*)a.out)[(long long)c * a.out_cs + n0 + pl] = from_f<Tout>(fmaf((tile[pl * P + c] - mean) * rstd, w, bb));
+        }
+    }
+}
+
+int pixels_norm_to_planes(const ss2d_relayout_params* p, cudaStream_t st) {
+    if (!p) return SS2D_EINVAL_NULL;
+    if (!p->rows || !p->planes) return SS2D_EINVAL_NULL;
+    if (!dtype_ok(p->rows_dtype) || !dtype_ok(p->planes_dtype)) return SS2D_EINVAL_DTYPE;
+    if (p->N <= 0 || p->C <= 0) return SS2D_EINVAL_SHAPE;
+    const size_t sr = dtype_size(p->rows_dtype), sp = dtype_size(p->planes_dtype);
+    const int pv = sr == 2 ? 8 : 4;
+    if (p->C % pv != 0) return SS2D_ENOTSUP;
+    if (!aligned_to(p->rows, 16) || !aligned_to(p->planes, sp) || !aligned_to(p->bias, 4) || !aligned_to(p->ln_weight, 4) ||
+        !aligned_to(p->ln_bias, 4))
+        return SS2D_EINVAL_ALIGN;
+    const long long cs = p->plane_stride ? p->plane_stride : p->N;
+    if (cs < p->N) return SS2D_EINVAL_STRIDE;
+    if (p->add || p->sum_out) return SS2D_ENOTSUP;
+    RowsArgs a;
+    a.in = p->rows; a.bias = (const float*)p->bias; a.lnw = (const float*)p->ln_weight; a.lnb = (const float*)p->ln_bias;
+    a.out = p->planes; a.N = p->N; a.out_cs = cs; a.C = (int)p->C; a.eps = p->eps;
+    const int tp = p->C <= 512 ? 32 : 16;
+    const size_t smem = ((size_t)tp * (p->C + 1) + 2 * tp) * sizeof(float);
+    if (smem > 200 * 1024) return SS2D_ENOTSUP;
+    const long long ctas = (p->N + tp - 1) / tp;
+    if (ctas > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
+#define SS2D_ROWS_LAUNCH_TP(TI, TO, TPV) { auto kern = pixels_norm_to_planes_kernel<TI, TO, TPV>; \
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return SS2D_ECUDA; \
+        kern<<<(unsigned)ctas, 256, smem, st>>>(a); }
+#define SS2D_ROWS_LAUNCH(TI, TO) { if (tp == 32) SS2D_ROWS_LAUNCH_TP(TI, TO, 32) else SS2D_ROWS_LAUNCH_TP(TI, TO, 16) }
+    const int ri = p->rows_dtype, po = p->planes_dtype;
+    if (ri == SS2D_F32 && po == SS2D_F32) SS2D_ROWS_LAUNCH(float, float)
+    else if (ri == SS2D_BF16 && po == SS2D_F32) SS2D_ROWS_LAUNCH(__nv_bfloat16, float)
+    else if (ri == SS2D_BF16 && po == SS2D_BF16) SS2D_ROWS_LAUNCH(__nv_bfloat16, __nv_bfloat16)
+    else if (ri == SS2D_F16 && po == SS2D_F32) SS2D_ROWS_LAUNCH(__half, float)
+    else if (ri == SS2D_F16 && po == SS2D_F16) SS2D_ROWS_LAUNCH(__half, __half)
+    else return SS2D_EINVAL_DTYPE;
+#undef SS2D_ROWS_LAUNCH_TP
+#undef SS2D_ROWS_LAUNCH
+    count_launch();
+    return check_launch();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Planes -> pixel-major rows, with the residual update in front: v = planes (+ add + bias); v is
+// optionally written back to the fp32 planes, and leaves as a 16-bit (or fp32) row per pixel.
+struct PlanesArgs {
+    float* planes;         // (C, N) fp32, plane stride cs
+    const void* add;       // (C, N) rows' dtype, same stride, or NULL
+    const float* bias;     // (C) or NULL
+    void* rows;            // (N, C)
+    long long N, cs;
+    int C, write_back;
+};
+
+template <typename T, int TP>
+__global__ void __launch_bounds__(256) planes_to_pixels_kernel(const PlanesArgs a) {
+    extern __shared__ float tile[];                       // [TP][C + 1]
+    const long long n0 = (long long)blockIdx.x * TP;
+    const int C = a.C, P = C + 1;
+    const int pl = threadIdx.x % TP, cw = threadIdx.x / TP;
+    constexpr int CW = 256 / TP;
+    const long long n = n0 + pl;
+    if (n < a.N) {
+        // the planes may be written back: four channels' loads are issued before the first store
+        for (int c0 = cw; c0 < C; c0 += 4 * CW) {
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = c0 + CW * j;
+                if (c < C) {
+                    const long long off = (long long)c * a.cs + n;
+                    v[j] = a.planes[off];
+                    if (a.add) v[j] += to_f<T>(((const T*)a.add)[off]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = c0 + CW * j;
+                if (c < C) {
+                    if (a.bias) v[j] += __ldg(a.bias + c);
+                    if (a.write_back) a.planes[(long long)c * a.cs + n] = v[j];
+                    tile[pl * P + c] = v[j];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    constexpr int PV = sizeof(T) == 2 ? 8 : 4;
+    const int pieces = C / PV;
+    const int live = (int)min((long long)TP, a.N - n0);
+    for (int idx = threadIdx.x; idx < live * pieces; idx += 256) {
+        const int pp = idx / pieces, c = (idx - pp * pieces) * PV;
+        float v[PV];
+#pragma unroll
+        for (int i = 0; i < PV; ++i) v[i] = tile[pp * P + c + i];
+        Vec<T, PV>::store((T*)a.rows + (n0 + pp) * C + c, v);
+    }
+}
+
+int planes_to_pixels(const ss2d_relayout_params* p, cudaStream_t st) {
+    if (!p) return SS2D_EINVAL_NULL;
+    if (!p->rows || !p->planes) return SS2D_EINVAL_NULL;
+    if (!dtype_ok(p->rows_dtype) || p->planes_dtype != SS2D_F32) return SS2D_EINVAL_DTYPE;
+    if (p->N <= 0 || p->C <= 0) return SS2D_EINVAL_SHAPE;
+    const size_t sr = dtype_size(p->rows_dtype);
+    const int pv = sr == 2 ? 8 : 4;
+    if (p->C % pv != 0) return SS2D_ENOTSUP;
+    if (!aligned_to(p->rows, 16) || !aligned_to(p->planes, 4) || !aligned_to(p->add, sr) || !aligned_to(p->bias, 4)) return SS2D_EINVAL_ALIGN;
+    const long long cs = p->plane_stride ? p->plane_stride : p->N;
+    if (cs < p->N) return SS2D_EINVAL_STRIDE;
+    if (p->ln_weight || p->ln_bias) return SS2D_ENOTSUP;
+    PlanesArgs a;
+    a.planes = (float*)p->planes; a.add = p->add; a.bias = (const float*)p->bias; a.rows = p->rows;
+    a.N = p->N; a.cs = cs; a.C = (int)p->C; a.write_back = p->sum_out != nullptr;
+    if (p->sum_out && p->sum_out != p->planes) return SS2D_ENOTSUP;      // the update is in place
+    const int tp = p->C <= 512 ? 32 : 16;
+    const size_t smem = (size_t)tp * (p->C + 1) * sizeof(float);
+    if (smem > 200 * 1024) return SS2D_ENOTSUP;
+    const long long ctas = (p->N + tp - 1) / tp;
+    if (ctas > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
+#define SS2D_PLANES_LAUNCH_TP(TT, TPV) { auto kern = planes_to_pixels_kernel<TT, TPV>; \
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return SS2D_ECUDA; \
+        kern<<<(unsigned)ctas, 256, smem, st>>>(a); }
+#define SS2D_PLANES_LAUNCH(TT) { if (tp == 32) SS2D_PLANES_LAUNCH_TP(TT, 32) else SS2D_PLANES_LAUNCH_TP(TT, 16) }
+    if (p->rows_dtype == SS2D_F32) SS2D_PLANES_LAUNCH(float)
+    else if (p->rows_dtype == SS2D_BF16) SS2D_PLANES_LAUNCH(__nv_bfloat16)
+    else SS2D_PLANES_LAUNCH(__half)
+#undef SS2D_PLANES_LAUNCH_TP
+#undef SS2D_PLANES_LAUNCH
+    count_launch();
+    return check_launch();
+}
+
+}  // namespace ss2d

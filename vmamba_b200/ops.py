@@ -14,7 +14,8 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from ._lib import ScanBwdParams, CrossParams, NormParams, PointwiseParams, ScanParams, check, lib
+from ._lib import (CrossParams, NormParams, PointwiseParams, RelayoutParams, ScanBwdParams, ScanParams, StemParams,
+                   check, lib)
 
 _DTYPES = {torch.float32: _lib.SS2D_F32, torch.float16: _lib.SS2D_F16, torch.bfloat16: _lib.SS2D_BF16}
 
@@ -438,3 +439,74 @@ def dwconv3x3_act(x: torch.Tensor, weight: torch.Tensor, bias=None, act="silu", 
     with torch.cuda.device(x.device):
         check(lib().ss2d_dwconv3x3_act(p, _stream(x)), "ss2d_dwconv3x3_act")
     return y
+
+
+# --------------------------------------------------------------------------------------------
+# patch embedding / downsampling seam: pixel-major (B, H, W, C) maps for the library's strided
+# convolutions, channel planes (C, B, H, W) for the trunk
+# --------------------------------------------------------------------------------------------
+def stem_supported(in_channels: int, c0: int) -> bool:
+    return in_channels == 3 and c0 in (32, 48, 64)
+
+
+def stem_conv_norm_act(img: torch.Tensor, weight: torch.Tensor, conv_bias=None, ln_weight=None, ln_bias=None,
+                       eps: float = 1e-5) -> torch.Tensor:
+    """GELU(LayerNorm2d(conv3x3 stride 2 pad 1 (img) + bias)): the first three modules of the v2 patch
+    embedding (vmamba.py:1928-1942) in one kernel.  img (B, 3, H, W) -> (B, H/2, W/2, C0) PIXEL-MAJOR."""
+    _require_cuda(img, weight, conv_bias, ln_weight, ln_bias)
+    img = img.contiguous()
+    B, Cin, H, W = img.shape
+    C0 = weight.shape[0]
+    if tuple(weight.shape) != (C0, Cin, 3, 3):
+        raise RuntimeError("weight must be (C0, in_channels, 3, 3)")
+    w = weight.contiguous().to(img.dtype)
+    f32 = lambda t: None if t is None else t.contiguous().float()
+    cb, lw, lb = f32(conv_bias), f32(ln_weight), f32(ln_bias)
+    y = torch.empty((B, (H + 1) // 2, (W + 1) // 2, C0), device=img.device, dtype=img.dtype)
+    p = StemParams(img.data_ptr(), w.data_ptr(), _ptr(cb), _ptr(lw), _ptr(lb), y.data_ptr(), B, H, W, C0, Cin,
+                   dtype_code(img), _ACTS["gelu"], eps, 0)
+    with torch.cuda.device(img.device):
+        check(lib().ss2d_stem_conv_norm_act(p, _stream(img)), "ss2d_stem_conv_norm_act")
+    return y
+
+
+def pixels_norm_to_planes(rows: torch.Tensor, bias=None, ln_weight=None, ln_bias=None, eps: float = 1e-5,
+                          out_dtype=torch.float32) -> torch.Tensor:
+    """LayerNorm over the last axis of a pixel-major (B, H, W, C) map (+ per-channel bias first),
+    written as channel planes (C, B, H, W): the LayerNorm2d behind a strided convolution
+    (vmamba.py:1940, 1969) and the layout change back to the trunk in one pass."""
+    _require_cuda(rows, bias, ln_weight, ln_bias)
+    if rows.dim() != 4 or not rows.is_contiguous():
+        raise RuntimeError("pixels_norm_to_planes expects a contiguous (B, H, W, C) tensor")
+    B, H, W, C = rows.shape
+    f32 = lambda t: None if t is None else t.contiguous().float()
+    bb, lw, lb = f32(bias), f32(ln_weight), f32(ln_bias)
+    out = torch.empty((C, B, H, W), device=rows.device, dtype=out_dtype)
+    p = RelayoutParams(rows.data_ptr(), out.data_ptr(), None, _ptr(bb), _ptr(lw), _ptr(lb), None, B * H * W, C, 0,
+                       dtype_code(rows), dtype_code(out), eps, 0)
+    with torch.cuda.device(rows.device):
+        check(lib().ss2d_pixels_norm_to_planes(p, _stream(rows)), "ss2d_pixels_norm_to_planes")
+    return out
+
+
+def planes_to_pixels(planes: torch.Tensor, add=None, add_bias=None, update: bool = False, out_dtype=None) -> torch.Tensor:
+    """fp32 channel planes (C, B, H, W) (+ add + add_bias[channel]) -> pixel-major (B, H, W, C) in
+    `out_dtype` (default: add's dtype, else fp32).  `update=True` writes the sum back into `planes`
+    (the last residual addition of a stage in front of the downsampling convolution, vmamba.py:1772/1777)."""
+    _require_cuda(planes, add, add_bias)
+    if planes.dim() != 4 or planes.dtype != torch.float32 or not planes.is_contiguous():
+        raise RuntimeError("planes_to_pixels expects a contiguous fp32 (C, B, H, W) tensor")
+    C, B, H, W = planes.shape
+    if out_dtype is None:
+        out_dtype = add.dtype if add is not None else torch.float32
+    if add is not None:
+        if add.shape != planes.shape:
+            raise RuntimeError("add must have the shape of the planes")
+        add = add.contiguous().to(out_dtype)
+    ab = None if add_bias is None else add_bias.contiguous().float()
+    rows = torch.empty((B, H, W, C), device=planes.device, dtype=out_dtype)
+    p = RelayoutParams(rows.data_ptr(), planes.data_ptr(), _ptr(add), _ptr(ab), None, None,
+                       planes.data_ptr() if update else None, B * H * W, C, 0, dtype_code(rows), dtype_code(planes), 0.0, 0)
+    with torch.cuda.device(planes.device):
+        check(lib().ss2d_planes_to_pixels(p, _stream(planes)), "ss2d_planes_to_pixels")
+    return rows
