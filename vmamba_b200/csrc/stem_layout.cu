@@ -95,7 +95,8 @@ __global__ void __launch_bounds__(128, 4) stem_conv_norm_act_kernel(const StemAr
                 }
             }
     // per pixel: conv output rounded to the storage type (as the stand-alone convolution would leave it),
-    // + bias, LayerNorm in fp32 over both halves (one exchange with the neighbouring lane), rounded, GELU, rounded
+    // + bias, LayerNorm in fp32 over both halves (one exchange with the neighbouring lane), GELU on the fp32
+    // value (LayerNorm runs and returns fp32 under autocast), one rounding at the store
     const float* bh = sb + half * CH;
     auto finish = [&](float2 (&acc)[CH / 2], int ox, bool store) {
         float s = 0.f;
@@ -123,8 +124,8 @@ __global__ void __launch_bounds__(128, 4) stem_conv_norm_act_kernel(const StemAr
             for (int j = 0; j < 4; ++j) {
                 const int c = 4 * c8 + j;
                 float2 v;
-                v.x = round_to<T>(fmaf((acc[c].x - mean) * rstd, bh[C0 + 2 * c], bh[2 * C0 + 2 * c]));
-                v.y = round_to<T>(fmaf((acc[c].y - mean) * rstd, bh[C0 + 2 * c + 1], bh[2 * C0 + 2 * c + 1]));
+                v.x = fmaf((acc[c].x - mean) * rstd, bh[C0 + 2 * c], bh[2 * C0 + 2 * c]);
+                v.y = fmaf((acc[c].y - mean) * rstd, bh[C0 + 2 * c + 1], bh[2 * C0 + 2 * c + 1]);
                 float2 r;
                 if constexpr (sizeof(T) == 2) r = gelu_pair_fast(v);
                 else r = make_float2(act_f<ACT_GELU>(v.x), act_f<ACT_GELU>(v.y));
@@ -185,40 +186,68 @@ struct RowsArgs {
 
 template <typename Tin, typename Tout, int TP>
 __global__ void __launch_bounds__(256) pixels_norm_to_planes_kernel(const RowsArgs a) {
-    extern __shared__ float tile[];                       // [TP][C + 1], then mean[TP], rstd[TP]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    extern __shared__ float tile[];                       // [TP][C + 1], then part[256 / TP][TP], scale[TP], shift[TP]
     const long long n0 = (long long)blockIdx.x * TP;
     const int C = a.C, P = C + 1;
-    float* stat = tile + TP * P;
+    float* part = tile + TP * P;
+    float* stat = part + 256;
     constexpr int PV = sizeof(Tin) == 2 ? 8 : 4;
     const int pieces = C / PV;
     const int live = (int)min((long long)TP, a.N - n0);
+    // A: rows (+ bias) -> tile
     for (int idx = threadIdx.x; idx < live * pieces; idx += 256) {
         const int pp = idx / pieces, c = (idx - pp * pieces) * PV;
-        float v[PV];
+        float v[PV], bv[PV];
         Vec<Tin, PV>::load((const Tin*)a.in + (n0 + pp) * C + c, v);
+        if (a.bias) Vec<float, PV>::load(a.bias + c, bv);
 #pragma unroll
-        for (int i = 0; i < PV; ++i) tile[pp * P + c + i] = v[i] + (a.bias ? __ldg(a.bias + c + i) : 0.f);
+        for (int i = 0; i < PV; ++i) tile[pp * P + c + i] = a.bias ? v[i] + bv[i] : v[i];
     }
     __syncthreads();
-    for (int pp = warp; pp < live; pp += 8) {
-        float s = 0.f, q = 0.f;
-        for (int c = lane; c < C; c += 32) s += tile[pp * P + c];
+    // B: statistics.  Thread (pixel pl, slice sl) sums the channels sl, sl + NS, ... of its pixel (the odd
+    // pitch keeps the 32 pixels of a warp on different banks); the NS partial sums meet in shared memory.
+    constexpr int NS = 256 / TP;
+    const int pl = threadIdx.x % TP, sl = threadIdx.x / TP;
+    float s = 0.f;
+    for (int c = sl; c < C; c += NS) s += tile[pl * P + c];
+    part[sl * TP + pl] = s;
+    __syncthreads();
+    float mean = 0.f;
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-        const float mean = s / C;
-        for (int c = lane; c < C; c += 32) { const float d = tile[pp * P + c] - mean; q = fmaf(d, d, q); }
+    for (int k = 0; k < NS; ++k) mean += part[k * TP + pl];
+    mean /= C;
+    float q = 0.f;
+    for (int c = sl; c < C; c += NS) { const float d = tile[pl * P + c] - mean; q = fmaf(d, d, q); }
+    __syncthreads();                                      // every partial sum has been read
+    part[sl * TP + pl] = q;
+    __syncthreads();
+    if (sl == 0) {
+        float qq = 0.f;
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) q += __shfl_xor_sync(0xffffffffu, q, off);
-        if (lane == 0) { stat[pp] = mean; stat[TP + pp] = rsqrtf(q / C + a.eps); }
+        for (int k = 0; k < NS; ++k) qq += part[k * TP + pl];
+        const float rstd = rsqrtf(qq / C + a.eps);
+        stat[pl] = rstd; stat[TP + pl] = -mean * rstd;
     }
     __syncthreads();
-    const int pl = threadIdx.x % TP, cw = threadIdx.x / TP;      // TP = 32: a warp per channel; TP = 16: two channels per warp
-    if (pl < live) {
-        const float mean = stat[pl], rstd = stat[TP + pl];
-        for (int c = cw; c < C; c += 256 / TP) {
+    // C: thread = four consecutive pixels of one channel -> one 16-byte (fp32) or 8-byte (16-bit) store
+    constexpr int Q4 = TP / 4;                            // threads per channel
+    const int p4 = (threadIdx.x % Q4) * 4, cw = threadIdx.x / Q4;
+    if (p4 < live) {
+        float sc[4], sh[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { sc[i] = stat[p4 + i]; sh[i] = stat[TP + p4 + i]; }
+        const bool full = p4 + 4 <= live && ((a.out_cs | n0) & 3) == 0;
+        for (int c = cw; c < C; c += 256 / Q4) {
             const float w = a.lnw ? __ldg(a.lnw + c) : 1.f, bb = a.lnb ? __ldg(a.lnb + c) : 0.f;
-            ((Tout*)a.out)[(long long)c * a.out_cs + n0 + pl] = from_f<Tout>(fmaf((tile[pl * P + c] - mean) * rstd, w, bb));
+            float o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[i] = fmaf(fmaf(tile[(p4 + i) * P + c], sc[i], sh[i]), w, bb);
+            Tout* dst = (Tout*)a.out + (long long)c * a.out_cs + n0 + p4;
+            if (full) Vec<Tout, 4>::store(dst, o);
+            else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) if (p4 + i < live) dst[i] = from_f<Tout>(o[i]);
+            }
         }
     }
 }
@@ -231,7 +260,7 @@ int pixels_norm_to_planes(const ss2d_relayout_params* p, cudaStream_t st) {
     const size_t sr = dtype_size(p->rows_dtype), sp = dtype_size(p->planes_dtype);
     const int pv = sr == 2 ? 8 : 4;
     if (p->C % pv != 0) return SS2D_ENOTSUP;
-    if (!aligned_to(p->rows, 16) || !aligned_to(p->planes, sp) || !aligned_to(p->bias, 4) || !aligned_to(p->ln_weight, 4) ||
+    if (!aligned_to(p->rows, 16) || !aligned_to(p->planes, 16) || !aligned_to(p->bias, 16) || !aligned_to(p->ln_weight, 4) ||
         !aligned_to(p->ln_bias, 4))
         return SS2D_EINVAL_ALIGN;
     const long long cs = p->plane_stride ? p->plane_stride : p->N;
@@ -241,7 +270,7 @@ int pixels_norm_to_planes(const ss2d_relayout_params* p, cudaStream_t st) {
     a.in = p->rows; a.bias = (const float*)p->bias; a.lnw = (const float*)p->ln_weight; a.lnb = (const float*)p->ln_bias;
     a.out = p->planes; a.N = p->N; a.out_cs = cs; a.C = (int)p->C; a.eps = p->eps;
     const int tp = p->C <= 512 ? 32 : 16;
-    const size_t smem = ((size_t)tp * (p->C + 1) + 2 * tp) * sizeof(float);
+    const size_t smem = ((size_t)tp * (p->C + 1) + 256 + 2 * tp) * sizeof(float);
     if (smem > 200 * 1024) return SS2D_ENOTSUP;
     const long long ctas = (p->N + tp - 1) / tp;
     if (ctas > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
