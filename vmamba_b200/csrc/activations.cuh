@@ -33,8 +33,10 @@ __device__ __forceinline__ float2 gelu_pair_fast(float2 v) {
     const float2 q = __fmul2_rn(pl, make_float2(ex2_approx(arg.x), ex2_approx(arg.y)));      // erfc(|v| / sqrt 2)
     const float2 cdf2 = make_float2(v.x < 0.f ? q.x : 2.f - q.x, v.y < 0.f ? q.y : 2.f - q.y);   // 1 + erf(v / sqrt 2)
     float2 r = __fmul2_rn(__fmul2_rn(v, make_float2(0.5f, 0.5f)), cdf2);
-    if (v.x < -3.5f) r.x = act_f<ACT_GELU>(v.x);
-    if (v.y < -3.5f) r.y = act_f<ACT_GELU>(v.y);
+    if (fminf(v.x, v.y) < -3.5f) {       // far tail (rare): the exact form for whichever value is there
+        if (v.x < -3.5f) r.x = act_f<ACT_GELU>(v.x);
+        if (v.y < -3.5f) r.y = act_f<ACT_GELU>(v.y);
+    }
     return r;
 }
 

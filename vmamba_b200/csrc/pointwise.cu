@@ -1,9 +1,10 @@
 // Elementwise producers around the SS2D core, channel-first maps, each one pass over HBM:
 //   bias_act      y = act(x + bias[d])                       (fc1 bias + GELU of the MLP, in place)
 //   dwconv3x3_act y = act(depthwise 3x3 conv of x, pad 1)    (the conv + SiLU in front of the core)
-// Rounding follows the chain of separate kernels these replace: the convolution / bias sum is
-// formed in fp32, rounded to the storage type, then the activation is evaluated in fp32 on that
-// rounded value and rounded again.
+// Rounding: the depthwise convolution sum is formed in fp32 and rounded to the storage type before the
+// activation (what the stand-alone convolution would hand over); the bias + GELU of 16-bit maps is
+// evaluated in fp32 on stored value + bias and rounded once (the reference rounds accumulator + bias
+// once inside its GEMM; the accumulator itself is not available here).
 #include "activations.cuh"
 
 namespace ss2d {
@@ -13,53 +14,60 @@ struct BiasActArgs {
     const void* x;
     const float* bias;
     void* y;
-    long long items;     // B * D * (L / PV)
+    long long rows;      // B * D rows of L elements (D rows of B * L for channel-major maps)
     int D, nv;           // nv = L / PV vectors per row
     int rows_per_channel;   // 1 for (B, D, ...) maps (channel = row % D); B for (D, B, ...) maps (channel = row / B)
+    int chunks_per_row;     // CTAs per row
 };
 
+// A CTA works inside ONE row, so the channel (and its bias) is found once per CTA and the element
+// loop has no division: the kernel is bound by instruction issue (the erf of GELU), not by HBM.
 template <typename T, int PV, int ACT>
 __global__ void __launch_bounds__(256) bias_act_kernel(const BiasActArgs a) {
     // x may be y: a store orders every later load behind it, so each pass loads kU vectors first
     constexpr int kU = 4;
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long it0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; it0 < a.items; it0 += kU * stride) {
+    const long long row = blockIdx.x / a.chunks_per_row;
+    const int chunk = blockIdx.x - (int)row * a.chunks_per_row;
+    const int d = (int)((row / a.rows_per_channel) % a.D);
+    const float b = a.bias ? __ldg(a.bias + d) : 0.f;
+    const T* __restrict__ xr = (const T*)a.x + row * (long long)a.nv * PV;
+    T* __restrict__ yr = (T*)a.y + row * (long long)a.nv * PV;
+    for (int it0 = chunk * 256 + threadIdx.x; it0 < a.nv; it0 += kU * 256 * a.chunks_per_row) {
         typename Vec<T, PV>::Raw raw[kU];
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
-            const long long it = it0 + u * stride;
-            if (it < a.items) raw[u] = Vec<T, PV>::template load_raw<false>((const T*)a.x + it * PV);
+            const int it = it0 + u * 256 * a.chunks_per_row;
+            if (it < a.nv) raw[u] = Vec<T, PV>::template load_raw<false>(xr + (long long)it * PV);
         }
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
-            const long long it = it0 + u * stride;
-            if (it >= a.items) break;
-            const long long row = it / a.nv;
-            const int d = (int)((row / a.rows_per_channel) % a.D);
-            const float b = a.bias ? __ldg(a.bias + d) : 0.f;
+            const int it = it0 + u * 256 * a.chunks_per_row;
+            if (it >= a.nv) break;
             float v[PV];
             Vec<T, PV>::unpack(raw[u], v);
             if constexpr (ACT == ACT_GELU && sizeof(T) == 2 && PV >= 2) {
 #pragma unroll
                 for (int i = 0; i < PV; i += 2) {
-                    const float2 r = gelu_pair_fast(make_float2(round_to<T>(v[i] + b), round_to<T>(v[i + 1] + b)));
+                    const float2 r = gelu_pair_fast(make_float2(v[i] + b, v[i + 1] + b));
                     v[i] = r.x; v[i + 1] = r.y;
                 }
             } else {
 #pragma unroll
                 for (int i = 0; i < PV; ++i) v[i] = act_f<ACT>(round_to<T>(v[i] + b));
             }
-            Vec<T, PV>::store((T*)a.y + it * PV, v);
+            Vec<T, PV>::store(yr + (long long)it * PV, v);
         }
     }
 }
 
 template <typename T, int PV>
-static void launch_bias_act(const BiasActArgs& a, int act, cudaStream_t st) {
-    long long ctas = (a.items + 255) / 256;
-    const long long cap = 148LL * 8 * 4;          // a few waves of resident CTAs, grid-stride beyond
-    if (ctas > cap) ctas = cap;
-    const unsigned g = (unsigned)ctas;
+static void launch_bias_act(BiasActArgs a, int act, cudaStream_t st) {
+    // about 4 vectors per thread; at least enough CTAs for a few waves
+    int chunks = (a.nv + 256 * 4 - 1) / (256 * 4);
+    if (chunks < 1) chunks = 1;
+    while ((long long)chunks * a.rows > (1LL << 30) && chunks > 1) chunks >>= 1;
+    a.chunks_per_row = chunks;
+    const unsigned g = (unsigned)(a.rows * chunks);
     if (act == ACT_GELU) bias_act_kernel<T, PV, ACT_GELU><<<g, 256, 0, st>>>(a);
     else if (act == ACT_SILU) bias_act_kernel<T, PV, ACT_SILU><<<g, 256, 0, st>>>(a);
     else bias_act_kernel<T, PV, ACT_NONE><<<g, 256, 0, st>>>(a);
@@ -68,7 +76,7 @@ static void launch_bias_act(const BiasActArgs& a, int act, cudaStream_t st) {
 template <typename T>
 static void launch_bias_act_v(BiasActArgs a, int pv, long long rows, long long L, int act, cudaStream_t st) {
     a.nv = (int)(L / pv);
-    a.items = rows * a.nv;
+    a.rows = rows;
     if (pv == 8) launch_bias_act<T, 8>(a, act, st);
     else if (pv == 4) launch_bias_act<T, 4>(a, act, st);
     else if (pv == 2) launch_bias_act<T, 2>(a, act, st);
@@ -90,7 +98,7 @@ int bias_act(const ss2d_pointwise_params* p, cudaStream_t st) {
     fit((long long)(reinterpret_cast<uintptr_t>(p->x) / s));
     fit((long long)(reinterpret_cast<uintptr_t>(p->y) / s));
     BiasActArgs a;
-    a.x = p->x; a.bias = (const float*)p->bias; a.y = p->y; a.D = (int)p->D; a.nv = 0; a.items = 0;
+    a.x = p->x; a.bias = (const float*)p->bias; a.y = p->y; a.D = (int)p->D; a.nv = 0; a.rows = 0; a.chunks_per_row = 1;
     a.rows_per_channel = p->channel_major ? (int)p->B : 1;
     const long long rows = p->B * p->D;
     if (p->dtype == SS2D_F32) launch_bias_act_v<float>(a, pv, rows, L, p->act, st);
