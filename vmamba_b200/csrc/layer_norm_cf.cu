@@ -3,9 +3,9 @@
 //
 // An "item" is PV consecutive pixels of one image; items are numbered across the whole batch so
 // that every lane of every warp has work whatever the map size (L = 49 or 196 pixels per image
-// would otherwise leave most of a 32-pixel tile empty).  threadIdx.x runs along items (each global
-// access of a warp is one contiguous PV*32-element run per channel), threadIdx.y splits the D
-// channels.  Mean and variance are the two-pass kind (sum of squared deviations), like the torch
+// would otherwise leave most of a tile empty).  threadIdx.x runs along the TX items of a CTA (a
+// warp's global access is one contiguous run of PV*TX elements per channel, two channels per
+// warp), threadIdx.y splits the D channels.  Mean and variance are the two-pass kind (sum of squared deviations), like the torch
 // operator this replaces; values stay in registers between the passes when D / NTY fits, else
 // they are re-read (from L1/L2).
 #include "common.cuh"
@@ -26,11 +26,11 @@ struct NormArgs {
     int skip_norm;           // 1: out = s converted, no statistics (a fused add + cast + layout change)
 };
 
-template <typename Tio, int NTY, int CACHE, int PV>
-__global__ void __launch_bounds__(32 * NTY) layer_norm_cf_kernel(const NormArgs a) {
-    __shared__ float red[NTY][32][PV];
+template <typename Tio, int NTY, int CACHE, int PV, int TX>
+__global__ void __launch_bounds__(TX * NTY) layer_norm_cf_kernel(const NormArgs a) {
+    __shared__ float red[NTY][TX][PV];
     const int tx = threadIdx.x, ty = threadIdx.y;
-    const int item = blockIdx.x * 32 + tx;
+    const int item = blockIdx.x * TX + tx;
     const bool live = item < a.items;
     const int bimg = live ? item / a.nv : 0;
     const long long pix = (long long)(live ? (item - bimg * a.nv) : 0) * PV;
@@ -214,16 +214,22 @@ __global__ void __launch_bounds__(32 * NTY) layer_norm_cf_kernel(const NormArgs 
     }
 }
 
+// 16 items per CTA: CTAs of 128 to 512 threads, several per SM, so that the load phase of one overlaps the
+// reduction / store phase of another (32 items per CTA, up to 1024 threads, was 12 % slower over a backbone
+// forward); a warp's access is still one run of 16 * PV pixels per channel.
+constexpr int kItemsPerCta = 16;
+
 template <typename Tio, int NTY, int CACHE, int PV>
 static void launch_one(const NormArgs& a, cudaStream_t st) {
-    layer_norm_cf_kernel<Tio, NTY, CACHE, PV><<<(unsigned)((a.items + 31) / 32), dim3(32, NTY), 0, st>>>(a);
+    layer_norm_cf_kernel<Tio, NTY, CACHE, PV, kItemsPerCta>
+        <<<(unsigned)((a.items + kItemsPerCta - 1) / kItemsPerCta), dim3(kItemsPerCta, NTY), 0, st>>>(a);
 }
 
 template <typename Tio>
 static void launch_norm(NormArgs a, int pv, long long B, cudaStream_t st) {
     const int D = a.D;
-    // registers hold CACHE * PV values per thread: at most 48 for CTAs of up to 512 threads,
-    // at most 24 for the 1024-thread CTAs (64 registers per thread)
+    // registers hold CACHE * PV values per thread: at most 48 while D <= 192, at most 24 beyond
+    // (more threads per CTA: keep about 64 registers per thread so that several CTAs share an SM)
     if (D > 32 * 12) pv = 1;
     else if (D > 16 * 12 && pv > 2) pv = 2;
     a.nv = a.L / pv;
