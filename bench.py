@@ -281,6 +281,14 @@ def run_ours(args):
         print(json.dumps({"roofline": roofline_of_core(model, peak, kind, args.roofline_batch, args.steps)}), flush=True)
         return
 
+    if args.forward_only:      # plain (un-graphed) forwards and nothing else: the case profiler captures use
+        img = torch.randn((BATCH, 3, IMG, IMG), device=f"cuda:{local}").to(torch.bfloat16)
+        for _ in range(max(1, args.steps)):
+            out = model(img)
+        torch.cuda.synchronize()
+        print(json.dumps({"forward_only": True, "batch": BATCH, "forwards": max(1, args.steps), "logits": list(out.shape)}), flush=True)
+        return
+
     # synthetic images: N(0,1), seeded per rank, bf16 in pinned host memory
     g = torch.Generator().manual_seed(1234 + rank)
     host_img = torch.randn((BATCH, 3, IMG, IMG), generator=g).to(torch.bfloat16).pin_memory()
@@ -439,6 +447,7 @@ def main():
     ap.add_argument("--sweep-gb", type=float, default=2.0, help="input gigabytes per sweep cell")
     ap.add_argument("--roofline-only", action="store_true", help="time only the fused SS2D core chain of stage 0")
     ap.add_argument("--roofline-batch", type=int, default=None, help="batch for --roofline-only (default 128)")
+    ap.add_argument("--forward-only", action="store_true", help="run --steps plain forwards of the model and exit (profiler captures)")
     args = ap.parse_args()
     if args.op_sweep:
         op_sweep(args)
