@@ -124,7 +124,7 @@ struct DwArgs {
     int BH, nb, units;              // rows per band, bands per plane, planes * nb
     int planes_per_channel;         // 1 for (B, D, H, W) maps, B for (D, B, H, W) maps
     int nrb;                        // row blocks of 8 per band
-    unsigned magic_fr, magic_nvw, magic_W, magic_nrb, magic_ppc, magic_nb, magic_frnvw, magic_nrbW;
+    unsigned magic_fr, magic_nvw, magic_W, magic_nrb, magic_ppc, magic_nb, magic_frnvw, magic_nrbW, magic_W2, magic_nrbW2;
 };
 
 __device__ __forceinline__ int mdiv(int n, unsigned magic) { return magic ? (int)__umulhi((unsigned)n, magic) : n; }   // magic 0: divisor 1
@@ -162,6 +162,45 @@ __global__ void __launch_bounds__(256) dwconv3x3_act_kernel(const DwArgs a) {
     __syncthreads();
     constexpr int kRows = 8;
     const int nrb = a.nrb;
+    if ((W & 1) == 0) {
+        // two neighbouring columns per thread: four frame values per row (two 8-byte loads) serve eighteen
+        // FMAs, and the two results leave as one store
+        const int W2 = W >> 1;
+        for (int i = threadIdx.x; i < np * nrb * W2; i += blockDim.x) {
+            const int pl = mdiv(i, a.magic_nrbW2), rem = i - pl * (nrb * W2);
+            const int rb = mdiv(rem, a.magic_W2), w = (rem - rb * W2) * 2;
+            const int u = unit0 + pl;
+            const int plane = mdiv(u, a.magic_nb), band = u - plane * a.nb;
+            const int r0 = rb * kRows;
+            const int rows = min(min(r0 + kRows, a.BH), H - band * a.BH) - r0;
+            if (rows <= 0) continue;
+            const int d = mdiv(plane, a.magic_ppc) % a.D;
+            const T* __restrict__ wk = (const T*)a.w + d * 9;
+            float k[9];
+#pragma unroll
+            for (int j = 0; j < 9; ++j) k[j] = to_f<T>(wk[j]);
+            const float b = a.bias ? __ldg(a.bias + d) : 0.f;
+            const float* src = sm + pl * frame + r0 * Wp + w;
+            float2 ta = *reinterpret_cast<const float2*>(src), tb = *reinterpret_cast<const float2*>(src + 2);
+            float2 ma = *reinterpret_cast<const float2*>(src + Wp), mb = *reinterpret_cast<const float2*>(src + Wp + 2);
+            T* __restrict__ out = (T*)a.y + ((long long)plane * H + band * a.BH + r0) * W + w;
+            for (int r = 0; r < rows; ++r) {
+                const float* bp = src + (r + 2) * Wp;
+                const float2 ba = *reinterpret_cast<const float2*>(bp), bb = *reinterpret_cast<const float2*>(bp + 2);
+                float a0 = b, a1 = b;
+                a0 = fmaf(k[0], ta.x, a0); a0 = fmaf(k[1], ta.y, a0); a0 = fmaf(k[2], tb.x, a0);
+                a1 = fmaf(k[0], ta.y, a1); a1 = fmaf(k[1], tb.x, a1); a1 = fmaf(k[2], tb.y, a1);
+                a0 = fmaf(k[3], ma.x, a0); a0 = fmaf(k[4], ma.y, a0); a0 = fmaf(k[5], mb.x, a0);
+                a1 = fmaf(k[3], ma.y, a1); a1 = fmaf(k[4], mb.x, a1); a1 = fmaf(k[5], mb.y, a1);
+                a0 = fmaf(k[6], ba.x, a0); a0 = fmaf(k[7], ba.y, a0); a0 = fmaf(k[8], bb.x, a0);
+                a1 = fmaf(k[6], ba.y, a1); a1 = fmaf(k[7], bb.x, a1); a1 = fmaf(k[8], bb.y, a1);
+                const float o[2] = {act_f<ACT>(round_to<T>(a0)), act_f<ACT>(round_to<T>(a1))};
+                Vec<T, 2>::store(out + r * W, o);
+                ta = ma; tb = mb; ma = ba; mb = bb;
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < np * nrb * W; i += blockDim.x) {
         const int pl = mdiv(i, a.magic_nrbW), rem = i - pl * (nrb * W);
         const int rb = mdiv(rem, a.magic_W), w = rem - rb * W;
@@ -221,6 +260,7 @@ static int launch_dw_v(DwArgs a, int pv, int act, size_t smem, unsigned grid, cu
     a.magic_fr = magic(FR); a.magic_nvw = magic(a.nvw); a.magic_W = magic(a.W); a.magic_nrb = magic(a.nrb);
     a.magic_ppc = magic(a.planes_per_channel); a.magic_nb = magic(a.nb);
     a.magic_frnvw = magic((long long)FR * a.nvw); a.magic_nrbW = magic((long long)a.nrb * a.W);
+    a.magic_W2 = magic(a.W / 2); a.magic_nrbW2 = magic((long long)a.nrb * (a.W / 2));
     if (pv == 8) return launch_dw<T, 8>(a, act, smem, grid, st);
     if (pv == 4) return launch_dw<T, 4>(a, act, smem, grid, st);
     if (pv == 2) return launch_dw<T, 2>(a, act, smem, grid, st);
