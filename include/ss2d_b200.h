@@ -207,6 +207,8 @@ int ss2d_dwconv3x3_act(const ss2d_pointwise_params *p, void *cuda_stream);
  *   dt_weight (4, D, R) act_dtype contiguous (dt_projs.weight viewed per route)
  *   delta[k]  (B, D, L) act_dtype  = dt_weight[k] . x_dbl[:, k, :R]  in the orientation order of route k
  *   bc[k]     (B, 2N, L) act_dtype = x_dbl[:, k, R:] (B rows then C rows) in the same order
+ * 16-bit maps with R > 12 run the contraction on the tensor cores (mma.sync, fp32 accumulation); the result is
+ * rounded to act_dtype once, like the library GEMM this replaces.
  * -------------------------------------------------------------------------------- */
 typedef struct ss2d_expand_params {
     const void *x_dbl;
@@ -222,7 +224,14 @@ typedef struct ss2d_expand_params {
     int64_t B, D, R, N, H, W;
     int32_t act_dtype;
     int32_t reserved0;
+    void *workspace;                    /* optional: ss2d_route_expand_workspace_bytes() bytes, 16-byte aligned */
+    int64_t workspace_bytes;
 } ss2d_expand_params;
+
+/* With a workspace the projected rows of the two column-major routes are transposed once, plane by plane, by a
+ * small kernel in front (2 * (R+2N) * B * H * W elements), and the expansion reads every route contiguously;
+ * without one (NULL) it gathers them with strided 2-byte loads, which costs about a third more time. */
+int64_t ss2d_route_expand_workspace_bytes(const ss2d_expand_params *p);
 
 int ss2d_route_expand(const ss2d_expand_params *p, void *cuda_stream);
 

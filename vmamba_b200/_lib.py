@@ -63,7 +63,7 @@ class ExpandParams(ctypes.Structure):
                 ("delta_batch_stride", _i64 * ROUTES), ("bc_batch_stride", _i64 * ROUTES),
                 ("delta_channel_stride", _i64 * ROUTES), ("bc_row_stride", _i64 * ROUTES),
                 ("B", _i64), ("D", _i64), ("R", _i64), ("N", _i64), ("H", _i64), ("W", _i64),
-                ("act_dtype", _i32), ("reserved0", _i32)]
+                ("act_dtype", _i32), ("reserved0", _i32), ("workspace", _vp), ("workspace_bytes", _i64)]
 
 
 class PointwiseParams(ctypes.Structure):
@@ -104,6 +104,7 @@ EXPORTS = {
     "ss2d_core_static_capacity": (_i64, []),
     "ss2d_layer_norm_cf": (ctypes.c_int, [ctypes.POINTER(NormParams), _vp]),
     "ss2d_route_expand": (ctypes.c_int, [ctypes.POINTER(ExpandParams), _vp]),
+    "ss2d_route_expand_workspace_bytes": (_i64, [ctypes.POINTER(ExpandParams)]),
     "ss2d_stem_conv_norm_act": (ctypes.c_int, [ctypes.POINTER(StemParams), _vp]),
     "ss2d_pixels_norm_to_planes": (ctypes.c_int, [ctypes.POINTER(RelayoutParams), _vp]),
     "ss2d_planes_to_pixels": (ctypes.c_int, [ctypes.POINTER(RelayoutParams), _vp]),

@@ -15,6 +15,7 @@ int core_fwd(const ss2d_core_params* p, cudaStream_t st);
 int core_fwd_static(const ss2d_core_params* p, cudaStream_t st);
 long long core_static_capacity();
 int route_expand(const ss2d_expand_params* p, cudaStream_t st);
+long long route_expand_workspace_bytes(const ss2d_expand_params* p);
 int stem_conv_norm_act(const ss2d_stem_params* p, cudaStream_t st);
 int pixels_norm_to_planes(const ss2d_relayout_params* p, cudaStream_t st);
 int planes_to_pixels(const ss2d_relayout_params* p, cudaStream_t st);
@@ -44,6 +45,7 @@ int ss2d_core_fwd_static(const ss2d_core_params* p, void* stream) { return ss2d:
 int64_t ss2d_core_static_capacity(void) { return ss2d::core_static_capacity(); }
 
 int ss2d_route_expand(const ss2d_expand_params* p, void* stream) { return ss2d::route_expand(p, (cudaStream_t)stream); }
+int64_t ss2d_route_expand_workspace_bytes(const ss2d_expand_params* p) { return ss2d::route_expand_workspace_bytes(p); }
 
 int ss2d_bias_act(const ss2d_pointwise_params* p, void* stream) { return ss2d::bias_act(p, (cudaStream_t)stream); }
 int ss2d_dwconv3x3_act(const ss2d_pointwise_params* p, void* stream) { return ss2d::dwconv3x3_act(p, (cudaStream_t)stream); }

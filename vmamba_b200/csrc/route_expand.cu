@@ -29,6 +29,8 @@ struct ExpandArgs {
     long long d_bs[4], d_cs[4], bc_bs[4], bc_rs[4];   // delta: batch / channel strides; B-C rows: batch / row strides
     int B, D, R, N2, C, H, W, L;       // N2 = 2N, C = R + 2N; L = run length (H*W, or B*H*W when images are adjacent)
     int Limg;                          // H * W
+    const void* xt;                    // transposed rows of routes 1, 3: (2, C, Btot, Limg), or NULL (gather)
+    long long xt_rs;                   // Btot * Limg
     int items_per_plane, items_total;  // L / VEC, B * L / VEC
 };
 
@@ -66,6 +68,8 @@ __global__ void __launch_bounds__(kExpThreads) route_expand_kernel(const ExpandA
                 const T* rp = src + (long long)row * a.xd_rs;
                 if (!col) {
                     Vec<T, VEC>::load(rp + q0, v);
+                } else if (a.xt) {
+                    Vec<T, VEC>::load((const T*)a.xt + ((long long)(k >> 1) * a.C + row) * a.xt_rs + (long long)b * a.Limg + q0, v);
                 } else {
                     int w = w0, h = h0, base = img0;      // a run may continue into the next image
 #pragma unroll
@@ -134,6 +138,160 @@ __global__ void __launch_bounds__(kExpThreads) route_expand_kernel(const ExpandA
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Tensor-core variant for 16-bit maps: delta tile (128 channels x 64 pixels) = W (128 x R) . X (R x 64)
+// with mma.sync m16n8k16 (fp32 accumulation, R zero-padded to a multiple of 16).  The contraction is
+// far too short for the tensor pipe to matter as arithmetic; what it buys is that the shared-memory
+// traffic and the issue slots of the FMA loop disappear, leaving the kernel with the write of delta.
+// Warp w owns channels [16 w, 16 w + 16) of the CTA's slice and all 64 pixels; the accumulators go
+// through a shared tile so that every channel row leaves as 16-byte vectors.
+constexpr int kMmaPix = 64;
+
+template <typename T> struct MmaK16;
+template <> struct MmaK16<__nv_bfloat16> {
+    static __device__ __forceinline__ void run(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+    }
+};
+template <> struct MmaK16<__half> {
+    static __device__ __forceinline__ void run(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+    }
+};
+
+constexpr int kMmaTilesPerCta = 8;      // pixel tiles per CTA: the staged weights serve 512 pixels
+
+template <typename T, int KP>
+__global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs a) {
+    constexpr int KPAD = KP + 8;                  // row pitch (elements) of the operand tiles: conflict-free fragment loads
+    constexpr int OPAD = kMmaPix + 8;
+    __shared__ __align__(16) T Ws[kDChunk * KPAD];     // [channel][k]
+    __shared__ __align__(16) T Xt[kMmaPix * KPAD];     // [pixel][k]
+    __shared__ __align__(16) T Os[kDChunk * OPAD];     // [channel][pixel]
+    const int k = blockIdx.y;
+    const bool col = (k & 1) != 0;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tiles_per_run = (a.L + kMmaPix - 1) / kMmaPix;
+    const int groups_per_run = (tiles_per_run + kMmaTilesPerCta - 1) / kMmaTilesPerCta;
+    const int b = blockIdx.x / groups_per_run;
+    const int tile0 = (blockIdx.x - b * groups_per_run) * kMmaTilesPerCta;
+    const T* __restrict__ xd = (const T*)a.xd + (long long)k * a.xd_ks + (long long)b * a.xd_bs;
+    const int dc = blockIdx.z * kDChunk;
+    const int dn = min(kDChunk, a.D - dc);
+    const T zero = from_f<T>(0.f);
+
+    // ---- weights of this channel slice, [channel][k], zero beyond R and beyond the slice ----------------
+    const T* __restrict__ wk = (const T*)a.wdt + (long long)k * a.D * a.R;
+    for (int i = tid; i < kDChunk * KP; i += 256) {
+        const int dl = i / KP, r = i - dl * KP;
+        Ws[dl * KPAD + r] = (dl < dn && r < a.R) ? wk[(long long)(dc + dl) * a.R + r] : zero;
+    }
+    // one projected row of eight pixels, gathered column-major for the odd routes
+    auto fetch8 = [&](int row, int q, T (&v)[8]) {
+        const T* rp = xd + (long long)row * a.xd_rs;
+        if (!col) {
+            *reinterpret_cast<uint4*>(v) = __ldg(reinterpret_cast<const uint4*>(rp + q));
+        } else if (a.xt) {
+            *reinterpret_cast<uint4*>(v) = __ldg(reinterpret_cast<const uint4*>(
+                (const T*)a.xt + ((long long)(k >> 1) * a.C + row) * a.xt_rs + (long long)b * a.Limg + q));
+        } else {
+            const int img0 = (q / a.Limg) * a.Limg, qi = q - img0;
+            int w = qi / a.H, h = qi - w * a.H, base = img0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = rp[base + h * a.W + w];
+                if (++h == a.H) { h = 0; if (++w == a.W) { w = 0; base += a.Limg; } }
+            }
+        }
+    };
+    const int g = lane >> 2, t4 = lane & 3;
+    const int m0 = warp * 16;
+    for (int tt = 0; tt < kMmaTilesPerCta; ++tt) {
+        const int q0 = (tile0 + tt) * kMmaPix;
+        if (q0 >= a.L) break;                        // uniform over the CTA
+        // ---- X tile, transposed to [pixel][k]; rows R .. KP-1 are zero.  Consecutive threads take consecutive
+        //      rows of the same eight pixels, so the transposed stores of a warp fall into consecutive words.
+        for (int i = tid; i < KP * (kMmaPix / 8); i += 256) {
+            const int p0 = (i / KP) * 8, r = i - (i / KP) * KP;
+            T v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = zero;
+            if (r < a.R && q0 + p0 < a.L) fetch8(r, q0 + p0, v);      // L is a multiple of 8: a chunk is wholly inside or outside
+#pragma unroll
+            for (int j = 0; j < 8; ++j) Xt[(p0 + j) * KPAD + r] = v[j];
+        }
+        // ---- B / C rows pass through (first channel slice only) ---------------------------------------------
+        if (blockIdx.z == 0) {
+            for (int i = tid; i < a.N2 * (kMmaPix / 8); i += 256) {
+                const int n = i / (kMmaPix / 8), p0 = (i - n * (kMmaPix / 8)) * 8;
+                const int q = q0 + p0;
+                if (q >= a.L) continue;
+                T v[8];
+                fetch8(a.R + n, q, v);
+                *reinterpret_cast<uint4*>((T*)a.bc[k] + b * a.bc_bs[k] + (long long)n * a.bc_rs[k] + q) = *reinterpret_cast<const uint4*>(v);
+            }
+        }
+        __syncthreads();                             // X tile (and, first time, the weights) in place
+
+        // ---- 16 channels x 64 pixels per warp ---------------------------------------------------------------
+        float acc[kMmaPix / 8][4];
+#pragma unroll
+        for (int nt = 0; nt < kMmaPix / 8; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+#pragma unroll
+        for (int k0 = 0; k0 < KP; k0 += 16) {
+            uint32_t af[4];
+            af[0] = *reinterpret_cast<const uint32_t*>(&Ws[(m0 + g) * KPAD + k0 + 2 * t4]);
+            af[1] = *reinterpret_cast<const uint32_t*>(&Ws[(m0 + g + 8) * KPAD + k0 + 2 * t4]);
+            af[2] = *reinterpret_cast<const uint32_t*>(&Ws[(m0 + g) * KPAD + k0 + 2 * t4 + 8]);
+            af[3] = *reinterpret_cast<const uint32_t*>(&Ws[(m0 + g + 8) * KPAD + k0 + 2 * t4 + 8]);
+#pragma unroll
+            for (int nt = 0; nt < kMmaPix / 8; ++nt) {
+                uint32_t bf[2];
+                bf[0] = *reinterpret_cast<const uint32_t*>(&Xt[(nt * 8 + g) * KPAD + k0 + 2 * t4]);
+                bf[1] = *reinterpret_cast<const uint32_t*>(&Xt[(nt * 8 + g) * KPAD + k0 + 2 * t4 + 8]);
+                MmaK16<T>::run(acc[nt], af, bf);
+            }
+        }
+        // ---- accumulators -> shared tile -> 16-byte stores along the pixels -----------------------------------
+#pragma unroll
+        for (int nt = 0; nt < kMmaPix / 8; ++nt) {
+            T lo[2] = {from_f<T>(acc[nt][0]), from_f<T>(acc[nt][1])};
+            T hi[2] = {from_f<T>(acc[nt][2]), from_f<T>(acc[nt][3])};
+            *reinterpret_cast<uint32_t*>(&Os[(m0 + g) * OPAD + nt * 8 + 2 * t4]) = *reinterpret_cast<const uint32_t*>(lo);
+            *reinterpret_cast<uint32_t*>(&Os[(m0 + g + 8) * OPAD + nt * 8 + 2 * t4]) = *reinterpret_cast<const uint32_t*>(hi);
+        }
+        __syncthreads();                             // output tile complete; every read of the X tile is done
+        T* __restrict__ dout = (T*)a.delta[k] + b * a.d_bs[k] + q0;
+        for (int i = tid; i < kDChunk * (kMmaPix / 8); i += 256) {
+            const int dl = i / (kMmaPix / 8), p0 = (i - dl * (kMmaPix / 8)) * 8;
+            if (dl < dn && q0 + p0 < a.L)
+                *reinterpret_cast<uint4*>(dout + (long long)(dc + dl) * a.d_cs[k] + p0) = *reinterpret_cast<const uint4*>(&Os[dl * OPAD + p0]);
+        }
+        // the next tile's X fill may start at once (other buffer than Os); its barrier orders the next Os writes
+        // behind these reads
+    }
+}
+
+template <typename T>
+static int launch_expand_mma(const ExpandArgs& a, cudaStream_t st) {
+    const long long tiles_per_run = (a.L + kMmaPix - 1) / kMmaPix;
+    const long long tiles = (long long)a.B * ((tiles_per_run + kMmaTilesPerCta - 1) / kMmaTilesPerCta);
+    if (tiles > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
+    const dim3 grid((unsigned)tiles, 4, (unsigned)((a.D + kDChunk - 1) / kDChunk));
+    const int kp = (a.R + 15) / 16 * 16;
+    if (kp == 16) route_expand_mma_kernel<T, 16><<<grid, 256, 0, st>>>(a);
+    else if (kp == 32) route_expand_mma_kernel<T, 32><<<grid, 256, 0, st>>>(a);
+    else if (kp == 48) route_expand_mma_kernel<T, 48><<<grid, 256, 0, st>>>(a);
+    else if (kp == 64) route_expand_mma_kernel<T, 64><<<grid, 256, 0, st>>>(a);
+    else return SS2D_ENOTSUP;
+    count_launch();
+    return check_launch();
+}
+
 template <typename T, int VEC, int NI>
 static int launch_expand(const ExpandArgs& a, cudaStream_t st) {
     const size_t smem = ((size_t)a.C * NI * VEC + (size_t)a.R * kDChunk) * sizeof(float);
@@ -161,6 +319,92 @@ static int launch_expand_v(const ExpandArgs& a, int vec, cudaStream_t st) {
         case 2: return launch_expand_ni<T, 2>(a, st);
         default: return launch_expand_ni<T, 1>(a, st);
     }
+}
+
+// Plane transposes of the projected rows of the two column-major routes: (route 1|3, row c, image b) plane
+// H x W (row-major) -> W x H, written as (2, C, Btot, L).  A CTA takes a few planes through shared memory
+// (pitch W + 1), reads and writes coalesced.
+struct TransArgs {
+    const void* xd;
+    void* xt;
+    long long xd_bs, xd_ks, xd_rs;
+    int C, B, H, W, L, planes, vec_ok;  // planes = 2 * C * B; vec_ok: every plane start is 16-byte aligned
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) plane_transpose_kernel(const TransArgs a) {
+    extern __shared__ __align__(16) unsigned char traw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int P = a.W + 1, psz = a.H * P;
+    T* tile = reinterpret_cast<T*>(traw) + (size_t)warp * psz;     // one plane per warp: no CTA barrier
+    constexpr int PV = 16 / (int)sizeof(T);
+    const bool vec = (a.L % PV) == 0 && a.vec_ok;
+    for (int pid = blockIdx.x * nwarps + warp; pid < a.planes; pid += gridDim.x * nwarps) {
+        const int b = pid % a.B, c = (pid / a.B) % a.C, kk = pid / (a.B * a.C);
+        const T* src = (const T*)a.xd + (long long)(2 * kk + 1) * a.xd_ks + (long long)b * a.xd_bs + (long long)c * a.xd_rs;
+        T* dst = (T*)a.xt + (long long)pid * a.L;
+        if (vec) {
+            for (int e = lane * PV; e < a.L; e += 32 * PV) {
+                T v[PV];
+                *reinterpret_cast<uint4*>(v) = __ldg(reinterpret_cast<const uint4*>(src + e));
+                int h = e / a.W, w = e - h * a.W;
+#pragma unroll
+                for (int i = 0; i < PV; ++i) {
+                    tile[h * P + w] = v[i];
+                    if (++w == a.W) { w = 0; ++h; }
+                }
+            }
+            __syncwarp();
+            for (int q = lane * PV; q < a.L; q += 32 * PV) {
+                T v[PV];
+                int w = q / a.H, h = q - w * a.H;
+#pragma unroll
+                for (int i = 0; i < PV; ++i) {
+                    v[i] = tile[h * P + w];
+                    if (++h == a.H) { h = 0; ++w; }
+                }
+                *reinterpret_cast<uint4*>(dst + q) = *reinterpret_cast<const uint4*>(v);
+            }
+        } else {
+            for (int e = lane; e < a.L; e += 32) { const int h = e / a.W, w = e - h * a.W; tile[h * P + w] = src[e]; }
+            __syncwarp();
+            for (int q = lane; q < a.L; q += 32) { const int w = q / a.H, h = q - w * a.H; dst[q] = tile[h * P + w]; }
+        }
+        __syncwarp();
+    }
+}
+
+static bool transpose_fits(const ss2d_expand_params* p) {
+    return (size_t)p->H * (p->W + 1) * dtype_size(p->act_dtype) <= 16 * 1024;
+}
+
+long long route_expand_workspace_bytes(const ss2d_expand_params* p) {
+    if (!p || !dtype_ok(p->act_dtype) || p->B <= 0 || p->R <= 0 || p->N <= 0 || p->H <= 0 || p->W <= 0) return -1;
+    if (!transpose_fits(p)) return 0;
+    return 2 * (p->R + 2 * p->N) * p->B * p->H * p->W * (long long)dtype_size(p->act_dtype);
+}
+
+template <typename T>
+static int launch_transpose(const ss2d_expand_params* p, cudaStream_t st) {
+    TransArgs t;
+    t.xd = p->x_dbl; t.xt = p->workspace;
+    t.xd_bs = p->x_dbl_batch_stride; t.xd_ks = p->x_dbl_route_stride; t.xd_rs = p->x_dbl_row_stride ? p->x_dbl_row_stride : p->H * p->W;
+    t.C = (int)(p->R + 2 * p->N); t.B = (int)p->B; t.H = (int)p->H; t.W = (int)p->W; t.L = (int)(p->H * p->W);
+    t.planes = 2 * t.C * t.B;
+    const size_t pv = 16 / sizeof(T);
+    t.vec_ok = (t.xd_bs % pv) == 0 && (t.xd_ks % pv) == 0 && (t.xd_rs % pv) == 0 && aligned_to(p->x_dbl, 16) && aligned_to(p->workspace, 16);
+    const size_t plane_bytes = ((size_t)t.H * (t.W + 1) * sizeof(T) + 15) / 16 * 16;
+    int warps = (int)(48 * 1024 / plane_bytes);
+    if (warps < 1) warps = 1;
+    if (warps > 8) warps = 8;
+    const size_t smem = plane_bytes * warps;
+    auto kern = plane_transpose_kernel<T>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return SS2D_ECUDA;
+    long long ctas = (t.planes + warps - 1) / warps;
+    if (ctas > 148 * 16) ctas = 148 * 16;
+    kern<<<(unsigned)ctas, warps * 32, smem, st>>>(t);
+    count_launch();
+    return check_launch();
 }
 
 int route_expand(const ss2d_expand_params* p, cudaStream_t st) {
@@ -199,6 +443,8 @@ int route_expand(const ss2d_expand_params* p, cudaStream_t st) {
         fit((long long)(reinterpret_cast<uintptr_t>(p->delta[k]) / s));
         fit((long long)(reinterpret_cast<uintptr_t>(p->bc[k]) / s));
     }
+    const bool mma_ok = vec == 8 && s == 2 && p->R <= 64 && (run % 8) == 0;
+    const int mma_min_r = 13;      // measured: for R = 6 and 12 the FMA kernel below is as fast or faster (its write dominates)
     // the staged rows (C rows x 64 items x vec floats) should stay near 28 KB so that several CTAs share an SM
     while (vec > 1 && C * 64 * vec * 4 > 28 * 1024) vec >>= 1;
     ExpandArgs a;
@@ -212,9 +458,24 @@ int route_expand(const ss2d_expand_params* p, cudaStream_t st) {
     a.xd_bs = p->x_dbl_batch_stride; a.xd_ks = p->x_dbl_route_stride; a.xd_rs = xd_rs;
     a.B = (int)p->B; a.D = (int)p->D; a.R = (int)p->R; a.N2 = (int)(2 * p->N); a.C = (int)C;
     a.H = (int)p->H; a.W = (int)p->W; a.L = (int)run; a.Limg = (int)L;
+    a.xt = nullptr; a.xt_rs = p->B * L;
+    if (p->workspace && transpose_fits(p)) {
+        if (p->workspace_bytes < route_expand_workspace_bytes(p)) return SS2D_EWORKSPACE;
+        if (!aligned_to(p->workspace, 16)) return SS2D_EINVAL_ALIGN;
+        int tr;
+        if (p->act_dtype == SS2D_F32) tr = launch_transpose<float>(p, st);
+        else if (p->act_dtype == SS2D_BF16) tr = launch_transpose<__nv_bfloat16>(p, st);
+        else tr = launch_transpose<__half>(p, st);
+        if (tr != SS2D_OK) return tr;
+        a.xt = p->workspace;
+    }
     if (flat) a.B = 1;
     a.items_per_plane = (int)(run / vec);
     a.items_total = (int)((flat ? 1 : p->B) * (run / vec));
+    if (mma_ok && p->R >= mma_min_r) {
+        if (p->act_dtype == SS2D_BF16) return launch_expand_mma<__nv_bfloat16>(a, st);
+        return launch_expand_mma<__half>(a, st);
+    }
     if (p->act_dtype == SS2D_F32) return launch_expand_v<float>(a, vec, st);
     if (p->act_dtype == SS2D_BF16) return launch_expand_v<__nv_bfloat16>(a, vec, st);
     return launch_expand_v<__half>(a, vec, st);

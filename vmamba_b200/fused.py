@@ -96,6 +96,10 @@ def project(x: torch.Tensor, w: CoreWeights, channel_major: bool = False):
     p.x_dbl, p.dt_weight = xd.data_ptr(), w.wdt.data_ptr()
     p.B, p.D, p.R, p.N, p.H, p.W = B, D, R, N, H, W
     p.act_dtype = ops.dtype_code(x)
+    need = int(lib().ss2d_route_expand_workspace_bytes(p))      # room for the transposed rows of the column-major routes
+    if need > 0:
+        ws = torch.empty(need, device=x.device, dtype=torch.uint8)
+        p.workspace, p.workspace_bytes = ws.data_ptr(), need
     with torch.cuda.device(x.device):
         check(lib().ss2d_route_expand(p, torch.cuda.current_stream(x.device).cuda_stream), "ss2d_route_expand")
     if channel_major:       # (pair, rows, B, L) per orientation
