@@ -394,7 +394,7 @@ static int launch_transpose(const ss2d_expand_params* p, cudaStream_t st) {
     const size_t pv = 16 / sizeof(T);
     t.vec_ok = (t.xd_bs % pv) == 0 && (t.xd_ks % pv) == 0 && (t.xd_rs % pv) == 0 && aligned_to(p->x_dbl, 16) && aligned_to(p->workspace, 16);
     const size_t plane_bytes = ((size_t)t.H * (t.W + 1) * sizeof(T) + 15) / 16 * 16;
-    int warps = (int)(48 * 1024 / plane_bytes);
+    int warps = (int)(32 * 1024 / plane_bytes);
     if (warps < 1) warps = 1;
     if (warps > 8) warps = 8;
     const size_t smem = plane_bytes * warps;
