@@ -105,7 +105,8 @@ def config0_inputs(seed: int = 0, Bt=2, D=96, H=56, W=56, N=1):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("VMAMBA_REFERENCE", "/root/reference"))
+    ap.add_argument("--ref", default=os.environ.get("VMAMBA_REFERENCE"), required="VMAMBA_REFERENCE" not in os.environ,
+                    help="checkout of MzeroMiko/VMamba (or set VMAMBA_REFERENCE)")
     args = ap.parse_args()
     ref = load_reference(args.ref)
     torch.set_grad_enabled(False)
