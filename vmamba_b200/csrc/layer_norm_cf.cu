@@ -230,7 +230,7 @@ static void launch_norm(NormArgs a, int pv, long long B, cudaStream_t st) {
     const int D = a.D;
     // registers hold CACHE * PV values per thread: at most 48 while D <= 192, at most 24 beyond
     // (more threads per CTA: keep about 64 registers per thread so that several CTAs share an SM)
-    if (D > 32 * 12) pv = 1;
+    if (D > 32 * 32) pv = 1;
     else if (D > 16 * 12 && pv > 2) pv = 2;
     a.nv = a.L / pv;
     a.items = (int)(B * a.nv);
@@ -241,8 +241,14 @@ static void launch_norm(NormArgs a, int pv, long long B, cudaStream_t st) {
     } else if (D <= 32 * 12) {
         if (pv == 2) launch_one<Tio, 32, 12, 2>(a, st); else launch_one<Tio, 32, 12, 1>(a, st);
     } else if (D <= 32 * 24) {
-        launch_one<Tio, 32, 24, 1>(a, st);
-    } else {      // more channels than 1024 threads can keep in registers: statistics pass, then re-read (from L2)
+        if (pv == 2) launch_one<Tio, 32, 24, 2>(a, st); else launch_one<Tio, 32, 24, 1>(a, st);
+    } else if (D <= 32 * 32) {
+        if (pv == 2) launch_one<Tio, 32, 32, 2>(a, st); else launch_one<Tio, 32, 32, 1>(a, st);
+    } else if (D <= 32 * 48) {
+        launch_one<Tio, 32, 48, 1>(a, st);
+    } else if (D <= 32 * 64) {
+        launch_one<Tio, 32, 64, 1>(a, st);
+    } else {      // more channels than 512 threads can keep in registers: statistics pass, then re-read (from L2)
         launch_one<Tio, 32, 0, 1>(a, st);
     }
 }
