@@ -207,3 +207,24 @@ def test_enable_fused_selects_supported_modules_only():
     assert model[0].forward_core(x) is x          # CPU tensor: falls through to the original core
     assert vb.disable_fused(model) == 1
     assert isinstance(model[0].forward_core, functools.partial)
+
+
+def test_checkpoint_key_normalisation():
+    """Older checkpoint namings are mapped as the reference's loaders map them (vmamba.py:1682-1697, 2061-2102)."""
+    import torch
+    from vmamba_b200.backbone import normalize_state_dict
+    z = torch.zeros(1)
+    old = {"model": {
+        "module.patch_embed.proj.weight": z, "patch_embed.norm.bias": z,
+        "layers.0.blocks.1.ln_1.weight": z, "layers.0.blocks.1.self_attention.x_proj_weight": z,
+        "layers.0.blocks.1.self_attention.dt_projs_weight": z, "layers.0.blocks.1.self_attention.dt_projs_bias": z,
+        "layers.2.downsample.norm.weight": z, "layers.2.downsample.reduction.weight": z,
+        "norm.weight": z, "head.bias": z, "layers.0.blocks.0.op.A_logs": z}}
+    new = normalize_state_dict(old)
+    assert set(new) == {
+        "patch_embed.0.weight", "patch_embed.2.bias", "layers.0.blocks.1.norm.weight",
+        "layers.0.blocks.1.op.x_proj.weight", "layers.0.blocks.1.op.dt_projs.weight", "layers.0.blocks.1.op.dt_projs_bias",
+        "layers.2.downsample.1.weight", "layers.2.downsample.2.weight", "classifier.norm.weight", "classifier.head.bias",
+        "layers.0.blocks.0.op.A_logs"}
+    same = normalize_state_dict(new)
+    assert set(same) == set(new)

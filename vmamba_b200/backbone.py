@@ -36,6 +36,39 @@ class _Block:
     __slots__ = ("n1w", "n1b", "w_in", "w_dw", "core", "w_out", "n2w", "n2b", "w1", "b1f", "w2", "b2f", "D")
 
 
+def normalize_state_dict(sd: dict) -> dict:
+    """Checkpoint keys in the current naming of the reference.  Applies the renames the reference's own
+    loaders apply (`VSSM._load_from_state_dict`, vmamba.py:2061-2102; `SS2D._load_from_state_dict`,
+    vmamba.py:1682-1697) and unwraps the {"model": ...} / {"state_dict": ...} containers its training
+    script writes, so that older released checkpoints load as they do there.  Returns a new dict; tensors
+    are shared, not copied."""
+    for key in ("model", "state_dict", "model_ema"):
+        if isinstance(sd.get(key), dict) and any(isinstance(v, torch.Tensor) or hasattr(v, "shape") for v in sd[key].values()):
+            sd = sd[key]
+            break
+    out = {}
+    prefix_map = [("patch_embed.proj", "patch_embed.0"), ("patch_embed.norm", "patch_embed.2")]
+    top_map = [("norm.", "classifier.norm."), ("head.", "classifier.head.")]
+    for k, v in sd.items():
+        nk = k[len("module."):] if k.startswith("module.") else k       # DistributedDataParallel wrapper
+        for src, dst in prefix_map:
+            if nk.startswith(src):
+                nk = dst + nk[len(src):]
+        for src, dst in top_map:
+            if nk.startswith(src):
+                nk = dst + nk[len(src):]
+        nk = re.sub(r"^(layers\.\d+\.blocks\.\d+)\.ln_1", r"\1.norm", nk)
+        nk = re.sub(r"^(layers\.\d+\.blocks\.\d+)\.self_attention", r"\1.op", nk)
+        nk = re.sub(r"^(layers\.\d+\.downsample)\.norm", r"\1.1", nk)
+        nk = re.sub(r"^(layers\.\d+\.downsample)\.reduction", r"\1.2", nk)
+        for src, dst in (("x_proj_weight", "x_proj.weight"), ("x_proj_bias", "x_proj.bias"),
+                         ("dt_projs_weight", "dt_projs.weight")):
+            if nk.endswith("." + src):
+                nk = nk[:-len(src)] + dst
+        out[nk] = v
+    return out
+
+
 class VSSMInfer:
     """Functional VMamba forward.  `VSSMInfer.from_state_dict(sd, dtype=torch.bfloat16)`."""
 
@@ -54,6 +87,7 @@ class VSSMInfer:
         dev = torch.device(device)
         m = VSSMInfer()
         m.dtype, m.device = dtype, dev
+        sd = normalize_state_dict(sd)
 
         def T(name, dt=None):
             v = sd[name]
