@@ -124,6 +124,8 @@ struct DwArgs {
     int BH, nb, units;              // rows per band, bands per plane, planes * nb
     int planes_per_channel;         // 1 for (B, D, H, W) maps, B for (D, B, H, W) maps
     int nrb;                        // row blocks of 8 per band
+    int flat;                       // whole planes, consecutive in memory and 16-byte aligned per CTA: flat vector loads / stores
+    unsigned magic_L;
     unsigned magic_fr, magic_nvw, magic_W, magic_nrb, magic_ppc, magic_nb, magic_frnvw, magic_nrbW, magic_W2, magic_nrbW2;
 };
 
@@ -143,6 +145,33 @@ __global__ void __launch_bounds__(256) dwconv3x3_act_kernel(const DwArgs a) {
         row[0] = 0.f; row[W + 1] = 0.f;
     }
     const T* __restrict__ x = (const T*)a.x;
+    T* obuf = reinterpret_cast<T*>(sm + ((a.PP * frame + 3) & ~3));   // flat mode: the CTA's outputs, np * H * W
+    if (a.flat) {
+        // whole planes, consecutive in memory: the CTA's input is one run of np * H * W elements, read as
+        // 16-byte vectors whatever the row length, and scattered into the frames
+        for (int i = threadIdx.x; i < np * 2 * Wp; i += blockDim.x) {       // rows above and below the image
+            const int pl = i / (2 * Wp), rem = i - pl * (2 * Wp);
+            sm[pl * frame + (rem < Wp ? rem : (H + 1) * Wp + rem - Wp)] = 0.f;
+        }
+        constexpr int FV = 16 / (int)sizeof(T);
+        const int total = np * H * W;
+        const T* src = x + (long long)unit0 * H * W;
+        for (int e0 = threadIdx.x * FV; e0 < total; e0 += blockDim.x * FV) {
+            int pl = mdiv(e0, a.magic_L), rem = e0 - pl * (H * W);
+            int h = mdiv(rem, a.magic_W), w = rem - h * W;
+            T v[FV];
+            if (e0 + FV <= total) *reinterpret_cast<uint4*>(v) = __ldg(reinterpret_cast<const uint4*>(src + e0));
+            else {
+#pragma unroll
+                for (int j = 0; j < FV; ++j) v[j] = (e0 + j < total) ? src[e0 + j] : from_f<T>(0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < FV; ++j) {
+                if (e0 + j < total) sm[pl * frame + (h + 1) * Wp + w + 1] = to_f<T>(v[j]);
+                if (++w == W) { w = 0; if (++h == H) { h = 0; ++pl; } }
+            }
+        }
+    } else
     for (int i = threadIdx.x; i < np * FR * a.nvw; i += blockDim.x) {
         const int pl = mdiv(i, a.magic_frnvw), rem = i - pl * (FR * a.nvw);
         const int fr = mdiv(rem, a.magic_nvw), v = rem - fr * a.nvw;
@@ -195,12 +224,12 @@ __global__ void __launch_bounds__(256) dwconv3x3_act_kernel(const DwArgs a) {
                 a0 = fmaf(k[6], ba.x, a0); a0 = fmaf(k[7], ba.y, a0); a0 = fmaf(k[8], bb.x, a0);
                 a1 = fmaf(k[6], ba.y, a1); a1 = fmaf(k[7], bb.x, a1); a1 = fmaf(k[8], bb.y, a1);
                 const float o[2] = {act_f<ACT>(round_to<T>(a0)), act_f<ACT>(round_to<T>(a1))};
-                Vec<T, 2>::store(out + r * W, o);
+                if (a.flat) Vec<T, 2>::store(obuf + (pl * H + r0 + r) * W + w, o);
+                else Vec<T, 2>::store(out + r * W, o);
                 ta = ma; tb = mb; ma = ba; mb = bb;
             }
         }
-        return;
-    }
+    } else
     for (int i = threadIdx.x; i < np * nrb * W; i += blockDim.x) {
         const int pl = mdiv(i, a.magic_nrbW), rem = i - pl * (nrb * W);
         const int rb = mdiv(rem, a.magic_W), w = rem - rb * W;
@@ -226,8 +255,19 @@ __global__ void __launch_bounds__(256) dwconv3x3_act_kernel(const DwArgs a) {
             acc = fmaf(k[0], t0, acc); acc = fmaf(k[1], t1, acc); acc = fmaf(k[2], t2, acc);
             acc = fmaf(k[3], m0, acc); acc = fmaf(k[4], m1, acc); acc = fmaf(k[5], m2, acc);
             acc = fmaf(k[6], b0, acc); acc = fmaf(k[7], b1, acc); acc = fmaf(k[8], b2, acc);
-            out[r * W] = from_f<T>(act_f<ACT>(round_to<T>(acc)));
+            if (a.flat) obuf[(pl * H + r0 + r) * W + w] = from_f<T>(act_f<ACT>(round_to<T>(acc)));
+            else out[r * W] = from_f<T>(act_f<ACT>(round_to<T>(acc)));
             t0 = m0; t1 = m1; t2 = m2; m0 = b0; m1 = b1; m2 = b2;
+        }
+    }
+    if (a.flat) {             // the CTA's outputs leave as one run of 16-byte vectors
+        __syncthreads();
+        constexpr int FV = 16 / (int)sizeof(T);
+        const int total = np * H * W;
+        T* dst = (T*)a.y + (long long)unit0 * H * W;
+        for (int e0 = threadIdx.x * FV; e0 < total; e0 += blockDim.x * FV) {
+            if (e0 + FV <= total) *reinterpret_cast<uint4*>(dst + e0) = *reinterpret_cast<const uint4*>(obuf + e0);
+            else for (int j = 0; e0 + j < total; ++j) dst[e0 + j] = obuf[e0 + j];
         }
     }
 }
@@ -261,6 +301,7 @@ static int launch_dw_v(DwArgs a, int pv, int act, size_t smem, unsigned grid, cu
     a.magic_ppc = magic(a.planes_per_channel); a.magic_nb = magic(a.nb);
     a.magic_frnvw = magic((long long)FR * a.nvw); a.magic_nrbW = magic((long long)a.nrb * a.W);
     a.magic_W2 = magic(a.W / 2); a.magic_nrbW2 = magic((long long)a.nrb * (a.W / 2));
+    a.magic_L = magic((long long)a.H * a.W);
     if (pv == 8) return launch_dw<T, 8>(a, act, smem, grid, st);
     if (pv == 4) return launch_dw<T, 4>(a, act, smem, grid, st);
     if (pv == 2) return launch_dw<T, 2>(a, act, smem, grid, st);
@@ -297,6 +338,17 @@ int dwconv3x3_act(const ss2d_pointwise_params* p, cudaStream_t st) {
     if (PP < 1) PP = 1;
     while (PP > 1 && PP * frame > 48 * 1024) --PP;
     if (PP > units) PP = units;
+    // flat mode: rows too short for 16-byte vectors, whole-plane bands, planes dense in memory; PP planes must
+    // keep every CTA's run 16-byte aligned
+    const long long fv = 16 / (long long)s;
+    bool flat = nb == 1 && pv == 1 && fv > 1 && aligned_to(p->x, 16) && aligned_to(p->y, 16);   // measured: pays only for odd row lengths
+    if (flat) {
+        long long step = fv;
+        for (long long gcd_a = L, gcd_b = fv; gcd_b; ) { const long long t = gcd_a % gcd_b; gcd_a = gcd_b; gcd_b = t; if (!gcd_b) step = fv / gcd_a; }
+        long long PPf = PP / step * step;
+        if (PPf < step) PPf = step;
+        if (PPf * (frame + L * s) + 32 > 64 * 1024) flat = false; else PP = PPf;
+    }
     const long long grid = (units + PP - 1) / PP;
     // every index split inside the kernel is a multiply-shift that needs numerator * divisor < 2^32
     if (units * nb >= (1LL << 32) || p->B * p->D * p->B >= (1LL << 32) || grid > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
@@ -305,7 +357,8 @@ int dwconv3x3_act(const ss2d_pointwise_params* p, cudaStream_t st) {
     a.D = (int)p->D; a.H = (int)p->H; a.W = (int)p->W; a.PP = (int)PP; a.nvw = 0;
     a.BH = (int)BH; a.nb = (int)nb; a.units = (int)units;
     a.planes_per_channel = p->channel_major ? (int)p->B : 1;
-    const size_t smem = (size_t)PP * frame;
+    a.flat = flat ? 1 : 0;
+    const size_t smem = flat ? ((size_t)PP * frame + 15) / 16 * 16 + ((size_t)PP * L * s + 15) / 16 * 16 : (size_t)PP * frame;
     if (p->dtype == SS2D_F32) return launch_dw_v<float>(a, pv, p->act, smem, (unsigned)grid, st);
     if (p->dtype == SS2D_BF16) return launch_dw_v<__nv_bfloat16>(a, pv, p->act, smem, (unsigned)grid, st);
     return launch_dw_v<__half>(a, pv, p->act, smem, (unsigned)grid, st);
