@@ -124,7 +124,8 @@ struct DwArgs {
     int BH, nb, units;              // rows per band, bands per plane, planes * nb
     int planes_per_channel;         // 1 for (B, D, H, W) maps, B for (D, B, H, W) maps
     int nrb;                        // row blocks of 8 per band
-    int flat;                       // whole planes, consecutive in memory and 16-byte aligned per CTA: flat vector loads / stores
+    int krows;                      // rows per thread in the compute phase (7 or 8: whichever divides the band better)
+    int flat;                       // bit 0: flat loads, bit 1: flat stores;  whole planes, consecutive in memory and 16-byte aligned per CTA: flat vector loads / stores
     unsigned magic_L;
     unsigned magic_fr, magic_nvw, magic_W, magic_nrb, magic_ppc, magic_nb, magic_frnvw, magic_nrbW, magic_W2, magic_nrbW2;
 };
@@ -146,7 +147,7 @@ __global__ void __launch_bounds__(256) dwconv3x3_act_kernel(const DwArgs a) {
     }
     const T* __restrict__ x = (const T*)a.x;
     T* obuf = reinterpret_cast<T*>(sm + ((a.PP * frame + 3) & ~3));   // flat mode: the CTA's outputs, np * H * W
-    if (a.flat) {
+    if (a.flat & 1) {
         // whole planes, consecutive in memory: the CTA's input is one run of np * H * W elements, read as
         // 16-byte vectors whatever the row length, and scattered into the frames
         for (int i = threadIdx.x; i < np * 2 * Wp; i += blockDim.x) {       // rows above and below the image
@@ -189,7 +190,7 @@ __global__ void __launch_bounds__(256) dwconv3x3_act_kernel(const DwArgs a) {
         for (int j = 0; j < PV; ++j) dst[j] = val[j];
     }
     __syncthreads();
-    constexpr int kRows = 8;
+    const int kRows = a.krows;
     const int nrb = a.nrb;
     if ((W & 1) == 0) {
         // two neighbouring columns per thread: four frame values per row (two 8-byte loads) serve eighteen
@@ -224,7 +225,7 @@ __global__ void __launch_bounds__(256) dwconv3x3_act_kernel(const DwArgs a) {
                 a0 = fmaf(k[6], ba.x, a0); a0 = fmaf(k[7], ba.y, a0); a0 = fmaf(k[8], bb.x, a0);
                 a1 = fmaf(k[6], ba.y, a1); a1 = fmaf(k[7], bb.x, a1); a1 = fmaf(k[8], bb.y, a1);
                 const float o[2] = {act_f<ACT>(round_to<T>(a0)), act_f<ACT>(round_to<T>(a1))};
-                if (a.flat) Vec<T, 2>::store(obuf + (pl * H + r0 + r) * W + w, o);
+                if (a.flat & 2) Vec<T, 2>::store(obuf + (pl * H + r0 + r) * W + w, o);
                 else Vec<T, 2>::store(out + r * W, o);
                 ta = ma; tb = mb; ma = ba; mb = bb;
             }
@@ -255,12 +256,12 @@ __global__ void __launch_bounds__(256) dwconv3x3_act_kernel(const DwArgs a) {
             acc = fmaf(k[0], t0, acc); acc = fmaf(k[1], t1, acc); acc = fmaf(k[2], t2, acc);
             acc = fmaf(k[3], m0, acc); acc = fmaf(k[4], m1, acc); acc = fmaf(k[5], m2, acc);
             acc = fmaf(k[6], b0, acc); acc = fmaf(k[7], b1, acc); acc = fmaf(k[8], b2, acc);
-            if (a.flat) obuf[(pl * H + r0 + r) * W + w] = from_f<T>(act_f<ACT>(round_to<T>(acc)));
+            if (a.flat & 2) obuf[(pl * H + r0 + r) * W + w] = from_f<T>(act_f<ACT>(round_to<T>(acc)));
             else out[r * W] = from_f<T>(act_f<ACT>(round_to<T>(acc)));
             t0 = m0; t1 = m1; t2 = m2; m0 = b0; m1 = b1; m2 = b2;
         }
     }
-    if (a.flat) {             // the CTA's outputs leave as one run of 16-byte vectors
+    if (a.flat & 2) {         // the CTA's outputs leave as one run of 16-byte vectors
         __syncthreads();
         constexpr int FV = 16 / (int)sizeof(T);
         const int total = np * H * W;
@@ -294,7 +295,8 @@ static int launch_dw(const DwArgs& a, int act, size_t smem, unsigned grid, cudaS
 template <typename T>
 static int launch_dw_v(DwArgs a, int pv, int act, size_t smem, unsigned grid, cudaStream_t st) {
     a.nvw = a.W / pv;
-    a.nrb = (a.BH + 7) / 8;
+    a.krows = (a.BH % 8 == 0 || a.BH % 7 != 0) ? 8 : 7;
+    a.nrb = (a.BH + a.krows - 1) / a.krows;
     auto magic = [](long long d) { return d > 1 ? (unsigned)(((1ULL << 32) + (unsigned long long)d - 1) / (unsigned long long)d) : 0u; };
     const int FR = a.BH + 2;
     a.magic_fr = magic(FR); a.magic_nvw = magic(a.nvw); a.magic_W = magic(a.W); a.magic_nrb = magic(a.nrb);
@@ -357,7 +359,7 @@ int dwconv3x3_act(const ss2d_pointwise_params* p, cudaStream_t st) {
     a.D = (int)p->D; a.H = (int)p->H; a.W = (int)p->W; a.PP = (int)PP; a.nvw = 0;
     a.BH = (int)BH; a.nb = (int)nb; a.units = (int)units;
     a.planes_per_channel = p->channel_major ? (int)p->B : 1;
-    a.flat = flat ? 1 : 0;
+    a.flat = flat ? 3 : 0;
     const size_t smem = flat ? ((size_t)PP * frame + 15) / 16 * 16 + ((size_t)PP * L * s + 15) / 16 * 16 : (size_t)PP * frame;
     if (p->dtype == SS2D_F32) return launch_dw_v<float>(a, pv, p->act, smem, (unsigned)grid, st);
     if (p->dtype == SS2D_BF16) return launch_dw_v<__nv_bfloat16>(a, pv, p->act, smem, (unsigned)grid, st);
