@@ -422,9 +422,11 @@ def test_core_long_map_takes_surface_kernels(vb):
     assert O.max_rel_err(host(y), ref) <= TOL_F32
 
 
-@pytest.mark.parametrize("ssm_ratio,dims", [(2.0, [16, 32, 64, 128]), (1.0, [24, 48, 96, 192])])
-def test_backbone_random_init_vs_oracle(vb, ssm_ratio, dims):
-    """VMamba-S/B-style blocks (ssm_ratio 2) and a second width, random init, against the CPU oracle."""
+@pytest.mark.parametrize("ssm_ratio,dims,hw", [(2.0, [16, 32, 64, 128], (64, 64)), (1.0, [24, 48, 96, 192], (64, 64)),
+                                               (1.0, [64, 128, 256, 512], (96, 160)), (2.0, [96, 192, 384, 768], (64, 96))])
+def test_backbone_random_init_vs_oracle(vb, ssm_ratio, dims, hw):
+    """VMamba-S/B-style blocks (ssm_ratio 2), several widths (the last two take the fused patch-embedding kernel),
+    non-square images with odd-sized deep maps (3 x 5, 2 x 3), random init, against the CPU oracle."""
     from oracle import backbone_oracle as BO
     from vmamba_b200.backbone import VSSMInfer
     sd = BO.random_state_dict([1, 1, 2, 1], dims, 1, ssm_ratio, 4.0, 10, 3, seed=4, with_outnorm=True)
@@ -432,7 +434,7 @@ def test_backbone_random_init_vs_oracle(vb, ssm_ratio, dims):
     for k in sd:                      # make LayerNorm affine terms and biases matter
         if k.endswith(".bias") or "norm" in k:
             sd[k] = (sd[k] + 0.1 * rng.standard_normal(sd[k].shape)).astype(np.float32)
-    img = rng.standard_normal((2, 3, 64, 64), dtype=np.float32)
+    img = rng.standard_normal((2, 3) + hw, dtype=np.float32)
     ref = BO.vssm_logits(img, sd)
     feats_ref = BO.backbone_features(img, sd)
     old = torch.backends.cudnn.allow_tf32
