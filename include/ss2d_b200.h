@@ -59,7 +59,9 @@ typedef struct ss2d_scan_params {
     void *out;
     int32_t in_dtype, out_dtype;
     int32_t delta_softplus;
-    int32_t reserved0;
+    int32_t delta_ratio;                /* channels sharing one delta row (and one delta_bias entry): delta is
+                                           (batch, dim / delta_ratio, seqlen), row r / delta_ratio serves channel r
+                                           (selective_scan_oflex.cpp:59, 176-183); 0 or 1 = one row per channel */
     int64_t batch, dim, dstate, seqlen, n_groups;
     int64_t u_batch_stride, u_dim_stride;
     int64_t delta_batch_stride, delta_dim_stride;
@@ -94,7 +96,9 @@ typedef struct ss2d_scan_bwd_params {
     int64_t workspace_bytes;
     int32_t in_dtype, dout_dtype;
     int32_t delta_softplus;
-    int32_t reserved0;
+    int32_t delta_ratio;                /* as in ss2d_scan_params; ddelta is still written per channel (batch, dim, seqlen)
+                                           and ddelta_bias per channel (dim): the caller sums the delta_ratio rows that
+                                           share an input row, as selective_scan_oflex.cpp:348-352 does */
     int64_t batch, dim, dstate, seqlen, n_groups;
     int64_t u_batch_stride, u_dim_stride;
     int64_t delta_batch_stride, delta_dim_stride;

@@ -189,3 +189,27 @@ def test_extension_module_surface(vb):
     ref = O.selective_scan_bwd(*(host(t) for t in (u, delta, A, B, C, D, bias, dout)), True, "f32")
     for name, got, r in zip(NAMES, (du, ddelta, dA, dB, dC, dD, dbias), ref):
         assert O.max_rel_err(host(got), r) <= TOL["f32"], name
+
+
+@pytest.mark.parametrize("ratio", [2, 3])
+def test_shared_delta_rows_forward_and_backward(vb, ratio):
+    """delta with dim / ratio rows, row r / ratio serving channel r (selective_scan_oflex.cpp:59, 176-183, 348-352).
+    The reference's pure-torch path has no such mode, so the oracle is fed the expanded delta and bias and its
+    per-channel gradients are summed over the rows that shared an input row."""
+    from vmamba_b200 import ops
+    Bt, K, Cd, N, L = 2, 2, 3 * ratio, 2, 150
+    u, delta_full, A, B, C, D, bias_full, dout = _random_case(Bt, K, Cd, N, L, seed=40 + ratio)
+    KC = K * Cd
+    delta = delta_full[:, ::ratio].copy()
+    bias = bias_full[::ratio].copy()
+    d_exp, b_exp = np.repeat(delta, ratio, axis=1), np.repeat(bias, ratio)
+    ref_y = O.selective_scan(u, d_exp, A, B, C, D, b_exp, True, True, "f32")
+    y = ops.selective_scan_fwd(dev(u), dev(delta), dev(A), dev(B), dev(C), dev(D), dev(bias), True, True)
+    assert O.max_rel_err(host(y), ref_y) <= TOL["f32"]
+    ref = list(O.selective_scan_bwd(u, d_exp, A, B, C, D, b_exp, dout, True, "f32"))
+    ref[1] = ref[1].reshape(Bt, KC // ratio, ratio, L).sum(2)
+    ref[6] = ref[6].reshape(KC // ratio, ratio).sum(1)
+    got = ops.selective_scan_bwd(dev(u), dev(delta), dev(A), dev(B), dev(C), dev(D), dev(bias), dev(dout), True)
+    assert tuple(got[1].shape) == (Bt, KC // ratio, L) and tuple(got[6].shape) == (KC // ratio,)
+    for name, x, r in zip(NAMES, got, ref):
+        assert O.max_rel_err(host(x), r) <= TOL["f32"], name

@@ -21,7 +21,7 @@ _i32, _i64, _vp, _f32 = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.
 
 class ScanParams(ctypes.Structure):
     _fields_ = [(n, _vp) for n in ("u", "delta", "A", "B", "C", "D", "delta_bias", "out")] + \
-               [(n, _i32) for n in ("in_dtype", "out_dtype", "delta_softplus", "reserved0")] + \
+               [(n, _i32) for n in ("in_dtype", "out_dtype", "delta_softplus", "delta_ratio")] + \
                [(n, _i64) for n in ("batch", "dim", "dstate", "seqlen", "n_groups",
                                     "u_batch_stride", "u_dim_stride", "delta_batch_stride", "delta_dim_stride",
                                     "out_batch_stride", "out_dim_stride",
@@ -33,7 +33,7 @@ class ScanBwdParams(ctypes.Structure):
     _fields_ = [(n, _vp) for n in ("u", "delta", "A", "B", "C", "D", "delta_bias", "dout",
                                    "du", "ddelta", "dA", "dB", "dC", "dD", "ddelta_bias", "workspace")] + \
                [("workspace_bytes", _i64)] + \
-               [(n, _i32) for n in ("in_dtype", "dout_dtype", "delta_softplus", "reserved0")] + \
+               [(n, _i32) for n in ("in_dtype", "dout_dtype", "delta_softplus", "delta_ratio")] + \
                [(n, _i64) for n in ("batch", "dim", "dstate", "seqlen", "n_groups",
                                     "u_batch_stride", "u_dim_stride", "delta_batch_stride", "delta_dim_stride",
                                     "dout_batch_stride", "dout_dim_stride",

@@ -19,6 +19,7 @@ struct ScanArgs {
     int64_t u_bs, u_ds, d_bs, d_ds, o_bs, o_ds;
     int64_t B_bs, B_gs, B_ss, C_bs, C_gs, C_ss;
     int softplus;
+    int64_t dratio;   // channels per delta row
 };
 
 constexpr int kWarpsPerCta = 4;
@@ -30,14 +31,14 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) selscan_fwd_n1_kernel(const
     if (row >= a.rows) return;
     const int64_t b = row / a.dim, r = row % a.dim, k = r / a.group_size;
     const Tin* __restrict__ u = (const Tin*)a.u + b * a.u_bs + r * a.u_ds;
-    const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + r * a.d_ds;
+    const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + (r / a.dratio) * a.d_ds;
     const Tin* __restrict__ Bm = (const Tin*)a.B + b * a.B_bs + k * a.B_gs;
     const Tin* __restrict__ Cm = (const Tin*)a.C + b * a.C_bs + k * a.C_gs;
     Tout* __restrict__ out = (Tout*)a.out + b * a.o_bs + r * a.o_ds;
     const float A2 = __ldg(a.A + r) * kLog2e;
     const bool has_D = a.D != nullptr;
     const float Dv = has_D ? __ldg(a.D + r) : 0.f;
-    const float bias = a.bias ? __ldg(a.bias + r) : 0.f;
+    const float bias = a.bias ? __ldg(a.bias + r / a.dratio) : 0.f;
     const bool sp = a.softplus != 0;
     const int L = (int)a.seqlen;
     constexpr int STEP = 32 * VEC;
@@ -102,7 +103,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) selscan_fwd_nx_kernel(const
     if (row >= a.rows) return;
     const int64_t b = row / a.dim, r = row % a.dim, k = r / a.group_size;
     const Tin* __restrict__ u = (const Tin*)a.u + b * a.u_bs + r * a.u_ds;
-    const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + r * a.d_ds;
+    const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + (r / a.dratio) * a.d_ds;
     const Tin* __restrict__ Bm = (const Tin*)a.B + b * a.B_bs + k * a.B_gs;
     const Tin* __restrict__ Cm = (const Tin*)a.C + b * a.C_bs + k * a.C_gs;
     Tout* __restrict__ out = (Tout*)a.out + b * a.o_bs + r * a.o_ds;
@@ -114,7 +115,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) selscan_fwd_nx_kernel(const
     __syncwarp();
     const bool has_D = a.D != nullptr;
     const float Dv = has_D ? __ldg(a.D + r) : 0.f;
-    const float bias = a.bias ? __ldg(a.bias + r) : 0.f;
+    const float bias = a.bias ? __ldg(a.bias + r / a.dratio) : 0.f;
     const bool sp = a.softplus != 0;
     const int L = (int)a.seqlen;
     constexpr int STEP = 32 * VEC;
@@ -209,6 +210,7 @@ int selective_scan_fwd(const ss2d_scan_params* p, cudaStream_t st) {
     if (p->batch <= 0 || p->dim <= 0 || p->dstate <= 0 || p->seqlen <= 0 || p->n_groups <= 0) return SS2D_EINVAL_SHAPE;
     if (p->dstate > SS2D_MAX_DSTATE) return SS2D_ENOTSUP;
     if (p->dim % p->n_groups != 0) return SS2D_EINVAL_SHAPE;
+    if (p->delta_ratio < 0 || (p->delta_ratio > 1 && p->dim % p->delta_ratio != 0)) return SS2D_EINVAL_SHAPE;
     if (p->seqlen > 0x3fffffffLL) return SS2D_ENOTSUP;
     const int64_t L = p->seqlen;
     // rows must not overlap: |stride| >= extent of what it steps over
@@ -234,6 +236,7 @@ int selective_scan_fwd(const ss2d_scan_params* p, cudaStream_t st) {
     a.B_bs = p->B_batch_stride; a.B_gs = p->B_group_stride; a.B_ss = p->B_state_stride;
     a.C_bs = p->C_batch_stride; a.C_gs = p->C_group_stride; a.C_ss = p->C_state_stride;
     a.softplus = p->delta_softplus;
+    a.dratio = p->delta_ratio > 1 ? p->delta_ratio : 1;
 
     // widest vector (in elements) that keeps every row start aligned for every tensor
     const int cap = (si == 2) ? 8 : 4;

@@ -35,6 +35,7 @@ struct BwdArgs {
     int64_t u_bs, u_ds, d_bs, d_ds, g_bs, g_ds;
     int64_t B_bs, B_gs, B_ss, C_bs, C_gs, C_ss;
     int N, n_groups, parts, nsteps, softplus;
+    int64_t dratio;   // channels per delta row
 };
 
 template <typename Tin, typename Tg, int VEC>
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(256) selscan_bwd_kernel(const BwdArgs a) {
     float* red = sm + (size_t)RW * (nsteps + 3) * N;                        // [RW][2][STEP]
 
     const Tin* __restrict__ u = (const Tin*)a.u + b * a.u_bs + r * a.u_ds;
-    const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + r * a.d_ds;
+    const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + (r / a.dratio) * a.d_ds;
     const Tg* __restrict__ gp = (const Tg*)a.dout + b * a.g_bs + r * a.g_ds;
     const Tin* __restrict__ Bm = (const Tin*)a.B + b * a.B_bs + k * a.B_gs;
     const Tin* __restrict__ Cm = (const Tin*)a.C + b * a.C_bs + k * a.C_gs;
@@ -66,7 +67,7 @@ __global__ void __launch_bounds__(256) selscan_bwd_kernel(const BwdArgs a) {
     Tin* __restrict__ dd = (Tin*)a.ddelta + (b * a.dim + r) * L;
     const bool has_D = a.D != nullptr;
     const float Dv = has_D ? __ldg(a.D + r) : 0.f;
-    const float bias = a.bias ? __ldg(a.bias + r) : 0.f;
+    const float bias = a.bias ? __ldg(a.bias + r / a.dratio) : 0.f;
     const bool sp = a.softplus != 0;
     using VI = Vec<Tin, VEC>;
     using VG = Vec<Tg, VEC>;
@@ -260,9 +261,9 @@ __global__ void __launch_bounds__(256) selscan_bwd_n1_kernel(const BwdArgs a, co
         if (ig >= a.group_size) continue;               // uniform over the warp
         const int64_t r = (int64_t)k * a.group_size + ig;
         const Tin* __restrict__ u = (const Tin*)a.u + b * a.u_bs + r * a.u_ds;
-        const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + r * a.d_ds;
+        const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + (r / a.dratio) * a.d_ds;
         const float A2 = __ldg(a.A + r) * kLog2e;
-        const float bias = a.bias ? __ldg(a.bias + r) : 0.f;
+        const float bias = a.bias ? __ldg(a.bias + r / a.dratio) : 0.f;
         float hc = 0.f;
         typename VI::Raw ru = {}, rd = {}, rb = {};
         int pos = lane * VEC;
@@ -312,7 +313,7 @@ __global__ void __launch_bounds__(256) selscan_bwd_n1_kernel(const BwdArgs a, co
             if (i < R && ig < a.group_size && in_l) {
                 const int64_t r = (int64_t)k * a.group_size + ig;
                 xu = VI::load_raw((const Tin*)a.u + b * a.u_bs + r * a.u_ds + pos);
-                xd = VI::load_raw((const Tin*)a.delta + b * a.d_bs + r * a.d_ds + pos);
+                xd = VI::load_raw((const Tin*)a.delta + b * a.d_bs + (r / a.dratio) * a.d_ds + pos);
                 xg = VG::load_raw((const Tg*)a.dout + b * a.g_bs + r * a.g_ds + pos);
             }
         };
@@ -326,7 +327,7 @@ __global__ void __launch_bounds__(256) selscan_bwd_n1_kernel(const BwdArgs a, co
             if (ig < a.group_size) {                    // uniform over the warp
                 const int64_t r = (int64_t)k * a.group_size + ig;
                 const float An = __ldg(a.A + r), A2 = An * kLog2e;
-                const float bias = a.bias ? __ldg(a.bias + r) : 0.f;
+                const float bias = a.bias ? __ldg(a.bias + r / a.dratio) : 0.f;
                 const float Dv = has_D ? __ldg(a.D + r) : 0.f;
                 float uv[VEC], dl[VEC], gv[VEC], dsp[VEC], av[VEC], P[VEC], hl[VEC], Q[VEC], El[VEC];
                 VI::unpack(ru, uv); VI::unpack(rd, dl); VG::unpack(rg, gv);
@@ -480,6 +481,7 @@ static int validate_bwd(const ss2d_scan_bwd_params* p) {
     if (p->batch <= 0 || p->dim <= 0 || p->dstate <= 0 || p->seqlen <= 0 || p->n_groups <= 0) return SS2D_EINVAL_SHAPE;
     if (p->dstate > SS2D_MAX_DSTATE) return SS2D_ENOTSUP;
     if (p->dim % p->n_groups != 0) return SS2D_EINVAL_SHAPE;
+    if (p->delta_ratio < 0 || (p->delta_ratio > 1 && p->dim % p->delta_ratio != 0)) return SS2D_EINVAL_SHAPE;
     if (p->seqlen > 0x3fffffffLL) return SS2D_ENOTSUP;
     const int64_t L = p->seqlen;
     if (p->u_dim_stride < L || p->delta_dim_stride < L || p->dout_dim_stride < L) return SS2D_EINVAL_STRIDE;
@@ -594,6 +596,7 @@ int selective_scan_bwd(const ss2d_scan_bwd_params* p, cudaStream_t st) {
     a.B_bs = p->B_batch_stride; a.B_gs = p->B_group_stride; a.B_ss = p->B_state_stride;
     a.C_bs = p->C_batch_stride; a.C_gs = p->C_group_stride; a.C_ss = p->C_state_stride;
     a.N = (int)p->dstate; a.n_groups = (int)p->n_groups; a.parts = c.parts; a.nsteps = c.nsteps; a.softplus = p->delta_softplus;
+    a.dratio = p->delta_ratio > 1 ? p->delta_ratio : 1;
     const int64_t ctas = p->batch * p->n_groups * c.parts;
     if (ctas > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
     const bool gf32 = p->dout_dtype == SS2D_F32;

@@ -52,8 +52,9 @@ def selective_scan_fwd(u, delta, A, B, C, D=None, delta_bias=None, delta_softplu
     Output fp32 if `out_float` (the reference's "oflex") else u.dtype.
     """
     _require_cuda(u, delta, A, B, C, D, delta_bias)
-    if u.dim() != 3 or delta.shape != u.shape:
-        raise RuntimeError(f"u and delta must be (batch, dim, L) with equal shapes, got {tuple(u.shape)} {tuple(delta.shape)}")
+    if u.dim() != 3 or delta.dim() != 3 or delta.shape[0] != u.shape[0] or delta.shape[2] != u.shape[2] \
+            or delta.shape[1] == 0 or u.shape[1] % delta.shape[1] != 0:
+        raise RuntimeError(f"u must be (batch, dim, L) and delta (batch, dim / r, L), got {tuple(u.shape)} {tuple(delta.shape)}")
     if B.dim() != 4 or C.shape != B.shape:
         raise RuntimeError("B and C must be (batch, n_groups, dstate, L) with equal shapes")
     batch, dim, L = u.shape
@@ -77,13 +78,14 @@ def selective_scan_fwd(u, delta, A, B, C, D=None, delta_bias=None, delta_softplu
     delta_bias = None if delta_bias is None else delta_bias.contiguous().float()
     if D is not None and D.numel() != dim:
         raise RuntimeError("D must have dim elements")
-    if delta_bias is not None and delta_bias.numel() != dim:
-        raise RuntimeError("delta_bias must have dim elements")
+    ratio = dim // delta.shape[1]        # channels sharing one delta row (selective_scan_oflex.cpp:59)
+    if delta_bias is not None and delta_bias.numel() != delta.shape[1]:
+        raise RuntimeError("delta_bias must have one element per delta row")
     out = torch.empty((batch, dim, L), device=u.device, dtype=torch.float32 if out_float else u.dtype)
     p = ScanParams()
     p.u, p.delta, p.A, p.B, p.C, p.D, p.delta_bias, p.out = (_ptr(t) for t in (u, delta, A, B, C, D, delta_bias, out))
     p.in_dtype, p.out_dtype = dtype_code(u), dtype_code(out)
-    p.delta_softplus = int(bool(delta_softplus))
+    p.delta_softplus, p.delta_ratio = int(bool(delta_softplus)), ratio
     p.batch, p.dim, p.dstate, p.seqlen, p.n_groups = batch, dim, N, L, K
     p.u_batch_stride, p.u_dim_stride = u.stride(0), u.stride(1)
     p.delta_batch_stride, p.delta_dim_stride = delta.stride(0), delta.stride(1)
@@ -123,7 +125,8 @@ def selective_scan_bwd(u, delta, A, B, C, D, delta_bias, dout, delta_softplus=Fa
     p.u, p.delta, p.A, p.B, p.C, p.D, p.delta_bias, p.dout = (_ptr(t) for t in (u, delta, A, B, C, D, delta_bias, dout))
     p.du, p.ddelta, p.dA, p.dB, p.dC, p.dD, p.ddelta_bias = (_ptr(t) for t in (du, ddelta, dA, dB, dC, dD, dbias))
     p.in_dtype, p.dout_dtype = dtype_code(u), dtype_code(dout)
-    p.delta_softplus = int(bool(delta_softplus))
+    ratio = dim // delta.shape[1]
+    p.delta_softplus, p.delta_ratio = int(bool(delta_softplus)), ratio
     p.batch, p.dim, p.dstate, p.seqlen, p.n_groups = batch, dim, N, L, K
     p.u_batch_stride, p.u_dim_stride = u.stride(0), u.stride(1)
     p.delta_batch_stride, p.delta_dim_stride = delta.stride(0), delta.stride(1)
@@ -137,6 +140,10 @@ def selective_scan_bwd(u, delta, A, B, C, D, delta_bias, dout, delta_softplus=Fa
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     with torch.cuda.device(u.device):
         check(lib().ss2d_selective_scan_bwd(p, _stream(u)), "ss2d_selective_scan_bwd")
+    if ratio > 1:       # rows that shared a delta row: their gradients add up (selective_scan_oflex.cpp:348-352)
+        ddelta = ddelta.view(batch, dim // ratio, ratio, L).float().sum(2).to(u.dtype)
+        if dbias is not None:
+            dbias = dbias.view(dim // ratio, ratio).sum(1)
     return du, ddelta, dA, dB, dC, dD, dbias
 
 
