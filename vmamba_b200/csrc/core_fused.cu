@@ -397,24 +397,8 @@ long long core_workspace_bytes(const ss2d_core_params* p) {
     return (long long)(p->B * p->D * p->H * p->W) * 4;
 }
 
-int core_fwd(const ss2d_core_params* p, cudaStream_t st) {
-    const int rc = validate_core(p);
-    if (rc != SS2D_OK) return rc;
-    if (p->N != 1) return SS2D_ENOTSUP;          // d_state > 1 runs through the operator-surface kernels
-    if (!p->with_norm && p->y_dtype != SS2D_F32) return SS2D_ENOTSUP;
-    PlaneConfig c;
-    if (!plan_planes(p, c)) return SS2D_ENOTSUP;  // plane too long for one CTA
-    const long long need = core_workspace_bytes(p);
-    float* merged = (float*)p->y;
-    if (need > 0) {
-        if (!p->workspace || p->workspace_bytes < need) return SS2D_EWORKSPACE;
-        if (!aligned_to(p->workspace, 256)) return SS2D_EINVAL_ALIGN;
-        merged = (float*)p->workspace;
-    } else if (!aligned_to(p->y, 16)) {
-        return SS2D_EINVAL_ALIGN;
-    } else if (p->y_batch_stride || p->y_channel_stride) {
-        return SS2D_ENOTSUP;     // the un-normalised fp32 map is written dense
-    }
+// Scan + merge kernel into `merged`, then (with_norm) the LayerNorm kernel into p->y.  Arguments validated by the caller.
+static int run_core(const ss2d_core_params* p, const PlaneConfig& c, float* merged, cudaStream_t st) {
     CoreArgs a;
     a.x = p->x;
     for (int k = 0; k < 4; ++k) {
@@ -444,6 +428,27 @@ int core_fwd(const ss2d_core_params* p, cudaStream_t st) {
     n.B = p->B; n.D = p->D; n.L = p->H * p->W; n.io_dtype = p->y_dtype; n.eps = p->ln_eps;
     n.out_batch_stride = p->y_batch_stride; n.out_channel_stride = p->y_channel_stride;
     return layer_norm_cf(&n, st);
+}
+
+int core_fwd(const ss2d_core_params* p, cudaStream_t st) {
+    const int rc = validate_core(p);
+    if (rc != SS2D_OK) return rc;
+    if (p->N != 1) return SS2D_ENOTSUP;          // d_state > 1 runs through the operator-surface kernels
+    if (!p->with_norm && p->y_dtype != SS2D_F32) return SS2D_ENOTSUP;
+    PlaneConfig c;
+    if (!plan_planes(p, c)) return SS2D_ENOTSUP;  // plane too long for one CTA
+    const long long need = core_workspace_bytes(p);
+    float* merged = (float*)p->y;
+    if (need > 0) {
+        if (!p->workspace || p->workspace_bytes < need) return SS2D_EWORKSPACE;
+        if (!aligned_to(p->workspace, 256)) return SS2D_EINVAL_ALIGN;
+        merged = (float*)p->workspace;
+    } else if (!aligned_to(p->y, 16)) {
+        return SS2D_EINVAL_ALIGN;
+    } else if (p->y_batch_stride || p->y_channel_stride) {
+        return SS2D_ENOTSUP;     // the un-normalised fp32 map is written dense
+    }
+    return run_core(p, c, merged, st);
 }
 
 
@@ -511,35 +516,7 @@ int core_fwd_static(const ss2d_core_params* p, cudaStream_t st) {
     } else if (!aligned_to(p->y, 16)) {
         return SS2D_EINVAL_ALIGN;
     }
-    CoreArgs a;
-    a.x = p->x;
-    for (int k = 0; k < 4; ++k) {
-        a.delta[k] = p->delta[k]; a.Bm[k] = p->Bm[k]; a.Cm[k] = p->Cm[k];
-        a.d_bs[k] = p->delta_batch_stride[k]; a.bc_bs[k] = p->bc_batch_stride[k];
-        a.d_cs[k] = p->delta_channel_stride[k] ? p->delta_channel_stride[k] : p->H * p->W;
-    }
-    a.A = (const float*)p->A; a.Dskip = (const float*)p->Dskip; a.bias = (const float*)p->delta_bias;
-    a.merged = merged;
-    a.x_bs = p->x_batch_stride ? p->x_batch_stride : p->D * p->H * p->W;
-    a.x_cs = p->x_channel_stride ? p->x_channel_stride : p->H * p->W;
-    a.B = (int)p->B; a.D = (int)p->D; a.H = (int)p->H; a.W = (int)p->W; a.L = (int)(p->H * p->W);
-    a.G = c.G; a.PP = c.PP; a.Wp = c.Wp;
-    auto magic = [](long long d) { return (unsigned)(((1ULL << 32) + (unsigned long long)d - 1) / (unsigned long long)d); };
-    a.magic_G = c.G > 1 ? magic(c.G) : 0; a.magic_W = p->W > 1 ? magic(p->W) : 0; a.magic_H = p->H > 1 ? magic(p->H) : 0;
-    a.groups_per_image = (int)((p->D + c.PP - 1) / c.PP);
-    const long long grid = (long long)p->B * a.groups_per_image;
-    if (grid > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
-    int r;
-    if (p->act_dtype == SS2D_F32) r = launch_core_v<float>(a, c, (unsigned)grid, st);
-    else if (p->act_dtype == SS2D_BF16) r = launch_core_v<__nv_bfloat16>(a, c, (unsigned)grid, st);
-    else r = launch_core_v<__half>(a, c, (unsigned)grid, st);
-    if (r != SS2D_OK) return r;
-    if (!p->with_norm) return SS2D_OK;
-    ss2d_norm_params n = {};
-    n.in = merged; n.weight = p->ln_weight; n.bias = p->ln_bias; n.out = p->y;
-    n.B = p->B; n.D = p->D; n.L = p->H * p->W; n.io_dtype = p->y_dtype; n.eps = p->ln_eps;
-    n.out_batch_stride = p->y_batch_stride; n.out_channel_stride = p->y_channel_stride;
-    return layer_norm_cf(&n, st);
+    return run_core(p, c, merged, st);
 }
 
 }  // namespace ss2d
