@@ -132,6 +132,28 @@ int ss2d_cross_scan(const ss2d_cross_params *p, void *cuda_stream);
 int ss2d_cross_merge(const ss2d_cross_params *p, void *cuda_stream);
 
 /* ------------------------------------------------------------------------------------
+ * CrossScan / CrossMerge with the reference's layout flags (cross_scan_fwd / cross_merge_fwd / their one-by-one
+ * forms, vmamba.py:41-245; CrossScanF / CrossMergeF, csm_triton.py:182-273).  In both calls in_channel_first names
+ * the layout of the map side ((B, C, H, W) or (B, H, W, C)) and out_channel_first the layout of the routes side
+ * ((B, 4, C, L) or (B, L, 4, C)), as in the reference.
+ *   ss2d_cross_scan_ex : map -> routes;  one_by_one: in is (B, 4, C, H, W), route k reads its own map
+ *   ss2d_cross_merge_ex: routes -> map (B, C, L) or (B, L, C);  one_by_one: no sum, out is (B, 4, C, L)
+ * one_by_one is implemented for channel-first tensors on both sides; with scans 1 it passes the four maps
+ * through unchanged, as the reference does.  Index-only variants, not tuned.
+ * -------------------------------------------------------------------------------- */
+typedef struct ss2d_cross_ex_params {
+    const void *in;
+    void *out;
+    int32_t dtype;
+    int32_t scans;
+    int32_t in_channel_first, out_channel_first, one_by_one, reserved0;
+    int64_t B, C, H, W;
+} ss2d_cross_ex_params;
+
+int ss2d_cross_scan_ex(const ss2d_cross_ex_params *p, void *cuda_stream);
+int ss2d_cross_merge_ex(const ss2d_cross_ex_params *p, void *cuda_stream);
+
+/* ------------------------------------------------------------------------------------
  * Fused SS2D core: CrossScan folded into the scan's loads + four-route selective scan
  * (d_state >= 1) + CrossMerge + LayerNorm over channels, for scans mode 0.  Replaces the
  * chain cross_scan_fn -> selective_scan_fn -> cross_merge_fn -> out_norm -> cast of

@@ -130,6 +130,51 @@ def cross_merge(ys: np.ndarray, scans: int = 0) -> np.ndarray:
 
 
 # --------------------------------------------------------------------------- #
+# layout and one-by-one variants of CrossScan / CrossMerge  (vmamba.py:41-245)
+# --------------------------------------------------------------------------- #
+def cross_scan_ex(x: np.ndarray, scans: int = 0, in_channel_first: bool = True, out_channel_first: bool = True,
+                  one_by_one: bool = False) -> np.ndarray:
+    """CrossScan with the reference's layout flags.
+
+    x: (B, C, H, W) or, channel-last, (B, H, W, C); one_by_one (channel-first only here): (B, 4, C, H, W),
+    route k reads its own map x[:, k] (vmamba.py:132-157).  Result (B, 4, C, L) or, with out_channel_first
+    False, (B, L, 4, C) (vmamba.py:79-82)."""
+    if one_by_one:
+        if not (in_channel_first and out_channel_first):
+            raise NotImplementedError("one_by_one is restated for channel-first tensors only")
+        B, K, C, H, W = x.shape
+        assert K == 4
+        y = np.stack([cross_scan(np.ascontiguousarray(x[:, k]), scans)[:, k] for k in range(4)], axis=1)
+        if scans == 1:                       # vmamba.py:142-143: `x.flatten(2, 3)` on the 5-d tensor merges C with H
+            y = x.reshape(B, 4, C * H, W).copy()
+        return y
+    xc = x if in_channel_first else np.ascontiguousarray(np.moveaxis(x, -1, 1))
+    y = cross_scan(xc, scans)                                   # (B, 4, C, L)
+    return y if out_channel_first else np.ascontiguousarray(y.transpose(0, 3, 1, 2))
+
+
+def cross_merge_ex(ys: np.ndarray, scans: int = 0, in_channel_first: bool = True, out_channel_first: bool = True,
+                   one_by_one: bool = False) -> np.ndarray:
+    """CrossMerge with the reference's layout flags: `out_channel_first` names the layout of the routes ys
+    ((B, 4, C, H, W) or (B, H, W, 4, C)), `in_channel_first` the layout of the result ((B, C, L) or (B, L, C)),
+    as in cross_merge_fwd (vmamba.py:87-130).  one_by_one (channel-first only here): every route is brought back
+    to row-major order separately, no sum: (B, 4, C, L) (vmamba.py:189-218)."""
+    if one_by_one:
+        if not (in_channel_first and out_channel_first):
+            raise NotImplementedError("one_by_one is restated for channel-first tensors only")
+        B, K, C, H, W = ys.shape
+        out = np.empty((B, 4, C, H * W), dtype=ys.dtype)
+        for k in range(4):
+            only = np.zeros_like(ys)
+            only[:, k] = ys[:, k]
+            out[:, k] = cross_merge(only, scans)                # x + 0 is exact: the un-permuted route k
+        return out
+    yc = ys if out_channel_first else np.ascontiguousarray(ys.transpose(0, 3, 4, 1, 2))     # (B,H,W,K,D) -> (B,K,D,H,W)
+    y = cross_merge(yc, scans)                                  # (B, C, L)
+    return y if in_channel_first else np.ascontiguousarray(y.transpose(0, 2, 1))
+
+
+# --------------------------------------------------------------------------- #
 # a5/a6: selective scan  (vmamba.py:791-834)
 # --------------------------------------------------------------------------- #
 def softplus(x: np.ndarray) -> np.ndarray:

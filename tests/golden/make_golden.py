@@ -127,6 +127,27 @@ def main():
                                                     True, True, False, 0, True))
     np.savez_compressed(os.path.join(HERE, "csm_small.npz"), **out)
 
+    # ---- 1b. layout flags (channel-last in / out) and one_by_one, through the reference's torch Functions ----
+    outl = {}
+    gl = torch.Generator().manual_seed(21)
+    for (H, W) in ((5, 7), (6, 6)):
+        xcf = torch.randn((2, 3, H, W), generator=gl)
+        ycf = torch.randn((2, 4, 3, H, W), generator=gl)
+        tag = f"{H}x{W}"
+        outl[f"{tag}_x"], outl[f"{tag}_ys"] = npf(xcf), npf(ycf)
+        for scans in (0, 1, 2, 3):
+            if scans == 3 and H != W:
+                continue
+            for icf in (True, False):
+                for ocf in (True, False):
+                    xin = xcf if icf else xcf.permute(0, 2, 3, 1).contiguous()
+                    yin = ycf if ocf else ycf.permute(0, 3, 4, 1, 2).contiguous()
+                    outl[f"{tag}_scan_s{scans}_i{int(icf)}_o{int(ocf)}"] = npf(ref.cross_scan_fn(xin, icf, ocf, False, scans, True))
+                    outl[f"{tag}_merge_s{scans}_i{int(icf)}_o{int(ocf)}"] = npf(ref.cross_merge_fn(yin, icf, ocf, False, scans, True))
+            outl[f"{tag}_scan1b1_s{scans}"] = npf(ref.cross_scan_fn(ycf, True, True, True, scans, True))
+            outl[f"{tag}_merge1b1_s{scans}"] = npf(ref.cross_merge_fn(ycf, True, True, True, scans, True))
+    np.savez_compressed(os.path.join(HERE, "csm_layouts_small.npz"), **outl)
+
     # ---- 2. selective scan, small cases over the flag space ---------------------
     cases = [
         dict(name="c0", Bt=2, K=4, Cd=3, N=1, L=37, D=True, bias=True, sp=True, dt="f32", oflex=True),

@@ -115,8 +115,10 @@ def test_operators_refuse_cpu_tensors():
         vb.cross_scan_fn(x)
     with pytest.raises(NotImplementedError):
         vb.selective_scan_fn(x, x, x, x, x, backend="torch")
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
         vb.cross_scan_fn(x, in_channel_first=False)
+    with pytest.raises(NotImplementedError):         # one_by_one exists for channel-first tensors only
+        vb.cross_scan_fn(torch.zeros(1, 3, 4, 4, 2), in_channel_first=False, out_channel_first=False, one_by_one=True)
 
 
 def test_install_patches_a_reference_like_module():

@@ -527,3 +527,41 @@ def test_vmamba_tiny_bf16_top1_agreement(vb):
     assert worst <= TOL_BF16
     assert total_m > total // 2 and agree_m == total_m
     assert agree >= 0.97 * total
+
+
+def test_cross_scan_merge_layout_flags_and_one_by_one(vb):
+    """Channel-last map / routes and one_by_one against the reference's torch Functions (stored fixture), forward
+    bit-exact; the backward of each Function is the other operator with the same flags (csm_triton.py:207-273)."""
+    g = np.load(os.path.join(G, "csm_layouts_small.npz"))
+    for tag, (H, W) in (("5x7", (5, 7)), ("6x6", (6, 6))):
+        x, ys = g[f"{tag}_x"], g[f"{tag}_ys"]
+        for scans in (0, 1, 2, 3):
+            if scans == 3 and H != W:
+                continue
+            for icf in (True, False):
+                for ocf in (True, False):
+                    xin = x if icf else np.ascontiguousarray(x.transpose(0, 2, 3, 1))
+                    yin = ys if ocf else np.ascontiguousarray(ys.transpose(0, 3, 4, 1, 2))
+                    key = f"s{scans}_i{int(icf)}_o{int(ocf)}"
+                    xt = dev(xin).requires_grad_(True)
+                    out = vb.cross_scan_fn(xt, icf, ocf, False, scans)
+                    assert np.array_equal(host(out), g[f"{tag}_scan_{key}"]), key
+                    gy = np.random.default_rng(scans).standard_normal(out.shape).astype(np.float32)
+                    out.backward(dev(gy))
+                    gy5 = gy.reshape(ys.shape) if ocf else gy.reshape(yin.shape)
+                    want = O.cross_merge_ex(gy5, scans, icf, ocf)
+                    assert np.array_equal(host(xt.grad).reshape(want.shape), want), key
+                    yt = dev(yin).requires_grad_(True)
+                    m = vb.cross_merge_fn(yt, icf, ocf, False, scans)
+                    assert np.array_equal(host(m), g[f"{tag}_merge_{key}"]), key
+                    gm = np.random.default_rng(scans + 9).standard_normal(m.shape).astype(np.float32)
+                    m.backward(dev(gm))
+                    gx = gm.reshape(x.shape) if icf else gm.reshape(xin.shape)
+                    want = O.cross_scan_ex(gx, scans, icf, ocf)
+                    assert np.array_equal(host(yt.grad).reshape(want.shape), want), key
+            out = vb.cross_scan_fn(dev(ys), True, True, True, scans)
+            assert np.array_equal(host(out), g[f"{tag}_scan1b1_s{scans}"]), scans
+            out = vb.cross_merge_fn(dev(ys), True, True, True, scans)
+            assert np.array_equal(host(out), g[f"{tag}_merge1b1_s{scans}"]), scans
+    with pytest.raises(NotImplementedError):
+        vb.cross_scan_fn(dev(g["5x7_ys"]).permute(0, 3, 4, 1, 2).contiguous(), False, False, True, 0)

@@ -35,6 +35,26 @@ def test_arange_known_answer():
     assert np.array_equal(O.cross_merge(xs.reshape(1, 4, 1, 4, 4), 0), 4 * x.reshape(1, 1, 16))
 
 
+def test_cross_scan_merge_layout_flags_and_one_by_one():
+    """Channel-last in / out and one_by_one against the reference's torch Functions (bit-exact data movement;
+    the merge sums in the reference's order)."""
+    g = load("csm_layouts_small.npz")
+    for tag, (H, W) in (("5x7", (5, 7)), ("6x6", (6, 6))):
+        x, ys = g[f"{tag}_x"], g[f"{tag}_ys"]
+        for scans in (0, 1, 2, 3):
+            if scans == 3 and H != W:
+                continue
+            for icf in (True, False):
+                for ocf in (True, False):
+                    xin = x if icf else np.ascontiguousarray(x.transpose(0, 2, 3, 1))
+                    yin = ys if ocf else np.ascontiguousarray(ys.transpose(0, 3, 4, 1, 2))
+                    key = f"s{scans}_i{int(icf)}_o{int(ocf)}"
+                    assert np.array_equal(O.cross_scan_ex(xin, scans, icf, ocf), g[f"{tag}_scan_{key}"]), key
+                    assert np.array_equal(O.cross_merge_ex(yin, scans, icf, ocf), g[f"{tag}_merge_{key}"]), key
+            assert np.array_equal(O.cross_scan_ex(ys, scans, one_by_one=True), g[f"{tag}_scan1b1_s{scans}"]), scans
+            assert np.array_equal(O.cross_merge_ex(ys, scans, one_by_one=True), g[f"{tag}_merge1b1_s{scans}"]), scans
+
+
 def _case(g, n):
     kw = dict(D=g[f"{n}_D"] if f"{n}_D" in g.files else None,
               delta_bias=g[f"{n}_bias"] if f"{n}_bias" in g.files else None,

@@ -46,6 +46,12 @@ class CrossParams(ctypes.Structure):
                 ("B", _i64), ("C", _i64), ("H", _i64), ("W", _i64)]
 
 
+class CrossExParams(ctypes.Structure):
+    _fields_ = [("in_", _vp), ("out", _vp), ("dtype", _i32), ("scans", _i32), ("in_channel_first", _i32),
+                ("out_channel_first", _i32), ("one_by_one", _i32), ("reserved0", _i32),
+                ("B", _i64), ("C", _i64), ("H", _i64), ("W", _i64)]
+
+
 class CoreParams(ctypes.Structure):
     _fields_ = [("x", _vp), ("delta", _vp * ROUTES), ("Bm", _vp * ROUTES), ("Cm", _vp * ROUTES),
                 ("A", _vp), ("Dskip", _vp), ("delta_bias", _vp), ("ln_weight", _vp), ("ln_bias", _vp),
@@ -98,6 +104,8 @@ EXPORTS = {
     "ss2d_selective_scan_bwd_workspace_bytes": (_i64, [ctypes.POINTER(ScanBwdParams)]),
     "ss2d_cross_scan": (ctypes.c_int, [ctypes.POINTER(CrossParams), _vp]),
     "ss2d_cross_merge": (ctypes.c_int, [ctypes.POINTER(CrossParams), _vp]),
+    "ss2d_cross_scan_ex": (ctypes.c_int, [ctypes.POINTER(CrossExParams), _vp]),
+    "ss2d_cross_merge_ex": (ctypes.c_int, [ctypes.POINTER(CrossExParams), _vp]),
     "ss2d_core_workspace_bytes": (_i64, [ctypes.POINTER(CoreParams)]),
     "ss2d_core_fwd": (ctypes.c_int, [ctypes.POINTER(CoreParams), _vp]),
     "ss2d_core_fwd_static": (ctypes.c_int, [ctypes.POINTER(CoreParams), _vp]),

@@ -9,6 +9,8 @@ int selective_scan_bwd(const ss2d_scan_bwd_params* p, cudaStream_t st);
 long long selective_scan_bwd_workspace_bytes(const ss2d_scan_bwd_params* p);
 int cross_scan(const ss2d_cross_params* p, cudaStream_t st);
 int cross_merge(const ss2d_cross_params* p, cudaStream_t st);
+int cross_scan_ex(const ss2d_cross_ex_params* p, cudaStream_t st);
+int cross_merge_ex(const ss2d_cross_ex_params* p, cudaStream_t st);
 int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st);
 long long core_workspace_bytes(const ss2d_core_params* p);
 int core_fwd(const ss2d_core_params* p, cudaStream_t st);
@@ -38,6 +40,8 @@ int ss2d_selective_scan_bwd(const ss2d_scan_bwd_params* p, void* stream) {
 int64_t ss2d_selective_scan_bwd_workspace_bytes(const ss2d_scan_bwd_params* p) { return ss2d::selective_scan_bwd_workspace_bytes(p); }
 int ss2d_cross_scan(const ss2d_cross_params* p, void* stream) { return ss2d::cross_scan(p, (cudaStream_t)stream); }
 int ss2d_cross_merge(const ss2d_cross_params* p, void* stream) { return ss2d::cross_merge(p, (cudaStream_t)stream); }
+int ss2d_cross_scan_ex(const ss2d_cross_ex_params* p, void* stream) { return ss2d::cross_scan_ex(p, (cudaStream_t)stream); }
+int ss2d_cross_merge_ex(const ss2d_cross_ex_params* p, void* stream) { return ss2d::cross_merge_ex(p, (cudaStream_t)stream); }
 int ss2d_layer_norm_cf(const ss2d_norm_params* p, void* stream) { return ss2d::layer_norm_cf(p, (cudaStream_t)stream); }
 int64_t ss2d_core_workspace_bytes(const ss2d_core_params* p) { return ss2d::core_workspace_bytes(p); }
 int ss2d_core_fwd(const ss2d_core_params* p, void* stream) { return ss2d::core_fwd(p, (cudaStream_t)stream); }

@@ -313,4 +313,118 @@ int cross_merge(const ss2d_cross_params* p, cudaStream_t st) {
     return check_launch();
 }
 
+// ------------------------------------------------------------------------------------------------
+// Layout and one-by-one variants (channel-last x and / or routes; every route reading its own map):
+// index-only variants of the two operators, off the benchmarked path.  One thread per (image, pixel,
+// channel) handles the four routes; the fastest thread index follows the contiguous axis of the
+// routes tensor (pixels for channel-first routes, channels for channel-last ones).
+struct CrossExArgs {
+    const void* in;
+    void* out;
+    RouteMap route[4];
+    long long B, C, H, W, L, total;
+    int x_cf, r_cf, one_by_one, scans;       // x / routes channel-first; every route has its own map
+    int flat_1b1_copy;                       // one_by_one, scans 1: the four maps pass through unchanged
+};
+
+__device__ __forceinline__ long long x_index(const CrossExArgs& a, long long b, int k, long long c, long long p) {
+    const long long K = a.one_by_one ? 4 : 1, kk = a.one_by_one ? k : 0;
+    return a.x_cf ? ((b * K + kk) * a.C + c) * a.L + p : ((b * a.L + p) * K + kk) * a.C + c;
+}
+__device__ __forceinline__ long long r_index(const CrossExArgs& a, long long b, int k, long long c, long long l) {
+    return a.r_cf ? ((b * 4 + k) * a.C + c) * a.L + l : ((b * a.L + l) * 4 + k) * a.C + c;
+}
+__device__ __forceinline__ void ex_decompose(const CrossExArgs& a, long long i, long long& b, long long& c, long long& p) {
+    if (a.r_cf) { p = i % a.L; const long long t = i / a.L; c = t % a.C; b = t / a.C; }
+    else { c = i % a.C; const long long t = i / a.C; p = t % a.L; b = t / a.L; }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) cross_scan_ex_kernel(const CrossExArgs a) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.total; i += (long long)gridDim.x * blockDim.x) {
+        long long b, c, p;
+        ex_decompose(a, i, b, c, p);
+        const long long h = p / a.W, w = p - h * a.W;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const RouteMap& m = a.route[k];
+            const long long l = a.flat_1b1_copy ? p : m.base + m.sh * h + m.sw * w;
+            ((T*)a.out)[r_index(a, b, k, c, l)] = ((const T*)a.in)[x_index(a, b, k, c, p)];
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) cross_merge_ex_kernel(const CrossExArgs a) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.total; i += (long long)gridDim.x * blockDim.x) {
+        long long b, c, p;
+        ex_decompose(a, i, b, c, p);
+        const long long h = p / a.W, w = p - h * a.W;
+        T v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const RouteMap& m = a.route[k];
+            const long long l = a.flat_1b1_copy ? p : m.base + m.sh * h + m.sw * w;
+            v[k] = ((const T*)a.in)[r_index(a, b, k, c, l)];
+        }
+        if (a.one_by_one) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ((T*)a.out)[x_index(a, b, k, c, p)] = v[k];
+        } else {
+            T r;
+            if (a.scans == 0 || a.scans == 2) r = add_t(add_t(v[0], v[2]), add_t(v[1], v[3]));
+            else if (a.scans == 3) r = add_t(add_t(add_t(v[0], v[1]), v[2]), v[3]);
+            else r = from_f<T>(((to_f<T>(v[0]) + to_f<T>(v[1])) + to_f<T>(v[2])) + to_f<T>(v[3]));
+            ((T*)a.out)[x_index(a, b, 0, c, p)] = r;
+        }
+    }
+}
+
+static int fill_ex(const ss2d_cross_ex_params* p, CrossExArgs& a) {
+    if (!p) return SS2D_EINVAL_NULL;
+    if (!p->in || !p->out) return SS2D_EINVAL_NULL;
+    if (!dtype_ok(p->dtype)) return SS2D_EINVAL_DTYPE;
+    if (p->scans < 0 || p->scans > 3) return SS2D_ENOTSUP;
+    if (p->B <= 0 || p->C <= 0 || p->H <= 0 || p->W <= 0) return SS2D_EINVAL_SHAPE;
+    if (p->scans == 3 && p->H != p->W) return SS2D_EINVAL_SHAPE;
+    if (p->H * p->W > 0x3fffffffLL) return SS2D_EINVAL_SHAPE;
+    if (p->one_by_one && !(p->in_channel_first && p->out_channel_first)) return SS2D_ENOTSUP;
+    const size_t s = dtype_size(p->dtype);
+    if (!aligned_to(p->in, s) || !aligned_to(p->out, s)) return SS2D_EINVAL_ALIGN;
+    a.in = p->in; a.out = p->out;
+    a.B = p->B; a.C = p->C; a.H = p->H; a.W = p->W; a.L = p->H * p->W; a.total = p->B * p->C * a.L;
+    a.x_cf = p->in_channel_first ? 1 : 0; a.r_cf = p->out_channel_first ? 1 : 0;
+    a.one_by_one = p->one_by_one ? 1 : 0; a.scans = p->scans;
+    a.flat_1b1_copy = (p->one_by_one && p->scans == 1) ? 1 : 0;
+    for (int k = 0; k < 4; ++k) a.route[k] = route_map(p->scans, k, p->H, p->W);
+    return SS2D_OK;
+}
+
+template <typename T, bool kScan>
+static int launch_ex(const CrossExArgs& a, cudaStream_t st) {
+    long long ctas = (a.total + 255) / 256;
+    if (ctas > 148LL * 32) ctas = 148LL * 32;
+    if constexpr (kScan) cross_scan_ex_kernel<T><<<(unsigned)ctas, 256, 0, st>>>(a);
+    else cross_merge_ex_kernel<T><<<(unsigned)ctas, 256, 0, st>>>(a);
+    count_launch();
+    return check_launch();
+}
+
+int cross_scan_ex(const ss2d_cross_ex_params* p, cudaStream_t st) {
+    CrossExArgs a;
+    const int rc = fill_ex(p, a);
+    if (rc != SS2D_OK) return rc;
+    if (p->dtype == SS2D_F32) return launch_ex<float, true>(a, st);
+    return launch_ex<unsigned short, true>(a, st);           // 16-bit types: a copy does not look inside
+}
+
+int cross_merge_ex(const ss2d_cross_ex_params* p, cudaStream_t st) {
+    CrossExArgs a;
+    const int rc = fill_ex(p, a);
+    if (rc != SS2D_OK) return rc;
+    if (p->dtype == SS2D_F32) return launch_ex<float, false>(a, st);
+    if (p->dtype == SS2D_BF16) return launch_ex<__nv_bfloat16, false>(a, st);
+    return launch_ex<__half, false>(a, st);
+}
+
 }  // namespace ss2d

@@ -14,7 +14,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from ._lib import (CrossParams, NormParams, PointwiseParams, RelayoutParams, ScanBwdParams, ScanParams, StemParams,
+from ._lib import (CrossExParams, CrossParams, NormParams, PointwiseParams, RelayoutParams, ScanBwdParams, ScanParams, StemParams,
                    check, lib)
 
 _DTYPES = {torch.float32: _lib.SS2D_F32, torch.float16: _lib.SS2D_F16, torch.bfloat16: _lib.SS2D_BF16}
@@ -248,70 +248,148 @@ selective_scan_cuda_oflex = _ExtShim()
 # CrossScan / CrossMerge
 # --------------------------------------------------------------------------------------------
 def _check_flags(in_channel_first, out_channel_first, one_by_one, scans):
-    if not (in_channel_first and out_channel_first):
-        raise NotImplementedError("vmamba_b200: channel-last CrossScan/CrossMerge is not implemented")
-    if one_by_one:
-        raise NotImplementedError("vmamba_b200: one_by_one CrossScan/CrossMerge is not implemented")
+    if one_by_one and not (in_channel_first and out_channel_first):
+        raise NotImplementedError("vmamba_b200: one_by_one CrossScan/CrossMerge is implemented for channel-first tensors only")
     if scans not in (0, 1, 2, 3):
         raise NotImplementedError(f"vmamba_b200: scans={scans} is not implemented")
 
 
-def cross_scan_fwd(x: torch.Tensor, scans: int = 0) -> torch.Tensor:
-    """(B, C, H, W) -> (B, 4, C, H*W), bit-exact data movement (vmamba.py:41-84)."""
+def _plain(in_channel_first, out_channel_first, one_by_one):
+    return bool(in_channel_first) and bool(out_channel_first) and not one_by_one
+
+
+def cross_scan_fwd(x: torch.Tensor, scans: int = 0, in_channel_first=True, out_channel_first=True,
+                   one_by_one=False) -> torch.Tensor:
+    """cross_scan_fwd / cross_scan1b1_fwd of the reference (vmamba.py:41-84, 130-183).  Default flags:
+    (B, C, H, W) -> (B, 4, C, H*W) through the tuned kernels; channel-last sides and one_by_one through the
+    index-only kernels (`ss2d_cross_scan_ex`)."""
     _require_cuda(x)
-    if x.dim() != 4:
-        raise RuntimeError("cross scan expects a (B, C, H, W) tensor")
+    _check_flags(in_channel_first, out_channel_first, one_by_one, scans)
     x = x.contiguous()
-    B, C, H, W = x.shape
-    y = torch.empty((B, 4, C, H * W), device=x.device, dtype=x.dtype)
-    p = CrossParams(x.data_ptr(), y.data_ptr(), dtype_code(x), scans, B, C, H, W)
+    if _plain(in_channel_first, out_channel_first, one_by_one):
+        if x.dim() != 4:
+            raise RuntimeError("cross_scan expects a (B, C, H, W) tensor")
+        B, C, H, W = x.shape
+        y = torch.empty((B, 4, C, H * W), device=x.device, dtype=x.dtype)
+        p = CrossParams(x.data_ptr(), y.data_ptr(), dtype_code(x), scans, B, C, H, W)
+        with torch.cuda.device(x.device):
+            check(lib().ss2d_cross_scan(p, _stream(x)), "ss2d_cross_scan")
+        return y
+    if one_by_one:
+        B, K, C, H, W = x.shape
+        if K != 4:
+            raise RuntimeError("one_by_one expects (B, 4, C, H, W)")
+        # the reference's `x.flatten(2, 3)` for scans 1 merges C with H (vmamba.py:142-143): same shape here
+        oshape = (B, 4, C * H, W) if scans == 1 else (B, 4, C, H * W)
+    elif in_channel_first:
+        B, C, H, W = x.shape
+    else:
+        B, H, W, C = x.shape
+    if not one_by_one:
+        oshape = (B, 4, C, H * W) if out_channel_first else (B, H * W, 4, C)
+    y = torch.empty(oshape, device=x.device, dtype=x.dtype)
+    p = CrossExParams(x.data_ptr(), y.data_ptr(), dtype_code(x), scans, int(bool(in_channel_first)),
+                      int(bool(out_channel_first)), int(bool(one_by_one)), 0, B, C, H, W)
     with torch.cuda.device(x.device):
-        check(lib().ss2d_cross_scan(p, _stream(x)), "ss2d_cross_scan")
+        check(lib().ss2d_cross_scan_ex(p, _stream(x)), "ss2d_cross_scan_ex")
     return y
 
 
-def cross_merge_fwd(ys: torch.Tensor, scans: int = 0) -> torch.Tensor:
-    """(B, 4, C, H, W) -> (B, C, H*W) (vmamba.py:87-130)."""
+def cross_merge_fwd(ys: torch.Tensor, scans: int = 0, in_channel_first=True, out_channel_first=True,
+                    one_by_one=False) -> torch.Tensor:
+    """cross_merge_fwd / cross_merge1b1_fwd of the reference (vmamba.py:87-130, 186-245).  `out_channel_first` names
+    the layout of ys ((B, 4, C, H, W) or (B, H, W, 4, C)), `in_channel_first` the layout of the result ((B, C, L)
+    or (B, L, C)), as there."""
     _require_cuda(ys)
-    if ys.dim() != 5 or ys.shape[1] != 4:
-        raise RuntimeError("cross merge expects a (B, 4, C, H, W) tensor")
+    _check_flags(in_channel_first, out_channel_first, one_by_one, scans)
     ys = ys.contiguous()
-    B, _, C, H, W = ys.shape
-    y = torch.empty((B, C, H * W), device=ys.device, dtype=ys.dtype)
-    p = CrossParams(ys.data_ptr(), y.data_ptr(), dtype_code(ys), scans, B, C, H, W)
+    if ys.dim() != 5:
+        raise RuntimeError("cross_merge expects a 5-d tensor of four routes")
+    if _plain(in_channel_first, out_channel_first, one_by_one):
+        B, K, C, H, W = ys.shape
+        if K != 4:
+            raise RuntimeError("cross_merge expects (B, 4, C, H, W)")
+        y = torch.empty((B, C, H * W), device=ys.device, dtype=ys.dtype)
+        p = CrossParams(ys.data_ptr(), y.data_ptr(), dtype_code(ys), scans, B, C, H, W)
+        with torch.cuda.device(ys.device):
+            check(lib().ss2d_cross_merge(p, _stream(ys)), "ss2d_cross_merge")
+        return y
+    if out_channel_first:
+        B, K, C, H, W = ys.shape
+    else:
+        B, H, W, K, C = ys.shape
+    if K != 4:
+        raise RuntimeError("cross_merge expects four routes")
+    if one_by_one:
+        oshape = (B, 4, C, H * W)
+    else:
+        oshape = (B, C, H * W) if in_channel_first else (B, H * W, C)
+    y = torch.empty(oshape, device=ys.device, dtype=ys.dtype)
+    p = CrossExParams(ys.data_ptr(), y.data_ptr(), dtype_code(ys), scans, int(bool(in_channel_first)),
+                      int(bool(out_channel_first)), int(bool(one_by_one)), 0, B, C, H, W)
     with torch.cuda.device(ys.device):
-        check(lib().ss2d_cross_merge(p, _stream(ys)), "ss2d_cross_merge")
+        check(lib().ss2d_cross_merge_ex(p, _stream(ys)), "ss2d_cross_merge_ex")
     return y
 
 
 class CrossScanF(torch.autograd.Function):
+    """CrossScanF of the reference (csm_triton.py:182-225): forward the scan, backward the merge of the same flags."""
+
     @staticmethod
     def forward(ctx, x, in_channel_first=True, out_channel_first=True, one_by_one=False, scans=0):
         _check_flags(in_channel_first, out_channel_first, one_by_one, scans)
-        ctx.shape, ctx.scans = tuple(x.shape), scans
-        return cross_scan_fwd(x, scans)
+        ctx.flags = (bool(in_channel_first), bool(out_channel_first), bool(one_by_one), scans)
+        if one_by_one:
+            B, _, C, H, W = x.shape
+        elif in_channel_first:
+            B, C, H, W = x.shape
+        else:
+            B, H, W, C = x.shape
+        ctx.shape = (B, C, H, W)
+        return cross_scan_fwd(x, scans, in_channel_first, out_channel_first, one_by_one)
 
     @staticmethod
     def backward(ctx, ys):
         # the adjoint of the four-route copy is the four-route sum (csm_triton.py:207-225)
+        icf, ocf, obo, scans = ctx.flags
         B, C, H, W = ctx.shape
-        ys = ys.contiguous().view(B, 4, C, H, W)
-        return cross_merge_fwd(ys, ctx.scans).view(B, C, H, W), None, None, None, None
+        ys = ys.contiguous().view(B, 4, C, H, W) if ocf else ys.contiguous().view(B, H, W, 4, C)
+        y = cross_merge_fwd(ys, scans, icf, ocf, obo)
+        if obo:
+            y = y.view(B, 4, C, H, W)
+        else:
+            y = y.view(B, C, H, W) if icf else y.view(B, H, W, C)
+        return y, None, None, None, None
 
 
 class CrossMergeF(torch.autograd.Function):
+    """CrossMergeF of the reference (csm_triton.py:228-273): forward the merge, backward the scan of the same flags."""
+
     @staticmethod
     def forward(ctx, ys, in_channel_first=True, out_channel_first=True, one_by_one=False, scans=0):
         _check_flags(in_channel_first, out_channel_first, one_by_one, scans)
-        ctx.shape, ctx.scans = (ys.shape[0], ys.shape[2], ys.shape[3], ys.shape[4]), scans
-        return cross_merge_fwd(ys, scans)
+        ctx.flags = (bool(in_channel_first), bool(out_channel_first), bool(one_by_one), scans)
+        if out_channel_first:
+            B, _, C, H, W = ys.shape
+        else:
+            B, H, W, _, C = ys.shape
+        ctx.shape = (B, C, H, W)
+        return cross_merge_fwd(ys, scans, in_channel_first, out_channel_first, one_by_one)
 
     @staticmethod
     def backward(ctx, x):
         # the adjoint of the four-route sum is the four-route copy (csm_triton.py:248-273)
+        icf, ocf, obo, scans = ctx.flags
         B, C, H, W = ctx.shape
-        xs = cross_scan_fwd(x.contiguous().view(B, C, H, W), ctx.scans)
-        return xs.view(B, 4, C, H, W), None, None, None, None
+        if obo:
+            if scans == 1:          # the forward passed the maps through; so does the adjoint
+                return x.contiguous().view(B, 4, C, H, W), None, None, None, None
+            xin = x.contiguous().view(B, 4, C, H, W)
+        else:
+            xin = x.contiguous().view(B, C, H, W) if icf else x.contiguous().view(B, H, W, C)
+        xs = cross_scan_fwd(xin, scans, icf, ocf, obo)
+        xs = xs.view(B, 4, C, H, W) if ocf else xs.view(B, H, W, 4, C)
+        return xs, None, None, None, None
 
 
 # the CUDA-backed Functions stand in for the reference's Triton Functions too
@@ -325,7 +403,7 @@ def cross_scan_fn(x, in_channel_first=True, out_channel_first=True, one_by_one=F
     _check_flags(in_channel_first, out_channel_first, one_by_one, scans)
     if torch.is_grad_enabled() and x.requires_grad:
         return CrossScanF.apply(x, in_channel_first, out_channel_first, one_by_one, scans)
-    return cross_scan_fwd(x, scans)
+    return cross_scan_fwd(x, scans, in_channel_first, out_channel_first, one_by_one)
 
 
 def cross_merge_fn(y, in_channel_first=True, out_channel_first=True, one_by_one=False, scans=0, force_torch=False):
@@ -333,7 +411,7 @@ def cross_merge_fn(y, in_channel_first=True, out_channel_first=True, one_by_one=
     _check_flags(in_channel_first, out_channel_first, one_by_one, scans)
     if torch.is_grad_enabled() and y.requires_grad:
         return CrossMergeF.apply(y, in_channel_first, out_channel_first, one_by_one, scans)
-    return cross_merge_fwd(y, scans)
+    return cross_merge_fwd(y, scans, in_channel_first, out_channel_first, one_by_one)
 
 
 # --------------------------------------------------------------------------------------------
