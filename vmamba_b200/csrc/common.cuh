@@ -153,6 +153,20 @@ __device__ __forceinline__ float softplus_fast(float x) {
     return (x > 20.0f) ? x : sp;
 }
 
+// softplus(x) and its derivative sigmoid(x) = e^x / (1 + e^x) from one exponential (threshold 20 as torch:
+// above it softplus is x and the derivative 1)
+__device__ __forceinline__ void softplus_and_grad(float x, float& sp, float& dsp) {
+    const float e = ex2_approx(x * kLog2e);
+    const float w = 1.0f + e;
+    const float series = e * fmaf(e, fmaf(e, 0.33333334f, -0.5f), 1.0f);
+    const float full = lg2_approx(w) * kLn2;
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(w));
+    const bool big = x > 20.0f;
+    sp = big ? x : ((e < 0.015625f) ? series : full);
+    dsp = big ? 1.0f : e * r;
+}
+
 // decay exp(dl * A) with A pre-multiplied by log2(e)
 __device__ __forceinline__ float decay_fast(float dl, float A_log2e) { return ex2_approx(dl * A_log2e); }
 

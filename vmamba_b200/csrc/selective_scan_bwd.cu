@@ -124,10 +124,7 @@ __global__ void __launch_bounds__(256) selscan_bwd_kernel(const BwdArgs a) {
             if (in) {
                 float x = dl[i] + bias;
                 dsp[i] = 1.f;
-                if (sp) {
-                    dsp[i] = x > 20.f ? 1.f : 1.f / (1.f + expf(-x));
-                    x = softplus_fast(x);
-                }
+                if (sp) softplus_and_grad(x, x, dsp[i]);
                 dl[i] = x;
             } else { dl[i] = 0.f; uv[i] = 0.f; gv[i] = 0.f; dsp[i] = 0.f; }
             du_acc[i] = has_D ? gv[i] * Dv : 0.f;
@@ -337,10 +334,7 @@ __global__ void __launch_bounds__(256) selscan_bwd_n1_kernel(const BwdArgs a, co
                     if (in_l) {
                         float x = dl[e] + bias;
                         dsp[e] = 1.f;
-                        if (sp) {
-                            dsp[e] = x > 20.f ? 1.f : 1.f / (1.f + expf(-x));
-                            x = softplus_fast(x);
-                        }
+                        if (sp) softplus_and_grad(x, x, dsp[e]);
                         dl[e] = x;
                         av[e] = decay_fast(x, A2);
                     } else { dl[e] = 0.f; uv[e] = 0.f; gv[e] = 0.f; dsp[e] = 0.f; av[e] = 1.f; }
