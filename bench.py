@@ -228,7 +228,8 @@ def op_sweep(args):
                 # gradients of the same cell: reads u, delta, dout (fp32), B, C; writes du, ddelta, dB, dC
                 from vmamba_b200 import ops as _ops
                 dout = torch.randn((Bt, K * D, L), device="cuda", generator=g)
-                ms = time_events(lambda: _ops.selective_scan_bwd(u, delta, A, Bm, Cm, Dp, bias, dout, True), args.steps)
+                _, ck = _ops.selective_scan_fwd(u, delta, A, Bm, Cm, Dp, bias, True, True, return_checkpoints=True)
+                ms = time_events(lambda: _ops.selective_scan_bwd(u, delta, A, Bm, Cm, Dp, bias, dout, True, ck), args.steps)
                 nbytes = Bt * L * (K * D * (2 * 2 + 4 + 2 * 2) + 4 * K * N * 2) + 4 * (2 * K * D * N + 4 * K * D)
                 gbs = nbytes / (ms * 1e-3) / 1e9
                 print(json.dumps({"op": "selective_scan_bwd", "dtype": "bf16, dout f32", "d_state": N, "D": D, "L": L, "batch": Bt,

@@ -68,6 +68,9 @@ typedef struct ss2d_scan_params {
     int64_t out_batch_stride, out_dim_stride;
     int64_t B_batch_stride, B_group_stride, B_state_stride;
     int64_t C_batch_stride, C_group_stride, C_state_stride;
+    void *checkpoints;                  /* optional, fp32 (batch, dim, ceil(seqlen / 128), dstate) contiguous: the state
+                                           in front of every 128th element, for ss2d_selective_scan_bwd (the reference
+                                           hands its backward the chunk states `x` the same way, selective_scan_oflex.cpp:208) */
 } ss2d_scan_params;
 
 int ss2d_selective_scan_fwd(const ss2d_scan_params *p, void *cuda_stream);
@@ -105,6 +108,7 @@ typedef struct ss2d_scan_bwd_params {
     int64_t dout_batch_stride, dout_dim_stride;
     int64_t B_batch_stride, B_group_stride, B_state_stride;
     int64_t C_batch_stride, C_group_stride, C_state_stride;
+    const void *checkpoints;            /* optional: what the forward call wrote; saves the pass that recomputes the states */
 } ss2d_scan_bwd_params;
 
 int64_t ss2d_selective_scan_bwd_workspace_bytes(const ss2d_scan_bwd_params *p);   /* < 0: invalid or unsupported arguments */

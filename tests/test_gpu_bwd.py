@@ -184,7 +184,7 @@ def test_extension_module_surface(vb):
     ext = vb.selective_scan_cuda_oflex
     out, x, *rest = ext.fwd(u, delta, A, B, C, D, bias, True, 1, True)
     assert torch.equal(out, vb.selective_scan_fwd(u, delta, A, B, C, D, bias, True, True))
-    assert tuple(x.shape) == (2, 12, 1, 2)
+    assert tuple(x.shape) == (2, 12, 2, 1)      # states in front of elements 0 and 128
     du, ddelta, dA, dB, dC, dD, dbias, *rest = ext.bwd(u, delta, A, B, C, D, bias, dout, x, True, 1)
     ref = O.selective_scan_bwd(*(host(t) for t in (u, delta, A, B, C, D, bias, dout)), True, "f32")
     for name, got, r in zip(NAMES, (du, ddelta, dA, dB, dC, dD, dbias), ref):
@@ -213,3 +213,29 @@ def test_shared_delta_rows_forward_and_backward(vb, ratio):
     assert tuple(got[1].shape) == (Bt, KC // ratio, L) and tuple(got[6].shape) == (KC // ratio,)
     for name, x, r in zip(NAMES, got, ref):
         assert O.max_rel_err(host(x), r) <= TOL["f32"], name
+
+
+@pytest.mark.parametrize("N,L", [(1, 3136), (1, 200), (3, 300), (1, 90)])
+def test_backward_with_and_without_forward_checkpoints(vb, N, L):
+    """The step states written by the forward call give the same gradients as recomputing them (to fp32 rounding: the
+    forward kernel composes the recurrence in 256-element steps, the recomputation in 128-element steps), and the
+    checkpoints are the oracle's states in front of every 128th element."""
+    from vmamba_b200 import ops
+    u, delta, A, B, C, D, bias, dout = _random_case(2, 2, 3, N, L, seed=L)
+    args = [dev(t) for t in (u, delta, A, B, C, D, bias)]
+    out, ck = ops.selective_scan_fwd(*args, True, True, return_checkpoints=True)
+    assert torch.equal(out, ops.selective_scan_fwd(*args, True, True))
+    g1 = ops.selective_scan_bwd(*args, dev(dout), True)
+    g2 = ops.selective_scan_bwd(*args, dev(dout), True, checkpoints=ck)
+    for a_, b_ in zip(g1, g2):
+        assert O.max_rel_err(host(a_), host(b_)) <= 1e-5
+    # states by the oracle's recurrence
+    dl = O.softplus(delta + bias[None, :, None])
+    Bx = np.repeat(B, 3, axis=1).reshape(2, 6, N, L)
+    h = np.zeros((2, 6, N), np.float32)
+    want = np.zeros((2, 6, (L + 127) // 128, N), np.float32)
+    for i in range(L):
+        if i % 128 == 0:
+            want[:, :, i // 128] = h
+        h = np.exp(dl[:, :, i, None] * A[None]) * h + (dl[:, :, i] * u[:, :, i])[:, :, None] * Bx[..., i]
+    assert O.max_rel_err(host(ck), want) <= 1e-4

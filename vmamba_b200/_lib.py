@@ -26,7 +26,8 @@ class ScanParams(ctypes.Structure):
                                     "u_batch_stride", "u_dim_stride", "delta_batch_stride", "delta_dim_stride",
                                     "out_batch_stride", "out_dim_stride",
                                     "B_batch_stride", "B_group_stride", "B_state_stride",
-                                    "C_batch_stride", "C_group_stride", "C_state_stride")]
+                                    "C_batch_stride", "C_group_stride", "C_state_stride")] + \
+               [("checkpoints", _vp)]
 
 
 class ScanBwdParams(ctypes.Structure):
@@ -38,7 +39,8 @@ class ScanBwdParams(ctypes.Structure):
                                     "u_batch_stride", "u_dim_stride", "delta_batch_stride", "delta_dim_stride",
                                     "dout_batch_stride", "dout_dim_stride",
                                     "B_batch_stride", "B_group_stride", "B_state_stride",
-                                    "C_batch_stride", "C_group_stride", "C_state_stride")]
+                                    "C_batch_stride", "C_group_stride", "C_state_stride")] + \
+               [("checkpoints", _vp)]
 
 
 class CrossParams(ctypes.Structure):

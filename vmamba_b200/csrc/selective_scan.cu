@@ -20,6 +20,8 @@ struct ScanArgs {
     int64_t B_bs, B_gs, B_ss, C_bs, C_gs, C_ss;
     int softplus;
     int64_t dratio;   // channels per delta row
+    float* ckpt;      // (rows, nck, dstate) or null
+    int64_t nck;
 };
 
 constexpr int kWarpsPerCta = 4;
@@ -76,6 +78,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) selscan_fwd_n1_kernel(const
         float eb = __shfl_up_sync(0xffffffffu, inc.b, 1);
         if (lane == 0) { ea = 1.f; eb = 0.f; }
         const float hin = fmaf(ea, hc, eb);
+        if (a.ckpt && (pos & 127) == 0 && pos < L) a.ckpt[row * a.nck + (pos >> 7)] = hin;     // state in front of element pos
         const float ta = __shfl_sync(0xffffffffu, inc.a, 31);
         const float tb = __shfl_sync(0xffffffffu, inc.b, 31);
         hc = fmaf(ta, hc, tb);
@@ -160,6 +163,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) selscan_fwd_nx_kernel(const
             if (lane == 0) { ea = 1.f; eb = 0.f; }
             const float hc = carry_s[warp][n];
             const float hin = fmaf(ea, hc, eb);
+            if (a.ckpt && (pos & 127) == 0 && in) a.ckpt[(row * a.nck + (pos >> 7)) * N + n] = hin;
             __syncwarp();
             if (lane == 31) carry_s[warp][n] = fmaf(inc.a, hc, inc.b);
 #pragma unroll
@@ -221,7 +225,7 @@ int selective_scan_fwd(const ss2d_scan_params* p, cudaStream_t st) {
     if (p->n_groups > 1 && (p->B_group_stride < L || p->C_group_stride < L)) return SS2D_EINVAL_STRIDE;
     const size_t si = dtype_size(p->in_dtype), so = dtype_size(p->out_dtype);
     if (!aligned_to(p->u, si) || !aligned_to(p->delta, si) || !aligned_to(p->B, si) || !aligned_to(p->C, si) ||
-        !aligned_to(p->out, so) || !aligned_to(p->A, 4) || !aligned_to(p->D, 4) || !aligned_to(p->delta_bias, 4))
+        !aligned_to(p->out, so) || !aligned_to(p->checkpoints, 4) || !aligned_to(p->A, 4) || !aligned_to(p->D, 4) || !aligned_to(p->delta_bias, 4))
         return SS2D_EINVAL_ALIGN;
 
     ScanArgs a;
@@ -237,6 +241,7 @@ int selective_scan_fwd(const ss2d_scan_params* p, cudaStream_t st) {
     a.C_bs = p->C_batch_stride; a.C_gs = p->C_group_stride; a.C_ss = p->C_state_stride;
     a.softplus = p->delta_softplus;
     a.dratio = p->delta_ratio > 1 ? p->delta_ratio : 1;
+    a.ckpt = (float*)p->checkpoints; a.nck = (L + 127) / 128;
 
     // widest vector (in elements) that keeps every row start aligned for every tensor
     const int cap = (si == 2) ? 8 : 4;

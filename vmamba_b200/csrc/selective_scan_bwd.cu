@@ -36,6 +36,8 @@ struct BwdArgs {
     int64_t B_bs, B_gs, B_ss, C_bs, C_gs, C_ss;
     int N, n_groups, parts, nsteps, softplus;
     int64_t dratio;   // channels per delta row
+    const float* ckpt;   // states in front of every 128th element (rows, nck, N), or null: recompute them
+    int64_t nck;
 };
 
 template <typename Tin, typename Tg, int VEC>
@@ -78,8 +80,13 @@ __global__ void __launch_bounds__(256) selscan_bwd_kernel(const BwdArgs a) {
     }
     __syncwarp();
 
-    // ---- pass 1: the state entering every step ---------------------------------------------------
-    for (int s = 0; s < nsteps; ++s) {
+    // ---- pass 1: the state entering every step (from the forward call's checkpoints when the steps line up) ------
+    const bool have_ckpt = a.ckpt != nullptr && STEP == 128;
+    if (have_ckpt) {
+        const float* ck = a.ckpt + (b * a.dim + r) * a.nck * N;
+        for (int i = lane; i < nsteps * N; i += 32) hstart[i] = valid ? ck[i] : 0.f;
+    }
+    for (int s = 0; s < (have_ckpt ? 0 : nsteps); ++s) {
         const int pos = s * STEP + lane * VEC;
         const bool in = valid && pos < L;
         float uv[VEC], dl[VEC];
@@ -257,6 +264,11 @@ __global__ void __launch_bounds__(256) selscan_bwd_n1_kernel(const BwdArgs a, co
         if (lane == 0) ecar[lr] = 0.f;
         if (ig >= a.group_size) continue;               // uniform over the warp
         const int64_t r = (int64_t)k * a.group_size + ig;
+        if (a.ckpt != nullptr && STEP == 128) {         // the forward call left the step states: no recomputation
+            const float* ck = a.ckpt + (b * a.dim + r) * a.nck;
+            for (int s = lane; s < nsteps; s += 32) hstart[(size_t)lr * nsteps + s] = ck[s];
+            continue;
+        }
         const Tin* __restrict__ u = (const Tin*)a.u + b * a.u_bs + r * a.u_ds;
         const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + (r / a.dratio) * a.d_ds;
         const float A2 = __ldg(a.A + r) * kLog2e;
@@ -591,6 +603,7 @@ int selective_scan_bwd(const ss2d_scan_bwd_params* p, cudaStream_t st) {
     a.C_bs = p->C_batch_stride; a.C_gs = p->C_group_stride; a.C_ss = p->C_state_stride;
     a.N = (int)p->dstate; a.n_groups = (int)p->n_groups; a.parts = c.parts; a.nsteps = c.nsteps; a.softplus = p->delta_softplus;
     a.dratio = p->delta_ratio > 1 ? p->delta_ratio : 1;
+    a.ckpt = (const float*)p->checkpoints; a.nck = (p->seqlen + 127) / 128;
     const int64_t ctas = p->batch * p->n_groups * c.parts;
     if (ctas > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
     const bool gf32 = p->dout_dtype == SS2D_F32;

@@ -45,11 +45,14 @@ def _ptr(t):
 # --------------------------------------------------------------------------------------------
 # selective scan
 # --------------------------------------------------------------------------------------------
-def selective_scan_fwd(u, delta, A, B, C, D=None, delta_bias=None, delta_softplus=False, out_float=True):
+def selective_scan_fwd(u, delta, A, B, C, D=None, delta_bias=None, delta_softplus=False, out_float=True,
+                       return_checkpoints=False):
     """out = selective scan of (u, delta, A, B, C [, D, delta_bias]); see include/ss2d_b200.h.
 
     u, delta: (batch, K*C, L); A: (K*C, N); B, C: (batch, K, N, L); D, delta_bias: (K*C,) fp32.
-    Output fp32 if `out_float` (the reference's "oflex") else u.dtype.
+    Output fp32 if `out_float` (the reference's "oflex") else u.dtype.  With `return_checkpoints` also the fp32
+    states in front of every 128th element, (batch, K*C, ceil(L/128), N), which `selective_scan_bwd` accepts
+    instead of recomputing them.
     """
     _require_cuda(u, delta, A, B, C, D, delta_bias)
     if u.dim() != 3 or delta.dim() != 3 or delta.shape[0] != u.shape[0] or delta.shape[2] != u.shape[2] \
@@ -92,14 +95,19 @@ def selective_scan_fwd(u, delta, A, B, C, D=None, delta_bias=None, delta_softplu
     p.out_batch_stride, p.out_dim_stride = out.stride(0), out.stride(1)
     p.B_batch_stride, p.B_group_stride, p.B_state_stride = B.stride(0), B.stride(1), B.stride(2)
     p.C_batch_stride, p.C_group_stride, p.C_state_stride = C.stride(0), C.stride(1), C.stride(2)
+    ckpt = None
+    if return_checkpoints:
+        ckpt = torch.empty((batch, dim, (L + 127) // 128, N), device=u.device, dtype=torch.float32)
+        p.checkpoints = ckpt.data_ptr()
     with torch.cuda.device(u.device):
         check(lib().ss2d_selective_scan_fwd(p, _stream(u)), "ss2d_selective_scan_fwd")
-    return out
+    return (out, ckpt) if return_checkpoints else out
 
 
-def selective_scan_bwd(u, delta, A, B, C, D, delta_bias, dout, delta_softplus=False):
+def selective_scan_bwd(u, delta, A, B, C, D, delta_bias, dout, delta_softplus=False, checkpoints=None):
     """Gradients (du, ddelta, dA, dB, dC, dD, ddelta_bias) of `selective_scan_fwd` for the upstream
     gradient dout (batch, dim, L), fp32 or u.dtype; dD / ddelta_bias are None where the input was None.
+    `checkpoints`: what `selective_scan_fwd(..., return_checkpoints=True)` returned (optional).
     Shapes and types of the results as selective_scan_cuda_oflex.bwd returns them
     (selective_scan_oflex.cpp:308-353)."""
     _require_cuda(u, delta, A, B, C, D, delta_bias, dout)
@@ -133,6 +141,11 @@ def selective_scan_bwd(u, delta, A, B, C, D, delta_bias, dout, delta_softplus=Fa
     p.dout_batch_stride, p.dout_dim_stride = dout.stride(0), dout.stride(1)
     p.B_batch_stride, p.B_group_stride, p.B_state_stride = B.stride(0), B.stride(1), B.stride(2)
     p.C_batch_stride, p.C_group_stride, p.C_state_stride = C.stride(0), C.stride(1), C.stride(2)
+    if checkpoints is not None:
+        if checkpoints.dtype != torch.float32 or tuple(checkpoints.shape) != (batch, dim, (L + 127) // 128, N) \
+                or not checkpoints.is_contiguous() or checkpoints.device != u.device:
+            raise RuntimeError("checkpoints must be the fp32 (batch, dim, ceil(L/128), dstate) tensor of the forward call")
+        p.checkpoints = checkpoints.data_ptr()
     need = int(lib().ss2d_selective_scan_bwd_workspace_bytes(p))
     if need < 0:
         raise RuntimeError("ss2d_selective_scan_bwd_workspace_bytes: invalid or unsupported arguments")
@@ -162,21 +175,23 @@ class SelectiveScanCuda(torch.autograd.Function):
         ctx.delta_softplus = delta_softplus
         ctx.backend = backend
         ctx.has_D, ctx.has_bias = D is not None, delta_bias is not None
-        saved = [u, delta, A, B, C] + ([D] if ctx.has_D else []) + ([delta_bias] if ctx.has_bias else [])
+        # the step states go to the backward call, as the reference's `x` does (csms6s.py:81-86)
+        out, ckpt = selective_scan_fwd(u, delta, A, B, C, D, delta_bias, delta_softplus, bool(oflex), return_checkpoints=True)
+        saved = [u, delta, A, B, C, ckpt] + ([D] if ctx.has_D else []) + ([delta_bias] if ctx.has_bias else [])
         ctx.save_for_backward(*saved)
-        return selective_scan_fwd(u, delta, A, B, C, D, delta_bias, delta_softplus, bool(oflex))
+        return out
 
     @staticmethod
     @torch.amp.custom_bwd(device_type="cuda")
     def backward(ctx, dout, *args):
         saved = list(ctx.saved_tensors)
-        u, delta, A, B, C = saved[:5]
-        rest = saved[5:]
+        u, delta, A, B, C, ckpt = saved[:6]
+        rest = saved[6:]
         D = rest.pop(0) if ctx.has_D else None
         delta_bias = rest.pop(0) if ctx.has_bias else None
         if dout.stride(-1) != 1:
             dout = dout.contiguous()
-        du, ddelta, dA, dB, dC, dD, dbias = selective_scan_bwd(u, delta, A, B, C, D, delta_bias, dout, ctx.delta_softplus)
+        du, ddelta, dA, dB, dC, dD, dbias = selective_scan_bwd(u, delta, A, B, C, D, delta_bias, dout, ctx.delta_softplus, ckpt)
         dA = dA.to(A.dtype)
         if dD is not None:
             dD = dD.to(D.dtype)
@@ -229,16 +244,16 @@ class _ExtShim:
 
     @staticmethod
     def fwd(u, delta, A, B, C, D=None, delta_bias=None, delta_softplus=False, nrows=1, out_float=True):
-        out = selective_scan_fwd(u, delta, A, B, C, D, delta_bias, delta_softplus, bool(out_float))
-        # the reference returns its chunk states here and wants them back in bwd; this library
-        # recomputes the states, so the tensor only keeps the shape (batch, dim, n_chunks, 2 * dstate)
-        n_chunks = (u.shape[-1] + 2047) // 2048
-        x = torch.zeros((u.shape[0], u.shape[1], n_chunks, 2 * A.shape[1]), device=u.device, dtype=torch.float32)
+        # the reference returns its chunk states `x` here and wants them back in bwd; so does this library, with
+        # its own spacing: (batch, dim, ceil(L / 128), dstate)
+        out, x = selective_scan_fwd(u, delta, A, B, C, D, delta_bias, delta_softplus, bool(out_float), return_checkpoints=True)
         return [out, x]
 
     @staticmethod
     def bwd(u, delta, A, B, C, D, delta_bias, dout, x=None, delta_softplus=False, nrows=1):
-        return list(selective_scan_bwd(u, delta, A, B, C, D, delta_bias, dout, delta_softplus))
+        L, N = u.shape[-1], A.shape[1]
+        ok = x is not None and x.dtype == torch.float32 and tuple(x.shape) == (u.shape[0], u.shape[1], (L + 127) // 128, N)
+        return list(selective_scan_bwd(u, delta, A, B, C, D, delta_bias, dout, delta_softplus, x.contiguous() if ok else None))
 
 
 selective_scan_cuda_oflex = _ExtShim()
