@@ -26,9 +26,15 @@ struct NormArgs {
     int skip_norm;           // 1: out = s converted, no statistics (a fused add + cast + layout change)
 };
 
-template <typename Tio, int NTY, int CACHE, int PV, int TX>
-__global__ void __launch_bounds__(TX * NTY) layer_norm_cf_kernel(const NormArgs a) {
-    __shared__ float red[NTY][TX][PV];
+// MODE picks what the compiler may assume.  0: nothing (every optional pointer is tested, D <= NTY * CACHE).
+// 1..3 are the shapes a backbone forward uses, with D == NTY * CACHE, `in`, weight and bias present and the
+// normalisation on: 1 = `in` alone; 2 = in + add, sum written back; 3 = in + add + add_bias, sum written back.
+// Without the per-channel tests of the general form the kernel issues about half the instructions.
+template <typename Tio, int NTY, int CACHE, int PV, int TX, int MODE>
+__global__ void __launch_bounds__(TX * NTY, (NTY == 32 && CACHE > 0 && CACHE * PV <= 24) ? 2 : 1) layer_norm_cf_kernel(const NormArgs a) {
+    static_assert(TX == 16 && NTY % 4 == 0, "a warp is two channel slices of 16 items");
+    constexpr int NP = NTY / 2;                      // partial sums per item after the in-warp step
+    __shared__ float red[2][NP][TX][PV];
     const int tx = threadIdx.x, ty = threadIdx.y;
     const int item = blockIdx.x * TX + tx;
     const bool live = item < a.items;
@@ -36,8 +42,13 @@ __global__ void __launch_bounds__(TX * NTY) layer_norm_cf_kernel(const NormArgs 
     const long long pix = (long long)(live ? (item - bimg * a.nv) : 0) * PV;
     const long long base = (long long)bimg * a.bs + pix;
     const float* __restrict__ src = a.in + base;
-    const Tio* __restrict__ addp = a.add ? (const Tio*)a.add + base : nullptr;
     const int D = a.D;
+    const bool has_in = MODE ? true : a.in != nullptr;
+    const bool has_add = MODE ? MODE >= 2 : a.add != nullptr;
+    const bool has_ab = MODE ? MODE == 3 : a.add_bias != nullptr;
+    const bool has_so = MODE ? MODE >= 2 : a.sum_out != nullptr;
+    const Tio* __restrict__ addp = has_add ? (const Tio*)a.add + base : nullptr;
+    auto in_range = [&](int d) { return MODE ? true : d < D; };
 
     auto fetch = [&](int d, float (&v)[PV]) {
         if (!live) {
@@ -46,36 +57,45 @@ __global__ void __launch_bounds__(TX * NTY) layer_norm_cf_kernel(const NormArgs 
             return;
         }
         const long long off = (long long)d * a.cs;
-        if (a.in) Vec<float, PV>::load_plain(src + off, v);      // `in` may alias `sum_out`: no read-only path
+        if (has_in) Vec<float, PV>::load_plain(src + off, v);      // `in` may alias `sum_out`: no read-only path
         else {
 #pragma unroll
             for (int i = 0; i < PV; ++i) v[i] = 0.f;
         }
-        if (addp) {
+        if (has_add) {
             float t[PV];
             Vec<Tio, PV>::load(addp + off, t);
 #pragma unroll
             for (int i = 0; i < PV; ++i) v[i] += t[i];
         }
-        if (a.add_bias) {
+        if (has_ab) {
             const float bb = __ldg(a.add_bias + d);
 #pragma unroll
             for (int i = 0; i < PV; ++i) v[i] += bb;
         }
-        if (a.sum_out) Vec<float, PV>::store(a.sum_out + base + off, v);
+        if (has_so) Vec<float, PV>::store(a.sum_out + base + off, v);
     };
-    auto reduce_over_ty = [&](float (&v)[PV]) {
+    // Sum over the NTY channel slices of an item.  A warp holds two slices of the same 16 items: one shuffle
+    // adds them, the even slice parks the pair sum, and after the barrier each half of the warp adds half of
+    // the NP pair sums, a second shuffle joining the halves.  `which` picks one of two buffers, so the
+    // second reduction needs no barrier to protect the first one's readers.
+    auto reduce_over_ty = [&](float (&v)[PV], int which) {
 #pragma unroll
-        for (int i = 0; i < PV; ++i) red[ty][tx][i] = v[i];
+        for (int i = 0; i < PV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], 16);
+        if ((ty & 1) == 0) Vec<float, PV>::store(&red[which][ty >> 1][tx][0], v);
         __syncthreads();
+        const int h = ty & 1;
 #pragma unroll
-        for (int i = 0; i < PV; ++i) {
-            float s = 0.f;
+        for (int i = 0; i < PV; ++i) v[i] = 0.f;
 #pragma unroll
-            for (int j = 0; j < NTY; ++j) s += red[j][tx][i];
-            v[i] = s;
+        for (int j = 0; j < NP / 2; ++j) {
+            float t[PV];
+            Vec<float, PV>::load_plain(&red[which][h * (NP / 2) + j][tx][0], t);
+#pragma unroll
+            for (int i = 0; i < PV; ++i) v[i] += t[i];
         }
-        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < PV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], 16);
     };
 
     float cache[CACHE > 0 ? CACHE : 1][PV];
@@ -89,30 +109,30 @@ __global__ void __launch_bounds__(TX * NTY) layer_norm_cf_kernel(const NormArgs 
 #pragma unroll
         for (int c = 0; c < CACHE; ++c) {
             const int d = ty + c * NTY;
-            if (live && d < D && a.in) Vec<float, PV>::load_plain(src + (long long)d * a.cs, cache[c]);
+            if (live && in_range(d) && has_in) Vec<float, PV>::load_plain(src + (long long)d * a.cs, cache[c]);
             else {
 #pragma unroll
                 for (int i = 0; i < PV; ++i) cache[c][i] = 0.f;
             }
         }
-        if (addp) {
+        if (has_add) {
 #pragma unroll
             for (int c = 0; c < CACHE; ++c) {
                 const int d = ty + c * NTY;
-                if (live && d < D) addraw[c] = Vec<Tio, PV>::load_raw(addp + (long long)d * a.cs);
+                if (live && in_range(d)) addraw[c] = Vec<Tio, PV>::load_raw(addp + (long long)d * a.cs);
             }
         }
 #pragma unroll
         for (int c = 0; c < CACHE; ++c) {
             const int d = ty + c * NTY;
-            if (live && d < D) {
-                if (addp) {
+            if (live && in_range(d)) {
+                if (has_add) {
                     float tv[PV];
                     Vec<Tio, PV>::unpack(addraw[c], tv);
 #pragma unroll
                     for (int i = 0; i < PV; ++i) cache[c][i] += tv[i];
                 }
-                if (a.add_bias) {
+                if (has_ab) {
                     const float bb = __ldg(a.add_bias + d);
 #pragma unroll
                     for (int i = 0; i < PV; ++i) cache[c][i] += bb;
@@ -121,11 +141,11 @@ __global__ void __launch_bounds__(TX * NTY) layer_norm_cf_kernel(const NormArgs 
 #pragma unroll
             for (int i = 0; i < PV; ++i) s[i] += cache[c][i];
         }
-        if (a.sum_out && live) {
+        if (has_so && live) {
 #pragma unroll
             for (int c = 0; c < CACHE; ++c) {
                 const int d = ty + c * NTY;
-                if (d < D) Vec<float, PV>::store(a.sum_out + base + (long long)d * a.cs, cache[c]);
+                if (in_range(d)) Vec<float, PV>::store(a.sum_out + base + (long long)d * a.cs, cache[c]);
             }
         }
     } else {
@@ -136,13 +156,14 @@ __global__ void __launch_bounds__(TX * NTY) layer_norm_cf_kernel(const NormArgs 
             for (int i = 0; i < PV; ++i) s[i] += v[i];
         }
     }
-    const bool norm = a.skip_norm == 0;      // uniform over the grid
-    if (norm) reduce_over_ty(s);
+    const bool norm = MODE ? true : a.skip_norm == 0;      // uniform over the grid
+    const float inv_d = 1.0f / (float)D;
+    if (norm) reduce_over_ty(s, 0);
     float mean[PV], q[PV];
 #pragma unroll
-    for (int i = 0; i < PV; ++i) { mean[i] = norm ? s[i] / (float)D : 0.f; q[i] = 0.f; }
+    for (int i = 0; i < PV; ++i) { mean[i] = norm ? s[i] * inv_d : 0.f; q[i] = 0.f; }
     // after the first pass the sum lives in sum_out (if any): re-reads must not add again
-    const float* __restrict__ again = a.sum_out ? a.sum_out + base : nullptr;
+    const float* __restrict__ again = has_so ? a.sum_out + base : nullptr;
     auto refetch = [&](int d, float (&v)[PV]) {
         if (!live) {
 #pragma unroll
@@ -151,18 +172,18 @@ __global__ void __launch_bounds__(TX * NTY) layer_norm_cf_kernel(const NormArgs 
         }
         const long long off = (long long)d * a.cs;
         if (again) { Vec<float, PV>::load_plain(again + off, v); return; }
-        if (a.in) Vec<float, PV>::load_plain(src + off, v);
+        if (has_in) Vec<float, PV>::load_plain(src + off, v);
         else {
 #pragma unroll
             for (int i = 0; i < PV; ++i) v[i] = 0.f;
         }
-        if (addp) {
+        if (has_add) {
             float t[PV];
             Vec<Tio, PV>::load(addp + off, t);
 #pragma unroll
             for (int i = 0; i < PV; ++i) v[i] += t[i];
         }
-        if (a.add_bias) {
+        if (has_ab) {
             const float bb = __ldg(a.add_bias + d);
 #pragma unroll
             for (int i = 0; i < PV; ++i) v[i] += bb;
@@ -172,7 +193,7 @@ __global__ void __launch_bounds__(TX * NTY) layer_norm_cf_kernel(const NormArgs 
         if constexpr (CACHE > 0) {
 #pragma unroll
             for (int c = 0; c < CACHE; ++c) {
-                if (ty + c * NTY < D) {
+                if (in_range(ty + c * NTY)) {
 #pragma unroll
                     for (int i = 0; i < PV; ++i) { const float t = cache[c][i] - mean[i]; q[i] = fmaf(t, t, q[i]); }
                 }
@@ -185,15 +206,16 @@ __global__ void __launch_bounds__(TX * NTY) layer_norm_cf_kernel(const NormArgs 
                 for (int i = 0; i < PV; ++i) { const float t = v[i] - mean[i]; q[i] = fmaf(t, t, q[i]); }
             }
         }
-        reduce_over_ty(q);
+        reduce_over_ty(q, 1);
     }
     if (!live) return;
     float rstd[PV];
 #pragma unroll
-    for (int i = 0; i < PV; ++i) rstd[i] = norm ? rsqrtf(q[i] / (float)D + a.eps) : 1.f;
+    for (int i = 0; i < PV; ++i) rstd[i] = norm ? rsqrtf(fmaf(q[i], inv_d, a.eps)) : 1.f;
     Tio* __restrict__ dst = (Tio*)a.out + (long long)bimg * a.obs + pix;
+    const bool has_w = MODE ? true : (norm && a.w), has_b = MODE ? true : (norm && a.b);
     auto emit = [&](int d, const float (&v)[PV]) {
-        const float g = (norm && a.w) ? __ldg(a.w + d) : 1.f, be = (norm && a.b) ? __ldg(a.b + d) : 0.f;
+        const float g = has_w ? __ldg(a.w + d) : 1.f, be = has_b ? __ldg(a.b + d) : 0.f;
         float o[PV];
 #pragma unroll
         for (int i = 0; i < PV; ++i) o[i] = fmaf((v[i] - mean[i]) * rstd[i], g, be);
@@ -203,7 +225,7 @@ __global__ void __launch_bounds__(TX * NTY) layer_norm_cf_kernel(const NormArgs 
 #pragma unroll
         for (int c = 0; c < CACHE; ++c) {
             const int d = ty + c * NTY;
-            if (d < D) emit(d, cache[c]);
+            if (in_range(d)) emit(d, cache[c]);
         }
     } else {
         for (int d = ty; d < D; d += NTY) {
@@ -221,8 +243,18 @@ constexpr int kItemsPerCta = 16;
 
 template <typename Tio, int NTY, int CACHE, int PV>
 static void launch_one(const NormArgs& a, cudaStream_t st) {
-    layer_norm_cf_kernel<Tio, NTY, CACHE, PV, kItemsPerCta>
-        <<<(unsigned)((a.items + kItemsPerCta - 1) / kItemsPerCta), dim3(kItemsPerCta, NTY), 0, st>>>(a);
+    const dim3 grid((unsigned)((a.items + kItemsPerCta - 1) / kItemsPerCta)), block(kItemsPerCta, NTY);
+    int mode = 0;
+    if constexpr (CACHE > 0 && CACHE <= 32) {
+        if (a.D == NTY * CACHE && a.in && a.w && a.b && !a.skip_norm) {
+            if (!a.add && !a.add_bias && !a.sum_out) mode = 1;
+            else if (a.add && a.sum_out) mode = a.add_bias ? 3 : 2;
+        }
+        if (mode == 1) { layer_norm_cf_kernel<Tio, NTY, CACHE, PV, kItemsPerCta, 1><<<grid, block, 0, st>>>(a); return; }
+        if (mode == 2) { layer_norm_cf_kernel<Tio, NTY, CACHE, PV, kItemsPerCta, 2><<<grid, block, 0, st>>>(a); return; }
+        if (mode == 3) { layer_norm_cf_kernel<Tio, NTY, CACHE, PV, kItemsPerCta, 3><<<grid, block, 0, st>>>(a); return; }
+    }
+    layer_norm_cf_kernel<Tio, NTY, CACHE, PV, kItemsPerCta, 0><<<grid, block, 0, st>>>(a);
 }
 
 template <typename Tio>
@@ -268,9 +300,15 @@ int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st) {
     if (!aligned_to(p->in, 4) || !aligned_to(p->out, so) || !aligned_to(p->weight, 4) || !aligned_to(p->bias, 4) ||
         !aligned_to(p->add, so) || !aligned_to(p->add_bias, 4) || !aligned_to(p->sum_out, 4))
         return SS2D_EINVAL_ALIGN;
+    // channel-major on both sides: the pixels of consecutive images follow one another, so the batch is one
+    // long row per channel (wider vectors for odd map sizes such as 7 x 7)
+    long long B = p->B, L = p->L;
+    if (bs == L && obs == L && B * L <= 0x7fffffffLL) { L *= B; B = 1; }
     int pv = 4;
     auto fit = [&](long long x) { if (x < 0) x = -x; while (pv > 1 && (x % pv) != 0) pv >>= 1; };
-    fit(p->L); fit(bs); fit(cs); fit(obs); fit(ocs);
+    fit(L);
+    if (B > 1) { fit(bs); fit(obs); }
+    fit(cs); fit(ocs);
     if (p->in) fit((long long)(reinterpret_cast<uintptr_t>(p->in) / 4));
     fit((long long)(reinterpret_cast<uintptr_t>(p->out) / so));
     if (p->add) fit((long long)(reinterpret_cast<uintptr_t>(p->add) / so));
@@ -278,11 +316,11 @@ int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st) {
     NormArgs a;
     a.in = (const float*)p->in; a.add = p->add; a.add_bias = (const float*)p->add_bias; a.sum_out = (float*)p->sum_out;
     a.w = (const float*)p->weight; a.b = (const float*)p->bias; a.out = p->out;
-    a.bs = bs; a.cs = cs; a.obs = obs; a.ocs = ocs; a.D = (int)p->D; a.L = (int)p->L; a.eps = p->eps; a.nv = 0; a.items = 0;
+    a.bs = bs; a.cs = cs; a.obs = obs; a.ocs = ocs; a.D = (int)p->D; a.L = (int)L; a.eps = p->eps; a.nv = 0; a.items = 0;
     a.skip_norm = p->skip_norm ? 1 : 0;
-    if (p->io_dtype == SS2D_F32) launch_norm<float>(a, pv, p->B, st);
-    else if (p->io_dtype == SS2D_BF16) launch_norm<__nv_bfloat16>(a, pv, p->B, st);
-    else launch_norm<__half>(a, pv, p->B, st);
+    if (p->io_dtype == SS2D_F32) launch_norm<float>(a, pv, B, st);
+    else if (p->io_dtype == SS2D_BF16) launch_norm<__nv_bfloat16>(a, pv, B, st);
+    else launch_norm<__half>(a, pv, B, st);
     count_launch();
     return check_launch();
 }
