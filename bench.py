@@ -267,6 +267,7 @@ def run_ours(args):
     import vmamba_b200  # noqa: F401  (fails loudly if the CUDA library is missing)
     from vmamba_b200 import _lib
     from vmamba_b200.backbone import VSSMInfer
+    from vmamba_b200.runner import GraphedBackbone
 
     global MODEL, BATCH, IMG
     if args.model:
@@ -297,20 +298,12 @@ def run_ours(args):
     dev_img = host_img.cuda(non_blocking=True)
     torch.cuda.synchronize()
 
-    # ---- capture one forward in a CUDA graph (static input / output buffers) -------------------
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        for _ in range(2):
-            model(dev_img)
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    l0 = _lib.launch_count()
-    with torch.cuda.graph(graph):
-        dev_out = model(dev_img)
-    launches_per_forward = _lib.launch_count() - l0
-    graph.replay()
+    # ---- one forward captured in a CUDA graph (static input / output buffers): the package's own runner ----
+    runner = GraphedBackbone(model, (BATCH, 3, IMG, IMG), dtype=torch.bfloat16)
+    runner.input.copy_(dev_img)
+    dev_out = runner.output
+    launches_per_forward = runner.launches_per_forward
+    runner.replay()
     torch.cuda.synchronize()
 
     def barrier():
@@ -337,36 +330,19 @@ def run_ours(args):
         return ms
 
     def step_device():
-        graph.replay()
+        runner.replay()
 
-    # End to end: every step copies its batch from pinned host memory and reads its logits back.  The copy
-    # runs on its own stream into one of two staging buffers, so the upload of step i+1 overlaps the
-    # forward of step i; the forward's input buffer is then filled device-to-device.
-    copy_stream = torch.cuda.Stream()
-    staging = [torch.empty_like(dev_img) for _ in range(2)]
-    h2d_done = [torch.cuda.Event() for _ in range(2)]
-    consumed = [torch.cuda.Event() for _ in range(2)]
-    e2e_it = [0]
-
+    # End to end through the public call: every step uploads its batch from pinned host memory (on a copy
+    # stream, into one of two staging buffers, so the upload of step i+1 overlaps the forward of step i),
+    # runs the forward and reads its logits back into pinned host memory.
     def step_e2e():
-        k = e2e_it[0] & 1
-        e2e_it[0] += 1
-        cur = torch.cuda.current_stream()
-        copy_stream.wait_event(consumed[k])              # staging[k] has been read by its previous step
-        with torch.cuda.stream(copy_stream):
-            staging[k].copy_(host_img, non_blocking=True)
-            h2d_done[k].record(copy_stream)
-        cur.wait_event(h2d_done[k])
-        dev_img.copy_(staging[k], non_blocking=True)
-        consumed[k].record(cur)
-        graph.replay()
-        host_out.copy_(dev_out, non_blocking=True)
+        runner.infer_host(host_img, host_out)
 
     def timed_e2e(steps, warmup):
         for _ in range(warmup):
             step_e2e()
         barrier()
-        copy_stream.wait_stream(torch.cuda.current_stream())   # no upload starts before the timed region does
+        runner.fence_uploads()                 # no upload starts before the timed region does
         return timed(step_e2e, steps, 0)
 
     warm = max(args.warmup, 3)

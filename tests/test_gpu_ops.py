@@ -565,3 +565,30 @@ def test_cross_scan_merge_layout_flags_and_one_by_one(vb):
             assert np.array_equal(host(out), g[f"{tag}_merge1b1_s{scans}"]), scans
     with pytest.raises(NotImplementedError):
         vb.cross_scan_fn(dev(g["5x7_ys"]).permute(0, 3, 4, 1, 2).contiguous(), False, False, True, 0)
+
+
+@pytest.mark.gpu
+def test_graphed_backbone_matches_eager(vb):
+    """GraphedBackbone: the replayed graph returns what the eager forward returns, for device input, for the
+    host-to-host call (twice, so that both staging buffers are used) and for the feature maps."""
+    from oracle import backbone_oracle as BO
+    from vmamba_b200.backbone import VSSMInfer
+    sd = BO.random_state_dict([1, 1, 2, 1], [64, 128, 256, 512], 1, 1.0, 4.0, 10, 3, seed=5, with_outnorm=True)
+    m = VSSMInfer.from_state_dict(sd, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(3)
+    imgs = [torch.randn((4, 3, 64, 64), generator=g).to(torch.bfloat16).pin_memory() for _ in range(3)]
+    runner = vb.GraphedBackbone(m, (4, 3, 64, 64))
+    assert runner.launches_per_forward > 30
+    for im in imgs:
+        want = m(im.cuda())
+        assert torch.equal(runner(im.cuda()), want)
+    host_out = torch.empty((4, want.shape[1]), dtype=torch.bfloat16).pin_memory()
+    for im in imgs:
+        got = runner.infer_host(im, host_out)
+        runner.done.synchronize()
+        assert torch.equal(got.cuda(), m(im.cuda()))
+    with pytest.raises(RuntimeError):
+        runner(torch.zeros((2, 3, 64, 64), device="cuda", dtype=torch.bfloat16))
+    fr = vb.GraphedBackbone(m, (4, 3, 64, 64), features=True)
+    for a, b in zip(fr(imgs[0].cuda()), m.features(imgs[0].cuda())):
+        assert torch.equal(a, b)

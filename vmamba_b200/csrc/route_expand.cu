@@ -32,6 +32,7 @@ struct ExpandArgs {
     const void* xt;                    // transposed rows of routes 1, 3: (2, C, Btot, Limg), or NULL (gather)
     long long xt_rs;                   // Btot * Limg
     int items_per_plane, items_total;  // L / VEC, B * L / VEC
+    int mma_tiles;                     // pixel tiles per CTA of the tensor-core kernel
 };
 
 constexpr int kExpThreads = 256;
@@ -163,7 +164,7 @@ template <> struct MmaK16<__half> {
     }
 };
 
-constexpr int kMmaTilesPerCta = 8;      // pixel tiles per CTA: the staged weights serve 512 pixels
+constexpr int kMmaTilesPerCta = 8;      // most pixel tiles per CTA: the staged weights then serve 512 pixels
 
 template <typename T, int KP>
 __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs a) {
@@ -176,9 +177,9 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
     const bool col = (k & 1) != 0;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tiles_per_run = (a.L + kMmaPix - 1) / kMmaPix;
-    const int groups_per_run = (tiles_per_run + kMmaTilesPerCta - 1) / kMmaTilesPerCta;
+    const int groups_per_run = (tiles_per_run + a.mma_tiles - 1) / a.mma_tiles;
     const int b = blockIdx.x / groups_per_run;
-    const int tile0 = (blockIdx.x - b * groups_per_run) * kMmaTilesPerCta;
+    const int tile0 = (blockIdx.x - b * groups_per_run) * a.mma_tiles;
     const T* __restrict__ xd = (const T*)a.xd + (long long)k * a.xd_ks + (long long)b * a.xd_bs;
     const int dc = blockIdx.z * kDChunk;
     const int dn = min(kDChunk, a.D - dc);
@@ -210,7 +211,7 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
     };
     const int g = lane >> 2, t4 = lane & 3;
     const int m0 = warp * 16;
-    for (int tt = 0; tt < kMmaTilesPerCta; ++tt) {
+    for (int tt = 0; tt < a.mma_tiles; ++tt) {
         const int q0 = (tile0 + tt) * kMmaPix;
         if (q0 >= a.L) break;                        // uniform over the CTA
         // ---- X tile, transposed to [pixel][k]; rows R .. KP-1 are zero.  Consecutive threads take consecutive
@@ -277,9 +278,14 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
 }
 
 template <typename T>
-static int launch_expand_mma(const ExpandArgs& a, cudaStream_t st) {
+static int launch_expand_mma(ExpandArgs a, cudaStream_t st) {
     const long long tiles_per_run = (a.L + kMmaPix - 1) / kMmaPix;
-    const long long tiles = (long long)a.B * ((tiles_per_run + kMmaTilesPerCta - 1) / kMmaTilesPerCta);
+    // Eight pixel tiles per CTA measured best for the 14 x 14 and 7 x 7 stages of a batch-128 forward (sums over
+    // ten launches: 1 tile 587 us, 2: 438, 4: 342, 8: 297, 16: 409, 32: 643): fewer tiles re-stage the weights
+    // too often, more leave too few CTAs.
+    const int per = kMmaTilesPerCta;
+    a.mma_tiles = per;
+    const long long tiles = (long long)a.B * ((tiles_per_run + per - 1) / per);
     if (tiles > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
     const dim3 grid((unsigned)tiles, 4, (unsigned)((a.D + kDChunk - 1) / kDChunk));
     const int kp = (a.R + 15) / 16 * 16;
