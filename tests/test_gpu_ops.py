@@ -245,7 +245,7 @@ def _run_core(vb, c, dtype, with_norm=True, unfused=False):
 
 
 CORE_SHAPES = [(2, 96, 56, 56), (2, 192, 28, 28), (2, 384, 14, 14), (3, 768, 7, 7), (1, 5, 9, 11), (2, 3, 6, 10),
-               (1, 2, 64, 64), (2, 7, 12, 20), (1, 4, 1, 16), (1, 3, 8, 1), (2, 10, 32, 24)]
+               (1, 2, 64, 64), (2, 7, 12, 20), (1, 4, 1, 16), (1, 3, 8, 1), (2, 10, 32, 24), (1, 6, 7, 14), (2, 5, 21, 7)]
 
 
 @pytest.mark.parametrize("shape", CORE_SHAPES)

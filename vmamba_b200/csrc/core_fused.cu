@@ -144,16 +144,39 @@ __device__ __forceinline__ AB route_local(const float2 (&ul)[(VEC + 1) / 2], con
     return AB{p, h};
 }
 
-// VEC consecutive fp32 values -> pairs (odd VEC = 1: the .y half is zero)
-template <typename T, int VEC>
-__device__ __forceinline__ void unpack_pairs(const typename Vec<T, VEC>::Raw& r, float2 (&v)[(VEC + 1) / 2]) {
-    float f[VEC];
-    Vec<T, VEC>::unpack(r, f);
-    if constexpr (VEC == 1) v[0] = make_float2(f[0], 0.f);
-    else {
+// Segment lengths that are not a power of two (7: one line of a 7 x 7 or half a line of a 14 x 14 map) cannot
+// be moved as one vector; they go element by element.  That is as many load instructions per element as the
+// one-element segments such maps would otherwise get, but every per-thread cost (index arithmetic, row
+// constants, the two CTA-wide scans) is then shared by seven elements instead of one.
+template <typename T, int VEC> struct VecScalar {
+    struct Raw { T e[VEC]; };
+    template <bool kReadOnly = true>
+    static __device__ __forceinline__ Raw load_raw(const T* p) {
+        Raw r;
 #pragma unroll
-        for (int j = 0; j < VEC / 2; ++j) v[j] = make_float2(f[2 * j], f[2 * j + 1]);
+        for (int i = 0; i < VEC; ++i) r.e[i] = kReadOnly ? __ldg(p + i) : p[i];
+        return r;
     }
+    static __device__ __forceinline__ void unpack(const Raw& r, float (&v)[VEC]) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] = to_f<T>(r.e[i]);
+    }
+    static __device__ __forceinline__ void store(T* p, const float (&v)[VEC]) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) p[i] = from_f<T>(v[i]);
+    }
+};
+template <typename T, int VEC> struct SegVec { using type = Vec<T, VEC>; };
+template <typename T> struct SegVec<T, 7> { using type = VecScalar<T, 7>; };
+
+// VEC consecutive values -> fp32 pairs (odd VEC: the .y half of the last pair is zero)
+template <typename T, int VEC>
+__device__ __forceinline__ void unpack_pairs(const typename SegVec<T, VEC>::type::Raw& r, float2 (&v)[(VEC + 1) / 2]) {
+    float f[VEC];
+    SegVec<T, VEC>::type::unpack(r, f);
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j) v[j] = make_float2(f[2 * j], f[2 * j + 1]);
+    if constexpr (VEC & 1) v[VEC / 2] = make_float2(f[VEC - 1], 0.f);
 }
 template <int VEC>
 __device__ __forceinline__ void load_pairs(const float* p, float2 (&v)[(VEC + 1) / 2]) {
@@ -203,7 +226,7 @@ __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a
     // one padded fp32 plane per channel: first x (for the transposed read), then, once every
     // column-orientation thread has taken its x values, the column-orientation result
     float* plane = smem + (size_t)pl * (H * Wp);
-    using VT = Vec<T, VEC>;
+    using VT = typename SegVec<T, VEC>::type;
     const int e0 = v * VEC;   // first element of this thread in either orientation order
     const long long plane_off = (long long)d * L + e0;
     const bool first = v == 0, last = v == a.G - 1;
@@ -261,7 +284,7 @@ __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a
 #pragma unroll
         for (int j = 0; j < NP; ++j) {
             ul[j].x = plane[cs.at(2 * j, Wp)];
-            ul[j].y = (VEC > 1) ? plane[cs.at(2 * j + 1, Wp)] : 0.f;
+            ul[j].y = (2 * j + 1 < VEC) ? plane[cs.at(2 * j + 1, Wp)] : 0.f;
         }
         const float2 Dsum = splat(__ldg(a.Dskip + D + d) + __ldg(a.Dskip + 3 * D + d));
 #pragma unroll
@@ -298,7 +321,7 @@ __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a
         float out[VEC];
 #pragma unroll
         for (int i = 0; i < VEC; ++i) out[i] = ((i & 1) ? yrow[i >> 1].y : yrow[i >> 1].x) + plane[rs.at(i, 1)];
-        Vec<float, VEC>::store(a.merged + (long long)b * D * L + plane_off, out);
+        SegVec<float, VEC>::type::store(a.merged + (long long)b * D * L + plane_off, out);
     }
 }
 
@@ -318,6 +341,11 @@ static bool plan_planes(const ss2d_core_params* p, PlaneConfig& c) {
     }
     // a thread's segment may wrap to the next line only at its middle: vec/2 divides H and W
     while (vec > 1 && (vec > p->H || vec > p->W || (p->H % (vec / 2)) != 0 || (p->W % (vec / 2)) != 0)) vec >>= 1;
+    // odd maps whose sides are multiples of 7 (7 x 7) would get one-element segments: seven-element segments,
+    // moved element by element, share the per-thread work of the pass between seven elements instead
+    // (234 -> 113 us for the two 7 x 7 launches of a batch-128 VMamba-T forward; for 14 x 14 maps, which get
+    // four-element vectors, the same change is 20 % slower)
+    if (vec == 1 && p->H % 7 == 0 && p->W % 7 == 0) vec = 7;
     // 16-byte loads are enough: an 8-wide fp32 vector is two of them
     // (alignment of the fp32 workspace is checked by the caller)
     const long long G = L / vec;
@@ -356,6 +384,7 @@ template <typename T>
 static int launch_core_v(const CoreArgs& a, const PlaneConfig& c, unsigned grid, cudaStream_t st) {
     switch (c.vec) {
         case 8: return launch_core_t<T, 8>(a, c, grid, st);
+        case 7: return launch_core_t<T, 7>(a, c, grid, st);
         case 4: return launch_core_t<T, 4>(a, c, grid, st);
         case 2: return launch_core_t<T, 2>(a, c, grid, st);
         default: return launch_core_t<T, 1>(a, c, grid, st);

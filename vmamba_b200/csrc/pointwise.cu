@@ -109,205 +109,133 @@ int bias_act(const ss2d_pointwise_params* p, cudaStream_t st) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// Depthwise 3x3, stride 1, zero padding 1.  A work unit is a band of BH rows of one plane (the whole
-// plane when it is small); a CTA owns PP units.  Each band is staged once in shared memory as fp32
-// with its two halo rows inside a one-pixel zero frame (pitch W + 2); consecutive threads then take
-// consecutive columns and walk 8 rows with the 3x3 window sliding in registers.  HBM traffic is the
-// minimum for whole planes (every element read once, written once); banded planes re-read two
-// halo rows per band.
-struct DwArgs {
-    const void* x;
-    const void* w;       // (D, 3, 3) storage type
-    const float* bias;   // (D) or null
-    void* y;
-    int D, H, W, PP, nvw;           // nvw = W / PV runs per row
-    int BH, nb, units;              // rows per band, bands per plane, planes * nb
-    int planes_per_channel;         // 1 for (B, D, H, W) maps, B for (D, B, H, W) maps
-    int nrb;                        // row blocks of 8 per band
-    int krows;                      // rows per thread in the compute phase (7 or 8: whichever divides the band better)
-    int flat;                       // bit 0: flat loads, bit 1: flat stores;  whole planes, consecutive in memory and 16-byte aligned per CTA: flat vector loads / stores
-    unsigned magic_L;
-    unsigned magic_fr, magic_nvw, magic_W, magic_nrb, magic_ppc, magic_nb, magic_frnvw, magic_nrbW, magic_W2, magic_nrbW2;
-};
-
+// Depthwise 3x3, stride 1, zero padding 1, no shared memory: a thread owns PV neighbouring columns of KR
+// consecutive rows.  It reads the KR + 2 input rows of its strip as one vector each (all issued before the
+// first result is needed), takes the column to the left and to the right of the strip from the neighbouring
+// lanes by shuffle (zero at the image border, a scalar load where the neighbour sits in another warp) and
+// slides the 3x3 window down in registers.  Lanes run along a row, then over the row blocks, then over the
+// planes, so a warp's loads and stores are contiguous runs.  (An earlier form staged whole planes in shared
+// memory as fp32 frames; it issued two to three times the instructions per output and was 25 % slower over a
+// backbone forward.)
 __device__ __forceinline__ int mdiv(int n, unsigned magic) { return magic ? (int)__umulhi((unsigned)n, magic) : n; }   // magic 0: divisor 1
 
-template <typename T, int PV, int ACT>
-__global__ void __launch_bounds__(256) dwconv3x3_act_kernel(const DwArgs a) {
-    extern __shared__ __align__(16) float sm[];
-    const int H = a.H, W = a.W, Wp = W + 2, FR = a.BH + 2;      // frame rows
-    const int unit0 = blockIdx.x * a.PP;
-    const int np = min(a.PP, a.units - unit0);
-    const int frame = FR * Wp;
-    // frame cells that no load will write: the left and right columns, and the rows above / below the image
-    for (int i = threadIdx.x; i < np * FR; i += blockDim.x) {
-        const int pl = mdiv(i, a.magic_fr), fr = i - pl * FR;
-        float* row = sm + pl * frame + fr * Wp;
-        row[0] = 0.f; row[W + 1] = 0.f;
-    }
-    const T* __restrict__ x = (const T*)a.x;
-    T* obuf = reinterpret_cast<T*>(sm + ((a.PP * frame + 3) & ~3));   // flat mode: the CTA's outputs, np * H * W
-    if (a.flat & 1) {
-        // whole planes, consecutive in memory: the CTA's input is one run of np * H * W elements, read as
-        // 16-byte vectors whatever the row length, and scattered into the frames
-        for (int i = threadIdx.x; i < np * 2 * Wp; i += blockDim.x) {       // rows above and below the image
-            const int pl = i / (2 * Wp), rem = i - pl * (2 * Wp);
-            sm[pl * frame + (rem < Wp ? rem : (H + 1) * Wp + rem - Wp)] = 0.f;
-        }
-        constexpr int FV = 16 / (int)sizeof(T);
-        const int total = np * H * W;
-        const T* src = x + (long long)unit0 * H * W;
-        for (int e0 = threadIdx.x * FV; e0 < total; e0 += blockDim.x * FV) {
-            int pl = mdiv(e0, a.magic_L), rem = e0 - pl * (H * W);
-            int h = mdiv(rem, a.magic_W), w = rem - h * W;
-            T v[FV];
-            if (e0 + FV <= total) *reinterpret_cast<uint4*>(v) = __ldg(reinterpret_cast<const uint4*>(src + e0));
-            else {
-#pragma unroll
-                for (int j = 0; j < FV; ++j) v[j] = (e0 + j < total) ? src[e0 + j] : from_f<T>(0.f);
-            }
-#pragma unroll
-            for (int j = 0; j < FV; ++j) {
-                if (e0 + j < total) sm[pl * frame + (h + 1) * Wp + w + 1] = to_f<T>(v[j]);
-                if (++w == W) { w = 0; if (++h == H) { h = 0; ++pl; } }
-            }
-        }
-    } else
-    for (int i = threadIdx.x; i < np * FR * a.nvw; i += blockDim.x) {
-        const int pl = mdiv(i, a.magic_frnvw), rem = i - pl * (FR * a.nvw);
-        const int fr = mdiv(rem, a.magic_nvw), v = rem - fr * a.nvw;
-        const int u = unit0 + pl;
-        const int plane = mdiv(u, a.magic_nb), band = u - plane * a.nb;
-        const int h = band * a.BH - 1 + fr;                       // image row held by this frame row
-        float val[PV];
-        if (h >= 0 && h < H) Vec<T, PV>::load(x + ((long long)plane * H + h) * W + v * PV, val);   // PV divides W
-        else {
-#pragma unroll
-            for (int j = 0; j < PV; ++j) val[j] = 0.f;
-        }
-        float* dst = sm + pl * frame + fr * Wp + v * PV + 1;
-#pragma unroll
-        for (int j = 0; j < PV; ++j) dst[j] = val[j];
-    }
-    __syncthreads();
-    const int kRows = a.krows;
-    const int nrb = a.nrb;
-    if ((W & 1) == 0) {
-        // two neighbouring columns per thread: four frame values per row (two 8-byte loads) serve eighteen
-        // FMAs, and the two results leave as one store
-        const int W2 = W >> 1;
-        for (int i = threadIdx.x; i < np * nrb * W2; i += blockDim.x) {
-            const int pl = mdiv(i, a.magic_nrbW2), rem = i - pl * (nrb * W2);
-            const int rb = mdiv(rem, a.magic_W2), w = (rem - rb * W2) * 2;
-            const int u = unit0 + pl;
-            const int plane = mdiv(u, a.magic_nb), band = u - plane * a.nb;
-            const int r0 = rb * kRows;
-            const int rows = min(min(r0 + kRows, a.BH), H - band * a.BH) - r0;
-            if (rows <= 0) continue;
-            const int d = mdiv(plane, a.magic_ppc) % a.D;
-            const T* __restrict__ wk = (const T*)a.w + d * 9;
-            float k[9];
-#pragma unroll
-            for (int j = 0; j < 9; ++j) k[j] = to_f<T>(wk[j]);
-            const float b = a.bias ? __ldg(a.bias + d) : 0.f;
-            const float* src = sm + pl * frame + r0 * Wp + w;
-            float2 ta = *reinterpret_cast<const float2*>(src), tb = *reinterpret_cast<const float2*>(src + 2);
-            float2 ma = *reinterpret_cast<const float2*>(src + Wp), mb = *reinterpret_cast<const float2*>(src + Wp + 2);
-            T* __restrict__ out = (T*)a.y + ((long long)plane * H + band * a.BH + r0) * W + w;
-            for (int r = 0; r < rows; ++r) {
-                const float* bp = src + (r + 2) * Wp;
-                const float2 ba = *reinterpret_cast<const float2*>(bp), bb = *reinterpret_cast<const float2*>(bp + 2);
-                float a0 = b, a1 = b;
-                a0 = fmaf(k[0], ta.x, a0); a0 = fmaf(k[1], ta.y, a0); a0 = fmaf(k[2], tb.x, a0);
-                a1 = fmaf(k[0], ta.y, a1); a1 = fmaf(k[1], tb.x, a1); a1 = fmaf(k[2], tb.y, a1);
-                a0 = fmaf(k[3], ma.x, a0); a0 = fmaf(k[4], ma.y, a0); a0 = fmaf(k[5], mb.x, a0);
-                a1 = fmaf(k[3], ma.y, a1); a1 = fmaf(k[4], mb.x, a1); a1 = fmaf(k[5], mb.y, a1);
-                a0 = fmaf(k[6], ba.x, a0); a0 = fmaf(k[7], ba.y, a0); a0 = fmaf(k[8], bb.x, a0);
-                a1 = fmaf(k[6], ba.y, a1); a1 = fmaf(k[7], bb.x, a1); a1 = fmaf(k[8], bb.y, a1);
-                const float o[2] = {act_f<ACT>(round_to<T>(a0)), act_f<ACT>(round_to<T>(a1))};
-                if (a.flat & 2) Vec<T, 2>::store(obuf + (pl * H + r0 + r) * W + w, o);
-                else Vec<T, 2>::store(out + r * W, o);
-                ta = ma; tb = mb; ma = ba; mb = bb;
-            }
-        }
-    } else
-    for (int i = threadIdx.x; i < np * nrb * W; i += blockDim.x) {
-        const int pl = mdiv(i, a.magic_nrbW), rem = i - pl * (nrb * W);
-        const int rb = mdiv(rem, a.magic_W), w = rem - rb * W;
-        const int u = unit0 + pl;
-        const int plane = mdiv(u, a.magic_nb), band = u - plane * a.nb;
-        const int r0 = rb * kRows;                                 // first row of this block inside the band
-        const int rows = min(min(r0 + kRows, a.BH), H - band * a.BH) - r0;
-        if (rows <= 0) continue;
-        const int d = mdiv(plane, a.magic_ppc) % a.D;
+struct DwStripArgs {
+    const void* x;
+    const void* w;
+    const float* bias;
+    void* y;
+    int D, H, W, nseg, nrb, total;  // nseg = W / PV strips per row, nrb = row blocks per plane, total threads with work
+    unsigned magic_nseg, magic_nrb, magic_ppc;
+};
+
+template <typename T, int PV, int KR, int ACT>
+__global__ void __launch_bounds__(256, PV == 8 ? 2 : 3) dwconv3x3_strip_kernel(const DwStripArgs a) {
+    const int H = a.H, W = a.W;
+    const int lane = threadIdx.x & 31;
+    const long long gi = (long long)blockIdx.x * 256 + threadIdx.x;
+    const bool valid = gi < a.total;
+    const int i = valid ? (int)gi : a.total - 1;      // spare threads shadow the last strip (they join the shuffles, store nothing)
+    const int t = mdiv(i, a.magic_nseg), seg = i - t * a.nseg;
+    const int plane = mdiv(t, a.magic_nrb), rb = t - plane * a.nrb;
+    const int d = mdiv(plane, a.magic_ppc) % a.D;
+    float k[9];
+    {
         const T* __restrict__ wk = (const T*)a.w + d * 9;
-        float k[9];
 #pragma unroll
         for (int j = 0; j < 9; ++j) k[j] = to_f<T>(wk[j]);
-        const float b = a.bias ? __ldg(a.bias + d) : 0.f;
-        const float* src = sm + pl * frame + r0 * Wp + w;        // frame row r0 is the row above output row r0
-        float t0 = src[0], t1 = src[1], t2 = src[2];
-        float m0 = src[Wp], m1 = src[Wp + 1], m2 = src[Wp + 2];
-        T* __restrict__ out = (T*)a.y + ((long long)plane * H + band * a.BH + r0) * W + w;
-        for (int r = 0; r < rows; ++r) {
-            const float* bp = src + (r + 2) * Wp;
-            const float b0 = bp[0], b1 = bp[1], b2 = bp[2];
-            float acc = b;
-            acc = fmaf(k[0], t0, acc); acc = fmaf(k[1], t1, acc); acc = fmaf(k[2], t2, acc);
-            acc = fmaf(k[3], m0, acc); acc = fmaf(k[4], m1, acc); acc = fmaf(k[5], m2, acc);
-            acc = fmaf(k[6], b0, acc); acc = fmaf(k[7], b1, acc); acc = fmaf(k[8], b2, acc);
-            if (a.flat & 2) obuf[(pl * H + r0 + r) * W + w] = from_f<T>(act_f<ACT>(round_to<T>(acc)));
-            else out[r * W] = from_f<T>(act_f<ACT>(round_to<T>(acc)));
-            t0 = m0; t1 = m1; t2 = m2; m0 = b0; m1 = b1; m2 = b2;
-        }
     }
-    if (a.flat & 2) {         // the CTA's outputs leave as one run of 16-byte vectors
-        __syncthreads();
-        constexpr int FV = 16 / (int)sizeof(T);
-        const int total = np * H * W;
-        T* dst = (T*)a.y + (long long)unit0 * H * W;
-        for (int e0 = threadIdx.x * FV; e0 < total; e0 += blockDim.x * FV) {
-            if (e0 + FV <= total) *reinterpret_cast<uint4*>(dst + e0) = *reinterpret_cast<const uint4*>(obuf + e0);
-            else for (int j = 0; e0 + j < total; ++j) dst[e0 + j] = obuf[e0 + j];
+    const float b = a.bias ? __ldg(a.bias + d) : 0.f;
+    const long long origin = (long long)plane * H * W + seg * PV;
+    const T* __restrict__ px = (const T*)a.x + origin;
+    T* __restrict__ py = (T*)a.y + origin;
+    const bool at_left = seg == 0, at_right = seg == a.nseg - 1;
+    const int r0 = rb * KR;
+
+    // the KR + 2 input rows of the strip, kept packed until they are needed (rows outside the image are zero)
+    using VT = Vec<T, PV>;
+    typename VT::Raw raw[KR + 2];
+    float edge_l[KR + 2], edge_r[KR + 2];      // columns next to the strip where the neighbour is in another warp
+#pragma unroll
+    for (int j = 0; j < KR + 2; ++j) {
+        const int h = r0 - 1 + j;
+        const bool in = h >= 0 && h < H;
+        const T* row = px + (long long)h * W;
+        if (in) raw[j] = VT::load_raw(row);
+        else {
+#pragma unroll
+            for (int q = 0; q < VT::kWords; ++q) raw[j].w[q] = 0u;
+        }
+        edge_l[j] = (in && lane == 0 && !at_left) ? to_f<T>(__ldg(row - 1)) : 0.f;
+        edge_r[j] = (in && lane == 31 && !at_right) ? to_f<T>(__ldg(row + PV)) : 0.f;
+    }
+    // window row: [left neighbour, PV own columns, right neighbour]
+    auto open_row = [&](int j, float (&wv)[PV + 2]) {
+        float v[PV];
+        VT::unpack(raw[j], v);
+        float l = __shfl_up_sync(0xffffffffu, v[PV - 1], 1), r = __shfl_down_sync(0xffffffffu, v[0], 1);
+        if (at_left) l = 0.f;
+        else if (lane == 0) l = edge_l[j];
+        if (at_right) r = 0.f;
+        else if (lane == 31) r = edge_r[j];
+        wv[0] = l; wv[PV + 1] = r;
+#pragma unroll
+        for (int q = 0; q < PV; ++q) wv[q + 1] = v[q];
+    };
+
+    float win[3][PV + 2];
+    open_row(0, win[0]);
+    open_row(1, win[1]);
+#pragma unroll
+    for (int j = 0; j < KR; ++j) {
+        open_row(j + 2, win[(j + 2) % 3]);
+        if (r0 + j < H && valid) {
+            float o[PV];
+#pragma unroll
+            for (int c = 0; c < PV; ++c) {
+                float acc = b;
+#pragma unroll
+                for (int dy = 0; dy < 3; ++dy)
+#pragma unroll
+                    for (int dx = 0; dx < 3; ++dx) acc = fmaf(k[dy * 3 + dx], win[(j + dy) % 3][c + dx], acc);
+                o[c] = acc;
+            }
+            if constexpr (sizeof(T) == 2 && PV >= 2) {
+                // conv result rounded to the storage type (as the library convolution returns it), then the activation
+#pragma unroll
+                for (int c = 0; c < PV; c += 2) {
+                    const float2 q = Half2Of<T>::unpack(Half2Of<T>::pack(o[c], o[c + 1]));
+                    o[c] = act_f<ACT>(q.x); o[c + 1] = act_f<ACT>(q.y);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < PV; ++c) o[c] = act_f<ACT>(round_to<T>(o[c]));
+            }
+            VT::store(py + (long long)(r0 + j) * W, o);
         }
     }
 }
 
-template <typename T, int PV>
-static int launch_dw(const DwArgs& a, int act, size_t smem, unsigned grid, cudaStream_t st) {
-    if (act == ACT_SILU) {
-        auto k = dwconv3x3_act_kernel<T, PV, ACT_SILU>;
-        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return SS2D_ECUDA;
-        k<<<grid, 256, smem, st>>>(a);
-    } else if (act == ACT_GELU) {
-        auto k = dwconv3x3_act_kernel<T, PV, ACT_GELU>;
-        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return SS2D_ECUDA;
-        k<<<grid, 256, smem, st>>>(a);
-    } else {
-        auto k = dwconv3x3_act_kernel<T, PV, ACT_NONE>;
-        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return SS2D_ECUDA;
-        k<<<grid, 256, smem, st>>>(a);
-    }
+template <typename T, int PV, int KR>
+static int launch_dw_strip_a(const DwStripArgs& a, int act, unsigned grid, cudaStream_t st) {
+    if (act == ACT_SILU) dwconv3x3_strip_kernel<T, PV, KR, ACT_SILU><<<grid, 256, 0, st>>>(a);
+    else if (act == ACT_GELU) dwconv3x3_strip_kernel<T, PV, KR, ACT_GELU><<<grid, 256, 0, st>>>(a);
+    else dwconv3x3_strip_kernel<T, PV, KR, ACT_NONE><<<grid, 256, 0, st>>>(a);
     count_launch();
     return check_launch();
 }
 
 template <typename T>
-static int launch_dw_v(DwArgs a, int pv, int act, size_t smem, unsigned grid, cudaStream_t st) {
-    a.nvw = a.W / pv;
-    a.krows = (a.BH % 8 == 0 || a.BH % 7 != 0) ? 8 : 7;
-    a.nrb = (a.BH + a.krows - 1) / a.krows;
-    auto magic = [](long long d) { return d > 1 ? (unsigned)(((1ULL << 32) + (unsigned long long)d - 1) / (unsigned long long)d) : 0u; };
-    const int FR = a.BH + 2;
-    a.magic_fr = magic(FR); a.magic_nvw = magic(a.nvw); a.magic_W = magic(a.W); a.magic_nrb = magic(a.nrb);
-    a.magic_ppc = magic(a.planes_per_channel); a.magic_nb = magic(a.nb);
-    a.magic_frnvw = magic((long long)FR * a.nvw); a.magic_nrbW = magic((long long)a.nrb * a.W);
-    a.magic_W2 = magic(a.W / 2); a.magic_nrbW2 = magic((long long)a.nrb * (a.W / 2));
-    a.magic_L = magic((long long)a.H * a.W);
-    if (pv == 8) return launch_dw<T, 8>(a, act, smem, grid, st);
-    if (pv == 4) return launch_dw<T, 4>(a, act, smem, grid, st);
-    if (pv == 2) return launch_dw<T, 2>(a, act, smem, grid, st);
-    return launch_dw<T, 1>(a, act, smem, grid, st);
+static int launch_dw_strip(DwStripArgs a, int pv, int kr, int act, unsigned grid, cudaStream_t st) {
+    if (kr == 8) {
+        if (pv == 8) return launch_dw_strip_a<T, 8, 8>(a, act, grid, st);
+        if (pv == 4) return launch_dw_strip_a<T, 4, 8>(a, act, grid, st);
+        if (pv == 2) return launch_dw_strip_a<T, 2, 8>(a, act, grid, st);
+        return launch_dw_strip_a<T, 1, 8>(a, act, grid, st);
+    }
+    if (pv == 8) return launch_dw_strip_a<T, 8, 7>(a, act, grid, st);
+    if (pv == 4) return launch_dw_strip_a<T, 4, 7>(a, act, grid, st);
+    if (pv == 2) return launch_dw_strip_a<T, 2, 7>(a, act, grid, st);
+    return launch_dw_strip_a<T, 1, 7>(a, act, grid, st);
 }
 
 int dwconv3x3_act(const ss2d_pointwise_params* p, cudaStream_t st) {
@@ -326,44 +254,21 @@ int dwconv3x3_act(const ss2d_pointwise_params* p, cudaStream_t st) {
     fit(p->W); fit(L);
     fit((long long)(reinterpret_cast<uintptr_t>(p->x) / s));
     fit((long long)(reinterpret_cast<uintptr_t>(p->y) / s));
-    // band height: the whole plane if its frame fits in 40 KB, else as many rows as do
-    const long long Wp = p->W + 2;
-    long long BH = p->H;
-    while (BH > 8 && (BH + 2) * Wp * 4 > 40 * 1024) BH = (BH + 1) / 2;
-    BH = (BH + 7) / 8 * 8;                      // whole 8-row blocks
-    if (BH > p->H) BH = p->H;
-    const long long nb = (p->H + BH - 1) / BH;
-    const size_t frame = (size_t)(BH + 2) * Wp * sizeof(float);
-    if (frame > 160 * 1024) return SS2D_ENOTSUP;
-    const long long units = p->B * p->D * nb;
-    long long PP = (2048 * 4 + BH * p->W - 1) / (BH * p->W);      // about 8192 outputs per CTA
-    if (PP < 1) PP = 1;
-    while (PP > 1 && PP * frame > 48 * 1024) --PP;
-    if (PP > units) PP = units;
-    // flat mode: rows too short for 16-byte vectors, whole-plane bands, planes dense in memory; PP planes must
-    // keep every CTA's run 16-byte aligned
-    const long long fv = 16 / (long long)s;
-    bool flat = nb == 1 && pv == 1 && fv > 1 && aligned_to(p->x, 16) && aligned_to(p->y, 16);   // measured: pays only for odd row lengths
-    if (flat) {
-        long long step = fv;
-        for (long long gcd_a = L, gcd_b = fv; gcd_b; ) { const long long t = gcd_a % gcd_b; gcd_a = gcd_b; gcd_b = t; if (!gcd_b) step = fv / gcd_a; }
-        long long PPf = PP / step * step;
-        if (PPf < step) PPf = step;
-        if (PPf * (frame + L * s) + 32 > 64 * 1024) flat = false; else PP = PPf;
-    }
-    const long long grid = (units + PP - 1) / PP;
+    const int kr = (p->H % 8 == 0 || p->H % 7 != 0) ? 8 : 7;      // rows per thread: whichever divides the map better
+    const long long nseg = p->W / pv, nrb = (p->H + kr - 1) / kr, planes = p->B * p->D;
+    const long long total = planes * nrb * nseg;
     // every index split inside the kernel is a multiply-shift that needs numerator * divisor < 2^32
-    if (units * nb >= (1LL << 32) || p->B * p->D * p->B >= (1LL << 32) || grid > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
-    DwArgs a;
+    if (total >= (1LL << 31) || total * nseg >= (1LL << 32) || planes * nrb * nrb >= (1LL << 32) || planes * p->B >= (1LL << 32))
+        return SS2D_EINVAL_SHAPE;
+    auto magic = [](long long d) { return d > 1 ? (unsigned)(((1ULL << 32) + (unsigned long long)d - 1) / (unsigned long long)d) : 0u; };
+    DwStripArgs a;
     a.x = p->x; a.w = p->weight; a.bias = (const float*)p->bias; a.y = p->y;
-    a.D = (int)p->D; a.H = (int)p->H; a.W = (int)p->W; a.PP = (int)PP; a.nvw = 0;
-    a.BH = (int)BH; a.nb = (int)nb; a.units = (int)units;
-    a.planes_per_channel = p->channel_major ? (int)p->B : 1;
-    a.flat = flat ? 3 : 0;
-    const size_t smem = flat ? ((size_t)PP * frame + 15) / 16 * 16 + ((size_t)PP * L * s + 15) / 16 * 16 : (size_t)PP * frame;
-    if (p->dtype == SS2D_F32) return launch_dw_v<float>(a, pv, p->act, smem, (unsigned)grid, st);
-    if (p->dtype == SS2D_BF16) return launch_dw_v<__nv_bfloat16>(a, pv, p->act, smem, (unsigned)grid, st);
-    return launch_dw_v<__half>(a, pv, p->act, smem, (unsigned)grid, st);
+    a.D = (int)p->D; a.H = (int)p->H; a.W = (int)p->W; a.nseg = (int)nseg; a.nrb = (int)nrb; a.total = (int)total;
+    a.magic_nseg = magic(nseg); a.magic_nrb = magic(nrb); a.magic_ppc = magic(p->channel_major ? p->B : 1);
+    const unsigned grid = (unsigned)((total + 255) / 256);
+    if (p->dtype == SS2D_F32) return launch_dw_strip<float>(a, pv, kr, p->act, grid, st);
+    if (p->dtype == SS2D_BF16) return launch_dw_strip<__nv_bfloat16>(a, pv, kr, p->act, grid, st);
+    return launch_dw_strip<__half>(a, pv, kr, p->act, grid, st);
 }
 
 }  // namespace ss2d
