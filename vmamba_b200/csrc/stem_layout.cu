@@ -182,6 +182,7 @@ struct RowsArgs {
     long long N, out_cs;
     int C;
     float eps;
+    unsigned magic_pieces;     // ceil(2^32 / (C / PV)), 0 for one piece per pixel
 };
 
 template <typename Tin, typename Tout, int TP>
@@ -196,7 +197,7 @@ __global__ void __launch_bounds__(256) pixels_norm_to_planes_kernel(const RowsAr
     const int live = (int)min((long long)TP, a.N - n0);
     // A: rows (+ bias) -> tile
     for (int idx = threadIdx.x; idx < live * pieces; idx += 256) {
-        const int pp = idx / pieces, c = (idx - pp * pieces) * PV;
+        const int pp = a.magic_pieces ? (int)__umulhi((unsigned)idx, a.magic_pieces) : idx, c = (idx - pp * pieces) * PV;
         float v[PV], bv[PV];
         Vec<Tin, PV>::load((const Tin*)a.in + (n0 + pp) * C + c, v);
         if (a.bias) Vec<float, PV>::load(a.bias + c, bv);
@@ -209,6 +210,7 @@ __global__ void __launch_bounds__(256) pixels_norm_to_planes_kernel(const RowsAr
     constexpr int NS = 256 / TP;
     const int pl = threadIdx.x % TP, sl = threadIdx.x / TP;
     float s = 0.f;
+#pragma unroll 4
     for (int c = sl; c < C; c += NS) s += tile[pl * P + c];
     part[sl * TP + pl] = s;
     __syncthreads();
@@ -217,6 +219,7 @@ __global__ void __launch_bounds__(256) pixels_norm_to_planes_kernel(const RowsAr
     for (int k = 0; k < NS; ++k) mean += part[k * TP + pl];
     mean /= C;
     float q = 0.f;
+#pragma unroll 4
     for (int c = sl; c < C; c += NS) { const float d = tile[pl * P + c] - mean; q = fmaf(d, d, q); }
     __syncthreads();                                      // every partial sum has been read
     part[sl * TP + pl] = q;
@@ -237,6 +240,7 @@ __global__ void __launch_bounds__(256) pixels_norm_to_planes_kernel(const RowsAr
 #pragma unroll
         for (int i = 0; i < 4; ++i) { sc[i] = stat[p4 + i]; sh[i] = stat[TP + p4 + i]; }
         const bool full = p4 + 4 <= live && ((a.out_cs | n0) & 3) == 0;
+#pragma unroll 2
         for (int c = cw; c < C; c += 256 / Q4) {
             const float w = a.lnw ? __ldg(a.lnw + c) : 1.f, bb = a.lnb ? __ldg(a.lnb + c) : 0.f;
             float o[4];
@@ -269,6 +273,7 @@ int pixels_norm_to_planes(const ss2d_relayout_params* p, cudaStream_t st) {
     RowsArgs a;
     a.in = p->rows; a.bias = (const float*)p->bias; a.lnw = (const float*)p->ln_weight; a.lnb = (const float*)p->ln_bias;
     a.out = p->planes; a.N = p->N; a.out_cs = cs; a.C = (int)p->C; a.eps = p->eps;
+    a.magic_pieces = (p->C / pv) > 1 ? (unsigned)(((1ULL << 32) + (unsigned long long)(p->C / pv) - 1) / (unsigned long long)(p->C / pv)) : 0u;
     const int tp = p->C <= 512 ? 32 : 16;
     const size_t smem = ((size_t)tp * (p->C + 1) + 256 + 2 * tp) * sizeof(float);
     if (smem > 200 * 1024) return SS2D_ENOTSUP;
@@ -301,6 +306,8 @@ struct PlanesArgs {
     void* rows;            // (N, C)
     long long N, cs;
     int C, write_back;
+    int quads;                 // 1: N, cs and the base addresses allow four pixels per load
+    unsigned magic_pieces;     // ceil(2^32 / (C / PV)), 0 for one piece per pixel
 };
 
 template <typename T, int TP>
@@ -308,6 +315,45 @@ __global__ void __launch_bounds__(256) planes_to_pixels_kernel(const PlanesArgs 
     extern __shared__ float tile[];                       // [TP][C + 1]
     const long long n0 = (long long)blockIdx.x * TP;
     const int C = a.C, P = C + 1;
+    if (a.quads) {
+        // thread = four consecutive pixels of one channel: one 16-byte load of the planes, one 8-byte (16-bit) load
+        // of `add`; a warp covers 32 pixels of four channels.  Two channels' loads are issued before the first store.
+        constexpr int Q = TP / 4, CW4 = 256 / Q;
+        const int p4 = (threadIdx.x % Q) * 4, cw = threadIdx.x / Q;
+        if (n0 + p4 < a.N) {
+            for (int c0 = cw; c0 < C; c0 += 2 * CW4) {
+                float v[2][4];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int c = c0 + CW4 * j;
+                    if (c < C) {
+                        const long long off = (long long)c * a.cs + n0 + p4;
+                        Vec<float, 4>::load_plain(a.planes + off, v[j]);
+                        if (a.add) {
+                            float t[4];
+                            Vec<T, 4>::load((const T*)a.add + off, t);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) v[j][i] += t[i];
+                        }
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int c = c0 + CW4 * j;
+                    if (c < C) {
+                        if (a.bias) {
+                            const float bb = __ldg(a.bias + c);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) v[j][i] += bb;
+                        }
+                        if (a.write_back) Vec<float, 4>::store(a.planes + (long long)c * a.cs + n0 + p4, v[j]);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) tile[(p4 + i) * P + c] = v[j][i];
+                    }
+                }
+            }
+        }
+    } else {
     const int pl = threadIdx.x % TP, cw = threadIdx.x / TP;
     constexpr int CW = 256 / TP;
     const long long n = n0 + pl;
@@ -335,12 +381,13 @@ __global__ void __launch_bounds__(256) planes_to_pixels_kernel(const PlanesArgs 
             }
         }
     }
+    }
     __syncthreads();
     constexpr int PV = sizeof(T) == 2 ? 8 : 4;
     const int pieces = C / PV;
     const int live = (int)min((long long)TP, a.N - n0);
     for (int idx = threadIdx.x; idx < live * pieces; idx += 256) {
-        const int pp = idx / pieces, c = (idx - pp * pieces) * PV;
+        const int pp = a.magic_pieces ? (int)__umulhi((unsigned)idx, a.magic_pieces) : idx, c = (idx - pp * pieces) * PV;
         float v[PV];
 #pragma unroll
         for (int i = 0; i < PV; ++i) v[i] = tile[pp * P + c + i];
@@ -363,6 +410,8 @@ int planes_to_pixels(const ss2d_relayout_params* p, cudaStream_t st) {
     PlanesArgs a;
     a.planes = (float*)p->planes; a.add = p->add; a.bias = (const float*)p->bias; a.rows = p->rows;
     a.N = p->N; a.cs = cs; a.C = (int)p->C; a.write_back = p->sum_out != nullptr;
+    a.quads = (p->N % 4 == 0 && cs % 4 == 0 && aligned_to(p->planes, 16) && aligned_to(p->add, 4 * sr)) ? 1 : 0;
+    a.magic_pieces = (p->C / pv) > 1 ? (unsigned)(((1ULL << 32) + (unsigned long long)(p->C / pv) - 1) / (unsigned long long)(p->C / pv)) : 0u;
     if (p->sum_out && p->sum_out != p->planes) return SS2D_ENOTSUP;      // the update is in place
     const int tp = p->C <= 512 ? 32 : 16;
     const size_t smem = (size_t)tp * (p->C + 1) * sizeof(float);
