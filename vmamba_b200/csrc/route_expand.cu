@@ -187,9 +187,18 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
 
     // ---- weights of this channel slice, [channel][k], zero beyond R and beyond the slice ----------------
     const T* __restrict__ wk = (const T*)a.wdt + (long long)k * a.D * a.R;
-    for (int i = tid; i < kDChunk * KP; i += 256) {
-        const int dl = i / KP, r = i - dl * KP;
-        Ws[dl * KPAD + r] = (dl < dn && r < a.R) ? wk[(long long)(dc + dl) * a.R + r] : zero;
+    if ((a.R & 7) == 0 && (reinterpret_cast<uintptr_t>(wk) & 15) == 0) {       // rows of whole 16-byte pieces
+        for (int i = tid; i < kDChunk * (KP / 8); i += 256) {
+            const int dl = i / (KP / 8), r = (i - dl * (KP / 8)) * 8;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (dl < dn && r < a.R) v = __ldg(reinterpret_cast<const uint4*>(wk + (long long)(dc + dl) * a.R + r));
+            *reinterpret_cast<uint4*>(&Ws[dl * KPAD + r]) = v;
+        }
+    } else {
+        for (int i = tid; i < kDChunk * KP; i += 256) {
+            const int dl = i / KP, r = i - dl * KP;
+            Ws[dl * KPAD + r] = (dl < dn && r < a.R) ? wk[(long long)(dc + dl) * a.R + r] : zero;
+        }
     }
     // one projected row of eight pixels, gathered column-major for the odd routes
     auto fetch8 = [&](int row, int q, T (&v)[8]) {
@@ -211,20 +220,40 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
     };
     const int g = lane >> 2, t4 = lane & 3;
     const int m0 = warp * 16;
+    // X tile, transposed to [pixel][k]; rows R .. KP-1 are zero.  Consecutive threads take consecutive rows of the
+    // same eight pixels, so the transposed stores of a warp fall into consecutive words.  The tile is read from
+    // global memory into registers one step ahead: the loads of tile t+1 are in flight while tile t is contracted.
+    constexpr int NI = (KP * (kMmaPix / 8) + 255) / 256;
+    T pre[NI][8];
+    auto load_tile = [&](int q0) {
+#pragma unroll
+        for (int n = 0; n < NI; ++n) {
+            const int i = tid + n * 256;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) pre[n][j] = zero;
+            if (i < KP * (kMmaPix / 8)) {
+                const int p0 = (i / KP) * 8, r = i - (i / KP) * KP;
+                if (r < a.R && q0 + p0 < a.L) fetch8(r, q0 + p0, pre[n]);      // L is a multiple of 8: a chunk is wholly inside or outside
+            }
+        }
+    };
+    auto store_tile = [&]() {
+#pragma unroll
+        for (int n = 0; n < NI; ++n) {
+            const int i = tid + n * 256;
+            if (i < KP * (kMmaPix / 8)) {
+                const int p0 = (i / KP) * 8, r = i - (i / KP) * KP;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) Xt[(p0 + j) * KPAD + r] = pre[n][j];
+            }
+        }
+    };
+    if (tile0 * kMmaPix < a.L) { load_tile(tile0 * kMmaPix); store_tile(); }
     for (int tt = 0; tt < a.mma_tiles; ++tt) {
         const int q0 = (tile0 + tt) * kMmaPix;
         if (q0 >= a.L) break;                        // uniform over the CTA
-        // ---- X tile, transposed to [pixel][k]; rows R .. KP-1 are zero.  Consecutive threads take consecutive
-        //      rows of the same eight pixels, so the transposed stores of a warp fall into consecutive words.
-        for (int i = tid; i < KP * (kMmaPix / 8); i += 256) {
-            const int p0 = (i / KP) * 8, r = i - (i / KP) * KP;
-            T v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = zero;
-            if (r < a.R && q0 + p0 < a.L) fetch8(r, q0 + p0, v);      // L is a multiple of 8: a chunk is wholly inside or outside
-#pragma unroll
-            for (int j = 0; j < 8; ++j) Xt[(p0 + j) * KPAD + r] = v[j];
-        }
+        const bool has_next = tt + 1 < a.mma_tiles && q0 + kMmaPix < a.L;
+        if (has_next) load_tile(q0 + kMmaPix);
         // ---- B / C rows pass through (first channel slice only) ---------------------------------------------
         if (blockIdx.z == 0) {
             for (int i = tid; i < a.N2 * (kMmaPix / 8); i += 256) {
@@ -266,14 +295,14 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
             *reinterpret_cast<uint32_t*>(&Os[(m0 + g + 8) * OPAD + nt * 8 + 2 * t4]) = *reinterpret_cast<const uint32_t*>(hi);
         }
         __syncthreads();                             // output tile complete; every read of the X tile is done
+        if (has_next) store_tile();                  // next X tile into the same buffer; the barrier at the top of the next step orders it
         T* __restrict__ dout = (T*)a.delta[k] + b * a.d_bs[k] + q0;
         for (int i = tid; i < kDChunk * (kMmaPix / 8); i += 256) {
             const int dl = i / (kMmaPix / 8), p0 = (i - dl * (kMmaPix / 8)) * 8;
             if (dl < dn && q0 + p0 < a.L)
                 *reinterpret_cast<uint4*>(dout + (long long)(dc + dl) * a.d_cs[k] + p0) = *reinterpret_cast<const uint4*>(&Os[dl * OPAD + p0]);
         }
-        // the next tile's X fill may start at once (other buffer than Os); its barrier orders the next Os writes
-        // behind these reads
+        // the barrier at the top of the next step orders the next writes of the output tile behind these reads
     }
 }
 
