@@ -309,9 +309,9 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
 template <typename T>
 static int launch_expand_mma(ExpandArgs a, cudaStream_t st) {
     const long long tiles_per_run = (a.L + kMmaPix - 1) / kMmaPix;
-    // Eight pixel tiles per CTA measured best for the 14 x 14 and 7 x 7 stages of a batch-128 forward (sums over
-    // ten launches: 1 tile 587 us, 2: 438, 4: 342, 8: 297, 16: 409, 32: 643): fewer tiles re-stage the weights
-    // too often, more leave too few CTAs.
+    // Eight pixel tiles per CTA: measured over the ten launches of the 14 x 14 and 7 x 7 stages of a batch-128
+    // forward, 4 and 8 tiles are equal (253 / 255 us), 16 and more leave too few CTAs, 1 or 2 re-stage the weights
+    // too often.
     const int per = kMmaTilesPerCta;
     a.mma_tiles = per;
     const long long tiles = (long long)a.B * ((tiles_per_run + per - 1) / per);
