@@ -41,43 +41,52 @@ struct CoreArgs {
 };
 
 struct ScanScratch {
-    AB wtot[2][32];
-    float wpre[2][32];
+    AB wtot[4][32];          // [2 * stream + direction][warp]
+    float wpre[4][32];
 };
 
 __device__ __forceinline__ int fast_div(int n, unsigned magic) { return magic ? (int)__umulhi((unsigned)n, magic) : n; }   // magic 0: divisor 1
 
 // CTA-wide scan of per-thread aggregates in thread order (forward) and in reverse thread order
-// (backward).  The state before the first thread is zero, so only the state entering each thread
-// is needed: hin_f for the forward route, hin_b for the backward route.
-__device__ __forceinline__ void cta_scan_pair(AB f, AB bk, int lane, int warp, int nwarps, ScanScratch& s,
-                                              float& hin_f, float& hin_b) {
-    const AB inc_f = warp_scan_inclusive(f, lane);
-    const AB inc_b = warp_scan_inclusive_rev(bk, lane);
-    if (lane == 31) s.wtot[0][warp] = inc_f;
-    if (lane == 0) s.wtot[1][warp] = inc_b;
-    __syncthreads();
-    if (warp == 0) {
-        const AB t = (lane < nwarps) ? s.wtot[0][lane] : AB{1.f, 0.f};
-        const AB sc = warp_scan_inclusive(t, lane);
-        float e = __shfl_up_sync(0xffffffffu, sc.b, 1);
-        if (lane == 0) e = 0.f;
-        s.wpre[0][lane] = e;
-    }
-    if (warp == (nwarps > 1 ? 1 : 0)) {
-        const AB t = (lane < nwarps) ? s.wtot[1][lane] : AB{1.f, 0.f};
-        const AB sc = warp_scan_inclusive_rev(t, lane);
-        float e = __shfl_down_sync(0xffffffffu, sc.b, 1);
-        if (lane == 31) e = 0.f;
-        s.wpre[1][lane] = e;
+// (backward), for NS independent streams at once (a thread may hold segments of NS planes: the streams
+// share the two barriers).  The state before the first thread is zero, so only the state entering each
+// thread is needed: hin_f for the forward route, hin_b for the backward route.
+template <int NS>
+__device__ __forceinline__ void cta_scan_pair(const AB (&f)[NS], const AB (&bk)[NS], int lane, int warp, int nwarps,
+                                              ScanScratch& s, float (&hin_f)[NS], float (&hin_b)[NS]) {
+    AB inc_f[NS], inc_b[NS];
+#pragma unroll
+    for (int q = 0; q < NS; ++q) {
+        inc_f[q] = warp_scan_inclusive(f[q], lane);
+        inc_b[q] = warp_scan_inclusive_rev(bk[q], lane);
+        if (lane == 31) s.wtot[2 * q][warp] = inc_f[q];
+        if (lane == 0) s.wtot[2 * q + 1][warp] = inc_b[q];
     }
     __syncthreads();
-    float ea = __shfl_up_sync(0xffffffffu, inc_f.a, 1), eb = __shfl_up_sync(0xffffffffu, inc_f.b, 1);
-    if (lane == 0) { ea = 1.f; eb = 0.f; }
-    hin_f = fmaf(ea, s.wpre[0][warp], eb);
-    float ra = __shfl_down_sync(0xffffffffu, inc_b.a, 1), rb = __shfl_down_sync(0xffffffffu, inc_b.b, 1);
-    if (lane == 31) { ra = 1.f; rb = 0.f; }
-    hin_b = fmaf(ra, s.wpre[1][warp], rb);
+    for (int job = warp; job < 2 * NS; job += nwarps) {         // one warp per (stream, direction)
+        const AB t = (lane < nwarps) ? s.wtot[job][lane] : AB{1.f, 0.f};
+        if ((job & 1) == 0) {
+            const AB sc = warp_scan_inclusive(t, lane);
+            float e = __shfl_up_sync(0xffffffffu, sc.b, 1);
+            if (lane == 0) e = 0.f;
+            s.wpre[job][lane] = e;
+        } else {
+            const AB sc = warp_scan_inclusive_rev(t, lane);
+            float e = __shfl_down_sync(0xffffffffu, sc.b, 1);
+            if (lane == 31) e = 0.f;
+            s.wpre[job][lane] = e;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < NS; ++q) {
+        float ea = __shfl_up_sync(0xffffffffu, inc_f[q].a, 1), eb = __shfl_up_sync(0xffffffffu, inc_f[q].b, 1);
+        if (lane == 0) { ea = 1.f; eb = 0.f; }
+        hin_f[q] = fmaf(ea, s.wpre[2 * q][warp], eb);
+        float ra = __shfl_down_sync(0xffffffffu, inc_b[q].a, 1), rb = __shfl_down_sync(0xffffffffu, inc_b[q].b, 1);
+        if (lane == 31) { ra = 1.f; rb = 0.f; }
+        hin_b[q] = fmaf(ra, s.wpre[2 * q + 1][warp], rb);
+    }
 }
 
 // Per-row constants of one route, pre-scaled for the arithmetic below.
@@ -204,7 +213,12 @@ struct SegAddr {
     __device__ __forceinline__ int at(int i, int minor_stride) const { return (i < VEC / 2 || VEC == 1 ? lo : hi) + i * minor_stride; }
 };
 
-template <typename T, int VEC, int MAXT, int MINB>
+// NPL = 2 (narrow segments only): a thread holds the same segment of TWO planes of its image, plane pl and plane
+// pl + PP/2.  A CTA pass costs about the same whatever the segment width (load, scan, barrier and store latencies in
+// sequence), so with four-element segments a pass moved half the pixels of an eight-element pass; two planes per
+// thread restore the pixels per pass, share the B / C rows (same image) and the index arithmetic, and the two
+// planes' scans share their barriers.
+template <typename T, int VEC, int NPL, int MAXT, int MINB>
 __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a) {
     extern __shared__ __align__(16) float smem[];
     __shared__ ScanScratch scr;
@@ -214,118 +228,163 @@ __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a
     const int b = blockIdx.x / a.groups_per_image;
     const int d0 = (blockIdx.x - b * a.groups_per_image) * a.PP;
     const int pp_here = min(a.PP, a.D - d0);
-    int pl = fast_div(t, a.magic_G);
-    const int v = t - pl * a.G;
+    const int pl0 = fast_div(t, a.magic_G);
+    const int v = t - pl0 * a.G;
+    const int half = a.PP / NPL;            // planes side by side in thread order
     // Threads past the last plane of the CTA (round-up to a warp, last channel group) run on the
     // last valid plane so that every load below is in range; they take no part in the scans
     // (identity aggregates) and store nothing.
-    const bool active = pl < pp_here;
-    pl = min(pl, pp_here - 1);
-    const int d = d0 + pl;
+    bool active[NPL];
+    int d[NPL];
+    float* plane[NPL];
     const int L = a.L, H = a.H, W = a.W, Wp = a.Wp, D = a.D;
-    // one padded fp32 plane per channel: first x (for the transposed read), then, once every
-    // column-orientation thread has taken its x values, the column-orientation result
-    float* plane = smem + (size_t)pl * (H * Wp);
+#pragma unroll
+    for (int s = 0; s < NPL; ++s) {
+        int pl = pl0 + s * half;
+        active[s] = pl0 < half && pl < pp_here;
+        pl = min(pl, pp_here - 1);
+        d[s] = d0 + pl;
+        // one padded fp32 plane per channel: first x (for the transposed read), then, once every
+        // column-orientation thread has taken its x values, the column-orientation result
+        plane[s] = smem + (size_t)pl * (H * Wp);
+    }
     using VT = typename SegVec<T, VEC>::type;
     const int e0 = v * VEC;   // first element of this thread in either orientation order
-    const long long plane_off = (long long)d * L + e0;
     const bool first = v == 0, last = v == a.G - 1;
 
     // ---- issue every HBM load of the pass up front: x and the four delta vectors -------------
-    const typename VT::Raw rx = VT::load_raw((const T*)a.x + b * a.x_bs + d * a.x_cs + e0);
-    const typename VT::Raw rd0 = VT::load_raw((const T*)a.delta[0] + b * a.d_bs[0] + d * a.d_cs[0] + e0);
-    const typename VT::Raw rd2 = VT::load_raw((const T*)a.delta[2] + b * a.d_bs[2] + d * a.d_cs[2] + e0);
-    const typename VT::Raw rd1 = VT::load_raw((const T*)a.delta[1] + b * a.d_bs[1] + d * a.d_cs[1] + e0);
-    const typename VT::Raw rd3 = VT::load_raw((const T*)a.delta[3] + b * a.d_bs[3] + d * a.d_cs[3] + e0);
-    float2 ul[NP], yrow[NP];
-    unpack_pairs<T, VEC>(rx, ul);
+    typename VT::Raw rx[NPL], rd0[NPL], rd1[NPL], rd2[NPL], rd3[NPL];
+#pragma unroll
+    for (int s = 0; s < NPL; ++s) {
+        rx[s] = VT::load_raw((const T*)a.x + b * a.x_bs + d[s] * a.x_cs + e0);
+        rd0[s] = VT::load_raw((const T*)a.delta[0] + b * a.d_bs[0] + d[s] * a.d_cs[0] + e0);
+        rd2[s] = VT::load_raw((const T*)a.delta[2] + b * a.d_bs[2] + d[s] * a.d_cs[2] + e0);
+        rd1[s] = VT::load_raw((const T*)a.delta[1] + b * a.d_bs[1] + d[s] * a.d_cs[1] + e0);
+        rd3[s] = VT::load_raw((const T*)a.delta[3] + b * a.d_bs[3] + d[s] * a.d_cs[3] + e0);
+    }
+    float2 ul[NPL][NP], yrow[NPL][NP];
 
     // ---- x into shared memory (row-major, padded pitch) -------------------------------------
     const int h0 = fast_div(e0, a.magic_W), w0 = e0 - h0 * W;
     const SegAddr<VEC> rs(h0, w0, W, Wp, 1);
-    if (active) {
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) plane[rs.at(i, 1)] = (i & 1) ? ul[i >> 1].y : ul[i >> 1].x;
+    for (int s = 0; s < NPL; ++s) {
+        unpack_pairs<T, VEC>(rx[s], ul[s]);
+        if (active[s]) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) plane[s][rs.at(i, 1)] = (i & 1) ? ul[s][i >> 1].y : ul[s][i >> 1].x;
+        }
     }
     const int wc = fast_div(e0, a.magic_H), hc = e0 - wc * H;
     const SegAddr<VEC> cs(wc, hc, H, 1, Wp);   // column-major walk: h is the fast index, stride Wp
 
     // ---- row orientation: routes 0 (forward) and 2 (backward) ---------------------------------
     {
-        float2 dv[NP], bv[NP], cv[NP], cPf[NP], cPb[NP];
-        const float2 Dsum = splat(__ldg(a.Dskip + d) + __ldg(a.Dskip + 2 * D + d));
+        float2 dv[NP], bv[NP], cv[NP], cPf[NPL][NP], cPb[NPL][NP];
+        AB af[NPL], ab[NPL];
 #pragma unroll
-        for (int j = 0; j < NP; ++j) { yrow[j] = mul2(Dsum, ul[j]); ul[j] = mul2(ul[j], splat(kLn2)); }
-        RouteConst rc;
-        rc.A = __ldg(a.A + d); rc.bias = __ldg(a.bias + d); rc.bias2 = rc.bias * kLog2e;
-        unpack_pairs<T, VEC>(rd0, dv);
-        unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Bm[0] + b * a.bc_bs[0] + e0), bv);
+        for (int s = 0; s < NPL; ++s) {
+            const float2 Dsum = splat(__ldg(a.Dskip + d[s]) + __ldg(a.Dskip + 2 * D + d[s]));
+#pragma unroll
+            for (int j = 0; j < NP; ++j) { yrow[s][j] = mul2(Dsum, ul[s][j]); ul[s][j] = mul2(ul[s][j], splat(kLn2)); }
+        }
+        unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Bm[0] + b * a.bc_bs[0] + e0), bv);      // one image: the planes share B and C
         unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Cm[0] + b * a.bc_bs[0] + e0), cv);
-        AB af = route_local<VEC, true, kPrecise>(ul, dv, bv, cv, rc, cPf, yrow);
-        rc.A = __ldg(a.A + 2 * D + d); rc.bias = __ldg(a.bias + 2 * D + d); rc.bias2 = rc.bias * kLog2e;
-        unpack_pairs<T, VEC>(rd2, dv);
+#pragma unroll
+        for (int s = 0; s < NPL; ++s) {
+            RouteConst rc;
+            rc.A = __ldg(a.A + d[s]); rc.bias = __ldg(a.bias + d[s]); rc.bias2 = rc.bias * kLog2e;
+            unpack_pairs<T, VEC>(rd0[s], dv);
+            af[s] = route_local<VEC, true, kPrecise>(ul[s], dv, bv, cv, rc, cPf[s], yrow[s]);
+        }
         unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Bm[2] + b * a.bc_bs[2] + e0), bv);
         unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Cm[2] + b * a.bc_bs[2] + e0), cv);
-        AB ab = route_local<VEC, false, kPrecise>(ul, dv, bv, cv, rc, cPb, yrow);
-        if (first) af.a = 0.f;
-        if (last) ab.a = 0.f;
-        if (!active) { af = AB{1.f, 0.f}; ab = AB{1.f, 0.f}; }
-        float hf, hb;
-        cta_scan_pair(af, ab, lane, warp, nwarps, scr, hf, hb);   // its barriers also order the x stores before the reads below
-        if (first) hf = 0.f;
-        if (last) hb = 0.f;
 #pragma unroll
-        for (int j = 0; j < NP; ++j) yrow[j] = fma2(cPf[j], splat(hf), fma2(cPb[j], splat(hb), yrow[j]));
+        for (int s = 0; s < NPL; ++s) {
+            RouteConst rc;
+            rc.A = __ldg(a.A + 2 * D + d[s]); rc.bias = __ldg(a.bias + 2 * D + d[s]); rc.bias2 = rc.bias * kLog2e;
+            unpack_pairs<T, VEC>(rd2[s], dv);
+            ab[s] = route_local<VEC, false, kPrecise>(ul[s], dv, bv, cv, rc, cPb[s], yrow[s]);
+            if (first) af[s].a = 0.f;
+            if (last) ab[s].a = 0.f;
+            if (!active[s]) { af[s] = AB{1.f, 0.f}; ab[s] = AB{1.f, 0.f}; }
+        }
+        float hf[NPL], hb[NPL];
+        cta_scan_pair<NPL>(af, ab, lane, warp, nwarps, scr, hf, hb);   // its barriers also order the x stores before the reads below
+#pragma unroll
+        for (int s = 0; s < NPL; ++s) {
+            if (first) hf[s] = 0.f;
+            if (last) hb[s] = 0.f;
+#pragma unroll
+            for (int j = 0; j < NP; ++j) yrow[s][j] = fma2(cPf[s][j], splat(hf[s]), fma2(cPb[s][j], splat(hb[s]), yrow[s][j]));
+        }
     }
 
     // ---- column orientation: routes 1 (forward) and 3 (backward) -------------------------------
     {
-        float2 dv[NP], bv[NP], cv[NP], cPf[NP], cPb[NP], ycol[NP];
+        float2 dv[NP], bv[NP], cv[NP], cPf[NPL][NP], cPb[NPL][NP], ycol[NPL][NP];
+        AB af[NPL], ab[NPL];
 #pragma unroll
-        for (int j = 0; j < NP; ++j) {
-            ul[j].x = plane[cs.at(2 * j, Wp)];
-            ul[j].y = (2 * j + 1 < VEC) ? plane[cs.at(2 * j + 1, Wp)] : 0.f;
+        for (int s = 0; s < NPL; ++s) {
+#pragma unroll
+            for (int j = 0; j < NP; ++j) {
+                ul[s][j].x = plane[s][cs.at(2 * j, Wp)];
+                ul[s][j].y = (2 * j + 1 < VEC) ? plane[s][cs.at(2 * j + 1, Wp)] : 0.f;
+            }
+            const float2 Dsum = splat(__ldg(a.Dskip + D + d[s]) + __ldg(a.Dskip + 3 * D + d[s]));
+#pragma unroll
+            for (int j = 0; j < NP; ++j) { ycol[s][j] = mul2(Dsum, ul[s][j]); ul[s][j] = mul2(ul[s][j], splat(kLn2)); }
         }
-        const float2 Dsum = splat(__ldg(a.Dskip + D + d) + __ldg(a.Dskip + 3 * D + d));
-#pragma unroll
-        for (int j = 0; j < NP; ++j) { ycol[j] = mul2(Dsum, ul[j]); ul[j] = mul2(ul[j], splat(kLn2)); }
-        RouteConst rc;
-        rc.A = __ldg(a.A + D + d); rc.bias = __ldg(a.bias + D + d); rc.bias2 = rc.bias * kLog2e;
-        unpack_pairs<T, VEC>(rd1, dv);
         unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Bm[1] + b * a.bc_bs[1] + e0), bv);
         unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Cm[1] + b * a.bc_bs[1] + e0), cv);
-        AB af = route_local<VEC, true, kPrecise>(ul, dv, bv, cv, rc, cPf, ycol);
-        rc.A = __ldg(a.A + 3 * D + d); rc.bias = __ldg(a.bias + 3 * D + d); rc.bias2 = rc.bias * kLog2e;
-        unpack_pairs<T, VEC>(rd3, dv);
+#pragma unroll
+        for (int s = 0; s < NPL; ++s) {
+            RouteConst rc;
+            rc.A = __ldg(a.A + D + d[s]); rc.bias = __ldg(a.bias + D + d[s]); rc.bias2 = rc.bias * kLog2e;
+            unpack_pairs<T, VEC>(rd1[s], dv);
+            af[s] = route_local<VEC, true, kPrecise>(ul[s], dv, bv, cv, rc, cPf[s], ycol[s]);
+        }
         unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Bm[3] + b * a.bc_bs[3] + e0), bv);
         unpack_pairs<T, VEC>(VT::load_raw((const T*)a.Cm[3] + b * a.bc_bs[3] + e0), cv);
-        AB ab = route_local<VEC, false, kPrecise>(ul, dv, bv, cv, rc, cPb, ycol);
-        if (first) af.a = 0.f;
-        if (last) ab.a = 0.f;
-        if (!active) { af = AB{1.f, 0.f}; ab = AB{1.f, 0.f}; }
-        float hf, hb;
-        cta_scan_pair(af, ab, lane, warp, nwarps, scr, hf, hb);   // every x value has been read before these barriers
-        if (first) hf = 0.f;
-        if (last) hb = 0.f;
 #pragma unroll
-        for (int j = 0; j < NP; ++j) ycol[j] = fma2(cPf[j], splat(hf), fma2(cPb[j], splat(hb), ycol[j]));
-        if (active) {
+        for (int s = 0; s < NPL; ++s) {
+            RouteConst rc;
+            rc.A = __ldg(a.A + 3 * D + d[s]); rc.bias = __ldg(a.bias + 3 * D + d[s]); rc.bias2 = rc.bias * kLog2e;
+            unpack_pairs<T, VEC>(rd3[s], dv);
+            ab[s] = route_local<VEC, false, kPrecise>(ul[s], dv, bv, cv, rc, cPb[s], ycol[s]);
+            if (first) af[s].a = 0.f;
+            if (last) ab[s].a = 0.f;
+            if (!active[s]) { af[s] = AB{1.f, 0.f}; ab[s] = AB{1.f, 0.f}; }
+        }
+        float hf[NPL], hb[NPL];
+        cta_scan_pair<NPL>(af, ab, lane, warp, nwarps, scr, hf, hb);   // every x value has been read before these barriers
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) plane[cs.at(i, Wp)] = (i & 1) ? ycol[i >> 1].y : ycol[i >> 1].x;
+        for (int s = 0; s < NPL; ++s) {
+            if (first) hf[s] = 0.f;
+            if (last) hb[s] = 0.f;
+#pragma unroll
+            for (int j = 0; j < NP; ++j) ycol[s][j] = fma2(cPf[s][j], splat(hf[s]), fma2(cPb[s][j], splat(hb[s]), ycol[s][j]));
+            if (active[s]) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) plane[s][cs.at(i, Wp)] = (i & 1) ? ycol[s][i >> 1].y : ycol[s][i >> 1].x;
+            }
         }
     }
     __syncthreads();
 
     // ---- merge: row result (registers) + column result (transposed read), one vector store ------
-    if (active) {
-        float out[VEC];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) out[i] = ((i & 1) ? yrow[i >> 1].y : yrow[i >> 1].x) + plane[rs.at(i, 1)];
-        SegVec<float, VEC>::type::store(a.merged + (long long)b * D * L + plane_off, out);
+    for (int s = 0; s < NPL; ++s) {
+        if (active[s]) {
+            float out[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) out[i] = ((i & 1) ? yrow[s][i >> 1].y : yrow[s][i >> 1].x) + plane[s][rs.at(i, 1)];
+            SegVec<float, VEC>::type::store(a.merged + (long long)b * D * L + (long long)d[s] * L + e0, out);
+        }
     }
 }
 
-struct PlaneConfig { int vec, G, PP, threads, Wp; size_t smem; };
+struct PlaneConfig { int vec, G, PP, threads, Wp, npl; size_t smem; };
 
 static bool plan_planes(const ss2d_core_params* p, PlaneConfig& c) {
     const long long L = p->H * p->W;
@@ -353,31 +412,43 @@ static bool plan_planes(const ss2d_core_params* p, PlaneConfig& c) {
     int PP = (int)(448 / G);          // ~14 warps per CTA: two CTAs per SM
     if (PP < 1) PP = 1;
     if (PP > p->D) PP = (int)p->D;
+    // segments of at most four elements: two planes per thread (the kernel's NPL = 2), twice the planes per CTA
+    // (677 -> 649 us for the eight 14 x 14 launches of a batch-128 VMamba-T forward)
+    const int npl = (vec <= 4 && 2 * PP <= p->D) ? 2 : 1;
+    PP *= npl;
     const int Wp = (int)(p->W | 1);   // odd pitch spreads the transposed accesses over banks
     size_t smem = (size_t)PP * p->H * Wp * sizeof(float);
-    while (smem > 200 * 1024 && PP > 1) { --PP; smem = (size_t)PP * p->H * Wp * sizeof(float); }
+    while (smem > 200 * 1024 && PP > npl) { PP -= npl; smem = (size_t)PP * p->H * Wp * sizeof(float); }
     if (smem > 200 * 1024) return false;
-    c.vec = vec; c.G = (int)G; c.PP = PP; c.Wp = Wp; c.smem = smem;
-    c.threads = (int)((PP * G + 31) / 32 * 32);
+    c.vec = vec; c.G = (int)G; c.PP = PP; c.Wp = Wp; c.smem = smem; c.npl = npl;
+    c.threads = (int)(((PP / npl) * G + 31) / 32 * 32);
     return true;
 }
 
-template <typename T, int VEC>
-static int launch_core_t(const CoreArgs& a, const PlaneConfig& c, unsigned grid, cudaStream_t st) {
+template <typename T, int VEC, int NPL>
+static int launch_core_n(const CoreArgs& a, const PlaneConfig& c, unsigned grid, cudaStream_t st) {
     cudaError_t e;
     if (c.threads <= 448) {           // 72 registers per thread at two CTAs per SM
-        auto kern = core_plane_kernel<T, VEC, 448, 2>;
+        auto kern = core_plane_kernel<T, VEC, NPL, 448, 2>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem);
         if (e != cudaSuccess) return SS2D_ECUDA;
         kern<<<grid, c.threads, c.smem, st>>>(a);
     } else {
-        auto kern = core_plane_kernel<T, VEC, 1024, 1>;
+        auto kern = core_plane_kernel<T, VEC, NPL, 1024, 1>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem);
         if (e != cudaSuccess) return SS2D_ECUDA;
         kern<<<grid, c.threads, c.smem, st>>>(a);
     }
     count_launch();
     return check_launch();
+}
+
+template <typename T, int VEC>
+static int launch_core_t(const CoreArgs& a, const PlaneConfig& c, unsigned grid, cudaStream_t st) {
+    if constexpr (VEC <= 4) {
+        if (c.npl == 2) return launch_core_n<T, VEC, 2>(a, c, grid, st);
+    }
+    return launch_core_n<T, VEC, 1>(a, c, grid, st);
 }
 
 template <typename T>
