@@ -173,6 +173,51 @@ def test_layer_norm_cf_fused_residual_update(vb, shape):
     assert O.max_rel_err(host(got32), O.layer_norm_cf(x + add, w, b)) <= 2e-5
 
 
+@pytest.mark.parametrize("shape", [(3, 96, 7, 7), (2, 192, 14, 14), (3, 384, 7, 7), (2, 768, 7, 7), (5, 128, 5, 3), (2, 1024, 3, 3)])
+def test_layer_norm_cf_channel_major(vb, shape):
+    """Channel-major maps (D, B, H, W): the batch is one long row per channel, so odd map sizes still move as vectors;
+    the three call shapes of a backbone forward (in; in + add written back; in + add + bias written back)."""
+    rng = np.random.default_rng(sum(shape) + 1)
+    x = rng.standard_normal(shape, dtype=np.float32) * 2 + 0.3
+    add = O.round_bf16(rng.standard_normal(shape, dtype=np.float32))
+    ab = rng.standard_normal(shape[1], dtype=np.float32)
+    w = rng.standard_normal(shape[1], dtype=np.float32)
+    b = rng.standard_normal(shape[1], dtype=np.float32)
+    cm = lambda a_: np.ascontiguousarray(a_.transpose(1, 0, 2, 3))
+    back = lambda t_: host(t_).transpose(1, 0, 2, 3)
+    got = vb.layer_norm_cf(dev(cm(x)), dev(w), dev(b), out_dtype=torch.bfloat16, channel_major=True)
+    assert O.max_rel_err(back(got), O.layer_norm_cf(x, w, b)) <= 8e-3
+    got32 = vb.layer_norm_cf(dev(cm(x)), dev(w), dev(b), channel_major=True)
+    assert O.max_rel_err(back(got32), O.layer_norm_cf(x, w, b)) <= 2e-5
+    xt = dev(cm(x))
+    got = vb.layer_norm_cf(xt, dev(w), dev(b), out_dtype=torch.bfloat16, add=dev(cm(add), torch.bfloat16), update=True, channel_major=True)
+    assert np.array_equal(back(xt), (x + add).astype(np.float32))
+    assert O.max_rel_err(back(got), O.layer_norm_cf(x + add, w, b)) <= 8e-3
+    xt = dev(cm(x))
+    s3 = x + add + ab.reshape(1, -1, 1, 1)
+    got = vb.layer_norm_cf(xt, dev(w), dev(b), out_dtype=torch.bfloat16, add=dev(cm(add), torch.bfloat16), add_bias=dev(ab), update=True,
+                           channel_major=True)
+    assert np.array_equal(back(xt), s3.astype(np.float32))
+    assert O.max_rel_err(back(got), O.layer_norm_cf(s3, w, b)) <= 8e-3
+    # channel-major in, batch-major out (the layout change of the feature maps)
+    got = vb.layer_norm_cf(dev(cm(x)), dev(w), dev(b), channel_major=True, out_channel_major=False)
+    assert O.max_rel_err(host(got), O.layer_norm_cf(x, w, b)) <= 2e-5
+
+
+@pytest.mark.parametrize("shape", [(3, 96, 14, 14), (2, 768, 7, 7), (2, 5, 9, 6)])
+def test_dwconv3x3_channel_major(vb, shape):
+    import torch.nn.functional as F
+    from vmamba_b200 import ops
+    rng = np.random.default_rng(sum(shape) + 2)
+    x = O.round_bf16(rng.standard_normal(shape, dtype=np.float32))
+    w = O.round_bf16(rng.standard_normal((shape[1], 1, 3, 3), dtype=np.float32) / 3)
+    ref = F.conv2d(torch.from_numpy(x), torch.from_numpy(w), None, padding=1, groups=shape[1]).to(torch.bfloat16).float()
+    ref = F.silu(ref).numpy()
+    xcm = np.ascontiguousarray(x.transpose(1, 0, 2, 3))
+    got = ops.dwconv3x3_act(dev(xcm, torch.bfloat16), dev(w, torch.bfloat16), None, "silu", channel_major=True)
+    assert O.max_rel_err(host(got).transpose(1, 0, 2, 3), ref) <= 8e-3
+
+
 # ------------------------------------------------------------------------------ elementwise producers
 @pytest.mark.parametrize("shape", [(2, 96, 56, 56), (2, 192, 28, 28), (3, 384, 14, 14), (2, 768, 7, 7), (1, 3, 5, 9), (1, 2, 1, 1),
                                    (1, 3, 256, 256), (1, 2, 130, 72)])
