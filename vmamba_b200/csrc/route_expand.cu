@@ -166,17 +166,18 @@ template <> struct MmaK16<__half> {
 
 constexpr int kMmaTilesPerCta = 8;      // most pixel tiles per CTA: the staged weights then serve 512 pixels
 
-template <typename T, int KP>
+// PIX pixels per step.
+template <typename T, int KP, int PIX>
 __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs a) {
     constexpr int KPAD = KP + 8;                  // row pitch (elements) of the operand tiles: conflict-free fragment loads
-    constexpr int OPAD = kMmaPix + 8;
+    constexpr int OPAD = PIX + 8;
     __shared__ __align__(16) T Ws[kDChunk * KPAD];     // [channel][k]
-    __shared__ __align__(16) T Xt[kMmaPix * KPAD];     // [pixel][k]
+    __shared__ __align__(16) T Xt[PIX * KPAD];     // [pixel][k]
     __shared__ __align__(16) T Os[kDChunk * OPAD];     // [channel][pixel]
     const int k = blockIdx.y;
     const bool col = (k & 1) != 0;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int tiles_per_run = (a.L + kMmaPix - 1) / kMmaPix;
+    const int tiles_per_run = (a.L + PIX - 1) / PIX;
     const int groups_per_run = (tiles_per_run + a.mma_tiles - 1) / a.mma_tiles;
     const int b = blockIdx.x / groups_per_run;
     const int tile0 = (blockIdx.x - b * groups_per_run) * a.mma_tiles;
@@ -223,7 +224,7 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
     // X tile, transposed to [pixel][k]; rows R .. KP-1 are zero.  Consecutive threads take consecutive rows of the
     // same eight pixels, so the transposed stores of a warp fall into consecutive words.  The tile is read from
     // global memory into registers one step ahead: the loads of tile t+1 are in flight while tile t is contracted.
-    constexpr int NI = (KP * (kMmaPix / 8) + 255) / 256;
+    constexpr int NI = (KP * (PIX / 8) + 255) / 256;
     T pre[NI][8];
     auto load_tile = [&](int q0) {
 #pragma unroll
@@ -231,7 +232,7 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
             const int i = tid + n * 256;
 #pragma unroll
             for (int j = 0; j < 8; ++j) pre[n][j] = zero;
-            if (i < KP * (kMmaPix / 8)) {
+            if (i < KP * (PIX / 8)) {
                 const int p0 = (i / KP) * 8, r = i - (i / KP) * KP;
                 if (r < a.R && q0 + p0 < a.L) fetch8(r, q0 + p0, pre[n]);      // L is a multiple of 8: a chunk is wholly inside or outside
             }
@@ -241,23 +242,23 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
 #pragma unroll
         for (int n = 0; n < NI; ++n) {
             const int i = tid + n * 256;
-            if (i < KP * (kMmaPix / 8)) {
+            if (i < KP * (PIX / 8)) {
                 const int p0 = (i / KP) * 8, r = i - (i / KP) * KP;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) Xt[(p0 + j) * KPAD + r] = pre[n][j];
             }
         }
     };
-    if (tile0 * kMmaPix < a.L) { load_tile(tile0 * kMmaPix); store_tile(); }
+    if (tile0 * PIX < a.L) { load_tile(tile0 * PIX); store_tile(); }
     for (int tt = 0; tt < a.mma_tiles; ++tt) {
-        const int q0 = (tile0 + tt) * kMmaPix;
+        const int q0 = (tile0 + tt) * PIX;
         if (q0 >= a.L) break;                        // uniform over the CTA
-        const bool has_next = tt + 1 < a.mma_tiles && q0 + kMmaPix < a.L;
-        if (has_next) load_tile(q0 + kMmaPix);
+        const bool has_next = tt + 1 < a.mma_tiles && q0 + PIX < a.L;
+        if (has_next) load_tile(q0 + PIX);
         // ---- B / C rows pass through (first channel slice only) ---------------------------------------------
         if (blockIdx.z == 0) {
-            for (int i = tid; i < a.N2 * (kMmaPix / 8); i += 256) {
-                const int n = i / (kMmaPix / 8), p0 = (i - n * (kMmaPix / 8)) * 8;
+            for (int i = tid; i < a.N2 * (PIX / 8); i += 256) {
+                const int n = i / (PIX / 8), p0 = (i - n * (PIX / 8)) * 8;
                 const int q = q0 + p0;
                 if (q >= a.L) continue;
                 T v[8];
@@ -268,9 +269,9 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
         __syncthreads();                             // X tile (and, first time, the weights) in place
 
         // ---- 16 channels x 64 pixels per warp ---------------------------------------------------------------
-        float acc[kMmaPix / 8][4];
+        float acc[PIX / 8][4];
 #pragma unroll
-        for (int nt = 0; nt < kMmaPix / 8; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+        for (int nt = 0; nt < PIX / 8; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
 #pragma unroll
         for (int k0 = 0; k0 < KP; k0 += 16) {
             uint32_t af[4];
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
             af[2] = *reinterpret_cast<const uint32_t*>(&Ws[(m0 + g) * KPAD + k0 + 2 * t4 + 8]);
             af[3] = *reinterpret_cast<const uint32_t*>(&Ws[(m0 + g + 8) * KPAD + k0 + 2 * t4 + 8]);
 #pragma unroll
-            for (int nt = 0; nt < kMmaPix / 8; ++nt) {
+            for (int nt = 0; nt < PIX / 8; ++nt) {
                 uint32_t bf[2];
                 bf[0] = *reinterpret_cast<const uint32_t*>(&Xt[(nt * 8 + g) * KPAD + k0 + 2 * t4]);
                 bf[1] = *reinterpret_cast<const uint32_t*>(&Xt[(nt * 8 + g) * KPAD + k0 + 2 * t4 + 8]);
@@ -288,7 +289,7 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
         }
         // ---- accumulators -> shared tile -> 16-byte stores along the pixels -----------------------------------
 #pragma unroll
-        for (int nt = 0; nt < kMmaPix / 8; ++nt) {
+        for (int nt = 0; nt < PIX / 8; ++nt) {
             T lo[2] = {from_f<T>(acc[nt][0]), from_f<T>(acc[nt][1])};
             T hi[2] = {from_f<T>(acc[nt][2]), from_f<T>(acc[nt][3])};
             *reinterpret_cast<uint32_t*>(&Os[(m0 + g) * OPAD + nt * 8 + 2 * t4]) = *reinterpret_cast<const uint32_t*>(lo);
@@ -297,8 +298,8 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
         __syncthreads();                             // output tile complete; every read of the X tile is done
         if (has_next) store_tile();                  // next X tile into the same buffer; the barrier at the top of the next step orders it
         T* __restrict__ dout = (T*)a.delta[k] + b * a.d_bs[k] + q0;
-        for (int i = tid; i < kDChunk * (kMmaPix / 8); i += 256) {
-            const int dl = i / (kMmaPix / 8), p0 = (i - dl * (kMmaPix / 8)) * 8;
+        for (int i = tid; i < kDChunk * (PIX / 8); i += 256) {
+            const int dl = i / (PIX / 8), p0 = (i - dl * (PIX / 8)) * 8;
             if (dl < dn && q0 + p0 < a.L)
                 *reinterpret_cast<uint4*>(dout + (long long)(dc + dl) * a.d_cs[k] + p0) = *reinterpret_cast<const uint4*>(&Os[dl * OPAD + p0]);
         }
@@ -308,7 +309,9 @@ __global__ void __launch_bounds__(256) route_expand_mma_kernel(const ExpandArgs 
 
 template <typename T>
 static int launch_expand_mma(ExpandArgs a, cudaStream_t st) {
-    const long long tiles_per_run = (a.L + kMmaPix - 1) / kMmaPix;
+    const int kp = (a.R + 15) / 16 * 16;
+    const int pix = kMmaPix;          // 128 pixels per step were measured for the shortest contraction: 4 % slower
+    const long long tiles_per_run = (a.L + pix - 1) / pix;
     // Eight pixel tiles per CTA: measured over the ten launches of the 14 x 14 and 7 x 7 stages of a batch-128
     // forward, 4 and 8 tiles are equal (253 / 255 us), 16 and more leave too few CTAs, 1 or 2 re-stage the weights
     // too often.
@@ -317,11 +320,10 @@ static int launch_expand_mma(ExpandArgs a, cudaStream_t st) {
     const long long tiles = (long long)a.B * ((tiles_per_run + per - 1) / per);
     if (tiles > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
     const dim3 grid((unsigned)tiles, 4, (unsigned)((a.D + kDChunk - 1) / kDChunk));
-    const int kp = (a.R + 15) / 16 * 16;
-    if (kp == 16) route_expand_mma_kernel<T, 16><<<grid, 256, 0, st>>>(a);
-    else if (kp == 32) route_expand_mma_kernel<T, 32><<<grid, 256, 0, st>>>(a);
-    else if (kp == 48) route_expand_mma_kernel<T, 48><<<grid, 256, 0, st>>>(a);
-    else if (kp == 64) route_expand_mma_kernel<T, 64><<<grid, 256, 0, st>>>(a);
+    if (kp == 16) route_expand_mma_kernel<T, 16, kMmaPix><<<grid, 256, 0, st>>>(a);
+    else if (kp == 32) route_expand_mma_kernel<T, 32, kMmaPix><<<grid, 256, 0, st>>>(a);
+    else if (kp == 48) route_expand_mma_kernel<T, 48, kMmaPix><<<grid, 256, 0, st>>>(a);
+    else if (kp == 64) route_expand_mma_kernel<T, 64, kMmaPix><<<grid, 256, 0, st>>>(a);
     else return SS2D_ENOTSUP;
     count_launch();
     return check_launch();
@@ -479,7 +481,7 @@ int route_expand(const ss2d_expand_params* p, cudaStream_t st) {
         fit((long long)(reinterpret_cast<uintptr_t>(p->bc[k]) / s));
     }
     const bool mma_ok = vec == 8 && s == 2 && p->R <= 64 && (run % 8) == 0;
-    const int mma_min_r = 13;      // measured: for R = 6 and 12 the FMA kernel below is as fast or faster (its write dominates)
+    const int mma_min_r = 1;      // every rank: with the pixel-tile prefetch the tensor-core kernel is 10 % faster than the FMA kernel for R = 6, 12 too
     // the staged rows (C rows x 64 items x vec floats) should stay near 28 KB so that several CTAs share an SM
     while (vec > 1 && C * 64 * vec * 4 > 28 * 1024) vec >>= 1;
     ExpandArgs a;
