@@ -7,11 +7,11 @@
 //   bc_k[b, n, q]    = x_dbl[b, k, R + n, pix(q)]   n < 2N            (B then C rows, activation type)
 // i.e. dt_projs (a grouped 1x1 convolution with a contraction length of only R = 6..64), the
 // split/contiguous copies, and the CrossScan permutation of the projected rows, in one pass whose
-// cost is the write of delta.  The contraction is far too short and the output far too large for
-// the tensor cores to matter: the kernel is bound by the delta write for R <= 12 and by fp32 FMA
-// issue (packed f32x2) for the deep, small stages.
+// cost is the write of delta.  Two kernels: the FMA form below (fp32 maps, unaligned runs) and the
+// mma.sync form further down (16-bit maps, every rank), which has no FMA loop and no weight
+// broadcasts through shared memory and is 10 to 30 % faster.
 //
-// Mapping: an "item" is VEC consecutive pixels q of one (image, route) plane.  A CTA stages the
+// Mapping of the FMA form: an "item" is VEC consecutive pixels q of one (image, route) plane.  A CTA stages the
 // R+2N projected rows of NI items in shared memory as fp32 (the column-major gather happens
 // here), then thread (item, channel group) accumulates 4 channels x VEC pixels at a time with
 // the weights broadcast from shared memory; lanes of a warp hold consecutive items, so every
