@@ -197,6 +197,23 @@ __device__ __forceinline__ AB warp_scan_inclusive_rev(AB v, int lane) {
     return v;
 }
 
+// ---- warp-level tensor-core step: D (16 x 8, fp32) += A (16 x 16, row-major) . B (16 x 8, column-major) -------
+template <typename T> struct MmaK16;
+template <> struct MmaK16<__nv_bfloat16> {
+    static __device__ __forceinline__ void run(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+    }
+};
+template <> struct MmaK16<__half> {
+    static __device__ __forceinline__ void run(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+    }
+};
+
 // ---- host-side helpers ---------------------------------------------------------------------
 inline size_t dtype_size(int dt) { return dt == SS2D_F32 ? 4 : 2; }
 inline bool dtype_ok(int dt) { return dt == SS2D_F32 || dt == SS2D_F16 || dt == SS2D_BF16; }

@@ -148,22 +148,6 @@ __global__ void __launch_bounds__(kExpThreads) route_expand_kernel(const ExpandA
 // through a shared tile so that every channel row leaves as 16-byte vectors.
 constexpr int kMmaPix = 64;
 
-template <typename T> struct MmaK16;
-template <> struct MmaK16<__nv_bfloat16> {
-    static __device__ __forceinline__ void run(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-    }
-};
-template <> struct MmaK16<__half> {
-    static __device__ __forceinline__ void run(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-    }
-};
-
 constexpr int kMmaTilesPerCta = 8;      // most pixel tiles per CTA: the staged weights then serve 512 pixels
 
 // PIX pixels per step.

@@ -13,6 +13,7 @@
 //   planes_to_pixels      (C, N) fp32 planes (+ add + bias, optionally written back) -> (N, C) pixel-major 16-bit
 // N counts the pixels of the whole batch (b, h, w): pixel-major row n and element n of every plane
 // are the same pixel.
+#include <cstdlib>
 #include "activations.cuh"
 
 namespace ss2d {
@@ -138,6 +139,189 @@ __global__ void __launch_bounds__(128, 4) stem_conv_norm_act_kernel(const StemAr
     finish(acc1, two ? ox0 + 1 : ox0, live && two);
 }
 
+// Tensor-core form for 16-bit images: the convolution of 16 output pixels is one 16 x C0 x 32 contraction
+// (27 taps, zero-padded) of mma.sync m16n8k16 steps.  A CTA walks output rows: the three input rows of the
+// three colour planes are staged in shared memory (zero frame included), warp w takes output pixels
+// 16 w .. 16 w + 15 of the row, gathers its im2col fragment from the staged rows (16 two-byte loads) and
+// keeps the weight fragments in registers for all its rows.  In the accumulator layout a pixel's C0 channels
+// sit in the four lanes of a quad, so the LayerNorm statistics need two shuffles; bias, LayerNorm and GELU
+// run on the accumulators and the quad stores 16 contiguous bytes per eight channels.
+// The FMA form above issues 61 instructions per output value, 16 of them packed FMAs; here the contraction
+// costs 1.5 per output and what remains is the GELU.
+template <typename T, int C0>
+__global__ void __launch_bounds__(512, 1) stem_mma_kernel(const StemArgs a, int rows_total, int vec_ok) {
+    extern __shared__ __align__(16) unsigned char stem_smem[];
+    constexpr int NT = C0 / 8;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int ntiles = (a.Wo + 15) / 16, nwarps = nthreads >> 5;
+    const int XP = 32 * ntiles + 16;                          // staged columns -8 .. 32 * tiles + 7: image column 0 sits 16-byte aligned
+    T* xs = reinterpret_cast<T*>(stem_smem);                  // [3 colours][3 rows][XP]
+    float* sb = reinterpret_cast<float*>(stem_smem + (((size_t)9 * XP * sizeof(T) + 15) & ~(size_t)15));   // bias, ln weight, ln bias
+    for (int i = tid; i < C0; i += nthreads) {
+        sb[i] = a.cbias ? a.cbias[i] : 0.f;
+        sb[C0 + i] = a.lnw ? a.lnw[i] : 1.f;
+        sb[2 * C0 + i] = a.lnb ? a.lnb[i] : 0.f;
+    }
+    // weight fragments: B[k][n] = w[n][k], k = (colour * 3 + ky) * 3 + kx, zero for k >= 27
+    uint32_t bw[NT][2][2];
+    {
+        const T* __restrict__ w = (const T*)a.w;
+        const T zero = from_f<T>(0.f);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int k = ks * 16 + 8 * h + 2 * t4, co = nt * 8 + g;
+                    T lo = k < 27 ? w[co * 27 + k] : zero, hi = k + 1 < 27 ? w[co * 27 + k + 1] : zero;
+                    bw[nt][ks][h] = (uint32_t)(*reinterpret_cast<unsigned short*>(&lo)) | ((uint32_t)(*reinterpret_cast<unsigned short*>(&hi)) << 16);
+                }
+    }
+    // shared-memory offsets of this lane's eight taps (pixel 0 of the row; add 2 * ox), -1 for the padding taps
+    int toff[2][2][2];
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int k = ks * 16 + 8 * h + 2 * t4 + e;
+                const int ci = k / 9, ky = (k - ci * 9) / 3, kx = k - ci * 9 - ky * 3;
+                toff[ks][h][e] = k < 27 ? (ci * 3 + ky) * XP + kx + 7 : -1;
+            }
+
+    // Input rows: with rows of whole 16-byte pieces the next output row's three input rows per colour are read
+    // into registers while the current row is computed, and go to shared memory as 16-byte stores.
+    const int W8 = a.W >> 3;
+    const bool vec_fill = vec_ok != 0;
+    uint4 pre[3];
+    auto load_row = [&](int row) {
+        const int b = row / a.Ho, oy = row - b * a.Ho;
+        const T* __restrict__ xb = (const T*)a.x + (long long)b * 3 * a.H * a.W;
+#pragma unroll
+        for (int sl = 0; sl < 3; ++sl) {
+            const int i = tid + sl * nthreads;
+            pre[sl] = make_uint4(0u, 0u, 0u, 0u);
+            if (i < 9 * W8) {
+                const int r = i / W8, c8 = i - r * W8;
+                const int ci = r / 3, ky = r - ci * 3, iy = 2 * oy - 1 + ky;
+                if (iy >= 0 && iy < a.H) pre[sl] = __ldg(reinterpret_cast<const uint4*>(xb + ((long long)ci * a.H + iy) * a.W + 8 * c8));
+            }
+        }
+    };
+    auto store_row = [&]() {
+#pragma unroll
+        for (int sl = 0; sl < 3; ++sl) {
+            const int i = tid + sl * nthreads;
+            if (i < 9 * W8) {
+                const int r = i / W8, c8 = i - r * W8;
+                *reinterpret_cast<uint4*>(xs + r * XP + 8 + 8 * c8) = pre[sl];
+            }
+        }
+    };
+    for (int i = tid; i < 9 * XP; i += nthreads) xs[i] = from_f<T>(0.f);      // the frame around the image stays zero
+    if (vec_fill && (int)blockIdx.x < rows_total) load_row(blockIdx.x);
+    __syncthreads();
+    for (int row = blockIdx.x; row < rows_total; row += gridDim.x) {
+        const int b = row / a.Ho, oy = row - b * a.Ho;
+        if (vec_fill) store_row();
+        else {
+            const T* __restrict__ xb = (const T*)a.x + (long long)b * 3 * a.H * a.W;
+            for (int i = tid; i < 9 * a.W; i += nthreads) {
+                const int r = i / a.W, ix = i - r * a.W;          // r = colour * 3 + ky
+                const int ci = r / 3, ky = r - ci * 3, iy = 2 * oy - 1 + ky;
+                xs[r * XP + 8 + ix] = (iy >= 0 && iy < a.H) ? xb[((long long)ci * a.H + iy) * a.W + ix] : from_f<T>(0.f);
+            }
+        }
+        __syncthreads();
+        if (vec_fill && row + (int)gridDim.x < rows_total) load_row(row + gridDim.x);      // in flight during the contraction
+        for (int tile = warp; tile < ntiles; tile += nwarps) {
+        const int ox_lo = 16 * tile + g, ox_hi = ox_lo + 8;
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            uint32_t af[4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                unsigned short v[2][2];                       // [pixel lo / hi][tap e]
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int o = toff[ks][h][e];
+                    v[0][e] = o >= 0 ? reinterpret_cast<const unsigned short*>(xs)[o + 2 * ox_lo] : (unsigned short)0;
+                    v[1][e] = o >= 0 ? reinterpret_cast<const unsigned short*>(xs)[o + 2 * ox_hi] : (unsigned short)0;
+                }
+                af[2 * h] = (uint32_t)v[0][0] | ((uint32_t)v[0][1] << 16);          // row g,     k 2t (+8h), 2t+1
+                af[2 * h + 1] = (uint32_t)v[1][0] | ((uint32_t)v[1][1] << 16);      // row g + 8
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) MmaK16<T>::run(acc[nt], af, bw[nt][ks]);
+        }
+        // per pixel (two per lane: rows g and g + 8): conv output rounded to the storage type, + bias, LayerNorm in fp32
+        // across the quad, GELU, one rounding at the store
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int ox = hh ? ox_hi : ox_lo;
+            float2 v[NT];
+            float s = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const float2 bb = *reinterpret_cast<const float2*>(sb + nt * 8 + 2 * t4);
+                v[nt].x = round_to<T>(acc[nt][2 * hh]) + bb.x;
+                v[nt].y = round_to<T>(acc[nt][2 * hh + 1]) + bb.y;
+                s += v[nt].x + v[nt].y;
+            }
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            const float mean = s * (1.f / C0);
+            float q = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const float dx = v[nt].x - mean, dy = v[nt].y - mean;
+                q = fmaf(dx, dx, q); q = fmaf(dy, dy, q);
+            }
+            q += __shfl_xor_sync(0xffffffffu, q, 1);
+            q += __shfl_xor_sync(0xffffffffu, q, 2);
+            const float rstd = rsqrtf(q * (1.f / C0) + a.eps);
+            if (ox < a.Wo) {
+                T* out = (T*)a.y + (((long long)b * a.Ho + oy) * a.Wo + ox) * C0 + 2 * t4;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const float2 lw = *reinterpret_cast<const float2*>(sb + C0 + nt * 8 + 2 * t4);
+                    const float2 lb = *reinterpret_cast<const float2*>(sb + 2 * C0 + nt * 8 + 2 * t4);
+                    float2 n2;
+                    n2.x = fmaf((v[nt].x - mean) * rstd, lw.x, lb.x);
+                    n2.y = fmaf((v[nt].y - mean) * rstd, lw.y, lb.y);
+                    const float2 r = gelu_pair_fast(n2);
+                    *reinterpret_cast<uint32_t*>(out + nt * 8) = Half2Of<T>::pack(r.x, r.y);
+                }
+            }
+        }
+        }
+        __syncthreads();                                      // every fragment of this row has been gathered
+    }
+}
+
+template <typename T>
+static int launch_stem_mma(const StemArgs& a, int C0, cudaStream_t st) {
+    const int tiles = (a.Wo + 15) / 16;
+    const int threads = 32 * (tiles < 16 ? tiles : 16);
+    const int XP = 32 * tiles + 16;
+    const int vec_ok = (a.W % 8 == 0 && aligned_to(a.x, 16) && 9 * (a.W / 8) <= 3 * threads) ? 1 : 0;
+    const size_t smem = (((size_t)9 * XP * sizeof(T) + 15) & ~(size_t)15) + 3 * (size_t)C0 * sizeof(float);
+    const long long rows = (long long)a.B * a.Ho;
+    static const int gmul = getenv("SS2D_STEM_GRID") ? atoi(getenv("SS2D_STEM_GRID")) : 8;
+    const unsigned grid = (unsigned)(rows < 148 * gmul ? rows : 148 * gmul);
+    if (C0 == 32) stem_mma_kernel<T, 32><<<grid, threads, smem, st>>>(a, (int)rows, vec_ok);
+    else if (C0 == 48) stem_mma_kernel<T, 48><<<grid, threads, smem, st>>>(a, (int)rows, vec_ok);
+    else stem_mma_kernel<T, 64><<<grid, threads, smem, st>>>(a, (int)rows, vec_ok);
+    count_launch();
+    return check_launch();
+}
+
 int stem_conv_norm_act(const ss2d_stem_params* p, cudaStream_t st) {
     if (!p) return SS2D_EINVAL_NULL;
     if (!p->x || !p->weight || !p->y) return SS2D_EINVAL_NULL;
@@ -154,6 +338,11 @@ int stem_conv_norm_act(const ss2d_stem_params* p, cudaStream_t st) {
     a.lnb = (const float*)p->ln_bias; a.y = p->y;
     a.B = (int)p->B; a.H = (int)p->H; a.W = (int)p->W; a.Ho = (int)((p->H + 1) / 2); a.Wo = (int)((p->W + 1) / 2);
     a.eps = p->eps;
+    static const int use_mma = getenv("SS2D_STEM_MMA") ? atoi(getenv("SS2D_STEM_MMA")) : 1;
+    if (use_mma && s == 2 && a.Wo <= 1024 && (long long)a.B * a.Ho <= 0x7fffffffLL && (p->C0 == 32 || p->C0 == 48 || p->C0 == 64)) {
+        if (p->dtype == SS2D_BF16) return launch_stem_mma<__nv_bfloat16>(a, (int)p->C0, st);
+        return launch_stem_mma<__half>(a, (int)p->C0, st);
+    }
     const long long total = 2LL * a.B * a.Ho * ((a.Wo + 1) / 2);      // two threads per pixel pair
     const unsigned grid = (unsigned)((total + 127) / 128);
 #define SS2D_STEM_CASE(TT, CC) stem_conv_norm_act_kernel<TT, CC><<<grid, 128, 0, st>>>(a)
