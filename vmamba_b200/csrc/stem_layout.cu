@@ -5,15 +5,14 @@
 // pass and no separate LayerNorm / cast pass touches HBM:
 //
 //   stem_conv_norm_act   image (B, 3, H, W) -> conv 3x3 stride 2 (3 -> C0) + bias -> LayerNorm over C0 -> GELU
-//                        -> (B, H/2, W/2, C0).  The first layer has 27 inputs per output value: far
-//                        too thin for tensor cores, bound by the 4x larger output write; one thread
-//                        owns two neighbouring output pixels with all C0 channels in registers, so the
-//                        LayerNorm needs no communication and the pixel-major store is one run per pixel.
+//                        -> (B, H/2, W/2, C0).  16-bit images: 16 output pixels x C0 channels x 27 taps as
+//                        mma.sync steps, LayerNorm and GELU on the accumulators (stem_mma_kernel); fp32
+//                        images: a pair of lanes owns two neighbouring output pixels with the C0 channels
+//                        in registers (packed FMAs), one lane exchange for the LayerNorm.
 //   pixels_norm_to_planes (N, C) pixel-major rows + bias -> LayerNorm over C -> (C, N) planes (fp32 or 16-bit)
 //   planes_to_pixels      (C, N) fp32 planes (+ add + bias, optionally written back) -> (N, C) pixel-major 16-bit
 // N counts the pixels of the whole batch (b, h, w): pixel-major row n and element n of every plane
 // are the same pixel.
-#include <cstdlib>
 #include "activations.cuh"
 
 namespace ss2d {
@@ -313,8 +312,8 @@ static int launch_stem_mma(const StemArgs& a, int C0, cudaStream_t st) {
     const int vec_ok = (a.W % 8 == 0 && aligned_to(a.x, 16) && 9 * (a.W / 8) <= 3 * threads) ? 1 : 0;
     const size_t smem = (((size_t)9 * XP * sizeof(T) + 15) & ~(size_t)15) + 3 * (size_t)C0 * sizeof(float);
     const long long rows = (long long)a.B * a.Ho;
-    static const int gmul = getenv("SS2D_STEM_GRID") ? atoi(getenv("SS2D_STEM_GRID")) : 8;
-    const unsigned grid = (unsigned)(rows < 148 * gmul ? rows : 148 * gmul);
+    // persistent CTAs, four per SM's worth (224 x 224 images, batch 128: 2 or 4 per SM 164 us, 8: 169, 32: 184)
+    const unsigned grid = (unsigned)(rows < 148 * 4 ? rows : 148 * 4);
     if (C0 == 32) stem_mma_kernel<T, 32><<<grid, threads, smem, st>>>(a, (int)rows, vec_ok);
     else if (C0 == 48) stem_mma_kernel<T, 48><<<grid, threads, smem, st>>>(a, (int)rows, vec_ok);
     else stem_mma_kernel<T, 64><<<grid, threads, smem, st>>>(a, (int)rows, vec_ok);
@@ -338,8 +337,7 @@ int stem_conv_norm_act(const ss2d_stem_params* p, cudaStream_t st) {
     a.lnb = (const float*)p->ln_bias; a.y = p->y;
     a.B = (int)p->B; a.H = (int)p->H; a.W = (int)p->W; a.Ho = (int)((p->H + 1) / 2); a.Wo = (int)((p->W + 1) / 2);
     a.eps = p->eps;
-    static const int use_mma = getenv("SS2D_STEM_MMA") ? atoi(getenv("SS2D_STEM_MMA")) : 1;
-    if (use_mma && s == 2 && a.Wo <= 1024 && (long long)a.B * a.Ho <= 0x7fffffffLL && (p->C0 == 32 || p->C0 == 48 || p->C0 == 64)) {
+    if (s == 2 && a.Wo <= 1024 && (long long)a.B * a.Ho <= 0x7fffffffLL && (p->C0 == 32 || p->C0 == 48 || p->C0 == 64)) {
         if (p->dtype == SS2D_BF16) return launch_stem_mma<__nv_bfloat16>(a, (int)p->C0, st);
         return launch_stem_mma<__half>(a, (int)p->C0, st);
     }
