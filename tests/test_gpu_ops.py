@@ -637,3 +637,21 @@ def test_graphed_backbone_matches_eager(vb):
     fr = vb.GraphedBackbone(m, (4, 3, 64, 64), features=True)
     for a, b in zip(fr(imgs[0].cuda()), m.features(imgs[0].cuda())):
         assert torch.equal(a, b)
+
+
+@pytest.mark.gpu
+def test_vmamba_tiny_fp16_forward(vb):
+    """The fp16 instantiations of every kernel on the backbone path (tensor-core patch embedding and route
+    expansion included): VMamba-T at 224 x 224 in fp16 against the fp32 forward of the same library."""
+    import bench
+    from vmamba_b200.backbone import VSSMInfer
+    sd = bench.synthetic_state_dict(0)
+    old = (torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32)
+    torch.backends.cudnn.allow_tf32 = torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        img = torch.randn((4, 3, 224, 224), device="cuda", generator=torch.Generator(device="cuda").manual_seed(11))
+        ref = VSSMInfer.from_state_dict(sd, dtype=torch.float32)(img).float()
+        got = VSSMInfer.from_state_dict(sd, dtype=torch.float16)(img.half()).float()
+    finally:
+        torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = old
+    assert float((got - ref).abs().max() / ref.abs().max()) <= 5e-3
