@@ -266,6 +266,17 @@ static void launch_norm(NormArgs a, int pv, long long B, cudaStream_t st) {
     else if (D > 16 * 12 && pv > 2) pv = 2;
     a.nv = a.L / pv;
     a.items = (int)(B * a.nv);
+    // widths that are 16 per channel slice (128, 256, 512: the VMamba-B dims) get exact shapes of their own,
+    // so that the specialised forms apply to them as well
+    if (D == 8 * 16 || D == 16 * 16 || D == 32 * 16) {
+        if (pv > 2) pv = 2;
+        a.nv = a.L / pv;
+        a.items = (int)(B * a.nv);
+        if (D == 8 * 16) { if (pv == 2) launch_one<Tio, 8, 16, 2>(a, st); else launch_one<Tio, 8, 16, 1>(a, st); }
+        else if (D == 16 * 16) { if (pv == 2) launch_one<Tio, 16, 16, 2>(a, st); else launch_one<Tio, 16, 16, 1>(a, st); }
+        else { if (pv == 2) launch_one<Tio, 32, 16, 2>(a, st); else launch_one<Tio, 32, 16, 1>(a, st); }
+        return;
+    }
     if (D <= 8 * 12) {
         if (pv == 4) launch_one<Tio, 8, 12, 4>(a, st); else if (pv == 2) launch_one<Tio, 8, 12, 2>(a, st); else launch_one<Tio, 8, 12, 1>(a, st);
     } else if (D <= 16 * 12) {
