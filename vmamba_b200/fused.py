@@ -208,9 +208,9 @@ def ss2d_core(x: torch.Tensor, w: CoreWeights, *, with_norm: bool = True, out_dt
     out_dtype = out_dtype or (x.dtype if with_norm else torch.float32)
     with torch.autocast("cuda", enabled=False):
         if not fused_supported(x.shape, w.d_state) or (channel_major and not with_norm):
-            if channel_major:
-                y = _ss2d_core_unfused(x.transpose(0, 1).contiguous(), w, with_norm, out_dtype)
-                return y.transpose(0, 1).contiguous()
+            if channel_major:      # the LayerNorm kernel writes the channel-major result itself (no transposing copy)
+                y = _ss2d_core_unfused(x.transpose(0, 1).contiguous(), w, with_norm, out_dtype, out_channel_major=with_norm)
+                return y if with_norm else y.transpose(0, 1).contiguous()
             return _ss2d_core_unfused(x, w, with_norm, out_dtype)
         return scan_merge_norm(x, project(x, w, channel_major), w, with_norm=with_norm, out_dtype=out_dtype,
                                workspace=workspace, channel_major=channel_major)
@@ -223,7 +223,7 @@ def _vec_of(L: int) -> int:
     return v
 
 
-def _ss2d_core_unfused(x, w: CoreWeights, with_norm: bool, out_dtype):
+def _ss2d_core_unfused(x, w: CoreWeights, with_norm: bool, out_dtype, out_channel_major: bool = False):
     """Same mathematics through the operator-surface kernels (cross scan -> projections ->
     selective scan -> cross merge -> LayerNorm), the order of vmamba.py:1536-1571."""
     B, D, H, W = x.shape
@@ -232,12 +232,12 @@ def _ss2d_core_unfused(x, w: CoreWeights, with_norm: bool, out_dtype):
     xs = ops.cross_scan_fwd(x, 0)                                        # (B, K, D, L)
     x_dbl = torch.matmul(w.wx.view(K, C, D), xs)                         # (B, K, C, L)
     dts = torch.matmul(w.wdt, x_dbl[:, :, :R]).reshape(B, K * D, L)
-    Bs = x_dbl[:, :, R:R + N].contiguous()
-    Cs = x_dbl[:, :, R + N:].contiguous()
+    Bs = x_dbl[:, :, R:R + N]                                            # strided views: the scan takes batch / group / state strides
+    Cs = x_dbl[:, :, R + N:]
     ys = ops.selective_scan_fwd(xs.view(B, K * D, L), dts, w.A, Bs, Cs, w.Ds, w.dt_bias, True, True)
     y = ops.cross_merge_fwd(ys.view(B, K, D, H, W), 0).view(B, D, H, W)
     if with_norm:
-        y = ops.layer_norm_cf(y, w.ln_weight, w.ln_bias, w.eps, out_dtype)
+        return ops.layer_norm_cf(y, w.ln_weight, w.ln_bias, w.eps, out_dtype, out_channel_major=out_channel_major)
     return y.to(out_dtype)
 
 
