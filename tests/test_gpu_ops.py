@@ -467,6 +467,26 @@ def test_core_long_map_takes_surface_kernels(vb):
     assert O.max_rel_err(host(y), ref) <= TOL_F32
 
 
+@pytest.mark.parametrize("dtype,with_norm", [("f32", True), ("bf16", True), ("f32", False)])
+def test_core_long_map_channel_major(vb, dtype, with_norm):
+    """Long planes on a channel-major map (D, B, H, W): the operator kernels run on that layout directly (batch
+    folded into the plane count of CrossScan / CrossMerge, strided rows in the scan); three images, d_state 2."""
+    c = _core_case(3, 6, 96, 100, N=2, seed=22, Cmodel=40)
+    ref = O.ss2d_core(c["x"], c["wx"], c["wdt"], c["bias"], c["A_logs"], c["Ds"], c["lw"], c["lb"], d_state=2,
+                      dt_rank=c["R"]) if (with_norm and dtype == "f32") else None
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    w = vb.CoreWeights.build(dev(c["wx"]), dev(c["wdt"]), dev(c["bias"]), dev(c["A_logs"]), dev(c["Ds"]), dev(c["lw"]),
+                             dev(c["lb"]), d_state=c["N"], dt_rank=c["R"], dtype=td)
+    x = dev(c["x"], td)
+    want = vb.ss2d_core(x, w, with_norm=with_norm)                                   # batch-major path
+    got = vb.ss2d_core(x.transpose(0, 1).contiguous(), w, with_norm=with_norm, channel_major=True)
+    assert got.shape == (6, 3, 96, 100) and got.dtype == want.dtype
+    tol = TOL_F32 if dtype == "f32" else TOL_BF16
+    assert O.max_rel_err(host(got).transpose(1, 0, 2, 3), host(want)) <= tol
+    if ref is not None:
+        assert O.max_rel_err(host(got).transpose(1, 0, 2, 3), ref) <= tol
+
+
 @pytest.mark.parametrize("ssm_ratio,dims,hw", [(2.0, [16, 32, 64, 128], (64, 64)), (1.0, [24, 48, 96, 192], (64, 64)),
                                                (1.0, [64, 128, 256, 512], (96, 160)), (2.0, [96, 192, 384, 768], (64, 96))])
 def test_backbone_random_init_vs_oracle(vb, ssm_ratio, dims, hw):

@@ -208,9 +208,8 @@ def ss2d_core(x: torch.Tensor, w: CoreWeights, *, with_norm: bool = True, out_dt
     out_dtype = out_dtype or (x.dtype if with_norm else torch.float32)
     with torch.autocast("cuda", enabled=False):
         if not fused_supported(x.shape, w.d_state) or (channel_major and not with_norm):
-            if channel_major:      # the LayerNorm kernel writes the channel-major result itself (no transposing copy)
-                y = _ss2d_core_unfused(x.transpose(0, 1).contiguous(), w, with_norm, out_dtype, out_channel_major=with_norm)
-                return y if with_norm else y.transpose(0, 1).contiguous()
+            if channel_major:
+                return _ss2d_core_unfused_cm(x, w, with_norm, out_dtype)
             return _ss2d_core_unfused(x, w, with_norm, out_dtype)
         return scan_merge_norm(x, project(x, w, channel_major), w, with_norm=with_norm, out_dtype=out_dtype,
                                workspace=workspace, channel_major=channel_major)
@@ -238,6 +237,27 @@ def _ss2d_core_unfused(x, w: CoreWeights, with_norm: bool, out_dtype, out_channe
     y = ops.cross_merge_fwd(ys.view(B, K, D, H, W), 0).view(B, D, H, W)
     if with_norm:
         return ops.layer_norm_cf(y, w.ln_weight, w.ln_bias, w.eps, out_dtype, out_channel_major=out_channel_major)
+    return y.to(out_dtype)
+
+
+def _ss2d_core_unfused_cm(x, w: CoreWeights, with_norm: bool, out_dtype):
+    """The same chain on a channel-major map (D, B, H, W) without a layout copy: the batch is folded into the
+    plane count of CrossScan / CrossMerge (their routes stay per plane), each projection is one GEMM per route
+    over all images, and the selective scan reads and writes (route, channel, image) rows through its strides."""
+    D, B, H, W = x.shape
+    L, R, N = H * W, w.dt_rank, w.d_state
+    C = R + 2 * N
+    xs = ops.cross_scan_fwd(x.view(1, D * B, H, W), 0).view(K, D, B * L)         # route k: (D, B, L)
+    x_dbl = torch.bmm(w.wx.view(K, C, D), xs)                                    # (K, C, B*L)
+    dts = torch.bmm(w.wdt, x_dbl[:, :R])                                         # (K, D, B*L)
+    rows = lambda t: t.view(K * D, B, L).permute(1, 0, 2)                        # (B, K*D, L) view of (K, D, B, L)
+    bc = x_dbl.view(K, C, B, L).permute(2, 0, 1, 3)                              # (B, K, C, L) view
+    ys = torch.empty((K * D, B, L), device=x.device, dtype=torch.float32)
+    ops.selective_scan_fwd(rows(xs), rows(dts), w.A, bc[:, :, R:R + N], bc[:, :, R + N:], w.Ds, w.dt_bias, True, True,
+                           out=ys.permute(1, 0, 2))
+    y = ops.cross_merge_fwd(ys.view(1, K, D * B, H, W), 0).view(D, B, H, W)
+    if with_norm:
+        return ops.layer_norm_cf(y, w.ln_weight, w.ln_bias, w.eps, out_dtype, channel_major=True)
     return y.to(out_dtype)
 
 

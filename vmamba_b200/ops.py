@@ -46,13 +46,14 @@ def _ptr(t):
 # selective scan
 # --------------------------------------------------------------------------------------------
 def selective_scan_fwd(u, delta, A, B, C, D=None, delta_bias=None, delta_softplus=False, out_float=True,
-                       return_checkpoints=False):
+                       return_checkpoints=False, out=None):
     """out = selective scan of (u, delta, A, B, C [, D, delta_bias]); see include/ss2d_b200.h.
 
     u, delta: (batch, K*C, L); A: (K*C, N); B, C: (batch, K, N, L); D, delta_bias: (K*C,) fp32.
     Output fp32 if `out_float` (the reference's "oflex") else u.dtype.  With `return_checkpoints` also the fp32
     states in front of every 128th element, (batch, K*C, ceil(L/128), N), which `selective_scan_bwd` accepts
-    instead of recomputing them.
+    instead of recomputing them.  `out`: optional result tensor of that shape and type (any batch / row strides,
+    elements of a row contiguous), e.g. a permuted view, so that the result lands in the caller's layout.
     """
     _require_cuda(u, delta, A, B, C, D, delta_bias)
     if u.dim() != 3 or delta.dim() != 3 or delta.shape[0] != u.shape[0] or delta.shape[2] != u.shape[2] \
@@ -84,7 +85,11 @@ def selective_scan_fwd(u, delta, A, B, C, D=None, delta_bias=None, delta_softplu
     ratio = dim // delta.shape[1]        # channels sharing one delta row (selective_scan_oflex.cpp:59)
     if delta_bias is not None and delta_bias.numel() != delta.shape[1]:
         raise RuntimeError("delta_bias must have one element per delta row")
-    out = torch.empty((batch, dim, L), device=u.device, dtype=torch.float32 if out_float else u.dtype)
+    out_dtype = torch.float32 if out_float else u.dtype
+    if out is None:
+        out = torch.empty((batch, dim, L), device=u.device, dtype=out_dtype)
+    elif tuple(out.shape) != (batch, dim, L) or out.dtype != out_dtype or out.stride(-1) != 1 or out.device != u.device:
+        raise RuntimeError("out must be (batch, dim, L) of the result type on u's device with contiguous rows")
     p = ScanParams()
     p.u, p.delta, p.A, p.B, p.C, p.D, p.delta_bias, p.out = (_ptr(t) for t in (u, delta, A, B, C, D, delta_bias, out))
     p.in_dtype, p.out_dtype = dtype_code(u), dtype_code(out)
