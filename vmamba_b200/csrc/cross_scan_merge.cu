@@ -45,31 +45,35 @@ struct CrossArgs {
     RouteMap route[4];
 };
 
+// Index arithmetic inside a plane is 32-bit (the callers bound H * W and the tile count by 2^31): with 64-bit
+// divisions and products the kernels issued about 200 instructions per element and were bound by that.
 template <typename T>
 __global__ void __launch_bounds__(kTile * kRowsPerPass) cross_scan_kernel(const CrossArgs a) {
     __shared__ T tile[kTile][kTile + 1];
-    const long long t = blockIdx.x;
-    const long long tw = t % a.tiles_w, th = (t / a.tiles_w) % a.tiles_h, plane = t / (a.tiles_w * a.tiles_h);
-    const long long b = plane / a.C, c = plane % a.C, L = a.H * a.W;
-    const T* __restrict__ x = (const T*)a.in + plane * L;
-    const long long h0 = th * kTile, w0 = tw * kTile;
+    const unsigned t = blockIdx.x, tiles_w = (unsigned)a.tiles_w, tiles_h = (unsigned)a.tiles_h, C = (unsigned)a.C;
+    const unsigned tw = t % tiles_w, rest = t / tiles_w, th = rest % tiles_h, plane = rest / tiles_h;
+    const unsigned b = plane / C, c = plane - b * C;
+    const int H = (int)a.H, W = (int)a.W, L = H * W;
+    const T* __restrict__ x = (const T*)a.in + (long long)plane * L;
+    const int h0 = (int)th * kTile, w0 = (int)tw * kTile;
     const int tx = threadIdx.x, ty = threadIdx.y;
 #pragma unroll
     for (int j = 0; j < kTile; j += kRowsPerPass) {
-        const long long h = h0 + ty + j, w = w0 + tx;
-        if (h < a.H && w < a.W) tile[ty + j][tx] = x[h * a.W + w];
+        const int h = h0 + ty + j, w = w0 + tx;
+        if (h < H && w < W) tile[ty + j][tx] = x[h * W + w];
     }
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const RouteMap m = a.route[k];
-        T* __restrict__ y = (T*)a.out + ((b * 4 + k) * a.C + c) * L;
+        const int base = (int)a.route[k].base, sh = (int)a.route[k].sh, sw = (int)a.route[k].sw;
+        const bool col_like = a.route[k].col_like != 0;
+        T* __restrict__ y = (T*)a.out + ((long long)(b * 4 + k) * C + c) * L;
 #pragma unroll
         for (int j = 0; j < kTile; j += kRowsPerPass) {
             // row-like: thread x index runs along w; column-like: along h (transposed read)
-            const int lh = m.col_like ? tx : ty + j, lw = m.col_like ? ty + j : tx;
-            const long long h = h0 + lh, w = w0 + lw;
-            if (h < a.H && w < a.W) y[m.base + m.sh * h + m.sw * w] = tile[lh][lw];
+            const int lh = col_like ? tx : ty + j, lw = col_like ? ty + j : tx;
+            const int h = h0 + lh, w = w0 + lw;
+            if (h < H && w < W) y[base + sh * h + sw * w] = tile[lh][lw];
         }
     }
 }
@@ -80,34 +84,36 @@ template <typename T> __device__ __forceinline__ T add_t(T x, T y) { return from
 template <typename T>
 __global__ void __launch_bounds__(kTile * kRowsPerPass) cross_merge_kernel(const CrossArgs a, const int scans) {
     __shared__ T tile[4][kTile][kTile + 1];
-    const long long t = blockIdx.x;
-    const long long tw = t % a.tiles_w, th = (t / a.tiles_w) % a.tiles_h, plane = t / (a.tiles_w * a.tiles_h);
-    const long long b = plane / a.C, c = plane % a.C, L = a.H * a.W;
-    const long long h0 = th * kTile, w0 = tw * kTile;
+    const unsigned t = blockIdx.x, tiles_w = (unsigned)a.tiles_w, tiles_h = (unsigned)a.tiles_h, C = (unsigned)a.C;
+    const unsigned tw = t % tiles_w, rest = t / tiles_w, th = rest % tiles_h, plane = rest / tiles_h;
+    const unsigned b = plane / C, c = plane - b * C;
+    const int H = (int)a.H, W = (int)a.W, L = H * W;
+    const int h0 = (int)th * kTile, w0 = (int)tw * kTile;
     const int tx = threadIdx.x, ty = threadIdx.y;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const RouteMap m = a.route[k];
-        const T* __restrict__ ys = (const T*)a.in + ((b * 4 + k) * a.C + c) * L;
+        const int base = (int)a.route[k].base, sh = (int)a.route[k].sh, sw = (int)a.route[k].sw;
+        const bool col_like = a.route[k].col_like != 0;
+        const T* __restrict__ ys = (const T*)a.in + ((long long)(b * 4 + k) * C + c) * L;
 #pragma unroll
         for (int j = 0; j < kTile; j += kRowsPerPass) {
-            const int lh = m.col_like ? tx : ty + j, lw = m.col_like ? ty + j : tx;
-            const long long h = h0 + lh, w = w0 + lw;
-            if (h < a.H && w < a.W) tile[k][lh][lw] = ys[m.base + m.sh * h + m.sw * w];
+            const int lh = col_like ? tx : ty + j, lw = col_like ? ty + j : tx;
+            const int h = h0 + lh, w = w0 + lw;
+            if (h < H && w < W) tile[k][lh][lw] = ys[base + sh * h + sw * w];
         }
     }
     __syncthreads();
-    T* __restrict__ y = (T*)a.out + plane * L;
+    T* __restrict__ y = (T*)a.out + (long long)plane * L;
 #pragma unroll
     for (int j = 0; j < kTile; j += kRowsPerPass) {
-        const long long h = h0 + ty + j, w = w0 + tx;
-        if (h < a.H && w < a.W) {
+        const int h = h0 + ty + j, w = w0 + tx;
+        if (h < H && w < W) {
             const T v0 = tile[0][ty + j][tx], v1 = tile[1][ty + j][tx], v2 = tile[2][ty + j][tx], v3 = tile[3][ty + j][tx];
             T r;
             if (scans == 0 || scans == 2) r = add_t(add_t(v0, v2), add_t(v1, v3));   // (y0+y2) + (y1+y3)
             else if (scans == 3) r = add_t(add_t(add_t(v0, v1), v2), v3);            // ((y0+y1)+y2)+y3
             else r = from_f<T>(((to_f<T>(v0) + to_f<T>(v1)) + to_f<T>(v2)) + to_f<T>(v3));   // one reduction, rounded once
-            y[h * a.W + w] = r;
+            y[h * W + w] = r;
         }
     }
 }
@@ -267,6 +273,7 @@ static int fill_args(const ss2d_cross_params* p, CrossArgs& a) {
     if (!dtype_ok(p->dtype)) return SS2D_EINVAL_DTYPE;
     if (p->scans < 0 || p->scans > 3) return SS2D_ENOTSUP;
     if (p->B <= 0 || p->C <= 0 || p->H <= 0 || p->W <= 0) return SS2D_EINVAL_SHAPE;
+    if (p->H * p->W > 0x3fffffffLL || p->C > 0x7fffffffLL || p->B * p->C > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;   // 32-bit indices inside a plane
     const size_t s = dtype_size(p->dtype);
     if (!aligned_to(p->in, s) || !aligned_to(p->out, s)) return SS2D_EINVAL_ALIGN;
     a.in = p->in; a.out = p->out;
