@@ -135,8 +135,12 @@ struct PlaneArgs {
 
 __device__ __forceinline__ int mdiv_u(int n, unsigned magic) { return magic ? (int)__umulhi((unsigned)n, magic) : n; }
 
+// the same map with 32-bit fields (positions inside a plane fit): keeps 64-bit products out of the inner loops
+struct RouteMapI { int base, sh, sw, col_like; };
+__device__ __forceinline__ RouteMapI narrow(const RouteMap& m) { return RouteMapI{(int)m.base, (int)m.sh, (int)m.sw, (int)m.col_like}; }
+
 // source position (flat h*W + w) read by step l of a route
-__device__ __forceinline__ int route_src(const RouteMap& m, int l, int H, int W, unsigned magic_H) {
+__device__ __forceinline__ int route_src(const RouteMapI& m, int l, int H, int W, unsigned magic_H) {
     if (!m.col_like) return m.sw > 0 ? l : (int)m.base - l;            // row-major, forward or reversed
     // l = base + sh*h + sw*w with |sh| = 1, |sw| = H: recover (h, w)
     const int t = (int)(m.sw > 0 ? 0 : -m.sw * (W - 1));                // offset so that the w term is non-negative
@@ -160,16 +164,16 @@ __global__ void __launch_bounds__(256) cross_scan_plane_kernel(const PlaneArgs a
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const RouteMap m = a.route[k];
+        const RouteMapI m = narrow(a.route[k]);
         for (int i = threadIdx.x; i < n; i += blockDim.x) {
             const int pl = mdiv_u(i, a.magic_nvec), l0 = (i - pl * a.nvec) * PV;
-            const long long plane = plane0 + pl;
-            const long long b = plane / a.C, c = plane - b * a.C;
+            const unsigned plane = (unsigned)plane0 + (unsigned)pl;            // B * C < 2^31 (checked by the caller)
+            const unsigned b = plane / (unsigned)a.C, c = plane - b * (unsigned)a.C;
             typename Vec<T, PV>::Raw r;
             T* e = reinterpret_cast<T*>(&r);
 #pragma unroll
             for (int j = 0; j < PV; ++j) e[j] = sm[pl * L + route_src(m, l0 + j, a.H, a.W, a.magic_H)];
-            Vec<T, PV>::store_raw((T*)a.out + ((b * 4 + k) * a.C + c) * L + l0, r);
+            Vec<T, PV>::store_raw((T*)a.out + ((long long)(b * 4 + k) * a.C + c) * L + l0, r);
         }
     }
 }
@@ -185,14 +189,17 @@ __global__ void __launch_bounds__(256) cross_merge_plane_kernel(const PlaneArgs 
     for (int k = 0; k < 4; ++k) {
         for (int i = threadIdx.x; i < n; i += blockDim.x) {
             const int pl = mdiv_u(i, a.magic_nvec), l0 = (i - pl * a.nvec) * PV;
-            const long long plane = plane0 + pl;
-            const long long b = plane / a.C, c = plane - b * a.C;
-            Vec<T, PV>::store_raw(sm + ((size_t)k * a.PP + pl) * L + l0,
-                                  Vec<T, PV>::load_raw((const T*)a.in + ((b * 4 + k) * a.C + c) * L + l0));
+            const unsigned plane = (unsigned)plane0 + (unsigned)pl;
+            const unsigned b = plane / (unsigned)a.C, c = plane - b * (unsigned)a.C;
+            Vec<T, PV>::store_raw(sm + (k * a.PP + pl) * L + l0,
+                                  Vec<T, PV>::load_raw((const T*)a.in + ((long long)(b * 4 + k) * a.C + c) * L + l0));
         }
     }
     __syncthreads();
     T* __restrict__ y = (T*)a.out + plane0 * L;
+    RouteMapI rm[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) rm[k] = narrow(a.route[k]);
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const int pl = mdiv_u(i, a.magic_nvec), p0 = (i - pl * a.nvec) * PV;
         typename Vec<T, PV>::Raw r;
@@ -204,8 +211,7 @@ __global__ void __launch_bounds__(256) cross_merge_plane_kernel(const PlaneArgs 
             T v[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const RouteMap& m = a.route[k];
-                v[k] = sm[((size_t)k * a.PP + pl) * L + (int)(m.base + m.sh * h + m.sw * w)];
+                v[k] = sm[(k * a.PP + pl) * L + rm[k].base + rm[k].sh * h + rm[k].sw * w];
             }
             if (scans == 0 || scans == 2) e[j] = add_t(add_t(v[0], v[2]), add_t(v[1], v[3]));
             else if (scans == 3) e[j] = add_t(add_t(add_t(v[0], v[1]), v[2]), v[3]);
