@@ -10,7 +10,8 @@
 namespace ss2d {
 
 constexpr int kTile = 32;
-constexpr int kRowsPerPass = 4;   // CTA = 32 x 4 threads, eight passes per tile (8 x: 143 / 250 us for CrossScan / CrossMerge of 512 planes of 256 x 256, 4 x: 131 / 226)
+constexpr int kRowsPerPass = 4;   // CrossScan tile kernel: CTA = 32 x 4 threads, eight passes per tile
+constexpr int kMergeRows = 2;     // CrossMerge tile kernel: CTA = 32 x 2 threads (512 planes of 256 x 256: scan 143 / 131 / 142 us, merge 250 / 226 / 197 us with 8 / 4 / 2 rows)
 
 struct RouteMap {
     // l = base + sh * h + sw * w ; col_like: |sh| == 1 (contiguous along h)
@@ -82,7 +83,7 @@ __global__ void __launch_bounds__(kTile * kRowsPerPass) cross_scan_kernel(const 
 template <typename T> __device__ __forceinline__ T add_t(T x, T y) { return from_f<T>(to_f<T>(x) + to_f<T>(y)); }
 
 template <typename T>
-__global__ void __launch_bounds__(kTile * kRowsPerPass) cross_merge_kernel(const CrossArgs a, const int scans) {
+__global__ void __launch_bounds__(kTile * kMergeRows) cross_merge_kernel(const CrossArgs a, const int scans) {
     __shared__ T tile[4][kTile][kTile + 1];
     const unsigned t = blockIdx.x, tiles_w = (unsigned)a.tiles_w, tiles_h = (unsigned)a.tiles_h, C = (unsigned)a.C;
     const unsigned tw = t % tiles_w, rest = t / tiles_w, th = rest % tiles_h, plane = rest / tiles_h;
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(kTile * kRowsPerPass) cross_merge_kernel(const
         const bool col_like = a.route[k].col_like != 0;
         const T* __restrict__ ys = (const T*)a.in + ((long long)(b * 4 + k) * C + c) * L;
 #pragma unroll
-        for (int j = 0; j < kTile; j += kRowsPerPass) {
+        for (int j = 0; j < kTile; j += kMergeRows) {
             const int lh = col_like ? tx : ty + j, lw = col_like ? ty + j : tx;
             const int h = h0 + lh, w = w0 + lw;
             if (h < H && w < W) tile[k][lh][lw] = ys[base + sh * h + sw * w];
@@ -105,7 +106,7 @@ __global__ void __launch_bounds__(kTile * kRowsPerPass) cross_merge_kernel(const
     __syncthreads();
     T* __restrict__ y = (T*)a.out + (long long)plane * L;
 #pragma unroll
-    for (int j = 0; j < kTile; j += kRowsPerPass) {
+    for (int j = 0; j < kTile; j += kMergeRows) {
         const int h = h0 + ty + j, w = w0 + tx;
         if (h < H && w < W) {
             const T v0 = tile[0][ty + j][tx], v1 = tile[1][ty + j][tx], v2 = tile[2][ty + j][tx], v3 = tile[3][ty + j][tx];
@@ -318,7 +319,7 @@ int cross_merge(const ss2d_cross_params* p, cudaStream_t st) {
         else if (p->dtype == SS2D_BF16) { if (plan_plane<__nv_bfloat16>(p, 4, pa, pv, smem)) return merge_plane_v<__nv_bfloat16>(pa, p->scans, pv, smem, st); }
         else if (plan_plane<__half>(p, 4, pa, pv, smem)) return merge_plane_v<__half>(pa, p->scans, pv, smem, st);
     }
-    const dim3 blk(kTile, kRowsPerPass);
+    const dim3 blk(kTile, kMergeRows);
     if (p->dtype == SS2D_F32) cross_merge_kernel<float><<<(unsigned)a.n_tiles, blk, 0, st>>>(a, p->scans);
     else if (p->dtype == SS2D_BF16) cross_merge_kernel<__nv_bfloat16><<<(unsigned)a.n_tiles, blk, 0, st>>>(a, p->scans);
     else cross_merge_kernel<__half><<<(unsigned)a.n_tiles, blk, 0, st>>>(a, p->scans);
