@@ -201,6 +201,12 @@ typedef struct ss2d_core_params {
 
 int64_t ss2d_core_workspace_bytes(const ss2d_core_params *p);
 int ss2d_core_fwd(const ss2d_core_params *p, void *cuda_stream);
+/* SS2D_OK when ss2d_core_fwd takes this problem itself (d_state 1, a plane that fits one CTA with the
+ * given alignments and strides), otherwise the status ss2d_core_fwd would return before launching
+ * anything (SS2D_ENOTSUP: use the operator-surface kernels).  Reads sizes, dtypes, strides and the
+ * alignment of the pointers only; the workspace fields are ignored and nothing is dereferenced.  Takes the
+ * place of the shape tests of selective_scan_fwd (selective_scan_oflex.cpp:152-204) for the fused call. */
+int ss2d_core_supported(const ss2d_core_params *p);
 
 /* ------------------------------------------------------------------------------------
  * Elementwise producers around the core, channel-first (B, D, H, W) contiguous maps of `dtype`.
@@ -306,7 +312,8 @@ typedef struct ss2d_norm_params {
     int32_t io_dtype;
     float eps;
     int32_t skip_norm;      /* 1: out = s converted to io_dtype, no normalisation (fused add, cast, layout change) */
-    int32_t reserved0;
+    int32_t descending;     /* 1: the map is walked from its last image to its first.  Same result; for an `in` that the
+                             * kernel before wrote front to back and that is larger than L2, the end is still cached */
 } ss2d_norm_params;
 
 int ss2d_layer_norm_cf(const ss2d_norm_params *p, void *cuda_stream);

@@ -84,7 +84,7 @@ class NormParams(ctypes.Structure):
     _fields_ = [("in_", _vp), ("add", _vp), ("add_bias", _vp), ("sum_out", _vp), ("weight", _vp), ("bias", _vp),
                 ("out", _vp), ("B", _i64), ("D", _i64), ("L", _i64), ("batch_stride", _i64), ("channel_stride", _i64),
                 ("out_batch_stride", _i64), ("out_channel_stride", _i64), ("io_dtype", _i32), ("eps", _f32),
-                ("skip_norm", _i32), ("reserved0", _i32)]
+                ("skip_norm", _i32), ("descending", _i32)]
 
 
 class StemParams(ctypes.Structure):
@@ -110,6 +110,7 @@ EXPORTS = {
     "ss2d_cross_merge_ex": (ctypes.c_int, [ctypes.POINTER(CrossExParams), _vp]),
     "ss2d_core_workspace_bytes": (_i64, [ctypes.POINTER(CoreParams)]),
     "ss2d_core_fwd": (ctypes.c_int, [ctypes.POINTER(CoreParams), _vp]),
+    "ss2d_core_supported": (ctypes.c_int, [ctypes.POINTER(CoreParams)]),
     "ss2d_core_fwd_static": (ctypes.c_int, [ctypes.POINTER(CoreParams), _vp]),
     "ss2d_core_static_capacity": (_i64, []),
     "ss2d_layer_norm_cf": (ctypes.c_int, [ctypes.POINTER(NormParams), _vp]),

@@ -14,6 +14,7 @@ int cross_merge_ex(const ss2d_cross_ex_params* p, cudaStream_t st);
 int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st);
 long long core_workspace_bytes(const ss2d_core_params* p);
 int core_fwd(const ss2d_core_params* p, cudaStream_t st);
+int core_supported(const ss2d_core_params* p);
 int core_fwd_static(const ss2d_core_params* p, cudaStream_t st);
 long long core_static_capacity();
 int route_expand(const ss2d_expand_params* p, cudaStream_t st);
@@ -45,6 +46,7 @@ int ss2d_cross_merge_ex(const ss2d_cross_ex_params* p, void* stream) { return ss
 int ss2d_layer_norm_cf(const ss2d_norm_params* p, void* stream) { return ss2d::layer_norm_cf(p, (cudaStream_t)stream); }
 int64_t ss2d_core_workspace_bytes(const ss2d_core_params* p) { return ss2d::core_workspace_bytes(p); }
 int ss2d_core_fwd(const ss2d_core_params* p, void* stream) { return ss2d::core_fwd(p, (cudaStream_t)stream); }
+int ss2d_core_supported(const ss2d_core_params* p) { return ss2d::core_supported(p); }
 int ss2d_core_fwd_static(const ss2d_core_params* p, void* stream) { return ss2d::core_fwd_static(p, (cudaStream_t)stream); }
 int64_t ss2d_core_static_capacity(void) { return ss2d::core_static_capacity(); }
 

@@ -21,9 +21,13 @@
 // by all channels of an image and stay in L1/L2.  They are read in the activation type (the type
 // the projection produced them in): every thread re-reads them for every plane, and with 16-bit
 // elements a warp's load is one contiguous 512-byte run instead of two half-used 1 KB runs.
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
+#include "core_routes.cuh"
 
 namespace ss2d {
 
@@ -384,6 +388,28 @@ __global__ void __launch_bounds__(MAXT, MINB) core_plane_kernel(const CoreArgs a
     }
 }
 
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device): the attribute only ever has to grow.
+static cudaError_t ensure_dynamic_smem(const void* kern, size_t bytes) {
+    struct Entry { const void* kern; int dev; size_t bytes; };
+    static std::mutex mu;
+    static std::vector<Entry> seen;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(mu);
+    for (Entry& en : seen)
+        if (en.kern == kern && en.dev == dev) {
+            if (en.bytes >= bytes) return cudaSuccess;
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+            if (e == cudaSuccess) en.bytes = bytes;
+            return e;
+        }
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) seen.push_back(Entry{kern, dev, bytes});
+    return e;
+}
+
 struct PlaneConfig { int vec, G, PP, threads, Wp, npl; size_t smem; };
 
 static bool plan_planes(const ss2d_core_params* p, PlaneConfig& c) {
@@ -430,12 +456,12 @@ static int launch_core_n(const CoreArgs& a, const PlaneConfig& c, unsigned grid,
     cudaError_t e;
     if (c.threads <= 448) {           // 72 registers per thread at two CTAs per SM
         auto kern = core_plane_kernel<T, VEC, NPL, 448, 2>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem);
+        e = ensure_dynamic_smem((const void*)kern, c.smem);
         if (e != cudaSuccess) return SS2D_ECUDA;
         kern<<<grid, c.threads, c.smem, st>>>(a);
     } else {
         auto kern = core_plane_kernel<T, VEC, NPL, 1024, 1>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem);
+        e = ensure_dynamic_smem((const void*)kern, c.smem);
         if (e != cudaSuccess) return SS2D_ECUDA;
         kern<<<grid, c.threads, c.smem, st>>>(a);
     }
@@ -460,6 +486,92 @@ static int launch_core_v(const CoreArgs& a, const PlaneConfig& c, unsigned grid,
         case 2: return launch_core_t<T, 2>(a, c, grid, st);
         default: return launch_core_t<T, 1>(a, c, grid, st);
     }
+}
+
+
+// ---- route-stream kernel (core_routes.cuh): which planes it takes, and its launch -----------------------------
+struct RoutePlan { int S, SV; size_t smem; };
+
+// 0: choose by shape (default), 1: always the plane kernel, 2: the route-stream kernel wherever it applies.
+// Read once from SS2D_CORE_KERNEL = plane | routes (a switch for measurements; both kernels pass the same tests).
+static int core_kernel_choice() {
+    static const int choice = [] {
+        const char* v = std::getenv("SS2D_CORE_KERNEL");
+        if (!v) return 0;
+        if (!std::strcmp(v, "plane")) return 1;
+        if (!std::strcmp(v, "routes")) return 2;
+        return 0;
+    }();
+    return choice;
+}
+
+static bool plan_routes(const ss2d_core_params* p, RoutePlan& r) {
+    const long long L = p->H * p->W;
+    const size_t s = dtype_size(p->act_dtype);
+    if (L % 4 != 0 || p->W % 4 != 0) return false;
+    auto el = [&](const void* q) { return (long long)(reinterpret_cast<uintptr_t>(q) / s); };
+    int vec = 8;
+    auto fit = [&](long long x) { if (x < 0) x = -x; while (vec > 1 && (x % vec) != 0) vec >>= 1; };
+    fit(L); fit(el(p->x)); fit(p->x_batch_stride); fit(p->x_channel_stride);
+    for (int k = 0; k < 4; ++k) {
+        fit(el(p->delta[k]));
+        fit(el(p->Bm[k])); fit(el(p->Cm[k]));
+        fit(p->delta_batch_stride[k]); fit(p->bc_batch_stride[k]); fit(p->delta_channel_stride[k]);
+    }
+    if (vec < 4) return false;
+    r.S = vec;
+    r.SV = (vec == 8 && p->W % 8 == 0) ? 8 : 4;
+    r.smem = (size_t)L * (8 + s);
+    return r.smem <= 227 * 1024;
+}
+
+template <typename T, int S, int SV, int MINB, int kRoll>
+static int launch_routes_k(const RouteArgs& a, const RoutePlan& r, unsigned grid, cudaStream_t st) {
+    auto kern = core_route_kernel<T, S, SV, MINB, kRoll>;
+    if (ensure_dynamic_smem((const void*)kern, r.smem) != cudaSuccess) return SS2D_ECUDA;
+    kern<<<grid, 128, r.smem, st>>>(a);
+    count_launch();
+    return check_launch();
+}
+
+template <typename T, int MINB>
+static int launch_routes_t(const RouteArgs& a, const RoutePlan& r, unsigned grid, cudaStream_t st) {
+    if (r.S == 8) return r.SV == 8 ? launch_routes_k<T, 8, 8, MINB, 0>(a, r, grid, st) : launch_routes_k<T, 8, 4, MINB, 0>(a, r, grid, st);
+    return launch_routes_k<T, 4, 4, MINB, 0>(a, r, grid, st);
+}
+
+static int run_routes(const ss2d_core_params* p, const RoutePlan& r, float* merged, cudaStream_t st) {
+    RouteArgs a;
+    a.x = p->x;
+    for (int k = 0; k < 4; ++k) {
+        a.delta[k] = p->delta[k]; a.Bm[k] = p->Bm[k]; a.Cm[k] = p->Cm[k];
+        a.d_bs[k] = p->delta_batch_stride[k]; a.bc_bs[k] = p->bc_batch_stride[k];
+        a.d_cs[k] = p->delta_channel_stride[k] ? p->delta_channel_stride[k] : p->H * p->W;
+    }
+    a.A = (const float*)p->A; a.Dskip = (const float*)p->Dskip; a.bias = (const float*)p->delta_bias;
+    a.merged = merged;
+    a.x_bs = p->x_batch_stride ? p->x_batch_stride : p->D * p->H * p->W;
+    a.x_cs = p->x_channel_stride ? p->x_channel_stride : p->H * p->W;
+    a.B = (int)p->B; a.D = (int)p->D; a.H = (int)p->H; a.W = (int)p->W; a.L = (int)(p->H * p->W);
+    a.magic_H = p->H > 1 ? (unsigned)(((1ULL << 32) + (unsigned long long)p->H - 1) / (unsigned long long)p->H) : 0;
+    const long long grid = p->B * p->D;
+    if (grid > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
+    if (p->act_dtype == SS2D_F32) return launch_routes_t<float, 4>(a, r, (unsigned)grid, st);
+    if (p->act_dtype == SS2D_BF16) return launch_routes_t<__nv_bfloat16, 7>(a, r, (unsigned)grid, st);
+    return launch_routes_t<__half, 7>(a, r, (unsigned)grid, st);
+}
+
+// The scan + merge kernel for this call.  Measured on B200 (bf16, scan + merge alone): the route-stream kernel wins
+// where its chunks are well filled and seven CTAs fit an SM (56 x 56: 0.223 against 0.267 ms at batch 128 x 96
+// channels; 32 x 32: 0.106 against 0.112 ms), and loses where a quarter of the last chunk's lanes idle (28 x 28:
+// 0.148 against 0.141 ms) or shared memory leaves five CTAs per SM (64 x 64: 0.231 against 0.219 ms).
+static bool use_routes(const ss2d_core_params* p, RoutePlan& r) {
+    const int choice = core_kernel_choice();
+    if (choice == 1 || !plan_routes(p, r)) return false;
+    if (choice == 2) return true;
+    const long long L = p->H * p->W, chunk = 32 * r.S;
+    const long long chunks = (L + chunk - 1) / chunk;
+    return r.S == 8 && 10 * L >= 9 * chunks * chunk && r.smem <= 32 * 1024;
 }
 
 int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st);
@@ -497,8 +609,14 @@ long long core_workspace_bytes(const ss2d_core_params* p) {
     return (long long)(p->B * p->D * p->H * p->W) * 4;
 }
 
-// Scan + merge kernel into `merged`, then (with_norm) the LayerNorm kernel into p->y.  Arguments validated by the caller.
-static int run_core(const ss2d_core_params* p, const PlaneConfig& c, float* merged, cudaStream_t st) {
+struct CorePlan { bool routes; RoutePlan r; PlaneConfig c; };
+
+static bool plan_core(const ss2d_core_params* p, CorePlan& plan) {
+    plan.routes = use_routes(p, plan.r);
+    return plan.routes || plan_planes(p, plan.c);
+}
+
+static int run_planes(const ss2d_core_params* p, const PlaneConfig& c, float* merged, cudaStream_t st) {
     CoreArgs a;
     a.x = p->x;
     for (int k = 0; k < 4; ++k) {
@@ -517,38 +635,58 @@ static int run_core(const ss2d_core_params* p, const PlaneConfig& c, float* merg
     a.groups_per_image = (int)((p->D + c.PP - 1) / c.PP);
     const long long grid = (long long)p->B * a.groups_per_image;
     if (grid > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
-    int r;
-    if (p->act_dtype == SS2D_F32) r = launch_core_v<float>(a, c, (unsigned)grid, st);
-    else if (p->act_dtype == SS2D_BF16) r = launch_core_v<__nv_bfloat16>(a, c, (unsigned)grid, st);
-    else r = launch_core_v<__half>(a, c, (unsigned)grid, st);
+    if (p->act_dtype == SS2D_F32) return launch_core_v<float>(a, c, (unsigned)grid, st);
+    if (p->act_dtype == SS2D_BF16) return launch_core_v<__nv_bfloat16>(a, c, (unsigned)grid, st);
+    return launch_core_v<__half>(a, c, (unsigned)grid, st);
+}
+
+// Scan + merge kernel into `merged`, then (with_norm) the LayerNorm kernel into p->y.  Arguments validated by the caller.
+static int run_core(const ss2d_core_params* p, const CorePlan& plan, float* merged, cudaStream_t st) {
+    const int r = plan.routes ? run_routes(p, plan.r, merged, st) : run_planes(p, plan.c, merged, st);
     if (r != SS2D_OK) return r;
     if (!p->with_norm) return SS2D_OK;
     ss2d_norm_params n = {};
     n.in = merged; n.weight = p->ln_weight; n.bias = p->ln_bias; n.out = p->y;
     n.B = p->B; n.D = p->D; n.L = p->H * p->W; n.io_dtype = p->y_dtype; n.eps = p->ln_eps;
     n.out_batch_stride = p->y_batch_stride; n.out_channel_stride = p->y_channel_stride;
+    n.descending = 1;         // the scan kernel wrote `merged` front to back: its end is what L2 still holds
     return layer_norm_cf(&n, st);
 }
 
-int core_fwd(const ss2d_core_params* p, cudaStream_t st) {
+// Checks shared by the two entry points; on success `plan` is filled and `need` holds the scratch bytes (0: the
+// merged map goes straight to p->y).
+static int prepare_core(const ss2d_core_params* p, CorePlan& plan, long long& need) {
     const int rc = validate_core(p);
     if (rc != SS2D_OK) return rc;
     if (p->N != 1) return SS2D_ENOTSUP;          // d_state > 1 runs through the operator-surface kernels
     if (!p->with_norm && p->y_dtype != SS2D_F32) return SS2D_ENOTSUP;
-    PlaneConfig c;
-    if (!plan_planes(p, c)) return SS2D_ENOTSUP;  // plane too long for one CTA
-    const long long need = core_workspace_bytes(p);
+    if (!plan_core(p, plan)) return SS2D_ENOTSUP;  // plane too long for one CTA
+    need = core_workspace_bytes(p);
+    if (need == 0) {
+        if (!aligned_to(p->y, 16)) return SS2D_EINVAL_ALIGN;
+        if (p->y_batch_stride || p->y_channel_stride) return SS2D_ENOTSUP;     // the un-normalised fp32 map is written dense
+    }
+    return SS2D_OK;
+}
+
+int core_supported(const ss2d_core_params* p) {
+    CorePlan plan;
+    long long need = 0;
+    return prepare_core(p, plan, need);
+}
+
+int core_fwd(const ss2d_core_params* p, cudaStream_t st) {
+    CorePlan plan;
+    long long need = 0;
+    const int rc = prepare_core(p, plan, need);
+    if (rc != SS2D_OK) return rc;
     float* merged = (float*)p->y;
     if (need > 0) {
         if (!p->workspace || p->workspace_bytes < need) return SS2D_EWORKSPACE;
         if (!aligned_to(p->workspace, 256)) return SS2D_EINVAL_ALIGN;
         merged = (float*)p->workspace;
-    } else if (!aligned_to(p->y, 16)) {
-        return SS2D_EINVAL_ALIGN;
-    } else if (p->y_batch_stride || p->y_channel_stride) {
-        return SS2D_ENOTSUP;     // the un-normalised fp32 map is written dense
     }
-    return run_core(p, c, merged, st);
+    return run_core(p, plan, merged, st);
 }
 
 
@@ -601,22 +739,17 @@ static int static_scratch_for_current_device(float** out) {
 long long core_static_capacity() { return kStaticScratchFloats; }
 
 int core_fwd_static(const ss2d_core_params* p, cudaStream_t st) {
-    const int rc = validate_core(p);
+    CorePlan plan;
+    long long need = 0;
+    const int rc = prepare_core(p, plan, need);
     if (rc != SS2D_OK) return rc;
-    if (p->N != 1) return SS2D_ENOTSUP;
-    if (!p->with_norm && p->y_dtype != SS2D_F32) return SS2D_ENOTSUP;
-    PlaneConfig c;
-    if (!plan_planes(p, c)) return SS2D_ENOTSUP;
-    const long long need = core_workspace_bytes(p);
     float* merged = (float*)p->y;
     if (need > 0) {
         if (need > kStaticScratchBytes) return SS2D_ETOOBIG;
         const int r = static_scratch_for_current_device(&merged);
         if (r != SS2D_OK) return r;
-    } else if (!aligned_to(p->y, 16)) {
-        return SS2D_EINVAL_ALIGN;
     }
-    return run_core(p, c, merged, st);
+    return run_core(p, plan, merged, st);
 }
 
 }  // namespace ss2d

@@ -24,6 +24,7 @@ struct NormArgs {
     int D, L, nv, items;     // nv = L / PV items per image, items = B * nv
     float eps;
     int skip_norm;           // 1: out = s converted, no statistics (a fused add + cast + layout change)
+    int descending;          // 1: CTAs take the items from the last to the first
 };
 
 // MODE picks what the compiler may assume.  0: nothing (every optional pointer is tested, D <= NTY * CACHE).
@@ -36,7 +37,7 @@ __global__ void __launch_bounds__(TX * NTY, (NTY == 32 && CACHE > 0 && CACHE * P
     constexpr int NP = NTY / 2;                      // partial sums per item after the in-warp step
     __shared__ float red[2][NP][TX][PV];
     const int tx = threadIdx.x, ty = threadIdx.y;
-    const int item = blockIdx.x * TX + tx;
+    const int item = (a.descending ? gridDim.x - 1 - blockIdx.x : blockIdx.x) * TX + tx;
     const bool live = item < a.items;
     const int bimg = live ? item / a.nv : 0;
     const long long pix = (long long)(live ? (item - bimg * a.nv) : 0) * PV;
@@ -329,6 +330,7 @@ int layer_norm_cf(const ss2d_norm_params* p, cudaStream_t st) {
     a.w = (const float*)p->weight; a.b = (const float*)p->bias; a.out = p->out;
     a.bs = bs; a.cs = cs; a.obs = obs; a.ocs = ocs; a.D = (int)p->D; a.L = (int)L; a.eps = p->eps; a.nv = 0; a.items = 0;
     a.skip_norm = p->skip_norm ? 1 : 0;
+    a.descending = p->descending ? 1 : 0;
     if (p->io_dtype == SS2D_F32) launch_norm<float>(a, pv, B, st);
     else if (p->io_dtype == SS2D_BF16) launch_norm<__nv_bfloat16>(a, pv, B, st);
     else launch_norm<__half>(a, pv, B, st);

@@ -188,10 +188,32 @@ def scan_merge_norm(x: torch.Tensor, proj, w: CoreWeights, *, with_norm: bool = 
     return y
 
 
-def fused_supported(x_shape, d_state: int) -> bool:
-    """True when `ss2d_core_fwd` handles the case itself (d_state 1, plane fits one CTA)."""
-    L = x_shape[2] * x_shape[3]
-    return d_state == 1 and (L // _vec_of(L)) <= 1024
+def fused_supported(x_shape, d_state: int, dtype: torch.dtype = torch.bfloat16, channel_major: bool = False) -> bool:
+    """True when `ss2d_core_fwd` takes the case itself.  Asks the library (`ss2d_core_supported`), which applies
+    the rules of its launch planner to dense, 16-byte aligned streams of this shape, so the answer cannot drift
+    from what the call will do."""
+    if channel_major:
+        D, B, H, W = x_shape
+    else:
+        B, D, H, W = x_shape
+    L = H * W
+    p = CoreParams()
+    fake = 4096                                   # an aligned address; the query dereferences nothing
+    p.x = p.A = p.Dskip = p.delta_bias = p.y = fake
+    for k in range(K):
+        p.delta[k] = p.Bm[k] = p.Cm[k] = fake
+        if channel_major:
+            p.delta_batch_stride[k], p.delta_channel_stride[k], p.bc_batch_stride[k] = L, B * L, L
+        else:
+            p.delta_batch_stride[k], p.delta_channel_stride[k], p.bc_batch_stride[k] = 2 * D * L, L, 4 * int(d_state) * L
+    p.B, p.D, p.H, p.W, p.N = B, D, H, W, int(d_state)
+    code = {torch.float32: _lib.SS2D_F32, torch.float16: _lib.SS2D_F16, torch.bfloat16: _lib.SS2D_BF16}[dtype]
+    p.act_dtype = p.y_dtype = code
+    p.with_norm = 1
+    if channel_major:
+        p.x_batch_stride = p.y_batch_stride = L
+        p.x_channel_stride = p.y_channel_stride = B * L
+    return int(lib().ss2d_core_supported(p)) == _lib.SS2D_OK
 
 
 def ss2d_core(x: torch.Tensor, w: CoreWeights, *, with_norm: bool = True, out_dtype=None,
@@ -207,19 +229,20 @@ def ss2d_core(x: torch.Tensor, w: CoreWeights, *, with_norm: bool = True, out_dt
         raise RuntimeError(f"x has {x.shape[0 if channel_major else 1]} channels, weights were built for {w.d_inner}")
     out_dtype = out_dtype or (x.dtype if with_norm else torch.float32)
     with torch.autocast("cuda", enabled=False):
-        if not fused_supported(x.shape, w.d_state) or (channel_major and not with_norm):
+        def unfused():
             if channel_major:
                 return _ss2d_core_unfused_cm(x, w, with_norm, out_dtype)
             return _ss2d_core_unfused(x, w, with_norm, out_dtype)
-        return scan_merge_norm(x, project(x, w, channel_major), w, with_norm=with_norm, out_dtype=out_dtype,
-                               workspace=workspace, channel_major=channel_major)
 
-
-def _vec_of(L: int) -> int:
-    v = 8
-    while v > 1 and L % v:
-        v >>= 1
-    return v
+        if not fused_supported(x.shape, w.d_state, x.dtype, channel_major) or (channel_major and not with_norm):
+            return unfused()
+        try:
+            return scan_merge_norm(x, project(x, w, channel_major), w, with_norm=with_norm, out_dtype=out_dtype,
+                                   workspace=workspace, channel_major=channel_major)
+        except _lib.Ss2dError as e:        # refused before any launch (an alignment the query could not see)
+            if e.status != _lib.SS2D_ENOTSUP:
+                raise
+            return unfused()
 
 
 def _ss2d_core_unfused(x, w: CoreWeights, with_norm: bool, out_dtype, out_channel_major: bool = False):
@@ -316,6 +339,10 @@ def enable_fused(model: torch.nn.Module, verbose: bool = False) -> int:
 
         def fused_core(x, _m=mod, _cache=cache, _orig=orig, **kwargs):
             if getattr(_m, "__DEBUG__", False) or _m.training or not x.is_cuda:
+                return _orig(x, **kwargs)
+            # the fused call builds no autograd graph: whenever a gradient could be asked for through this
+            # module (input gradients in eval mode, un-frozen parameters), the differentiable original runs
+            if torch.is_grad_enabled() and (x.requires_grad or any(q.requires_grad for q in _m.parameters())):
                 return _orig(x, **kwargs)
             w = _cache.get(x.dtype)
             if w is None:
