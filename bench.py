@@ -182,13 +182,17 @@ def roofline_of_core(model, peak_gbs, peak_kind, batch=None, iters=20):
     alg = B * L * (D * s + K * D * s + 2 * K * N * s + D * s) + 4 * (K * D * N + 2 * K * D) + 2 * 4 * D
     scan_bytes = B * L * (D * s + K * D * s + 2 * K * N * s + D * 4)
     ach = alg / (t_chain * 1e-3) / 1e9
-    # DRAM bytes of the two kernels from an ncu capture of this chain at batch 48 (profiles/
-    # ss2d_chain_stage0_dram_traffic.md): 16.5 bytes per (pixel, channel), scaled by the units of this launch
-    traffic = 16.5 * B * D * L if (D == 96 and s == 2) else None
+    # DRAM bytes of the chain's two kernels: an ncu capture of this very command line at batch 128 (one launch of each
+    # kernel, caches left as the previous launch left them) gave 392 MB read + 164 MB written by the scan + merge kernel
+    # and 128 MB read + 72 MB written by the LayerNorm kernel, 19.6 bytes per (pixel, channel); other batch sizes are
+    # scaled by their (pixel, channel) count.
+    traffic = 19.6 * B * D * L if (D == 96 and s == 2) else None
     return {
         "bound": "hbm", "achieved": ach, "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs, "traffic": traffic,
         "peak_kind": f"of {peak_kind}",
-        "kernel": "core_plane_kernel + layer_norm_cf_kernel (fused SS2D scan+merge+LayerNorm chain)",
+        "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of core_route_kernel and layer_norm_cf_kernel, "
+                          "batch 128, --cache-control none; scaled by (pixel, channel) count" if traffic else None,
+        "kernel": "core_route_kernel + layer_norm_cf_kernel (fused SS2D scan+merge+LayerNorm chain)",
         "workload": f"stage 0 of {MODEL} at 224x224: B={B} D={D} H=W={H} bf16",
         "algorithmic_bytes_per_launch": alg, "chain_ms": t_chain,
         "scan_merge_kernel_ms": t_scan, "scan_merge_kernel_gbs": scan_bytes / (t_scan * 1e-3) / 1e9,
