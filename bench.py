@@ -255,6 +255,65 @@ def op_sweep(args):
         del x, ys
 
 
+def reference_modules_leg(local: int, steps: int = 5):
+    """The UNMODIFIED reference modules (the staged copy of its one-file vmamba.py) on this library's operators:
+    `install()` + `enable_fused()`, eager, bf16 autocast, batch 128 - the drop-in use of the library, reported
+    beside the headline.  Also the top-1 agreement measured like for like: this library's bf16 backbone against the
+    reference's own pure-torch path under bf16 autocast on the same GPU, same weights, 256 synthetic images.
+    Returns None where no checkout was staged (oracle/stage_ref.py)."""
+    import torch
+    from oracle import stage_ref              # checker-side loader of the reference's own file; not a product path
+    if not stage_ref.staged("vmamba.py"):
+        return None
+    import vmamba_b200 as vb
+    from vmamba_b200.backbone import VSSMInfer
+    ref = stage_ref.load("vmamba.py", "vmamba_reference_bench")
+    torch.manual_seed(0)
+    m = ref.vmamba_tiny_s1l8().eval().cuda(local)
+    g = torch.Generator().manual_seed(7)
+    out = {"model": "vmamba.py:vmamba_tiny_s1l8 (unmodified reference modules), eager, torch.autocast bf16"}
+    # ---- like-for-like top-1: reference pure-torch bf16 autocast vs this library's bf16 backbone ----
+    img = torch.randn((256, 3, IMG, IMG), generator=g).cuda(local)
+    orig_scan, orig_merge = ref.cross_scan_fn, ref.cross_merge_fn
+    ref.cross_scan_fn = lambda *a, **k: orig_scan(*a, **{**k, "force_torch": True})
+    ref.cross_merge_fn = lambda *a, **k: orig_merge(*a, **{**k, "force_torch": True})
+    try:
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            want16 = torch.cat([m(img[i:i + 32]) for i in range(0, 256, 32)]).float()
+        with torch.no_grad():
+            want32 = torch.cat([m(img[i:i + 32]) for i in range(0, 64, 32)]).float()
+    finally:
+        ref.cross_scan_fn, ref.cross_merge_fn = orig_scan, orig_merge
+    sd = {k: v.detach().float().cpu().numpy() for k, v in m.state_dict().items()}
+    lib = VSSMInfer.from_state_dict(sd, dtype=torch.bfloat16, device=f"cuda:{local}")
+    lib16 = torch.cat([lib(img[i:i + 64].to(torch.bfloat16)) for i in range(0, 256, 64)]).float()
+    noise = float((want16[:64] - want32).abs().max())
+    top2 = want16.topk(2, dim=1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 4 * noise
+    agree = lib16.argmax(1) == want16.argmax(1)
+    out["top1_like_for_like"] = {
+        "images": 256, "raw": float(agree.float().mean()), "clear_margin_images": int(clear.sum()),
+        "clear_margin_agreement": float(agree[clear].float().mean()) if int(clear.sum()) else None,
+        "reference_bf16_vs_fp32_logit_noise": noise, "max_abs_logit_diff": float((lib16 - want16).abs().max()),
+        "comparator": "reference CrossScanF/CrossMergeF + selective_scan_torch under torch.autocast(bf16) on this GPU"}
+    del lib, lib16, want16, want32
+    # ---- throughput of the reference modules on the library: surface operators, then the fused core ----
+    x = img[:BATCH] if BATCH <= 256 else img
+    x = torch.randn((BATCH, 3, IMG, IMG), generator=g).cuda(local)
+    vb.install(ref)
+    try:
+        def fwd():
+            with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+                return m(x)
+        out["img_s_surface_operators"] = BATCH / (time_events(fwd, steps) * 1e-3)
+        out["fused_modules"] = vb.enable_fused(m)
+        out["img_s_fused_core"] = BATCH / (time_events(fwd, steps) * 1e-3)
+    finally:
+        vb.disable_fused(m)
+        vb.uninstall(ref)
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -359,7 +418,7 @@ def run_ours(args):
     value = total_imgs / (ms_dev * 1e-3)
     e2e = total_imgs / (ms_e2e * 1e-3)
 
-    roof = cpu = parity = None
+    roof = cpu = parity = refmod = None
     if rank == 0:
         peak, kind = peaks()
         roof = roofline_of_core(model, peak, kind)
@@ -376,6 +435,8 @@ def run_ours(args):
             got32 = m32(torch.from_numpy(img_np).cuda()).cpu().numpy()
             torch.backends.cudnn.allow_tf32 = old_tf32
             del m32
+            if not args.no_reference_modules:
+                refmod = reference_modules_leg(local)
             den = float(np.abs(ref).max())
             parity = {"images": int(ref.shape[0]), "oracle": "oracle/backbone_oracle.vssm_logits (fp32, CPU)",
                       "max_rel_err_fp32": float(np.abs(got32 - ref).max()) / den,
@@ -411,6 +472,8 @@ def run_ours(args):
         line["cpu_baseline"] = cpu
     if parity is not None:
         line["parity"] = parity
+    if refmod is not None:
+        line["reference_modules"] = refmod
     print(json.dumps(line), flush=True)
 
 
@@ -421,6 +484,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-modules", action="store_true", help="skip the leg that runs the staged reference modules")
     ap.add_argument("--model", default=None, help="vmamba_tiny_s1l8 (default) | vmamba_small_s2l15 | vmamba_base_s2l15")
     ap.add_argument("--batch", type=int, default=None, help="images per GPU per step (default 128)")
     ap.add_argument("--img", type=int, default=None, help="image side (default 224)")
