@@ -271,6 +271,33 @@ int64_t ss2d_route_expand_workspace_bytes(const ss2d_expand_params *p);
 
 int ss2d_route_expand(const ss2d_expand_params *p, void *cuda_stream);
 
+/* ------------------------------------------------------------------------------------
+ * Fused MLP of a VSS block on a channel-major map:  y = W2 . gelu(W1 . x + b1), erf-form GELU, the
+ * hidden activations (4C per pixel) kept on chip.  Replaces fc1, the activation and fc2 of
+ * Mlp.forward (vmamba.py:1151-1167, channel-first form :1060-1064); the fc2 bias is NOT added
+ * (ss2d_layer_norm_cf adds it with the residual update, as `add_bias`).
+ *   x  (C, N)  dtype (SS2D_BF16 or SS2D_F16), N = B*H*W pixels contiguous per channel, N % 8 == 0
+ *   w1 (hidden, C) dtype, row-major; b1 (hidden) fp32; w2 (C, hidden) dtype, row-major
+ *   y  (C, N)  dtype
+ * Runs on the tcgen05 tensor cores (fp32 accumulation in tensor memory), operands staged by TMA.
+ * ss2d_mlp_supported returns SS2D_OK when ss2d_mlp_fwd takes the problem (hidden == 4 C and a width
+ * whose weights fit one SM: C == 96), else the status ss2d_mlp_fwd would return without launching
+ * (SS2D_ENOTSUP: use two GEMMs and ss2d_bias_act).
+ * -------------------------------------------------------------------------------- */
+typedef struct ss2d_mlp_params {
+    const void *x;
+    const void *w1;
+    const void *b1;
+    const void *w2;
+    void *y;
+    int64_t C, hidden, N;
+    int32_t dtype;
+    int32_t reserved0;
+} ss2d_mlp_params;
+
+int ss2d_mlp_supported(const ss2d_mlp_params *p);
+int ss2d_mlp_fwd(const ss2d_mlp_params *p, void *cuda_stream);
+
 /* Allocation-free form of ss2d_core_fwd.  It has no counterpart in the reference: it exists for
  * callers that can hand over inputs and outputs but cannot obtain device memory themselves (an
  * operator slot of a serving runtime that passes only pre-placed tensors, a host language bound to

@@ -675,3 +675,50 @@ def test_vmamba_tiny_fp16_forward(vb):
     finally:
         torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = old
     assert float((got - ref).abs().max() / ref.abs().max()) <= 5e-3
+
+
+# ------------------------------------------------------------------ fused MLP (tcgen05)
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("B,H,W", [(1, 8, 16), (2, 56, 56), (3, 10, 12), (5, 7, 8)])
+def test_mlp_fused_vs_oracle(vb, dtype, B, H, W):
+    """fc2(gelu(fc1(x) + b1)) in one tcgen05 kernel against the fp32 statement of Mlp.forward (vmamba.py:1151-1167)
+    on the same 16-bit inputs: whole tiles, a ragged last tile (N = 360, 280), a single partial tile."""
+    from vmamba_b200 import ops
+    C = 96
+    td = torch.bfloat16 if dtype == "bf16" else torch.float16
+    rng = np.random.default_rng(B * 100 + H)
+    x = dev(rng.standard_normal((C, B, H, W), dtype=np.float32), td)
+    w1 = dev((rng.standard_normal((4 * C, C), dtype=np.float32) / np.sqrt(C)).astype(np.float32), td)
+    b1 = dev((0.3 * rng.standard_normal(4 * C)).astype(np.float32))
+    w2 = dev((rng.standard_normal((C, 4 * C), dtype=np.float32) / np.sqrt(4 * C)).astype(np.float32), td)
+    assert ops.mlp_supported(C, 4 * C, B * H * W, td)
+    y = ops.mlp_fused(x, w1, b1, w2)
+    assert y.dtype == td and y.shape == x.shape
+    xf = x.float().cpu().numpy().reshape(C, -1).astype(np.float64)
+    h = w1.float().cpu().numpy().astype(np.float64) @ xf + b1.cpu().numpy().astype(np.float64)[:, None]
+    from math import erf
+    g = 0.5 * h * (1.0 + np.vectorize(erf)(h / np.sqrt(2.0)))
+    g = torch.from_numpy(g).to(td).double().numpy()                    # the hidden activations enter fc2 in the 16-bit type
+    ref = (w2.float().cpu().numpy().astype(np.float64) @ g).reshape(C, B, H, W)
+    assert O.max_rel_err(host(y), ref) <= (TOL_BF16 if dtype == "bf16" else 4e-3)
+    assert torch.equal(y, ops.mlp_fused(x, w1, b1, w2)), "no atomics: results must be bit-identical run to run"
+    # large activations: the saturating polynomial must give x (or 0) beyond its fitted range
+    xb = x * 30
+    yb = ops.mlp_fused(xb, w1, b1, w2)
+    hb = w1.float().cpu().numpy().astype(np.float64) @ xb.float().cpu().numpy().reshape(C, -1).astype(np.float64) + b1.cpu().numpy().astype(np.float64)[:, None]
+    gb = torch.from_numpy(0.5 * hb * (1.0 + np.vectorize(erf)(hb / np.sqrt(2.0)))).to(td).double().numpy()
+    refb = (w2.float().cpu().numpy().astype(np.float64) @ gb).reshape(C, B, H, W)
+    assert np.isfinite(host(yb)).all() and O.max_rel_err(host(yb), refb) <= (TOL_BF16 if dtype == "bf16" else 4e-3)
+
+
+@pytest.mark.gpu
+def test_mlp_fused_refuses_what_it_cannot_take(vb):
+    from vmamba_b200 import ops
+    assert not ops.mlp_supported(192, 768, 1024, torch.bfloat16)        # weights do not fit one SM
+    assert not ops.mlp_supported(96, 384, 1023, torch.bfloat16)         # row pitch not a multiple of 16 bytes
+    assert not ops.mlp_supported(96, 192, 1024, torch.bfloat16)         # hidden != 4 C
+    assert not ops.mlp_supported(96, 384, 1024, torch.float32)
+    x = torch.zeros((192, 1, 8, 16), device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        ops.mlp_fused(x, torch.zeros((768, 192), device="cuda"), torch.zeros(768, device="cuda"), torch.zeros((192, 768), device="cuda"))

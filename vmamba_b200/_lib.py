@@ -99,6 +99,11 @@ class RelayoutParams(ctypes.Structure):
                [("rows_dtype", _i32), ("planes_dtype", _i32), ("eps", _f32), ("reserved0", _i32)]
 
 
+class MlpParams(ctypes.Structure):
+    _fields_ = [(n, _vp) for n in ("x", "w1", "b1", "w2", "y")] + [(n, _i64) for n in ("C", "hidden", "N")] + \
+               [("dtype", _i32), ("reserved0", _i32)]
+
+
 EXPORTS = {
     # name: (restype, argtypes)
     "ss2d_selective_scan_fwd": (ctypes.c_int, [ctypes.POINTER(ScanParams), _vp]),
@@ -121,6 +126,8 @@ EXPORTS = {
     "ss2d_planes_to_pixels": (ctypes.c_int, [ctypes.POINTER(RelayoutParams), _vp]),
     "ss2d_bias_act": (ctypes.c_int, [ctypes.POINTER(PointwiseParams), _vp]),
     "ss2d_dwconv3x3_act": (ctypes.c_int, [ctypes.POINTER(PointwiseParams), _vp]),
+    "ss2d_mlp_supported": (ctypes.c_int, [ctypes.POINTER(MlpParams)]),
+    "ss2d_mlp_fwd": (ctypes.c_int, [ctypes.POINTER(MlpParams), _vp]),
     "ss2d_version": (ctypes.c_int, []),
     "ss2d_strerror": (ctypes.c_char_p, [ctypes.c_int]),
     "ss2d_launch_count": (_i64, []),

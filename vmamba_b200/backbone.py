@@ -169,8 +169,11 @@ class VSSMInfer:
         h = ss2d_core(h, b.core, channel_major=True)                              # forward_core     :1584
         o = self._pw(b.w_out, h)                                                  # out_proj         :1588
         h = ops.layer_norm_cf(x, b.n2w, b.n2b, 1e-5, self.dtype, add=o, update=True, channel_major=True)   # :1772, 1777
-        h = ops.bias_act_(self._pw(b.w1, h), b.b1f, "gelu", channel_major=True)   # Mlp fc1 + GELU   :1160-1163
-        m = self._pw(b.w2, h)                                                     # fc2 (its bias joins the residual update)
+        if ops.mlp_supported(h.shape[0], b.w1.shape[0], h.numel() // h.shape[0], h.dtype):
+            m = ops.mlp_fused(h, b.w1, b.b1f, b.w2)                               # Mlp: fc1 + GELU + fc2, one kernel :1151-1167
+        else:
+            h = ops.bias_act_(self._pw(b.w1, h), b.b1f, "gelu", channel_major=True)   # Mlp fc1 + GELU   :1160-1163
+            m = self._pw(b.w2, h)                                                 # fc2 (its bias joins the residual update)
         if nxt is None:          # end of a stage: the caller decides what consumes x + m + bias
             return x, (m, b.b2f)
         return x, ops.layer_norm_cf(x, nxt[0], nxt[1], 1e-5, self.dtype, add=m, add_bias=b.b2f, update=True,

@@ -18,6 +18,8 @@ int core_supported(const ss2d_core_params* p);
 int core_fwd_static(const ss2d_core_params* p, cudaStream_t st);
 long long core_static_capacity();
 int route_expand(const ss2d_expand_params* p, cudaStream_t st);
+int mlp_supported(const ss2d_mlp_params* p);
+int mlp_fwd(const ss2d_mlp_params* p, cudaStream_t st);
 long long route_expand_workspace_bytes(const ss2d_expand_params* p);
 int stem_conv_norm_act(const ss2d_stem_params* p, cudaStream_t st);
 int pixels_norm_to_planes(const ss2d_relayout_params* p, cudaStream_t st);
@@ -59,6 +61,9 @@ int ss2d_dwconv3x3_act(const ss2d_pointwise_params* p, void* stream) { return ss
 int ss2d_stem_conv_norm_act(const ss2d_stem_params* p, void* stream) { return ss2d::stem_conv_norm_act(p, (cudaStream_t)stream); }
 int ss2d_pixels_norm_to_planes(const ss2d_relayout_params* p, void* stream) { return ss2d::pixels_norm_to_planes(p, (cudaStream_t)stream); }
 int ss2d_planes_to_pixels(const ss2d_relayout_params* p, void* stream) { return ss2d::planes_to_pixels(p, (cudaStream_t)stream); }
+
+int ss2d_mlp_supported(const ss2d_mlp_params* p) { return ss2d::mlp_supported(p); }
+int ss2d_mlp_fwd(const ss2d_mlp_params* p, void* stream) { return ss2d::mlp_fwd(p, (cudaStream_t)stream); }
 
 int ss2d_version(void) { return SS2D_ABI_VERSION; }
 int64_t ss2d_launch_count(void) { return ss2d::g_launches.load(std::memory_order_relaxed); }

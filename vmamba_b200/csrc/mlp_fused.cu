@@ -1,0 +1,494 @@
+// Fused MLP of a VSS block on the 5th-generation tensor cores:  y = W2 . gelu(W1 . x + b1)  on a channel-major
+// map x (C, N) of N = B*H*W pixels, the 4C-wide hidden activations never leaving the SM.  Replaces fc1, the bias +
+// GELU pass and fc2 of Mlp.forward (vmamba.py:1151-1167); the fc2 bias joins the residual update in the LayerNorm
+// kernel that consumes y.
+//
+// One persistent CTA per SM walks tiles of 128 pixels.  Per tile and per chunk of 64 hidden units:
+//   GEMM 1   H^T (128 px x 64)   = X^T (128 px x C) . W1_chunk^T (C x 64)      tcgen05.mma, accumulator in TMEM
+//   epilogue H^T -> registers (tcgen05.ld) -> + b1 -> GELU -> bf16 -> shared memory, laid out as an MMA operand
+//   GEMM 2   Y^T (128 px x C)   += G (128 px x 64) . W2_chunk^T (64 x C)       accumulator in TMEM over all chunks
+// then Y^T -> registers -> 16-bit -> global, channel-major.  X^T is read straight from the channel-major map: a TMA
+// box of 64 pixels x C channels is the "MN-major" operand form of the tensor core (pixels contiguous), so no transpose
+// happens anywhere.  Both weight matrices stay in shared memory for the life of the CTA (C = 96: 144 KB), loaded once
+// by TMA; x tiles are double-buffered TMA loads.  Warp 0 issues TMA, warp 1 the MMAs of GEMM 1, warp 2 those of GEMM 2
+// (one lane each, each blocking on its own barriers: a single issuing thread that polled both streams spent its time
+// on descriptor arithmetic and polling, sharing a scheduler with four epilogue warps), sixteen warps run the epilogues
+// in two groups that take alternate chunks.  TMEM holds two H chunks and two Y tiles, so the tensor core works on
+// chunk j+1 and on the next tile while the epilogue warps are busy; the Y tile is written out one chunk into the next
+// tile.  The epilogue is what bounds the kernel (128 x 4C GELUs per tile, about 11 fp32 operations each, against the
+// 2.4 k cycles of the tile's MMAs), which is why erf is a polynomial on the FMA pipe (gelu error <= 7.5e-4) and not the
+// exp / reciprocal form: two MUFU operations per value alone would take 2.6 times as long as the tile's MMAs.
+//
+// Every wait on an mbarrier is bounded: when one runs out, the kernel raises an error flag in global memory, every role
+// leaves its loop, TMEM is released and the kernel returns; the host reports SS2D_ECUDA on the next status query.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace ss2d {
+
+namespace {
+
+constexpr int kTilePx = 128;       // pixels per tile = M of the MMAs
+constexpr int kHC = 64;            // hidden units per chunk = N of GEMM 1, K of GEMM 2
+constexpr int kEpiWarps = 16;
+constexpr int kFirstEpiWarp = 4;   // warps 0..3: TMA producer, GEMM 1 issuer, GEMM 2 issuer, (spare)
+constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
+constexpr unsigned kSpinLimit = 1u << 22;
+
+// ---- PTX wrappers --------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n"
+        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Non-blocking test of a phase.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n"
+        " mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the limit ran out or another role has already given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (unsigned i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D (TMEM) (+)= A (smem descriptor) . B (smem descriptor); 16-bit inputs, fp32 accumulation
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns: lane i of the warp gets row (quarter base + i)
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- operand descriptors (the layouts TMA writes with its 128- / 64-byte swizzle) --------------------------------------
+// Shared-memory matrix descriptor: start address, leading and stride byte offsets (all >> 4), descriptor version 1,
+// swizzle mode.  For the swizzled layouts used here:
+//   K-major  (rows of 64 / 32 contraction elements): stride offset = 8 rows (1024 / 512 bytes), leading offset unused
+//   MN-major (rows of 64 M elements, one row per contraction index): stride offset = 8 rows of the contraction
+//            (1024 bytes), leading offset = distance between blocks of 64 M elements
+constexpr uint64_t kSw128 = 2ull << 61, kSw64 = 4ull << 61;
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lead_bytes, uint32_t stride_bytes, uint64_t swizzle) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lead_bytes >> 4) & 0x3fffu) << 16) |
+           ((uint64_t)((stride_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | swizzle;
+}
+// Instruction descriptor: fp32 accumulator, 16-bit A / B of format `fmt` (0 fp16, 1 bf16), A MN-major or K-major, B K-major
+__host__ __device__ constexpr uint32_t instr_desc(int fmt, bool a_mn_major, int M, int N) {
+    return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// ---- GELU (erf form) on the FMA pipe -----------------------------------------------------------------------------------
+// gelu(v) = v * Phi(v), Phi(v) = 1/2 + z P(z^2) with z = v / sqrt 2 and P an even polynomial of degree 12 fitted to
+// erf(z) / (2 z) on |z| <= 3.  The final fused multiply-add saturates to [0, 1], which is Phi's range; beyond the fitted
+// range P(t) >= 1 / (2 sqrt t) for every t > 9 (its leading coefficient is positive), so |z P| >= 1/2 there and the result
+// is exactly 0 or 1 without a clamp on the argument.  |gelu error| <= 7.5e-4 for every v, a fifth of a bf16 step at 1.
+__device__ __forceinline__ float fma_sat(float a, float b, float c) {
+    float d;
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float2 gelu_pair_poly(float2 v) {
+    const float kC = 0.70710678118654752f;
+    const float2 z = __fmul2_rn(v, make_float2(kC, kC));
+    const float2 t = __fmul2_rn(z, z);
+    float2 p = make_float2(1.840303185e-06f, 1.840303185e-06f);
+    p = __ffma2_rn(p, t, make_float2(-6.794340152e-05f, -6.794340152e-05f));
+    p = __ffma2_rn(p, t, make_float2(1.058246824e-03f, 1.058246824e-03f));
+    p = __ffma2_rn(p, t, make_float2(-9.187800810e-03f, -9.187800810e-03f));
+    p = __ffma2_rn(p, t, make_float2(4.991913959e-02f, 4.991913959e-02f));
+    p = __ffma2_rn(p, t, make_float2(-1.834703386e-01f, -1.834703386e-01f));
+    p = __ffma2_rn(p, t, make_float2(5.632318258e-01f, 5.632318258e-01f));
+    const float2 phi = make_float2(fma_sat(p.x, z.x, 0.5f), fma_sat(p.y, z.y, 0.5f));
+    return __fmul2_rn(v, phi);
+}
+
+template <typename T> struct Fmt;
+template <> struct Fmt<__nv_bfloat16> { static constexpr int id = 1; static constexpr CUtensorMapDataType tm = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; };
+template <> struct Fmt<__half> { static constexpr int id = 0; static constexpr CUtensorMapDataType tm = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; };
+
+struct MlpArgs {
+    const float* b1;
+    void* y;
+    long long N;
+    int tiles;
+    int* error_flag;
+};
+
+// Shared memory of the C-channel kernel (byte offsets from a 1024-aligned base)
+template <int C> struct MlpSmem {
+    static constexpr int HID = 4 * C, NCH = HID / kHC, KC1 = C / 32;     // hidden width, chunks, 32-wide K slices of W1
+    static constexpr int kW1 = 0;                                        // [KC1][HID rows][64 B], 64-byte swizzle
+    static constexpr int kW1Bytes = KC1 * HID * 64;
+    static constexpr int kW2 = kW1 + kW1Bytes;                           // [NCH][C rows][128 B], 128-byte swizzle
+    static constexpr int kW2Block = C * 128, kW2Bytes = NCH * kW2Block;
+    static constexpr int kX = kW2 + kW2Bytes;                            // [2 stages][2 halves][C rows][128 B]
+    static constexpr int kXHalf = C * 128, kXStage = 2 * kXHalf;
+    static constexpr int kG = kX + 2 * kXStage;                          // [2][128 rows][128 B]
+    static constexpr int kGBuf = kTilePx * 128;
+    static constexpr int kBars = kG + 2 * kGBuf;
+    static constexpr int kBias = kBars + 256;                            // fc1 bias, fp32
+    static constexpr int kTotal = kBias + HID * 4;
+    static_assert(C % 32 == 0 && (C * 128) % 1024 == 0, "operand blocks must be whole swizzle atoms");
+};
+
+enum { BAR_W = 0, BAR_XF = 1, BAR_XE = 3, BAR_HF = 5, BAR_HE = 7, BAR_GF = 9, BAR_GE = 11, BAR_YF = 13, BAR_YE = 15, BAR_COUNT = 17 };
+
+template <typename T, int C>
+__global__ void __launch_bounds__(kThreads, 1)
+mlp_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW1,
+                 const __grid_constant__ CUtensorMap tmW2, const MlpArgs a) {
+    using S = MlpSmem<C>;
+    constexpr int NCH = S::NCH;
+    constexpr int kTmemCols = 512;
+    constexpr int kColH = 0, kColY = 2 * kHC;                  // TMEM columns: two H chunks, then two Y tiles of C columns
+    static_assert(kColY + 2 * C <= kTmemCols, "TMEM holds two H chunks and two Y tiles");
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + S::kBars);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bars + BAR_W, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bars + BAR_XF + i, 1); mbar_init(bars + BAR_XE + i, 1);
+            mbar_init(bars + BAR_HF + i, 1); mbar_init(bars + BAR_HE + i, kEpiWarps / 2);
+            mbar_init(bars + BAR_GF + i, kEpiWarps / 2); mbar_init(bars + BAR_GE + i, 1);
+            mbar_init(bars + BAR_YF + i, 1); mbar_init(bars + BAR_YE + i, kEpiWarps);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < S::HID; i += kThreads) reinterpret_cast<float*>(sm + S::kBias)[i] = __ldg(a.b1 + i);
+    if (warp == 1) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int ntiles_mine = (a.tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(bars + BAR_W, S::kW1Bytes + S::kW2Bytes);
+            for (int kc = 0; kc < S::KC1; ++kc)
+                for (int r0 = 0; r0 < S::HID; r0 += 192)
+                    tma_load_2d(sm + S::kW1 + (kc * S::HID + r0) * 64, &tmW1, kc * 32, r0, bars + BAR_W);
+            for (int j = 0; j < NCH; ++j) tma_load_2d(sm + S::kW2 + j * S::kW2Block, &tmW2, j * kHC, 0, bars + BAR_W);
+            for (int it = 0; it < ntiles_mine; ++it) {
+                const int s = it & 1;
+                if (it >= 2 && !mbar_wait(bars + BAR_XE + s, ((it >> 1) - 1) & 1, abort_flag)) break;
+                const long long p0 = (long long)(blockIdx.x + (long long)it * gridDim.x) * kTilePx;
+                mbar_expect_tx(bars + BAR_XF + s, S::kXStage);
+                tma_load_2d(sm + S::kX + s * S::kXStage, &tmX, (int)p0, 0, bars + BAR_XF + s);
+                tma_load_2d(sm + S::kX + s * S::kXStage + S::kXHalf, &tmX, (int)p0 + 64, 0, bars + BAR_XF + s);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- GEMM 1 issuer
+        // H^T (chunk c) = X^T . W1_c^T as soon as the x tile is there and the epilogue has read chunk c - 2 out of the H
+        // buffer.  Chunks are numbered across tiles.  The thread's instruction stream is kept short (descriptors are
+        // a constant plus an offset): it shares its scheduler with four epilogue warps.
+        if (lane == 0) {
+            constexpr uint32_t idesc1 = instr_desc(Fmt<T>::id, true, kTilePx, kHC);
+            const uint32_t sbase = smem_u32(sm);
+            const uint64_t a_base = smem_desc(sbase + S::kX, S::kXHalf, 1024, kSw128);
+            const uint64_t b_base = smem_desc(sbase + S::kW1, 16, 512, kSw64);
+            bool ok = mbar_wait(bars + BAR_W, 0, abort_flag);
+            const int total = ntiles_mine * NCH;
+            for (int c1 = 0, it = 0, j = 0; ok && c1 < total; ++c1) {
+                const int s = it & 1, b = c1 & 1;
+                if (j == 0) ok = mbar_wait(bars + BAR_XF + s, (it >> 1) & 1, abort_flag);
+                if (ok && c1 >= 2) ok = mbar_wait(bars + BAR_HE + b, ((c1 >> 1) - 1) & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t da0 = a_base + (uint64_t)((s * S::kXStage) >> 4);
+                const uint64_t db0 = b_base + (uint64_t)((j * kHC * 64) >> 4);
+#pragma unroll
+                for (int k = 0; k < C / 16; ++k)               // 16 channels per instruction
+                    tc_mma(tmem + kColH + b * kHC, da0 + (uint64_t)((k * 2048) >> 4),
+                           db0 + (uint64_t)((((k >> 1) * S::HID) * 64 + (k & 1) * 32) >> 4), idesc1, k > 0 ? 1u : 0u);
+                tc_commit(bars + BAR_HF + b);
+                if (j == NCH - 1) tc_commit(bars + BAR_XE + s);        // the x tile has been read by all its MMAs
+                if (++j == NCH) { j = 0; ++it; }
+            }
+        }
+    } else if (warp == 2) {
+        // ---------------------------------------------------------------- GEMM 2 issuer
+        // Y^T (+)= G_c . W2_c^T as soon as the epilogue has written G_c (and, at the start of a tile, read the Y tile
+        // that used this accumulator two tiles ago).
+        if (lane == 0) {
+            constexpr uint32_t idesc2 = instr_desc(Fmt<T>::id, false, kTilePx, C);
+            const uint32_t sbase = smem_u32(sm);
+            const uint64_t a_base = smem_desc(sbase + S::kG, 16, 1024, kSw128);
+            const uint64_t b_base = smem_desc(sbase + S::kW2, 16, 1024, kSw128);
+            bool ok = mbar_wait(bars + BAR_W, 0, abort_flag);
+            const int total = ntiles_mine * NCH;
+            for (int c2 = 0, it = 0, j = 0; ok && c2 < total; ++c2) {
+                const int yb = it & 1, b = c2 & 1;
+                ok = mbar_wait(bars + BAR_GF + b, (c2 >> 1) & 1, abort_flag);
+                if (ok && j == 0 && it >= 2) ok = mbar_wait(bars + BAR_YE + yb, ((it >> 1) - 1) & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t da0 = a_base + (uint64_t)((b * S::kGBuf) >> 4);
+                const uint64_t db0 = b_base + (uint64_t)((j * S::kW2Block) >> 4);
+#pragma unroll
+                for (int k = 0; k < kHC / 16; ++k)
+                    tc_mma(tmem + kColY + yb * C, da0 + (uint64_t)((k * 32) >> 4), db0 + (uint64_t)((k * 32) >> 4), idesc2,
+                           (j > 0 || k > 0) ? 1u : 0u);
+                tc_commit(bars + BAR_GE + b);                  // the G buffer is free once these MMAs have read it
+                if (j == NCH - 1) tc_commit(bars + BAR_YF + yb);
+                if (++j == NCH) { j = 0; ++it; }
+            }
+        }
+    } else if (warp >= kFirstEpiWarp) {
+        // ---------------------------------------------------------------- epilogue warps
+        // Two groups of eight warps; group 0 takes the even chunks (H / G buffer 0), group 1 the odd ones, so that the
+        // waits of one group (TMEM load, proxy fence, hand-over to the MMA warp) are covered by the arithmetic of the other.
+        const int ew = warp - kFirstEpiWarp;
+        const int grp = ew >> 3;
+        const int quarter = warp & 3;                          // TMEM lanes this warp may read: 32 * (warp id % 4) ...
+        const int colh = (ew >> 2) & 1;                        // ... and its half of a chunk's columns
+        const int row = quarter * 32 + lane;                   // pixel of the tile
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+        const float* bias_s = reinterpret_cast<const float*>(sm + S::kBias);
+        T* __restrict__ yout = (T*)a.y;
+        static_assert(NCH % 2 == 0, "chunks alternate between the two epilogue groups");
+        constexpr int CQ = C / 4;                                       // channels per warp: (group, column half) picks a quarter
+        static_assert(CQ % 8 == 0, "a warp reads its channels in groups of 8 columns");
+        const int cq0 = (grp * 2 + colh) * CQ;
+        bool ok = true;
+        // Y^T of tile `it` -> 16-bit -> global, channel-major.  Called one chunk into the NEXT tile, when the tile's last
+        // GEMM 2 has long finished and the tensor core already has the next tile's chunks to work on.
+        auto y_epilogue = [&](int it) {
+            const int yb = it & 1;
+            const long long p0 = (long long)(blockIdx.x + (long long)it * gridDim.x) * kTilePx;
+            if (!mbar_wait(bars + BAR_YF + yb, (it >> 1) & 1, abort_flag)) return false;
+            tc_fence_after();
+            const bool live = p0 + row < a.N;
+            T* __restrict__ ycol_ptr = yout + (long long)cq0 * a.N + p0 + row;
+#pragma unroll
+            for (int c0 = 0; c0 < CQ; c0 += 8) {
+                uint32_t r[8];
+                tmem_ld8(lane_base + kColY + yb * C + cq0 + c0, r);
+                tmem_ld_wait();
+                if (live) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ycol_ptr[(long long)(c0 + i) * a.N] = from_f<T>(__uint_as_float(r[i]));
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bars + BAR_YE + yb);             // the Y tile is in registers / on its way out
+            return true;
+        };
+        for (int it = 0; ok && it < ntiles_mine; ++it) {
+            for (int j = grp; ok && j < NCH; j += 2) {
+                const int g = it * NCH + j, b = grp;           // global chunk index; its buffers
+                ok = mbar_wait(bars + BAR_HF + b, (g >> 1) & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t r0[16], r1[16];
+                const uint32_t col = kColH + b * kHC + colh * 32;
+                tmem_ld16(lane_base + col, r0);
+                tmem_ld16(lane_base + col + 16, r1);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bars + BAR_HE + b);          // the H chunk is in registers
+                const float4* bias = reinterpret_cast<const float4*>(bias_s + j * kHC + colh * 32);
+                uint32_t packed[16];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const float4 bq = bias[q];
+                    const uint32_t* src = q < 4 ? r0 + 4 * q : r1 + 4 * (q - 4);
+                    const float2 lo = gelu_pair_poly(__fadd2_rn(make_float2(__uint_as_float(src[0]), __uint_as_float(src[1])), make_float2(bq.x, bq.y)));
+                    const float2 hi = gelu_pair_poly(__fadd2_rn(make_float2(__uint_as_float(src[2]), __uint_as_float(src[3])), make_float2(bq.z, bq.w)));
+                    packed[2 * q] = Half2Of<T>::pack(lo.x, lo.y);
+                    packed[2 * q + 1] = Half2Of<T>::pack(hi.x, hi.y);
+                }
+                if (g >= 2) ok = mbar_wait(bars + BAR_GE + b, ((g >> 1) - 1) & 1, abort_flag);
+                if (!ok) break;
+                // G as a K-major operand with the 128-byte swizzle: row = pixel, 16-byte unit u of the row at u ^ (row % 8)
+                unsigned char* grow = sm + S::kG + b * S::kGBuf + row * 128;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int unit = (colh * 4 + u) ^ (row & 7);
+                    *reinterpret_cast<uint4*>(grow + unit * 16) = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+                }
+                fence_async_smem();                                     // generic-proxy writes -> visible to the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bars + BAR_GF + b);
+                if (j == grp && it > 0) ok = y_epilogue(it - 1);
+            }
+        }
+        if (ok && ntiles_mine > 0) y_epilogue(ntiles_mine - 1);
+    }
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, kTmemCols); }
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(a.error_flag, 1);
+}
+
+// ---- host ------------------------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return fn;
+}
+
+// 2-D map of a row-major (rows, cols) matrix of 16-bit elements: box (box_rows, box_cols), inner dimension = columns
+bool make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, long long rows, long long cols, int box_rows, int box_cols,
+              CUtensorMapSwizzle sw) {
+    EncodeFn enc = encode_fn();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int* error_flag_for_current_device() {
+    static std::mutex mu;
+    static int* flags[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!flags[dev]) {
+        // mapped, pinned host memory: the kernel can raise the flag and the host can read it without a copy
+        int* h = nullptr;
+        if (cudaHostAlloc((void**)&h, sizeof(int), cudaHostAllocMapped) != cudaSuccess) return nullptr;
+        *h = 0;
+        flags[dev] = h;
+    }
+    return flags[dev];
+}
+
+template <typename T, int C>
+int launch_mlp(const ss2d_mlp_params* p, cudaStream_t st) {
+    using S = MlpSmem<C>;
+    CUtensorMap tmX, tmW1, tmW2;
+    const long long N = p->N;
+    if (!make_map(&tmX, Fmt<T>::tm, p->x, C, N, C, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return SS2D_ECUDA;
+    if (!make_map(&tmW1, Fmt<T>::tm, p->w1, 4 * C, C, 192, 32, CU_TENSOR_MAP_SWIZZLE_64B)) return SS2D_ECUDA;
+    if (!make_map(&tmW2, Fmt<T>::tm, p->w2, C, 4 * C, C, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return SS2D_ECUDA;
+    int* host_flag = error_flag_for_current_device();
+    if (!host_flag) return SS2D_ECUDA;
+    if (*host_flag) return SS2D_ECUDA;                     // an earlier launch on this device gave up on a wait
+    int* dev_flag = nullptr;
+    if (cudaHostGetDevicePointer((void**)&dev_flag, host_flag, 0) != cudaSuccess) return SS2D_ECUDA;
+    auto kern = mlp_fused_kernel<T, C>;
+    constexpr int smem = S::kTotal + 1024;
+    static bool attr_ok[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_ok[dev & 63]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return SS2D_ECUDA;
+        attr_ok[dev & 63] = true;
+    }
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return SS2D_ECUDA;
+    MlpArgs a;
+    a.b1 = (const float*)p->b1; a.y = p->y; a.N = N;
+    a.tiles = (int)((N + kTilePx - 1) / kTilePx);
+    a.error_flag = dev_flag;
+    const int grid = a.tiles < sms ? a.tiles : sms;
+    kern<<<grid, kThreads, smem, st>>>(tmX, tmW1, tmW2, a);
+    count_launch();
+    return check_launch();
+}
+
+}  // namespace
+
+int mlp_supported(const ss2d_mlp_params* p) {
+    if (!p) return SS2D_EINVAL_NULL;
+    if (!p->x || !p->w1 || !p->b1 || !p->w2 || !p->y) return SS2D_EINVAL_NULL;
+    if (p->dtype != SS2D_BF16 && p->dtype != SS2D_F16) return SS2D_ENOTSUP;     // fp32 maps: the library GEMMs
+    if (p->C <= 0 || p->N <= 0) return SS2D_EINVAL_SHAPE;
+    if (p->hidden != 4 * p->C) return SS2D_ENOTSUP;
+    if (p->C != 96) return SS2D_ENOTSUP;                                         // widths whose weights fit one SM
+    if (p->N % 8 != 0 || p->N > 0x7fffff00LL) return SS2D_ENOTSUP;               // 16-byte row pitch for TMA
+    if (!aligned_to(p->x, 16) || !aligned_to(p->y, 2) || !aligned_to(p->w1, 16) || !aligned_to(p->w2, 16) || !aligned_to(p->b1, 16))
+        return SS2D_EINVAL_ALIGN;
+    return SS2D_OK;
+}
+
+int mlp_fwd(const ss2d_mlp_params* p, cudaStream_t st) {
+    const int rc = mlp_supported(p);
+    if (rc != SS2D_OK) return rc;
+    if (p->dtype == SS2D_BF16) return launch_mlp<__nv_bfloat16, 96>(p, st);
+    return launch_mlp<__half, 96>(p, st);
+}
+
+}  // namespace ss2d

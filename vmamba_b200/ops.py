@@ -526,6 +526,36 @@ def bias_act_(x: torch.Tensor, bias=None, act="gelu", channel_major: bool = Fals
     return x
 
 
+def mlp_supported(C: int, hidden: int, n_pixels: int, dtype: torch.dtype) -> bool:
+    """True when `mlp_fused` takes a channel-major (C, n_pixels) map itself (the library's planner decides)."""
+    if dtype not in (torch.bfloat16, torch.float16):
+        return False
+    from ._lib import MlpParams
+    fake = 4096                                   # an aligned address; the query dereferences nothing
+    p = MlpParams(fake, fake, fake, fake, fake, C, hidden, n_pixels, _DTYPES[dtype], 0)
+    return int(lib().ss2d_mlp_supported(p)) == 0
+
+
+def mlp_fused(x: torch.Tensor, w1: torch.Tensor, b1: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+    """fc2(gelu(fc1(x) + b1)) of Mlp.forward (vmamba.py:1151-1167) on a channel-major (C, B, H, W) map in one
+    kernel on the tcgen05 tensor cores; the fc2 bias is left to the residual update that follows.
+    w1: (4C, C), b1: (4C,) fp32, w2: (C, 4C)."""
+    _require_cuda(x, w1, b1, w2)
+    if x.dim() != 4 or not x.is_contiguous():
+        raise RuntimeError("mlp_fused expects a contiguous channel-major (C, B, H, W) map")
+    from ._lib import MlpParams
+    C = x.shape[0]
+    N = x.numel() // C
+    w1 = w1.contiguous().to(x.dtype)
+    w2 = w2.contiguous().to(x.dtype)
+    b1 = b1.contiguous().float()
+    y = torch.empty_like(x)
+    p = MlpParams(x.data_ptr(), w1.data_ptr(), b1.data_ptr(), w2.data_ptr(), y.data_ptr(), C, w1.shape[0], N, dtype_code(x), 0)
+    with torch.cuda.device(x.device):
+        check(lib().ss2d_mlp_fwd(p, _stream(x)), "ss2d_mlp_fwd")
+    return y
+
+
 def dwconv3x3_act(x: torch.Tensor, weight: torch.Tensor, bias=None, act="silu", channel_major: bool = False) -> torch.Tensor:
     """act(depthwise 3x3 convolution, padding 1) of a (B, D, H, W) map ((D, B, H, W) with
     `channel_major`): conv2d + SiLU in front of the SS2D core (vmamba.py:1582-1583).
