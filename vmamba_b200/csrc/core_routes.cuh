@@ -110,6 +110,7 @@ __device__ __forceinline__ void walk_route(const RouteArgs& a, const int b, cons
     // 16-bit maps accumulate in units of 1 / ln 2 (the step size stays a base-2 logarithm); the merge rescales
     const float Dk = __ldg(a.Dskip + k * a.D + d) * (kPrecise ? 1.f : 1.f / kLn2);
     const bool first_lane = lane == (kBack ? 31 : 0);
+    const bool swap_units = (lane & 4) != 0;
     const int last_seg = L - S;                        // L is a multiple of S
     const int nc = (L + CH - 1) / CH;
     const int half = (nc + 1) >> 1;
@@ -215,17 +216,38 @@ __device__ __forceinline__ void walk_route(const RouteArgs& a, const int b, cons
             }
         }
         float* q = acc + min(e, last_seg);
-        if (s >= nA) {                                           // same for the whole warp
-            float old[S];
-            Vec<float, S>::load_plain(q, old);
+        if constexpr (S == 8) {
+            // A lane's eight floats are two 16-byte units, 32 bytes from the next lane's: taken in the same order by every
+            // lane, lanes j and j + 4 of a quarter-warp would meet in the same banks on every access.  Lanes 4..7 of each
+            // group of eight therefore take their upper unit first.
+            const int first = swap_units ? 4 : 0, second = 4 - first;
+            float2 u0 = swap_units ? y[2] : y[0], u1 = swap_units ? y[3] : y[1];     // unit accessed first
+            float2 v0 = swap_units ? y[0] : y[2], v1 = swap_units ? y[1] : y[3];     // unit accessed second
+            if (s >= nA) {                                       // same for the whole warp
+                float o[4], w[4];
+                Vec<float, 4>::load_plain(q + first, o);
+                Vec<float, 4>::load_plain(q + second, w);
+                u0 = __fadd2_rn(u0, make_float2(o[0], o[1])); u1 = __fadd2_rn(u1, make_float2(o[2], o[3]));
+                v0 = __fadd2_rn(v0, make_float2(w[0], w[1])); v1 = __fadd2_rn(v1, make_float2(w[2], w[3]));
+            }
+            if (active) {
+                const float a0[4] = {u0.x, u0.y, u1.x, u1.y}, a1[4] = {v0.x, v0.y, v1.x, v1.y};
+                Vec<float, 4>::store(q + first, a0);
+                Vec<float, 4>::store(q + second, a1);
+            }
+        } else {
+            if (s >= nA) {
+                float old[S];
+                Vec<float, S>::load_plain(q, old);
 #pragma unroll
-            for (int j = 0; j < NP; ++j) y[j] = __fadd2_rn(y[j], make_float2(old[2 * j], old[2 * j + 1]));
-        }
-        if (active) {
-            float yo[S];
+                for (int j = 0; j < NP; ++j) y[j] = __fadd2_rn(y[j], make_float2(old[2 * j], old[2 * j + 1]));
+            }
+            if (active) {
+                float yo[S];
 #pragma unroll
-            for (int j = 0; j < NP; ++j) { yo[2 * j] = y[j].x; yo[2 * j + 1] = y[j].y; }
-            Vec<float, S>::store(q, yo);
+                for (int j = 0; j < NP; ++j) { yo[2 * j] = y[j].x; yo[2 * j + 1] = y[j].y; }
+                Vec<float, S>::store(q, yo);
+            }
         }
         e += STEP;
     }

@@ -36,7 +36,7 @@ constexpr int kHC = 64;            // hidden units per chunk = N of GEMM 1, K of
 constexpr int kEpiWarps = 16;
 constexpr int kFirstEpiWarp = 4;   // warps 0..3: TMA producer, GEMM 1 issuer, GEMM 2 issuer, (spare)
 constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
-constexpr unsigned kSpinLimit = 1u << 22;
+constexpr unsigned kSpinLimit = 1u << 18;
 
 // ---- PTX wrappers --------------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -50,30 +50,24 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One attempt: the thread sleeps until the phase completes or about `kWaitSliceNs` have passed, so a waiting warp
+// issues a handful of instructions per slice instead of spinning against the warps that have arithmetic to do.
+constexpr uint32_t kWaitSliceNs = 20000;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n .reg .pred p;\n"
-        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         " selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitSliceNs) : "memory");
     return ok != 0;
 }
-// Non-blocking test of a phase.
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n .reg .pred p;\n"
-        " mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        " selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false when the limit ran out or another role has already given up.
+// Bounded wait (at most kSpinLimit slices, a few seconds).  Returns false when the limit ran out or another role has
+// already given up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     for (unsigned i = 0; i < kSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
+        if (*abort_flag) return false;
     }
     *abort_flag = 1;
     return false;
