@@ -28,8 +28,14 @@ MODEL = "vmamba_tiny_s1l8"
 BATCH = 128            # per GPU, the batch the reference quotes its throughput on
 IMG = 224
 NUM_CLASSES = 1000
-METRIC = "VMamba-T img/s @224^2 bf16 (batch 128 per GPU, inference)"
 UNIT = "img/s"
+FEATURES = False       # config 3: the dense-prediction backbone returns four feature maps instead of logits
+LABELS = {"vmamba_tiny_s1l8": "VMamba-T", "vmamba_small_s2l15": "VMamba-S", "vmamba_base_s2l15": "VMamba-B"}
+
+
+def metric_name() -> str:
+    what = "dense-prediction backbone, four feature maps" if FEATURES else "inference"
+    return f"{LABELS.get(MODEL, MODEL)} img/s @{IMG}^2 bf16 (batch {BATCH} per GPU, {what})"
 
 
 def peaks():
@@ -96,7 +102,8 @@ def synthetic_state_dict(seed: int = 0):
     """Random init of VMamba-T in the reference's value distributions (no checkpoint can travel)."""
     from oracle import backbone_oracle as BO     # host-side generator of the synthetic weights only
     cfg = BO.CONFIGS[MODEL]
-    return BO.random_state_dict(cfg["depths"], cfg["dims"], cfg["d_state"], cfg["ssm_ratio"], 4.0, NUM_CLASSES, 3, seed)
+    return BO.random_state_dict(cfg["depths"], cfg["dims"], cfg["d_state"], cfg["ssm_ratio"], 4.0, NUM_CLASSES, 3, seed,
+                                with_outnorm=FEATURES)
 
 
 def cpu_baseline(sd, n_images: int, repeats: int = 1):
@@ -134,7 +141,7 @@ def run_reference(args):
     sec = sum(times) / len(times)
     val = n_img / sec
     line = {
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
+        "impl": "reference", "metric": metric_name(), "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
         "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"{MODEL} inference, {IMG}x{IMG}, CPU oracle (port of the reference's pure-torch path); "
@@ -200,6 +207,35 @@ def roofline_of_core(model, peak_gbs, peak_kind, batch=None, iters=20):
     }
 
 
+def mlp_leg(model, batch=None, iters=20):
+    """The fused MLP kernel (tcgen05) of the first stage-0 block alone, beside the three launches it replaces."""
+    import torch
+    from vmamba_b200 import ops
+    b = model.blocks[0][0]
+    C, B = b.w1.shape[1], batch or 128
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((C, B, 56, 56), device="cuda", generator=g).to(model.dtype)
+    if not ops.mlp_supported(C, b.w1.shape[0], x.numel() // C, x.dtype):
+        return None
+
+    def unfused():
+        h = torch.matmul(b.w1, x.view(C, -1)).view(b.w1.shape[0], B, 56, 56)
+        ops.bias_act_(h, b.b1f, "gelu", channel_major=True)
+        return torch.matmul(b.w2, h.view(b.w1.shape[0], -1))
+    t_f = time_events(lambda: ops.mlp_fused(x, b.w1, b.b1f, b.w2), iters)
+    t_u = time_events(unfused, iters)
+    flops = 4.0 * C * b.w1.shape[0] * (x.numel() // C)
+    tf_peak = None
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            tf_peak = float(json.load(f)["bf16_tflops"])
+    tf = flops / (t_f * 1e-3) / 1e12
+    return {"kernel": "mlp_fused_kernel (fc1 + bias + GELU + fc2, tcgen05)", "workload": f"C={C} hidden={b.w1.shape[0]} pixels={x.numel() // C} bf16",
+            "ms": t_f, "tflops": tf, "peak_tflops": tf_peak, "frac_of_measured_bf16_peak": (tf / tf_peak) if tf_peak else None,
+            "replaced_launches_ms": t_u, "note": "bound by the GELU epilogue on the FMA pipe, not by the tensor pipe"}
+
+
 def op_sweep(args):
     """Operator-surface sweep (the selective-scan op alone, bf16 u/delta/B/C, fp32 state and output) over
     d_state x channels x length, plus CrossScan / CrossMerge; one JSON line per cell with the achieved
@@ -215,20 +251,26 @@ def op_sweep(args):
         for D in (96, 384, 768):
             for L in (196, 3136, 16384, 65536):
                 Bt = max(1, int(args.sweep_gb * 1e9 / (16 * L * (D + N))))
-                u = torch.randn((Bt, K * D, L), device="cuda", generator=g).to(torch.bfloat16)
-                delta = torch.randn((Bt, K * D, L), device="cuda", generator=g).to(torch.bfloat16)
-                Bm = torch.randn((Bt, K, N, L), device="cuda", generator=g).to(torch.bfloat16)
-                Cm = torch.randn((Bt, K, N, L), device="cuda", generator=g).to(torch.bfloat16)
+                # drawn in bf16 directly: an fp32 draw of a 20 GB tensor would need 40 GB more for a moment
+                u = torch.randn((Bt, K * D, L), device="cuda", generator=g, dtype=torch.bfloat16)
+                delta = torch.randn((Bt, K * D, L), device="cuda", generator=g, dtype=torch.bfloat16)
+                Bm = torch.randn((Bt, K, N, L), device="cuda", generator=g, dtype=torch.bfloat16)
+                Cm = torch.randn((Bt, K, N, L), device="cuda", generator=g, dtype=torch.bfloat16)
                 A = -torch.arange(1, N + 1, device="cuda", dtype=torch.float32).repeat(K * D, 1)
                 Dp = torch.ones(K * D, device="cuda")
                 dt = torch.exp(torch.rand(K * D, device="cuda", generator=g) * (math.log(0.1) - math.log(1e-3)) + math.log(1e-3))
                 bias = dt + torch.log(-torch.expm1(-dt))
-                ms = time_events(lambda: vb.selective_scan_fwd(u, delta, A, Bm, Cm, Dp, bias, True, True), args.steps)
+                out = torch.empty((Bt, K * D, L), device="cuda", dtype=torch.float32)     # one output buffer for all launches
+                ms = time_events(lambda: vb.selective_scan_fwd(u, delta, A, Bm, Cm, Dp, bias, True, True, out=out), args.steps)
+                del out
                 nbytes = Bt * L * (K * D * (2 * 2 + 4) + 2 * K * N * 2) + 4 * (K * D * N + 2 * K * D)
                 gbs = nbytes / (ms * 1e-3) / 1e9
                 print(json.dumps({"op": "selective_scan_fwd", "dtype": "bf16->f32", "d_state": N, "D": D, "L": L, "batch": Bt,
                                   "ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": gbs, "frac": gbs / peak,
                                   "peak_gbs": peak, "peak_kind": f"of {kind}"}), flush=True)
+                if args.sweep_gb > 8:          # the gradient cell needs four more maps of this size: small sweeps only
+                    del u, delta, Bm, Cm
+                    continue
                 # gradients of the same cell: reads u, delta, dout (fp32), B, C; writes du, ddelta, dB, dC
                 from vmamba_b200 import ops as _ops
                 dout = torch.randn((Bt, K * D, L), device="cuda", generator=g)
@@ -241,7 +283,7 @@ def op_sweep(args):
                                   "peak_gbs": peak, "peak_kind": f"of {kind}"}), flush=True)
                 del u, delta, Bm, Cm, dout
     for (D, H) in ((96, 56), (384, 14), (96, 256)):
-        Bt = max(1, int(args.sweep_gb * 1e9 / (10 * D * H * H)))
+        Bt = max(1, int(min(args.sweep_gb, 8.0) * 1e9 / (10 * D * H * H)))
         x = torch.randn((Bt, D, H, H), device="cuda", generator=g).to(torch.bfloat16)
         ms = time_events(lambda: vb.cross_scan_fwd(x, 0), args.steps)
         nb = x.numel() * 2 * 5
@@ -332,7 +374,11 @@ def run_ours(args):
     from vmamba_b200.backbone import VSSMInfer
     from vmamba_b200.runner import GraphedBackbone
 
-    global MODEL, BATCH, IMG
+    global MODEL, BATCH, IMG, FEATURES
+    if args.config == 2:       # VMamba-S, global batch 256 sharded over the ranks
+        MODEL, BATCH, IMG = "vmamba_small_s2l15", max(1, 256 // world), 224
+    elif args.config == 3:     # VMamba-B as a dense-prediction backbone: 1024 x 1024, global batch 16, four feature maps
+        MODEL, BATCH, IMG, FEATURES = "vmamba_base_s2l15", max(1, 16 // world), 1024, True
     if args.model:
         MODEL = args.model
     if args.batch:
@@ -346,6 +392,10 @@ def run_ours(args):
         print(json.dumps({"roofline": roofline_of_core(model, peak, kind, args.roofline_batch, args.steps)}), flush=True)
         return
 
+    if args.mlp_only:          # the fused MLP kernel alone (small cases for profiler captures)
+        print(json.dumps({"mlp_fused": mlp_leg(model, args.roofline_batch, args.steps)}), flush=True)
+        return
+
     if args.forward_only:      # plain (un-graphed) forwards and nothing else: the case profiler captures use
         img = torch.randn((BATCH, 3, IMG, IMG), device=f"cuda:{local}").to(torch.bfloat16)
         for _ in range(max(1, args.steps)):
@@ -357,14 +407,17 @@ def run_ours(args):
     # synthetic images: N(0,1), seeded per rank, bf16 in pinned host memory
     g = torch.Generator().manual_seed(1234 + rank)
     host_img = torch.randn((BATCH, 3, IMG, IMG), generator=g).to(torch.bfloat16).pin_memory()
-    host_out = torch.empty((BATCH, NUM_CLASSES), dtype=torch.bfloat16).pin_memory()
     dev_img = host_img.cuda(non_blocking=True)
     torch.cuda.synchronize()
 
     # ---- one forward captured in a CUDA graph (static input / output buffers): the package's own runner ----
-    runner = GraphedBackbone(model, (BATCH, 3, IMG, IMG), dtype=torch.bfloat16)
+    runner = GraphedBackbone(model, (BATCH, 3, IMG, IMG), dtype=torch.bfloat16, features=FEATURES)
     runner.input.copy_(dev_img)
     dev_out = runner.output
+    outs = dev_out if isinstance(dev_out, (list, tuple)) else [dev_out]
+    host_outs = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+    host_out = host_outs if FEATURES else host_outs[0]
+    d2h_bytes = sum(o.numel() * o.element_size() for o in outs)
     launches_per_forward = runner.launches_per_forward
     runner.replay()
     torch.cuda.synchronize()
@@ -409,19 +462,24 @@ def run_ours(args):
         return timed(step_e2e, steps, 0)
 
     warm = max(args.warmup, 3)
+    # several timed regions of exactly `steps` steps each; the median region is the one reported
+    n_regions = 3 if args.steps <= 100 else 1
     sampler = ClockSampler(local).start() if rank == 0 else None
-    ms_dev = timed(step_device, args.steps, warm)
+    regions_dev = [timed(step_device, args.steps, warm if i == 0 else 0) for i in range(n_regions)]
     clocks = sampler.stop() if sampler else None
-    ms_e2e = timed_e2e(args.steps, warm)
+    regions_e2e = [timed_e2e(args.steps, warm if i == 0 else 1) for i in range(n_regions)]
+    ms_dev = sorted(regions_dev)[n_regions // 2]
+    ms_e2e = sorted(regions_e2e)[n_regions // 2]
 
     total_imgs = BATCH * world * args.steps
     value = total_imgs / (ms_dev * 1e-3)
     e2e = total_imgs / (ms_e2e * 1e-3)
 
-    roof = cpu = parity = refmod = None
+    roof = cpu = parity = refmod = mlp = None
     if rank == 0:
         peak, kind = peaks()
         roof = roofline_of_core(model, peak, kind)
+        mlp = mlp_leg(model)
         if world == 1 and not args.no_cpu_baseline and MODEL == "vmamba_tiny_s1l8" and IMG == 224:
             v, cores, desc = cpu_baseline(sd, 4)
             cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
@@ -450,11 +508,12 @@ def run_ours(args):
         return
     act_mb = BATCH * 96 * 56 * 56 * 2 / 1e6
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
+        "metric": metric_name(), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
         "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{MODEL} (" + ("VMamba-T, dims 96/192/384/768, depths 2/2/8/2, " if MODEL == "vmamba_tiny_s1l8" else "") +
                                f"v05_noz, d_state 1) backbone inference, random init, {BATCH} images of 3x{IMG}x{IMG} per GPU per step",
+                   "output": "four LayerNorm'ed feature maps (strides 4, 8, 16, 32)" if FEATURES else "logits",
                    "global_batch": BATCH * world, "parallelism": f"replicas x{world}, batch-sharded, no collective",
                    "l2": f"no flush needed: one stage-0 activation is {act_mb:.0f} MB and a step streams several GB, "
                          "far more than the 126 MB L2",
@@ -463,10 +522,12 @@ def run_ours(args):
                    "published_reference": "1686 img/s on A100, fp32 without AMP (README.md:91) - other hardware and "
                                           "precision, so vs_baseline stays null"},
         "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": host_img.numel() * 2 * world,
-                "d2h_bytes_per_step": host_out.numel() * 2 * world, "ms_per_step": ms_e2e / args.steps},
+                "d2h_bytes_per_step": d2h_bytes * world, "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": launches_per_forward * args.steps * world,
         "gpu_launches_per_step_per_gpu": launches_per_forward,
         "clocks": clocks, "roofline": roof,
+        "timed_regions": {"count": n_regions, "steps_each": args.steps, "reported": "median region",
+                          "device_ms": regions_dev, "e2e_ms": regions_e2e},
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
@@ -474,6 +535,8 @@ def run_ours(args):
         line["parity"] = parity
     if refmod is not None:
         line["reference_modules"] = refmod
+    if mlp is not None:
+        line["mlp_fused"] = mlp
     print(json.dumps(line), flush=True)
 
 
@@ -485,6 +548,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-modules", action="store_true", help="skip the leg that runs the staged reference modules")
+    ap.add_argument("--config", type=int, default=1, choices=[1, 2, 3, 4],
+                    help="BASELINE configuration: 1 VMamba-T batch 128 per GPU (default); 2 VMamba-S, global batch 256 over the "
+                         "ranks; 3 VMamba-B 1024x1024 dense-prediction backbone, global batch 16 over the ranks, four feature "
+                         "maps read back; 4 the operator sweep with inputs sized by the 40 GB rule (1 GPU)")
     ap.add_argument("--model", default=None, help="vmamba_tiny_s1l8 (default) | vmamba_small_s2l15 | vmamba_base_s2l15")
     ap.add_argument("--batch", type=int, default=None, help="images per GPU per step (default 128)")
     ap.add_argument("--img", type=int, default=None, help="image side (default 224)")
@@ -492,8 +559,11 @@ def main():
     ap.add_argument("--sweep-gb", type=float, default=2.0, help="input gigabytes per sweep cell")
     ap.add_argument("--roofline-only", action="store_true", help="time only the fused SS2D core chain of stage 0")
     ap.add_argument("--roofline-batch", type=int, default=None, help="batch for --roofline-only (default 128)")
+    ap.add_argument("--mlp-only", action="store_true", help="time only the fused MLP kernel of a stage-0 block (batch: --roofline-batch)")
     ap.add_argument("--forward-only", action="store_true", help="run --steps plain forwards of the model and exit (profiler captures)")
     args = ap.parse_args()
+    if args.config == 4:
+        args.op_sweep, args.sweep_gb = True, 40.0
     if args.op_sweep:
         op_sweep(args)
     elif args.impl == "reference":
