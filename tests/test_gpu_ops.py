@@ -98,6 +98,55 @@ def test_selective_scan_lengths(vb, L, dtype):
     assert torch.equal(y, y2), "the scan must be deterministic"
 
 
+def test_selective_scan_every_length_to_300(vb):
+    """Every row length from 1 to 300 (each residue of the vector widths, every partial last step), fp32 and bf16,
+    in one launch per length against the C oracle."""
+    rng = np.random.default_rng(300)
+    Bt, K, Cd, N = 1, 2, 3, 1
+    for dtype in ("f32", "bf16"):
+        td = torch.float32 if dtype == "f32" else torch.bfloat16
+        for L in range(1, 301):
+            inp = dict(u=rng.standard_normal((Bt, K * Cd, L), dtype=np.float32),
+                       delta=rng.standard_normal((Bt, K * Cd, L), dtype=np.float32),
+                       A=-np.exp(rng.standard_normal((K * Cd, N), dtype=np.float32) * 0.5),
+                       B=rng.standard_normal((Bt, K, N, L), dtype=np.float32),
+                       C=rng.standard_normal((Bt, K, N, L), dtype=np.float32),
+                       D=rng.standard_normal(K * Cd, dtype=np.float32),
+                       bias=(rng.standard_normal(K * Cd, dtype=np.float32) - 3.0))
+            if dtype == "bf16":
+                for k in ("u", "delta", "B", "C"):
+                    inp[k] = O.round_bf16(inp[k])
+            ref = CO.selective_scan(inp["u"], inp["delta"], inp["A"], inp["B"], inp["C"], inp["D"], inp["bias"], True)
+            y = vb.selective_scan_fn(dev(inp["u"], td), dev(inp["delta"], td), dev(inp["A"]), dev(inp["B"], td),
+                                     dev(inp["C"], td), dev(inp["D"]), dev(inp["bias"]), True, True)
+            assert O.max_rel_err(host(y), ref) <= TOL_F32, f"L = {L}, {dtype}"
+
+
+@pytest.mark.parametrize("L,KD", [(3136, 384), (16384, 96), (196, 3072)])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_selective_scan_dstate16_sweep_shapes(vb, L, KD, dtype):
+    """d_state 16 on the shapes of the operator sweep: stage-0 and long rows, 3072 rows (4 x 768 channels), fp32 and
+    bf16 activations with fp32 state, A = -(1..16) as at initialisation, against the C oracle."""
+    rng = np.random.default_rng(L + KD)
+    Bt, K, N = 2, 4, 16
+    inp = dict(u=rng.standard_normal((Bt, KD, L), dtype=np.float32),
+               delta=rng.standard_normal((Bt, KD, L), dtype=np.float32),
+               A=-np.tile(np.arange(1, N + 1, dtype=np.float32)[None], (KD, 1)),
+               B=rng.standard_normal((Bt, K, N, L), dtype=np.float32),
+               C=rng.standard_normal((Bt, K, N, L), dtype=np.float32),
+               D=np.ones(KD, np.float32),
+               bias=(rng.standard_normal(KD).astype(np.float32) - 4.0))
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    if dtype == "bf16":
+        for k in ("u", "delta", "B", "C"):
+            inp[k] = O.round_bf16(inp[k])
+    ref = CO.selective_scan(inp["u"], inp["delta"], inp["A"], inp["B"], inp["C"], inp["D"], inp["bias"], True)
+    y = vb.selective_scan_fn(dev(inp["u"], td), dev(inp["delta"], td), dev(inp["A"]), dev(inp["B"], td),
+                             dev(inp["C"], td), dev(inp["D"]), dev(inp["bias"]), True, True)
+    assert y.dtype == torch.float32
+    assert O.max_rel_err(host(y), ref) <= TOL_F32      # the inputs are rounded on both sides: fp32 tolerance holds
+
+
 @pytest.mark.parametrize("N,L,K", [(2, 100, 4), (16, 640, 4), (16, 196, 1), (64, 50, 2), (256, 33, 1)])
 def test_selective_scan_dstate(vb, N, L, K):
     rng = np.random.default_rng(N * 1000 + L)
@@ -260,6 +309,21 @@ def test_bias_act(vb, shape, act):
 
 
 # ------------------------------------------------------------------------------ fused core
+def _project_library(x, w):
+    """What `fused.project` returns, by library calls only (batched GEMMs and copies): the cross-check of
+    `ss2d_route_expand`."""
+    from vmamba_b200.fused import RouteStreams
+    B, D, H, W = x.shape
+    L, R, N = H * W, w.dt_rank, w.d_state
+    C = R + 2 * N
+    xd = torch.matmul(w.wx, x.reshape(B, D, L)).view(B, 2, 2, C, H, W)    # route k = 2*i + j
+    xd_even = xd[:, :, 0].reshape(B, 2, C, L)
+    xd_odd = xd[:, :, 1].transpose(-1, -2).reshape(B, 2, C, L)
+    delta_even = torch.matmul(w.wdt[0::2], xd_even[:, :, :R])
+    delta_odd = torch.matmul(w.wdt[1::2], xd_odd[:, :, :R])
+    return RouteStreams(xd_even[:, :, R:].contiguous(), xd_odd[:, :, R:].contiguous(), delta_even, delta_odd, False)
+
+
 def _core_case(Bt, D, H, W, N, seed, Cmodel=None):
     import math
     rng = np.random.default_rng(seed)
@@ -318,6 +382,36 @@ def test_fused_core_bf16(vb, shape):
     assert O.max_rel_err(host(y), ref) <= TOL_BF16
 
 
+@pytest.mark.parametrize("shape", [(1, 8, 50, 84), (2, 6, 63, 64), (1, 4, 45, 48), (2, 8, 100, 168)])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_fused_core_detection_map_sizes(vb, shape, dtype):
+    """Map sizes of detection / segmentation inputs (800 x 1344 at strides 16 and 8, odd sides): whichever kernel the
+    planner picks, or the operator-surface chain when it refuses, the result matches the oracle."""
+    c = _core_case(*shape, N=1, seed=sum(shape) + 7, Cmodel=64)
+    ref = O.ss2d_core(c["x"], c["wx"], c["wdt"], c["bias"], c["A_logs"], c["Ds"], c["lw"], c["lb"], d_state=1, dt_rank=c["R"],
+                      act_dtype=("bf16" if dtype == "bf16" else "f32"))
+    y = _run_core(vb, c, dtype)
+    assert O.max_rel_err(host(y), ref) <= (TOL_F32 if dtype == "f32" else TOL_BF16)
+
+
+@pytest.mark.parametrize("shape", [(1, 16, 56, 56), (1, 8, 14, 14)])
+def test_fused_core_extreme_step_sizes(vb, shape):
+    """delta + bias from -40 to +60: softplus in its two tails.  The 16-bit fast path computes log2(1 + 2^x') with the
+    argument clamped at 126 (exact up to x = 87) and flushes e^x below 2^-24 to zero; both stay inside the bf16
+    tolerance of the reference, which switches to x above 20 and keeps e^x below."""
+    c = _core_case(*shape, N=1, seed=5, Cmodel=32)
+    rng = np.random.default_rng(9)
+    # the extremes come from the fp32 bias (exact on both sides); delta itself stays of order one, so that its own
+    # 16-bit rounding does not decide the comparison
+    c["bias"] = (c["bias"] + rng.uniform(-35, 65, c["bias"].shape)).astype(np.float32)
+    for dtype, tol in (("f32", TOL_F32), ("bf16", TOL_BF16)):
+        ref = O.ss2d_core(c["x"], c["wx"], c["wdt"], c["bias"], c["A_logs"], c["Ds"], c["lw"], c["lb"], d_state=1,
+                          dt_rank=c["R"], act_dtype=("bf16" if dtype == "bf16" else "f32"))
+        y = _run_core(vb, c, dtype)
+        assert np.isfinite(host(y)).all()
+        assert O.max_rel_err(host(y), ref) <= tol, dtype
+
+
 @pytest.mark.parametrize("shape,N,Cm", [((2, 96, 56, 56), 1, None), ((3, 384, 14, 14), 1, None), ((2, 768, 7, 7), 1, None),
                                         ((1, 5, 9, 11), 1, None), ((2, 12, 6, 10), 4, 64), ((1, 256, 16, 8), 2, 1024)])
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
@@ -330,7 +424,7 @@ def test_route_expand_vs_library_projection(vb, shape, N, Cm, dtype):
                              dev(c["lb"]), d_state=N, dt_rank=c["R"], dtype=td)
     x = dev(c["x"], td)
     got = fused.project(x, w)
-    ref = fused.project_library(x, w)
+    ref = _project_library(x, w)
     # channel-major maps: the streams come out as (pair, rows, B, L); same values
     got_cm = fused.project(x.transpose(0, 1).contiguous(), w, channel_major=True)
     for g_, r_, name in zip(got_cm, ref, ("bc_even", "bc_odd", "delta_even", "delta_odd")):

@@ -86,6 +86,54 @@ def test_static_scratch_entry_matches_workspace_entry(dtype):
         assert torch.equal(y_new, y_ref), "same kernels on the same inputs: results must be bit-identical"
 
 
+def test_static_scratch_entry_against_the_oracle_and_without_norm():
+    """The same entry point against the CPU oracle (not only against its sibling), and its `with_norm = 0` form, which
+    needs no scratch at all: the merged fp32 map goes straight to y, and strided y is refused as by `ss2d_core_fwd`."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from oracle import ss2d_oracle as O
+    import vmamba_b200 as vb
+    from vmamba_b200 import _lib, fused
+    L = _lib.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    rng = np.random.default_rng(3)
+    Bt, D, H, W, N, K = 2, 24, 12, 20, 1, 4
+    R = math.ceil(D / 16)
+    x = rng.standard_normal((Bt, D, H, W), dtype=np.float32)
+    wx = (rng.standard_normal((K * (R + 2 * N), D), dtype=np.float32) / np.sqrt(D)).astype(np.float32)
+    wdt = (rng.standard_normal((K * D, R), dtype=np.float32) * R ** -0.5).astype(np.float32)
+    dt = np.exp(rng.random((K, D), dtype=np.float32) * (np.log(0.1) - np.log(1e-3)) + np.log(1e-3))
+    bias = (dt + np.log(-np.expm1(-dt))).astype(np.float32)
+    A_logs = (0.2 * rng.standard_normal((K * D, N))).astype(np.float32)
+    Ds = (1 + 0.2 * rng.standard_normal(K * D)).astype(np.float32)
+    lw, lb = (1 + 0.2 * rng.standard_normal(D)).astype(np.float32), (0.2 * rng.standard_normal(D)).astype(np.float32)
+    ref, parts = O.ss2d_core(x, wx, wdt, bias, A_logs, Ds, lw, lb, d_state=N, dt_rank=R, return_parts=True)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    w = vb.CoreWeights.build(dev(wx), dev(wdt), dev(bias), dev(A_logs), dev(Ds), dev(lw), dev(lb), d_state=N, dt_rank=R,
+                             dtype=torch.float32)
+    xt = dev(x)
+    proj = fused.project(xt, w)
+    y = torch.full((Bt, D, H, W), float("nan"), device="cuda")
+    assert L.ss2d_core_fwd_static(_params(vb, xt, proj, w, y), stream) == 0
+    torch.cuda.synchronize()
+    assert O.max_rel_err(y.cpu().numpy(), ref) <= 1e-4
+    # without the LayerNorm: fp32 merged map, no scratch involved
+    ym = torch.full((Bt, D, H, W), float("nan"), device="cuda")
+    p = _params(vb, xt, proj, w, ym)
+    p.with_norm = 0
+    assert L.ss2d_core_workspace_bytes(p) == 0
+    assert L.ss2d_core_fwd_static(p, stream) == 0
+    torch.cuda.synchronize()
+    assert O.max_rel_err(ym.cpu().numpy(), parts["merged"]) <= 1e-4
+    # a strided y cannot take the dense merged map: refused, as by ss2d_core_fwd, before any launch
+    p.y_batch_stride, p.y_channel_stride = H * W, Bt * H * W
+    before = _lib.launch_count()
+    assert L.ss2d_core_fwd_static(p, stream) == _lib.SS2D_ENOTSUP
+    assert L.ss2d_core_fwd(p, stream) == _lib.SS2D_ENOTSUP
+    assert _lib.launch_count() == before
+
+
 def test_static_scratch_entry_rejects_oversized_and_bad_calls():
     from vmamba_b200 import _lib
     L = _lib.lib()

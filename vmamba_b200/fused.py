@@ -116,20 +116,6 @@ class RouteStreams(tuple):
         return self
 
 
-def project_library(x: torch.Tensor, w: CoreWeights):
-    """Same result as `project` with library calls only (batched GEMMs and copies); kept as the
-    cross-check of `ss2d_route_expand` in the tests."""
-    B, D, H, W = x.shape
-    L, R, N = H * W, w.dt_rank, w.d_state
-    C = R + 2 * N
-    xd = torch.matmul(w.wx, x.reshape(B, D, L)).view(B, 2, 2, C, H, W)    # route k = 2*i + j
-    xd_even = xd[:, :, 0].reshape(B, 2, C, L)
-    xd_odd = xd[:, :, 1].transpose(-1, -2).reshape(B, 2, C, L)
-    delta_even = torch.matmul(w.wdt[0::2], xd_even[:, :, :R])
-    delta_odd = torch.matmul(w.wdt[1::2], xd_odd[:, :, :R])
-    return RouteStreams(xd_even[:, :, R:].contiguous(), xd_odd[:, :, R:].contiguous(), delta_even, delta_odd, False)
-
-
 def scan_merge_norm(x: torch.Tensor, proj, w: CoreWeights, *, with_norm: bool = True, out_dtype=None,
                     workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                     channel_major: bool = False) -> torch.Tensor:
