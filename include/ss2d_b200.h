@@ -35,7 +35,8 @@ typedef enum ss2d_status {
     SS2D_ENOTSUP = -6,         /* valid request that this build does not implement */
     SS2D_ECUDA = -7,           /* the CUDA runtime reported an error at launch */
     SS2D_EWORKSPACE = -8,      /* workspace missing or too small */
-    SS2D_ETOOBIG = -9          /* problem exceeds the built-in scratch of an allocation-free entry point */
+    SS2D_ETOOBIG = -9,         /* problem exceeds the built-in scratch of an allocation-free entry point */
+    SS2D_EINVAL_DEVICE = -10   /* debug checks on: a pointer is host memory or belongs to another GPU than the current one */
 } ss2d_status;
 
 /* ------------------------------------------------------------------------------------
@@ -297,6 +298,13 @@ typedef struct ss2d_mlp_params {
 
 int ss2d_mlp_supported(const ss2d_mlp_params *p);
 int ss2d_mlp_fwd(const ss2d_mlp_params *p, void *cuda_stream);
+
+/* Debug checks (off by default; on with the environment variable SS2D_DEBUG_CHECKS=1 at load time or by this call).
+ * When on, every entry point that launches kernels first asks the driver about each pointer it was given
+ * (cudaPointerGetAttributes) and returns SS2D_EINVAL_DEVICE, before any launch, for host memory or memory of a GPU
+ * other than the current one - the consistency the reference gets from its tensor checks (u.is_cuda() and same-device
+ * guards, selective_scan_oflex.cpp:152-204).  Costs a driver call per pointer, hence the switch.  Returns the old state. */
+int ss2d_set_debug_checks(int on);
 
 /* Allocation-free form of ss2d_core_fwd.  It has no counterpart in the reference: it exists for
  * callers that can hand over inputs and outputs but cannot obtain device memory themselves (an

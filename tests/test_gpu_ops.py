@@ -816,3 +816,74 @@ def test_mlp_fused_refuses_what_it_cannot_take(vb):
     x = torch.zeros((192, 1, 8, 16), device="cuda", dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):
         ops.mlp_fused(x, torch.zeros((768, 192), device="cuda"), torch.zeros(768, device="cuda"), torch.zeros((192, 768), device="cuda"))
+
+
+# ------------------------------------------------------------------ debug checks, guard bands
+@pytest.mark.gpu
+def test_debug_checks_refuse_host_pointers_before_any_launch(vb):
+    """With the debug checks on, a pointer that is not memory of the current GPU is refused (SS2D_EINVAL_DEVICE) before
+    anything is launched; off (the default), the same valid call goes through unchanged."""
+    from vmamba_b200 import _lib
+    L = _lib.lib()
+    x = torch.randn(2, 3, 5, 7, device="cuda")
+    out = torch.empty(2, 4, 3, 35, device="cuda")
+    host = torch.randn(2, 3, 5, 7).pin_memory()
+    stream = torch.cuda.current_stream().cuda_stream
+    old = L.ss2d_set_debug_checks(1)
+    try:
+        before = _lib.launch_count()
+        bad = _lib.CrossParams(host.data_ptr(), out.data_ptr(), _lib.SS2D_F32, 0, 2, 3, 5, 7)
+        assert L.ss2d_cross_scan(bad, stream) == -10
+        assert _lib.launch_count() == before
+        assert b"debug checks" in L.ss2d_strerror(-10)
+        good = _lib.CrossParams(x.data_ptr(), out.data_ptr(), _lib.SS2D_F32, 0, 2, 3, 5, 7)
+        assert L.ss2d_cross_scan(good, stream) == 0
+        assert np.array_equal(host_np(out), O.cross_scan(host_np(x), 0))
+    finally:
+        L.ss2d_set_debug_checks(old)
+
+
+def host_np(t):
+    return t.detach().float().cpu().numpy()
+
+
+@pytest.mark.gpu
+def test_outputs_are_fully_written_and_stay_inside_their_buffers(vb):
+    """Every output is carved out of a larger buffer filled with NaN, with guard bands on both sides: after the call
+    the guards are untouched and no NaN is left inside (outputs are overwritten, never accumulated into)."""
+    from vmamba_b200 import fused, ops
+    G = 4096
+
+    def carve(shape, dtype):
+        n = int(np.prod(shape))
+        buf = torch.full((n + 2 * G,), float("nan"), device="cuda", dtype=dtype)
+        return buf, buf[G:G + n].view(shape)
+
+    def intact(buf, view):
+        return bool(torch.isnan(buf[:G]).all() and torch.isnan(buf[-G:]).all() and torch.isfinite(view.float()).all())
+
+    c = _core_case(2, 24, 56, 56, N=1, seed=77, Cmodel=32)
+    for td in (torch.float32, torch.bfloat16):
+        w = vb.CoreWeights.build(dev(c["wx"]), dev(c["wdt"]), dev(c["bias"]), dev(c["A_logs"]), dev(c["Ds"]), dev(c["lw"]),
+                                 dev(c["lb"]), d_state=1, dt_rank=c["R"], dtype=td)
+        x = dev(c["x"], td)
+        proj = fused.project(x, w)
+        buf, y = carve(x.shape, td)
+        fused.scan_merge_norm(x, proj, w, out=y)                      # route-stream kernel (56 x 56) + LayerNorm
+        assert intact(buf, y)
+        x14 = x[:, :, :14, :14].contiguous()
+        buf, y = carve(x14.shape, td)
+        fused.scan_merge_norm(x14, fused.project(x14, w), w, out=y)   # plane kernel (14 x 14) + LayerNorm
+        assert intact(buf, y)
+    # operator surface
+    u = torch.randn(2, 12, 300, device="cuda")
+    buf, out = carve((2, 12, 300), torch.float32)
+    ops.selective_scan_fwd(u, torch.randn_like(u), -torch.rand(12, 1, device="cuda"), torch.randn(2, 4, 1, 300, device="cuda"),
+                           torch.randn(2, 4, 1, 300, device="cuda"), torch.ones(12, device="cuda"), torch.zeros(12, device="cuda"),
+                           True, True, out=out)
+    assert intact(buf, out)
+    # fused MLP: ragged last tile
+    xm = torch.randn(96, 3, 10, 12, device="cuda").to(torch.bfloat16)
+    buf, y = carve(xm.shape, torch.bfloat16)
+    ops.mlp_fused(xm, torch.randn(384, 96, device="cuda") / 10, torch.zeros(384, device="cuda"), torch.randn(96, 384, device="cuda") / 20, out=y)
+    assert intact(buf, y)

@@ -128,6 +128,7 @@ EXPORTS = {
     "ss2d_dwconv3x3_act": (ctypes.c_int, [ctypes.POINTER(PointwiseParams), _vp]),
     "ss2d_mlp_supported": (ctypes.c_int, [ctypes.POINTER(MlpParams)]),
     "ss2d_mlp_fwd": (ctypes.c_int, [ctypes.POINTER(MlpParams), _vp]),
+    "ss2d_set_debug_checks": (ctypes.c_int, [ctypes.c_int]),
     "ss2d_version": (ctypes.c_int, []),
     "ss2d_strerror": (ctypes.c_char_p, [ctypes.c_int]),
     "ss2d_launch_count": (_i64, []),

@@ -536,7 +536,7 @@ def mlp_supported(C: int, hidden: int, n_pixels: int, dtype: torch.dtype) -> boo
     return int(lib().ss2d_mlp_supported(p)) == 0
 
 
-def mlp_fused(x: torch.Tensor, w1: torch.Tensor, b1: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+def mlp_fused(x: torch.Tensor, w1: torch.Tensor, b1: torch.Tensor, w2: torch.Tensor, out=None) -> torch.Tensor:
     """fc2(gelu(fc1(x) + b1)) of Mlp.forward (vmamba.py:1151-1167) on a channel-major (C, B, H, W) map in one
     kernel on the tcgen05 tensor cores; the fc2 bias is left to the residual update that follows.
     w1: (4C, C), b1: (4C,) fp32, w2: (C, 4C)."""
@@ -549,7 +549,9 @@ def mlp_fused(x: torch.Tensor, w1: torch.Tensor, b1: torch.Tensor, w2: torch.Ten
     w1 = w1.contiguous().to(x.dtype)
     w2 = w2.contiguous().to(x.dtype)
     b1 = b1.contiguous().float()
-    y = torch.empty_like(x)
+    y = torch.empty_like(x) if out is None else out
+    if y.shape != x.shape or y.dtype != x.dtype or not y.is_contiguous():
+        raise RuntimeError("out must be a contiguous tensor of x's shape and dtype")
     p = MlpParams(x.data_ptr(), w1.data_ptr(), b1.data_ptr(), w2.data_ptr(), y.data_ptr(), C, w1.shape[0], N, dtype_code(x), 0)
     with torch.cuda.device(x.device):
         check(lib().ss2d_mlp_fwd(p, _stream(x)), "ss2d_mlp_fwd")
