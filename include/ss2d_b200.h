@@ -141,10 +141,13 @@ int ss2d_cross_merge(const ss2d_cross_params *p, void *cuda_stream);
  * forms, vmamba.py:41-245; CrossScanF / CrossMergeF, csm_triton.py:182-273).  In both calls in_channel_first names
  * the layout of the map side ((B, C, H, W) or (B, H, W, C)) and out_channel_first the layout of the routes side
  * ((B, 4, C, L) or (B, L, 4, C)), as in the reference.
- *   ss2d_cross_scan_ex : map -> routes;  one_by_one: in is (B, 4, C, H, W), route k reads its own map
- *   ss2d_cross_merge_ex: routes -> map (B, C, L) or (B, L, C);  one_by_one: no sum, out is (B, 4, C, L)
- * one_by_one is implemented for channel-first tensors on both sides; with scans 1 it passes the four maps
- * through unchanged, as the reference does.  Index-only variants, not tuned.
+ *   ss2d_cross_scan_ex : map -> routes;  one_by_one: in is (B, 4, C, H, W) or, channel-last, (B, H, W, 4, C), and
+ *                        route k reads its own map
+ *   ss2d_cross_merge_ex: routes -> map (B, C, L) or (B, L, C);  one_by_one: no sum, out is (B, 4, C, L) or, with
+ *                        in_channel_first 0, (B, L, 4, C)
+ * one_by_one with channel-first tensors on both sides takes scans 0-3; with a channel-last side it takes scans 0-2,
+ * the route sets the reference's GPU kernel defines (csm_triton.py:313-336), and returns SS2D_ENOTSUP for 3.  With
+ * scans 1 the four maps pass through in row-major order.  Index-only variants, not tuned.
  * -------------------------------------------------------------------------------- */
 typedef struct ss2d_cross_ex_params {
     const void *in;

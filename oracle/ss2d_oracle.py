@@ -136,18 +136,20 @@ def cross_scan_ex(x: np.ndarray, scans: int = 0, in_channel_first: bool = True, 
                   one_by_one: bool = False) -> np.ndarray:
     """CrossScan with the reference's layout flags.
 
-    x: (B, C, H, W) or, channel-last, (B, H, W, C); one_by_one (channel-first only here): (B, 4, C, H, W),
-    route k reads its own map x[:, k] (vmamba.py:132-157).  Result (B, 4, C, L) or, with out_channel_first
-    False, (B, L, 4, C) (vmamba.py:79-82)."""
+    x: (B, C, H, W) or, channel-last, (B, H, W, C); one_by_one: (B, 4, C, H, W) or, channel-last, (B, H, W, 4, C),
+    route k reads its own map x[:, k] (csm_triton.py:88-131).  Result (B, 4, C, L) or, with out_channel_first
+    False, (B, L, 4, C) (csm_triton.py:420, the shapes the reference's GPU path allocates).  The reference's torch
+    path returns the same memory for every combination but one_by_one, scans 1, channel-first in and channel-last
+    out, where its `flatten(2, 3)` on the 5-d tensor merges C with H before the permute (csm_triton.py:101, 126);
+    its GPU path (csm_triton.py:403-431) has no such case, and this restatement follows the GPU path there."""
     if one_by_one:
-        if not (in_channel_first and out_channel_first):
-            raise NotImplementedError("one_by_one is restated for channel-first tensors only")
-        B, K, C, H, W = x.shape
+        xc = x if in_channel_first else np.ascontiguousarray(x.transpose(0, 3, 4, 1, 2))   # (B,H,W,4,C) -> (B,4,C,H,W)
+        B, K, C, H, W = xc.shape
         assert K == 4
-        y = np.stack([cross_scan(np.ascontiguousarray(x[:, k]), scans)[:, k] for k in range(4)], axis=1)
-        if scans == 1:                       # vmamba.py:142-143: `x.flatten(2, 3)` on the 5-d tensor merges C with H
-            y = x.reshape(B, 4, C * H, W).copy()
-        return y
+        y = np.stack([cross_scan(np.ascontiguousarray(xc[:, k]), scans)[:, k] for k in range(4)], axis=1)
+        if scans == 1 and in_channel_first and out_channel_first:
+            return xc.reshape(B, 4, C * H, W).copy()    # csm_triton.py:101: the torch path's shape, same memory
+        return y if out_channel_first else np.ascontiguousarray(y.transpose(0, 3, 1, 2))
     xc = x if in_channel_first else np.ascontiguousarray(np.moveaxis(x, -1, 1))
     y = cross_scan(xc, scans)                                   # (B, 4, C, L)
     return y if out_channel_first else np.ascontiguousarray(y.transpose(0, 3, 1, 2))
@@ -157,18 +159,17 @@ def cross_merge_ex(ys: np.ndarray, scans: int = 0, in_channel_first: bool = True
                    one_by_one: bool = False) -> np.ndarray:
     """CrossMerge with the reference's layout flags: `out_channel_first` names the layout of the routes ys
     ((B, 4, C, H, W) or (B, H, W, 4, C)), `in_channel_first` the layout of the result ((B, C, L) or (B, L, C)),
-    as in cross_merge_fwd (vmamba.py:87-130).  one_by_one (channel-first only here): every route is brought back
-    to row-major order separately, no sum: (B, 4, C, L) (vmamba.py:189-218)."""
+    as in cross_merge_fwd (vmamba.py:87-130).  one_by_one: every route is brought back to row-major order
+    separately, no sum: (B, 4, C, L) or, with in_channel_first False, (B, L, 4, C) (csm_triton.py:134-179)."""
     if one_by_one:
-        if not (in_channel_first and out_channel_first):
-            raise NotImplementedError("one_by_one is restated for channel-first tensors only")
-        B, K, C, H, W = ys.shape
+        yc = ys if out_channel_first else np.ascontiguousarray(ys.transpose(0, 3, 4, 1, 2))
+        B, K, C, H, W = yc.shape
         out = np.empty((B, 4, C, H * W), dtype=ys.dtype)
         for k in range(4):
-            only = np.zeros_like(ys)
-            only[:, k] = ys[:, k]
+            only = np.zeros_like(yc)
+            only[:, k] = yc[:, k]
             out[:, k] = cross_merge(only, scans)                # x + 0 is exact: the un-permuted route k
-        return out
+        return out if in_channel_first else np.ascontiguousarray(out.transpose(0, 3, 1, 2))
     yc = ys if out_channel_first else np.ascontiguousarray(ys.transpose(0, 3, 4, 1, 2))     # (B,H,W,K,D) -> (B,K,D,H,W)
     y = cross_merge(yc, scans)                                  # (B, C, L)
     return y if in_channel_first else np.ascontiguousarray(y.transpose(0, 2, 1))

@@ -2,8 +2,10 @@
 
     python oracle/stage_ref.py [--ref /path/to/VMamba]
 
-Copies, unmodified, the one-file distribution `vmamba.py` and `classification/models/csms6s.py`
-of a MzeroMiko/VMamba checkout into `oracle/_ref/`.  That folder is git-ignored: nothing of the
+Copies, unmodified, the one-file distribution `vmamba.py` and, from `classification/models/`,
+`csms6s.py`, `csm_triton.py` and the full `vmamba.py` (staged as `tree_vmamba.py`: it holds the
+cascade scan mode, which the one-file distribution dropped) of a MzeroMiko/VMamba checkout into
+`oracle/_ref/`.  That folder is git-ignored: nothing of the
 reference enters the history, the copy only travels with the working tree to machines that have
 no checkout (the GPU box), where `tests/test_gpu_reference_modules.py` and `bench.py` run the
 unmodified modules on this library's operators.  Without a checkout the script does nothing and
@@ -24,7 +26,9 @@ import warnings
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF_DIR = os.path.join(HERE, "_ref")
-FILES = {"vmamba.py": "vmamba.py", "csms6s.py": os.path.join("classification", "models", "csms6s.py")}
+_MODELS = os.path.join("classification", "models")
+FILES = {"vmamba.py": "vmamba.py", "csms6s.py": os.path.join(_MODELS, "csms6s.py"),
+         "csm_triton.py": os.path.join(_MODELS, "csm_triton.py"), "tree_vmamba.py": os.path.join(_MODELS, "vmamba.py")}
 
 
 def stage(ref_root: str = "/root/reference") -> list:
@@ -77,6 +81,13 @@ def _install_stubs():
             setattr(nn, name, None)
         fv.nn = nn
         sys.modules.update({"fvcore": fv, "fvcore.nn": nn})
+    if "mamba2.ssd_minimal" not in sys.modules:
+        # classification/models/vmamba.py:33-36 imports the chunked Mamba-2 scan of its `m0` family at module import;
+        # that family is not staged, the name only has to resolve
+        pkg, mod = types.ModuleType("mamba2"), types.ModuleType("mamba2.ssd_minimal")
+        mod.selective_scan_chunk_fn = None
+        pkg.ssd_minimal = mod
+        sys.modules.update({"mamba2": pkg, "mamba2.ssd_minimal": mod})
 
 
 def load(name: str = "vmamba.py", module_name: str | None = None):
@@ -89,9 +100,13 @@ def load(name: str = "vmamba.py", module_name: str | None = None):
     spec = importlib.util.spec_from_file_location(module_name, path)
     mod = importlib.util.module_from_spec(spec)
     sys.modules[module_name] = mod
-    with warnings.catch_warnings():
-        warnings.simplefilter("ignore")
-        spec.loader.exec_module(mod)
+    sys.path.insert(0, REF_DIR)         # tree_vmamba.py falls back to `from csm_triton import ...` (vmamba.py:22-30)
+    try:
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            spec.loader.exec_module(mod)
+    finally:
+        sys.path.remove(REF_DIR)
     return mod
 
 

@@ -146,6 +146,19 @@ def main():
                     outl[f"{tag}_merge_s{scans}_i{int(icf)}_o{int(ocf)}"] = npf(ref.cross_merge_fn(yin, icf, ocf, False, scans, True))
             outl[f"{tag}_scan1b1_s{scans}"] = npf(ref.cross_scan_fn(ycf, True, True, True, scans, True))
             outl[f"{tag}_merge1b1_s{scans}"] = npf(ref.cross_merge_fn(ycf, True, True, True, scans, True))
+            # one_by_one with a channel-last side: the torch Functions define scans 0 and 1 (their branch for 2 indexes the
+            # wrong axes, csm_triton.py:117-123); for scans 1 with channel-first in and channel-last out their flatten(2, 3)
+            # merges C with H before the permute, which the reference's GPU kernel does not: that combination is left out
+            if scans in (0, 1):
+                ycl = ycf.permute(0, 3, 4, 1, 2).contiguous()
+                for icf in (True, False):
+                    for ocf in (True, False):
+                        if icf and ocf:
+                            continue
+                        key = f"s{scans}_i{int(icf)}_o{int(ocf)}"
+                        if not (scans == 1 and icf and not ocf):
+                            outl[f"{tag}_scan1b1_{key}"] = npf(ref.cross_scan_fn(ycf if icf else ycl, icf, ocf, True, scans, True))
+                        outl[f"{tag}_merge1b1_{key}"] = npf(ref.cross_merge_fn(ycf if ocf else ycl, icf, ocf, True, scans, True))
     np.savez_compressed(os.path.join(HERE, "csm_layouts_small.npz"), **outl)
 
     # ---- 2. selective scan, small cases over the flag space ---------------------

@@ -117,8 +117,8 @@ def test_operators_refuse_cpu_tensors():
         vb.selective_scan_fn(x, x, x, x, x, backend="torch")
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         vb.cross_scan_fn(x, in_channel_first=False)
-    with pytest.raises(NotImplementedError):         # one_by_one exists for channel-first tensors only
-        vb.cross_scan_fn(torch.zeros(1, 3, 4, 4, 2), in_channel_first=False, out_channel_first=False, one_by_one=True)
+    with pytest.raises(NotImplementedError):         # one_by_one with a channel-last side: route sets 0-2 only
+        vb.cross_scan_fn(torch.zeros(1, 3, 3, 4, 2), in_channel_first=False, out_channel_first=False, one_by_one=True, scans=3)
 
 
 def test_install_patches_a_reference_like_module():

@@ -722,8 +722,38 @@ def test_cross_scan_merge_layout_flags_and_one_by_one(vb):
             assert np.array_equal(host(out), g[f"{tag}_scan1b1_s{scans}"]), scans
             out = vb.cross_merge_fn(dev(ys), True, True, True, scans)
             assert np.array_equal(host(out), g[f"{tag}_merge1b1_s{scans}"]), scans
+            if scans == 3:
+                continue
+            # one map per route with a channel-last side: the stored results of the reference's torch Functions where
+            # they define one (scans 0 and 1), the oracle's restatement of its GPU kernel for every combination
+            ycl = np.ascontiguousarray(ys.transpose(0, 3, 4, 1, 2))
+            for icf, ocf in ((True, False), (False, True), (False, False)):
+                key = f"s{scans}_i{int(icf)}_o{int(ocf)}"
+                xin, yin = (ys if icf else ycl), (ys if ocf else ycl)
+                xt = dev(xin).requires_grad_(True)
+                out = vb.cross_scan_fn(xt, icf, ocf, True, scans)
+                want = O.cross_scan_ex(xin, scans, icf, ocf, True)
+                assert out.shape == want.shape and np.array_equal(host(out), want), key
+                if f"{tag}_scan1b1_{key}" in g.files:
+                    assert np.array_equal(host(out), g[f"{tag}_scan1b1_{key}"]), key
+                gy = np.random.default_rng(scans + 20).standard_normal(out.shape).astype(np.float32)
+                out.backward(dev(gy))
+                gy5 = gy.reshape(ys.shape) if ocf else gy.reshape(ycl.shape)
+                want = O.cross_merge_ex(gy5, scans, icf, ocf, True)
+                assert np.array_equal(host(xt.grad).reshape(want.shape), want), key
+                yt = dev(yin).requires_grad_(True)
+                m = vb.cross_merge_fn(yt, icf, ocf, True, scans)
+                want = O.cross_merge_ex(yin, scans, icf, ocf, True)
+                assert m.shape == want.shape and np.array_equal(host(m), want), key
+                if f"{tag}_merge1b1_{key}" in g.files:
+                    assert np.array_equal(host(m), g[f"{tag}_merge1b1_{key}"]), key
+                gm = np.random.default_rng(scans + 30).standard_normal(m.shape).astype(np.float32)
+                m.backward(dev(gm))
+                gx = gm.reshape(ys.shape[0], 4, ys.shape[2], H, W) if icf else gm.reshape(ycl.shape)
+                want = O.cross_scan_ex(gx, scans, icf, ocf, True)
+                assert np.array_equal(host(yt.grad).reshape(want.shape), want), key
     with pytest.raises(NotImplementedError):
-        vb.cross_scan_fn(dev(g["5x7_ys"]).permute(0, 3, 4, 1, 2).contiguous(), False, False, True, 0)
+        vb.cross_scan_fn(dev(g["6x6_ys"]).permute(0, 3, 4, 1, 2).contiguous(), False, False, True, 3)
 
 
 @pytest.mark.gpu

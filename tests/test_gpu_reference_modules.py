@@ -9,6 +9,7 @@ recipe, vmamba.py:2384).  The tests skip where no checkout was staged.
 """
 import os
 import sys
+import zlib
 
 import numpy as np
 import pytest
@@ -176,3 +177,123 @@ def test_top1_like_for_like_against_reference_bf16(vb, ref):
           f"reference bf16-vs-fp32 logit noise {noise:.3e}")
     assert (lib16 - want16).abs().max().item() <= 4 * noise + 1e-3
     assert int(clear.sum()) > 0 and bool(agree[clear].all())
+
+
+# ------------------------------------------------------------------------------------------------
+# every forward type of the reference's SS2D that runs in the reference itself, on this library
+# ------------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def tree():
+    """The full `classification/models/vmamba.py` with its own `csm_triton.py` and `csms6s.py` (no compiled
+    extension importable: its selective scan is the reference's torch recurrence)."""
+    if not stage_ref.staged("tree_vmamba.py"):
+        pytest.skip("classification/models/vmamba.py not staged")
+    names = ("csm_triton", "csms6s", "selective_scan_cuda_oflex", "selective_scan_cuda_core", "selective_scan_cuda")
+    saved = {k: sys.modules.pop(k, None) for k in names}
+    try:
+        mod = stage_ref.load("tree_vmamba.py", "vmamba_tree_reference_gpu")
+        yield mod, sys.modules["csm_triton"], sys.modules["csms6s"]
+    finally:
+        for k in names:
+            sys.modules.pop(k, None)
+            if saved[k] is not None:
+                sys.modules[k] = saved[k]
+
+
+class _torch_path:
+    """The reference's own eager path: its torch CrossScanF / CrossMergeF (csm_triton.py:182-273) and
+    `selective_scan_torch` (csms6s.py:30-70), whatever backend the module asks for."""
+
+    def __init__(self, tree):
+        self.mod, self.csm, self.s6 = tree
+
+    def __enter__(self):
+        mod, csm, s6 = self.mod, self.csm, self.s6
+        self.saved = mod.cross_scan_fn, mod.cross_merge_fn, mod.selective_scan_fn
+
+        def scan(x, in_channel_first=True, out_channel_first=True, one_by_one=False, scans=0, force_torch=False):
+            return csm.CrossScanF.apply(x, in_channel_first, out_channel_first, one_by_one, scans)
+
+        def merge(y, in_channel_first=True, out_channel_first=True, one_by_one=False, scans=0, force_torch=False):
+            return csm.CrossMergeF.apply(y, in_channel_first, out_channel_first, one_by_one, scans)
+
+        eager = s6.selective_scan_fn        # bound now: for the one-file distribution `s6` is `mod` itself
+        mod.cross_scan_fn, mod.cross_merge_fn = scan, merge
+        mod.selective_scan_fn = lambda *a, **k: eager(*a, **{**k, "backend": "torch"})
+        return self
+
+    def __exit__(self, *exc):
+        self.mod.cross_scan_fn, self.mod.cross_merge_fn, self.mod.selective_scan_fn = self.saved
+
+
+FORWARD_TYPES = [
+    # forward_type, d_state, channel_first, (H, W)
+    ("v0", 16, False, (7, 9)), ("v0seq", 16, False, (7, 9)), ("v0", 1, False, (14, 14)),
+    ("v01", 4, False, (7, 9)), ("v02", 1, False, (7, 9)), ("v03", 2, True, (7, 9)), ("v04", 1, False, (9, 7)),
+    ("v05", 1, True, (14, 14)), ("v05_noz_oact", 1, True, (7, 9)), ("v05_nozact", 16, False, (7, 9)), ("v3", 1, True, (7, 9)),
+    ("v051d", 1, True, (7, 9)), ("v052d", 1, False, (7, 9)),
+    ("v052d3", 1, True, (8, 8)),        # the debug route set: only the one-file distribution has it (vmamba.py:62-68)
+    ("v052dc", 1, True, (7, 9)), ("v052dc", 4, True, (14, 14)),
+    ("v05_onsoftmax", 1, True, (7, 9)), ("v05_ondwconv3", 1, True, (7, 9)),
+]
+
+
+@pytest.mark.parametrize("ft,N,cf,hw", FORWARD_TYPES)
+def test_reference_ss2d_forward_types_on_library(vb, tree, ref, ft, N, cf, hw):
+    """One SS2D module of the reference per forward type (vmamba.py:425-445: v0, v0seq, v01-v05 and their
+    postfixes, the one-direction / two-direction / debug route sets, the cascade row-then-column mode, v3), built by
+    the reference and run unchanged with `install()`: output and gradients against the same module on the
+    reference's eager path."""
+    if ft == "v052d3":
+        tree = (ref, ref, ref)
+    mod = tree[0]
+    torch.manual_seed(zlib.crc32(ft.encode()) % 1000)
+    d_model = 24
+    m = mod.SS2D(d_model=d_model, d_state=N, ssm_ratio=2.0, dt_rank="auto", d_conv=3, conv_bias=False,
+                 forward_type=ft, channel_first=cf).cuda().eval()
+    shape = (2, d_model) + hw if cf else (2,) + hw + (d_model,)
+    x = torch.randn(shape, device="cuda")
+    old = torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cudnn.allow_tf32 = torch.backends.cuda.matmul.allow_tf32 = False
+    params = [p for p in m.parameters() if p.requires_grad]
+    try:
+        with _torch_path(tree):
+            xr = x.clone().requires_grad_(True)
+            want = m(xr)
+            gout = torch.randn_like(want)
+            want_g = torch.autograd.grad(want, [xr] + params, gout, allow_unused=True)
+        vb.install(mod)
+        try:
+            from vmamba_b200 import _lib
+            n0 = _lib.launch_count()
+            xg = x.clone().requires_grad_(True)
+            got = m(xg)
+            assert _lib.launch_count() > n0, "the module's forward did not reach the CUDA library"
+            got_g = torch.autograd.grad(got, [xg] + params, gout, allow_unused=True)
+            with torch.no_grad():
+                plain = m(x)
+            with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+                got16 = m(x)
+        finally:
+            vb.uninstall(mod)
+    finally:
+        torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = old
+    w = want.detach().cpu().numpy()
+    assert O.max_rel_err(got.detach().cpu().numpy(), w) <= TOL_F32
+    assert O.max_rel_err(plain.cpu().numpy(), w) <= TOL_F32
+    assert O.max_rel_err(got16.float().cpu().numpy(), w) <= 3e-2
+    for a, b in zip(got_g, want_g):
+        assert (a is None) == (b is None)
+        if a is not None:
+            assert O.max_rel_err(a.cpu().numpy(), b.cpu().numpy()) <= 5e-4
+
+
+def test_reference_xv_forward_types_raise_in_the_reference(tree):
+    """The `xv*` family hands 4-d B / C maps to `cross_scan_fn(..., one_by_one=True)` (vmamba.py:871-872), and both of
+    the reference's Functions unpack five dimensions there (csm_triton.py:186, 406): the family does not run in
+    the reference, so there is nothing to be a drop-in for."""
+    mod = tree[0]
+    m = mod.SS2D(d_model=16, d_state=1, ssm_ratio=2.0, dt_rank="auto", d_conv=3, conv_bias=False,
+                 forward_type="xv1a", channel_first=True).cuda().eval()
+    with pytest.raises(ValueError), torch.no_grad():
+        m(torch.randn(2, 16, 6, 6, device="cuda"))

@@ -53,6 +53,16 @@ def test_cross_scan_merge_layout_flags_and_one_by_one():
                     assert np.array_equal(O.cross_merge_ex(yin, scans, icf, ocf), g[f"{tag}_merge_{key}"]), key
             assert np.array_equal(O.cross_scan_ex(ys, scans, one_by_one=True), g[f"{tag}_scan1b1_s{scans}"]), scans
             assert np.array_equal(O.cross_merge_ex(ys, scans, one_by_one=True), g[f"{tag}_merge1b1_s{scans}"]), scans
+            if scans > 1:
+                continue
+            ycl = np.ascontiguousarray(ys.transpose(0, 3, 4, 1, 2))     # one map per route, channel-last
+            for icf, ocf in ((True, False), (False, True), (False, False)):
+                key = f"s{scans}_i{int(icf)}_o{int(ocf)}"
+                if f"{tag}_scan1b1_{key}" in g.files:       # scans 1, i1_o0: the torch path's C*H merge, not stored
+                    got = O.cross_scan_ex(ys if icf else ycl, scans, icf, ocf, True)
+                    assert np.array_equal(got, g[f"{tag}_scan1b1_{key}"]), key
+                got = O.cross_merge_ex(ys if ocf else ycl, scans, icf, ocf, True)
+                assert np.array_equal(got, g[f"{tag}_merge1b1_{key}"]), key
 
 
 def _case(g, n):

@@ -402,7 +402,9 @@ static int fill_ex(const ss2d_cross_ex_params* p, CrossExArgs& a) {
     if (p->B <= 0 || p->C <= 0 || p->H <= 0 || p->W <= 0) return SS2D_EINVAL_SHAPE;
     if (p->scans == 3 && p->H != p->W) return SS2D_EINVAL_SHAPE;
     if (p->H * p->W > 0x3fffffffLL) return SS2D_EINVAL_SHAPE;
-    if (p->one_by_one && !(p->in_channel_first && p->out_channel_first)) return SS2D_ENOTSUP;
+    // one map per route with a channel-last side: the route sets the reference's GPU kernel defines (csm_triton.py:313-336:
+    // 0, 1 and 2; its torch branch for 2 indexes the wrong axes, csm_triton.py:117-123, and neither path has 3)
+    if (p->one_by_one && !(p->in_channel_first && p->out_channel_first) && p->scans > 2) return SS2D_ENOTSUP;
     const size_t s = dtype_size(p->dtype);
     if (!aligned_to(p->in, s) || !aligned_to(p->out, s)) return SS2D_EINVAL_ALIGN;
     a.in = p->in; a.out = p->out;

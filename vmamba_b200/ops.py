@@ -268,8 +268,10 @@ selective_scan_cuda_oflex = _ExtShim()
 # CrossScan / CrossMerge
 # --------------------------------------------------------------------------------------------
 def _check_flags(in_channel_first, out_channel_first, one_by_one, scans):
-    if one_by_one and not (in_channel_first and out_channel_first):
-        raise NotImplementedError("vmamba_b200: one_by_one CrossScan/CrossMerge is implemented for channel-first tensors only")
+    if one_by_one and not (in_channel_first and out_channel_first) and scans not in (0, 1, 2):
+        raise NotImplementedError("vmamba_b200: one_by_one CrossScan/CrossMerge with a channel-last side is implemented for "
+                                  "scans 0, 1 and 2, the route sets the reference's GPU kernel defines "
+                                  "(csm_triton.py:313-336)")
     if scans not in (0, 1, 2, 3):
         raise NotImplementedError(f"vmamba_b200: scans={scans} is not implemented")
 
@@ -296,11 +298,19 @@ def cross_scan_fwd(x: torch.Tensor, scans: int = 0, in_channel_first=True, out_c
             check(lib().ss2d_cross_scan(p, _stream(x)), "ss2d_cross_scan")
         return y
     if one_by_one:
-        B, K, C, H, W = x.shape
+        if in_channel_first:
+            B, K, C, H, W = x.shape
+        else:
+            B, H, W, K, C = x.shape
         if K != 4:
-            raise RuntimeError("one_by_one expects (B, 4, C, H, W)")
-        # the reference's `x.flatten(2, 3)` for scans 1 merges C with H (vmamba.py:142-143): same shape here
-        oshape = (B, 4, C * H, W) if scans == 1 else (B, 4, C, H * W)
+            raise RuntimeError("one_by_one expects (B, 4, C, H, W) or (B, H, W, 4, C)")
+        if not out_channel_first:
+            oshape = (B, H * W, 4, C)
+        elif in_channel_first and scans == 1:
+            # the reference's `x.flatten(2, 3)` for scans 1 merges C with H (vmamba.py:142-143): same shape here
+            oshape = (B, 4, C * H, W)
+        else:
+            oshape = (B, 4, C, H * W)
     elif in_channel_first:
         B, C, H, W = x.shape
     else:
@@ -341,7 +351,7 @@ def cross_merge_fwd(ys: torch.Tensor, scans: int = 0, in_channel_first=True, out
     if K != 4:
         raise RuntimeError("cross_merge expects four routes")
     if one_by_one:
-        oshape = (B, 4, C, H * W)
+        oshape = (B, 4, C, H * W) if in_channel_first else (B, H * W, 4, C)
     else:
         oshape = (B, C, H * W) if in_channel_first else (B, H * W, C)
     y = torch.empty(oshape, device=ys.device, dtype=ys.dtype)
@@ -360,7 +370,10 @@ class CrossScanF(torch.autograd.Function):
         _check_flags(in_channel_first, out_channel_first, one_by_one, scans)
         ctx.flags = (bool(in_channel_first), bool(out_channel_first), bool(one_by_one), scans)
         if one_by_one:
-            B, _, C, H, W = x.shape
+            if in_channel_first:
+                B, _, C, H, W = x.shape
+            else:
+                B, H, W, _, C = x.shape
         elif in_channel_first:
             B, C, H, W = x.shape
         else:
@@ -376,7 +389,7 @@ class CrossScanF(torch.autograd.Function):
         ys = ys.contiguous().view(B, 4, C, H, W) if ocf else ys.contiguous().view(B, H, W, 4, C)
         y = cross_merge_fwd(ys, scans, icf, ocf, obo)
         if obo:
-            y = y.view(B, 4, C, H, W)
+            y = y.view(B, 4, C, H, W) if icf else y.view(B, H, W, 4, C)
         else:
             y = y.view(B, C, H, W) if icf else y.view(B, H, W, C)
         return y, None, None, None, None
@@ -402,9 +415,9 @@ class CrossMergeF(torch.autograd.Function):
         icf, ocf, obo, scans = ctx.flags
         B, C, H, W = ctx.shape
         if obo:
-            if scans == 1:          # the forward passed the maps through; so does the adjoint
+            if scans == 1 and icf and ocf:      # the forward passed the maps through; so does the adjoint
                 return x.contiguous().view(B, 4, C, H, W), None, None, None, None
-            xin = x.contiguous().view(B, 4, C, H, W)
+            xin = x.contiguous().view(B, 4, C, H, W) if icf else x.contiguous().view(B, H, W, 4, C)
         else:
             xin = x.contiguous().view(B, C, H, W) if icf else x.contiguous().view(B, H, W, C)
         xs = cross_scan_fwd(xin, scans, icf, ocf, obo)
