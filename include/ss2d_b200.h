@@ -302,6 +302,33 @@ typedef struct ss2d_mlp_params {
 int ss2d_mlp_supported(const ss2d_mlp_params *p);
 int ss2d_mlp_fwd(const ss2d_mlp_params *p, void *cuda_stream);
 
+/* ------------------------------------------------------------------------------------
+ * 1x1 projection of a channel-major map:  out (M, N) = w (M, K) . x (K, N) (+ bias[m]), N = B*H*W pixels
+ * contiguous in every row.  With the stacked x_proj weights of the four routes as w ((4 (R + 2N), D)) this is
+ * the x_proj contraction of forward_corev2 (vmamba.py:1536-1538: a grouped conv1d on the (B, 4 D, L) scan copy)
+ * computed on the un-scanned map, which a 1x1 projection permits; with a bias it is Linear2d.forward
+ * (vmamba.py:1062-1075).
+ *   x   (K, N)  dtype (SS2D_BF16 or SS2D_F16), rows x_row_stride elements apart (0 = N; a multiple of 8)
+ *   w   (M, K)  dtype, row-major, M <= 256, K a multiple of 32
+ *   bias (M) fp32 or NULL;   out (M, N) dtype, rows out_row_stride elements apart (0 = N)
+ * Runs on the tcgen05 tensor cores (fp32 accumulation in tensor memory), operands staged by TMA.
+ * ss2d_linear_supported returns SS2D_OK when ss2d_linear_fwd takes the problem, else the status it would
+ * return without launching (SS2D_ENOTSUP: use a library GEMM).
+ * -------------------------------------------------------------------------------- */
+typedef struct ss2d_linear_params {
+    const void *x;
+    const void *w;
+    const void *bias;
+    void *out;
+    int64_t M, K, N;
+    int64_t x_row_stride, out_row_stride;
+    int32_t dtype;
+    int32_t reserved0;
+} ss2d_linear_params;
+
+int ss2d_linear_supported(const ss2d_linear_params *p);
+int ss2d_linear_fwd(const ss2d_linear_params *p, void *cuda_stream);
+
 /* Debug checks (off by default; on with the environment variable SS2D_DEBUG_CHECKS=1 at load time or by this call).
  * When on, every entry point that launches kernels first asks the driver about each pointer it was given
  * (cudaPointerGetAttributes) and returns SS2D_EINVAL_DEVICE, before any launch, for host memory or memory of a GPU

@@ -848,6 +848,48 @@ def test_mlp_fused_refuses_what_it_cannot_take(vb):
         ops.mlp_fused(x, torch.zeros((768, 192), device="cuda"), torch.zeros(768, device="cuda"), torch.zeros((192, 768), device="cuda"))
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("M,K,N", [(32, 96, 2 * 56 * 56), (56, 192, 3 * 28 * 28), (104, 384, 5 * 14 * 14 + 4),
+                                   (48, 768, 8 * 49), (8, 32, 8), (256, 64, 1000), (96, 96, 128 * 149 + 72), (192, 192, 776)])
+def test_linear_cf_vs_float64(vb, dtype, M, K, N):
+    """w . x (+ bias) on the tcgen05 tensor cores against the float64 product of the same 16-bit inputs: the four
+    x_proj shapes of the first three stages of a VMamba-T forward (4 (R + 2N) rows from D channels), the longest
+    contraction, a single partial tile, the widest output, more tiles than SMs with a ragged last one."""
+    from vmamba_b200 import ops
+    td = torch.bfloat16 if dtype == "bf16" else torch.float16
+    rng = np.random.default_rng(M * 7 + K)
+    x = dev(rng.standard_normal((K, N), dtype=np.float32), td)
+    w = dev((rng.standard_normal((M, K), dtype=np.float32) / np.sqrt(K)).astype(np.float32), td)
+    b = dev((0.5 * rng.standard_normal(M)).astype(np.float32))
+    assert ops.linear_supported(M, K, N, td)
+    ref = w.float().cpu().numpy().astype(np.float64) @ x.float().cpu().numpy().astype(np.float64)
+    tol = 4e-3 if dtype == "bf16" else 6e-4          # one rounding of the result to the 16-bit type
+    y = ops.linear_cf(x, w)
+    assert y.shape == (M, N) and y.dtype == td
+    assert O.max_rel_err(host(y), ref) <= tol
+    assert torch.equal(y, ops.linear_cf(x, w)), "results must be bit-identical run to run"
+    yb = ops.linear_cf(x, w, bias=b)
+    assert O.max_rel_err(host(yb), ref + b.cpu().numpy().astype(np.float64)[:, None]) <= tol
+    # the canary rows around a caller-supplied output stay untouched
+    buf = torch.full((M + 2, N), 7.0, device="cuda", dtype=td)
+    ops.linear_cf(x, w, out=buf[1:M + 1])
+    assert torch.equal(buf[1:M + 1], y) and bool((buf[0] == 7).all()) and bool((buf[M + 1] == 7).all())
+
+
+@pytest.mark.gpu
+def test_linear_cf_refuses_what_it_cannot_take(vb):
+    from vmamba_b200 import ops
+    assert not ops.linear_supported(257, 96, 1024, torch.bfloat16)      # more output rows than one accumulator holds
+    assert not ops.linear_supported(32, 100, 1024, torch.bfloat16)      # channels not a multiple of the 32-wide slices
+    assert not ops.linear_supported(200, 768, 6272, torch.bfloat16)     # weights that leave no room for the ring of x slices
+    assert not ops.linear_supported(28, 96, 1024, torch.bfloat16)       # output rows not a multiple of 8
+    assert not ops.linear_supported(32, 96, 1023, torch.bfloat16)       # row pitch not a multiple of 16 bytes
+    assert not ops.linear_supported(32, 96, 1024, torch.float32)
+    with pytest.raises(RuntimeError):
+        ops.linear_cf(torch.zeros((100, 64), device="cuda", dtype=torch.bfloat16), torch.zeros((8, 100), device="cuda"))
+
+
 # ------------------------------------------------------------------ debug checks, guard bands
 @pytest.mark.gpu
 def test_debug_checks_refuse_host_pointers_before_any_launch(vb):

@@ -104,6 +104,11 @@ class MlpParams(ctypes.Structure):
                [("dtype", _i32), ("reserved0", _i32)]
 
 
+class LinearParams(ctypes.Structure):
+    _fields_ = [(n, _vp) for n in ("x", "w", "bias", "out")] + \
+               [(n, _i64) for n in ("M", "K", "N", "x_row_stride", "out_row_stride")] + [("dtype", _i32), ("reserved0", _i32)]
+
+
 EXPORTS = {
     # name: (restype, argtypes)
     "ss2d_selective_scan_fwd": (ctypes.c_int, [ctypes.POINTER(ScanParams), _vp]),
@@ -128,6 +133,8 @@ EXPORTS = {
     "ss2d_dwconv3x3_act": (ctypes.c_int, [ctypes.POINTER(PointwiseParams), _vp]),
     "ss2d_mlp_supported": (ctypes.c_int, [ctypes.POINTER(MlpParams)]),
     "ss2d_mlp_fwd": (ctypes.c_int, [ctypes.POINTER(MlpParams), _vp]),
+    "ss2d_linear_supported": (ctypes.c_int, [ctypes.POINTER(LinearParams)]),
+    "ss2d_linear_fwd": (ctypes.c_int, [ctypes.POINTER(LinearParams), _vp]),
     "ss2d_set_debug_checks": (ctypes.c_int, [ctypes.c_int]),
     "ss2d_version": (ctypes.c_int, []),
     "ss2d_strerror": (ctypes.c_char_p, [ctypes.c_int]),

@@ -24,6 +24,8 @@ long long core_static_capacity();
 int route_expand(const ss2d_expand_params* p, cudaStream_t st);
 int mlp_supported(const ss2d_mlp_params* p);
 int mlp_fwd(const ss2d_mlp_params* p, cudaStream_t st);
+int linear_supported(const ss2d_linear_params* p);
+int linear_fwd(const ss2d_linear_params* p, cudaStream_t st);
 long long route_expand_workspace_bytes(const ss2d_expand_params* p);
 int stem_conv_norm_act(const ss2d_stem_params* p, cudaStream_t st);
 int pixels_norm_to_planes(const ss2d_relayout_params* p, cudaStream_t st);
@@ -142,6 +144,13 @@ int ss2d_mlp_fwd(const ss2d_mlp_params* p, void* stream) {
     ss2d::Range nvtx_("ss2d_mlp_fwd");
     if (p) SS2D_CHECK_PTRS(p->x, p->w1, p->b1, p->w2, p->y);
     return ss2d::mlp_fwd(p, (cudaStream_t)stream);
+}
+
+int ss2d_linear_supported(const ss2d_linear_params* p) { return ss2d::linear_supported(p); }
+int ss2d_linear_fwd(const ss2d_linear_params* p, void* stream) {
+    ss2d::Range nvtx_("ss2d_linear_fwd");
+    if (p) SS2D_CHECK_PTRS(p->x, p->w, p->bias, p->out);
+    return ss2d::linear_fwd(p, (cudaStream_t)stream);
 }
 
 int ss2d_version(void) { return SS2D_ABI_VERSION; }

@@ -76,7 +76,10 @@ def project(x: torch.Tensor, w: CoreWeights, channel_major: bool = False):
     if channel_major:
         # one GEMM over the whole batch: (4C x D) . (D x B*L) -> rows (route, c), columns (b, l); the route
         # streams keep that shape: delta (orientation, pair, D, B, L), B/C rows (orientation, pair, 2N, B, L)
-        xd = torch.matmul(w.wx, x.reshape(D, B * L))
+        if ops.linear_supported(K * C, D, B * L, x.dtype):
+            xd = ops.linear_cf(x.reshape(D, B * L), w.wx)             # x_proj on the tensor cores (ss2d_linear_fwd)
+        else:
+            xd = torch.matmul(w.wx, x.reshape(D, B * L))              # fp32 maps, odd widths: the library GEMM
         p.x_dbl_batch_stride, p.x_dbl_route_stride, p.x_dbl_row_stride = L, C * B * L, B * L
         delta = torch.empty((2, 2, D, B, L), device=x.device, dtype=x.dtype)
         bc = torch.empty((2, 2, 2 * N, B, L), device=x.device, dtype=x.dtype)

@@ -571,6 +571,40 @@ def mlp_fused(x: torch.Tensor, w1: torch.Tensor, b1: torch.Tensor, w2: torch.Ten
     return y
 
 
+def linear_supported(M: int, K: int, n_pixels: int, dtype: torch.dtype) -> bool:
+    """True when `linear_cf` takes a dense (K, n_pixels) map itself (the library's planner decides)."""
+    if dtype not in (torch.bfloat16, torch.float16):
+        return False
+    from ._lib import LinearParams
+    fake = 4096                                   # an aligned address; the query dereferences nothing
+    p = LinearParams(fake, fake, None, fake, M, K, n_pixels, 0, 0, _DTYPES[dtype], 0)
+    return int(lib().ss2d_linear_supported(p)) == 0
+
+
+def linear_cf(x: torch.Tensor, w: torch.Tensor, bias=None, out=None) -> torch.Tensor:
+    """w . x (+ bias) for a channel-major map x (K, ...) of contiguous pixels: the 1x1 projection of Linear2d.forward
+    (vmamba.py:1062-1075) and, with the stacked weights of the four routes, x_proj of forward_corev2 on the
+    un-scanned map (vmamba.py:1536-1538), on the tcgen05 tensor cores.  w: (M, K) with M <= 256; returns (M, ...)."""
+    _require_cuda(x, w, bias)
+    if not x.is_contiguous():
+        raise RuntimeError("linear_cf expects a contiguous channel-major map")
+    from ._lib import LinearParams
+    K = x.shape[0]
+    N = x.numel() // K
+    w = w.contiguous().to(x.dtype)
+    if w.dim() != 2 or w.shape[1] != K:
+        raise RuntimeError("linear_cf expects weights of shape (M, K)")
+    M = w.shape[0]
+    b = None if bias is None else bias.contiguous().float()
+    y = torch.empty((M,) + tuple(x.shape[1:]), device=x.device, dtype=x.dtype) if out is None else out
+    if y.numel() != M * N or y.dtype != x.dtype or not y.is_contiguous():
+        raise RuntimeError("out must be a contiguous (M, ...) tensor of x's dtype")
+    p = LinearParams(x.data_ptr(), w.data_ptr(), None if b is None else b.data_ptr(), y.data_ptr(), M, K, N, 0, 0, dtype_code(x), 0)
+    with torch.cuda.device(x.device):
+        check(lib().ss2d_linear_fwd(p, _stream(x)), "ss2d_linear_fwd")
+    return y
+
+
 def dwconv3x3_act(x: torch.Tensor, weight: torch.Tensor, bias=None, act="silu", channel_major: bool = False) -> torch.Tensor:
     """act(depthwise 3x3 convolution, padding 1) of a (B, D, H, W) map ((D, B, H, W) with
     `channel_major`): conv2d + SiLU in front of the SS2D core (vmamba.py:1582-1583).
