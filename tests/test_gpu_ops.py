@@ -39,7 +39,11 @@ def test_cross_scan_merge_golden(vb, scans):
     assert np.array_equal(host(vb.cross_merge_fn(dev(g["ys"]), scans=scans)), g[f"merge_s{scans}"])
 
 
-@pytest.mark.parametrize("shape", [(1, 1, 1, 1), (2, 3, 5, 7), (1, 5, 56, 57), (3, 2, 33, 32), (2, 7, 64, 31), (1, 2, 1, 40)])
+@pytest.mark.parametrize("shape", [(1, 1, 1, 1), (2, 3, 5, 7), (1, 5, 56, 57), (3, 2, 33, 32), (2, 7, 64, 31), (1, 2, 1, 40),
+                                   # whole-plane kernels (odd shared-memory pitch) at the backbone's map sizes
+                                   (2, 3, 56, 56), (1, 3, 28, 28), (2, 5, 14, 14), (3, 4, 7, 7), (1, 2, 32, 48), (1, 2, 128, 64),
+                                   # tile kernels: 16-bit pairs (even sides, ragged tiles), single elements (odd side)
+                                   (1, 2, 192, 200), (1, 1, 130, 190), (1, 2, 181, 190), (1, 1, 256, 256)])
 @pytest.mark.parametrize("scans", [0, 1, 2, 3])
 def test_cross_scan_merge_vs_oracle(vb, shape, scans):
     rng = np.random.default_rng(hash((shape, scans)) & 0xffff)

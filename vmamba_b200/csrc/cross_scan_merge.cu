@@ -5,6 +5,8 @@
 // (scan) or written (merge) with w fastest, column-like routes go through a padded shared-memory
 // transpose so that both the global reads and the global writes of every route are coalesced.
 // Data movement only: results are bit-identical to indexing.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace ss2d {
@@ -75,6 +77,48 @@ __global__ void __launch_bounds__(kTile * kRowsPerPass) cross_scan_kernel(const 
             const int lh = col_like ? tx : ty + j, lw = col_like ? ty + j : tx;
             const int h = h0 + lh, w = w0 + lw;
             if (h < H && w < W) y[base + sh * h + sw * w] = tile[lh][lw];
+        }
+    }
+}
+
+// 16-bit maps with even H and W: a thread moves PAIRS of elements as one 32-bit word.  A 2-byte access per lane runs the
+// load/store unit at a fraction of its rate (the kernel above reached 0.24 of the copy bandwidth on 256 x 256 bf16
+// planes).  Tile: 64 x 64 elements = 32 words along the fast index of either orientation; a reversed route writes the
+// pair at the mirrored address with its halves swapped.
+constexpr int kPairTile = 64;
+__global__ void __launch_bounds__(256) cross_scan_pair_kernel(const CrossArgs a) {
+    __shared__ __align__(4) uint16_t tile[kPairTile][kPairTile + 2];       // pitch 33 words
+    const unsigned t = blockIdx.x, tiles_w = (unsigned)a.tiles_w, tiles_h = (unsigned)a.tiles_h, C = (unsigned)a.C;
+    const unsigned tw = t % tiles_w, rest = t / tiles_w, th = rest % tiles_h, plane = rest / tiles_h;
+    const unsigned b = plane / C, c = plane - b * C;
+    const int H = (int)a.H, W = (int)a.W, L = H * W;
+    const uint16_t* __restrict__ x = (const uint16_t*)a.in + (long long)plane * L;
+    const int h0 = (int)th * kPairTile, w0 = (int)tw * kPairTile;
+    const int tx = threadIdx.x, ty = threadIdx.y;          // 32 x 8
+#pragma unroll
+    for (int j = 0; j < kPairTile; j += 8) {
+        const int h = h0 + ty + j, w = w0 + 2 * tx;
+        if (h < H && w < W) *reinterpret_cast<uint32_t*>(&tile[ty + j][2 * tx]) = *reinterpret_cast<const uint32_t*>(x + h * W + w);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int base = (int)a.route[k].base, sh = (int)a.route[k].sh, sw = (int)a.route[k].sw;
+        const bool col_like = a.route[k].col_like != 0;
+        uint16_t* __restrict__ y = (uint16_t*)a.out + ((long long)(b * 4 + k) * C + c) * L;
+#pragma unroll
+        for (int j = 0; j < kPairTile; j += 8) {
+            // the pair runs along w (row-like) or along h (column-like); `step` is the route's stride along the pair
+            const int lh = col_like ? 2 * tx : ty + j, lw = col_like ? ty + j : 2 * tx;
+            const int h = h0 + lh, w = w0 + lw;
+            if (h < H && w < W) {
+                const uint32_t e0 = col_like ? tile[lh][lw] : tile[lh][lw];
+                const uint32_t e1 = col_like ? tile[lh + 1][lw] : tile[lh][lw + 1];
+                const int step = col_like ? sh : sw;               // +1 or -1
+                const int l0 = base + sh * h + sw * w;
+                if (step > 0) *reinterpret_cast<uint32_t*>(y + l0) = e0 | (e1 << 16);
+                else *reinterpret_cast<uint32_t*>(y + l0 - 1) = e1 | (e0 << 16);
+            }
         }
     }
 }
@@ -152,16 +196,29 @@ __device__ __forceinline__ int route_src(const RouteMapI& m, int l, int H, int W
     return h * W + w;
 }
 
+// Shared-memory planes have an odd line pitch (W | 1 for a row-major plane, H | 1 for a column-major one): the gathers of
+// the permutation then walk down a line with consecutive lanes in different banks.  With the natural pitch (56 for a
+// 56 x 56 map) 32 lanes fell into 4 banks and the kernels ran at a third of the copy bandwidth.
 template <typename T, int PV>
 __global__ void __launch_bounds__(256) cross_scan_plane_kernel(const PlaneArgs a) {
     extern __shared__ __align__(16) unsigned char smraw[];
-    T* sm = reinterpret_cast<T*>(smraw);
+    T* sm = reinterpret_cast<T*>(smraw);                   // [PP][H][Wp]
     const long long plane0 = (long long)blockIdx.x * a.PP;
     const int np = (int)min((long long)a.PP, a.planes - plane0);
-    const int L = a.L, n = np * a.nvec;
+    const int L = a.L, n = np * a.nvec, W = a.W, H = a.H, Wp = W | 1, Lp = H * Wp;
     const T* __restrict__ x = (const T*)a.in + plane0 * L;
-    for (int i = threadIdx.x; i < n; i += blockDim.x)
-        Vec<T, PV>::store_raw(sm + i * PV, Vec<T, PV>::load_raw(x + (long long)i * PV));
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int pl = mdiv_u(i, a.magic_nvec), p0 = (i - pl * a.nvec) * PV;
+        const typename Vec<T, PV>::Raw r = Vec<T, PV>::load_raw(x + (long long)i * PV);
+        const T* e = reinterpret_cast<const T*>(&r);
+        int h = mdiv_u(p0, a.magic_W), w = p0 - h * W;
+        T* dst = sm + pl * Lp;
+#pragma unroll
+        for (int j = 0; j < PV; ++j) {
+            dst[h * Wp + w] = e[j];
+            if (++w == W) { w = 0; ++h; }
+        }
+    }
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -172,8 +229,29 @@ __global__ void __launch_bounds__(256) cross_scan_plane_kernel(const PlaneArgs a
             const unsigned b = plane / (unsigned)a.C, c = plane - b * (unsigned)a.C;
             typename Vec<T, PV>::Raw r;
             T* e = reinterpret_cast<T*>(&r);
+            const T* src = sm + pl * Lp;
+            if (!m.col_like) {
+                // row-major route, forward or reversed: source pixel l or L - 1 - l
+                int p = m.sw > 0 ? l0 : m.base - l0;
+                int h = mdiv_u(p, a.magic_W), w = p - h * W;
 #pragma unroll
-            for (int j = 0; j < PV; ++j) e[j] = sm[pl * L + route_src(m, l0 + j, a.H, a.W, a.magic_H)];
+                for (int j = 0; j < PV; ++j) {
+                    e[j] = src[h * Wp + w];
+                    if (m.sw > 0) { if (++w == W) { w = 0; ++h; } }
+                    else { if (--w < 0) { w = W - 1; --h; } }
+                }
+            } else {
+                // column-major route: l - base = sh * h + sw * w with |sh| = 1, |sw| = H; walk h first
+                const int t = (int)(m.sw > 0 ? 0 : -m.sw * (W - 1));
+                const int r0 = l0 - m.base + t + (m.sh < 0 ? (H - 1) : 0);     // = hh + H * ww with hh, ww in range
+                int ww = mdiv_u(r0, a.magic_H), hh = r0 - ww * H;
+#pragma unroll
+                for (int j = 0; j < PV; ++j) {
+                    const int h = m.sh > 0 ? hh : H - 1 - hh, w = m.sw > 0 ? ww : W - 1 - ww;
+                    e[j] = src[h * Wp + w];
+                    if (++hh == H) { hh = 0; ++ww; }
+                }
+            }
             Vec<T, PV>::store_raw((T*)a.out + ((long long)(b * 4 + k) * a.C + c) * L + l0, r);
         }
     }
@@ -182,41 +260,59 @@ __global__ void __launch_bounds__(256) cross_scan_plane_kernel(const PlaneArgs a
 template <typename T, int PV>
 __global__ void __launch_bounds__(256) cross_merge_plane_kernel(const PlaneArgs a, const int scans) {
     extern __shared__ __align__(16) unsigned char smraw[];
-    T* sm = reinterpret_cast<T*>(smraw);                   // [4][PP][L]: every route's plane, in its own order
+    T* sm = reinterpret_cast<T*>(smraw);                   // [4][PP][padded plane]: every route's plane, in its own order
     const long long plane0 = (long long)blockIdx.x * a.PP;
     const int np = (int)min((long long)a.PP, a.planes - plane0);
-    const int L = a.L, n = np * a.nvec;
+    const int L = a.L, n = np * a.nvec, W = a.W, H = a.H;
+    const int Wp = W | 1, Hp = H | 1;
+    const int Lmax = max(H * Wp, W * Hp);                  // room of one padded plane, whichever way it is laid out
+    // a route's plane in shared memory: lines of its fast index (w for row-major routes, h for column-major ones)
+    RouteMapI rm[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
+        rm[k] = narrow(a.route[k]);
+        const int fast = rm[k].col_like ? H : W, pitch = rm[k].col_like ? Hp : Wp;
+        const int b_lo = rm[k].base % fast, b_hi = rm[k].base / fast;
+        rm[k].base = b_lo + pitch * b_hi;
+        if (rm[k].col_like) rm[k].sw = rm[k].sw > 0 ? Hp : -Hp;
+        else rm[k].sh = rm[k].sh > 0 ? Wp : -Wp;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const bool col = rm[k].col_like != 0;
+        const int fast = col ? H : W, pitch = col ? Hp : Wp;
+        const unsigned magic_fast = col ? a.magic_H : a.magic_W;
         for (int i = threadIdx.x; i < n; i += blockDim.x) {
             const int pl = mdiv_u(i, a.magic_nvec), l0 = (i - pl * a.nvec) * PV;
             const unsigned plane = (unsigned)plane0 + (unsigned)pl;
             const unsigned b = plane / (unsigned)a.C, c = plane - b * (unsigned)a.C;
-            Vec<T, PV>::store_raw(sm + (k * a.PP + pl) * L + l0,
-                                  Vec<T, PV>::load_raw((const T*)a.in + ((long long)(b * 4 + k) * a.C + c) * L + l0));
+            const typename Vec<T, PV>::Raw r = Vec<T, PV>::load_raw((const T*)a.in + ((long long)(b * 4 + k) * a.C + c) * L + l0);
+            const T* e = reinterpret_cast<const T*>(&r);
+            int line = mdiv_u(l0, magic_fast), pos = l0 - line * fast;
+            T* dst = sm + (k * a.PP + pl) * Lmax;
+#pragma unroll
+            for (int j = 0; j < PV; ++j) {
+                dst[line * pitch + pos] = e[j];
+                if (++pos == fast) { pos = 0; ++line; }
+            }
         }
     }
     __syncthreads();
     T* __restrict__ y = (T*)a.out + plane0 * L;
-    RouteMapI rm[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) rm[k] = narrow(a.route[k]);
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const int pl = mdiv_u(i, a.magic_nvec), p0 = (i - pl * a.nvec) * PV;
         typename Vec<T, PV>::Raw r;
         T* e = reinterpret_cast<T*>(&r);
+        int h = mdiv_u(p0, a.magic_W), w = p0 - h * W;
 #pragma unroll
         for (int j = 0; j < PV; ++j) {
-            const int p = p0 + j;
-            const int h = mdiv_u(p, a.magic_W), w = p - h * a.W;
             T v[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                v[k] = sm[(k * a.PP + pl) * L + rm[k].base + rm[k].sh * h + rm[k].sw * w];
-            }
+            for (int k = 0; k < 4; ++k) v[k] = sm[(k * a.PP + pl) * Lmax + rm[k].base + rm[k].sh * h + rm[k].sw * w];
             if (scans == 0 || scans == 2) e[j] = add_t(add_t(v[0], v[2]), add_t(v[1], v[3]));
             else if (scans == 3) e[j] = add_t(add_t(add_t(v[0], v[1]), v[2]), v[3]);
             else e[j] = from_f<T>(((to_f<T>(v[0]) + to_f<T>(v[1])) + to_f<T>(v[2])) + to_f<T>(v[3]));
+            if (++w == W) { w = 0; ++h; }
         }
         Vec<T, PV>::store_raw(y + (long long)i * PV, r);
     }
@@ -226,20 +322,22 @@ __global__ void __launch_bounds__(256) cross_merge_plane_kernel(const PlaneArgs 
 template <typename T>
 static bool plan_plane(const ss2d_cross_params* p, int copies, PlaneArgs& a, int& pv, size_t& smem) {
     const long long L = p->H * p->W;
-    if (L * (long long)sizeof(T) * copies > 64 * 1024) return false;
+    // shared-memory room of one plane with its odd line pitch (the merge keeps planes of either orientation)
+    const long long Lp = copies == 1 ? p->H * (p->W | 1) : std::max(p->H * (p->W | 1), p->W * (p->H | 1));
+    if (Lp * (long long)sizeof(T) * copies > 64 * 1024) return false;
     pv = 16 / (int)sizeof(T);
     auto fit = [&](long long x) { while (pv > 1 && (x % pv) != 0) pv >>= 1; };
     fit(L);
     fit((long long)(reinterpret_cast<uintptr_t>(p->in) / sizeof(T)));
     fit((long long)(reinterpret_cast<uintptr_t>(p->out) / sizeof(T)));
     long long PP = (4096 + L - 1) / L;        // about 4096 elements per CTA
-    while (PP > 1 && PP * L * (long long)sizeof(T) * copies > 64 * 1024) --PP;
+    while (PP > 1 && PP * Lp * (long long)sizeof(T) * copies > 64 * 1024) --PP;
     a.in = p->in; a.out = p->out; a.planes = p->B * p->C; a.C = (int)p->C; a.H = (int)p->H; a.W = (int)p->W;
     a.L = (int)L; a.PP = (int)PP; a.nvec = (int)(L / pv);
     for (int k = 0; k < 4; ++k) a.route[k] = route_map(p->scans, k, p->H, p->W);
     auto magic = [](long long d) { return d > 1 ? (unsigned)(((1ULL << 32) + (unsigned long long)d - 1) / (unsigned long long)d) : 0u; };
     a.magic_H = magic(p->H); a.magic_W = magic(p->W); a.magic_nvec = magic(a.nvec);
-    smem = (size_t)PP * L * sizeof(T) * copies;
+    smem = (size_t)PP * Lp * sizeof(T) * copies;
     return (a.planes + PP - 1) / PP <= 0x7fffffffLL;
 }
 
@@ -297,10 +395,22 @@ int cross_scan(const ss2d_cross_params* p, cudaStream_t st) {
     CrossArgs a;
     const int rc = fill_args(p, a);
     if (rc != SS2D_OK) return rc;
-    {
+    // 16-bit maps with even sides: the pair kernel for every map that fills most of a 64 x 64 tile (0.87 of the copy
+    // bandwidth on 256 x 256 planes against 0.60 for the whole-plane kernel on 128 x 128 ones)
+    const bool pairs = p->dtype != SS2D_F32 && p->H % 2 == 0 && p->W % 2 == 0 && aligned_to(p->in, 4) && aligned_to(p->out, 4);
+    if (!(pairs && p->H >= 48 && p->W >= 48)) {
         PlaneArgs pa; int pv; size_t smem;
         if (p->dtype == SS2D_F32) { if (plan_plane<float>(p, 1, pa, pv, smem)) return scan_plane_v<float>(pa, pv, smem, st); }
         else if (plan_plane<uint16_t>(p, 1, pa, pv, smem)) return scan_plane_v<uint16_t>(pa, pv, smem, st);
+    }
+    if (pairs) {
+        CrossArgs q = a;
+        q.tiles_h = (p->H + kPairTile - 1) / kPairTile;
+        q.tiles_w = (p->W + kPairTile - 1) / kPairTile;
+        q.n_tiles = q.tiles_h * q.tiles_w * p->B * p->C;
+        cross_scan_pair_kernel<<<(unsigned)q.n_tiles, dim3(32, 8), 0, st>>>(q);
+        count_launch();
+        return check_launch();
     }
     const dim3 blk(kTile, kRowsPerPass);
     if (p->dtype == SS2D_F32) cross_scan_kernel<float><<<(unsigned)a.n_tiles, blk, 0, st>>>(a);
