@@ -236,6 +236,40 @@ def mlp_leg(model, batch=None, iters=20):
             "replaced_launches_ms": t_u, "note": "bound by the GELU epilogue on the FMA pipe, not by the tensor pipe"}
 
 
+def xproj_leg(model, batch=None, iters=20, stage=0):
+    """The x_proj kernel (`ss2d_linear_fwd`, tcgen05) of the first block of a stage alone, beside the library GEMM on
+    the same operands; bytes = x read once + the projected rows written once."""
+    import torch
+    from vmamba_b200 import ops
+    w = model.blocks[stage][0].core
+    hw = 56 >> stage
+    D, B = w.d_inner, batch or 128
+    M = w.wx.shape[0]
+    g = torch.Generator(device="cuda").manual_seed(0)
+    # several input buffers in turn, so that a launch never finds its x in L2
+    nb = max(2, int(400e6 // ((D + M) * B * hw * hw * 2)) + 1)
+    xs = [torch.randn((D, B * hw * hw), device="cuda", generator=g).to(model.dtype) for _ in range(nb)]
+    if not ops.linear_supported(M, D, xs[0].shape[1], xs[0].dtype):
+        return None
+    out = torch.empty((M, xs[0].shape[1]), device="cuda", dtype=model.dtype)
+    state = {"i": 0}
+
+    def own():
+        state["i"] = (state["i"] + 1) % nb
+        ops.linear_cf(xs[state["i"]], w.wx, out=out)
+
+    def library():
+        state["i"] = (state["i"] + 1) % nb
+        torch.matmul(w.wx, xs[state["i"]], out=out)
+    t_o = time_events(own, iters * nb)
+    t_l = time_events(library, iters * nb)
+    peak, kind = peaks()
+    by = (D + M) * xs[0].shape[1] * 2
+    return {"kernel": "linear_cf_kernel (x_proj, tcgen05 + TMA)", "workload": f"M={M} K={D} pixels={xs[0].shape[1]} bf16, {nb} input buffers in turn",
+            "ms": t_o, "gbs": by / t_o / 1e6, "frac_of_measured_hbm": by / t_o / 1e6 / peak, "peak_kind": kind, "library_gemm_ms": t_l,
+            "note": "timed launch by launch: includes the launch gap, which a captured graph does not have"}
+
+
 def op_sweep(args):
     """Operator-surface sweep (the selective-scan op alone, bf16 u/delta/B/C, fp32 state and output) over
     d_state x channels x length, plus CrossScan / CrossMerge; one JSON line per cell with the achieved
@@ -394,6 +428,10 @@ def run_ours(args):
 
     if args.mlp_only:          # the fused MLP kernel alone (small cases for profiler captures)
         print(json.dumps({"mlp_fused": mlp_leg(model, args.roofline_batch, args.steps)}), flush=True)
+        return
+
+    if args.xproj_only:        # the x_proj kernel alone (small cases for profiler captures)
+        print(json.dumps({"xproj": xproj_leg(model, args.roofline_batch, args.steps, args.stage)}), flush=True)
         return
 
     if args.forward_only:      # plain (un-graphed) forwards and nothing else: the case profiler captures use
@@ -559,6 +597,8 @@ def main():
     ap.add_argument("--sweep-gb", type=float, default=2.0, help="input gigabytes per sweep cell")
     ap.add_argument("--roofline-only", action="store_true", help="time only the fused SS2D core chain of stage 0")
     ap.add_argument("--roofline-batch", type=int, default=None, help="batch for --roofline-only (default 128)")
+    ap.add_argument("--xproj-only", action="store_true", help="time only the x_proj kernel of a block (stage: --stage, batch: --roofline-batch)")
+    ap.add_argument("--stage", type=int, default=0, help="stage whose first block --xproj-only takes (0..2)")
     ap.add_argument("--mlp-only", action="store_true", help="time only the fused MLP kernel of a stage-0 block (batch: --roofline-batch)")
     ap.add_argument("--forward-only", action="store_true", help="run --steps plain forwards of the model and exit (profiler captures)")
     args = ap.parse_args()
