@@ -328,6 +328,27 @@ def _project_library(x, w):
     return RouteStreams(xd_even[:, :, R:].contiguous(), xd_odd[:, :, R:].contiguous(), delta_even, delta_odd, False)
 
 
+def _project_float64(c, dtype):
+    """The same four streams from a float64 statement of x_proj and dt_projs on the un-scanned map (vmamba.py:1536-1543),
+    with the roundings to the activation type where the reference has them (the projected rows, then the step sizes)."""
+    rnd = (lambda a: a) if dtype == "f32" else (lambda a: O.round_bf16(a.astype(np.float32)).astype(np.float64))
+    x = rnd(c["x"].astype(np.float64))
+    B, D, H, W = x.shape
+    R, N = c["R"], c["N"]
+    C, L = R + 2 * N, H * W
+    wx = rnd(c["wx"].astype(np.float64)).reshape(4, C, D)
+    wdt = rnd(c["wdt"].astype(np.float64)).reshape(4, D, R)
+    out = {}
+    for k in range(4):
+        xd = rnd(np.einsum("cd,bdhw->bchw", wx[k], x))                       # projected rows of route k, pixel order (h, w)
+        if k % 2 == 1:
+            xd = xd.transpose(0, 1, 3, 2)                                    # column-major routes: pixel order (w, h)
+        xd = xd.reshape(B, C, L)
+        out[k] = (rnd(np.einsum("dr,brl->bdl", wdt[k], xd[:, :R])), xd[:, R:])
+    stack = lambda j, i: np.stack([out[j][i], out[j + 2][i]], axis=1)
+    return stack(0, 1), stack(1, 1), stack(0, 0), stack(1, 0)               # bc_even, bc_odd, delta_even, delta_odd
+
+
 def _core_case(Bt, D, H, W, N, seed, Cmodel=None):
     import math
     rng = np.random.default_rng(seed)
@@ -420,7 +441,9 @@ def test_fused_core_extreme_step_sizes(vb, shape):
                                         ((1, 5, 9, 11), 1, None), ((2, 12, 6, 10), 4, 64), ((1, 256, 16, 8), 2, 1024)])
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_route_expand_vs_library_projection(vb, shape, N, Cm, dtype):
-    """ss2d_route_expand against the same projections done with library GEMMs and copies."""
+    """x_proj (ss2d_linear_fwd on channel-major 16-bit maps, else the library GEMM) and ss2d_route_expand against a
+    float64 statement of the reference's projections, and against the same projections done with library GEMMs and
+    copies."""
     from vmamba_b200 import fused
     c = _core_case(*shape, N=N, seed=7, Cmodel=Cm)
     td = torch.float32 if dtype == "f32" else torch.bfloat16
@@ -438,6 +461,13 @@ def test_route_expand_vs_library_projection(vb, shape, N, Cm, dtype):
             assert O.max_rel_err(host(g_), host(r_)) <= (1e-5 if dtype == "f32" else 8e-3), name
         else:
             assert O.max_rel_err(host(g_), host(r_)) <= (1e-5 if dtype == "f32" else 8e-3), name
+    # against float64 with the reference's roundings: a projected row that lands on the other side of a rounding
+    # boundary moves one step of the 16-bit type, and with it the step sizes it feeds
+    want = _project_float64(c, dtype)
+    for streams in (got, [g_.permute(2, 0, 1, 3) for g_ in got_cm]):
+        for g_, r_, name in zip(streams, want, ("bc_even", "bc_odd", "delta_even", "delta_odd")):
+            assert tuple(g_.shape) == r_.shape, name
+            assert O.max_rel_err(host(g_), r_) <= (2e-5 if dtype == "f32" else 1.6e-2), name
     for g_, r_, name in zip(got, ref, ("bc_even", "bc_odd", "delta_even", "delta_odd")):
         assert g_.shape == r_.shape, name
         if name.startswith("bc"):
