@@ -30,12 +30,13 @@ def test_library_exports_every_declared_symbol():
 
 def test_struct_layout_matches_header(tmp_path):
     prog = tmp_path / "sz.c"
-    prog.write_text('#include "ss2d_b200.h"\n#include <stdio.h>\n#include <stddef.h>\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",'
+    prog.write_text('#include "ss2d_b200.h"\n#include <stdio.h>\n#include <stddef.h>\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",'
                     'sizeof(ss2d_scan_params),sizeof(ss2d_cross_params),sizeof(ss2d_core_params),sizeof(ss2d_norm_params),'
                     'offsetof(ss2d_core_params,delta_batch_stride),offsetof(ss2d_scan_params,batch),'
                     'sizeof(ss2d_expand_params),sizeof(ss2d_pointwise_params),offsetof(ss2d_expand_params,B),'
                     'offsetof(ss2d_norm_params,io_dtype),sizeof(ss2d_scan_bwd_params),offsetof(ss2d_scan_bwd_params,in_dtype),'
-                    'offsetof(ss2d_scan_bwd_params,C_state_stride));return 0;}\n')
+                    'offsetof(ss2d_scan_bwd_params,C_state_stride),sizeof(ss2d_linear_params),offsetof(ss2d_linear_params,dtype),'
+                    'sizeof(ss2d_mlp_params),offsetof(ss2d_mlp_params,dtype));return 0;}\n')
     exe = tmp_path / "sz"
     subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), str(prog), "-o", str(exe)])
     got = [int(t) for t in subprocess.check_output([str(exe)]).split()]
@@ -43,7 +44,8 @@ def test_struct_layout_matches_header(tmp_path):
             ctypes.sizeof(_lib.NormParams), _lib.CoreParams.delta_batch_stride.offset, _lib.ScanParams.batch.offset,
             ctypes.sizeof(_lib.ExpandParams), ctypes.sizeof(_lib.PointwiseParams), _lib.ExpandParams.B.offset,
             _lib.NormParams.io_dtype.offset, ctypes.sizeof(_lib.ScanBwdParams), _lib.ScanBwdParams.in_dtype.offset,
-            _lib.ScanBwdParams.C_state_stride.offset]
+            _lib.ScanBwdParams.C_state_stride.offset, ctypes.sizeof(_lib.LinearParams), _lib.LinearParams.dtype.offset,
+            ctypes.sizeof(_lib.MlpParams), _lib.MlpParams.dtype.offset]
     assert got == want
 
 
