@@ -151,6 +151,48 @@ def test_selective_scan_dstate16_sweep_shapes(vb, L, KD, dtype):
     assert O.max_rel_err(host(y), ref) <= TOL_F32      # the inputs are rounded on both sides: fp32 tolerance holds
 
 
+@pytest.mark.parametrize("N,L,dtype,opt", [(16, 200, "bf16", True), (16, 68, "f32", True), (8, 160, "bf16", False),
+                                           (4, 32, "f32", False), (16, 392, "f16", True), (16, 196, "bf16", True)])
+def test_selective_scan_many_rows_small_state(vb, N, L, dtype, opt):
+    """d_state 4 / 8 / 16 with enough rows (B x 4 x 384 = 39 936) for the lanes-are-rows kernel: whole and ragged tiles
+    (L = 200 = 12 x 16 + 8; L = 196, a 14 x 14 map, whose 16-bit rows allow 8-byte pieces only), 16-bit and fp32 tensors, with and without D / bias / softplus, A drawn per row, against the
+    C oracle; the states it leaves for the backward pass against the forward kernel for fewer rows."""
+    rng = np.random.default_rng(N * 100 + L)
+    Bt, K, Dm = 26, 4, 384
+    KD = K * Dm
+    inp = dict(u=rng.standard_normal((Bt, KD, L), dtype=np.float32),
+               delta=rng.standard_normal((Bt, KD, L), dtype=np.float32),
+               A=-np.exp(0.3 * rng.standard_normal((KD, N), dtype=np.float32)) * np.arange(1, N + 1, dtype=np.float32)[None],
+               B=rng.standard_normal((Bt, K, N, L), dtype=np.float32),
+               C=rng.standard_normal((Bt, K, N, L), dtype=np.float32))
+    D = (1.0 + 0.2 * rng.standard_normal(KD)).astype(np.float32) if opt else None
+    bias = (rng.standard_normal(KD).astype(np.float32) - 3.0) if opt else None
+    if not opt:                          # no softplus: the step sizes themselves have to be positive
+        inp["delta"] = (0.3 * np.abs(inp["delta"])).astype(np.float32)
+    td = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[dtype]
+    if dtype != "f32":
+        for k in ("u", "delta", "B", "C"):
+            inp[k] = dev(inp[k], td).float().cpu().numpy()
+    ref = CO.selective_scan(inp["u"], inp["delta"], inp["A"].astype(np.float32), inp["B"], inp["C"], D, bias, opt)
+    args = (dev(inp["u"], td), dev(inp["delta"], td), dev(inp["A"].astype(np.float32)), dev(inp["B"], td), dev(inp["C"], td),
+            None if D is None else dev(D), None if bias is None else dev(bias), opt, True)
+    from vmamba_b200 import _lib
+    n0 = _lib.launch_count()
+    y = vb.selective_scan_fn(*args)
+    assert _lib.launch_count() == n0 + 1
+    assert y.dtype == torch.float32 and O.max_rel_err(host(y), ref) <= TOL_F32
+    assert torch.equal(y, vb.selective_scan_fn(*args)), "results must be bit-identical run to run"
+    # same values as the warp-per-row kernel gives for a slice with too few rows for this one
+    few = tuple(t[:2] if isinstance(t, torch.Tensor) and t.dim() >= 3 else t for t in args)
+    assert O.max_rel_err(host(vb.selective_scan_fn(*few)), ref[:2]) <= TOL_F32
+    assert O.max_rel_err(host(y[:2]), host(vb.selective_scan_fn(*few))) <= 2e-6
+    from vmamba_b200 import ops
+    _, ck = ops.selective_scan_fwd(*args[:8], True, return_checkpoints=True)
+    _, ck_few = ops.selective_scan_fwd(*few[:8], True, return_checkpoints=True)
+    assert ck.shape == (Bt, KD, (L + 127) // 128, N)
+    assert O.max_rel_err(host(ck[:2]), host(ck_few)) <= 2e-6
+
+
 @pytest.mark.parametrize("N,L,K", [(2, 100, 4), (16, 640, 4), (16, 196, 1), (64, 50, 2), (256, 33, 1)])
 def test_selective_scan_dstate(vb, N, L, K):
     rng = np.random.default_rng(N * 1000 + L)

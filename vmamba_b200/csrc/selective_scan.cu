@@ -174,6 +174,183 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) selscan_fwd_nx_kernel(const
     }
 }
 
+// d_state 4 / 8 / 16 with many rows: LANES ARE ROWS.  A warp owns 32 consecutive rows of one (image, group) and every
+// lane walks its own row element by element with all NS states in registers: the recurrence is a plain fused
+// multiply-add per (element, state) - no running products, no fix-up, no shuffle scan (the warp-per-row kernel above
+// spends 13.7 instructions per (element, state), 2.2 of them in the scans; this form needs 5: scale, ex2, B u, h, y) -
+// and the NS states of a lane are NS independent dependency chains.  The B / C values of an element are the same for
+// the 32 rows of the warp: they are staged once per tile as fp32 and read as broadcast 16-byte loads.  Tiles of 16
+// elements: u and delta (32 rows x 16 elements) and B / C (NS rows x 16 elements) are loaded as 16-byte pieces, unpacked
+// and stored transposed ([element][row], pitch 33: conflict-free both ways); the outputs leave through the same buffer
+// as 16-byte vectors.  Warps of a CTA never wait for each other.  The kernel is bound by the MUFU pipe (NS + 2
+// transcendentals per element and lane).
+constexpr int kRowsTile = 16;          // elements per tile: 6.8 KB of shared memory per warp at 16 states, six CTAs per SM
+constexpr int kRowsWarps = 4;
+template <int NS> struct RowsSmem {
+    static constexpr int kPitch = 33;
+    static constexpr int kBCPitch = NS + 4;                      // rows stay 16-byte aligned
+    static constexpr int kFloatsPerWarp = 2 * kRowsTile * kPitch + 2 * kRowsTile * kBCPitch;
+};
+
+template <typename Tin, typename Tout, int NS, int EPP>
+__global__ void __launch_bounds__(kRowsWarps * 32, 6) selscan_fwd_rows_kernel(const ScanArgs a) {
+    using S = RowsSmem<NS>;
+    // EPP: elements per piece moved by one load (16 bytes; 8 bytes for 16-bit rows whose length is a multiple of 4 only)
+    constexpr int PPR = kRowsTile / EPP;                         // pieces per row of a tile
+    constexpr int OPP = EPP < 16 / (int)sizeof(Tout) ? EPP : 16 / (int)sizeof(Tout), OPR = kRowsTile / OPP;
+    extern __shared__ __align__(16) float rows_sm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* su = rows_sm + (size_t)warp * S::kFloatsPerWarp;       // [t][row]; overwritten by the outputs
+    float* sd = su + kRowsTile * S::kPitch;
+    float* sB = sd + kRowsTile * S::kPitch;                      // [t][n]
+    float* sC = sB + kRowsTile * S::kBCPitch;
+    const int64_t row0 = ((int64_t)blockIdx.x * kRowsWarps + warp) * 32;
+    if (row0 >= a.rows) return;
+    const int64_t b = row0 / a.dim, r0 = row0 % a.dim, k = r0 / a.group_size;     // 32 rows: one image, one group
+    const int64_t r = r0 + lane;
+    const Tin* __restrict__ u = (const Tin*)a.u + b * a.u_bs + r0 * a.u_ds;
+    const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + r0 * a.d_ds;
+    const Tin* __restrict__ Bm = (const Tin*)a.B + b * a.B_bs + k * a.B_gs;
+    const Tin* __restrict__ Cm = (const Tin*)a.C + b * a.C_bs + k * a.C_gs;
+    Tout* __restrict__ out = (Tout*)a.out + b * a.o_bs + r0 * a.o_ds;
+    float A2[NS], h[NS];
+#pragma unroll
+    for (int n = 0; n < NS; ++n) { A2[n] = __ldg(a.A + r * NS + n) * kLog2e; h[n] = 0.f; }
+    const bool has_D = a.D != nullptr;
+    const float Dv = has_D ? __ldg(a.D + r) : 0.f;
+    const float bias = a.bias ? __ldg(a.bias + r) : 0.f;
+    const bool sp = a.softplus != 0;
+    const int L = (int)a.seqlen;
+    using VI = Vec<Tin, EPP>;
+    using VO = Vec<Tout, OPP>;
+
+    for (int t0 = 0; t0 < L; t0 += kRowsTile) {
+        // ---- stage the tile: 16-byte pieces in, fp32 transposed out (L is a multiple of the piece: a piece is inside or outside)
+#pragma unroll
+        for (int j = 0; j < PPR; ++j) {
+            const int idx = j * 32 + lane, rr = idx / PPR, piece = idx - rr * PPR;
+            const int pos = t0 + piece * EPP;
+            float uv[EPP], dv[EPP];
+            if (pos < L) {
+                VI::load(u + rr * a.u_ds + pos, uv);
+                VI::load(dt + rr * a.d_ds + pos, dv);
+            } else {
+#pragma unroll
+                for (int e = 0; e < EPP; ++e) { uv[e] = 0.f; dv[e] = 0.f; }
+            }
+#pragma unroll
+            for (int e = 0; e < EPP; ++e) {
+                su[(piece * EPP + e) * S::kPitch + rr] = uv[e];
+                sd[(piece * EPP + e) * S::kPitch + rr] = dv[e];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < (NS * PPR + 31) / 32; ++j) {
+            const int idx = j * 32 + lane, n = idx / PPR, piece = idx - n * PPR;
+            const int pos = t0 + piece * EPP;
+            if (n < NS) {
+                float bv[EPP], cv[EPP];
+                if (pos < L) {
+                    VI::load(Bm + n * a.B_ss + pos, bv);
+                    VI::load(Cm + n * a.C_ss + pos, cv);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < EPP; ++e) { bv[e] = 0.f; cv[e] = 0.f; }
+                }
+#pragma unroll
+                for (int e = 0; e < EPP; ++e) {
+                    sB[(piece * EPP + e) * S::kBCPitch + n] = bv[e];
+                    sC[(piece * EPP + e) * S::kBCPitch + n] = cv[e];
+                }
+            }
+        }
+        __syncwarp();
+        // ---- the recurrence: this lane's row, element by element
+        const int tn = min(kRowsTile, L - t0);
+#pragma unroll 2
+        for (int t = 0; t < tn; ++t) {
+            const float uv = su[t * S::kPitch + lane];
+            float d = sd[t * S::kPitch + lane] + bias;
+            if (sp) d = softplus_fast(d);
+            const float du = d * uv;
+            float y = has_D ? Dv * uv : 0.f, y1 = 0.f;           // two partial sums: half the dependent chain
+            if (a.ckpt && ((t0 + t) & 127) == 0) {               // the states in front of element t0 + t
+                float* ck = a.ckpt + ((row0 + lane) * a.nck + ((t0 + t) >> 7)) * NS;
+#pragma unroll
+                for (int n = 0; n < NS; n += 4) *reinterpret_cast<float4*>(ck + n) = make_float4(h[n], h[n + 1], h[n + 2], h[n + 3]);
+            }
+#pragma unroll
+            for (int n4 = 0; n4 < NS; n4 += 4) {
+                const float4 b4 = *reinterpret_cast<const float4*>(sB + t * S::kBCPitch + n4);
+                const float4 c4 = *reinterpret_cast<const float4*>(sC + t * S::kBCPitch + n4);
+                const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, cc[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int n = n4 + i;
+                    h[n] = fmaf(decay_fast(d, A2[n]), h[n], du * bb[i]);
+                    if (i & 1) y1 = fmaf(cc[i], h[n], y1);
+                    else y = fmaf(cc[i], h[n], y);
+                }
+            }
+            su[t * S::kPitch + lane] = y + y1;
+        }
+        __syncwarp();
+        // ---- outputs: 16-byte pieces along each row
+#pragma unroll
+        for (int j = 0; j < OPR; ++j) {
+            const int idx = j * 32 + lane, rr = idx / OPR, piece = idx - rr * OPR;
+            const int pos = t0 + piece * OPP;
+            if (pos < L) {
+                float ov[OPP];
+#pragma unroll
+                for (int e = 0; e < OPP; ++e) ov[e] = su[(piece * OPP + e) * S::kPitch + rr];
+                VO::store(out + rr * a.o_ds + pos, ov);
+            }
+        }
+        __syncwarp();
+    }
+}
+
+template <typename Tin, typename Tout, int NS, int EPP>
+static int launch_rows(const ScanArgs& a, cudaStream_t st) {
+    using S = RowsSmem<NS>;
+    const size_t smem = (size_t)kRowsWarps * S::kFloatsPerWarp * sizeof(float);
+    auto kern = selscan_fwd_rows_kernel<Tin, Tout, NS, EPP>;
+    static bool attr_ok[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_ok[dev & 63]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return SS2D_ECUDA;
+        attr_ok[dev & 63] = true;
+    }
+    const int64_t warps = a.rows / 32;
+    const int64_t ctas = (warps + kRowsWarps - 1) / kRowsWarps;
+    if (ctas > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
+    kern<<<(unsigned)ctas, kRowsWarps * 32, smem, st>>>(a);
+    count_launch();
+    return check_launch();
+}
+
+// The lanes-are-rows kernel takes a problem when its rows come in whole groups of 32 per (image, group), every tensor
+// allows pieces of at least 8 bytes, each row has its own delta row, and there are enough rows to fill the GPU with warps.
+template <typename Tin, typename Tout, int EPP>
+static int rows_by_state(const ScanArgs& a, cudaStream_t st) {
+    if (a.dstate == 16) return launch_rows<Tin, Tout, 16, EPP>(a, st);
+    if (a.dstate == 8) return launch_rows<Tin, Tout, 8, EPP>(a, st);
+    return launch_rows<Tin, Tout, 4, EPP>(a, st);
+}
+template <typename Tin, typename Tout>
+static int try_rows(const ScanArgs& a, int vec, cudaStream_t st, bool& taken) {
+    taken = false;
+    if (a.dstate != 4 && a.dstate != 8 && a.dstate != 16) return SS2D_OK;
+    if (vec < 4 || a.dratio != 1 || a.group_size % 32 != 0 || a.rows < 32LL * 148 * 8) return SS2D_OK;
+    taken = true;
+    if constexpr (sizeof(Tin) == 2) {
+        if (vec >= 8) return rows_by_state<Tin, Tout, 8>(a, st);
+    }
+    return rows_by_state<Tin, Tout, 4>(a, st);
+}
+
 template <typename Tin, typename Tout, int VEC>
 static int launch_scan(const ScanArgs& a, cudaStream_t st) {
     const int64_t ctas = (a.rows + kWarpsPerCta - 1) / kWarpsPerCta;
@@ -188,6 +365,11 @@ static int launch_scan(const ScanArgs& a, cudaStream_t st) {
 
 template <typename Tin, typename Tout>
 static int dispatch_vec(const ScanArgs& a, int vec, cudaStream_t st) {
+    {
+        bool taken;
+        const int rc = try_rows<Tin, Tout>(a, vec, st, taken);
+        if (taken) return rc;
+    }
     if constexpr (sizeof(Tin) == 2) {
         if (vec >= 8) return launch_scan<Tin, Tout, 8>(a, st);
     }
