@@ -89,6 +89,34 @@ def test_selective_scan_bwd_fp32_vs_oracle(vb, Bt, K, Cd, N, L):
         assert err <= TOL["f32"], (name, err)
 
 
+@pytest.mark.parametrize("L,dt,oflex,opt", [(200, "f32", True, True), (392, "bf16", True, True), (136, "bf16", False, True),
+                                            (196, "f16", True, False), (16, "f32", True, True)])
+def test_selective_scan_bwd_many_rows(vb, L, dt, oflex, opt):
+    """d_state 1 with enough rows (26 x 4 x 384 = 39 936) for the lanes-are-rows backward kernel: rows of one chunk and a
+    ragged second one (L = 200), several chunks (392), a 14 x 14 map (196), a single tile; every gradient against
+    the oracle, and against the warp-per-row kernel on the first two images (too few rows for this one)."""
+    Bt, K, Cd = 26, 4, 384
+    u, delta, A, B, C, D, bias, dout = _random_case(Bt, K, Cd, 1, L, seed=L, with_D=opt, with_bias=opt)
+    if dt != "f32":
+        rnd = lambda a: O._round_to(a, dt)
+        u, delta, B, C = rnd(u), rnd(delta), rnd(B), rnd(C)
+        if not oflex:
+            dout = rnd(dout)
+    from vmamba_b200 import _lib
+    n0 = _lib.launch_count()
+    got = _autograd(vb, u, delta, A, B, C, D, bias, dout, True, oflex, dt)
+    assert _lib.launch_count() == n0 + 3          # forward, backward, fold
+    ref = O.selective_scan_bwd(u, delta, A, B, C, D, bias, dout, True, dt)
+    for name, x, r in zip(NAMES, got, ref):
+        assert (x is None) == (r is None), name
+        if x is not None:
+            err = O.max_rel_err(x, r)
+            assert err <= TOL[dt], (name, err)
+    few = _autograd(vb, u[:2], delta[:2], A, B[:2], C[:2], D, bias, dout[:2], True, oflex, dt)
+    for name, x, y in zip(NAMES[:2] + NAMES[3:5], got[:2] + got[3:5], few[:2] + few[3:5]):      # du, ddelta, dB, dC: per image
+        assert O.max_rel_err(x[:2], y) <= (2e-5 if dt == "f32" else TOL[dt]), name
+
+
 @pytest.mark.parametrize("dt", ["bf16", "f16"])
 @pytest.mark.parametrize("oflex", [True, False])
 def test_selective_scan_bwd_16bit_vs_oracle(vb, dt, oflex):

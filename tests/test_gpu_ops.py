@@ -152,9 +152,10 @@ def test_selective_scan_dstate16_sweep_shapes(vb, L, KD, dtype):
 
 
 @pytest.mark.parametrize("N,L,dtype,opt", [(16, 200, "bf16", True), (16, 68, "f32", True), (8, 160, "bf16", False),
-                                           (4, 32, "f32", False), (16, 392, "f16", True), (16, 196, "bf16", True)])
+                                           (4, 32, "f32", False), (16, 392, "f16", True), (16, 196, "bf16", True),
+                                           (1, 196, "bf16", True), (1, 64, "f32", False)])
 def test_selective_scan_many_rows_small_state(vb, N, L, dtype, opt):
-    """d_state 4 / 8 / 16 with enough rows (B x 4 x 384 = 39 936) for the lanes-are-rows kernel: whole and ragged tiles
+    """d_state 4 / 8 / 16 (and 1 on short rows) with enough rows (B x 4 x 384 = 39 936) for the lanes-are-rows kernel: whole and ragged tiles
     (L = 200 = 12 x 16 + 8; L = 196, a 14 x 14 map, whose 16-bit rows allow 8-byte pieces only), 16-bit and fp32 tensors, with and without D / bias / softplus, A drawn per row, against the
     C oracle; the states it leaves for the backward pass against the forward kernel for fewer rows."""
     rng = np.random.default_rng(N * 100 + L)

@@ -1,5 +1,6 @@
 // Shared device helpers for the SS2D kernels (sm_100a).
 #pragma once
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -221,5 +222,11 @@ inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintp
 
 void count_launch(int n = 1);
 int check_launch();   // cudaPeekAtLastError -> SS2D_OK / SS2D_ECUDA
+
+// SS2D_SCAN_ROWS=0 keeps the selective-scan operators on their warp-per-row kernels (a switch for comparisons)
+inline bool rows_kernels_enabled() {
+    static const bool on = [] { const char* e = getenv("SS2D_SCAN_ROWS"); return !(e && e[0] == '0'); }();
+    return on;
+}
 
 }  // namespace ss2d

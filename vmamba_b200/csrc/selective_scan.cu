@@ -188,7 +188,7 @@ constexpr int kRowsTile = 16;          // elements per tile: 6.8 KB of shared me
 constexpr int kRowsWarps = 4;
 template <int NS> struct RowsSmem {
     static constexpr int kPitch = 33;
-    static constexpr int kBCPitch = NS + 4;                      // rows stay 16-byte aligned
+    static constexpr int kBCPitch = NS >= 4 ? NS + 4 : NS;       // 16-byte aligned rows for the 16-byte reads of four states
     static constexpr int kFloatsPerWarp = 2 * kRowsTile * kPitch + 2 * kRowsTile * kBCPitch;
 };
 
@@ -276,20 +276,33 @@ __global__ void __launch_bounds__(kRowsWarps * 32, 6) selscan_fwd_rows_kernel(co
             float y = has_D ? Dv * uv : 0.f, y1 = 0.f;           // two partial sums: half the dependent chain
             if (a.ckpt && ((t0 + t) & 127) == 0) {               // the states in front of element t0 + t
                 float* ck = a.ckpt + ((row0 + lane) * a.nck + ((t0 + t) >> 7)) * NS;
+                if constexpr (NS >= 4) {
 #pragma unroll
-                for (int n = 0; n < NS; n += 4) *reinterpret_cast<float4*>(ck + n) = make_float4(h[n], h[n + 1], h[n + 2], h[n + 3]);
+                    for (int n = 0; n < NS; n += 4) *reinterpret_cast<float4*>(ck + n) = make_float4(h[n], h[n + 1], h[n + 2], h[n + 3]);
+                } else {
+#pragma unroll
+                    for (int n = 0; n < NS; ++n) ck[n] = h[n];
+                }
             }
+            if constexpr (NS >= 4) {
 #pragma unroll
-            for (int n4 = 0; n4 < NS; n4 += 4) {
-                const float4 b4 = *reinterpret_cast<const float4*>(sB + t * S::kBCPitch + n4);
-                const float4 c4 = *reinterpret_cast<const float4*>(sC + t * S::kBCPitch + n4);
-                const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, cc[4] = {c4.x, c4.y, c4.z, c4.w};
+                for (int n4 = 0; n4 < NS; n4 += 4) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(sB + t * S::kBCPitch + n4);
+                    const float4 c4 = *reinterpret_cast<const float4*>(sC + t * S::kBCPitch + n4);
+                    const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, cc[4] = {c4.x, c4.y, c4.z, c4.w};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int n = n4 + i;
-                    h[n] = fmaf(decay_fast(d, A2[n]), h[n], du * bb[i]);
-                    if (i & 1) y1 = fmaf(cc[i], h[n], y1);
-                    else y = fmaf(cc[i], h[n], y);
+                    for (int i = 0; i < 4; ++i) {
+                        const int n = n4 + i;
+                        h[n] = fmaf(decay_fast(d, A2[n]), h[n], du * bb[i]);
+                        if (i & 1) y1 = fmaf(cc[i], h[n], y1);
+                        else y = fmaf(cc[i], h[n], y);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int n = 0; n < NS; ++n) {
+                    h[n] = fmaf(decay_fast(d, A2[n]), h[n], du * sB[t * S::kBCPitch + n]);
+                    y = fmaf(sC[t * S::kBCPitch + n], h[n], y);
                 }
             }
             su[t * S::kPitch + lane] = y + y1;
@@ -337,13 +350,16 @@ template <typename Tin, typename Tout, int EPP>
 static int rows_by_state(const ScanArgs& a, cudaStream_t st) {
     if (a.dstate == 16) return launch_rows<Tin, Tout, 16, EPP>(a, st);
     if (a.dstate == 8) return launch_rows<Tin, Tout, 8, EPP>(a, st);
-    return launch_rows<Tin, Tout, 4, EPP>(a, st);
+    if (a.dstate == 4) return launch_rows<Tin, Tout, 4, EPP>(a, st);
+    return launch_rows<Tin, Tout, 1, EPP>(a, st);
 }
 template <typename Tin, typename Tout>
 static int try_rows(const ScanArgs& a, int vec, cudaStream_t st, bool& taken) {
     taken = false;
-    if (a.dstate != 4 && a.dstate != 8 && a.dstate != 16) return SS2D_OK;
-    if (vec < 4 || a.dratio != 1 || a.group_size % 32 != 0 || a.rows < 32LL * 148 * 8) return SS2D_OK;
+    // d_state 1: short rows only (bf16, fraction of the copy bandwidth, this kernel against the warp-per-row one: 0.42 / 0.35
+    // at L = 196, 0.42 / 0.54 at L = 784; the warp-per-row kernel reaches 0.8 from L = 3136 up)
+    if (a.dstate == 1 ? a.seqlen > 256 : (a.dstate != 4 && a.dstate != 8 && a.dstate != 16)) return SS2D_OK;
+    if (vec < 4 || a.dratio != 1 || a.group_size % 32 != 0 || a.rows < 32LL * 148 * 8 || !rows_kernels_enabled()) return SS2D_OK;
     taken = true;
     if constexpr (sizeof(Tin) == 2) {
         if (vec >= 8) return rows_by_state<Tin, Tout, 8>(a, st);

@@ -21,6 +21,8 @@
 // Sums that cross CTAs (dB / dC over the CTAs of a group, dA / dD / dbias over the batch) go to an
 // fp32 workspace as partials and are folded by a second kernel in a fixed order: no atomics, the
 // result is bit-identical from run to run.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace ss2d {
@@ -38,6 +40,7 @@ struct BwdArgs {
     int64_t dratio;   // channels per delta row
     const float* ckpt;   // states in front of every 128th element (rows, nck, N), or null: recompute them
     int64_t nck;
+    int64_t rows;        // batch * dim
 };
 
 template <typename Tin, typename Tg, int VEC>
@@ -434,6 +437,178 @@ __global__ void __launch_bounds__(256) selscan_bwd_n1_kernel(const BwdArgs a, co
     }
 }
 
+// d_state 1 with many rows and the forward call's checkpoints: LANES ARE ROWS.  A warp owns 32 consecutive rows of one
+// (image, group); every lane walks its own row, so the two recurrences are plain fused multiply-adds per element (no
+// running products, no shuffle scans, no CTA barrier), the per-row sums (dA, dD, dbias) stay in registers, and the
+// sums over the rows of a group (dB, dC) are column sums of a shared tile.  The row is walked chunk by chunk (128
+// elements, the checkpoint interval) from its end: a forward sweep over the chunk leaves the state in front of each of
+// its eight 16-element tiles, then the tiles are taken in reverse: forward over the tile with the states kept in
+// registers, backward over the same 16 elements.  Tiles are staged as in the forward lanes-are-rows kernel: pieces of
+// four elements in, fp32 transposed ([element][row], pitch 33) in shared memory, du / ddelta out through the same
+// buffers.  The chunk is read twice (sweep, then tiles); the second read finds it in L2.
+constexpr int kBwdTile = 16, kBwdRowsWarps = 4, kBwdPitch = 33;
+constexpr int kBwdFloatsPerWarp = 4 * kBwdTile * kBwdPitch + 8 * 32 + 2 * kBwdTile;
+
+template <typename Tin, typename Tg>
+__global__ void __launch_bounds__(kBwdRowsWarps * 32, 4) selscan_bwd_rows_kernel(const BwdArgs a) {
+    extern __shared__ float sm[];
+    constexpr int T = kBwdTile, P = kBwdPitch, PE = 4;         // PE: elements per piece (8 bytes of a 16-bit tensor)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* su = sm + (size_t)warp * kBwdFloatsPerWarp;         // u, then du
+    float* sd = su + T * P;                                    // delta, then ddelta
+    float* sg = sd + T * P;                                    // dout, then the rows' dB terms
+    float* sx = sg + T * P;                                    // the rows' dC terms
+    float* hs = sx + T * P;                                    // [tile of the chunk][row]: state in front of the tile
+    float* sB = hs + 8 * 32;
+    float* sC = sB + T;
+    const int64_t row0 = ((int64_t)blockIdx.x * kBwdRowsWarps + warp) * 32;
+    const int L = (int)a.seqlen;
+    if (row0 >= a.rows) return;
+    const int64_t b = row0 / a.dim, r0 = row0 % a.dim, k = r0 / a.group_size, part = (r0 - k * a.group_size) / 32;
+    const int64_t r = r0 + lane;
+    const Tin* __restrict__ u = (const Tin*)a.u + b * a.u_bs + r0 * a.u_ds;
+    const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + r0 * a.d_ds;
+    const Tg* __restrict__ gp = (const Tg*)a.dout + b * a.g_bs + r0 * a.g_ds;
+    const Tin* __restrict__ Bm = (const Tin*)a.B + b * a.B_bs + k * a.B_gs;
+    const Tin* __restrict__ Cm = (const Tin*)a.C + b * a.C_bs + k * a.C_gs;
+    Tin* __restrict__ du = (Tin*)a.du + (b * a.dim + r0) * L;
+    Tin* __restrict__ dd = (Tin*)a.ddelta + (b * a.dim + r0) * L;
+    float* __restrict__ bc_out = a.bcpart + (((size_t)b * a.n_groups + k) * a.parts + part) * 2 * (size_t)L;
+    const float* __restrict__ ck = a.ckpt + (b * a.dim + r) * a.nck;
+    const float An = __ldg(a.A + r), A2 = An * kLog2e;
+    const bool has_D = a.D != nullptr;
+    const float Dv = has_D ? __ldg(a.D + r) : 0.f;
+    const float bias = a.bias ? __ldg(a.bias + r) : 0.f;
+    const bool sp = a.softplus != 0;
+    using VI = Vec<Tin, PE>;
+    using VG = Vec<Tg, PE>;
+
+    // a tile of 32 rows x 16 elements of one tensor: four pieces per lane in, fp32 transposed out
+    auto stage_in = [&](auto* src, int64_t stride, int t0, float* dst) {
+        using E = std::remove_cv_t<std::remove_pointer_t<decltype(src)>>;
+#pragma unroll
+        for (int j = 0; j < T / PE; ++j) {
+            const int idx = j * 32 + lane, rr = idx / (T / PE), piece = idx - rr * (T / PE);
+            const int pos = t0 + piece * PE;
+            float v[PE];
+            if (pos < L) Vec<E, PE>::load(src + rr * stride + pos, v);
+            else {
+#pragma unroll
+                for (int e = 0; e < PE; ++e) v[e] = 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < PE; ++e) dst[(piece * PE + e) * P + rr] = v[e];
+        }
+    };
+    auto stage_row = [&](const Tin* src, int t0, float* dst, int first_lane) {     // one row of 16 elements (B or C)
+        const int piece = lane - first_lane;
+        if (piece >= 0 && piece < T / PE) {
+            const int pos = t0 + piece * PE;
+            float v[PE];
+            if (pos < L) VI::load(src + pos, v);
+            else {
+#pragma unroll
+                for (int e = 0; e < PE; ++e) v[e] = 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < PE; ++e) dst[piece * PE + e] = v[e];
+        }
+    };
+    auto stage_out = [&](const float* src, Tin* dst_rows, int t0) {
+#pragma unroll
+        for (int j = 0; j < T / PE; ++j) {
+            const int idx = j * 32 + lane, rr = idx / (T / PE), piece = idx - rr * (T / PE);
+            const int pos = t0 + piece * PE;
+            if (pos < L) {
+                float v[PE];
+#pragma unroll
+                for (int e = 0; e < PE; ++e) v[e] = src[(piece * PE + e) * P + rr];
+                VI::store(dst_rows + (int64_t)rr * L + pos, v);
+            }
+        }
+    };
+
+    float e_carry = 0.f, dA_acc = 0.f, dD_acc = 0.f, db_acc = 0.f;
+    for (int c = (int)a.nck - 1; c >= 0; --c) {
+        const int c0 = c * 128;
+        const int ntiles = min(8, (L - c0 + T - 1) / T);
+        // ---- forward sweep over the chunk: the state in front of each tile
+        float h = ck[c];
+        for (int j = 0; j < ntiles; ++j) {
+            hs[j * 32 + lane] = h;
+            if (j == ntiles - 1) break;
+            const int t0 = c0 + j * T;                         // a whole tile: it is not the last of the row
+            stage_in(u, a.u_ds, t0, su);
+            stage_in(dt, a.d_ds, t0, sd);
+            stage_row(Bm, t0, sB, 0);
+            __syncwarp();
+#pragma unroll 4
+            for (int t = 0; t < T; ++t) {
+                float d = sd[t * P + lane] + bias;
+                if (sp) d = softplus_fast(d);
+                h = fmaf(decay_fast(d, A2), h, d * su[t * P + lane] * sB[t]);
+            }
+            __syncwarp();
+        }
+        // ---- the tiles of the chunk, last first
+        for (int j = ntiles - 1; j >= 0; --j) {
+            const int t0 = c0 + j * T;
+            stage_in(u, a.u_ds, t0, su);
+            stage_in(dt, a.d_ds, t0, sd);
+            stage_in(gp, a.g_ds, t0, sg);
+            stage_row(Bm, t0, sB, 0);
+            stage_row(Cm, t0, sC, 4);
+            __syncwarp();
+            float av[T], dv[T], hl[T], ds[T];
+            const float hstart = hs[j * 32 + lane];
+            h = hstart;
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+                const bool ok = t0 + t < L;                    // beyond the row: a = 1, everything else 0
+                float x = sd[t * P + lane] + bias, g1 = 1.f;
+                if (sp) softplus_and_grad(x, x, g1);
+                x = ok ? x : 0.f;
+                ds[t] = ok ? g1 : 0.f;
+                dv[t] = x;
+                av[t] = decay_fast(x, A2);
+                h = fmaf(av[t], h, x * su[t * P + lane] * sB[t]);
+                hl[t] = h;
+            }
+#pragma unroll
+            for (int t = T - 1; t >= 0; --t) {
+                const float g = sg[t * P + lane], uv = su[t * P + lane], Bt = sB[t], Ct = sC[t];
+                const float dh = fmaf(Ct, g, e_carry);
+                const float hprev = t == 0 ? hstart : hl[t > 0 ? t - 1 : 0];
+                const float dhd = dh * dv[t];
+                const float tt = av[t] * hprev;
+                const float ddl = dh * fmaf(An, tt, Bt * uv) * ds[t];
+                su[t * P + lane] = fmaf(dhd, Bt, has_D ? g * Dv : 0.f);      // du
+                sd[t * P + lane] = ddl;                                     // ddelta
+                sg[t * P + lane] = dhd * uv;                                // this row's dB term
+                sx[t * P + lane] = g * hl[t];                               // this row's dC term
+                dA_acc = fmaf(dhd, tt, dA_acc);
+                dD_acc = fmaf(g, uv, dD_acc);
+                db_acc += ddl;
+                e_carry = av[t] * dh;
+            }
+            __syncwarp();
+            {   // sums over the 32 rows: lanes 0..15 the dB of element lane, lanes 16..31 the dC of element lane - 16
+                const int el = lane & 15;
+                const float* src = (lane < 16 ? sg : sx) + el * P;
+                float acc = 0.f;
+#pragma unroll
+                for (int rr = 0; rr < 32; ++rr) acc += src[rr];
+                if (t0 + el < L) bc_out[(size_t)(lane >> 4) * L + t0 + el] = acc;
+            }
+            stage_out(su, du, t0);
+            stage_out(sd, dd, t0);
+            __syncwarp();
+        }
+    }
+    float* rr = a.rowred + (b * a.dim + r) * 3;
+    rr[0] = dA_acc; rr[1] = dD_acc; rr[2] = db_acc;
+}
+
 // Folds the partials: dA / dD / dbias over the batch, dB / dC over the CTAs of a group (and rounds
 // them to the storage type).  One thread per output element, fixed summation order.
 template <typename Tin>
@@ -466,7 +641,7 @@ __global__ void selscan_bwd_fold_kernel(const float* rowred, const float* bcpart
     }
 }
 
-struct BwdPlan { int vec, rw, parts, nsteps, R; size_t smem; int64_t ws_floats, rowred_floats; };
+struct BwdPlan { int vec, rw, parts, nsteps, R; size_t smem; int64_t ws_floats, rowred_floats; bool rows; };
 
 static int common_pow2b(std::initializer_list<int64_t> xs, int cap) {
     int v = cap;
@@ -537,6 +712,14 @@ static int plan_bwd(const ss2d_scan_bwd_params* p, BwdPlan& c) {
         c.R = R; c.smem = smem_n1(rw, R);
         c.parts = (int)((gs + (int64_t)rw * R - 1) / ((int64_t)rw * R));
     }
+    // lanes-are-rows kernel: d_state 1, the forward call's checkpoints at hand, rows in whole groups of 32 per
+    // (image, group), pieces of four elements everywhere, a delta row per row, enough rows to fill the GPU with warps
+    c.rows = p->dstate == 1 && p->checkpoints != nullptr && gs % 32 == 0 && p->delta_ratio <= 1 && c.vec >= 4 &&
+             p->batch * p->dim >= 32LL * 148 * 8 && rows_kernels_enabled();
+    if (c.rows) {
+        c.parts = (int)(gs / 32);
+        c.smem = (size_t)kBwdRowsWarps * kBwdFloatsPerWarp * sizeof(float);
+    }
     c.rowred_floats = p->batch * p->dim * (p->dstate + 2);
     c.ws_floats = c.rowred_floats + p->batch * p->n_groups * c.parts * 2 * p->dstate * L;
     return SS2D_OK;
@@ -565,7 +748,20 @@ static int launch_bwd(const BwdArgs& a, const BwdPlan& c, int64_t ctas, cudaStre
 }
 
 template <typename Tin, typename Tg>
+static int launch_bwd_rows(const BwdArgs& a, const BwdPlan& c, cudaStream_t st) {
+    auto kern = selscan_bwd_rows_kernel<Tin, Tg>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem) != cudaSuccess) return SS2D_ECUDA;
+    const int64_t warps = a.rows / 32;
+    const int64_t ctas = (warps + kBwdRowsWarps - 1) / kBwdRowsWarps;
+    if (ctas > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
+    kern<<<(unsigned)ctas, kBwdRowsWarps * 32, c.smem, st>>>(a);
+    count_launch();
+    return check_launch();
+}
+
+template <typename Tin, typename Tg>
 static int dispatch_bwd(const BwdArgs& a, const BwdPlan& c, int64_t ctas, cudaStream_t st) {
+    if (c.rows) return launch_bwd_rows<Tin, Tg>(a, c, st);
     if (c.vec >= 4) return launch_bwd<Tin, Tg, 4>(a, c, ctas, st);
     if (c.vec >= 2) return launch_bwd<Tin, Tg, 2>(a, c, ctas, st);
     return launch_bwd<Tin, Tg, 1>(a, c, ctas, st);
@@ -604,6 +800,7 @@ int selective_scan_bwd(const ss2d_scan_bwd_params* p, cudaStream_t st) {
     a.N = (int)p->dstate; a.n_groups = (int)p->n_groups; a.parts = c.parts; a.nsteps = c.nsteps; a.softplus = p->delta_softplus;
     a.dratio = p->delta_ratio > 1 ? p->delta_ratio : 1;
     a.ckpt = (const float*)p->checkpoints; a.nck = (p->seqlen + 127) / 128;
+    a.rows = p->batch * p->dim;
     const int64_t ctas = p->batch * p->n_groups * c.parts;
     if (ctas > 0x7fffffffLL) return SS2D_EINVAL_SHAPE;
     const bool gf32 = p->dout_dtype == SS2D_F32;
