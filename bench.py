@@ -387,6 +387,10 @@ def reference_modules_leg(local: int, steps: int = 5):
     finally:
         vb.disable_fused(m)
         vb.uninstall(ref)
+    # ---- the same module handed to accelerate(): this library's backbone on the module's weights, eager (no graph) ----
+    fast = vb.accelerate(m)
+    x16 = x.to(torch.bfloat16)
+    out["img_s_accelerated_module"] = BATCH / (time_events(lambda: fast(x16), steps) * 1e-3)
     return out
 
 

@@ -107,6 +107,60 @@ def test_reference_vssm_on_library_operators(vb, ref, dims, depths, hw, ratio):
         torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = old
 
 
+def test_accelerate_hands_back_an_equivalent_inference_module(vb, ref):
+    """accelerate(): a reference VSSM / Backbone_VSSM -> this library's backbone on the module's own weights; logits and
+    feature maps against the CPU oracle, a family the backbone does not reproduce is refused."""
+    m, img = _model(ref, 32, [1, 1, 2, 1], (64, 64), 1.0)
+    want = _oracle_logits(m, img)
+    m = m.cuda()
+    fast = vb.accelerate(m)
+    assert isinstance(fast, torch.nn.Module) and not fast.training
+    got = fast(img.cuda())
+    assert got.shape == want.shape and O.max_rel_err(got.float().cpu().numpy(), want) <= TOL_BF16
+    old = torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cudnn.allow_tf32 = torch.backends.cuda.matmul.allow_tf32 = False      # fp32 means fp32 in the library calls too
+    try:
+        _accelerate_fp32_checks(vb, ref, m, img, want)
+    finally:
+        torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = old
+
+
+def _accelerate_fp32_checks(vb, ref, m, img, want):
+    fast = vb.accelerate(m)
+    fast32 = vb.accelerate(m, dtype=torch.float32)
+    assert O.max_rel_err(fast32(img.cuda()).float().cpu().numpy(), want) <= TOL_F32
+    assert m.training is False and not hasattr(ref, "__vmamba_b200_saved__")      # the module is left as it was
+    with pytest.raises(RuntimeError):
+        fast.train()
+    # the dense-prediction backbone: four LayerNorm'ed maps
+    torch.manual_seed(1)
+    bb = ref.Backbone_VSSM(out_indices=(0, 1, 2, 3), pretrained=None, depths=[1, 1, 2, 1], dims=32, drop_path_rate=0.0, patch_size=4,
+                           in_chans=3, num_classes=10, ssm_d_state=1, ssm_ratio=1.0, ssm_dt_rank="auto", ssm_act_layer="silu",
+                           ssm_conv=3, ssm_conv_bias=False, ssm_drop_rate=0.0, ssm_init="v0", forward_type="v05_noz",
+                           mlp_ratio=4.0, mlp_act_layer="gelu", mlp_drop_rate=0.0, gmlp=False, patch_norm=True, norm_layer="ln2d",
+                           downsample_version="v3", patchembed_version="v2", use_checkpoint=False, posembed=False,
+                           imgsize=64).cuda().eval()
+    fb = vb.accelerate(bb, dtype=torch.float32)
+    vb.install(ref)
+    try:
+        with torch.no_grad():
+            maps = bb(img.cuda())
+    finally:
+        vb.uninstall(ref)
+    outs = fb(img.cuda())
+    assert len(outs) == len(maps) == 4
+    for a_, b_ in zip(outs, maps):
+        assert a_.shape == b_.shape and O.max_rel_err(a_.float().cpu().numpy(), b_.float().cpu().numpy()) <= 2e-4
+    # a block with a z branch (forward_type v05) is another family
+    cfg = dict(depths=[1, 1, 1, 1], dims=16, drop_path_rate=0.0, patch_size=4, in_chans=3, num_classes=10, ssm_d_state=1,
+               ssm_ratio=1.0, ssm_dt_rank="auto", ssm_act_layer="silu", ssm_conv=3, ssm_conv_bias=False, ssm_drop_rate=0.0,
+               ssm_init="v0", forward_type="v05", mlp_ratio=4.0, mlp_act_layer="gelu", mlp_drop_rate=0.0, gmlp=False,
+               patch_norm=True, norm_layer="ln2d", downsample_version="v3", patchembed_version="v2", use_checkpoint=False,
+               posembed=False, imgsize=64)
+    with pytest.raises(NotImplementedError):
+        vb.accelerate(ref.VSSM(**cfg).cuda().eval())
+
+
 @pytest.mark.skipif(not stage_ref.staged("csms6s.py"), reason="csms6s.py not staged")
 def test_reference_csms6s_on_extension_stand_in(vb):
     """The reference's own csms6s.py, imported unchanged after `preseed_extension_module()`: its SelectiveScanCuda

@@ -11,6 +11,7 @@ from .ops import (CrossMerge, CrossMergeF, CrossMergeTritonF, CrossScan, CrossSc
 from .fused import CoreWeights, disable_fused, enable_fused, ss2d_core, ss2d_core_autograd  # noqa: E402
 from .patch import install, preseed_extension_module, preseed_sys_modules, uninstall  # noqa: E402
 from .runner import GraphedBackbone  # noqa: E402
+from .backbone import AcceleratedVSSM, VSSMInfer, accelerate  # noqa: E402
 
 __all__ = [
     "selective_scan_fn", "selective_scan_fwd", "selective_scan_bwd", "SelectiveScanCuda", "SelectiveScanOflex",
@@ -19,4 +20,5 @@ __all__ = [
     "CrossScanF", "CrossMergeF", "CrossScanTritonF", "CrossMergeTritonF", "CrossScan", "CrossMerge",
     "layer_norm_cf", "ss2d_core", "ss2d_core_autograd", "CoreWeights", "enable_fused", "disable_fused",
     "install", "uninstall", "preseed_sys_modules", "preseed_extension_module", "GraphedBackbone",
+    "VSSMInfer", "AcceleratedVSSM", "accelerate",
 ]

@@ -255,3 +255,82 @@ class VSSMInfer:
             w, b = self.outnorm[i]
             res.append(self._ln(outs[i], w, b, torch.float32, out_cm=False))
         return res
+
+
+class AcceleratedVSSM(torch.nn.Module):
+    """A reference `VSSM` / `Backbone_VSSM` module replaced, for inference, by this library's backbone on the same
+    weights: `forward(images)` returns what the module's own forward returns (logits, vmamba.py:2027-2035, or the list of
+    LayerNorm'ed feature maps, vmamba.py:2133-2153).  Built by `accelerate`."""
+
+    def __init__(self, fast: VSSMInfer, features: bool, out_indices: Sequence[int]):
+        super().__init__()
+        self.fast, self._features, self.out_indices = fast, features, tuple(out_indices)
+        self.training = False
+
+    @torch.no_grad()
+    def forward(self, images: torch.Tensor):
+        images = images.to(device=self.fast.device, dtype=self.fast.dtype)
+        if self._features:
+            return self.fast.features(images, self.out_indices)
+        return self.fast(images)
+
+    def train(self, mode: bool = True):
+        if mode:
+            raise RuntimeError("AcceleratedVSSM is an inference module: train the reference module on the operator "
+                               "surface (vmamba_b200.install) instead")
+        return super().train(False)
+
+
+def accelerate(model: torch.nn.Module, dtype: torch.dtype = torch.bfloat16, check: bool = True) -> AcceleratedVSSM:
+    """The one-call drop-in at model level: a reference `VSSM` (or `Backbone_VSSM`) of the `v05_noz` channel-first family
+    on a CUDA device -> an inference module that runs this library's backbone (channel-major maps, fused SS2D core,
+    tcgen05 x_proj and MLP kernels) on the module's own weights.
+
+    With `check` the two are compared on two random 64 x 64 images in fp32 before the module is handed over (the
+    reference side runs on this library's operator surface for the comparison); a model of another family, or one this
+    library does not reproduce, raises NotImplementedError instead of returning something that computes something else.
+    """
+    import sys
+    params = list(model.parameters())
+    if not params or not params[0].is_cuda:
+        raise RuntimeError("accelerate() expects a module on a CUDA device (there is no CPU path)")
+    device = params[0].device
+    features = hasattr(model, "out_indices") and not hasattr(model, "classifier")
+    out_indices = tuple(getattr(model, "out_indices", (0, 1, 2, 3)))
+    sd = model.state_dict()
+    try:
+        fast = VSSMInfer.from_state_dict(sd, dtype=dtype, device=device)
+    except (KeyError, NotImplementedError, RuntimeError) as e:
+        raise NotImplementedError(f"accelerate(): not a v05_noz channel-first VSSM this library reproduces ({e})") from e
+    if check:
+        from . import patch
+        was_training = model.training
+        ref_module = sys.modules.get(type(model).__module__)
+        probe = VSSMInfer.from_state_dict(sd, dtype=torch.float32, device=device)
+        g = torch.Generator(device="cpu").manual_seed(0)
+        x = torch.randn((2, 3, 64, 64), generator=g).to(device)
+        old = torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cudnn.allow_tf32 = torch.backends.cuda.matmul.allow_tf32 = False
+        installed = ref_module is not None and not hasattr(ref_module, "__vmamba_b200_saved__")
+        try:
+            if installed:
+                patch.install(ref_module)
+            model.eval()
+            with torch.no_grad():
+                want = model(x)
+                got = probe.features(x, out_indices) if features else probe(x)
+        except Exception as e:      # the reference module itself could not run this input on the operator surface
+            raise NotImplementedError(f"accelerate(): the module did not run on the operator surface ({type(e).__name__}: {e})") from e
+        finally:
+            if installed:
+                patch.uninstall(ref_module)
+            model.train(was_training)
+            torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = old
+        pairs = list(zip(want, got)) if features else [(want, got)]
+        for w_, g_ in pairs:
+            err = (w_.float() - g_.float()).abs().max().item() / max(w_.float().abs().max().item(), 1e-30)
+            if not (err <= 1e-3):
+                raise NotImplementedError(f"accelerate(): this library's backbone does not reproduce the module "
+                                          f"(max relative difference {err:.2e} on a 64 x 64 probe)")
+        del probe
+    return AcceleratedVSSM(fast, features, out_indices)
