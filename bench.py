@@ -387,6 +387,29 @@ def reference_modules_leg(local: int, steps: int = 5):
     finally:
         vb.disable_fused(m)
         vb.uninstall(ref)
+    # ---- one training step of the same module on the operator surface (forward, backward through SelectiveScanCuda /
+    #      CrossScanF / CrossMergeF of this library, SGD update), eager, bf16 autocast ----
+    vb.install(ref)
+    try:
+        m.train()
+        opt = torch.optim.SGD(m.parameters(), lr=1e-4)
+        tb = min(BATCH, 64)
+        xt = x[:tb]
+
+        def train_step():
+            opt.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = m(xt).float().logsumexp(1).mean()
+            loss.backward()
+            opt.step()
+        out["train_img_s_surface_operators"] = tb / (time_events(train_step, max(3, steps // 2)) * 1e-3)
+        out["train_batch"] = tb
+    except Exception as e:      # the inference lines above stand on their own
+        out["train_img_s_surface_operators"] = None
+        out["train_error"] = f"{type(e).__name__}: {e}"[:200]
+    finally:
+        m.eval()
+        vb.uninstall(ref)
     # ---- the same module handed to accelerate(): this library's backbone on the module's weights, eager (no graph) ----
     fast = vb.accelerate(m)
     x16 = x.to(torch.bfloat16)
