@@ -48,11 +48,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return false;
 }
 
-// The same for the two threads of a load-bound pipeline (TMA producer, MMA issuer): attempts without a sleep hint,
-// which return as soon as the phase completes (a hinted wait was measured to wake late: 4 us per trip round an 8-stage
-// ring instead of 1.5).  Bounded by attempts.
+// The same for the threads of a load-bound pipeline (TMA producer, MMA issuer, the epilogue's hand-over): attempts
+// without a sleep hint.  Bounded by time: every 256 missed attempts the global nanosecond timer is read, and two seconds
+// after the first miss the wait gives up (error flag, as above).
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait_prompt(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    for (unsigned i = 0; i < (1u << 26); ++i) {
+    unsigned long long t0 = 0;
+    for (unsigned i = 0;; ++i) {
         uint32_t ok;
         asm volatile(
             "{\n .reg .pred p;\n"
@@ -60,7 +66,12 @@ __device__ __forceinline__ bool mbar_wait_prompt(uint64_t* bar, uint32_t parity,
             " selp.u32 %0, 1, 0, p;\n}"
             : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
         if (ok) return true;
-        if ((i & 1023) == 1023 && *abort_flag) return false;
+        if ((i & 255) == 255) {
+            if (*abort_flag) return false;
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 2000000000ull) break;
+        }
     }
     *abort_flag = 1;
     return false;
