@@ -31,8 +31,14 @@ FILES = {"vmamba.py": "vmamba.py", "csms6s.py": os.path.join(_MODELS, "csms6s.py
          "csm_triton.py": os.path.join(_MODELS, "csm_triton.py"), "tree_vmamba.py": os.path.join(_MODELS, "vmamba.py")}
 
 
-def stage(ref_root: str = "/root/reference") -> list:
+def default_checkout() -> str:
+    """Where a VMamba checkout is looked for: $VMAMBA_REFERENCE, else a folder `reference` beside this repository."""
+    return os.environ.get("VMAMBA_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def stage(ref_root: str | None = None) -> list:
     done = []
+    ref_root = ref_root or default_checkout()
     if not os.path.isdir(ref_root):
         return done
     os.makedirs(REF_DIR, exist_ok=True)
@@ -112,5 +118,5 @@ def load(name: str = "vmamba.py", module_name: str | None = None):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=None, help="VMamba checkout (default: $VMAMBA_REFERENCE or ../reference)")
     print("staged:", stage(ap.parse_args().ref))
