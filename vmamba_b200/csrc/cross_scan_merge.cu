@@ -207,93 +207,105 @@ __global__ void __launch_bounds__(256) cross_scan_plane_kernel(const PlaneArgs a
     const int np = (int)min((long long)a.PP, a.planes - plane0);
     const int L = a.L, n = np * a.nvec, W = a.W, H = a.H, Wp = W | 1, Lp = H * Wp;
     const T* __restrict__ x = (const T*)a.in + plane0 * L;
+    RouteMapI rm[4];
+    bool any_col = false;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { rm[k] = narrow(a.route[k]); any_col = any_col || rm[k].col_like; }
+    // ---- every vector of x: straight out for the row-major routes (as it is, or mirrored with its elements reversed),
+    //      into the padded shared plane for the column-major ones
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const int pl = mdiv_u(i, a.magic_nvec), p0 = (i - pl * a.nvec) * PV;
+        const unsigned plane = (unsigned)plane0 + (unsigned)pl;                // B * C < 2^31 (checked by the caller)
+        const unsigned b = plane / (unsigned)a.C, c = plane - b * (unsigned)a.C;
         const typename Vec<T, PV>::Raw r = Vec<T, PV>::load_raw(x + (long long)i * PV);
         const T* e = reinterpret_cast<const T*>(&r);
-        int h = mdiv_u(p0, a.magic_W), w = p0 - h * W;
-        T* dst = sm + pl * Lp;
+        typename Vec<T, PV>::Raw rev;
+        T* er = reinterpret_cast<T*>(&rev);
 #pragma unroll
-        for (int j = 0; j < PV; ++j) {
-            dst[h * Wp + w] = e[j];
-            if (++w == W) { w = 0; ++h; }
+        for (int j = 0; j < PV; ++j) er[j] = e[PV - 1 - j];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (rm[k].col_like) continue;
+            T* dst = (T*)a.out + ((long long)(b * 4 + k) * a.C + c) * L;
+            if (rm[k].sw > 0) Vec<T, PV>::store_raw(dst + p0, r);
+            else Vec<T, PV>::store_raw(dst + (L - PV - p0), rev);
+        }
+        if (any_col) {
+            int h = mdiv_u(p0, a.magic_W), w = p0 - h * W;
+            T* dst = sm + pl * Lp;
+#pragma unroll
+            for (int j = 0; j < PV; ++j) {
+                dst[h * Wp + w] = e[j];
+                if (++w == W) { w = 0; ++h; }
+            }
         }
     }
+    if (!any_col) return;                                  // uniform over the grid
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const RouteMapI m = narrow(a.route[k]);
+        const RouteMapI m = rm[k];
+        if (!m.col_like) continue;
         for (int i = threadIdx.x; i < n; i += blockDim.x) {
             const int pl = mdiv_u(i, a.magic_nvec), l0 = (i - pl * a.nvec) * PV;
-            const unsigned plane = (unsigned)plane0 + (unsigned)pl;            // B * C < 2^31 (checked by the caller)
+            const unsigned plane = (unsigned)plane0 + (unsigned)pl;
             const unsigned b = plane / (unsigned)a.C, c = plane - b * (unsigned)a.C;
             typename Vec<T, PV>::Raw r;
             T* e = reinterpret_cast<T*>(&r);
             const T* src = sm + pl * Lp;
-            if (!m.col_like) {
-                // row-major route, forward or reversed: source pixel l or L - 1 - l
-                int p = m.sw > 0 ? l0 : m.base - l0;
-                int h = mdiv_u(p, a.magic_W), w = p - h * W;
+            // column-major route: l - base = sh * h + sw * w with |sh| = 1, |sw| = H; walk h first
+            const int t = (int)(m.sw > 0 ? 0 : -m.sw * (W - 1));
+            const int r0 = l0 - m.base + t + (m.sh < 0 ? (H - 1) : 0);     // = hh + H * ww with hh, ww in range
+            int ww = mdiv_u(r0, a.magic_H), hh = r0 - ww * H;
 #pragma unroll
-                for (int j = 0; j < PV; ++j) {
-                    e[j] = src[h * Wp + w];
-                    if (m.sw > 0) { if (++w == W) { w = 0; ++h; } }
-                    else { if (--w < 0) { w = W - 1; --h; } }
-                }
-            } else {
-                // column-major route: l - base = sh * h + sw * w with |sh| = 1, |sw| = H; walk h first
-                const int t = (int)(m.sw > 0 ? 0 : -m.sw * (W - 1));
-                const int r0 = l0 - m.base + t + (m.sh < 0 ? (H - 1) : 0);     // = hh + H * ww with hh, ww in range
-                int ww = mdiv_u(r0, a.magic_H), hh = r0 - ww * H;
-#pragma unroll
-                for (int j = 0; j < PV; ++j) {
-                    const int h = m.sh > 0 ? hh : H - 1 - hh, w = m.sw > 0 ? ww : W - 1 - ww;
-                    e[j] = src[h * Wp + w];
-                    if (++hh == H) { hh = 0; ++ww; }
-                }
+            for (int j = 0; j < PV; ++j) {
+                const int h = m.sh > 0 ? hh : H - 1 - hh, w = m.sw > 0 ? ww : W - 1 - ww;
+                e[j] = src[h * Wp + w];
+                if (++hh == H) { hh = 0; ++ww; }
             }
             Vec<T, PV>::store_raw((T*)a.out + ((long long)(b * 4 + k) * a.C + c) * L + l0, r);
         }
     }
 }
 
+// Row-major routes (forward or reversed) are read straight from global memory as the vectors the output wants; only
+// the column-major routes (at most two) pass through shared memory, each plane in its own order with an odd line pitch.
 template <typename T, int PV>
 __global__ void __launch_bounds__(256) cross_merge_plane_kernel(const PlaneArgs a, const int scans) {
     extern __shared__ __align__(16) unsigned char smraw[];
-    T* sm = reinterpret_cast<T*>(smraw);                   // [4][PP][padded plane]: every route's plane, in its own order
+    T* sm = reinterpret_cast<T*>(smraw);                   // [2][PP][W][H | 1]
     const long long plane0 = (long long)blockIdx.x * a.PP;
     const int np = (int)min((long long)a.PP, a.planes - plane0);
     const int L = a.L, n = np * a.nvec, W = a.W, H = a.H;
-    const int Wp = W | 1, Hp = H | 1;
-    const int Lmax = max(H * Wp, W * Hp);                  // room of one padded plane, whichever way it is laid out
-    // a route's plane in shared memory: lines of its fast index (w for row-major routes, h for column-major ones)
+    const int Hp = H | 1, Lp = W * Hp;
     RouteMapI rm[4];
+    int slot[4], nslots = 0;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         rm[k] = narrow(a.route[k]);
-        const int fast = rm[k].col_like ? H : W, pitch = rm[k].col_like ? Hp : Wp;
-        const int b_lo = rm[k].base % fast, b_hi = rm[k].base / fast;
-        rm[k].base = b_lo + pitch * b_hi;
-        if (rm[k].col_like) rm[k].sw = rm[k].sw > 0 ? Hp : -Hp;
-        else rm[k].sh = rm[k].sh > 0 ? Wp : -Wp;
+        slot[k] = -1;
+        if (rm[k].col_like) {
+            slot[k] = nslots++;
+            const int b_lo = rm[k].base % H, b_hi = rm[k].base / H;
+            rm[k].base = b_lo + Hp * b_hi;
+            rm[k].sw = rm[k].sw > 0 ? Hp : -Hp;
+        }
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const bool col = rm[k].col_like != 0;
-        const int fast = col ? H : W, pitch = col ? Hp : Wp;
-        const unsigned magic_fast = col ? a.magic_H : a.magic_W;
+        if (slot[k] < 0) continue;
         for (int i = threadIdx.x; i < n; i += blockDim.x) {
             const int pl = mdiv_u(i, a.magic_nvec), l0 = (i - pl * a.nvec) * PV;
             const unsigned plane = (unsigned)plane0 + (unsigned)pl;
             const unsigned b = plane / (unsigned)a.C, c = plane - b * (unsigned)a.C;
             const typename Vec<T, PV>::Raw r = Vec<T, PV>::load_raw((const T*)a.in + ((long long)(b * 4 + k) * a.C + c) * L + l0);
             const T* e = reinterpret_cast<const T*>(&r);
-            int line = mdiv_u(l0, magic_fast), pos = l0 - line * fast;
-            T* dst = sm + (k * a.PP + pl) * Lmax;
+            int line = mdiv_u(l0, a.magic_H), pos = l0 - line * H;
+            T* dst = sm + (slot[k] * a.PP + pl) * Lp;
 #pragma unroll
             for (int j = 0; j < PV; ++j) {
-                dst[line * pitch + pos] = e[j];
-                if (++pos == fast) { pos = 0; ++line; }
+                dst[line * Hp + pos] = e[j];
+                if (++pos == H) { pos = 0; ++line; }
             }
         }
     }
@@ -301,18 +313,34 @@ __global__ void __launch_bounds__(256) cross_merge_plane_kernel(const PlaneArgs 
     T* __restrict__ y = (T*)a.out + plane0 * L;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const int pl = mdiv_u(i, a.magic_nvec), p0 = (i - pl * a.nvec) * PV;
-        typename Vec<T, PV>::Raw r;
-        T* e = reinterpret_cast<T*>(&r);
+        const unsigned plane = (unsigned)plane0 + (unsigned)pl;
+        const unsigned b = plane / (unsigned)a.C, c = plane - b * (unsigned)a.C;
+        T v[4][PV];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (slot[k] >= 0) continue;
+            const T* src = (const T*)a.in + ((long long)(b * 4 + k) * a.C + c) * L;
+            const bool fwd = rm[k].sw > 0;
+            const typename Vec<T, PV>::Raw r = Vec<T, PV>::load_raw(src + (fwd ? p0 : L - PV - p0));
+            const T* e = reinterpret_cast<const T*>(&r);
+#pragma unroll
+            for (int j = 0; j < PV; ++j) v[k][j] = e[fwd ? j : PV - 1 - j];
+        }
         int h = mdiv_u(p0, a.magic_W), w = p0 - h * W;
 #pragma unroll
         for (int j = 0; j < PV; ++j) {
-            T v[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) v[k] = sm[(k * a.PP + pl) * Lmax + rm[k].base + rm[k].sh * h + rm[k].sw * w];
-            if (scans == 0 || scans == 2) e[j] = add_t(add_t(v[0], v[2]), add_t(v[1], v[3]));
-            else if (scans == 3) e[j] = add_t(add_t(add_t(v[0], v[1]), v[2]), v[3]);
-            else e[j] = from_f<T>(((to_f<T>(v[0]) + to_f<T>(v[1])) + to_f<T>(v[2])) + to_f<T>(v[3]));
+            for (int k = 0; k < 4; ++k)
+                if (slot[k] >= 0) v[k][j] = sm[(slot[k] * a.PP + pl) * Lp + rm[k].base + rm[k].sh * h + rm[k].sw * w];
             if (++w == W) { w = 0; ++h; }
+        }
+        typename Vec<T, PV>::Raw r;
+        T* e = reinterpret_cast<T*>(&r);
+#pragma unroll
+        for (int j = 0; j < PV; ++j) {
+            if (scans == 0 || scans == 2) e[j] = add_t(add_t(v[0][j], v[2][j]), add_t(v[1][j], v[3][j]));
+            else if (scans == 3) e[j] = add_t(add_t(add_t(v[0][j], v[1][j]), v[2][j]), v[3][j]);
+            else e[j] = from_f<T>(((to_f<T>(v[0][j]) + to_f<T>(v[1][j])) + to_f<T>(v[2][j])) + to_f<T>(v[3][j]));
         }
         Vec<T, PV>::store_raw(y + (long long)i * PV, r);
     }
@@ -323,7 +351,7 @@ template <typename T>
 static bool plan_plane(const ss2d_cross_params* p, int copies, PlaneArgs& a, int& pv, size_t& smem) {
     const long long L = p->H * p->W;
     // shared-memory room of one plane with its odd line pitch (the merge keeps planes of either orientation)
-    const long long Lp = copies == 1 ? p->H * (p->W | 1) : std::max(p->H * (p->W | 1), p->W * (p->H | 1));
+    const long long Lp = copies == 1 ? p->H * (p->W | 1) : p->W * (p->H | 1);    // scan: x row-major; merge: column-major routes
     if (Lp * (long long)sizeof(T) * copies > 64 * 1024) return false;
     pv = 16 / (int)sizeof(T);
     auto fit = [&](long long x) { while (pv > 1 && (x % pv) != 0) pv >>= 1; };
@@ -425,9 +453,9 @@ int cross_merge(const ss2d_cross_params* p, cudaStream_t st) {
     if (rc != SS2D_OK) return rc;
     {
         PlaneArgs pa; int pv; size_t smem;
-        if (p->dtype == SS2D_F32) { if (plan_plane<float>(p, 4, pa, pv, smem)) return merge_plane_v<float>(pa, p->scans, pv, smem, st); }
-        else if (p->dtype == SS2D_BF16) { if (plan_plane<__nv_bfloat16>(p, 4, pa, pv, smem)) return merge_plane_v<__nv_bfloat16>(pa, p->scans, pv, smem, st); }
-        else if (plan_plane<__half>(p, 4, pa, pv, smem)) return merge_plane_v<__half>(pa, p->scans, pv, smem, st);
+        if (p->dtype == SS2D_F32) { if (plan_plane<float>(p, 2, pa, pv, smem)) return merge_plane_v<float>(pa, p->scans, pv, smem, st); }
+        else if (p->dtype == SS2D_BF16) { if (plan_plane<__nv_bfloat16>(p, 2, pa, pv, smem)) return merge_plane_v<__nv_bfloat16>(pa, p->scans, pv, smem, st); }
+        else if (plan_plane<__half>(p, 2, pa, pv, smem)) return merge_plane_v<__half>(pa, p->scans, pv, smem, st);
     }
     const dim3 blk(kTile, kMergeRows);
     if (p->dtype == SS2D_F32) cross_merge_kernel<float><<<(unsigned)a.n_tiles, blk, 0, st>>>(a, p->scans);
