@@ -128,23 +128,39 @@ template <typename T> __device__ __forceinline__ T add_t(T x, T y) { return from
 
 template <typename T>
 __global__ void __launch_bounds__(kTile * kMergeRows) cross_merge_kernel(const CrossArgs a, const int scans) {
-    __shared__ T tile[4][kTile][kTile + 1];
+    __shared__ T tile[2][kTile][kTile + 1];               // the column-like routes (at most two); the others are read in place
     const unsigned t = blockIdx.x, tiles_w = (unsigned)a.tiles_w, tiles_h = (unsigned)a.tiles_h, C = (unsigned)a.C;
     const unsigned tw = t % tiles_w, rest = t / tiles_w, th = rest % tiles_h, plane = rest / tiles_h;
     const unsigned b = plane / C, c = plane - b * C;
     const int H = (int)a.H, W = (int)a.W, L = H * W;
     const int h0 = (int)th * kTile, w0 = (int)tw * kTile;
     const int tx = threadIdx.x, ty = threadIdx.y;
+    int slot[4], nslots = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) slot[k] = a.route[k].col_like ? nslots++ : -1;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
+        if (slot[k] < 0) continue;
         const int base = (int)a.route[k].base, sh = (int)a.route[k].sh, sw = (int)a.route[k].sw;
-        const bool col_like = a.route[k].col_like != 0;
         const T* __restrict__ ys = (const T*)a.in + ((long long)(b * 4 + k) * C + c) * L;
 #pragma unroll
         for (int j = 0; j < kTile; j += kMergeRows) {
-            const int lh = col_like ? tx : ty + j, lw = col_like ? ty + j : tx;
+            const int lh = tx, lw = ty + j;               // thread x index runs along h: the route's contiguous direction
             const int h = h0 + lh, w = w0 + lw;
-            if (h < H && w < W) tile[k][lh][lw] = ys[base + sh * h + sw * w];
+            if (h < H && w < W) tile[slot[k]][lh][lw] = ys[base + sh * h + sw * w];
+        }
+    }
+    // the row-like routes' values of this thread's output elements: their loads fly together with the ones above
+    T direct[4][kTile / kMergeRows];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (slot[k] >= 0) continue;
+        const int base = (int)a.route[k].base, sh = (int)a.route[k].sh, sw = (int)a.route[k].sw;
+        const T* __restrict__ ys = (const T*)a.in + ((long long)(b * 4 + k) * C + c) * L;
+#pragma unroll
+        for (int j = 0; j < kTile; j += kMergeRows) {
+            const int h = h0 + ty + j, w = w0 + tx;
+            if (h < H && w < W) direct[k][j / kMergeRows] = ys[base + sh * h + sw * w];
         }
     }
     __syncthreads();
@@ -153,11 +169,13 @@ __global__ void __launch_bounds__(kTile * kMergeRows) cross_merge_kernel(const C
     for (int j = 0; j < kTile; j += kMergeRows) {
         const int h = h0 + ty + j, w = w0 + tx;
         if (h < H && w < W) {
-            const T v0 = tile[0][ty + j][tx], v1 = tile[1][ty + j][tx], v2 = tile[2][ty + j][tx], v3 = tile[3][ty + j][tx];
+            T v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = slot[k] >= 0 ? tile[slot[k]][ty + j][tx] : direct[k][j / kMergeRows];
             T r;
-            if (scans == 0 || scans == 2) r = add_t(add_t(v0, v2), add_t(v1, v3));   // (y0+y2) + (y1+y3)
-            else if (scans == 3) r = add_t(add_t(add_t(v0, v1), v2), v3);            // ((y0+y1)+y2)+y3
-            else r = from_f<T>(((to_f<T>(v0) + to_f<T>(v1)) + to_f<T>(v2)) + to_f<T>(v3));   // one reduction, rounded once
+            if (scans == 0 || scans == 2) r = add_t(add_t(v[0], v[2]), add_t(v[1], v[3]));   // (y0+y2) + (y1+y3)
+            else if (scans == 3) r = add_t(add_t(add_t(v[0], v[1]), v[2]), v[3]);            // ((y0+y1)+y2)+y3
+            else r = from_f<T>(((to_f<T>(v[0]) + to_f<T>(v[1])) + to_f<T>(v[2])) + to_f<T>(v[3]));   // one reduction, rounded once
             y[h * W + w] = r;
         }
     }
