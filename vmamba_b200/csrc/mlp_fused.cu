@@ -21,6 +21,7 @@
 //
 // Every wait on an mbarrier is bounded: when one runs out, the kernel raises an error flag in global memory, every role
 // leaves its loop, TMEM is released and the kernel returns; the host reports SS2D_ECUDA on the next status query.
+#include "activations.cuh"
 #include "tc05.cuh"
 
 namespace ss2d {
@@ -34,31 +35,6 @@ constexpr int kHC = 64;            // hidden units per chunk = N of GEMM 1, K of
 constexpr int kEpiWarps = 16;
 constexpr int kFirstEpiWarp = 4;   // warps 0..3: TMA producer, GEMM 1 issuer, GEMM 2 issuer, (spare)
 constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
-// ---- GELU (erf form) on the FMA pipe -----------------------------------------------------------------------------------
-// gelu(v) = v * Phi(v), Phi(v) = 1/2 + z P(z^2) with z = v / sqrt 2 and P an even polynomial of degree 12 fitted to
-// erf(z) / (2 z) on |z| <= 3.  The final fused multiply-add saturates to [0, 1], which is Phi's range; beyond the fitted
-// range P(t) >= 1 / (2 sqrt t) for every t > 9 (its leading coefficient is positive), so |z P| >= 1/2 there and the result
-// is exactly 0 or 1 without a clamp on the argument.  |gelu error| <= 7.5e-4 for every v, a fifth of a bf16 step at 1.
-__device__ __forceinline__ float fma_sat(float a, float b, float c) {
-    float d;
-    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
-__device__ __forceinline__ float2 gelu_pair_poly(float2 v) {
-    const float kC = 0.70710678118654752f;
-    const float2 z = __fmul2_rn(v, make_float2(kC, kC));
-    const float2 t = __fmul2_rn(z, z);
-    float2 p = make_float2(1.840303185e-06f, 1.840303185e-06f);
-    p = __ffma2_rn(p, t, make_float2(-6.794340152e-05f, -6.794340152e-05f));
-    p = __ffma2_rn(p, t, make_float2(1.058246824e-03f, 1.058246824e-03f));
-    p = __ffma2_rn(p, t, make_float2(-9.187800810e-03f, -9.187800810e-03f));
-    p = __ffma2_rn(p, t, make_float2(4.991913959e-02f, 4.991913959e-02f));
-    p = __ffma2_rn(p, t, make_float2(-1.834703386e-01f, -1.834703386e-01f));
-    p = __ffma2_rn(p, t, make_float2(5.632318258e-01f, 5.632318258e-01f));
-    const float2 phi = make_float2(fma_sat(p.x, z.x, 0.5f), fma_sat(p.y, z.y, 0.5f));
-    return __fmul2_rn(v, phi);
-}
-
 struct MlpArgs {
     const float* b1;
     void* y;

@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(128, 4) stem_conv_norm_act_kernel(const StemAr
                 v.x = fmaf((acc[c].x - mean) * rstd, bh[C0 + 2 * c], bh[2 * C0 + 2 * c]);
                 v.y = fmaf((acc[c].y - mean) * rstd, bh[C0 + 2 * c + 1], bh[2 * C0 + 2 * c + 1]);
                 float2 r;
-                if constexpr (sizeof(T) == 2) r = gelu_pair_fast(v);
+                if constexpr (sizeof(T) == 2) r = gelu_pair_poly(v);
                 else r = make_float2(act_f<ACT_GELU>(v.x), act_f<ACT_GELU>(v.y));
                 o[2 * j] = r.x; o[2 * j + 1] = r.y;
             }
@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(512, 1) stem_mma_kernel(const StemArgs a, int 
                     float2 n2;
                     n2.x = fmaf((v[nt].x - mean) * rstd, lw.x, lb.x);
                     n2.y = fmaf((v[nt].y - mean) * rstd, lw.y, lb.y);
-                    const float2 r = gelu_pair_fast(n2);
+                    const float2 r = gelu_pair_poly(n2);
                     *reinterpret_cast<uint32_t*>(out + nt * 8) = Half2Of<T>::pack(r.x, r.y);
                 }
             }
