@@ -183,35 +183,73 @@ __global__ void __launch_bounds__(256, PV == 8 ? 2 : 3) dwconv3x3_strip_kernel(c
         for (int q = 0; q < PV; ++q) wv[q + 1] = v[q];
     };
 
-    float win[3][PV + 2];
-    open_row(0, win[0]);
-    open_row(1, win[1]);
+    if constexpr (PV >= 2) {
+        // Packed form: two neighbouring output columns share every instruction (FFMA2).  A window row is kept as pairs
+        // at both alignments - (0,1)(2,3).. for the taps dx = 0 and 2, (1,2)(3,4).. for dx = 1 - so that no pair has to
+        // be assembled inside the tap loop; the sums run in the same order as the scalar form (same results).
+        constexpr int NE = PV / 2 + 1, NO = PV / 2;
+        float2 we[3][NE], wo[3][NO];
+        auto open_pairs = [&](int j, int slot) {
+            float wv[PV + 2];
+            open_row(j, wv);
 #pragma unroll
-    for (int j = 0; j < KR; ++j) {
-        open_row(j + 2, win[(j + 2) % 3]);
-        if (r0 + j < H && valid) {
-            float o[PV];
+            for (int q = 0; q < NE; ++q) we[slot][q] = make_float2(wv[2 * q], wv[2 * q + 1]);
 #pragma unroll
-            for (int c = 0; c < PV; ++c) {
-                float acc = b;
+            for (int q = 0; q < NO; ++q) wo[slot][q] = make_float2(wv[2 * q + 1], wv[2 * q + 2]);
+        };
+        open_pairs(0, 0);
+        open_pairs(1, 1);
 #pragma unroll
-                for (int dy = 0; dy < 3; ++dy)
+        for (int j = 0; j < KR; ++j) {
+            open_pairs(j + 2, (j + 2) % 3);
+            if (r0 + j < H && valid) {
+                float2 acc[PV / 2];
 #pragma unroll
-                    for (int dx = 0; dx < 3; ++dx) acc = fmaf(k[dy * 3 + dx], win[(j + dy) % 3][c + dx], acc);
-                o[c] = acc;
-            }
-            if constexpr (sizeof(T) == 2 && PV >= 2) {
-                // conv result rounded to the storage type (as the library convolution returns it), then the activation
+                for (int c = 0; c < PV / 2; ++c) acc[c] = make_float2(b, b);
 #pragma unroll
-                for (int c = 0; c < PV; c += 2) {
-                    const float2 q = Half2Of<T>::unpack(Half2Of<T>::pack(o[c], o[c + 1]));
-                    o[c] = act_f<ACT>(q.x); o[c + 1] = act_f<ACT>(q.y);
+                for (int dy = 0; dy < 3; ++dy) {
+                    const int sl = (j + dy) % 3;
+#pragma unroll
+                    for (int dx = 0; dx < 3; ++dx) {
+                        const float2 kk = make_float2(k[dy * 3 + dx], k[dy * 3 + dx]);
+#pragma unroll
+                        for (int c = 0; c < PV / 2; ++c)
+                            acc[c] = __ffma2_rn(kk, dx == 1 ? wo[sl][c] : we[sl][c + dx / 2], acc[c]);
+                    }
                 }
-            } else {
+                float o[PV];
 #pragma unroll
-                for (int c = 0; c < PV; ++c) o[c] = act_f<ACT>(round_to<T>(o[c]));
+                for (int c = 0; c < PV / 2; ++c) {
+                    float2 q = acc[c];
+                    // conv result rounded to the storage type (as the library convolution returns it), then the activation
+                    if constexpr (sizeof(T) == 2) q = Half2Of<T>::unpack(Half2Of<T>::pack(q.x, q.y));
+                    if constexpr (ACT == ACT_SILU && sizeof(T) == 2) q = silu_pair_fast(q);
+                    else { q.x = act_f<ACT>(q.x); q.y = act_f<ACT>(q.y); }
+                    o[2 * c] = q.x; o[2 * c + 1] = q.y;
+                }
+                VT::store(py + (long long)(r0 + j) * W, o);
             }
-            VT::store(py + (long long)(r0 + j) * W, o);
+        }
+    } else {
+        float win[3][PV + 2];
+        open_row(0, win[0]);
+        open_row(1, win[1]);
+#pragma unroll
+        for (int j = 0; j < KR; ++j) {
+            open_row(j + 2, win[(j + 2) % 3]);
+            if (r0 + j < H && valid) {
+                float o[PV];
+#pragma unroll
+                for (int c = 0; c < PV; ++c) {
+                    float acc = b;
+#pragma unroll
+                    for (int dy = 0; dy < 3; ++dy)
+#pragma unroll
+                        for (int dx = 0; dx < 3; ++dx) acc = fmaf(k[dy * 3 + dx], win[(j + dy) % 3][c + dx], acc);
+                    o[c] = act_f<ACT>(round_to<T>(acc));
+                }
+                VT::store(py + (long long)(r0 + j) * W, o);
+            }
         }
     }
 }
