@@ -232,3 +232,32 @@ def test_checkpoint_key_normalisation():
         "layers.0.blocks.0.op.A_logs"}
     same = normalize_state_dict(new)
     assert set(same) == set(new)
+
+
+def test_tensor_core_planners_answer_without_a_gpu():
+    """`ss2d_linear_supported` / `ss2d_mlp_supported` decide from the parameter block alone: what the tcgen05 kernels take,
+    what goes to the library GEMM; nothing is launched."""
+    import torch
+    from vmamba_b200 import ops
+    before = _lib.launch_count()
+    bf = torch.bfloat16
+    assert ops.linear_supported(32, 96, 128 * 3136, bf)            # x_proj of VMamba-T stage 0
+    assert ops.linear_supported(56, 192, 128 * 784, torch.float16)
+    assert ops.linear_supported(104, 384, 128 * 196, bf)
+    assert not ops.linear_supported(200, 768, 128 * 49, bf)        # stage 3: the stacked weights leave no room for the ring
+    assert not ops.linear_supported(32, 96, 1001, bf)              # rows not a multiple of 16 bytes
+    assert not ops.linear_supported(32, 96, 1024, torch.float32)
+    assert ops.mlp_supported(96, 384, 128 * 3136, bf)
+    assert not ops.mlp_supported(192, 768, 128 * 784, bf)
+    L = _lib.lib()
+    assert L.ss2d_linear_fwd(None, None) == -1 and L.ss2d_linear_supported(None) == -1
+    p = _lib.LinearParams()
+    assert L.ss2d_linear_fwd(p, None) == -1                        # null tensors
+    assert _lib.launch_count() == before
+
+
+def test_accelerate_refuses_modules_that_are_not_on_a_gpu():
+    import torch
+    import vmamba_b200 as vb
+    with pytest.raises(RuntimeError, match="CUDA"):
+        vb.accelerate(torch.nn.Linear(4, 4))
