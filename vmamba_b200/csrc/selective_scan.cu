@@ -345,7 +345,7 @@ static int launch_rows(const ScanArgs& a, cudaStream_t st) {
 }
 
 // The lanes-are-rows kernel takes a problem when its rows come in whole groups of 32 per (image, group), every tensor
-// allows pieces of at least 8 bytes, each row has its own delta row, and there are enough rows to fill the GPU with warps.
+// allows pieces of at least 8 bytes, each row has its own delta row, and there are enough rows (below).
 template <typename Tin, typename Tout, int EPP>
 static int rows_by_state(const ScanArgs& a, cudaStream_t st) {
     if (a.dstate == 16) return launch_rows<Tin, Tout, 16, EPP>(a, st);
@@ -359,7 +359,10 @@ static int try_rows(const ScanArgs& a, int vec, cudaStream_t st, bool& taken) {
     // d_state 1: short rows only (bf16, fraction of the copy bandwidth, this kernel against the warp-per-row one: 0.42 / 0.35
     // at L = 196, 0.42 / 0.54 at L = 784; the warp-per-row kernel reaches 0.8 from L = 3136 up)
     if (a.dstate == 1 ? a.seqlen > 256 : (a.dstate != 4 && a.dstate != 8 && a.dstate != 16)) return SS2D_OK;
-    if (vec < 4 || a.dratio != 1 || a.group_size % 32 != 0 || a.rows < 32LL * 148 * 8 || !rows_kernels_enabled()) return SS2D_OK;
+    // enough rows to fill the GPU with warps of 32 rows.  Measured crossover against the warp-per-row kernels (d_state 16,
+    // bf16): 12 288 rows tie, 26 112 rows 0.105 against 0.067 of the copy bandwidth, 6 144 rows 0.027 against 0.058
+    const long long min_rows = 32LL * 148 * (a.dstate == 1 ? 8 : 3);
+    if (vec < 4 || a.dratio != 1 || a.group_size % 32 != 0 || a.rows < min_rows || !rows_kernels_enabled()) return SS2D_OK;
     taken = true;
     if constexpr (sizeof(Tin) == 2) {
         if (vec >= 8) return rows_by_state<Tin, Tout, 8>(a, st);
