@@ -609,6 +609,217 @@ __global__ void __launch_bounds__(kBwdRowsWarps * 32, 4) selscan_bwd_rows_kernel
     rr[0] = dA_acc; rr[1] = dD_acc; rr[2] = db_acc;
 }
 
+// d_state 4 / 8 / 16 with many rows and the forward call's checkpoints: lanes are rows, as above, with the NS states of
+// a row in registers.  Per chunk of 128 elements a forward sweep leaves the NS states in front of tiles 1..7 in shared
+// memory; a tile is then taken state by state (forward over its 16 elements with the decays and states kept in
+// registers, then backward), du / ddelta accumulating over the states in registers, the rows' dB / dC terms of one
+// state going through two shared tiles whose columns are summed by the warp.  u, dout, the step sizes and the
+// accumulators of the tile stay in registers, so that the shared-memory traffic per (element, state) is the two
+// broadcast loads of B and C, two stores and the column sums.
+template <int NS> struct BwdRowsN {
+    static constexpr int kFloatsPerWarp = 5 * kBwdTile * kBwdPitch + 7 * NS * 32 + 2 * NS * kBwdTile;
+};
+
+template <typename Tin, typename Tg, int NS>
+__global__ void __launch_bounds__(kBwdRowsWarps * 32, 2) selscan_bwd_rows_nx_kernel(const BwdArgs a) {
+    extern __shared__ float sm[];
+    constexpr int T = kBwdTile, P = kBwdPitch, PE = 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* su = sm + (size_t)warp * BwdRowsN<NS>::kFloatsPerWarp;   // u, then du
+    float* sd = su + T * P;                                    // delta, then ddelta
+    float* sg = sd + T * P;                                    // dout, then the derivative of the softplus
+    float* sb = sg + T * P;                                    // the rows' dB terms of one state
+    float* sc = sb + T * P;                                    // the rows' dC terms of one state
+    float* hs = sc + T * P;                                    // [tile 1..7 of the chunk][state][row]
+    float* sB = hs + 7 * NS * 32;                              // [state][element]
+    float* sC = sB + NS * T;
+    const int64_t row0 = ((int64_t)blockIdx.x * kBwdRowsWarps + warp) * 32;
+    const int L = (int)a.seqlen;
+    if (row0 >= a.rows) return;
+    const int64_t b = row0 / a.dim, r0 = row0 % a.dim, k = r0 / a.group_size, part = (r0 - k * a.group_size) / 32;
+    const int64_t r = r0 + lane;
+    const Tin* __restrict__ u = (const Tin*)a.u + b * a.u_bs + r0 * a.u_ds;
+    const Tin* __restrict__ dt = (const Tin*)a.delta + b * a.d_bs + r0 * a.d_ds;
+    const Tg* __restrict__ gp = (const Tg*)a.dout + b * a.g_bs + r0 * a.g_ds;
+    const Tin* __restrict__ Bm = (const Tin*)a.B + b * a.B_bs + k * a.B_gs;
+    const Tin* __restrict__ Cm = (const Tin*)a.C + b * a.C_bs + k * a.C_gs;
+    Tin* __restrict__ du = (Tin*)a.du + (b * a.dim + r0) * L;
+    Tin* __restrict__ dd = (Tin*)a.ddelta + (b * a.dim + r0) * L;
+    float* __restrict__ bc_out = a.bcpart + (((size_t)b * a.n_groups + k) * a.parts + part) * 2 * (size_t)NS * L;
+    const float* __restrict__ ck = a.ckpt + (b * a.dim + r) * a.nck * NS;
+    float A2[NS], e_carry[NS], dA_acc[NS];
+#pragma unroll
+    for (int n = 0; n < NS; ++n) { A2[n] = __ldg(a.A + r * NS + n) * kLog2e; e_carry[n] = 0.f; dA_acc[n] = 0.f; }
+    const bool has_D = a.D != nullptr;
+    const float Dv = has_D ? __ldg(a.D + r) : 0.f;
+    const float bias = a.bias ? __ldg(a.bias + r) : 0.f;
+    const bool sp = a.softplus != 0;
+    using VI = Vec<Tin, PE>;
+
+    auto stage_in = [&](auto* src, int64_t stride, int t0, float* dst) {
+        using E = std::remove_cv_t<std::remove_pointer_t<decltype(src)>>;
+#pragma unroll
+        for (int j = 0; j < T / PE; ++j) {
+            const int idx = j * 32 + lane, rr = idx / (T / PE), piece = idx - rr * (T / PE);
+            const int pos = t0 + piece * PE;
+            float v[PE];
+            if (pos < L) Vec<E, PE>::load(src + rr * stride + pos, v);
+            else {
+#pragma unroll
+                for (int e = 0; e < PE; ++e) v[e] = 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < PE; ++e) dst[(piece * PE + e) * P + rr] = v[e];
+        }
+    };
+    // the NS rows of B (and of C) for a tile: 4 pieces of four elements per row
+    auto stage_bc = [&](int t0, bool with_c) {
+        constexpr int PIECES = NS * (T / PE);
+        for (int idx = lane; idx < (with_c ? 2 : 1) * PIECES; idx += 32) {
+            const int which = idx / PIECES, rem = idx - which * PIECES, n = rem / (T / PE), piece = rem - n * (T / PE);
+            const int pos = t0 + piece * PE;
+            const Tin* src = which ? Cm + n * a.C_ss : Bm + n * a.B_ss;
+            float v[PE];
+            if (pos < L) VI::load(src + pos, v);
+            else {
+#pragma unroll
+                for (int e = 0; e < PE; ++e) v[e] = 0.f;
+            }
+            float* dst = (which ? sC : sB) + n * T + piece * PE;
+#pragma unroll
+            for (int e = 0; e < PE; ++e) dst[e] = v[e];
+        }
+    };
+    auto stage_out = [&](const float* src, Tin* dst_rows, int t0) {
+#pragma unroll
+        for (int j = 0; j < T / PE; ++j) {
+            const int idx = j * 32 + lane, rr = idx / (T / PE), piece = idx - rr * (T / PE);
+            const int pos = t0 + piece * PE;
+            if (pos < L) {
+                float v[PE];
+#pragma unroll
+                for (int e = 0; e < PE; ++e) v[e] = src[(piece * PE + e) * P + rr];
+                VI::store(dst_rows + (int64_t)rr * L + pos, v);
+            }
+        }
+    };
+
+    float dD_acc = 0.f, db_acc = 0.f;
+    for (int c = (int)a.nck - 1; c >= 0; --c) {
+        const int c0 = c * 128;
+        const int ntiles = min(8, (L - c0 + T - 1) / T);
+        // ---- forward sweep over the chunk: the states in front of tiles 1 .. ntiles-1
+        {
+            float h[NS];
+#pragma unroll
+            for (int n = 0; n < NS; ++n) h[n] = ck[c * NS + n];
+            for (int j = 0; j + 1 < ntiles; ++j) {
+                const int t0 = c0 + j * T;                     // a whole tile: it is not the last of the row
+                stage_in(u, a.u_ds, t0, su);
+                stage_in(dt, a.d_ds, t0, sd);
+                stage_bc(t0, false);
+                __syncwarp();
+#pragma unroll 2
+                for (int t = 0; t < T; ++t) {
+                    float d = sd[t * P + lane] + bias;
+                    if (sp) d = softplus_fast(d);
+                    const float dux = d * su[t * P + lane];
+#pragma unroll
+                    for (int n = 0; n < NS; ++n) h[n] = fmaf(decay_fast(d, A2[n]), h[n], dux * sB[n * T + t]);
+                }
+#pragma unroll
+                for (int n = 0; n < NS; ++n) hs[(j * NS + n) * 32 + lane] = h[n];
+                __syncwarp();
+            }
+        }
+        // ---- the tiles of the chunk, last first
+        for (int j = ntiles - 1; j >= 0; --j) {
+            const int t0 = c0 + j * T;
+            stage_in(u, a.u_ds, t0, su);
+            stage_in(dt, a.d_ds, t0, sd);
+            stage_in(gp, a.g_ds, t0, sg);
+            stage_bc(t0, true);
+            __syncwarp();
+            float uv[T], gv[T], dv[T], du_acc[T], ddl[T];
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+                const bool ok = t0 + t < L;                    // beyond the row: a = 1, everything else 0
+                float x = sd[t * P + lane] + bias, g1 = 1.f;
+                if (sp) softplus_and_grad(x, x, g1);
+                dv[t] = ok ? x : 0.f;
+                uv[t] = su[t * P + lane];
+                gv[t] = sg[t * P + lane];
+                sg[t * P + lane] = ok ? g1 : 0.f;               // read back when ddelta is complete
+                du_acc[t] = has_D ? gv[t] * Dv : 0.f;
+                ddl[t] = 0.f;
+                dD_acc = fmaf(gv[t], uv[t], dD_acc);
+            }
+            // One state per iteration, NOT unrolled (sixteen copies of the body do not fit the instruction cache: the
+            // unrolled form ran four times slower).  The per-state registers are used at index 0 and the three arrays
+            // rotate by one place per iteration, so that they are back in order after NS iterations.
+#pragma unroll 1
+            for (int n = 0; n < NS; ++n) {
+                const float A2n = A2[0], An = A2n * kLn2;
+                const float hstart = j == 0 ? ck[c * NS + n] : hs[((j - 1) * NS + n) * 32 + lane];
+                const float* __restrict__ Bn = sB + n * T;
+                const float* __restrict__ Cn = sC + n * T;
+                float av[T], hl[T];
+                float h = hstart;
+#pragma unroll
+                for (int t = 0; t < T; ++t) {
+                    av[t] = decay_fast(dv[t], A2n);
+                    h = fmaf(av[t], h, dv[t] * uv[t] * Bn[t]);
+                    hl[t] = h;
+                }
+                float e = e_carry[0], dA_loc = 0.f;
+#pragma unroll
+                for (int t = T - 1; t >= 0; --t) {
+                    const float Bt = Bn[t], cg = Cn[t] * gv[t];
+                    const float dh = cg + e;
+                    e = fmaf(av[t], e, av[t] * cg);               // one fused multiply-add on the chain
+                    const float hprev = t == 0 ? hstart : hl[t > 0 ? t - 1 : 0];
+                    const float dhd = dh * dv[t];
+                    const float tt = av[t] * hprev;
+                    ddl[t] = fmaf(dh, fmaf(An, tt, Bt * uv[t]), ddl[t]);
+                    du_acc[t] = fmaf(dhd, Bt, du_acc[t]);
+                    sb[t * P + lane] = dhd * uv[t];
+                    sc[t * P + lane] = gv[t] * hl[t];
+                    dA_loc = fmaf(dhd, tt, dA_loc);
+                }
+                const float dA_n = dA_acc[0] + dA_loc;
+#pragma unroll
+                for (int i = 0; i + 1 < NS; ++i) { A2[i] = A2[i + 1]; e_carry[i] = e_carry[i + 1]; dA_acc[i] = dA_acc[i + 1]; }
+                A2[NS - 1] = A2n; e_carry[NS - 1] = e; dA_acc[NS - 1] = dA_n;
+                __syncwarp();
+                {   // sums over the 32 rows: lanes 0..15 the dB of element lane, lanes 16..31 the dC of element lane - 16
+                    const int el = lane & 15;
+                    const float* src = (lane < 16 ? sb : sc) + el * P;
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int rr = 0; rr < 32; ++rr) acc[rr & 3] += src[rr];
+                    if (t0 + el < L) bc_out[((size_t)(lane >> 4) * NS + n) * L + t0 + el] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+                }
+                __syncwarp();
+            }
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+                const float v = ddl[t] * sg[t * P + lane];
+                db_acc += v;
+                su[t * P + lane] = du_acc[t];
+                sd[t * P + lane] = v;
+            }
+            __syncwarp();
+            stage_out(su, du, t0);
+            stage_out(sd, dd, t0);
+            __syncwarp();
+        }
+    }
+    float* rr = a.rowred + (b * a.dim + r) * (NS + 2);
+#pragma unroll
+    for (int n = 0; n < NS; ++n) rr[n] = dA_acc[n];
+    rr[NS] = dD_acc; rr[NS + 1] = db_acc;
+}
+
 // Folds the partials: dA / dD / dbias over the batch, dB / dC over the CTAs of a group (and rounds
 // them to the storage type).  One thread per output element, fixed summation order.
 template <typename Tin>
@@ -718,9 +929,18 @@ static int plan_bwd(const ss2d_scan_bwd_params* p, BwdPlan& c) {
     // L = 3136, 36 864 rows 0.99 against 1.11 ms; 49 152 rows of 196 elements 0.095 against 0.158 ms)
     c.rows = p->dstate == 1 && p->checkpoints != nullptr && gs % 32 == 0 && p->delta_ratio <= 1 && c.vec >= 4 &&
              p->batch * p->dim >= 32LL * 148 * 7 && rows_kernels_enabled();
+    // the same form for d_state 4 / 8 / 16.  Measured (d_state 16, bf16): 15-20 ms against 35-47 ms of the warp-per-row kernel
+    // on 2 GB of rows; 57 against 115 ms on 6 528 rows of 65 536 elements, where 1.4 warps per SM walk at their own latency
+    const bool rows_nx = (p->dstate == 4 || p->dstate == 8 || p->dstate == 16) && p->checkpoints != nullptr && gs % 32 == 0 &&
+                         p->delta_ratio <= 1 && c.vec >= 4 && p->batch * p->dim >= 32LL * 148 && rows_kernels_enabled();
     if (c.rows) {
         c.parts = (int)(gs / 32);
         c.smem = (size_t)kBwdRowsWarps * kBwdFloatsPerWarp * sizeof(float);
+    } else if (rows_nx) {
+        c.rows = true;
+        c.parts = (int)(gs / 32);
+        const int per_warp = p->dstate == 16 ? BwdRowsN<16>::kFloatsPerWarp : p->dstate == 8 ? BwdRowsN<8>::kFloatsPerWarp : BwdRowsN<4>::kFloatsPerWarp;
+        c.smem = (size_t)kBwdRowsWarps * per_warp * sizeof(float);
     }
     c.rowred_floats = p->batch * p->dim * (p->dstate + 2);
     c.ws_floats = c.rowred_floats + p->batch * p->n_groups * c.parts * 2 * p->dstate * L;
@@ -751,7 +971,10 @@ static int launch_bwd(const BwdArgs& a, const BwdPlan& c, int64_t ctas, cudaStre
 
 template <typename Tin, typename Tg>
 static int launch_bwd_rows(const BwdArgs& a, const BwdPlan& c, cudaStream_t st) {
-    auto kern = selscan_bwd_rows_kernel<Tin, Tg>;
+    void (*kern)(const BwdArgs) = selscan_bwd_rows_kernel<Tin, Tg>;
+    if (a.N == 16) kern = selscan_bwd_rows_nx_kernel<Tin, Tg, 16>;
+    else if (a.N == 8) kern = selscan_bwd_rows_nx_kernel<Tin, Tg, 8>;
+    else if (a.N == 4) kern = selscan_bwd_rows_nx_kernel<Tin, Tg, 4>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem) != cudaSuccess) return SS2D_ECUDA;
     const int64_t warps = a.rows / 32;
     const int64_t ctas = (warps + kBwdRowsWarps - 1) / kBwdRowsWarps;
