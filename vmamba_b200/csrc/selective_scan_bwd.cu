@@ -708,6 +708,18 @@ __global__ void __launch_bounds__(kBwdRowsWarps * 32, 2) selscan_bwd_rows_nx_ker
     for (int c = (int)a.nck - 1; c >= 0; --c) {
         const int c0 = c * 128;
         const int ntiles = min(8, (L - c0 + T - 1) / T);
+        if (c > 0) {     // the chunk in front of this one, on its way into L2 while this one is worked on (a row per lane)
+            const char* pu = reinterpret_cast<const char*>(u + lane * a.u_ds + c0 - 128);
+            const char* pd = reinterpret_cast<const char*>(dt + lane * a.d_ds + c0 - 128);
+            const char* pg = reinterpret_cast<const char*>(gp + lane * a.g_ds + c0 - 128);
+#pragma unroll
+            for (int i = 0; i < 128 * (int)sizeof(Tin); i += 128) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(pu + i));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(pd + i));
+            }
+#pragma unroll
+            for (int i = 0; i < 128 * (int)sizeof(Tg); i += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(pg + i));
+        }
         // ---- forward sweep over the chunk: the states in front of tiles 1 .. ntiles-1
         {
             float h[NS];
@@ -740,19 +752,22 @@ __global__ void __launch_bounds__(kBwdRowsWarps * 32, 2) selscan_bwd_rows_nx_ker
             stage_in(gp, a.g_ds, t0, sg);
             stage_bc(t0, true);
             __syncwarp();
-            float uv[T], gv[T], dv[T], du_acc[T], ddl[T];
+            // Over the states of an element: S1 = sum of dh B, S2 = sum of dh A a h_prev.  Then du = d' S1 + g D and
+            // dd' = S2 + u S1.
+            float duv[T], gv[T], dv[T], S1[T], S2[T];
 #pragma unroll
             for (int t = 0; t < T; ++t) {
                 const bool ok = t0 + t < L;                    // beyond the row: a = 1, everything else 0
                 float x = sd[t * P + lane] + bias, g1 = 1.f;
                 if (sp) softplus_and_grad(x, x, g1);
                 dv[t] = ok ? x : 0.f;
-                uv[t] = su[t * P + lane];
+                const float uv = su[t * P + lane];
+                duv[t] = dv[t] * uv;
                 gv[t] = sg[t * P + lane];
                 sg[t * P + lane] = ok ? g1 : 0.f;               // read back when ddelta is complete
-                du_acc[t] = has_D ? gv[t] * Dv : 0.f;
-                ddl[t] = 0.f;
-                dD_acc = fmaf(gv[t], uv[t], dD_acc);
+                S1[t] = 0.f;
+                S2[t] = 0.f;
+                dD_acc = fmaf(gv[t], uv, dD_acc);
             }
             // One state per iteration, NOT unrolled (sixteen copies of the body do not fit the instruction cache: the
             // unrolled form ran four times slower).  The per-state registers are used at index 0 and the three arrays
@@ -768,23 +783,22 @@ __global__ void __launch_bounds__(kBwdRowsWarps * 32, 2) selscan_bwd_rows_nx_ker
 #pragma unroll
                 for (int t = 0; t < T; ++t) {
                     av[t] = decay_fast(dv[t], A2n);
-                    h = fmaf(av[t], h, dv[t] * uv[t] * Bn[t]);
+                    h = fmaf(av[t], h, duv[t] * Bn[t]);
                     hl[t] = h;
                 }
                 float e = e_carry[0], dA_loc = 0.f;
 #pragma unroll
                 for (int t = T - 1; t >= 0; --t) {
-                    const float Bt = Bn[t], cg = Cn[t] * gv[t];
+                    const float cg = Cn[t] * gv[t];
                     const float dh = cg + e;
                     e = fmaf(av[t], e, av[t] * cg);               // one fused multiply-add on the chain
                     const float hprev = t == 0 ? hstart : hl[t > 0 ? t - 1 : 0];
-                    const float dhd = dh * dv[t];
-                    const float tt = av[t] * hprev;
-                    ddl[t] = fmaf(dh, fmaf(An, tt, Bt * uv[t]), ddl[t]);
-                    du_acc[t] = fmaf(dhd, Bt, du_acc[t]);
-                    sb[t * P + lane] = dhd * uv[t];
+                    const float x = dh * (av[t] * hprev);
+                    S1[t] = fmaf(dh, Bn[t], S1[t]);
+                    S2[t] = fmaf(An, x, S2[t]);
+                    dA_loc = fmaf(dv[t], x, dA_loc);
+                    sb[t * P + lane] = dh * duv[t];
                     sc[t * P + lane] = gv[t] * hl[t];
-                    dA_loc = fmaf(dhd, tt, dA_loc);
                 }
                 const float dA_n = dA_acc[0] + dA_loc;
 #pragma unroll
@@ -803,9 +817,9 @@ __global__ void __launch_bounds__(kBwdRowsWarps * 32, 2) selscan_bwd_rows_nx_ker
             }
 #pragma unroll
             for (int t = 0; t < T; ++t) {
-                const float v = ddl[t] * sg[t * P + lane];
+                const float v = fmaf(su[t * P + lane], S1[t], S2[t]) * sg[t * P + lane];
                 db_acc += v;
-                su[t * P + lane] = du_acc[t];
+                su[t * P + lane] = fmaf(dv[t], S1[t], has_D ? gv[t] * Dv : 0.f);
                 sd[t * P + lane] = v;
             }
             __syncwarp();
