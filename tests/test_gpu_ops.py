@@ -878,6 +878,31 @@ def test_vmamba_tiny_fp16_forward(vb):
     assert float((got - ref).abs().max() / ref.abs().max()) <= 5e-3
 
 
+@pytest.mark.gpu
+def test_config1_full_size_properties(vb):
+    """The headline workload at its full size (VMamba-T, 128 images of 224 x 224, bf16), through properties that do
+    not depend on the size: a second run and the replayed graph return the same bits; every image's logits are what
+    the same image gets in a batch of 16 (the batch is sharded by image, nothing crosses images), within the
+    rounding of the 16-bit maps, and the arg-max of a clearly decided image does not move."""
+    import bench
+    from vmamba_b200.backbone import VSSMInfer
+    m = VSSMInfer.from_state_dict(bench.synthetic_state_dict(0), dtype=torch.bfloat16)
+    img = torch.randn((128, 3, 224, 224), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)).to(torch.bfloat16)
+    full = m(img)
+    assert full.shape == (128, 1000) and bool(torch.isfinite(full.float()).all())
+    assert torch.equal(m(img), full)
+    runner = vb.GraphedBackbone(m, (128, 3, 224, 224))
+    assert torch.equal(runner(img), full)
+    scale = float(full.float().abs().max())
+    for i0 in (0, 48, 112):
+        part = m(img[i0:i0 + 16]).float()
+        ref = full[i0:i0 + 16].float()
+        assert float((part - ref).abs().max()) <= 2e-2 * scale, i0
+        top2 = ref.topk(2, dim=1).values
+        clear = (top2[:, 0] - top2[:, 1]) > 4e-2 * scale
+        assert bool((part.argmax(1) == ref.argmax(1))[clear].all()), i0
+
+
 # ------------------------------------------------------------------ fused MLP (tcgen05)
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["bf16", "f16"])
