@@ -219,9 +219,10 @@ class VSSMInfer:
             m, mb = pend
             d = self.down[i]
             if d is not None:
-                # downsample v3 (vmamba.py:1964-1971): x += m + bias and the pixel-major 16-bit input of the
-                # strided convolution in one pass; its bias + LayerNorm + the way back to planes in another
-                xin = ops.planes_to_pixels(x, add=m, add_bias=mb, update=True, out_dtype=self.dtype)
+                # downsample v3 (vmamba.py:1964-1971): x + m + bias as the pixel-major 16-bit input of the strided
+                # convolution in one pass (the sum goes back into x only when the stage's map is asked for: the
+                # convolution's output replaces the residual stream); its bias + LayerNorm + the way back to planes in another
+                xin = ops.planes_to_pixels(x, add=m, add_bias=mb, update=want_features, out_dtype=self.dtype)
                 if want_features:
                     outs.append(x.clone())
                 x = ops.pixels_norm_to_planes(self._conv_s2(xin, d["w"]), d["bf"], d["nw"], d["nb"])
