@@ -612,10 +612,12 @@ __global__ void __launch_bounds__(kBwdRowsWarps * 32, 4) selscan_bwd_rows_kernel
 // d_state 4 / 8 / 16 with many rows and the forward call's checkpoints: lanes are rows, as above, with the NS states of
 // a row in registers.  Per chunk of 128 elements a forward sweep leaves the NS states in front of tiles 1..7 in shared
 // memory; a tile is then taken state by state (forward over its 16 elements with the decays and states kept in
-// registers, then backward), du / ddelta accumulating over the states in registers, the rows' dB / dC terms of one
-// state going through two shared tiles whose columns are summed by the warp.  u, dout, the step sizes and the
-// accumulators of the tile stay in registers, so that the shared-memory traffic per (element, state) is the two
-// broadcast loads of B and C, two stores and the column sums.
+// registers, then backward), two sums over the states (from which du and ddelta follow) accumulating in registers, the
+// rows' dB / dC terms of one state going through two shared tiles whose columns are summed by the warp.  dout, the step
+// sizes, their products with u and the two sums of the tile stay in registers, so that the shared-memory traffic per
+// (element, state) is the broadcast loads of B and C, two stores and the column sums.  That traffic and the two
+// transcendentals per (element, state) bound the kernel: a form with 8-element tiles and twice the warps per SM ran at
+// the same speed.
 template <int NS> struct BwdRowsN {
     static constexpr int kFloatsPerWarp = 5 * kBwdTile * kBwdPitch + 7 * NS * 32 + 2 * NS * kBwdTile;
 };
