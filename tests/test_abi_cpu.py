@@ -256,6 +256,43 @@ def test_tensor_core_planners_answer_without_a_gpu():
     assert _lib.launch_count() == before
 
 
+def test_backward_planner_picks_the_rows_kernels_by_row_count():
+    """`ss2d_selective_scan_bwd_workspace_bytes` is the planner's answer without a launch: the lanes-are-rows kernels
+    (one dB / dC partial per 32 rows of a group) are taken with the forward call's checkpoints and enough rows, the
+    warp-per-row kernels (a partial per CTA of 8 rows, d_state > 1) otherwise."""
+    L = _lib.lib()
+    dummy = 0x10000                       # any aligned non-null address: the planner only looks at alignment
+
+    def ws(batch, dim, N, seqlen, groups, ckpt):
+        p = _lib.ScanBwdParams()
+        for name in ("u", "delta", "A", "B", "C", "dout", "du", "ddelta", "dA", "dB", "dC"):
+            setattr(p, name, dummy)
+        p.in_dtype, p.dout_dtype, p.delta_softplus = 2, 0, 1          # bf16 rows, fp32 dout
+        p.batch, p.dim, p.dstate, p.seqlen, p.n_groups = batch, dim, N, seqlen, groups
+        p.u_batch_stride = p.delta_batch_stride = p.dout_batch_stride = dim * seqlen
+        p.u_dim_stride = p.delta_dim_stride = p.dout_dim_stride = seqlen
+        p.B_batch_stride = p.C_batch_stride = groups * N * seqlen
+        p.B_group_stride = p.C_group_stride = N * seqlen
+        p.B_state_stride = p.C_state_stride = seqlen
+        p.checkpoints = dummy if ckpt else None
+        return L.ss2d_selective_scan_bwd_workspace_bytes(p)
+
+    def expect(batch, dim, N, seqlen, groups, parts):
+        return 4 * (batch * dim * (N + 2) + batch * groups * parts * 2 * N * seqlen)
+
+    before = _lib.launch_count()
+    gs = 768
+    # d_state 16: 6144 rows with checkpoints -> a partial per 32 rows; without checkpoints or with too few rows -> per 8 rows
+    assert ws(2, 4 * gs, 16, 3136, 4, True) == expect(2, 4 * gs, 16, 3136, 4, gs // 32)
+    assert ws(2, 4 * gs, 16, 3136, 4, False) == expect(2, 4 * gs, 16, 3136, 4, gs // 8)
+    assert ws(1, 4 * gs, 16, 3136, 4, True) == expect(1, 4 * gs, 16, 3136, 4, gs // 8)
+    # d_state 1: from 33 152 rows up
+    assert ws(16, 4 * gs, 1, 784, 4, True) == expect(16, 4 * gs, 1, 784, 4, gs // 32)
+    assert ws(8, 4 * gs, 1, 784, 4, True) != expect(8, 4 * gs, 1, 784, 4, gs // 32)
+    assert ws(2, 4 * gs, 16, 0, 4, True) < 0                          # invalid sizes: no plan
+    assert _lib.launch_count() == before
+
+
 def test_accelerate_refuses_modules_that_are_not_on_a_gpu():
     import torch
     import vmamba_b200 as vb
