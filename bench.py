@@ -614,7 +614,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-modules", action="store_true", help="skip the leg that runs the staged reference modules")
     ap.add_argument("--config", type=int, default=1, choices=[1, 2, 3, 4],
-                    help="BASELINE configuration: 1 VMamba-T batch 128 per GPU (default); 2 VMamba-S, global batch 256 over the "
+                    help="benchmark configuration: 1 VMamba-T batch 128 per GPU (default); 2 VMamba-S, global batch 256 over the "
                          "ranks; 3 VMamba-B 1024x1024 dense-prediction backbone, global batch 16 over the ranks, four feature "
                          "maps read back; 4 the operator sweep with inputs sized by the 40 GB rule (1 GPU)")
     ap.add_argument("--model", default=None, help="vmamba_tiny_s1l8 (default) | vmamba_small_s2l15 | vmamba_base_s2l15")
